@@ -1,0 +1,132 @@
+"""The CPU oracle against the golden vectors produced by the reference's own Python functions
+(tests/golden/make_golden.py). Bit-exact for codes, scale bytes, phase bytes and RNG draws."""
+import numpy as np
+import pytest
+
+from conftest import golden
+
+import oracle
+
+
+def test_hash_uniform_and_rounding_modes():
+    g = golden("hash")
+    for i in range(4):
+        n, seed, step, off = (int(v) for v in g[f"args{i}"])
+        assert np.array_equal(oracle.hash_uniform(n, seed, step, off), g[f"u{i}"])
+    L = oracle.lib()
+    for mode, (j, k) in (("sr", (0, 1)), ("strat", (10, 16)), ("rtn", (0, 1))):   # bitrev(5 % 16, 4) = 10
+        got = np.array([L.blo_rounding_u(i, oracle.ROUNDING[mode], 11, 5, j, k) for i in range(64)], np.float32)
+        assert np.array_equal(got, g[f"round_{mode}"]), mode
+
+
+def test_e4m3_codec():
+    g = golden("e4m3")
+    enc = oracle.e4m3_encode(g["v"])
+    assert np.array_equal(enc, g["bytes"])
+    assert np.array_equal(oracle.e4m3_decode(enc), g["decoded"])
+    assert np.array_equal(oracle.e4m3_decode(np.arange(127, dtype=np.uint8)),
+                          np.array([oracle.lib().blo_e4m3_decode(i) for i in range(127)], np.float32))
+
+
+def test_quantize_rtn_ties_and_zero_blocks():
+    g = golden("quantize")
+    codes, scales, gs = oracle.quantize_rows(g["rtn_x"], None, "rtn")
+    assert np.float32(gs) == g["rtn_g"][0]
+    assert np.array_equal(scales, g["rtn_scales"])
+    assert np.array_equal(codes, g["rtn_codes"])
+    assert np.array_equal(oracle.dequantize(codes, scales, gs), g["rtn_deq_f32"])
+    codes2, scales2, _ = oracle.quantize_rows(g["rtn_x"] * np.float32(0.5), float(g["rtn_g"][0]), "rtn")
+    assert np.array_equal(codes2, g["rtng_codes"]) and np.array_equal(scales2, g["rtng_scales"])
+
+
+@pytest.mark.parametrize("seed", [1, 77])
+def test_quantize_sr(seed):
+    g = golden("quantize")
+    codes, scales, gs = oracle.quantize_rows(g["sr_x"], None, "sr", seed=seed)
+    assert np.float32(gs) == g[f"sr{seed}_g"][0]
+    assert np.array_equal(scales, g[f"sr{seed}_scales"])
+    assert np.array_equal(codes, g[f"sr{seed}_codes"])
+
+
+def test_blocked_scale_layout():
+    g = golden("quantize")
+    assert np.array_equal(oracle.to_blocked(g["blk_in"]), g["blk_out"])
+
+
+def test_hadamard_matrix():
+    assert np.array_equal(oracle.hadamard16(), golden("transposed")["H16"])
+
+
+@pytest.mark.parametrize("rot", ["rot", "plain"])
+@pytest.mark.parametrize("mode", ["rtn", "sr"])
+def test_transposed_quantizer(rot, mode):
+    g = golden("transposed")
+    H = g["H16"] if rot == "rot" else None
+    codes, scales = oracle.quantize_t(g["t_x"], H, float(g["t_bound"][0]), mode, seed=9)
+    assert np.array_equal(scales, g[f"t_{rot}_{mode}_scales"])
+    assert np.array_equal(codes, g[f"t_{rot}_{mode}_codes"])
+
+
+def test_weight_transpose_requantization():
+    g = golden("transposed")
+    codes, scales, gs = oracle.quantize_rows(g["w"], None, "rtn")
+    assert np.array_equal(codes, g["w_codes"]) and np.array_equal(scales, g["w_scales"])
+    assert np.float32(gs) == g["w_g"][0]
+    tc, ts = oracle.requantize_t(codes, scales, gs)
+    assert np.array_equal(ts, g["wt_scales"])
+    assert np.array_equal(tc, g["wt_codes"])
+
+
+def _step_names():
+    return [str(n) for n in golden("step")["names"]]
+
+
+@pytest.mark.parametrize("name", _step_names())
+def test_lattice_step(name):
+    g = golden("step")
+    bits = int(name.split("_")[0][1:])
+    rule = "fit_latent" if "fit_latent" in name else name.split("_")[1]
+    rounding = name.split("_")[-1]
+    trust_lr = 1.0 if rounding == "sr" else 0.0
+    phase = g[f"phase_in_b{bits}"] if bits else None
+    codes, ph, scales = oracle.lattice_step(
+        g["codes"], phase, g["scales"], float(g["g"][0]), g["D"], lr=float(g["lr"][0]), weight_decay=0.01,
+        phase_bits=bits, rounding=rounding, seed=7, step=3, scale_rule=rule,
+        trust=0.1 if trust_lr == 0.0 else 0.01, trust_lr=trust_lr)
+    assert np.array_equal(scales, g[name + "_scales"])
+    assert np.array_equal(codes, g[name + "_codes"])
+    if bits:
+        assert np.array_equal(ph, g[name + "_phase"])
+
+
+@pytest.mark.parametrize("kind", ["raw", "sign", "colnorm"])
+@pytest.mark.parametrize("clip", [1.0, 0.25])
+def test_direction_close_to_reference(kind, clip):
+    """The oracle fixes its own reduction order (documented in bl_oracle.c), so colnorm and clipped directions agree
+    with the reference to a few ulp rather than bit for bit; sign with clip >= 1 is exact."""
+    g = golden("direction")
+    D, _ = oracle.direction(g["G"], kind, clip)
+    ref = g[f"{kind}_clip{clip}"]
+    if kind == "sign" and clip >= 1.0:
+        assert np.array_equal(D, ref)
+    else:
+        np.testing.assert_allclose(D, ref, rtol=4e-7, atol=0.0)
+
+
+def test_direction_raw_clipped_big():
+    g = golden("direction")
+    D, (rho, div) = oracle.direction(g["G_big"], "raw", 1.0)
+    assert div > 1.0
+    np.testing.assert_allclose(D, g["raw_big"], rtol=4e-7, atol=0.0)
+
+
+def test_gemm_statement_matches_exact_route():
+    """dequantize-and-contract of bf16 operands reproduces the reference's exact-route outputs to bf16 rounding."""
+    import torch
+    g = golden("linear")
+    wd = oracle.dequantize(g["codes"], g["scales"], float(g["g"][0]))
+    wb = torch.from_numpy(wd).to(torch.bfloat16)
+    x = torch.from_numpy(g["x"]).to(torch.bfloat16)
+    y = oracle.gemm_bf16_nt(x.view(torch.int16).numpy().view(np.uint16), wb.view(torch.int16).numpy().view(np.uint16))
+    ref = g["y"]
+    assert np.linalg.norm(y - ref) / np.linalg.norm(ref) < 4e-3
