@@ -1,0 +1,307 @@
+"""Operator layer: the call sites of the reference's ``torch.ops.bitlattice.*`` operators (``bitlattice/_ops.py``,
+schemas in the reference's ``csrc/bindings.cpp:75-134``) bound to the C ABI of ``libbitlattice_b200.so``.
+
+Function names and argument meaning follow the reference so the layers above (tensor, backend, optimizer) read the
+same; tensors are allocated here with torch and handed to the library as raw pointers on the current CUDA stream.
+There is no CPU or PyTorch fallback: an input that is not a contiguous CUDA tensor of a supported shape raises.
+"""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from . import _C
+from . import formats as F
+
+HAVE_EXT = True            # the library is mandatory; importing this package fails without it (see _C.lib)
+
+_ROUNDING = {"sr": 0, "strat": 1, "rtn": 2}
+_RULE = {"fixed": 0, "fit": 1, "fit_latent": 2}
+_DIRECTION = {"raw": 0, "sign": 1, "colnorm": 2}
+
+
+def _require(t: torch.Tensor, name: str, dtype=None) -> torch.Tensor:
+    if not isinstance(t, torch.Tensor) or not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor (this build has no CPU path)")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise RuntimeError(f"{name} must be {dtype}, got {t.dtype}")
+    return t
+
+
+def _bytes(t: torch.Tensor) -> torch.Tensor:
+    return t if t.dtype == torch.uint8 else t.view(torch.uint8)
+
+
+def _is_nvfp4(fmt) -> bool:
+    fmt = F.get(fmt)
+    sc = fmt.scale
+    return fmt.kind == "table" and fmt.bits == 4 and sc.group == 16 and sc.dtype == "e4m3" and sc.global_scale
+
+
+def cuda_ok(fmt, rows: int, cols: int, device) -> bool:
+    """Whether the kernels take this tensor: NVFP4 on a CUDA device with rows made of 16-element groups."""
+    return torch.device(device).type == "cuda" and _is_nvfp4(fmt) and cols % 16 == 0
+
+
+def phase_container(phase_bits: int) -> int:
+    return 0 if phase_bits == 0 else 1 if phase_bits == 1 else 2 if phase_bits == 2 else 4 if phase_bits <= 4 else 8
+
+
+def phase_numel(n: int) -> int:
+    return math.ceil(n / 8) * 8
+
+
+def bitrev(v: int, bits: int) -> int:
+    r = 0
+    for _ in range(bits):
+        r = (r << 1) | (v & 1)
+        v >>= 1
+    return r
+
+
+def strat_args(rounding: str, step: int, strata: int) -> tuple[int, int]:
+    if rounding != "strat":
+        return 0, 1
+    bits = max(1, (strata - 1).bit_length())
+    k = 1 << bits
+    return bitrev(step % k, bits), k
+
+
+def kappa(trust: float, trust_lr: float, lr: float) -> float:
+    return trust if trust_lr <= 0 else min(trust, trust_lr * lr)
+
+
+# ------------------------------------------------------------------------------------------------ storage <-> dense
+
+def dequantize(packed, scales, global_scale, zeros, fmt, rows: int, cols: int, dtype=torch.bfloat16):
+    """Dense [rows, cols] tensor of the represented values (reference: bitlattice/_ops.py:55-61)."""
+    if zeros is not None or not _is_nvfp4(fmt):
+        raise RuntimeError("only NVFP4 tensors (no zero points) are built")
+    _require(packed, "packed", torch.uint8)
+    _require(scales, "scales")
+    _require(global_scale, "global_scale", torch.float32)
+    if dtype not in _C.DTYPE:
+        raise RuntimeError(f"dequantize to {dtype} is not built (float32, bfloat16, float16 are)")
+    out = torch.empty(rows, cols, dtype=dtype, device=packed.device)
+    _C.call("bl_nvfp4_dequantize", _C.ptr(packed), _C.ptr(scales), _C.ptr(global_scale), rows, cols, _C.ptr(out),
+            _C.DTYPE[dtype], _C.device_of(packed), _C.stream_of(packed))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ lattice update
+
+def step_quantized(packed, phase, scales, global_scale, zeros, D, fmt, rows: int, cols: int, *, lr: float,
+                   weight_decay: float, phase_bits: int, phase_cb: int, rounding: str, seed: int, step: int,
+                   strata: int, scale_rule: str, trust: float, trust_lr: float, offset: int = 0) -> torch.Tensor:
+    """In-place update of ``packed`` (and ``phase``) given the fp32 direction ``D``; returns the new scales tensor
+    (reference: bitlattice/_ops.py:76-86)."""
+    if zeros is not None or not _is_nvfp4(fmt):
+        raise RuntimeError("only NVFP4 tensors (no zero points) are built")
+    _require(packed, "packed", torch.uint8)
+    _require(scales, "scales")
+    _require(global_scale, "global_scale", torch.float32)
+    Df = D.reshape(-1).float().contiguous()
+    _require(Df, "D")
+    if Df.numel() != rows * cols:
+        raise RuntimeError("D: float32 [rows*cols]")
+    if phase_bits > 0:
+        _require(phase, "phase", torch.uint8)
+    new_scales = torch.empty_like(scales)
+    j, k = strat_args(rounding, step, strata)
+    _C.call("bl_nvfp4_step_quantized", _C.ptr(packed), _C.ptr(phase) if phase_bits > 0 else None, _C.ptr(scales),
+            _C.ptr(new_scales), _C.ptr(global_scale), _C.ptr(Df), rows, cols, int(offset) & 0xFFFFFFFFFFFFFFFF,
+            phase_bits, phase_cb, float(lr), float(1.0 - lr * weight_decay), _ROUNDING[rounding],
+            int(seed) & 0xFFFFFFFF, int(step) & 0xFFFFFFFF, j, k, _RULE[scale_rule],
+            float(kappa(trust, trust_lr, lr)), _C.device_of(packed), _C.stream_of(packed))
+    return new_scales
+
+
+_scratch: dict = {}
+
+
+def _scratch_for(device: torch.device, nbytes: int) -> torch.Tensor | None:
+    """A per-device scratch buffer that only grows (column statistics of the fused update)."""
+    if nbytes == 0:
+        return None
+    buf = _scratch.get(device)
+    if buf is None or buf.numel() < nbytes:
+        buf = _scratch[device] = torch.empty(nbytes, dtype=torch.uint8, device=device)
+    return buf
+
+
+def update_scratch_bytes(rows: int, cols: int, direction: str, clip: float) -> int:
+    return int(_C.lib().bl_update_scratch_bytes(rows, cols, _DIRECTION[direction], float(clip)))
+
+
+def lattice_update(packed, phase, scales, global_scale, zeros, G, fmt, rows: int, cols: int, *, lr: float,
+                   weight_decay: float, phase_bits: int, phase_cb: int, rounding: str, seed: int, step: int,
+                   strata: int, scale_rule: str, trust: float, trust_lr: float, direction: str, clip: float = 1.0,
+                   offset: int = 0, scratch: torch.Tensor | None = None) -> None:
+    """Direction + lattice step in one pass over the gradient ``G`` (bf16 / fp16 / fp32), everything in place,
+    scales included (reference: torch.ops.bitlattice.lattice_update, csrc/update.cpp:30-53)."""
+    if zeros is not None or not _is_nvfp4(fmt):
+        raise RuntimeError("only NVFP4 tensors (no zero points) are built")
+    if direction not in _DIRECTION:
+        raise RuntimeError(f"direction {direction!r} is outside this build (raw, sign, colnorm are built)")
+    _require(packed, "packed", torch.uint8)
+    _require(scales, "scales")
+    _require(global_scale, "global_scale", torch.float32)
+    _require(G, "gradient")
+    if G.dtype not in _C.DTYPE or G.numel() != rows * cols:
+        raise RuntimeError("gradient: bf16, fp16 or fp32 with rows*cols elements")
+    if phase_bits > 0:
+        _require(phase, "phase", torch.uint8)
+    need = update_scratch_bytes(rows, cols, direction, clip)
+    if scratch is None:
+        scratch = _scratch_for(packed.device, need)
+    j, k = strat_args(rounding, step, strata)
+    _C.call("bl_nvfp4_lattice_update", _C.ptr(packed), _C.ptr(phase) if phase_bits > 0 else None, _C.ptr(scales),
+            _C.ptr(global_scale), _C.ptr(G), _C.DTYPE[G.dtype], rows, cols, int(offset) & 0xFFFFFFFFFFFFFFFF,
+            phase_bits, phase_cb, float(lr), float(1.0 - lr * weight_decay), _ROUNDING[rounding],
+            int(seed) & 0xFFFFFFFF, int(step) & 0xFFFFFFFF, j, k, _RULE[scale_rule],
+            float(kappa(trust, trust_lr, lr)), _DIRECTION[direction], float(clip), _C.ptr(scratch),
+            scratch.numel() if scratch is not None else 0, _C.device_of(packed), _C.stream_of(packed))
+
+
+def direction(G, kind: str, r=None, c=None, k: int = 1, beta2: float = 0.95, block=0, ns_steps: int = 5,
+              ns_dtype: str = "bf16", sinkhorn_iters: int = 2, clip: float = 1.0, **unused) -> torch.Tensor:
+    """Update direction as float32 [rows, cols], RMS clipped to ``clip`` (reference: bitlattice/_ops.py:110-144).
+    'raw', 'sign' and 'colnorm' are built."""
+    if kind not in _DIRECTION:
+        raise RuntimeError(f"direction {kind!r} is outside this build (raw, sign, colnorm are built)")
+    G2 = G.reshape(1, -1) if G.dim() == 1 else G.reshape(G.shape[0], -1)
+    G2 = _require(G2.contiguous(), "gradient")
+    if G2.dtype not in _C.DTYPE:
+        G2 = G2.float()
+    rows, cols = G2.shape
+    D = torch.empty(rows, cols, dtype=torch.float32, device=G2.device)
+    scratch = _scratch_for(G2.device, update_scratch_bytes(rows, cols, kind, clip))
+    _C.call("bl_direction", _C.ptr(G2), _C.DTYPE[G2.dtype], rows, cols, _DIRECTION[kind], float(clip), _C.ptr(D),
+            _C.ptr(scratch), scratch.numel() if scratch is not None else 0, _C.device_of(G2), _C.stream_of(G2))
+    return D
+
+
+# ------------------------------------------------------------------------------------------------ operand quantizers
+
+def blocked_scale_bytes(rows: int, cols16: int) -> int:
+    return int(_C.lib().bl_blocked_scale_bytes(rows, cols16))
+
+
+def amax_global(x: torch.Tensor) -> torch.Tensor:
+    """fp32 [4]: [0] = max|x|, [1] = the per-tensor NVFP4 scale max(amax/(6*448), 1e-12)
+    (reference: bitlattice/backend.py:240-241)."""
+    _require(x, "x")
+    out = torch.empty(4, dtype=torch.float32, device=x.device)
+    _C.call("bl_nvfp4_amax", _C.ptr(x), _C.DTYPE[x.dtype], x.numel(), _C.ptr(out), _C.device_of(x), _C.stream_of(x))
+    return out
+
+
+def _scale_buffer(rows: int, cols16: int, blocked: bool, device) -> torch.Tensor:
+    if blocked:
+        return torch.empty(blocked_scale_bytes(rows, cols16), dtype=torch.uint8, device=device)
+    return torch.empty(rows, cols16, dtype=torch.uint8, device=device)
+
+
+def quantize_nvfp4(x: torch.Tensor, global_scale: torch.Tensor, seed: int = -1, step: int = 0, blocked: bool = False):
+    """x [rows, cols] -> (packed [rows, cols/2] uint8, scales). ``blocked``: scales in the GEMM's 128x4-tiled layout
+    (flat uint8), else float8_e4m3fn [rows, cols/16] (reference: torch.ops.bitlattice.quantize_nvfp4)."""
+    _require(x, "x")
+    _require(global_scale, "global_scale", torch.float32)
+    if x.dtype not in _C.DTYPE:
+        raise RuntimeError("x must be bf16, fp16 or fp32")
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    packed = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
+    scales = _scale_buffer(rows, cols // 16, blocked, x.device)
+    _C.call("bl_nvfp4_quantize", _C.ptr(x), _C.DTYPE[x.dtype], rows, cols, _C.ptr(global_scale), int(seed),
+            int(step) & 0xFFFFFFFF, _C.ptr(packed), _C.ptr(scales), int(blocked), _C.device_of(x), _C.stream_of(x))
+    return packed, scales if blocked else scales.view(torch.float8_e4m3fn)
+
+
+def quantize_nvfp4_t(x: torch.Tensor, hadamard: torch.Tensor | None, seed: int = -1, step: int = 0,
+                     global_scale: torch.Tensor | None = None, blocked: bool = False):
+    """x [M, K] -> NVFP4 of x^T (rotated by ``hadamard`` along M): (packed [K, M/2], scales, global [1])
+    (reference: torch.ops.bitlattice.quantize_nvfp4_t)."""
+    _require(x, "x")
+    if x.dim() != 2:
+        raise RuntimeError("x must be a contiguous 2-D CUDA tensor")
+    if x.dtype not in _C.DTYPE:
+        raise RuntimeError("x must be bf16, fp16 or fp32")
+    M, K = x.shape
+    if hadamard is not None:
+        _require(hadamard, "hadamard", torch.float32)
+        if hadamard.numel() != 256:
+            raise RuntimeError("hadamard must be a contiguous fp32 [16, 16] tensor")
+    packed = torch.empty(K, M // 2, dtype=torch.uint8, device=x.device)
+    scales = _scale_buffer(K, M // 16, blocked, x.device)
+    gout = torch.empty(1, dtype=torch.float32, device=x.device)
+    bound = amax = None
+    if global_scale is not None:
+        bound = _require(global_scale.to(torch.float32).reshape(1).contiguous(), "global_scale")
+    else:
+        amax = torch.empty(4, dtype=torch.float32, device=x.device)
+    _C.call("bl_nvfp4_quantize_t", _C.ptr(x), _C.DTYPE[x.dtype], M, K, _C.ptr(hadamard), int(seed),
+            int(step) & 0xFFFFFFFF, _C.ptr(bound), _C.ptr(amax), _C.ptr(packed), _C.ptr(scales), _C.ptr(gout),
+            int(blocked), _C.device_of(x), _C.stream_of(x))
+    return packed, scales if blocked else scales.view(torch.float8_e4m3fn), gout
+
+
+def requantize_nvfp4_t(packed: torch.Tensor, scales: torch.Tensor, global_scale: torch.Tensor, blocked: bool = False):
+    """NVFP4 W [N, K] -> NVFP4 of W^T: (packed [K, N/2], scales, global [1])
+    (reference: torch.ops.bitlattice.requantize_nvfp4_t)."""
+    _require(packed, "packed", torch.uint8)
+    _require(scales, "scales")
+    g = _require(global_scale.to(torch.float32).reshape(1).contiguous(), "global_scale")
+    N, K = packed.shape[0], packed.shape[1] * 2
+    out = torch.empty(K, N // 2, dtype=torch.uint8, device=packed.device)
+    osc = _scale_buffer(K, N // 16, blocked, packed.device)
+    gout = torch.empty(1, dtype=torch.float32, device=packed.device)
+    _C.call("bl_nvfp4_requantize_t", _C.ptr(packed), _C.ptr(scales), _C.ptr(g), N, K, _C.ptr(out), _C.ptr(osc),
+            _C.ptr(gout), int(blocked), _C.device_of(packed), _C.stream_of(packed))
+    return out, osc if blocked else osc.view(torch.float8_e4m3fn), gout
+
+
+def to_blocked(scales: torch.Tensor) -> torch.Tensor:
+    """[rows, cols16] scale bytes -> flat 128x4-tiled layout (reference: bitlattice/backend.py:179-188)."""
+    _require(scales, "scales")
+    rows, cols16 = scales.shape
+    out = torch.empty(blocked_scale_bytes(rows, cols16), dtype=torch.uint8, device=scales.device)
+    _C.call("bl_nvfp4_scales_to_blocked", _C.ptr(scales), rows, cols16, _C.ptr(out), _C.device_of(scales),
+            _C.stream_of(scales))
+    return out
+
+
+# ------------------------------------------------------------------------------------------------ GEMM
+
+def nvfp4_gemm(a_packed, a_sf, a_global, b_packed, b_sf, b_global, out_dtype=torch.bfloat16,
+               out: torch.Tensor | None = None) -> torch.Tensor:
+    """(A B^T) * ga * gb for NVFP4 A [M, K], B [N, K] with blocked scales; fp32 accumulation on FP4 tensor cores
+    (reference: bitlattice/backend.py:280-290)."""
+    _require(a_packed, "a_packed", torch.uint8)
+    _require(b_packed, "b_packed", torch.uint8)
+    _require(a_sf, "a_sf")
+    _require(b_sf, "b_sf")
+    M, K = a_packed.shape[0], a_packed.shape[1] * 2
+    N = b_packed.shape[0]
+    if b_packed.shape[1] * 2 != K:
+        raise RuntimeError(f"operand K mismatch: {K} vs {b_packed.shape[1] * 2}")
+    if a_sf.numel() < blocked_scale_bytes(M, K // 16) or b_sf.numel() < blocked_scale_bytes(N, K // 16):
+        raise RuntimeError("scale buffers are smaller than the blocked layout of their operands")
+    ga = _require(a_global.reshape(-1), "a_global", torch.float32)
+    gb = _require(b_global.reshape(-1), "b_global", torch.float32)
+    if out is None:
+        out = torch.empty(M, N, dtype=out_dtype, device=a_packed.device)
+    _C.call("bl_nvfp4_gemm", _C.ptr(a_packed), _C.ptr(a_sf), _C.ptr(ga), _C.ptr(b_packed), _C.ptr(b_sf), _C.ptr(gb),
+            M, N, K, _C.ptr(out), _C.DTYPE[out.dtype], out.stride(0), _C.device_of(a_packed), _C.stream_of(a_packed))
+    return out
+
+
+def gemm_status(device: int = 0) -> int:
+    """Device-side error code of the GEMM kernels since the last call (0: none); synchronizes the device."""
+    st = ctypes.c_int(0)
+    _C.call("bl_nvfp4_gemm_status", ctypes.byref(st), int(device))
+    return st.value

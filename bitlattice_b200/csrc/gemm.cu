@@ -1,0 +1,418 @@
+// Block-scaled NVFP4 GEMM on the 5th-generation tensor cores (tcgen05) of sm_100a.
+//
+//   out[m][n] = (ga * gb) * sum_k A[m][k] * B[n][k]
+//
+// A [M, K] and B [N, K] are K-major packed E2M1 codes with one UE4M3 scale per 16 elements of K (the scales in the
+// 128x4-tiled layout), ga / gb the fp32 per-tensor scales read on the device. This is the contraction the reference
+// delegates to cuBLASLt through torch._scaled_mm (bitlattice/backend.py:267-290); forward, input-gradient and
+// weight-gradient GEMMs of the layer are all of this form (bitlattice/backend.py:502-510, 606-624).
+//
+// Kernel structure (one CTA per 128 x BN output tile, 192 threads):
+//   warp 0      producer: TMA loads of the A and B code tiles (128-byte swizzle) and bulk copies of their scale
+//               blobs into a ring of shared-memory stages, signalled through mbarriers (full / empty)
+//   warp 1      MMA issuer: owns the tensor-memory allocation; per stage copies the scale blobs into tensor memory
+//               (tcgen05.cp) and issues four tcgen05.mma.kind::mxf4nvf4.block_scale (K = 64 each) accumulating in
+//               tensor memory; tcgen05.commit releases the stage and finally publishes the accumulator
+//   warps 2..5  epilogue: tcgen05.ld of the accumulator (each warp its 32-lane quarter), scale by ga*gb, convert and
+//               store
+// K per stage is 256 elements = one 128-byte swizzle row. Every wait on an mbarrier is bounded: on expiry the kernel
+// raises an error flag, lets all warps fall through to the common exit and frees its tensor memory.
+#include <cuda.h>
+
+#include <mutex>
+
+#include "common.cuh"
+
+namespace blb {
+
+constexpr int kBM = 128;          // rows of A per tile
+constexpr int kBK = 256;          // elements of K per stage (128 bytes of packed codes)
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kSpinLimit = 1u << 21;   // polls of one mbarrier wait before the kernel gives up
+
+__device__ int g_gemm_error = 0;  // 0 ok; otherwise the code of the wait that expired
+
+// ------------------------------------------------------------------------------------------------ PTX wrappers
+
+__device__ __forceinline__ uint32_t smem_u32(const void* p) { return static_cast<uint32_t>(__cvta_generic_to_shared(p)); }
+
+__device__ __forceinline__ void mbar_init(uint32_t bar, uint32_t count) {
+  asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(bar), "r"(count));
+}
+
+__device__ __forceinline__ void mbar_expect_tx(uint32_t bar, uint32_t bytes) {
+  asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
+  uint32_t ok;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "mbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(ok)
+      : "r"(bar), "r"(parity)
+      : "memory");
+  return ok != 0;
+}
+
+// Bounded wait: returns false when the limit expires, or when another warp of this CTA (*abort_flag) or another CTA
+// (g_gemm_error) already gave up.
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    if ((i & 1023u) == 1023u && (*abort_flag != 0 || *reinterpret_cast<volatile int*>(&g_gemm_error) != 0))
+      return false;
+  }
+  *abort_flag = code;
+  atomicCAS(&g_gemm_error, 0, code);
+  return false;
+}
+
+__device__ __forceinline__ void tma_load_2d(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void bulk_load(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+               ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+               : "memory");
+}
+
+__device__ __forceinline__ void tcgen05_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tcgen05_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+
+__device__ __forceinline__ void tmem_alloc(uint32_t smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// shared-memory matrix descriptor, K-major operand tile with 128-byte swizzle: 8-row groups 1024 bytes apart
+__device__ __forceinline__ uint64_t operand_desc(uint32_t saddr) {
+  return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (1ull << 16) | (64ull << 32) | (1ull << 46) | (2ull << 61);
+}
+
+// descriptor of one 512-byte scale blob (32 rows of 16 bytes, no swizzle: 8-row groups 128 bytes apart)
+__device__ __forceinline__ uint64_t scale_desc(uint32_t saddr) {
+  return static_cast<uint64_t>((saddr & 0x3FFFFu) >> 4) | (8ull << 32) | (1ull << 46);
+}
+
+// 32 rows x 128 bits of shared memory -> 4 columns of tensor memory, replicated into the four 32-lane quarters
+__device__ __forceinline__ void tmem_copy_scales(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+__device__ __forceinline__ void mma_nvf4(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t sfa,
+                                         uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+
+// the mbarrier is arrived on once all tcgen05 operations issued so far by this thread have completed
+__device__ __forceinline__ void mma_commit(uint32_t bar) {
+  asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+__device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t r[32]) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+  asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+// ------------------------------------------------------------------------------------------------ kernel
+
+template <int BN, int STAGES>
+struct GemmSmem {
+  static constexpr uint32_t kA = kBM * (kBK / 2);          // 16 KiB
+  static constexpr uint32_t kB = BN * (kBK / 2);
+  static constexpr uint32_t kSFA = (kBM / 128) * 4 * 512;  // four 512-byte blobs per 128 rows and 256 K
+  static constexpr uint32_t kSFB = (BN / 128) * 4 * 512;
+  static constexpr uint32_t kStage = kA + kB + kSFA + kSFB;
+  static constexpr uint32_t kBars = 1024;                  // barriers + tensor-memory address + abort flag
+  static constexpr uint32_t kTotal = STAGES * kStage + kBars + 1024;   // + slack to align the base to 1024 bytes
+};
+
+struct GemmArgs {
+  const uint8_t* a_sf;
+  const uint8_t* b_sf;
+  const float* a_global;
+  const float* b_global;
+  void* out;
+  int64_t M, N, K, ldc;
+  int out_dtype;
+  int num_m, num_n;
+};
+
+template <typename O>
+__device__ __forceinline__ void store_row32(O* dst, const uint32_t acc[32], float alpha, int ncols_valid) {
+  // 32 consecutive outputs of one row; ncols_valid is a multiple of 8
+#pragma unroll
+  for (int c = 0; c < 32; c += 8) {
+    if (c >= ncols_valid) break;
+    if constexpr (sizeof(O) == 4) {
+      float4 v0 = make_float4(__uint_as_float(acc[c]) * alpha, __uint_as_float(acc[c + 1]) * alpha,
+                              __uint_as_float(acc[c + 2]) * alpha, __uint_as_float(acc[c + 3]) * alpha);
+      float4 v1 = make_float4(__uint_as_float(acc[c + 4]) * alpha, __uint_as_float(acc[c + 5]) * alpha,
+                              __uint_as_float(acc[c + 6]) * alpha, __uint_as_float(acc[c + 7]) * alpha);
+      reinterpret_cast<float4*>(dst + c)[0] = v0;
+      reinterpret_cast<float4*>(dst + c)[1] = v1;
+    } else {
+      O o[8];
+#pragma unroll
+      for (int j = 0; j < 8; ++j) o[j] = from_f<O>(__uint_as_float(acc[c + j]) * alpha);
+      *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(o);
+    }
+  }
+}
+
+template <int BN, int STAGES>
+__global__ void __launch_bounds__(kGemmThreads) gemm_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                            const __grid_constant__ CUtensorMap map_b, GemmArgs args) {
+  using S = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;                  // operand tiles need 1024-byte alignment
+  uint8_t* base_ptr = smem_raw + (base - raw_addr);
+  const uint32_t bars = base + STAGES * S::kStage;
+  uint8_t* bars_ptr = base_ptr + STAGES * S::kStage;
+  // barrier block: full[STAGES], empty[STAGES], accumulator-ready, then the tensor-memory address and the abort flag
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  const uint32_t acc_bar = bars + 8u * (2 * STAGES);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 8 * (2 * STAGES + 1));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 8 * (2 * STAGES + 1) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+
+  // tile of this CTA: groups of 16 row tiles share their column tiles while they are hot in L2
+  constexpr int kGroup = 16;
+  const int pid = blockIdx.x;
+  const int per_group = kGroup * args.num_n;
+  const int group = pid / per_group;
+  const int first_m = group * kGroup;
+  const int group_m = min(args.num_m - first_m, kGroup);
+  const int tile_m = first_m + (pid % per_group) % group_m;
+  const int tile_n = (pid % per_group) / group_m;
+  const int64_t m0 = static_cast<int64_t>(tile_m) * kBM, n0 = static_cast<int64_t>(tile_n) * BN;
+
+  const int num_k_tiles = static_cast<int>((args.K + kBK - 1) / kBK);
+  const int nkb = static_cast<int>((args.K + 63) / 64);               // scale blobs per 128 rows along K
+
+  constexpr uint32_t kTmemCols = BN <= 64 ? 128 : (BN <= 192 ? 256 : 512);
+  constexpr uint32_t kSfaCol = BN;            // accumulator: columns [0, BN); then 16 columns of A scales
+  constexpr uint32_t kSfbCol = BN + 16;       // then (BN/32)*4 columns of B scales
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+      for (int kt = 0; kt < num_k_tiles; ++kt) {
+        const int s = kt % STAGES;
+        const uint32_t round = kt / STAGES;
+        if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, 1)) break;
+        const uint32_t stage = base + s * S::kStage;
+        const int blobs = min(4, nkb - kt * 4);
+        const uint32_t sf_bytes = blobs * 512u;
+        mbar_expect_tx(full_bar(s), S::kA + S::kB + sf_bytes * (1 + BN / 128));
+        tma_load_2d(stage, &map_a, kt * (kBK / 2), static_cast<int>(m0), full_bar(s));
+        tma_load_2d(stage + S::kA, &map_b, kt * (kBK / 2), static_cast<int>(n0), full_bar(s));
+        const uint8_t* sfa = args.a_sf + (static_cast<int64_t>(tile_m) * nkb + kt * 4) * 512;
+        bulk_load(stage + S::kA + S::kB, sfa, sf_bytes, full_bar(s));
+#pragma unroll
+        for (int h = 0; h < BN / 128; ++h) {
+          const uint8_t* sfb = args.b_sf + ((static_cast<int64_t>(tile_n) * (BN / 128) + h) * nkb + kt * 4) * 512;
+          bulk_load(stage + S::kA + S::kB + S::kSFA + h * 2048, sfb, sf_bytes, full_bar(s));
+        }
+      }
+    }
+  } else if (warp == 1) {
+    // ---------------------------------------------------------------- MMA issuer
+    if (lane == 0) {
+      // instruction descriptor: E2M1 x E2M1, UE4M3 scales, K-major A and B, N = BN, M = 128, dense K = 64
+      constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (8u << 24);
+      bool ok = true;
+      for (int kt = 0; kt < num_k_tiles && ok; ++kt) {
+        const int s = kt % STAGES;
+        ok = mbar_wait(full_bar(s), (kt / STAGES) & 1, abort_flag, 2);
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t stage = base + s * S::kStage;
+        const int blocks = min(4, nkb - kt * 4);
+        for (int j = 0; j < blocks; ++j) {
+          tmem_copy_scales(tmem_base + kSfaCol + 4 * j, scale_desc(stage + S::kA + S::kB + j * 512));
+#pragma unroll
+          for (int h = 0; h < BN / 128; ++h)
+            tmem_copy_scales(tmem_base + kSfbCol + (BN / 32) * j + 4 * h,
+                             scale_desc(stage + S::kA + S::kB + S::kSFA + h * 2048 + j * 512));
+        }
+        const uint64_t adesc = operand_desc(stage), bdesc = operand_desc(stage + S::kA);
+        for (int j = 0; j < blocks; ++j)
+          mma_nvf4(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
+                   tmem_base + kSfbCol + (BN / 32) * j, (kt | j) != 0);
+        mma_commit(empty_bar(s));
+      }
+      if (ok) mma_commit(acc_bar);
+    }
+  } else {
+    // ---------------------------------------------------------------- epilogue
+    const bool ok = mbar_wait(acc_bar, 0, abort_flag, 3);
+    tcgen05_fence_after();
+    if (ok) {
+      const int quarter = warp & 3;                       // the 32 accumulator lanes this warp may read
+      const int64_t row = m0 + quarter * 32 + lane;
+      const float alpha = args.a_global[0] * args.b_global[0];
+#pragma unroll 1
+      for (int c = 0; c < BN; c += 32) {
+        uint32_t acc[32];
+        tmem_load32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c, acc);
+        const int64_t col = n0 + c;
+        if (row < args.M && col < args.N) {
+          const int64_t left = args.N - col;
+          const int valid = left < 32 ? static_cast<int>(left) : 32;
+          if (args.out_dtype == BL_BF16)
+            store_row32(static_cast<__nv_bfloat16*>(args.out) + row * args.ldc + col, acc, alpha, valid);
+          else if (args.out_dtype == BL_F16)
+            store_row32(static_cast<__half*>(args.out) + row * args.ldc + col, acc, alpha, valid);
+          else
+            store_row32(static_cast<float*>(args.out) + row * args.ldc + col, acc, alpha, valid);
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ host side
+
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                  const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                  CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+static EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = nullptr;
+  static std::once_flag once;
+  std::call_once(once, [] {
+    void* p = nullptr;
+    cudaDriverEntryPointQueryResult q;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) == cudaSuccess &&
+        q == cudaDriverEntryPointSuccess)
+      fn = reinterpret_cast<EncodeTiledFn>(p);
+  });
+  return fn;
+}
+
+// [rows, K/2] bytes, box of 128 bytes x box_rows rows, 128-byte swizzle, zero fill outside the tensor
+static int make_operand_map(CUtensorMap* map, const uint8_t* codes, int64_t rows, int64_t K, int box_rows) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  BL_REQUIRE(enc != nullptr, "gemm: the CUDA driver does not provide cuTensorMapEncodeTiled");
+  const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 2), static_cast<cuuint64_t>(rows)};
+  const cuuint64_t strides[1] = {static_cast<cuuint64_t>(K / 2)};
+  const cuuint32_t box[2] = {128u, static_cast<cuuint32_t>(box_rows)};
+  const cuuint32_t elem[2] = {1u, 1u};
+  const CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT8, 2, const_cast<uint8_t*>(codes), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  BL_REQUIRE(rc == CUDA_SUCCESS, "gemm: cuTensorMapEncodeTiled failed with code %d (rows %lld, K %lld)", (int)rc,
+             (long long)rows, (long long)K);
+  return 0;
+}
+
+template <int BN, int STAGES>
+static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, GemmArgs args, cudaStream_t st) {
+  using S = GemmSmem<BN, STAGES>;
+  CUtensorMap map_a, map_b;
+  if (int rc = make_operand_map(&map_a, a_codes, args.M, args.K, kBM)) return rc;
+  if (int rc = make_operand_map(&map_b, b_codes, args.N, args.K, BN)) return rc;
+  args.num_m = static_cast<int>((args.M + kBM - 1) / kBM);
+  args.num_n = static_cast<int>((args.N + BN - 1) / BN);
+  BL_CUDA(cudaFuncSetAttribute(gemm_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+  const int64_t tiles = static_cast<int64_t>(args.num_m) * args.num_n;
+  BL_REQUIRE(tiles <= 0x7FFFFFFF, "gemm: too many output tiles (%lld)", (long long)tiles);
+  gemm_kernel<BN, STAGES><<<static_cast<unsigned>(tiles), kGemmThreads, S::kTotal, st>>>(map_a, map_b, args);
+  BL_CUDA(cudaGetLastError());
+  return 0;
+}
+
+}  // namespace blb
+
+using namespace blb;
+
+extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const float* a_global, const uint8_t* b_codes,
+                             const uint8_t* b_sf, const float* b_global, int64_t M, int64_t N, int64_t K, void* out,
+                             int out_dtype, int64_t ldc, int device, bl_stream_t stream) {
+  BL_REQUIRE(a_codes && a_sf && a_global && b_codes && b_sf && b_global && out, "gemm: null buffer");
+  BL_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem %lld x %lld x %lld", (long long)M, (long long)N, (long long)K);
+  BL_REQUIRE(K % 32 == 0, "gemm: K = %lld is not a multiple of 32", (long long)K);
+  BL_REQUIRE(N % 8 == 0, "gemm: N = %lld is not a multiple of 8", (long long)N);
+  BL_REQUIRE(ldc >= N && ldc % 8 == 0, "gemm: output row stride %lld must be a multiple of 8 and at least N", (long long)ldc);
+  BL_REQUIRE(out_dtype >= BL_F32 && out_dtype <= BL_F16, "gemm: unknown output dtype %d", out_dtype);
+  BL_REQUIRE(aligned16(a_codes) && aligned16(b_codes) && aligned16(a_sf) && aligned16(b_sf) && aligned16(out),
+             "gemm: operands, scales and output must be 16-byte aligned");
+  BL_REQUIRE(M < (1ll << 31) && N < (1ll << 31) && K < (1ll << 31), "gemm: dimension exceeds 2^31");
+  BL_DEVICE(device);
+  GemmArgs args;
+  args.a_sf = a_sf;
+  args.b_sf = b_sf;
+  args.a_global = a_global;
+  args.b_global = b_global;
+  args.out = out;
+  args.M = M;
+  args.N = N;
+  args.K = K;
+  args.ldc = ldc;
+  args.out_dtype = out_dtype;
+  args.num_m = args.num_n = 0;
+  return launch_gemm<128, 3>(a_codes, b_codes, args, reinterpret_cast<cudaStream_t>(stream));
+}
+
+// Reads (and clears) the device-side error flag of the GEMM kernels: 0 = no bounded wait expired so far.
+// Synchronizes the device.
+extern "C" int bl_nvfp4_gemm_status(int* status, int device) {
+  BL_REQUIRE(status != nullptr, "gemm_status: null output");
+  BL_DEVICE(device);
+  int zero = 0;
+  BL_CUDA(cudaMemcpyFromSymbol(status, g_gemm_error, sizeof(int)));
+  BL_CUDA(cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int)));
+  return 0;
+}

@@ -1,0 +1,475 @@
+// NVFP4 operand quantizers, dequantization and the blocked scale layout.
+//
+// Reference semantics (compiled with --fmad=false; codes and scale bytes are bit-exact with these):
+//   round to nearest : bitlattice/reference.py:164-235 ('rtn': ties to the lower level, v / (scale*global));
+//                      reference kernel csrc/act_quant.cu:16-27,66-86
+//   stochastic       : bitlattice/fp4ref.py:71-78,103-150 ('sr': v * (1/(scale*global)), u = hash(flat index, seed, 0))
+//   transposed, H16  : csrc/act_quant.cu:100-148 (blocks of 16 along the rows of x, v <- v H summed in input order)
+//   W^T              : csrc/act_quant.cu:150-175 (values formed as (level*scale)*global, same per-tensor scale)
+//   dequantize       : bitlattice/reference.py:238-245
+//   blocked scales   : bitlattice/backend.py:179-188
+#include "common.cuh"
+
+namespace blb {
+
+constexpr int kQThreads = 256;
+
+// ------------------------------------------------------------------------------------------------ amax
+
+__device__ __forceinline__ void atomic_max_pos(float* addr, float v) {   // v >= 0: integer order == float order
+  atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
+}
+
+// out[0] = max|x| (out must start at zero), out[1] = max(out[0]/2688, 1e-12) written by the last block to finish
+template <typename T>
+__global__ void __launch_bounds__(kQThreads) amax_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ out) {
+  constexpr int per = 16 / sizeof(T);
+  const int64_t nvec = n / per;
+  float m = 0.0f;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < nvec;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint4 raw = reinterpret_cast<const uint4*>(x)[i];
+    const T* e = reinterpret_cast<const T*>(&raw);
+#pragma unroll
+    for (int j = 0; j < per; ++j) m = fmaxf(m, fabsf(to_f<T>(e[j])));
+  }
+  if (blockIdx.x == 0 && threadIdx.x < n - nvec * per) m = fmaxf(m, fabsf(to_f<T>(x[nvec * per + threadIdx.x])));
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  __shared__ float warp_max[kQThreads / 32];
+  if ((threadIdx.x & 31) == 0) warp_max[threadIdx.x >> 5] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) {
+    for (int w = 1; w < kQThreads / 32; ++w) m = fmaxf(m, warp_max[w]);
+    atomic_max_pos(out, m);
+    __threadfence();
+    unsigned* ticket = reinterpret_cast<unsigned*>(out + 2);
+    if (atomicAdd(ticket, 1u) == gridDim.x - 1) {
+      __threadfence();
+      const float a = *reinterpret_cast<volatile float*>(out);
+      out[1] = fmaxf(a / 2688.0f, 1e-12f);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ block quantizer
+
+// 8 of the 16 values of a block held by this lane (the partner lane, xor 1, holds the other 8): returns this
+// lane's 8 codes; *scale receives the E4M3 byte of the block.
+// SR == false: reference.quantize 'rtn'. SR == true: fp4ref.quantize 'sr' (idx0 = flat index of v[0]).
+template <bool SR>
+__device__ __forceinline__ uint32_t quantize_half_block(const float v[8], float g, uint32_t key, uint32_t idx0,
+                                                        uint32_t* scale) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  uint32_t out = 0;
+  if constexpr (!SR) {
+    const uint32_t sb = e4m3_encode(fmaxf(amax / 6.0f, 1e-12f) / g);
+    const float se = e4m3_decode(sb) * g;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out |= e2m1_code_nearest(v[i] / se) << (4 * i);
+    *scale = sb;
+  } else {
+    const uint32_t sb = e4m3_encode(amax / 6.0f / g);
+    const float t = e4m3_decode(sb) * g;
+    const float inv = t > 0.0f ? 1.0f / t : 0.0f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) out |= e2m1_code_sr(v[i] * inv, hash_uniform(idx0 + i, key)) << (4 * i);
+    *scale = sb;
+  }
+  return out;
+}
+
+// the reference kernel's own block rule for W^T (csrc/act_quant.cu:66-86): scale amax/6/g, s > 0 ? v/s : 0
+__device__ __forceinline__ uint32_t requantize_half_block(const float v[8], float g, uint32_t* scale) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
+  const uint32_t sb = e4m3_encode(amax / 6.0f / g);
+  const float s = e4m3_decode(sb) * g;
+  uint32_t out = 0;
+#pragma unroll
+  for (int i = 0; i < 8; ++i) out |= e2m1_code_nearest(s > 0.0f ? v[i] / s : 0.0f) << (4 * i);
+  *scale = sb;
+  return out;
+}
+
+__device__ __forceinline__ int64_t scale_index(int layout, int64_t r, int64_t c16, int64_t cols16) {
+  if (layout == BL_SF_ROWMAJOR) return r * cols16 + c16;
+  const int64_t nc = (cols16 + 3) >> 2;
+  return ((r >> 7) * nc + (c16 >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (c16 & 3);
+}
+
+// ------------------------------------------------------------------------------------------------ rows
+
+// x [rows, cols] -> codes [rows, cols/2], scales; one thread per 8 elements, lane pairs share a block
+template <typename T, bool SR>
+__global__ void __launch_bounds__(kQThreads) quantize_rows_kernel(const T* __restrict__ x, int64_t rows, int64_t cols,
+                                                                  const float* __restrict__ global, uint32_t key,
+                                                                  uint8_t* __restrict__ codes,
+                                                                  uint8_t* __restrict__ scales, int layout) {
+  const int64_t nchunks = rows * cols / 8;
+  const float g = global[0];
+  const int64_t cpr = cols / 8;
+  for (int64_t base = static_cast<int64_t>(blockIdx.x) * blockDim.x; base < nchunks;
+       base += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t ch = base + threadIdx.x;
+    const bool active = ch < nchunks;              // nchunks is even: a lane pair is active or idle together
+    float v[8];
+    if (active) {
+      load8(x + ch * 8, v);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = 0.0f;
+    }
+    uint32_t sb;
+    const uint32_t out = quantize_half_block<SR>(v, g, key, static_cast<uint32_t>(ch * 8), &sb);
+    if (!active) continue;
+    reinterpret_cast<uint32_t*>(codes)[ch] = out;
+    if ((threadIdx.x & 1) == 0) {
+      const int64_t r = ch / cpr, c16 = (ch - r * cpr) >> 1;
+      scales[scale_index(layout, r, c16, cols / 16)] = static_cast<uint8_t>(sb);
+    }
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ transposed
+
+constexpr int kTM = 128;   // rows of x per tile (8 blocks of 16)
+constexpr int kTK = 64;    // columns of x per tile
+
+// Rotated block column: v[j] = sum over i (ascending) of raw[i] * H[i][j]; this thread computes 8 of the 16 outputs
+// (j = 8*half .. 8*half+7) of the block whose 16 inputs are raw[].
+__device__ __forceinline__ void rotate_half(const float raw[16], const float* __restrict__ sH, int half, float v[8]) {
+#pragma unroll
+  for (int jj = 0; jj < 8; ++jj) {
+    const int j = half * 8 + jj;
+    float a = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) a = a + raw[i] * sH[i * 16 + j];
+    v[jj] = a;
+  }
+}
+
+// amax of the (rotated) transposed tensor; out as for amax_kernel but without the scale
+template <typename T>
+__global__ void __launch_bounds__(kQThreads) amax_t_kernel(const T* __restrict__ x, int64_t M, int64_t K,
+                                                           const float* __restrict__ H, float* __restrict__ out) {
+  __shared__ float sH[256];
+  if (H != nullptr) sH[threadIdx.x] = H[threadIdx.x];
+  __syncthreads();
+  const int64_t n = (M / 16) * K;
+  float m = 0.0f;
+  for (int64_t t = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; t < n;
+       t += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t k = t % K, mb = t / K;
+    float raw[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) raw[i] = to_f<T>(x[(mb * 16 + i) * K + k]);
+    if (H == nullptr) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) m = fmaxf(m, fabsf(raw[i]));
+    } else {
+      float v[8];
+      rotate_half(raw, sH, 0, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+      rotate_half(raw, sH, 1, v);
+#pragma unroll
+      for (int i = 0; i < 8; ++i) m = fmaxf(m, fabsf(v[i]));
+    }
+  }
+#pragma unroll
+  for (int o = 16; o > 0; o >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, o));
+  if ((threadIdx.x & 31) == 0) atomic_max_pos(out, m);
+}
+
+// global scale of the transposed operand: from a bound (given == 1: in[0] is the bound) or from an amax (in[0])
+__global__ void global_t_kernel(const float* __restrict__ in, int given, float* __restrict__ global_out) {
+  const float amax = given ? in[0] * 2688.0f : in[0];
+  global_out[0] = fmaxf(amax / 2688.0f, 1e-12f);
+}
+
+// x [M, K] -> NVFP4 of x^T. A CTA stages a [128, 64] tile of x in shared memory with coalesced row reads; the work
+// item (k, mb, half) quantizes 8 of the 16 rotated values of block mb of column k; lane pairs (half 0/1) share a block.
+template <typename T, bool SR>
+__global__ void __launch_bounds__(kQThreads) quantize_t_kernel(const T* __restrict__ x, int64_t M, int64_t K,
+                                                               const float* __restrict__ H,
+                                                               const float* __restrict__ global, uint32_t key,
+                                                               uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
+                                                               int layout) {
+  __shared__ float tile[kTM][kTK + 1];
+  __shared__ float sH[256];
+  if (H != nullptr) sH[threadIdx.x] = H[threadIdx.x];
+  const int64_t m0 = static_cast<int64_t>(blockIdx.y) * kTM, k0 = static_cast<int64_t>(blockIdx.x) * kTK;
+  for (int i = threadIdx.x; i < kTM * kTK; i += kQThreads) {
+    const int rr = i / kTK, cc = i % kTK;
+    const int64_t m = m0 + rr, k = k0 + cc;
+    tile[rr][cc] = (m < M && k < K) ? to_f<T>(x[m * K + k]) : 0.0f;
+  }
+  __syncthreads();
+  const float g = global[0];
+  // 64 columns x 8 blocks x 2 halves = 1024 work items, 4 per thread; lanes (2j, 2j+1) = halves of one block
+  for (int it = 0; it < 4; ++it) {
+    const int w = it * kQThreads + threadIdx.x;
+    const int half = w & 1, kk = (w >> 1) & (kTK - 1), mb = w >> 7;
+    const int64_t k = k0 + kk, m = m0 + mb * 16;
+    const bool active = k < K && m < M;               // M % 16 == 0: a block is inside or outside as a whole
+    float raw[16], v[8];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) raw[i] = tile[mb * 16 + i][kk];
+    if (H != nullptr) {
+      rotate_half(raw, sH, half, v);
+    } else {
+#pragma unroll
+      for (int i = 0; i < 8; ++i) v[i] = raw[half * 8 + i];
+    }
+    uint32_t sb;
+    const uint32_t idx0 = static_cast<uint32_t>(static_cast<uint64_t>(k) * static_cast<uint64_t>(M) + m + half * 8);
+    const uint32_t out = quantize_half_block<SR>(v, g, key, idx0, &sb);
+    if (!active) continue;
+    *reinterpret_cast<uint32_t*>(codes + k * (M / 2) + (m + half * 8) / 2) = out;
+    if (half == 0) scales[scale_index(layout, k, m / 16, M / 16)] = static_cast<uint8_t>(sb);
+  }
+}
+
+// NVFP4 W [N, K] -> NVFP4 of W^T [K, N]; same tiling, the tile holds (level*scale)*global
+__global__ void __launch_bounds__(kQThreads) requantize_t_kernel(const uint8_t* __restrict__ wcodes,
+                                                                 const uint8_t* __restrict__ wscales,
+                                                                 const float* __restrict__ global, int64_t N, int64_t K,
+                                                                 uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
+                                                                 float* __restrict__ global_out, int layout) {
+  __shared__ float tile[kTM][kTK + 1];
+  const float g = global[0];
+  if (blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) global_out[0] = g;
+  const int64_t n0 = static_cast<int64_t>(blockIdx.y) * kTM, k0 = static_cast<int64_t>(blockIdx.x) * kTK;
+  // 128 rows x 8 chunks of 8 columns
+  for (int i = threadIdx.x; i < kTM * (kTK / 8); i += kQThreads) {
+    const int rr = i / (kTK / 8), c8 = i % (kTK / 8);
+    const int64_t n = n0 + rr, k = k0 + c8 * 8;
+    if (n < N && k < K) {
+      const uint32_t word = *reinterpret_cast<const uint32_t*>(wcodes + n * (K / 2) + k / 2);
+      const float s = e4m3_decode(wscales[n * (K / 16) + k / 16]);
+#pragma unroll
+      for (int j = 0; j < 8; ++j) tile[rr][c8 * 8 + j] = level_of_rank(rank_of_code((word >> (4 * j)) & 0xFu)) * s * g;
+    } else {
+#pragma unroll
+      for (int j = 0; j < 8; ++j) tile[rr][c8 * 8 + j] = 0.0f;
+    }
+  }
+  __syncthreads();
+  for (int it = 0; it < 4; ++it) {
+    const int w = it * kQThreads + threadIdx.x;
+    const int half = w & 1, kk = (w >> 1) & (kTK - 1), nb = w >> 7;
+    const int64_t k = k0 + kk, n = n0 + nb * 16;
+    const bool active = k < K && n < N;
+    float v[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) v[i] = tile[nb * 16 + half * 8 + i][kk];
+    uint32_t sb;
+    const uint32_t out = requantize_half_block(v, g, &sb);
+    if (!active) continue;
+    *reinterpret_cast<uint32_t*>(codes + k * (N / 2) + (n + half * 8) / 2) = out;
+    if (half == 0) scales[scale_index(layout, k, n / 16, N / 16)] = static_cast<uint8_t>(sb);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ dequantize, layout
+
+template <typename O>
+__global__ void __launch_bounds__(kQThreads) dequantize_kernel(const uint8_t* __restrict__ codes,
+                                                               const uint8_t* __restrict__ scales,
+                                                               const float* __restrict__ global, int64_t nchunks,
+                                                               O* __restrict__ out) {
+  const float g = global[0];
+  for (int64_t ch = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; ch < nchunks;
+       ch += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const uint32_t word = reinterpret_cast<const uint32_t*>(codes)[ch];
+    const float s = e4m3_decode(scales[ch >> 1]) * g;
+    O o[8];
+#pragma unroll
+    for (int i = 0; i < 8; ++i) o[i] = from_f<O>(level_of_rank(rank_of_code((word >> (4 * i)) & 0xFu)) * s);
+    if constexpr (sizeof(O) == 4) {
+      reinterpret_cast<float4*>(out + ch * 8)[0] = *reinterpret_cast<float4*>(&o[0]);
+      reinterpret_cast<float4*>(out + ch * 8)[1] = *reinterpret_cast<float4*>(&o[4]);
+    } else {
+      *reinterpret_cast<uint4*>(out + ch * 8) = *reinterpret_cast<uint4*>(&o[0]);
+    }
+  }
+}
+
+__global__ void to_blocked_kernel(const uint8_t* __restrict__ scales, int64_t rows, int64_t cols16,
+                                  uint8_t* __restrict__ out) {
+  const int64_t n = rows * cols16;
+  for (int64_t i = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x; i < n;
+       i += static_cast<int64_t>(gridDim.x) * blockDim.x) {
+    const int64_t r = i / cols16, c = i - r * cols16;
+    out[scale_index(BL_SF_BLOCKED, r, c, cols16)] = scales[i];
+  }
+}
+
+static int grid_for(int64_t work, int threads, int device) {
+  const int64_t blocks = (work + threads - 1) / threads;
+  const int64_t cap = static_cast<int64_t>(sm_count(device)) * 16;
+  return static_cast<int>(blocks < 1 ? 1 : (blocks > cap ? cap : blocks));
+}
+
+static bool blocked_needs_padding(int64_t rows, int64_t cols16) { return (rows % 128) != 0 || (cols16 % 4) != 0; }
+
+}  // namespace blb
+
+using namespace blb;
+
+extern "C" size_t bl_blocked_scale_bytes(int64_t rows, int64_t cols16) {
+  if (rows <= 0 || cols16 <= 0) return 0;
+  return static_cast<size_t>(((rows + 127) / 128) * ((cols16 + 3) / 4) * 512);
+}
+
+extern "C" int bl_nvfp4_amax(const void* x, int dtype, int64_t n, float* out, int device, bl_stream_t stream) {
+  BL_REQUIRE(x && out && n > 0, "amax: null or empty input");
+  BL_REQUIRE(dtype >= BL_F32 && dtype <= BL_F16, "amax: unknown dtype %d", dtype);
+  BL_REQUIRE(aligned16(x) && aligned16(out), "amax: buffers must be 16-byte aligned");
+  BL_DEVICE(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  BL_CUDA(cudaMemsetAsync(out, 0, 16, st));
+  const int per = dtype == BL_F32 ? 4 : 8;
+  const int grid = grid_for(n / per + 1, kQThreads, device);
+  if (dtype == BL_BF16) amax_kernel<<<grid, kQThreads, 0, st>>>(static_cast<const __nv_bfloat16*>(x), n, out);
+  else if (dtype == BL_F16) amax_kernel<<<grid, kQThreads, 0, st>>>(static_cast<const __half*>(x), n, out);
+  else amax_kernel<<<grid, kQThreads, 0, st>>>(static_cast<const float*>(x), n, out);
+  BL_CUDA(cudaGetLastError());
+  return 0;
+}
+
+template <typename T>
+static int quantize_rows_typed(const T* x, int64_t rows, int64_t cols, const float* g, int64_t seed, uint32_t step,
+                               uint8_t* codes, uint8_t* scales, int layout, int device, cudaStream_t st) {
+  const int grid = grid_for(rows * cols / 8, kQThreads, device);
+  if (seed < 0)
+    quantize_rows_kernel<T, false><<<grid, kQThreads, 0, st>>>(x, rows, cols, g, 0u, codes, scales, layout);
+  else
+    quantize_rows_kernel<T, true><<<grid, kQThreads, 0, st>>>(x, rows, cols, g, hash_key(static_cast<uint32_t>(seed), step),
+                                                              codes, scales, layout);
+  BL_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int bl_nvfp4_quantize(const void* x, int dtype, int64_t rows, int64_t cols, const float* global_scale,
+                                 int64_t seed, uint32_t step, uint8_t* codes, uint8_t* scales, int sf_layout,
+                                 int device, bl_stream_t stream) {
+  BL_REQUIRE(x && global_scale && codes && scales, "quantize_nvfp4: null buffer");
+  BL_REQUIRE(rows > 0 && cols > 0 && cols % 16 == 0,
+             "quantize_nvfp4: last dimension must be a multiple of 16, got %lld x %lld", (long long)rows, (long long)cols);
+  BL_REQUIRE(dtype >= BL_F32 && dtype <= BL_F16, "quantize_nvfp4: unknown dtype %d", dtype);
+  BL_REQUIRE(sf_layout == BL_SF_ROWMAJOR || sf_layout == BL_SF_BLOCKED, "quantize_nvfp4: unknown scale layout %d", sf_layout);
+  BL_REQUIRE(aligned16(x) && aligned16(codes), "quantize_nvfp4: x and codes must be 16-byte aligned");
+  BL_DEVICE(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (sf_layout == BL_SF_BLOCKED && blocked_needs_padding(rows, cols / 16))
+    BL_CUDA(cudaMemsetAsync(scales, 0, bl_blocked_scale_bytes(rows, cols / 16), st));
+  if (dtype == BL_BF16)
+    return quantize_rows_typed(static_cast<const __nv_bfloat16*>(x), rows, cols, global_scale, seed, step, codes, scales, sf_layout, device, st);
+  if (dtype == BL_F16)
+    return quantize_rows_typed(static_cast<const __half*>(x), rows, cols, global_scale, seed, step, codes, scales, sf_layout, device, st);
+  return quantize_rows_typed(static_cast<const float*>(x), rows, cols, global_scale, seed, step, codes, scales, sf_layout, device, st);
+}
+
+template <typename T>
+static int quantize_t_typed(const T* x, int64_t M, int64_t K, const float* H, int64_t seed, uint32_t step,
+                            const float* bound, float* amax_scratch, uint8_t* codes, uint8_t* scales, float* gout,
+                            int layout, int device, cudaStream_t st) {
+  if (bound == nullptr) {
+    BL_CUDA(cudaMemsetAsync(amax_scratch, 0, 16, st));
+    amax_t_kernel<<<grid_for((M / 16) * K, kQThreads, device), kQThreads, 0, st>>>(x, M, K, H, amax_scratch);
+    BL_CUDA(cudaGetLastError());
+    global_t_kernel<<<1, 1, 0, st>>>(amax_scratch, 0, gout);
+  } else {
+    global_t_kernel<<<1, 1, 0, st>>>(bound, 1, gout);
+  }
+  BL_CUDA(cudaGetLastError());
+  const dim3 grid(static_cast<unsigned>((K + kTK - 1) / kTK), static_cast<unsigned>((M + kTM - 1) / kTM));
+  if (seed < 0)
+    quantize_t_kernel<T, false><<<grid, kQThreads, 0, st>>>(x, M, K, H, gout, 0u, codes, scales, layout);
+  else
+    quantize_t_kernel<T, true><<<grid, kQThreads, 0, st>>>(x, M, K, H, gout, hash_key(static_cast<uint32_t>(seed), step),
+                                                           codes, scales, layout);
+  BL_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int bl_nvfp4_quantize_t(const void* x, int dtype, int64_t M, int64_t K, const float* H, int64_t seed,
+                                   uint32_t step, const float* global_bound, float* amax_scratch, uint8_t* codes,
+                                   uint8_t* scales, float* global_out, int sf_layout, int device, bl_stream_t stream) {
+  BL_REQUIRE(x && codes && scales && global_out, "quantize_nvfp4_t: null buffer");
+  BL_REQUIRE(M > 0 && K > 0 && M % 16 == 0, "quantize_nvfp4_t: rows must be a multiple of 16, got %lld x %lld",
+             (long long)M, (long long)K);
+  BL_REQUIRE((M / 16) <= 65535 * 8, "quantize_nvfp4_t: too many rows (%lld)", (long long)M);
+  BL_REQUIRE(global_bound != nullptr || amax_scratch != nullptr,
+             "quantize_nvfp4_t: without a scale bound the amax pass needs a 4-float scratch buffer");
+  BL_REQUIRE(dtype >= BL_F32 && dtype <= BL_F16, "quantize_nvfp4_t: unknown dtype %d", dtype);
+  BL_REQUIRE(sf_layout == BL_SF_ROWMAJOR || sf_layout == BL_SF_BLOCKED, "quantize_nvfp4_t: unknown scale layout %d", sf_layout);
+  BL_REQUIRE(aligned16(codes), "quantize_nvfp4_t: codes must be 16-byte aligned");
+  BL_DEVICE(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (sf_layout == BL_SF_BLOCKED && blocked_needs_padding(K, M / 16))
+    BL_CUDA(cudaMemsetAsync(scales, 0, bl_blocked_scale_bytes(K, M / 16), st));
+  if (dtype == BL_BF16)
+    return quantize_t_typed(static_cast<const __nv_bfloat16*>(x), M, K, H, seed, step, global_bound, amax_scratch, codes, scales, global_out, sf_layout, device, st);
+  if (dtype == BL_F16)
+    return quantize_t_typed(static_cast<const __half*>(x), M, K, H, seed, step, global_bound, amax_scratch, codes, scales, global_out, sf_layout, device, st);
+  return quantize_t_typed(static_cast<const float*>(x), M, K, H, seed, step, global_bound, amax_scratch, codes, scales, global_out, sf_layout, device, st);
+}
+
+extern "C" int bl_nvfp4_requantize_t(const uint8_t* codes, const uint8_t* scales, const float* global_scale, int64_t N,
+                                     int64_t K, uint8_t* out_codes, uint8_t* out_scales, float* global_out,
+                                     int sf_layout, int device, bl_stream_t stream) {
+  BL_REQUIRE(codes && scales && global_scale && out_codes && out_scales && global_out, "requantize_nvfp4_t: null buffer");
+  BL_REQUIRE(N > 0 && K > 0 && N % 16 == 0 && K % 16 == 0,
+             "requantize_nvfp4_t: both dimensions must be multiples of 16, got %lld x %lld", (long long)N, (long long)K);
+  BL_REQUIRE(sf_layout == BL_SF_ROWMAJOR || sf_layout == BL_SF_BLOCKED, "requantize_nvfp4_t: unknown scale layout %d", sf_layout);
+  BL_REQUIRE(aligned16(codes) && aligned16(out_codes), "requantize_nvfp4_t: code buffers must be 16-byte aligned");
+  BL_DEVICE(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (sf_layout == BL_SF_BLOCKED && blocked_needs_padding(K, N / 16))
+    BL_CUDA(cudaMemsetAsync(out_scales, 0, bl_blocked_scale_bytes(K, N / 16), st));
+  const dim3 grid(static_cast<unsigned>((K + kTK - 1) / kTK), static_cast<unsigned>((N + kTM - 1) / kTM));
+  requantize_t_kernel<<<grid, kQThreads, 0, st>>>(codes, scales, global_scale, N, K, out_codes, out_scales, global_out,
+                                                  sf_layout);
+  BL_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int bl_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales, const float* global_scale, int64_t rows,
+                                   int64_t cols, void* out, int out_dtype, int device, bl_stream_t stream) {
+  BL_REQUIRE(codes && scales && global_scale && out, "dequantize: null buffer");
+  BL_REQUIRE(rows > 0 && cols > 0 && cols % 16 == 0, "dequantize: last dimension must be a multiple of 16, got %lld x %lld",
+             (long long)rows, (long long)cols);
+  BL_REQUIRE(out_dtype >= BL_F32 && out_dtype <= BL_F16, "dequantize: unknown output dtype %d", out_dtype);
+  BL_REQUIRE(aligned16(codes) && aligned16(out), "dequantize: codes and output must be 16-byte aligned");
+  BL_DEVICE(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int64_t nchunks = rows * cols / 8;
+  const int grid = grid_for(nchunks, kQThreads, device);
+  if (out_dtype == BL_BF16)
+    dequantize_kernel<<<grid, kQThreads, 0, st>>>(codes, scales, global_scale, nchunks, static_cast<__nv_bfloat16*>(out));
+  else if (out_dtype == BL_F16)
+    dequantize_kernel<<<grid, kQThreads, 0, st>>>(codes, scales, global_scale, nchunks, static_cast<__half*>(out));
+  else
+    dequantize_kernel<<<grid, kQThreads, 0, st>>>(codes, scales, global_scale, nchunks, static_cast<float*>(out));
+  BL_CUDA(cudaGetLastError());
+  return 0;
+}
+
+extern "C" int bl_nvfp4_scales_to_blocked(const uint8_t* scales, int64_t rows, int64_t cols16, uint8_t* out, int device,
+                                          bl_stream_t stream) {
+  BL_REQUIRE(scales && out && rows > 0 && cols16 > 0, "scales_to_blocked: null or empty input");
+  BL_DEVICE(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (blocked_needs_padding(rows, cols16)) BL_CUDA(cudaMemsetAsync(out, 0, bl_blocked_scale_bytes(rows, cols16), st));
+  to_blocked_kernel<<<grid_for(rows * cols16, kQThreads, device), kQThreads, 0, st>>>(scales, rows, cols16, out);
+  BL_CUDA(cudaGetLastError());
+  return 0;
+}

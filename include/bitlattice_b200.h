@@ -1,0 +1,153 @@
+/*
+ * C ABI of libbitlattice_b200.so: the NVFP4 LatticeTensor linear layer (quantizers + block-scaled FP4 GEMM) and the
+ * lattice optimizer update, hand-written CUDA for sm_100a.
+ *
+ * Every entry point replaces one operator of the reference's native extension (`torch.ops.bitlattice.*`, schemas in
+ * the reference's csrc/bindings.cpp:75-134) for the NVFP4 format only. Conventions shared by all of them:
+ *   - plain device pointers and sizes; the library never allocates or frees device memory (the caller owns every
+ *     buffer, outputs included) -- scratch memory, where an operation needs some, is passed in and its size comes
+ *     from the matching *_scratch_bytes function;
+ *   - all buffers are contiguous and 16-byte aligned; shapes are validated before anything is launched;
+ *   - work is enqueued on `stream` of CUDA device `device` and the call returns without synchronizing;
+ *   - the return value is 0 on success, non-zero on failure; bl_last_error() then describes the failure
+ *     (thread-local), which the Python layer raises as RuntimeError, as TORCH_CHECK does in the reference.
+ *
+ * Storage layout (bitlattice/formats.py:415, bitlattice/packing.py:22-33): a [rows, cols] NVFP4 tensor is
+ *   codes   uint8 [rows, cols/2]   E2M1 nibbles, element 2j in the low nibble of byte j
+ *   scales  uint8 [rows, cols/16]  E4M3 (float8_e4m3fn) bit patterns, one per 16 consecutive elements of a row
+ *   global  float [1]              per-tensor scale; value = level(code) * scale * global
+ * "Blocked" scales are the same bytes in the 128x4-tiled order of block-scaled GEMMs (bitlattice/backend.py:179-188):
+ * offset(r, c) = ((r/128) * ceil(cols16/4) + c/4) * 512 + (r%32) * 16 + ((r/32)%4) * 4 + c%4, zero padded.
+ */
+#ifndef BITLATTICE_B200_H
+#define BITLATTICE_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define BL_API __attribute__((visibility("default")))
+#else
+#define BL_API
+#endif
+
+typedef struct CUstream_st* bl_stream_t; /* a cudaStream_t */
+
+/* element types of dense inputs / outputs */
+enum { BL_F32 = 0, BL_BF16 = 1, BL_F16 = 2 };
+/* rounding of the lattice projection (bitlattice/_ops.py:22) */
+enum { BL_ROUND_SR = 0, BL_ROUND_STRAT = 1, BL_ROUND_RTN = 2 };
+/* group-scale rule (bitlattice/_ops.py:23) */
+enum { BL_RULE_FIXED = 0, BL_RULE_FIT = 1, BL_RULE_FIT_LATENT = 2 };
+/* update direction (bitlattice/_ops.py:24); only these three are built */
+enum { BL_DIR_RAW = 0, BL_DIR_SIGN = 1, BL_DIR_COLNORM = 2 };
+/* layout of block-scale outputs */
+enum { BL_SF_ROWMAJOR = 0, BL_SF_BLOCKED = 1 };
+
+BL_API int bl_version(void);
+BL_API const char* bl_last_error(void);
+
+/* ---- lattice update ------------------------------------------------------------------------------------------- */
+
+/* Replaces torch.ops.bitlattice.step_quantized for NVFP4 (csrc/bindings.cpp:77-81, csrc/lattice.cu:407-439,
+ * kernel :125-175). One lattice step given the fp32 direction D [rows*cols]: codes and phase are updated in place,
+ * the new scale bytes go to scales_out (scales_in is only read; the two may be the same buffer).
+ * phase: phase_bits-bit two's complement values in phase_cb-bit containers {1,2,4,8} packed little-endian along
+ * cols, [rows, cols*phase_cb/8]; NULL when phase_bits == 0. offset: RNG index of element (0, 0), so that a row
+ * shard or row tile draws the numbers of the whole tensor (csrc/update.cpp:50). cols % 16 == 0. */
+BL_API int bl_nvfp4_step_quantized(uint8_t* codes, uint8_t* phase, const uint8_t* scales_in, uint8_t* scales_out,
+                            const float* global_scale, const float* D, int64_t rows, int64_t cols, uint64_t offset,
+                            int phase_bits, int phase_cb, double lr, double decay, int rounding, uint32_t seed,
+                            uint32_t step, int strat_j, int strat_k, int rule, double kappa, int device,
+                            bl_stream_t stream);
+
+/* Scratch bytes bl_nvfp4_lattice_update / bl_direction need for a [rows, cols] gradient (0 when none is needed). */
+BL_API size_t bl_update_scratch_bytes(int64_t rows, int64_t cols, int direction, double clip);
+
+/* Replaces torch.ops.bitlattice.lattice_update for NVFP4 (csrc/bindings.cpp:119-124, csrc/update.cpp:30-53) with the
+ * direction fused: the gradient G [rows, cols] (grad_dtype BL_BF16 / BL_F32 / BL_F16) is read once by the update
+ * kernel and the fp32 direction is never written to memory. D = U / max(rms(U)/clip, 1) with U = G, sign(G) or
+ * G / (sqrt(mean_rows(G^2)) + 1e-30) (bitlattice/_ops.py:135-144, bitlattice/reference.py:488-490). Scales are
+ * updated in place. Directions other than sign with clip >= 1 first reduce column statistics into `scratch`
+ * (fixed reduction order: 128-row panels summed sequentially, then panels in ascending order). */
+BL_API int bl_nvfp4_lattice_update(uint8_t* codes, uint8_t* phase, uint8_t* scales, const float* global_scale,
+                            const void* grad, int grad_dtype, int64_t rows, int64_t cols, uint64_t offset,
+                            int phase_bits, int phase_cb, double lr, double decay, int rounding, uint32_t seed,
+                            uint32_t step, int strat_j, int strat_k, int rule, double kappa, int direction,
+                            double clip, void* scratch, size_t scratch_bytes, int device, bl_stream_t stream);
+
+/* Replaces torch.ops.bitlattice.direction for raw / sign / colnorm (csrc/bindings.cpp:90-92,
+ * csrc/directions.cpp:145-191): writes the fp32 direction D [rows, cols]. */
+BL_API int bl_direction(const void* grad, int grad_dtype, int64_t rows, int64_t cols, int direction, double clip, float* D,
+                 void* scratch, size_t scratch_bytes, int device, bl_stream_t stream);
+
+/* ---- storage <-> dense ---------------------------------------------------------------------------------------- */
+
+/* Replaces torch.ops.bitlattice.dequantize for NVFP4 (csrc/bindings.cpp:86-88, csrc/lattice.cu:323-339,466-492):
+ * out[r][c] = level * (scale * global) in out_dtype. */
+BL_API int bl_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales, const float* global_scale, int64_t rows,
+                        int64_t cols, void* out, int out_dtype, int device, bl_stream_t stream);
+
+/* ---- operand quantizers --------------------------------------------------------------------------------------- */
+
+/* The amax pass of bitlattice/backend.py:240-241: out[0] = max|x|, out[1] = max(out[0] / (6*448), 1e-12) (the
+ * per-tensor scale), out[2..3] are used as a counter. out: 4 floats. */
+BL_API int bl_nvfp4_amax(const void* x, int dtype, int64_t n, float* out, int device, bl_stream_t stream);
+
+/* Replaces torch.ops.bitlattice.quantize_nvfp4 (csrc/bindings.cpp:96, csrc/act_quant.cu:180-225): x [rows, cols]
+ * -> codes [rows, cols/2] + scales, blocks of 16 along cols, against the per-tensor scale *global_scale.
+ * seed < 0: round to nearest, ties to the lower level, v / (scale*global) (== bitlattice/reference.py:164-235).
+ * seed >= 0: stochastic rounding with u = hash(flat index, seed, step), v * (1/(scale*global))
+ * (== bitlattice/fp4ref.py:71-78,135-137). sf_layout BL_SF_BLOCKED needs
+ * bl_blocked_scale_bytes(rows, cols/16) bytes and receives the zero padding too. cols % 16 == 0. */
+BL_API int bl_nvfp4_quantize(const void* x, int dtype, int64_t rows, int64_t cols, const float* global_scale, int64_t seed,
+                      uint32_t step, uint8_t* codes, uint8_t* scales, int sf_layout, int device, bl_stream_t stream);
+
+/* Replaces torch.ops.bitlattice.quantize_nvfp4_t (csrc/bindings.cpp:97-98, csrc/act_quant.cu:100-148,230-270):
+ * x [M, K] -> NVFP4 of x^T, codes [K, M/2] + scales over [K, M/16], blocks of 16 along M, each block optionally
+ * rotated v <- v H (H: fp32 [16,16] or NULL; sequential sum over the 16 inputs). global_bound (device, [1]): a
+ * bound on the rotated tensor's per-tensor scale, used as max(bound*2688/2688, 1e-12); NULL: an amax pass over the
+ * rotated tensor finds it (amax_scratch: 4 floats). global_out [1] receives the scale used. M % 16 == 0. */
+BL_API int bl_nvfp4_quantize_t(const void* x, int dtype, int64_t M, int64_t K, const float* H, int64_t seed, uint32_t step,
+                        const float* global_bound, float* amax_scratch, uint8_t* codes, uint8_t* scales,
+                        float* global_out, int sf_layout, int device, bl_stream_t stream);
+
+/* Replaces torch.ops.bitlattice.requantize_nvfp4_t (csrc/bindings.cpp:99, csrc/act_quant.cu:150-175,273-294):
+ * NVFP4 W [N, K] -> NVFP4 of W^T, codes [K, N/2] + scales over [K, N/16], same per-tensor scale (copied to
+ * global_out). N % 16 == 0, K % 16 == 0. */
+BL_API int bl_nvfp4_requantize_t(const uint8_t* codes, const uint8_t* scales, const float* global_scale, int64_t N, int64_t K,
+                          uint8_t* out_codes, uint8_t* out_scales, float* global_out, int sf_layout, int device,
+                          bl_stream_t stream);
+
+/* Bytes of a blocked scale buffer for [rows, cols16] scales. */
+BL_API size_t bl_blocked_scale_bytes(int64_t rows, int64_t cols16);
+
+/* Replaces bitlattice.backend.to_blocked (bitlattice/backend.py:179-188): row-major scale bytes [rows, cols16] ->
+ * blocked layout with zero padding. */
+BL_API int bl_nvfp4_scales_to_blocked(const uint8_t* scales, int64_t rows, int64_t cols16, uint8_t* out, int device,
+                               bl_stream_t stream);
+
+/* ---- GEMM ----------------------------------------------------------------------------------------------------- */
+
+/* Replaces bitlattice.backend.fp4_mm, i.e. torch._scaled_mm / F.scaled_mm on NVFP4 operands plus the per-tensor
+ * scale kernel (bitlattice/backend.py:267-290, csrc/act_quant.cu:299-336):
+ *   out[m][n] = (*a_global * *b_global) * sum_k A[m][k] * B[n][k],  A [M, K], B [N, K], both K-major NVFP4
+ * on tcgen05 block-scaled FP4 tensor cores with fp32 accumulation in tensor memory. a_sf / b_sf: blocked scales.
+ * out: [M, N] in out_dtype, row stride ldc elements. K % 32 == 0, N % 8 == 0. */
+BL_API int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const float* a_global, const uint8_t* b_codes,
+                  const uint8_t* b_sf, const float* b_global, int64_t M, int64_t N, int64_t K, void* out,
+                  int out_dtype, int64_t ldc, int device, bl_stream_t stream);
+
+/* Every wait inside the GEMM kernel is bounded; when one expires the kernel records which (1 producer, 2 MMA issuer,
+ * 3 epilogue), frees its tensor memory and returns. This call synchronizes `device`, stores the recorded code
+ * (0: none) in *status and clears it. No counterpart in the reference (cuBLASLt reports nothing of the kind). */
+BL_API int bl_nvfp4_gemm_status(int* status, int device);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* BITLATTICE_B200_H */

@@ -1,0 +1,318 @@
+"""CUDA kernels (through the C ABI) against the CPU oracle and the reference's golden vectors.
+
+Bit-exact (torch.equal) for codes, scale bytes, phase bytes and fp32 directions; the GEMM is compared with the
+oracle's double-precision contraction of the dequantized operands within bf16 rounding (tolerances in the test).
+"""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden
+
+import oracle
+from bitlattice_b200 import _ops
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def dev(a, dtype=None):
+    t = torch.from_numpy(np.ascontiguousarray(a)) if isinstance(a, np.ndarray) else a
+    if dtype is not None:
+        t = t.to(dtype)
+    return t.to(DEV).contiguous()
+
+
+def host(t):
+    return t.detach().cpu().contiguous().view(torch.uint8).numpy() if t.dtype == torch.float8_e4m3fn else \
+        t.detach().cpu().contiguous().numpy()
+
+
+def nvfp4_weights(rows, cols, seed):
+    w = (torch.randn(rows, cols, generator=gen(seed)) * 0.02).numpy()
+    codes, scales, g = oracle.quantize_rows(w, None, "rtn")
+    return codes, scales, float(g)
+
+
+# ------------------------------------------------------------------------------------------------ lattice update
+
+def _golden_step_names():
+    return [str(n) for n in golden("step")["names"]]
+
+
+@pytest.mark.parametrize("name", _golden_step_names())
+def test_step_quantized_matches_reference_golden(name):
+    g = golden("step")
+    bits = int(name.split("_")[0][1:])
+    rule = "fit_latent" if "fit_latent" in name else name.split("_")[1]
+    rounding = name.split("_")[-1]
+    trust_lr = 1.0 if rounding == "sr" else 0.0
+    packed = dev(g["codes"])
+    phase = dev(g[f"phase_in_b{bits}"]) if bits else None
+    fmt = "nvfp4"
+    scales = _ops.step_quantized(packed, phase, dev(g["scales"]), dev(g["g"]), None, dev(g["D"]), fmt, 16, 128,
+                                 lr=float(g["lr"][0]), weight_decay=0.01, phase_bits=bits,
+                                 phase_cb=_ops.phase_container(bits), rounding=rounding, seed=7, step=3, strata=16,
+                                 scale_rule=rule, trust=0.1 if trust_lr == 0.0 else 0.01, trust_lr=trust_lr)
+    assert np.array_equal(host(scales), g[name + "_scales"])
+    assert np.array_equal(host(packed), g[name + "_codes"])
+    if bits:
+        assert np.array_equal(host(phase), g[name + "_phase"])
+
+
+@pytest.mark.parametrize("bits", [0, 1, 2, 3, 4, 5, 8])
+@pytest.mark.parametrize("rule", ["fixed", "fit", "fit_latent"])
+def test_step_quantized_matches_oracle(bits, rule):
+    rows, cols = 96, 272                       # cols/8 = 34 chunks: ragged against the 32-wide thread rows
+    codes, scales, g = nvfp4_weights(rows, cols, 1)
+    cb = _ops.phase_container(bits)
+    half = 1 << max(bits - 1, 0)
+    ph = None
+    if bits:
+        from bitlattice_b200.packing import pack
+        raw = torch.randint(-half, half, (rows, cols), generator=gen(2 + bits), dtype=torch.int32)
+        ph = pack(raw & ((1 << bits) - 1), cb).numpy()
+    D = torch.randn(rows, cols, generator=gen(3)).numpy()
+    se = oracle.e4m3_decode(scales).mean() * g
+    kw = dict(lr=0.3 * float(se), weight_decay=0.01, phase_bits=bits, rounding="sr", seed=7, step=3,
+              scale_rule=rule, trust=0.1, trust_lr=0.0)
+    rc, rp, rs = oracle.lattice_step(codes, ph, scales, g, D, offset=12345, **kw)
+    packed, phase = dev(codes), (dev(ph) if bits else None)
+    new_scales = _ops.step_quantized(packed, phase, dev(scales), dev(np.array([g], np.float32)), None, dev(D), "nvfp4",
+                                     rows, cols, phase_cb=cb, strata=16, offset=12345, **kw)
+    assert np.array_equal(host(new_scales), rs)
+    assert np.array_equal(host(packed), rc)
+    if bits:
+        assert np.array_equal(host(phase), rp)
+    if rule != "fixed":
+        assert (rs != scales).mean() > 0.05          # the refit is exercised
+
+
+@pytest.mark.parametrize("direction", ["sign", "raw", "colnorm"])
+@pytest.mark.parametrize("clip", [1.0, 0.25])
+@pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32])
+def test_fused_update_matches_oracle(direction, clip, gdtype):
+    rows, cols = 300, 512                       # three row panels of the column statistics, the last one short
+    codes, scales, g = nvfp4_weights(rows, cols, 4)
+    G = (torch.randn(rows, cols, generator=gen(5)) * (3.0 if direction == "raw" else 1e-3)).to(gdtype)
+    G[3, 5] = 0.0
+    D, (rho, div) = oracle.direction(G.float().numpy(), direction, clip)
+    kw = dict(lr=3e-3, weight_decay=0.0, phase_bits=4, rounding="sr", seed=1234, step=1, scale_rule="fit", trust=0.1,
+              trust_lr=0.0)
+    ph0 = np.zeros((rows, cols // 2), np.uint8)
+    rc, rp, rs = oracle.lattice_step(codes, ph0, scales, g, D, **kw)
+    packed, phase, sc = dev(codes), dev(ph0), dev(scales)
+    _ops.lattice_update(packed, phase, sc, dev(np.array([g], np.float32)), None, dev(G), "nvfp4", rows, cols,
+                        phase_cb=4, strata=16, direction=direction, clip=clip, **kw)
+    assert np.array_equal(host(sc), rs)
+    assert np.array_equal(host(packed), rc)
+    assert np.array_equal(host(phase), rp)
+    # and the direction operator on its own, bit for bit
+    Dg = _ops.direction(dev(G), direction, clip=clip)
+    assert np.array_equal(host(Dg), D)
+
+
+def test_direction_close_to_reference_golden():
+    g = golden("direction")
+    for kind in ("raw", "sign", "colnorm"):
+        for clip in (1.0, 0.25):
+            D = host(_ops.direction(dev(g["G"], torch.bfloat16), kind, clip=clip))
+            ref = g[f"{kind}_clip{clip}"]
+            if kind == "sign" and clip >= 1.0:
+                assert np.array_equal(D, ref)
+            else:
+                np.testing.assert_allclose(D, ref, rtol=4e-7, atol=0.0)
+
+
+def test_row_shards_reproduce_the_whole_update():
+    """A row shard updated with offset = first_row * cols equals the same rows of the unsharded update
+    (the reference's row tiles, csrc/update.cpp:50; the N-sharded layers rely on it)."""
+    rows, cols = 256, 1024
+    codes, scales, g = nvfp4_weights(rows, cols, 6)
+    G = (torch.randn(rows, cols, generator=gen(7)) * 1e-3).to(torch.bfloat16)
+    gs = dev(np.array([g], np.float32))
+    kw = dict(lr=3e-3, weight_decay=0.0, phase_bits=4, phase_cb=4, rounding="sr", seed=99, step=2, strata=16,
+              scale_rule="fit", trust=0.1, trust_lr=0.0, direction="sign")
+    whole = [dev(codes), dev(np.zeros((rows, cols // 2), np.uint8)), dev(scales)]
+    _ops.lattice_update(whole[0], whole[1], whole[2], gs, None, dev(G), "nvfp4", rows, cols, **kw)
+    for r0, r1 in ((0, 64), (64, 256)):
+        part = [dev(codes[r0:r1]), dev(np.zeros((r1 - r0, cols // 2), np.uint8)), dev(scales[r0:r1])]
+        _ops.lattice_update(part[0], part[1], part[2], gs, None, dev(G[r0:r1]), "nvfp4", r1 - r0, cols,
+                            offset=r0 * cols, **kw)
+        for a, b in zip(part, whole):
+            assert torch.equal(a, b[r0:r1])
+
+
+def test_update_rejects_bad_arguments():
+    codes, scales, g = nvfp4_weights(16, 64, 8)
+    gs = dev(np.array([g], np.float32))
+    kw = dict(lr=1e-3, weight_decay=0.0, phase_bits=0, phase_cb=0, rounding="sr", seed=0, step=1, strata=16,
+              scale_rule="fit", trust=0.1, trust_lr=0.0)
+    with pytest.raises(RuntimeError, match="multiple of 16"):
+        _ops.lattice_update(dev(codes)[:, :28].contiguous(), None, dev(scales), gs, None,
+                            torch.zeros(16, 56, device=DEV, dtype=torch.bfloat16), "nvfp4", 16, 56,
+                            direction="sign", **kw)
+    with pytest.raises(RuntimeError, match="outside this build"):
+        _ops.lattice_update(dev(codes), None, dev(scales), gs, None,
+                            torch.zeros(16, 64, device=DEV, dtype=torch.bfloat16), "nvfp4", 16, 64,
+                            direction="muon", **kw)
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        _ops.lattice_update(torch.from_numpy(codes), None, dev(scales), gs, None,
+                            torch.zeros(16, 64, device=DEV, dtype=torch.bfloat16), "nvfp4", 16, 64,
+                            direction="sign", **kw)
+
+
+# ------------------------------------------------------------------------------------------------ quantizers
+
+def test_activation_quantizer_matches_reference_golden():
+    g = golden("quantize")
+    x = dev(g["rtn_x"])                 # fp32: the tie row is not representable in bf16
+    am = _ops.amax_global(x)
+    assert host(am)[1] == g["rtn_g"][0]
+    packed, scales = _ops.quantize_nvfp4(x, am[1:2])
+    assert np.array_equal(host(scales), g["rtn_scales"])
+    assert np.array_equal(host(packed), g["rtn_codes"])
+    deq = _ops.dequantize(packed, scales, am[1:2].clone(), None, "nvfp4", 32, 128, torch.float32)
+    assert np.array_equal(host(deq), g["rtn_deq_f32"])
+    deq16 = _ops.dequantize(packed, scales, am[1:2].clone(), None, "nvfp4", 32, 128, torch.bfloat16)
+    assert np.array_equal(host(deq16.view(torch.int16)), g["rtn_deq_bf16"])
+    for seed in (1, 77):
+        gy = dev(g["sr_x"], torch.bfloat16)
+        am = _ops.amax_global(gy)
+        assert host(am)[1] == g[f"sr{seed}_g"][0]
+        packed, scales = _ops.quantize_nvfp4(gy, am[1:2], seed=seed)
+        assert np.array_equal(host(scales), g[f"sr{seed}_scales"])
+        assert np.array_equal(host(packed), g[f"sr{seed}_codes"])
+
+
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("mode", ["rtn", "sr"])
+def test_row_quantizer_matches_oracle(dtype, mode):
+    rows, cols = 77, 1040
+    x = (torch.randn(rows, cols, generator=gen(10)) * (1.0 if mode == "rtn" else 1e-2)).to(dtype)
+    x[5, 32:48] = 0.0
+    xf = x.float().numpy()
+    rc, rs, g = oracle.quantize_rows(xf, None, mode, seed=31)
+    am = _ops.amax_global(dev(x))
+    assert host(am)[0] == np.abs(xf).max() and host(am)[1] == g
+    packed, scales = _ops.quantize_nvfp4(dev(x), am[1:2], seed=31 if mode == "sr" else -1)
+    assert np.array_equal(host(scales), rs)
+    assert np.array_equal(host(packed), rc)
+    packed_b, blocked = _ops.quantize_nvfp4(dev(x), am[1:2], seed=31 if mode == "sr" else -1, blocked=True)
+    assert torch.equal(packed_b, packed)
+    assert np.array_equal(host(blocked), oracle.to_blocked(rs))
+    assert np.array_equal(host(_ops.to_blocked(scales.view(torch.uint8))), oracle.to_blocked(rs))
+
+
+def test_blocked_layout_matches_reference_golden():
+    g = golden("quantize")
+    assert np.array_equal(host(_ops.to_blocked(dev(g["blk_in"]))), g["blk_out"])
+
+
+@pytest.mark.parametrize("rot", ["rot", "plain"])
+@pytest.mark.parametrize("mode", ["rtn", "sr"])
+def test_transposed_quantizer_matches_reference_golden(rot, mode):
+    g = golden("transposed")
+    x = dev(g["t_x"], torch.bfloat16)
+    H = dev(g["H16"]) if rot == "rot" else None
+    packed, scales, gout = _ops.quantize_nvfp4_t(x, H, 9 if mode == "sr" else -1, 0, dev(g["t_bound"]))
+    assert host(gout)[0] == np.float32(oracle.global_from_bound(float(g["t_bound"][0])))
+    assert np.array_equal(host(scales), g[f"t_{rot}_{mode}_scales"])
+    assert np.array_equal(host(packed), g[f"t_{rot}_{mode}_codes"])
+
+
+@pytest.mark.parametrize("mode", ["rtn", "sr"])
+def test_transposed_quantizer_matches_oracle_ragged(mode):
+    M, K = 208, 200                                   # neither a multiple of the 128 x 64 staging tile
+    x = (torch.randn(M, K, generator=gen(11)) * 1e-2).to(torch.bfloat16)
+    H = oracle.hadamard16()
+    bound = oracle.global_from_amax(float(x.float().abs().max())) * 4.0
+    g = oracle.global_from_bound(bound)
+    rc, rs = oracle.quantize_t(x.float().numpy(), H, g, mode, seed=5)
+    packed, scales, gout = _ops.quantize_nvfp4_t(dev(x), dev(H), 5 if mode == "sr" else -1, 0,
+                                                 dev(np.array([bound], np.float32)))
+    assert host(gout)[0] == np.float32(g)
+    assert np.array_equal(host(scales), rs)
+    assert np.array_equal(host(packed), rc)
+    _, blocked, _ = _ops.quantize_nvfp4_t(dev(x), dev(H), 5 if mode == "sr" else -1, 0,
+                                          dev(np.array([bound], np.float32)), blocked=True)
+    assert np.array_equal(host(blocked), oracle.to_blocked(rs))
+    # without a bound the scale comes from an amax pass over the rotated tensor
+    packed2, scales2, g2 = _ops.quantize_nvfp4_t(dev(x), dev(H), -1, 0, None)
+    assert 0 < host(g2)[0] <= np.float32(g)
+
+
+def test_weight_transpose_requantization():
+    g = golden("transposed")
+    packed, scales, gout = _ops.requantize_nvfp4_t(dev(g["w_codes"]), dev(g["w_scales"]), dev(g["w_g"]))
+    assert host(gout)[0] == g["w_g"][0]
+    assert np.array_equal(host(scales), g["wt_scales"])
+    assert np.array_equal(host(packed), g["wt_codes"])
+    codes, sc, gs = nvfp4_weights(208, 160, 12)
+    rc, rs = oracle.requantize_t(codes, sc, gs)
+    packed, scales, _ = _ops.requantize_nvfp4_t(dev(codes), dev(sc), dev(np.array([gs], np.float32)))
+    assert np.array_equal(host(scales), rs) and np.array_equal(host(packed), rc)
+
+
+# ------------------------------------------------------------------------------------------------ GEMM
+
+def _operand(rows, K, seed, scale):
+    x = (torch.randn(rows, K, generator=gen(seed)) * scale).numpy()
+    codes, sf, g = oracle.quantize_rows(x, None, "rtn")
+    return codes, sf, float(g)
+
+
+@pytest.mark.parametrize("M,N,K", [(128, 128, 256), (128, 128, 64), (256, 384, 1024), (100, 136, 96), (48, 64, 128),
+                                   (1, 8, 32), (300, 520, 2048)])
+def test_gemm_matches_oracle(M, N, K):
+    """Tolerance: the tensor core accumulates exact E2M1 x E2M1 x UE4M3 x UE4M3 products in fp32 and the result is
+    rounded once to bf16 -> every element within 2^-8 relative (one bf16 ulp) of the double-precision contraction,
+    plus an absolute term for cancellation inside the fp32 accumulation."""
+    ac, asf, ga = _operand(M, K, 20, 1.0)
+    bc, bsf, gb = _operand(N, K, 21, 0.02)
+    ref = oracle.gemm_nt(ac, asf, ga, bc, bsf, gb)
+    y = _ops.nvfp4_gemm(dev(ac), _ops.to_blocked(dev(asf)), dev(np.array([ga], np.float32)), dev(bc),
+                        _ops.to_blocked(dev(bsf)), dev(np.array([gb], np.float32)))
+    assert _ops.gemm_status(0) == 0
+    got = y.float().cpu().numpy()
+    scale = np.abs(ref).max()
+    assert np.all(np.abs(got - ref) <= 2.0 ** -8 * np.abs(ref) + 2e-5 * scale), \
+        float(np.abs(got - ref).max() / scale)
+    yf = _ops.nvfp4_gemm(dev(ac), _ops.to_blocked(dev(asf)), dev(np.array([ga], np.float32)), dev(bc),
+                         _ops.to_blocked(dev(bsf)), dev(np.array([gb], np.float32)), out_dtype=torch.float32)
+    np.testing.assert_allclose(yf.cpu().numpy(), ref, rtol=2e-5, atol=2e-5 * scale)
+
+
+def test_gemm_is_linear_in_row_blocks_at_scale():
+    """Size-independent property at a layer-sized problem: the product of stacked operands is the stack of products
+    (bit for bit: tiles never mix rows), and equal inputs give equal outputs."""
+    M, N, K = 2048, 3072, 4096
+    g0 = torch.Generator(device=DEV).manual_seed(0)
+    a = torch.randint(0, 256, (M, K // 2), device=DEV, dtype=torch.uint8, generator=g0)
+    b = torch.randint(0, 256, (N, K // 2), device=DEV, dtype=torch.uint8, generator=g0)
+    asf = torch.randint(40, 72, (M, K // 16), device=DEV, dtype=torch.uint8, generator=g0)
+    bsf = torch.randint(40, 72, (N, K // 16), device=DEV, dtype=torch.uint8, generator=g0)
+    one = torch.ones(1, device=DEV)
+    full = _ops.nvfp4_gemm(a, _ops.to_blocked(asf), one, b, _ops.to_blocked(bsf), one)
+    again = _ops.nvfp4_gemm(a, _ops.to_blocked(asf), one, b, _ops.to_blocked(bsf), one)
+    assert torch.equal(full, again)
+    top = _ops.nvfp4_gemm(a[:1024].contiguous(), _ops.to_blocked(asf[:1024].contiguous()), one, b,
+                          _ops.to_blocked(bsf), one)
+    assert torch.equal(top, full[:1024])
+    right = _ops.nvfp4_gemm(a, _ops.to_blocked(asf), one, b[1024:].contiguous(),
+                            _ops.to_blocked(bsf[1024:].contiguous()), one)
+    assert torch.equal(right, full[:, 1024:])
+    assert _ops.gemm_status(0) == 0
+    assert torch.isfinite(full.float()).all() and full.float().abs().max() > 0
+
+
+def test_gemm_rejects_bad_shapes():
+    one = torch.ones(1, device=DEV)
+    a = torch.zeros(16, 24, device=DEV, dtype=torch.uint8)      # K = 48
+    sf = torch.zeros(512, device=DEV, dtype=torch.uint8)
+    with pytest.raises(RuntimeError, match="multiple of 32"):
+        _ops.nvfp4_gemm(a, sf, one, a, sf, one)
