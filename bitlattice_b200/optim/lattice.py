@@ -1,0 +1,236 @@
+"""Lattice optimizer for NVFP4 weights: every weight is updated directly in its storage format, without master
+weights (mirror of the reference's ``bitlattice/optim/lattice.py`` for the part on the hot path).
+
+One step of a parameter W with gradient G:
+    D = direction(G), RMS-clipped          sign | colnorm | raw
+    t = latent(W, phase) * (1 - lr*wd) - lr*D
+    refit the group scales inside the trust region, then project t back to (code, phase) with unbiased rounding.
+Direction, scale refit and projection run as ONE pass over codes, phase and gradient on the GPU
+(``bl_nvfp4_lattice_update``); the fp32 direction is never materialised and no row tiling is needed.
+
+Same constructor, option names, validation errors, per-parameter seeds (``seed + 7919 * index``), step counters and
+state layout (``state[p]["phase"]``: uint8 [rows, cols * container_bits / 8]) as the reference, so optimizer state
+interchanges. Not built, and refused with NotImplementedError: Newton-Schulz / factored / sinkhorn directions,
+momentum, neuron-wise normalization, row-sparse gradients, native-format (non-lattice) parameters, host-memory state
+and the overlap worker.
+"""
+from __future__ import annotations
+
+import contextlib
+import threading
+from typing import Any
+
+import torch
+
+from .. import _ops
+from ..packing import packed_cols
+from ..tensor import LatticeTensor
+
+__all__ = ["DEFAULTS", "DIRECTIONS", "MOMENTA", "ROUNDINGS", "SCALE_RULES", "Lattice", "defer_fused_updates"]
+
+# windows in which no fused update is applied, across all optimizers and autograd threads (reference: lattice.py:33-45)
+_deferred = 0
+_deferred_lock = threading.Lock()
+
+
+def defer_fused_updates(delta: int) -> None:
+    """Open (+1) or close (-1) a window in which fused optimizers apply no update: gradients arriving meanwhile are
+    summed in ``.grad`` and applied by the next arrival outside every window, or by ``step()``."""
+    global _deferred
+    with _deferred_lock:
+        _deferred = max(0, _deferred + delta)
+
+
+DIRECTIONS = ("muon_block", "muon", "factored", "sinkhorn", "colnorm", "sign", "raw")
+BUILT_DIRECTIONS = ("colnorm", "sign", "raw")
+MOMENTA = ("none", "fp32", "ternary", "bf16", "int8", "fp8", "nvfp4")
+ROUNDINGS = ("sr", "strat", "rtn")
+SCALE_RULES = ("fit", "fit_latent", "fixed")
+
+DEFAULTS: dict[str, Any] = dict(
+    lr=3e-3, direction="muon_block", vector_direction="factored", phase_bits=2, rounding="sr", scale_rule="fit",
+    momentum="none", beta1=0.9, beta2=0.95, weight_decay=0.0, clip=1.0, block=512, ns_steps=5, ns_dtype="bf16",
+    ns_coeffs="muon", ns_algo="auto", sinkhorn_iters=2, trust=0.01, trust_lr=1.0, strata=16, tile_elems=1 << 24,
+    normalize="none", row_beta=0.95, row_eps=1e-8,
+)
+
+
+def _validate(g: dict) -> None:
+    """Same checks, same exception types as the reference (lattice.py:62-76); then what this build leaves out."""
+    for key, allowed in (("direction", DIRECTIONS), ("vector_direction", DIRECTIONS), ("momentum", MOMENTA),
+                         ("rounding", ROUNDINGS), ("scale_rule", SCALE_RULES)):
+        if g[key] not in allowed:
+            raise ValueError(f"{key}={g[key]!r}; expected one of {allowed}")
+    if not 0 <= g["phase_bits"] <= 8:
+        raise ValueError("phase_bits must be in [0, 8]")
+    if g["vector_direction"] in ("muon", "muon_block"):
+        raise ValueError("vector_direction cannot be a matrix direction")
+    if g["normalize"] not in ("none", "row"):
+        raise ValueError("normalize must be 'none' or 'row'")
+    if g["direction"] not in BUILT_DIRECTIONS:
+        raise NotImplementedError(f"direction={g['direction']!r} is outside this build; built: {BUILT_DIRECTIONS} "
+                                  "(pass direction= explicitly: the reference's default 'muon_block' is not built)")
+    if g["momentum"] != "none":
+        raise NotImplementedError("momentum is outside this build (momentum='none' is built)")
+    if g["normalize"] != "none":
+        raise NotImplementedError("neuron-wise normalization is outside this build")
+    for p in g["params"]:
+        if not isinstance(p, LatticeTensor):
+            raise NotImplementedError("only NVFP4 LatticeTensor parameters are built; native-format parameters "
+                                      f"(shape {tuple(p.shape)}, {p.dtype}) need the reference's native step")
+        if not _ops.cuda_ok(p.fmt, p.rows, p.cols, p.packed.device):
+            raise RuntimeError(f"parameter of shape {tuple(p.shape)} on {p.packed.device}: the update kernels need an "
+                               "NVFP4 weight on a CUDA device with rows made of 16-element groups")
+
+
+class Lattice(torch.optim.Optimizer):
+    """The Lattice optimizer (reference: bitlattice/optim/lattice.py:125-145).
+
+    ``params``          an iterable of LatticeTensor parameters or param-group dicts (any key of ``DEFAULTS`` per group)
+    ``fused_backward``  apply each parameter's update as soon as its gradient is accumulated and free the gradient
+                        (the step then only advances); peak memory holds one gradient
+    ``seed``            base of the per-parameter RNG seeds: parameter number i uses (seed + 7919 * i) mod 2^32
+    A parameter that is a row shard of a larger weight sets ``p._bl_row_offset`` to its first global row: the update
+    then draws the random numbers of the unsharded tensor (as the reference's row tiles do, csrc/update.cpp:50).
+    """
+
+    def __init__(self, params, preset: str | None = None, *, lr: float = DEFAULTS["lr"], state: str = "gpu",
+                 fused_backward: bool = False, seed: int = 0, weight_decay: float = 0.0, overlap: bool = False,
+                 **options):
+        from .presets import PRESETS, REFERENCE_PRESETS
+        if preset is not None:
+            if preset in REFERENCE_PRESETS:
+                raise NotImplementedError(f"preset {preset!r} uses directions outside this build")
+            if preset not in PRESETS:
+                raise KeyError(f"unknown preset {preset!r}; known: {sorted(PRESETS)}")
+            options = {**PRESETS[preset], **options}
+        options.pop("head_momentum", None)
+        unknown = set(options) - set(DEFAULTS)
+        if unknown:
+            raise TypeError(f"unknown options {sorted(unknown)}")
+        if isinstance(params, torch.nn.Module):
+            params = [p for p in params.parameters() if p.requires_grad]
+        defaults = {**DEFAULTS, **options, "lr": lr, "weight_decay": options.get("weight_decay", weight_decay)}
+        super().__init__(params, defaults)
+        if state not in ("gpu", "ram", "auto"):
+            raise ValueError("state must be 'gpu', 'ram' or 'auto'")
+        if state != "gpu":
+            raise NotImplementedError("optimizer state in host memory is outside this build (state='gpu' is built)")
+        if overlap:
+            raise NotImplementedError("the overlap worker is outside this build")
+        for g in self.param_groups:
+            _validate(g)
+        self.state_placement = "gpu"
+        self.seed = int(seed)
+        self.fused_backward = fused_backward
+        self.overlap = False
+        self._pid = {}
+        for g in self.param_groups:
+            for p in g["params"]:
+                self._pid[p] = len(self._pid)
+        self._group_of = {p: g for g in self.param_groups for p in g["params"]}
+        self._done: set = set()
+        self._defer = 0
+        self._hooks = []
+        if fused_backward:
+            for p in self._pid:
+                if p.requires_grad:
+                    self._hooks.append(p.register_post_accumulate_grad_hook(self._on_grad))
+
+    # fused backward: the hook runs on the autograd thread that accumulated the gradient
+
+    def _on_grad(self, p: torch.Tensor) -> None:
+        if p.grad is None or self._defer or _deferred:
+            return
+        with torch.no_grad():
+            self._update(p, self._group_of[p])
+        p.grad = None
+        self._done.add(p)
+
+    @staticmethod
+    def _invalidate(p: torch.Tensor) -> None:
+        p._bl_version = getattr(p, "_bl_version", 0) + 1          # derived GEMM operands of the old version are stale
+        from ..backend import drop_cached
+        drop_cached(p)
+
+    def wait(self) -> None:
+        """Updates are issued on the caller's stream, in order: nothing to wait for."""
+
+    def synchronize(self) -> None:
+        for dev in {p.device for p in self._pid if p.is_cuda}:
+            torch.cuda.synchronize(dev)
+
+    @torch.no_grad()
+    def step(self, closure=None):
+        loss = None
+        if closure is not None:
+            with torch.enable_grad():
+                loss = closure()
+        for g in self.param_groups:
+            for p in g["params"]:
+                if p in self._done or p.grad is None:
+                    continue
+                with torch.cuda.device(p.device):
+                    self._update(p, g)
+                if self.fused_backward:
+                    p.grad = None
+        self._done.clear()
+        return loss
+
+    @contextlib.contextmanager
+    def accumulate(self):
+        """Gradient accumulation with ``fused_backward``: inside the context gradients are summed in ``.grad`` and no
+        update is applied; the next backward pass outside the context applies the update with the total."""
+        self._defer += 1
+        try:
+            yield
+        finally:
+            self._defer -= 1
+
+    def state_dict(self):
+        self.synchronize()
+        return super().state_dict()
+
+    def zero_grad(self, set_to_none: bool = True):
+        super().zero_grad(set_to_none=True)
+
+    def remove_hooks(self) -> None:
+        for h in self._hooks:
+            h.remove()
+        self._hooks.clear()
+
+    def _update(self, p: LatticeTensor, g: dict, G: torch.Tensor | None = None) -> None:
+        self._invalidate(p)
+        st = self.state[p]
+        st["step"] = st.get("step", 0) + 1
+        seed = (self.seed + 7919 * self._pid[p]) & 0xFFFFFFFF
+        G = p.grad if G is None else G
+        if G.is_sparse:
+            raise NotImplementedError("row-sparse gradients are outside this build")
+        rows, cols = p.rows, p.cols
+        bits = g["phase_bits"]
+        cb = _ops.phase_container(bits)
+        if bits and "phase" not in st:
+            st["phase"] = torch.zeros(rows, packed_cols(cols, cb), dtype=torch.uint8, device=p.packed.device)
+        G2 = G.reshape(rows, cols)
+        if G2.dtype not in (torch.bfloat16, torch.float16, torch.float32):
+            G2 = G2.float()
+        _ops.lattice_update(p.packed, st.get("phase") if bits else None, p.scales, p.global_scale, None,
+                            G2.contiguous(), p.fmt, rows, cols, lr=g["lr"], weight_decay=g["weight_decay"],
+                            phase_bits=bits, phase_cb=cb, rounding=g["rounding"], seed=seed, step=st["step"],
+                            strata=g["strata"], scale_rule=g["scale_rule"], trust=g["trust"], trust_lr=g["trust_lr"],
+                            direction=g["direction"], clip=g["clip"],
+                            offset=int(getattr(p, "_bl_row_offset", 0)) * cols)
+
+    def state_bits(self) -> dict[str, float]:
+        """Logical optimizer state in bits, by component (only the phase exists in this build)."""
+        out = {"phase": 0.0, "factors": 0.0, "momentum": 0.0}
+        for g in self.param_groups:
+            for p in g["params"]:
+                out["phase"] += p.numel() * g["phase_bits"]
+        out["total"] = sum(out.values())
+        return out
+
+    def state_bytes(self) -> int:
+        return sum(v.numel() * v.element_size() for st in self.state.values() for v in st.values()
+                   if torch.is_tensor(v))

@@ -1,0 +1,225 @@
+"""LatticeTensor: a torch.Tensor subclass holding a weight as NVFP4 storage.
+
+Mirror of the reference's ``bitlattice/tensor.py`` for the linear-layer path: the logical tensor (shape, dtype) is what
+PyTorch code sees; the storage is ``packed`` E2M1 codes, ``scales`` (E4M3 per 16 elements) and ``global_scale``
+(fp32 [1]) in exactly the reference's layout, so checkpoints and optimizer state interchange. ``F.linear`` with a
+LatticeTensor weight goes through :class:`_LatticeLinear`; any other operator sees the dequantized weight.
+
+Quantization and dequantization run on the GPU kernels of this package (there is no CPU path): ``from_float`` needs a
+CUDA tensor. Only ``method="rtn"`` is built (the reference's default ``"mse"`` search is a set-up time choice outside
+the hot path); high-precision columns (``keep``) and zero points are not part of NVFP4 and are not built.
+"""
+from __future__ import annotations
+
+import torch
+from torch.utils._pytree import tree_map
+
+from . import _ops
+from . import formats as F
+
+__all__ = ["LatticeTensor", "is_lattice", "to_parameter"]
+
+_PARTS = ("packed", "scales", "global_scale")
+
+
+def is_lattice(t) -> bool:
+    return isinstance(t, LatticeTensor)
+
+
+class LatticeTensor(torch.Tensor):
+    packed: torch.Tensor
+    scales: torch.Tensor
+    global_scale: torch.Tensor
+    fmt: F.Format
+
+    @staticmethod
+    def __new__(cls, packed, scales, global_scale, zeros, fmt, shape, dtype=torch.bfloat16, hi_idx=None, hi_val=None,
+                requires_grad=False):
+        if zeros is not None or hi_idx is not None or hi_val is not None:
+            raise ValueError("zero points and high-precision columns are not part of the NVFP4 path")
+        t = torch.Tensor._make_wrapper_subclass(cls, torch.Size(shape), dtype=dtype, device=packed.device,
+                                                requires_grad=requires_grad)
+        t.packed, t.scales, t.global_scale = packed, scales, global_scale
+        t.zeros = t.hi_idx = t.hi_val = None
+        t.fmt = F.get(fmt)
+        t.compute = None                 # a bitlattice_b200.Compute, or None: exact
+        return t
+
+    def __init__(self, *args, **kwargs):
+        super().__init__()
+
+    # construction
+
+    @classmethod
+    def from_float(cls, w: torch.Tensor, fmt="nvfp4", method: str = "rtn", keep: float = 0.0,
+                   dtype: torch.dtype | None = None, **unused) -> "LatticeTensor":
+        """Quantize a dense CUDA tensor: per-tensor scale amax/(6*448), E4M3 group scales amax16/6/global, codes by
+        round to nearest with ties to the lower level (== reference.quantize(w, "nvfp4", "rtn"))."""
+        fmt = F.get(fmt)
+        if method != "rtn":
+            raise NotImplementedError(f"quantization method {method!r} is outside this build; use method='rtn'")
+        if keep:
+            raise NotImplementedError("high-precision columns (keep > 0) are outside this build")
+        if not w.is_cuda:
+            raise RuntimeError("LatticeTensor.from_float needs a CUDA tensor (this build has no CPU path)")
+        w2 = (w.detach().reshape(1, -1) if w.dim() == 1 else w.detach().reshape(w.shape[0], -1)).float().contiguous()
+        am = _ops.amax_global(w2)
+        g = am[1:2].clone()
+        packed, scales = _ops.quantize_nvfp4(w2, g, -1, 0)
+        logical = dtype or (w.dtype if w.dtype.is_floating_point else torch.bfloat16)
+        return cls(packed, scales, g, None, fmt, w.shape, logical)
+
+    # views of the storage
+
+    @property
+    def rows(self) -> int:
+        return 1 if self.dim() == 1 else self.shape[0]
+
+    @property
+    def cols(self) -> int:
+        return self.numel() // self.rows
+
+    def parts(self) -> dict:
+        return {k: getattr(self, k) for k in _PARTS}
+
+    def dequantize(self, dtype: torch.dtype | None = None) -> torch.Tensor:
+        dtype = dtype or self.dtype
+        kd = dtype if dtype in (torch.float32, torch.bfloat16, torch.float16) else torch.float32
+        w = _ops.dequantize(self.packed, self.scales, self.global_scale, None, self.fmt, self.rows, self.cols, kd)
+        return w.to(dtype).reshape(self.shape)
+
+    def storage_bytes(self) -> int:
+        return sum(t.numel() * t.element_size() for t in self.parts().values())
+
+    def __repr__(self, *, tensor_contents=None) -> str:
+        return (f"LatticeTensor(shape={tuple(self.shape)}, format={self.fmt.name}, dtype={self.dtype}, "
+                f"device={self.device})")
+
+    def __tensor_flatten__(self):
+        return list(_PARTS), (self.fmt, tuple(self.shape), self.dtype)
+
+    @staticmethod
+    def __tensor_unflatten__(inner, ctx, outer_size, outer_stride):
+        fmt, shape, dtype = ctx
+        return LatticeTensor(inner["packed"], inner["scales"], inner["global_scale"], None, fmt, shape, dtype)
+
+    def _map(self, fn, shape=None, dtype=None) -> "LatticeTensor":
+        t = LatticeTensor(fn(self.packed), fn(self.scales), fn(self.global_scale), None, self.fmt,
+                          shape or self.shape, dtype or self.dtype)
+        t.compute = self.compute
+        return t
+
+    # operator interception
+
+    @classmethod
+    def __torch_function__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        if func is torch.nn.functional.linear:
+            x, w = args[0], args[1]
+            b = args[2] if len(args) > 2 else kwargs.get("bias")
+            if isinstance(w, LatticeTensor) and not isinstance(x, LatticeTensor):
+                return _LatticeLinear.apply(x, w, b)
+        with torch._C.DisableTorchFunctionSubclass():
+            return func(*args, **kwargs)
+
+    @classmethod
+    def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
+        kwargs = kwargs or {}
+        aten = torch.ops.aten
+        if func in (aten.detach.default, aten.alias.default):
+            return args[0]._map(lambda t: t)
+        if func is aten.clone.default:
+            return args[0]._map(lambda t: t.clone())
+        if func is aten._to_copy.default:
+            src = args[0]
+            device = kwargs.get("device", src.device)
+            dtype = kwargs.get("dtype", src.dtype)
+            keep = dtype if dtype is not None and dtype.is_floating_point else src.dtype
+            return src._map(lambda t: t.to(device), dtype=keep)
+        if func is aten.copy_.default:
+            dst, src = args[0], args[1]
+            dst._bl_version = getattr(dst, "_bl_version", 0) + 1          # invalidates derived GEMM operands
+            if not (isinstance(src, LatticeTensor) and src.fmt == dst.fmt):
+                dense = src.dequantize(torch.float32) if isinstance(src, LatticeTensor) else src
+                src = LatticeTensor.from_float(dense.to(dst.device), dst.fmt, method="rtn", dtype=dst.dtype)
+            for k in _PARTS:
+                d, s = getattr(dst, k), getattr(src, k)
+                if d.shape == s.shape:
+                    d.copy_(s)
+                else:
+                    setattr(dst, k, s.to(dst.device).clone())
+            return dst
+        if func is aten.is_same_size.default:
+            return args[0].shape == args[1].shape
+
+        def unwrap(t):
+            return t.dequantize() if isinstance(t, LatticeTensor) else t
+
+        return func(*tree_map(unwrap, args), **tree_map(unwrap, kwargs))
+
+
+class _LatticeLinear(torch.autograd.Function):
+    """y = x W^T + b for a lattice weight; the route (exact / fp4 / fp4_all) comes from the compute policy
+    (reference: bitlattice/tensor.py:204-288)."""
+
+    @staticmethod
+    def forward(ctx, x, w: LatticeTensor, bias):
+        from . import backend
+        from .compute_policy import route
+        ctx.w = w
+        ctx.has_bias = bias is not None
+        ctx.policy, comp = route(x, w)
+        ctx.recipe = comp.nvfp4                     # backward runs on other threads: keep the forward's choice
+        need_w = ctx.needs_input_grad[1]
+        if ctx.policy == "fp4_all":
+            ctx.x_meta = (x.shape, x.dtype)
+            if need_w:
+                y, xt = backend.fp4_forward_saving(x, w, bias, ctx.recipe)
+                meta = torch.tensor([int(xt.blocked), xt.rotate_seed], dtype=torch.int64)
+                ctx.save_for_backward(xt.packed, xt.scales, xt.global_scale, meta)
+                return y
+            ctx.save_for_backward()
+            return backend.nvfp4_linear(x, w, bias, ctx.recipe)
+        ctx.save_for_backward(x if need_w else None)
+        if ctx.policy == "fp4":
+            return backend.nvfp4_linear(x, w, bias, ctx.recipe)
+        return torch.nn.functional.linear(x, w.dequantize(x.dtype), bias)
+
+    @staticmethod
+    def backward(ctx, gy):
+        w = ctx.w
+        gb = gy.reshape(-1, gy.shape[-1]).sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        if ctx.policy == "fp4_all":
+            from . import backend
+            shape, dtype = ctx.x_meta
+            saved = ctx.saved_tensors
+            xt = None
+            if saved:
+                blocked, seed = saved[3].tolist()
+                xt = backend.Fp4Operand(saved[0], saved[1], saved[2], bool(blocked), seed)
+            gx, gw = backend.fp4_backward(gy, w, xt, ctx.needs_input_grad[0],
+                                          ctx.needs_input_grad[1] and xt is not None, ctx.recipe)
+            gx = gx.to(dtype).reshape(shape) if gx is not None else None
+            gw = gw.to(w.dtype) if gw is not None else None
+            return gx, gw, gb
+        (x,) = ctx.saved_tensors
+        W = w.dequantize(gy.dtype)
+        gx = gy @ W if ctx.needs_input_grad[0] else None
+        gw = None
+        if ctx.needs_input_grad[1] and x is not None:
+            gw = (gy.reshape(-1, gy.shape[-1]).t() @ x.reshape(-1, x.shape[-1])).to(w.dtype)
+        return gx, gw, gb
+
+
+def to_parameter(t: LatticeTensor, requires_grad: bool = True) -> torch.nn.Parameter:
+    return torch.nn.Parameter(t, requires_grad=requires_grad)
+
+
+def _register_safe_globals() -> None:
+    """Allow torch.load(weights_only=True) of state dicts containing LatticeTensor."""
+    add = getattr(torch.serialization, "add_safe_globals", None)
+    if add is not None:
+        add([LatticeTensor, F.TableFormat, F.ScaleSpec])
+
+
+_register_safe_globals()

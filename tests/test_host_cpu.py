@@ -1,0 +1,136 @@
+"""Host-side logic that needs no GPU: formats, packing, the compute policy, optimizer option checks, and that the
+product fails loudly (instead of falling back) when asked to compute without a CUDA device."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden
+
+import bitlattice_b200 as bl
+from bitlattice_b200 import _ops, formats as F
+from bitlattice_b200.packing import pack, packed_cols, sign_extend, unpack
+
+
+def cpu_weight(rows=32, cols=64, requires_grad=True):
+    import oracle
+    w = (torch.randn(rows, cols, generator=torch.Generator().manual_seed(0)) * 0.02).numpy()
+    codes, scales, g = oracle.quantize_rows(w, None, "rtn")
+    t = bl.LatticeTensor(torch.from_numpy(codes), torch.from_numpy(scales).view(torch.float8_e4m3fn),
+                         torch.tensor([g]), None, "nvfp4", (rows, cols), torch.bfloat16)
+    return torch.nn.Parameter(t, requires_grad=requires_grad)
+
+
+def test_nvfp4_tables_match_reference_format():
+    fmt = F.get("nvfp4")
+    t = fmt.tables()
+    assert fmt.levels == (-6.0, -4.0, -3.0, -2.0, -1.5, -1.0, -0.5, 0.0, 0.5, 1.0, 1.5, 2.0, 3.0, 4.0, 6.0)
+    assert t["rank"].tolist() == [7, 8, 9, 10, 11, 12, 13, 14, 7, 6, 5, 4, 3, 2, 1, 0]
+    assert t["sorted_code"].tolist() == [15, 14, 13, 12, 11, 10, 9, 0, 1, 2, 3, 4, 5, 6, 7]
+    assert fmt.scale.shape(8, 64) == (8, 4) and fmt.container_bits == 4
+    with pytest.raises(KeyError):
+        F.get("int4")
+    with pytest.raises(ValueError):
+        fmt.scale.groups_per_row(24)
+
+
+@pytest.mark.parametrize("bits", [1, 2, 4, 8])
+def test_packing_round_trip_and_layout(bits):
+    g = torch.Generator().manual_seed(bits)
+    codes = torch.randint(0, 1 << bits, (5, 64), generator=g, dtype=torch.int32)
+    p = pack(codes, bits)
+    assert p.dtype == torch.uint8 and p.shape == (5, packed_cols(64, bits))
+    assert torch.equal(unpack(p, bits, 64), codes)
+    if bits == 4:                                   # element 2j in the low nibble of byte j
+        assert int(p[0, 0]) == int(codes[0, 0]) | (int(codes[0, 1]) << 4)
+    half = 1 << (bits - 1)
+    signed = torch.arange(-half, half, dtype=torch.int32)
+    assert torch.equal(sign_extend(signed & ((1 << bits) - 1), bits), signed.long())
+    with pytest.raises(ValueError):
+        packed_cols(7, 4) if bits == 4 else packed_cols(63, bits) if bits != 8 else pack(codes, 16)
+
+
+def test_packing_matches_reference_golden_phase_bytes():
+    """The golden phase inputs were packed by the reference's own pack(); unpack -> pack reproduces them."""
+    g = golden("step")
+    for bits in (1, 2, 3, 4, 8):
+        cb = _ops.phase_container(bits)
+        raw = torch.from_numpy(g[f"phase_in_b{bits}"])
+        assert torch.equal(pack(unpack(raw, cb, 128), cb), raw)
+
+
+def test_phase_containers_and_trust_region():
+    assert [_ops.phase_container(b) for b in range(9)] == [0, 1, 2, 4, 4, 8, 8, 8, 8]
+    assert _ops.kappa(0.1, 1.0, 3e-3) == 3e-3 and _ops.kappa(0.1, 0.0, 3e-3) == 0.1
+    assert _ops.strat_args("strat", 5, 16) == (10, 16) and _ops.strat_args("sr", 5, 16) == (0, 1)
+
+
+def test_compute_policy_routes_and_requirements():
+    p = cpu_weight()
+    x = torch.zeros(4, 64, dtype=torch.bfloat16)
+    from bitlattice_b200.compute_policy import route
+    assert route(x, p)[0] == "exact"
+    with bl.compute("fp4_all"):
+        with pytest.raises(RuntimeError, match="not on a CUDA device"):
+            route(x, p)
+    assert bl.COMPUTE_PRESETS["fp4"].route == "fp4" and bl.COMPUTE_PRESETS["fp4_all"].route == "fp4_all"
+    with pytest.raises(ValueError):
+        bl.Compute("mxfp8")
+    with pytest.raises(ValueError):
+        bl.backend.Fp4Recipe(rotation=128)
+    with pytest.raises(ValueError):
+        bl.compute_policy.as_compute("quartet2")
+    bad = cpu_weight(rows=24, cols=64)
+    assert "multiple of 32" in bl.backend.fp4_unfit(bad, 0, True)
+    assert "multiple of 16" in bl.backend.fp4_unfit(bad, 0, False)
+
+
+def test_no_cpu_fallback_anywhere():
+    p = cpu_weight()
+    with pytest.raises(RuntimeError, match="CUDA tensor"):
+        p.dequantize()
+    with pytest.raises(RuntimeError, match="CUDA"):
+        torch.nn.functional.linear(torch.zeros(4, 64, dtype=torch.bfloat16), p)
+    with pytest.raises(RuntimeError, match="CUDA"):
+        bl.LatticeTensor.from_float(torch.zeros(32, 64), "nvfp4", method="rtn")
+    with pytest.raises(NotImplementedError):
+        bl.LatticeTensor.from_float(torch.zeros(32, 64), "nvfp4", method="mse")
+
+
+def test_optimizer_options_validated_like_the_reference():
+    p = cpu_weight()
+    with pytest.raises(ValueError):
+        bl.Lattice([p], direction="adam")
+    with pytest.raises(TypeError):
+        bl.Lattice([p], direction="sign", betas=(0.9, 0.99))
+    with pytest.raises(ValueError):
+        bl.Lattice([p], direction="sign", phase_bits=9)
+    with pytest.raises(ValueError):
+        bl.Lattice([p], direction="sign", state="disk")
+    with pytest.raises(KeyError):
+        bl.Lattice([p], "nonexistent")
+    for kw in (dict(), dict(direction="muon"), dict(direction="sign", momentum="bf16"),
+               dict(direction="sign", state="ram"), dict(direction="sign", overlap=True)):
+        with pytest.raises(NotImplementedError):
+            bl.Lattice([p], **kw)
+    with pytest.raises(NotImplementedError):
+        bl.Lattice([p], "muon")
+    with pytest.raises(NotImplementedError):
+        bl.Lattice([torch.nn.Parameter(torch.zeros(4, 16))], direction="sign")
+    with pytest.raises(RuntimeError, match="CUDA device"):
+        bl.Lattice([p], direction="sign")              # a CPU weight cannot be updated: no CPU path
+
+
+def test_lattice_tensor_container_semantics():
+    p = cpu_weight(requires_grad=False)
+    assert p.shape == (32, 64) and p.dtype == torch.bfloat16 and p.rows == 32 and p.cols == 64
+    assert p.storage_bytes() == 32 * 32 + 32 * 4 + 4
+    c = p.detach().clone()
+    assert bl.is_lattice(c) and torch.equal(c.packed, p.packed) and c.packed.data_ptr() != p.packed.data_ptr()
+    q = cpu_weight(requires_grad=False)
+    q.packed.zero_()
+    q.copy_(p)
+    assert torch.equal(q.packed, p.packed) and getattr(q, "_bl_version", 0) == 1
+    names, ctx = p.__tensor_flatten__()
+    assert names == ["packed", "scales", "global_scale"]
+    r = bl.LatticeTensor.__tensor_unflatten__(p.parts(), ctx, None, None)
+    assert torch.equal(r.scales.view(torch.uint8), p.scales.view(torch.uint8))

@@ -1,0 +1,254 @@
+"""The reference-facing Python layer on the GPU: LatticeTensor, the linear autograd function under the compute
+policy, and the Lattice optimizer, against golden vectors of the reference and the CPU oracle."""
+import numpy as np
+import pytest
+import torch
+
+from conftest import golden
+
+import bitlattice_b200 as bl
+import oracle
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda"
+
+
+def gen(seed):
+    return torch.Generator().manual_seed(seed)
+
+
+def rel(a, b):
+    return ((a.float() - b.float()).norm() / b.float().norm()).item()
+
+
+def lattice_from(codes, scales, g, shape, dtype=torch.bfloat16):
+    return bl.LatticeTensor(torch.from_numpy(np.ascontiguousarray(codes)).to(DEV),
+                            torch.from_numpy(np.ascontiguousarray(scales)).to(DEV).view(torch.float8_e4m3fn),
+                            torch.from_numpy(np.ascontiguousarray(g)).to(DEV), None, "nvfp4", shape, dtype)
+
+
+def test_from_float_and_dequantize_match_reference_golden():
+    g = golden("linear")
+    w = bl.LatticeTensor.from_float(torch.from_numpy(g["w"]).to(DEV), "nvfp4", method="rtn", dtype=torch.bfloat16)
+    assert np.array_equal(w.packed.cpu().numpy(), g["codes"])
+    assert np.array_equal(w.scales.view(torch.uint8).cpu().numpy(), g["scales"])
+    assert w.global_scale.cpu().numpy()[0] == g["g"][0]
+    q = golden("quantize")
+    t = lattice_from(q["rtn_codes"], q["rtn_scales"], q["rtn_g"], (32, 128))
+    assert np.array_equal(t.dequantize(torch.float32).cpu().numpy(), q["rtn_deq_f32"])
+    assert np.array_equal(t.dequantize().view(torch.int16).cpu().numpy(), q["rtn_deq_bf16"])
+
+
+def test_exact_route_matches_reference_golden():
+    """Tolerance: the reference values come from bf16 matmuls on the CPU, these from bf16 matmuls on the GPU; both
+    round the same exact products differently -> relative Frobenius error below 1e-2."""
+    g = golden("linear")
+    p = torch.nn.Parameter(lattice_from(g["codes"], g["scales"], g["g"], (64, 128)))
+    x = torch.from_numpy(g["x"]).to(DEV, torch.bfloat16).requires_grad_(True)
+    y = torch.nn.functional.linear(x, p)
+    y.backward(torch.from_numpy(g["gy"]).to(DEV, torch.bfloat16))
+    assert rel(y.detach().cpu(), torch.from_numpy(g["y"])) < 1e-2
+    assert rel(x.grad.cpu(), torch.from_numpy(g["gx"])) < 1e-2
+    assert rel(p.grad.cpu(), torch.from_numpy(g["gw"])) < 1e-2
+    assert p.grad.dtype == torch.bfloat16 and p.grad.shape == (64, 128)
+
+
+@pytest.mark.parametrize("M", [1, 7, 256])
+def test_fp4_linear_matches_quantized_reference(M):
+    """The reference's own bound (tests/test_backend.py:23-32): rel < 1e-2 against dequant(quant(x)) @ dequant(W)^T."""
+    x = torch.randn(M, 512, generator=gen(1)).to(torch.bfloat16)
+    w = bl.LatticeTensor.from_float((torch.randn(384, 512, generator=gen(2)) * 0.05).to(DEV), "nvfp4", method="rtn",
+                                    dtype=torch.bfloat16)
+    xc, xs, xg = oracle.quantize_rows(x.float().numpy(), None, "rtn")
+    ref = oracle.dequantize(xc, xs, xg) @ w.dequantize(torch.float32).cpu().numpy().T
+    with bl.compute("fp4"):
+        y = torch.nn.functional.linear(x.to(DEV), torch.nn.Parameter(w))
+    assert y.shape == (M, 384) and rel(y.cpu(), torch.from_numpy(ref)) < 1e-2
+    assert bl._ops.gemm_status(0) == 0
+
+
+@pytest.mark.parametrize("M", [5, 96, 512])
+def test_fp4_all_gradients_close_to_exact(M):
+    """The reference's bound (tests/test_backend.py:77-94): y, dx, dw within 0.25 relative error of the exact route."""
+    x = torch.randn(M, 256, generator=gen(3)).to(DEV, torch.bfloat16)
+    w = bl.LatticeTensor.from_float((torch.randn(128, 256, generator=gen(4)) * 0.05).to(DEV), "nvfp4", method="rtn")
+    gy = torch.randn(M, 128, generator=gen(5)).to(DEV, torch.bfloat16)
+    out = {}
+    for pol in ("exact", "fp4_all"):
+        p = torch.nn.Parameter(w.detach().clone())
+        xi = x.clone().requires_grad_(True)
+        with bl.compute(pol):
+            y = torch.nn.functional.linear(xi, p)
+        y.backward(gy)
+        out[pol] = (y.detach(), xi.grad, p.grad)
+    for name, r, got in zip(("y", "dx", "dw"), out["exact"], out["fp4_all"]):
+        assert got.shape == r.shape and rel(got, r) < 0.25, (name, rel(got, r))
+    assert bl._ops.gemm_status(0) == 0
+
+
+def test_fp4_all_operands_are_bit_exact_and_outputs_follow_them():
+    """Every operand of the three GEMMs equals the oracle's quantization (codes and scale bytes), and each GEMM
+    output equals the oracle's contraction of those operands within bf16 rounding."""
+    M, K, N = 96, 256, 128
+    x = torch.randn(M, K, generator=gen(6)).to(torch.bfloat16)
+    gy = (torch.randn(M, N, generator=gen(7)) * 1e-2).to(torch.bfloat16)
+    wd = (torch.randn(N, K, generator=gen(8)) * 0.02)
+    w = bl.LatticeTensor.from_float(wd.to(DEV), "nvfp4", method="rtn", dtype=torch.bfloat16)
+    wc, ws, wg = oracle.quantize_rows(wd.numpy(), None, "rtn")
+    assert np.array_equal(w.packed.cpu().numpy(), wc)
+    H = oracle.hadamard16()
+    # oracle operands
+    xc, xs, xg = oracle.quantize_rows(x.float().numpy(), None, "rtn")
+    xtg = oracle.global_from_bound(float(np.float32(xg) * np.float32(4.0)))
+    xtc, xts = oracle.quantize_t(x.float().numpy(), H, xtg, "rtn")
+    bl.backend.set_sr_seed(100)
+    gc, gs, gg = oracle.quantize_rows(gy.float().numpy(), None, "sr", seed=100)
+    wtc, wts = oracle.requantize_t(wc, ws, wg)
+    gtg = oracle.global_from_bound(float(np.float32(gg) * np.float32(4.0)))
+    gtc, gts = oracle.quantize_t(gy.float().numpy(), H, gtg, "sr", seed=101)
+    y_ref = oracle.gemm_nt(xc, xs, xg, wc, ws, wg)
+    gx_ref = oracle.gemm_nt(gc, gs, gg, wtc, wts, wg)
+    gw_ref = oracle.gemm_nt(gtc, gts, gtg, xtc, xts, xtg)
+    # product
+    p = torch.nn.Parameter(w)
+    xi = x.to(DEV).requires_grad_(True)
+    with bl.compute("fp4_all"):
+        y = torch.nn.functional.linear(xi, p)
+        xt = y.grad_fn.saved_tensors
+        assert np.array_equal(xt[0].cpu().numpy(), xtc)
+        assert np.array_equal(xt[1].cpu().numpy(), oracle.to_blocked(xts))
+        assert xt[2].cpu().numpy()[0] == np.float32(xtg)
+        y.backward(gy.to(DEV))
+    wt = bl.backend.weight_t_operand(p)
+    assert np.array_equal(wt.packed.cpu().numpy(), wtc) and np.array_equal(wt.scales.cpu().numpy(),
+                                                                            oracle.to_blocked(wts))
+    for name, got, ref in (("y", y, y_ref), ("gx", xi.grad, gx_ref), ("gw", p.grad, gw_ref)):
+        got = got.detach().float().cpu().numpy()
+        assert np.all(np.abs(got - ref) <= 2.0 ** -8 * np.abs(ref) + 2e-5 * np.abs(ref).max()), name
+    assert bl._ops.gemm_status(0) == 0
+
+
+def test_cached_weight_operands_follow_updates():
+    lin_w = bl.LatticeTensor.from_float((torch.randn(128, 256, generator=gen(9)) * 0.05).to(DEV), "nvfp4", method="rtn",
+                                        dtype=torch.bfloat16)
+    p = torch.nn.Parameter(lin_w)
+    x = torch.randn(64, 256, generator=gen(10)).to(DEV, torch.bfloat16)
+    opt = bl.Lattice([p], lr=5e-2, direction="sign", phase_bits=2)
+    with bl.compute("fp4_all"):
+        y1 = torch.nn.functional.linear(x, p)
+        y1.float().square().mean().backward()
+        opt.step()
+        opt.zero_grad()
+        y2 = torch.nn.functional.linear(x, p)
+        bl.backend._OPERANDS.clear()
+        y3 = torch.nn.functional.linear(x, p)
+    assert not torch.equal(y1, y2)
+    assert torch.equal(y2, y3)
+
+
+# ------------------------------------------------------------------------------------------------ optimizer
+
+def _golden_opt_names():
+    return [str(n) for n in golden("optimizer")["names"]]
+
+
+@pytest.mark.parametrize("key", _golden_opt_names())
+def test_optimizer_matches_reference_golden(key):
+    """Two steps of bl.optim.Lattice over two parameters reproduce the reference's CPU run bit for bit: codes, scale
+    bytes and phase bytes (this pins the per-parameter seeds, step counters and state layout too)."""
+    g = golden("optimizer")
+    direction, bits, rule = key.split("_")[0], int(key.split("_")[1][1:]), key.split("_", 2)[2]
+    trust_lr = {"sign_b4_fit": 1.0, "raw_b2_fit": 0.0, "sign_b0_fixed": 1.0, "sign_b8_fit_latent": 0.0}[key]
+    shapes = [(32, 64), (16, 128)]
+    ps = [torch.nn.Parameter(lattice_from(g[f"{key}_p{i}_codes0"], g[f"{key}_p{i}_scales0"], g[f"{key}_p{i}_g"], s))
+          for i, s in enumerate(shapes)]
+    opt = bl.optim.Lattice(ps, lr=3e-3, direction=direction, phase_bits=bits, scale_rule=rule, seed=1234, trust=0.1,
+                           trust_lr=trust_lr)
+    for s in range(2):
+        for i, p in enumerate(ps):
+            p.grad = torch.from_numpy(g[f"{key}_p{i}_G{s}"]).to(DEV, torch.bfloat16)
+        opt.step()
+    for i, p in enumerate(ps):
+        assert np.array_equal(p.scales.view(torch.uint8).cpu().numpy(), g[f"{key}_p{i}_scales"]), (key, i)
+        assert np.array_equal(p.packed.cpu().numpy(), g[f"{key}_p{i}_codes"]), (key, i)
+        if bits:
+            assert np.array_equal(opt.state[p]["phase"].cpu().numpy(), g[f"{key}_p{i}_phase"]), (key, i)
+    assert opt.state_bits()["phase"] == bits * sum(p.numel() for p in ps)
+
+
+def _make_params(seed=11):
+    return [torch.nn.Parameter(bl.LatticeTensor.from_float((torch.randn(s, generator=gen(seed + i)) * 0.05).to(DEV),
+                                                           "nvfp4", method="rtn", dtype=torch.bfloat16))
+            for i, s in enumerate([(64, 128), (32, 256)])]
+
+
+def _run(ps, opt, steps, micro=1, accumulate=False):
+    for s in range(steps):
+        for m in range(micro):
+            last = m == micro - 1
+            ctx = opt.accumulate() if (accumulate and not last) else torch.autograd.profiler.record_function("step")
+            with ctx:
+                loss = 0
+                for i, p in enumerate(ps):
+                    x = torch.randn(16, p.shape[1], generator=gen(100 + 10 * s + m)).to(DEV, torch.bfloat16)
+                    loss = loss + torch.nn.functional.linear(x, p).float().square().mean()
+                loss.backward()
+        opt.step()
+        opt.zero_grad()
+
+
+def test_fused_backward_matches_step():
+    """Reference identity (tests/test_optim.py:60-71): applying updates from the gradient hooks equals step()."""
+    a, b = _make_params(), _make_params()
+    o1 = bl.Lattice(a, lr=5e-3, direction="colnorm", phase_bits=4, seed=3)
+    o2 = bl.Lattice(b, lr=5e-3, direction="colnorm", phase_bits=4, seed=3, fused_backward=True)
+    _run(a, o1, 3)
+    _run(b, o2, 3)
+    assert all(p.grad is None for p in b)
+    for p, q in zip(a, b):
+        assert torch.equal(p.packed, q.packed) and torch.equal(p.scales.view(torch.uint8), q.scales.view(torch.uint8))
+        assert torch.equal(o1.state[p]["phase"], o2.state[q]["phase"])
+
+
+def test_accumulate_equals_summed_gradient():
+    """Reference identity (tests/test_parallel.py:131-156): with fused_backward, micro-batches inside accumulate()
+    are summed and applied once."""
+    a, b = _make_params(20), _make_params(20)
+    o1 = bl.Lattice(a, lr=5e-3, direction="sign", phase_bits=2, seed=5)
+    o2 = bl.Lattice(b, lr=5e-3, direction="sign", phase_bits=2, seed=5, fused_backward=True)
+    _run(a, o1, 2, micro=3)                         # plain: gradients sum in .grad, one step
+    _run(b, o2, 2, micro=3, accumulate=True)
+    for p, q in zip(a, b):
+        assert torch.equal(p.packed, q.packed) and torch.equal(o1.state[p]["phase"], o2.state[q]["phase"])
+
+
+def test_state_dict_round_trip():
+    ps = _make_params(30)
+    opt = bl.Lattice(ps, lr=5e-3, direction="sign", phase_bits=4)
+    _run(ps, opt, 1)
+    sd = opt.state_dict()
+    opt2 = bl.Lattice(ps, lr=5e-3, direction="sign", phase_bits=4)
+    opt2.load_state_dict(sd)
+    k = next(iter(opt.state))
+    assert torch.equal(opt2.state[k]["phase"], opt.state[k]["phase"]) and opt2.state[k]["step"] == 1
+    assert opt.state_bytes() == sum(p.numel() // 2 for p in ps)
+
+
+def test_row_shard_update_equals_whole_update():
+    """N-sharding: shards carrying _bl_row_offset reproduce the unsharded update of the same rows."""
+    from bitlattice_b200.parallel import shard_rows
+    w = bl.LatticeTensor.from_float((torch.randn(128, 256, generator=gen(40)) * 0.05).to(DEV), "nvfp4", method="rtn",
+                                    dtype=torch.bfloat16)
+    G = (torch.randn(128, 256, generator=gen(41)) * 1e-2).to(DEV, torch.bfloat16)
+    whole = torch.nn.Parameter(w.detach().clone())
+    ow = bl.Lattice([whole], lr=3e-3, direction="sign", phase_bits=4, seed=9)
+    whole.grad = G
+    ow.step()
+    for rank in range(2):
+        sh = torch.nn.Parameter(shard_rows(w, rank, 2))
+        sh._bl_row_offset = sh.data._bl_row_offset if hasattr(sh.data, "_bl_row_offset") else rank * 64
+        os_ = bl.Lattice([sh], lr=3e-3, direction="sign", phase_bits=4, seed=9)
+        sh.grad = G[rank * 64:(rank + 1) * 64].contiguous()
+        os_.step()
+        assert torch.equal(sh.packed, whole.packed[rank * 64:(rank + 1) * 64])
+        assert torch.equal(os_.state[sh]["phase"], ow.state[whole]["phase"][rank * 64:(rank + 1) * 64])
