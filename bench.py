@@ -1,0 +1,322 @@
+#!/usr/bin/env python
+"""Benchmark of the NVFP4 hot path on B200: linear forward + dgrad + wgrad on FP4 tensor cores with the lattice
+update fused into backward, over an 8B-class decoder linear stack.
+
+    python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
+    python -m torch.distributed.run --nnodes=1 --nproc-per-node N --master-addr 127.0.0.1 --master-port P \
+        bench.py --gpus N --steps K --warmup W
+
+Workload ("cfg4_8b_linear_stack"): `--layers` decoder layers (default 36) of {q, o: 4096x4096; k, v: 1024x4096;
+gate, up: 12288x4096; down: 4096x12288} NVFP4 weights, `--tokens` tokens (default 16 x 4096), bf16 activations
+~ N(0,1), upstream gradients ~ N(0, 1e-2^2), weights ~ N(0, 0.02^2), all synthetic and seeded. One step = for every
+linear: y = F.linear(x, W) under compute("fp4_all"), y.backward(gy) -> dgrad + wgrad, and the lattice update of W
+(colnorm direction, 4-bit phase, stochastic projection, scale refit with trust region 0.1) from the gradient hook.
+With N > 1 every weight is sharded along N (rows) over the ranks: activations are all-gathered, input gradients
+reduce-scattered (NCCL), the update is local; total work is fixed (strong scaling).
+
+Prints one JSON line (rank 0). `value` is whole-job TFLOP/s with inputs resident in HBM; `e2e` is the same step with
+the step's inputs copied from pinned host memory and a checksum read back inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import os
+import statistics
+import subprocess
+import sys
+import threading
+import time
+
+ROOT = os.path.dirname(os.path.abspath(__file__))
+sys.path.insert(0, ROOT)
+
+LAYER = (("q", 4096, 4096), ("k", 1024, 4096), ("v", 1024, 4096), ("o", 4096, 4096),
+         ("gate", 12288, 4096), ("up", 12288, 4096), ("down", 4096, 12288))
+OPT = dict(lr=3e-3, direction="colnorm", phase_bits=4, rounding="sr", scale_rule="fit", trust=0.1, trust_lr=0.0,
+           seed=1234)
+BYTES_PER_WEIGHT = 4.125      # codes r+w 1.0, 4-bit phase r+w 1.0, bf16 gradient 2.0, E4M3 scales r+w 0.125
+
+
+def parse():
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=3)
+    ap.add_argument("--warmup", type=int, default=3)
+    ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
+    ap.add_argument("--tokens", type=int, default=16 * 4096)
+    ap.add_argument("--layers", type=int, default=36)
+    ap.add_argument("--cpu-tokens", type=int, default=16384, help="tokens of the bounded CPU sample")
+    return ap.parse_args()
+
+
+def measured_peaks():
+    path = os.path.join(ROOT, "MEASURED_PEAKS.json")
+    if os.path.exists(path):
+        with open(path) as f:
+            p = json.load(f)
+        return dict(hbm=p["hbm_gbs"], bf16=p["bf16_tflops"], bf16_sustained=p["bf16_tflops_sustained"],
+                    source="measured")
+    return dict(hbm=6650.0, bf16=1590.0, bf16_sustained=1400.0, source="fallback")
+
+
+class Clocks:
+    """Samples nvidia-smi clocks and throttle reasons while the timed region runs."""
+
+    Q = ("index,clocks.sm,clocks.max.sm,power.draw,clocks_event_reasons.active,clocks_event_reasons.hw_slowdown,"
+         "clocks_event_reasons.hw_thermal_slowdown,clocks_event_reasons.sw_thermal_slowdown,"
+         "clocks_event_reasons.sw_power_cap")
+
+    def __init__(self, index: int):
+        self.index, self.proc, self.lines = index, None, []
+
+    def start(self):
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.Q}", "--format=csv,noheader,nounits",
+                                          "-lms", "200", "-i", str(self.index)], stdout=subprocess.PIPE, text=True)
+            threading.Thread(target=self._read, daemon=True).start()
+        except OSError:
+            self.proc = None
+
+    def _read(self):
+        for line in self.proc.stdout:
+            self.lines.append(line.strip())
+
+    def stop(self) -> dict:
+        if self.proc is None:
+            return {"sm_mhz": None, "sm_max_mhz": None, "reasons": ["nvidia-smi unavailable"]}
+        self.proc.terminate()
+        sm, mx, reasons = [], [], set()
+        for ln in self.lines:
+            f = [x.strip() for x in ln.split(",")]
+            if len(f) < 9:
+                continue
+            try:
+                sm.append(float(f[1]))
+                mx.append(float(f[2]))
+            except ValueError:
+                continue
+            for name, v in zip(("hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"), f[5:9]):
+                if v.lower().startswith("active"):
+                    reasons.add(name)
+        return {"sm_mhz": statistics.median(sm) if sm else None, "sm_max_mhz": max(mx) if mx else None,
+                "samples": len(sm), "reasons": sorted(reasons)}
+
+
+# ---------------------------------------------------------------------------------------------------- CPU arm
+
+def cpu_sample(tokens: int, repeats: int = 1):
+    """The reference's CPU path for one q-projection (4096 x 4096) on `tokens` tokens, restated by the oracle:
+    exact-route forward / dgrad / wgrad (dequantize to bf16, bf16 x bf16 -> fp32 contractions) and one lattice update
+    (colnorm direction + step). Returns (seconds per repeat, flops, weights, threads)."""
+    import numpy as np
+    import torch
+    import oracle
+    N = K = 4096
+    g = torch.Generator().manual_seed(0)
+    w = (torch.randn(N, K, generator=g) * 0.02).numpy()
+    x = torch.randn(tokens, K, generator=g).to(torch.bfloat16)
+    gy = (torch.randn(tokens, N, generator=g) * 1e-2).to(torch.bfloat16)
+    codes, scales, gs = oracle.quantize_rows(w, None, "rtn")
+    phase = np.zeros((N, K // 2), np.uint8)
+    bits = lambda t: t.contiguous().view(torch.int16).numpy().view(np.uint16)
+    times = []
+    for _ in range(repeats):
+        t0 = time.perf_counter()
+        wd = torch.from_numpy(oracle.dequantize(codes, scales, gs)).to(torch.bfloat16)
+        y = oracle.gemm_bf16_nt(bits(x), bits(wd))                                  # [M, N]
+        gx = oracle.gemm_bf16_nt(bits(gy), bits(wd.t()))                            # [M, K]
+        gw = oracle.gemm_bf16_nt(bits(gy.t()), bits(x.t()))                         # [N, K]
+        G = torch.from_numpy(gw).to(torch.bfloat16).float().numpy()
+        D, _ = oracle.direction(G, "colnorm", 1.0)
+        codes, phase, scales = oracle.lattice_step(codes, phase, scales, gs, D, lr=OPT["lr"], phase_bits=4,
+                                                   rounding="sr", seed=OPT["seed"], step=1, scale_rule="fit",
+                                                   trust=0.1, trust_lr=0.0)
+        times.append(time.perf_counter() - t0)
+        del y, gx
+    return min(times), 6.0 * tokens * N * K, N * K, oracle.num_threads()
+
+
+def run_reference(a):
+    """`--impl reference`: the reference's own CPU implementation of the path (its pure-PyTorch code cannot travel
+    to the GPU box, so the oracle -- the port pinned to it by the golden vectors -- is what runs), all host threads,
+    each step a bounded sample of the workload."""
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return
+    for _ in range(max(a.warmup, 0) and 1):
+        cpu_sample(a.cpu_tokens)
+    ts = []
+    for _ in range(a.steps):
+        t, flops, weights, threads = cpu_sample(a.cpu_tokens)
+        ts.append(t)
+    t = sum(ts) / len(ts)
+    sample = (f"one q-projection 4096x4096, {a.cpu_tokens} tokens: exact-route fwd+dgrad+wgrad (bf16 operands, fp32 "
+              f"accumulate) + colnorm lattice update, per step")
+    val = flops / t / 1e12
+    print(json.dumps({
+        "impl": "reference", "metric": "nvfp4_linear_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s",
+        "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (CPU exact route)", "data": "synthetic",
+        "config": {"workload": "cfg4_8b_linear_stack", "sample": sample},
+        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
+        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+    }))
+
+
+# ---------------------------------------------------------------------------------------------------- GPU arm
+
+def run_ours(a):
+    import torch
+    import torch.distributed as dist
+    import bitlattice_b200 as bl
+    from bitlattice_b200 import _C
+    from bitlattice_b200.parallel import column_parallel_linear, shard_rows
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    if world > 1:
+        dist.init_process_group("nccl", device_id=dev)
+    M = a.tokens
+    assert M % (world * 32) == 0, "tokens must split evenly over the ranks in multiples of 32"
+    Ms = M // world
+
+    # weights: every rank draws the full matrix from the same seed, quantizes it (one per-tensor scale) and keeps
+    # its row shard
+    params, meta = [], []
+    for layer in range(a.layers):
+        for i, (name, N, K) in enumerate(LAYER):
+            gen = torch.Generator(device=dev).manual_seed(1000 * layer + i)
+            wd = torch.randn(N, K, device=dev, generator=gen) * 0.02
+            w = bl.LatticeTensor.from_float(wd, "nvfp4", method="rtn", dtype=torch.bfloat16)
+            del wd
+            if world > 1:
+                w = shard_rows(w, rank, world)
+            p = torch.nn.Parameter(w)
+            p._bl_row_offset = getattr(w, "_bl_row_offset", 0)
+            params.append(p)
+            meta.append((name, N, K))
+    opt = bl.Lattice(params, fused_backward=True, **OPT)
+
+    # inputs: token shard of x per distinct K, feature shard of gy per distinct N
+    gen = torch.Generator(device=dev).manual_seed(7 + rank)
+    xs = {K: torch.randn(Ms, K, device=dev, generator=gen).to(torch.bfloat16) for K in (4096, 12288)}
+    gys = {N: (torch.randn(M, N // world, device=dev, generator=gen) * 1e-2).to(torch.bfloat16)
+           for N in (4096, 1024, 12288)}
+    host = {k: v.cpu().pin_memory() for k, v in {**{("x", K): t for K, t in xs.items()},
+                                                 **{("g", N): t for N, t in gys.items()}}.items()}
+    h2d_bytes = sum(t.numel() * t.element_size() for t in host.values())
+    flops = sum(6.0 * M * N * K for _, N, K in meta)
+    weights = sum(N * K for _, N, K in meta)
+    group = dist.group.WORLD if world > 1 else None
+
+    def step(from_host: bool):
+        if from_host:
+            for K in xs:
+                xs[K].copy_(host[("x", K)], non_blocking=True)
+            for N in gys:
+                gys[N].copy_(host[("g", N)], non_blocking=True)
+        check = torch.zeros((), device=dev)
+        with bl.compute("fp4_all"):
+            for li in range(a.layers):
+                xin = {K: t.detach().requires_grad_(True) for K, t in xs.items()}
+                for j, (name, N, K) in enumerate(LAYER):
+                    p = params[li * len(LAYER) + j]
+                    y = column_parallel_linear(xin[K], p, group)
+                    y.backward(gys[N])
+                if from_host:
+                    check = check + xin[4096].grad[0, :8].float().sum()
+        opt.step()
+        return float(check.item()) if from_host else 0.0
+
+    def timed(n, from_host):
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        s.record()
+        for _ in range(n):
+            step(from_host)
+        e.record()
+        torch.cuda.synchronize()
+        if world > 1:
+            dist.barrier()
+        t = torch.tensor([s.elapsed_time(e)], device=dev)
+        if world > 1:
+            dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return t.item() / 1e3
+
+    for _ in range(max(a.warmup, 3)):
+        step(False)
+    clocks = Clocks(local)
+    if rank == 0:
+        clocks.start()
+    _C.Counters.reset(timed={"bl_nvfp4_gemm", "bl_nvfp4_lattice_update"})
+    secs = timed(a.steps, False)
+    launches = _C.Counters.launches
+    gemm_ms, gemm_calls = _C.Counters.elapsed_ms("bl_nvfp4_gemm")
+    upd_ms, upd_calls = _C.Counters.elapsed_ms("bl_nvfp4_lattice_update")
+    _C.Counters.reset()
+    clock_info = clocks.stop() if rank == 0 else None
+    step(True)
+    e2e_steps = max(1, min(a.steps, 3))
+    e2e_secs = timed(e2e_steps, True)
+    status = bl._ops.gemm_status(local)
+    if world > 1:
+        dist.barrier()
+    if rank != 0:
+        if world > 1:
+            dist.destroy_process_group()
+        return
+
+    peaks = measured_peaks()
+    per_step = secs / a.steps
+    fp4_peak = 4.0 * peaks["bf16_sustained"]
+    gemm_flops_rank = a.steps * flops / world                     # this rank's share of the contraction work
+    gemm_tf = gemm_flops_rank / (gemm_ms / 1e3) / 1e12 if gemm_ms else None
+    upd_bytes_rank = a.steps * weights * BYTES_PER_WEIGHT / world
+    upd_gbs = upd_bytes_rank / (upd_ms / 1e3) / 1e9 if upd_ms else None
+    out = {
+        "metric": "nvfp4_linear_fwd_bwd_tflops", "value": flops / per_step / 1e12, "unit": "TFLOP/s",
+        "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": per_step * 1e3,
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "nvfp4 (e2m1 x ue4m3, fp32 acc)",
+        "data": "synthetic",
+        "config": {"workload": "cfg4_8b_linear_stack", "layers": a.layers, "tokens": M,
+                   "linears_per_layer": [f"{n}:{N}x{K}" for n, N, K in LAYER], "update": OPT,
+                   "parallelism": f"N-sharded x{world}" if world > 1 else "single GPU",
+                   "l2": "inputs larger than L2 (weights, activations and gradients of a step exceed 126 MB)"},
+        "e2e": {"value": flops / (e2e_secs / e2e_steps) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes,
+                "d2h_bytes_per_step": 4, "steps": e2e_steps},
+        "gpu_launches": launches,
+        "gemm_error_flag": status,
+        "clocks": clock_info,
+        "roofline": {"bound": "tensor", "kernel": "gemm_kernel (tcgen05 mxf4nvf4)", "achieved": gemm_tf,
+                     "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tf / fp4_peak if gemm_tf else None,
+                     "traffic": None, "launches": gemm_calls,
+                     "peak_note": f"4 x bf16 sustained cuBLAS ({peaks['source']}); nominal dense FP4 9000",
+                     "frac_of_nominal": gemm_tf / 9000.0 if gemm_tf else None},
+        "update": {"metric": "lattice_update_hbm_gbs", "value": upd_gbs, "unit": "GB/s", "calls": upd_calls,
+                   "bytes_per_weight": BYTES_PER_WEIGHT,
+                   "roofline": {"bound": "hbm", "achieved": upd_gbs, "peak": peaks["hbm"], "unit": "GB/s",
+                                "frac": upd_gbs / peaks["hbm"] if upd_gbs else None, "traffic": None,
+                                "peak_note": f"copy bandwidth ({peaks['source']}); nominal 8000"}},
+    }
+    if world == 1:
+        t, cflops, _, threads = cpu_sample(a.cpu_tokens)
+        out["cpu_baseline"] = {"value": cflops / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
+                               "sample": f"one q-projection 4096x4096 at {a.cpu_tokens} tokens (exact route fwd+dgrad+"
+                                         f"wgrad + colnorm lattice update), {t:.2f} s"}
+    print(json.dumps(out))
+    if world > 1:
+        dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    args = parse()
+    if args.impl == "reference":
+        run_reference(args)
+    else:
+        run_ours(args)

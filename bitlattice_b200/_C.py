@@ -88,5 +88,40 @@ def check(status: int) -> None:
         raise RuntimeError(lib().bl_last_error().decode("utf-8", "replace"))
 
 
-def call(name: str, *args) -> None:
-    check(getattr(lib(), name)(*args))
+# kernels each entry point launches (memsets not counted); the lattice update launches 3 when it needs column
+# statistics, the transposed quantizer 3 without a scale bound
+KERNELS_PER_CALL = {"bl_nvfp4_step_quantized": 1, "bl_nvfp4_lattice_update": 1, "bl_direction": 1,
+                    "bl_nvfp4_dequantize": 1, "bl_nvfp4_amax": 1, "bl_nvfp4_quantize": 1, "bl_nvfp4_quantize_t": 2,
+                    "bl_nvfp4_requantize_t": 1, "bl_nvfp4_scales_to_blocked": 1, "bl_nvfp4_gemm": 1}
+
+
+class Counters:
+    """Launch accounting for benchmarks: ``launches`` counts this library's kernels; with ``timed`` set to a set of
+    entry-point names, every call of one of them is bracketed by CUDA events on its stream (``events[name]``)."""
+
+    launches = 0
+    timed: set | None = None
+    events: dict = {}
+
+    @classmethod
+    def reset(cls, timed=None) -> None:
+        cls.launches, cls.timed, cls.events = 0, (set(timed) if timed else None), {}
+
+    @classmethod
+    def elapsed_ms(cls, name: str) -> tuple[float, int]:
+        """(total milliseconds, calls) of a timed entry point; synchronize the device first."""
+        ev = cls.events.get(name, [])
+        return sum(a.elapsed_time(b) for a, b in ev), len(ev)
+
+
+def call(name: str, *args, extra_kernels: int = 0) -> None:
+    fn = getattr(lib(), name)
+    if Counters.timed is not None and name in Counters.timed:
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        check(fn(*args))
+        b.record()
+        Counters.events.setdefault(name, []).append((a, b))
+    else:
+        check(fn(*args))
+    Counters.launches += KERNELS_PER_CALL.get(name, 0) + extra_kernels

@@ -164,7 +164,8 @@ def lattice_update(packed, phase, scales, global_scale, zeros, G, fmt, rows: int
             phase_bits, phase_cb, float(lr), float(1.0 - lr * weight_decay), _ROUNDING[rounding],
             int(seed) & 0xFFFFFFFF, int(step) & 0xFFFFFFFF, j, k, _RULE[scale_rule],
             float(kappa(trust, trust_lr, lr)), _DIRECTION[direction], float(clip), _C.ptr(scratch),
-            scratch.numel() if scratch is not None else 0, _C.device_of(packed), _C.stream_of(packed))
+            scratch.numel() if scratch is not None else 0, _C.device_of(packed), _C.stream_of(packed),
+            extra_kernels=2 if need else 0)
 
 
 def direction(G, kind: str, r=None, c=None, k: int = 1, beta2: float = 0.95, block=0, ns_steps: int = 5,
@@ -181,7 +182,8 @@ def direction(G, kind: str, r=None, c=None, k: int = 1, beta2: float = 0.95, blo
     D = torch.empty(rows, cols, dtype=torch.float32, device=G2.device)
     scratch = _scratch_for(G2.device, update_scratch_bytes(rows, cols, kind, clip))
     _C.call("bl_direction", _C.ptr(G2), _C.DTYPE[G2.dtype], rows, cols, _DIRECTION[kind], float(clip), _C.ptr(D),
-            _C.ptr(scratch), scratch.numel() if scratch is not None else 0, _C.device_of(G2), _C.stream_of(G2))
+            _C.ptr(scratch), scratch.numel() if scratch is not None else 0, _C.device_of(G2), _C.stream_of(G2),
+            extra_kernels=2 if scratch is not None else 0)
     return D
 
 
@@ -246,7 +248,7 @@ def quantize_nvfp4_t(x: torch.Tensor, hadamard: torch.Tensor | None, seed: int =
         amax = torch.empty(4, dtype=torch.float32, device=x.device)
     _C.call("bl_nvfp4_quantize_t", _C.ptr(x), _C.DTYPE[x.dtype], M, K, _C.ptr(hadamard), int(seed),
             int(step) & 0xFFFFFFFF, _C.ptr(bound), _C.ptr(amax), _C.ptr(packed), _C.ptr(scales), _C.ptr(gout),
-            int(blocked), _C.device_of(x), _C.stream_of(x))
+            int(blocked), _C.device_of(x), _C.stream_of(x), extra_kernels=0 if bound is not None else 1)
     return packed, scales if blocked else scales.view(torch.float8_e4m3fn), gout
 
 
