@@ -19,6 +19,7 @@
 // raises an error flag, lets all warps fall through to the common exit and frees its tensor memory.
 #include <cuda.h>
 
+#include <cstdlib>
 #include <mutex>
 
 #include "common.cuh"
@@ -216,6 +217,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_kernel(const __grid_constan
 
   const int num_k_tiles = static_cast<int>((args.K + kBK - 1) / kBK);
   const int nkb = static_cast<int>((args.K + 63) / 64);               // scale blobs per 128 rows along K
+  const int nrb_b = static_cast<int>((args.N + 127) / 128);           // 128-row scale blocks of B
 
   constexpr uint32_t kTmemCols = BN <= 64 ? 128 : (BN <= 192 ? 256 : 512);
   constexpr uint32_t kSfaCol = BN;            // accumulator: columns [0, BN); then 16 columns of A scales
@@ -249,13 +251,14 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_kernel(const __grid_constan
         const uint32_t stage = base + s * S::kStage;
         const int blobs = min(4, nkb - kt * 4);
         const uint32_t sf_bytes = blobs * 512u;
-        mbar_expect_tx(full_bar(s), S::kA + S::kB + sf_bytes * (1 + BN / 128));
+        const int b_blocks = min(BN / 128, nrb_b - tile_n * (BN / 128));     // 128-row scale blocks of B that exist
+        mbar_expect_tx(full_bar(s), S::kA + S::kB + sf_bytes * (1 + b_blocks));
         tma_load_2d(stage, &map_a, kt * (kBK / 2), static_cast<int>(m0), full_bar(s));
         tma_load_2d(stage + S::kA, &map_b, kt * (kBK / 2), static_cast<int>(n0), full_bar(s));
         const uint8_t* sfa = args.a_sf + (static_cast<int64_t>(tile_m) * nkb + kt * 4) * 512;
         bulk_load(stage + S::kA + S::kB, sfa, sf_bytes, full_bar(s));
 #pragma unroll
-        for (int h = 0; h < BN / 128; ++h) {
+        for (int h = 0; h < b_blocks; ++h) {
           const uint8_t* sfb = args.b_sf + ((static_cast<int64_t>(tile_n) * (BN / 128) + h) * nkb + kt * 4) * 512;
           bulk_load(stage + S::kA + S::kB + S::kSFA + h * 2048, sfb, sf_bytes, full_bar(s));
         }
@@ -403,6 +406,11 @@ extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const 
   args.ldc = ldc;
   args.out_dtype = out_dtype;
   args.num_m = args.num_n = 0;
+  static const int bn = [] {
+    const char* e = getenv("BL_GEMM_BN");
+    return e ? atoi(e) : 128;
+  }();
+  if (bn == 256) return launch_gemm<256, 4>(a_codes, b_codes, args, reinterpret_cast<cudaStream_t>(stream));
   return launch_gemm<128, 3>(a_codes, b_codes, args, reinterpret_cast<cudaStream_t>(stream));
 }
 
