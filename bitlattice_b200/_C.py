@@ -45,6 +45,7 @@ _SIGNATURES = {
     "bl_nvfp4_gemm": (_c.c_int, [_P, _P, _P, _P, _P, _P, _c.c_int64, _c.c_int64, _c.c_int64, _P, _c.c_int,
                                  _c.c_int64, _c.c_int, _P]),
     "bl_nvfp4_gemm_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.c_int]),
+    "bl_selftest_division": (_c.c_int, [_c.c_uint64, _c.c_uint32, _c.POINTER(_c.c_uint64), _c.c_int]),
 }
 
 _lib = None
@@ -59,7 +60,7 @@ def lib() -> ctypes.CDLL:
     global _lib
     if _lib is None:
         if not os.path.exists(LIB_PATH):
-            raise ImportError(f"{LIB_PATH} is missing: build it with `python -m bitlattice_b200.csrc.build` "
+            raise ImportError(f"{LIB_PATH} is missing: build it with `python bitlattice_b200/csrc/build.py` "
                               "(there is no fallback implementation)")
         L = ctypes.CDLL(LIB_PATH)
         for name, (res, args) in _SIGNATURES.items():

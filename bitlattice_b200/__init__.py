@@ -9,7 +9,7 @@ rebuilt for B200 (sm_100a) behind the reference's Python API.
     y.backward(gy)                                   # ... and the fused lattice update of w from the hook
 
 All arithmetic runs in ``libbitlattice_b200.so`` (hand-written CUDA behind a C ABI, ``include/bitlattice_b200.h``);
-importing the package loads it and fails if it has not been built (``python -m bitlattice_b200.csrc.build``).
+importing the package loads it and fails if it has not been built (``python bitlattice_b200/csrc/build.py``).
 """
 from . import _C
 

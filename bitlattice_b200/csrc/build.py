@@ -1,6 +1,6 @@
 """Builds libbitlattice_b200.so (the C-ABI CUDA library) in-tree with nvcc for sm_100a.
 
-    python -m bitlattice_b200.csrc.build [--force] [--verbose]
+    python bitlattice_b200/csrc/build.py [--force] [--verbose]
 
 The kernels that must reproduce the reference's fp32 rounding bit for bit (update.cu, quant.cu) are compiled with
 --fmad=false, as the reference's extension is (its setup.py:21-22); the GEMM keeps fused multiply-adds.

@@ -156,6 +156,89 @@ __device__ __forceinline__ uint32_t e2m1_code_sr(float v, float u) {
   return (v < 0.0f && m ? 8u : 0u) | m;
 }
 
+// ---------------------------------------------------------------------------------------------- device: division
+// x / y rounded to nearest, from a correctly rounded reciprocal ry = __frcp_rn(y) that the caller shares between many
+// quotients: one product and two residual corrections with fused multiply-adds (the sequence compilers emit for an
+// fp32 division, minus the reciprocal and the range checks). The residuals are exact, so the result is the correctly
+// rounded quotient whenever no intermediate leaves the normal range; outside it the plain division is used.
+__device__ __forceinline__ float div_rn(float x, float y, float ry) {
+  float q = x * ry;
+  const float aq = fabsf(q);
+  if (!(aq > 1e-30f && aq < 1e30f)) return x / y;      // zero, tiny, huge or non-finite: the general path
+  float e = fmaf(-y, q, x);
+  q = fmaf(e, ry, q);
+  e = fmaf(-y, q, x);
+  return fmaf(e, ry, q);
+}
+
+// ---------------------------------------------------------------------------------------------- device: fast E2M1
+// The hardware conversion cvt.rn.satfinite.e2m1x2.f32 rounds two floats to E2M1 nibbles (ties to even, -0 kept).
+// It gives the reference's code (ties to the lower level, +0 only) whenever its input is not at, or within rounding
+// error of, a midpoint between two levels; the callers below establish that by converting a lower and an upper bound
+// of the exact quotient and comparing, and take the exact ladder otherwise.
+
+// byte with the code of `hi` in the upper and of `lo` in the lower nibble
+__device__ __forceinline__ uint32_t cvt_e2m1x2(float hi, float lo) {
+  uint32_t r;
+  asm("{\n\t.reg .b8 t;\n\tcvt.rn.satfinite.e2m1x2.f32 t, %1, %2;\n\tcvt.u32.u8 %0, t;\n\t}" : "=r"(r) : "f"(hi), "f"(lo));
+  return r;
+}
+
+// 8 floats -> 8 nibbles (element i in nibble i)
+__device__ __forceinline__ uint32_t cvt_e2m1x8(const float v[8]) {
+  return cvt_e2m1x2(v[1], v[0]) | (cvt_e2m1x2(v[3], v[2]) << 8) | (cvt_e2m1x2(v[5], v[4]) << 16) |
+         (cvt_e2m1x2(v[7], v[6]) << 24);
+}
+
+// clear the sign bit of every nibble whose magnitude is zero (-0 -> +0: the reference never writes code 8)
+__device__ __forceinline__ uint32_t e2m1_drop_negative_zero(uint32_t w) {
+  const uint32_t m = w & 0x77777777u;
+  const uint32_t nz = (m | (m >> 1) | (m >> 2)) & 0x11111111u;
+  return m | (w & (nz << 3));
+}
+
+// Round-to-nearest codes (ties to the lower level) of v[i] / se for 8 values, se > 0.
+// inv_lo / inv_hi: (1/se) scaled by (1 - 2^-20) and (1 + 2^-20): v*inv_lo and v*inv_hi bracket the exact quotient
+// (the two roundings of each product are below 2^-22 relative), E2M1 rounding is monotone, so equal conversions of
+// the two bounds equal the conversion of the quotient, which then is no tie.
+// the exact ladder for 8 values: kept out of line so the common path stays small
+static __device__ __noinline__ uint32_t e2m1_nearest_x8_exact(float v0, float v1, float v2, float v3, float v4, float v5,
+                                                       float v6, float v7, float se) {
+  return e2m1_code_nearest(v0 / se) | (e2m1_code_nearest(v1 / se) << 4) | (e2m1_code_nearest(v2 / se) << 8) |
+         (e2m1_code_nearest(v3 / se) << 12) | (e2m1_code_nearest(v4 / se) << 16) | (e2m1_code_nearest(v5 / se) << 20) |
+         (e2m1_code_nearest(v6 / se) << 24) | (e2m1_code_nearest(v7 / se) << 28);
+}
+
+__device__ __forceinline__ uint32_t e2m1_nearest_x8(const float v[8], float se, float inv_lo, float inv_hi) {
+  float a[8], b[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    a[i] = v[i] * inv_lo;
+    b[i] = v[i] * inv_hi;
+  }
+  const uint32_t wa = cvt_e2m1x8(a), wb = cvt_e2m1x8(b);
+  if (__builtin_expect(wa == wb, 1)) return e2m1_drop_negative_zero(wa);
+  return e2m1_nearest_x8_exact(v[0], v[1], v[2], v[3], v[4], v[5], v[6], v[7], se);   // at or next to a midpoint
+}
+
+// Stochastic-rounding codes of x[i] = v[i] * inv (bitlattice/fp4ref.py:71-78) for 8 values; u from hash(idx0 + i).
+// lo = largest level <= min(|x|, 6) (the float truncated to one mantissa bit, or 0 / 0.5 below 1), gap to the next.
+__device__ __forceinline__ uint32_t e2m1_sr_x8(const float v[8], float inv, uint32_t key, uint32_t idx0) {
+  float r[8];
+#pragma unroll
+  for (int i = 0; i < 8; ++i) {
+    const float x = v[i] * inv;
+    const float a = fminf(fabsf(x), 6.0f);
+    const uint32_t ab = __float_as_uint(a);
+    const float lo = a >= 1.0f ? __uint_as_float(ab & 0xFFC00000u) : (a >= 0.5f ? 0.5f : 0.0f);
+    const float gap = a >= 2.0f ? __uint_as_float((ab & 0x7F800000u) - 0x00800000u) : 0.5f;
+    const float u = hash_uniform(idx0 + i, key);
+    const bool up = lo < 6.0f && u * gap < a - lo;
+    r[i] = copysignf(up ? lo + gap : lo, x);
+  }
+  return e2m1_drop_negative_zero(cvt_e2m1x8(r));
+}
+
 // ---------------------------------------------------------------------------------------------- device: dense loads
 
 template <typename T> __device__ __forceinline__ float to_f(T v);

@@ -147,6 +147,12 @@ BL_API int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const floa
  * (0: none) in *status and clears it. No counterpart in the reference (cuBLASLt reports nothing of the kind). */
 BL_API int bl_nvfp4_gemm_status(int* status, int device);
 
+/* Diagnostic, no counterpart in the reference: the kernels replace fp32 divisions that share a divisor by a product
+ * with its correctly rounded reciprocal plus two fused residual corrections. This runs that routine against the
+ * plain division on n pseudo-random operand pairs (synchronously, with a temporary 8-byte device allocation) and
+ * stores the number of results that differ in any bit; the test-suite requires 0. */
+BL_API int bl_selftest_division(uint64_t n, uint32_t seed, uint64_t* mismatches, int device);
+
 #ifdef __cplusplus
 }
 #endif
