@@ -32,6 +32,7 @@ constexpr int kGemmThreads = 192;
 constexpr uint32_t kSpinLimit = 1u << 21;   // polls of one mbarrier wait before the kernel gives up
 
 __device__ int g_gemm_error = 0;  // 0 ok; otherwise the code of the wait that expired
+__device__ unsigned long long g_gemm_prof[8];   // cycle counters of the persistent kernel (debug bit 8)
 
 // ------------------------------------------------------------------------------------------------ PTX wrappers
 
@@ -161,6 +162,7 @@ struct GemmArgs {
   int64_t M, N, K, ldc;
   int out_dtype;
   int num_m, num_n;
+  int debug;      // experiments only: 1 skip stores, 2 skip MMAs, 4 skip scale copies
 };
 
 template <typename O>
@@ -277,7 +279,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_kernel(const __grid_constan
         tcgen05_fence_after();
         const uint32_t stage = base + s * S::kStage;
         const int blocks = min(4, nkb - kt * 4);
-        for (int j = 0; j < blocks; ++j) {
+        for (int j = 0; j < blocks && !(args.debug & 4); ++j) {
           tmem_copy_scales(tmem_base + kSfaCol + 4 * j, scale_desc(stage + S::kA + S::kB + j * 512));
 #pragma unroll
           for (int h = 0; h < BN / 128; ++h)
@@ -285,7 +287,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_kernel(const __grid_constan
                              scale_desc(stage + S::kA + S::kB + S::kSFA + h * 2048 + j * 512));
         }
         const uint64_t adesc = operand_desc(stage), bdesc = operand_desc(stage + S::kA);
-        for (int j = 0; j < blocks; ++j)
+        for (int j = 0; j < blocks && !(args.debug & 2); ++j)
           mma_nvf4(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
                    tmem_base + kSfbCol + (BN / 32) * j, (kt | j) != 0);
         mma_commit(empty_bar(s));
@@ -305,6 +307,196 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_kernel(const __grid_constan
         uint32_t acc[32];
         tmem_load32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c, acc);
         const int64_t col = n0 + c;
+        if (row < args.M && col < args.N && !(args.debug & 1)) {
+          const int64_t left = args.N - col;
+          const int valid = left < 32 ? static_cast<int>(left) : 32;
+          if (args.out_dtype == BL_BF16)
+            store_row32(static_cast<__nv_bfloat16*>(args.out) + row * args.ldc + col, acc, alpha, valid);
+          else if (args.out_dtype == BL_F16)
+            store_row32(static_cast<__half*>(args.out) + row * args.ldc + col, acc, alpha, valid);
+          else
+            store_row32(static_cast<float*>(args.out) + row * args.ldc + col, acc, alpha, valid);
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ persistent kernel
+// One CTA per SM walks over 128 x 256 output tiles (tile = blockIdx.x + i * gridDim.x, same grouped order). The
+// producer warp runs ahead across tile boundaries, so the shared-memory ring stays full while the epilogue drains the
+// accumulator; the MMA warp only waits for the drain (tmem_empty) before the first MMA of the next tile.
+//   warp 0: producer   warp 1: MMA issuer + tensor-memory owner   warps 2..9: epilogue (two warps per 32-lane
+//   quarter, each taking one 128-column half of the accumulator)
+constexpr int kPersistThreads = 320;
+
+__device__ __forceinline__ void mbar_arrive(uint32_t bar) {
+  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+}
+
+template <int STAGES>
+__global__ void __launch_bounds__(kPersistThreads, 1) gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                             const __grid_constant__ CUtensorMap map_b,
+                                                                             GemmArgs args) {
+  constexpr int BN = 256;
+  using S = GemmSmem<BN, STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw_addr);
+  const uint32_t bars = base + STAGES * S::kStage;
+  uint8_t* bars_ptr = base_ptr + STAGES * S::kStage;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  const uint32_t acc_full = bars + 8u * (2 * STAGES);        // accumulator of the current tile is complete
+  const uint32_t acc_empty = bars + 8u * (2 * STAGES + 1);   // accumulator has been read out (8 warp arrivals)
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 8 * (2 * STAGES + 2));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 8 * (2 * STAGES + 2) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int num_tiles = args.num_m * args.num_n;
+  const int num_k_tiles = static_cast<int>((args.K + kBK - 1) / kBK);
+  const int nkb = static_cast<int>((args.K + 63) / 64);
+  const int nrb_b = static_cast<int>((args.N + 127) / 128);
+  constexpr uint32_t kTmemCols = 512;
+  constexpr uint32_t kSfaCol = BN, kSfbCol = BN + 16;
+
+  constexpr int kGroup = 16;
+  auto tile_coords = [&](int pid, int& tile_m, int& tile_n) {
+    const int per_group = kGroup * args.num_n;
+    const int group = pid / per_group;
+    const int first_m = group * kGroup;
+    const int group_m = min(args.num_m - first_m, kGroup);
+    tile_m = first_m + (pid % per_group) % group_m;
+    tile_n = (pid % per_group) / group_m;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 8);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+      uint32_t it = 0;                                   // k-tiles issued so far, over all tiles of this CTA
+      bool ok = true;
+      long long t_wait = 0, t0 = clock64();
+      for (int pid = blockIdx.x; pid < num_tiles && ok; pid += gridDim.x) {
+        int tile_m, tile_n;
+        tile_coords(pid, tile_m, tile_n);
+        const int b_blocks = min(BN / 128, nrb_b - tile_n * (BN / 128));
+        for (int kt = 0; kt < num_k_tiles; ++kt, ++it) {
+          const int s = it % STAGES;
+          const uint32_t round = it / STAGES;
+          const long long w0 = clock64();
+          if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, 1)) {
+            ok = false;
+            break;
+          }
+          t_wait += clock64() - w0;
+          const uint32_t stage = base + s * S::kStage;
+          const int blobs = min(4, nkb - kt * 4);
+          const uint32_t sf_bytes = blobs * 512u;
+          mbar_expect_tx(full_bar(s), S::kA + S::kB + sf_bytes * (1 + b_blocks));
+          tma_load_2d(stage, &map_a, kt * (kBK / 2), tile_m * kBM, full_bar(s));
+          tma_load_2d(stage + S::kA, &map_b, kt * (kBK / 2), tile_n * BN, full_bar(s));
+          bulk_load(stage + S::kA + S::kB, args.a_sf + (static_cast<int64_t>(tile_m) * nkb + kt * 4) * 512, sf_bytes,
+                    full_bar(s));
+          for (int h = 0; h < b_blocks; ++h)
+            bulk_load(stage + S::kA + S::kB + S::kSFA + h * 2048,
+                      args.b_sf + ((static_cast<int64_t>(tile_n) * (BN / 128) + h) * nkb + kt * 4) * 512, sf_bytes,
+                      full_bar(s));
+        }
+      }
+      if (args.debug & 8) {
+        atomicAdd(&g_gemm_prof[0], static_cast<unsigned long long>(t_wait));
+        atomicAdd(&g_gemm_prof[1], static_cast<unsigned long long>(clock64() - t0));
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (8u << 24);
+      uint32_t it = 0, local_tile = 0;
+      bool ok = true;
+      long long t_full = 0, t_acc = 0, t0 = clock64();
+      for (int pid = blockIdx.x; pid < num_tiles && ok; pid += gridDim.x, ++local_tile) {
+        if (local_tile > 0) {
+          const long long w0 = clock64();
+          ok = mbar_wait(acc_empty, (local_tile - 1) & 1, abort_flag, 4);
+          t_acc += clock64() - w0;
+          if (!ok) break;
+          tcgen05_fence_after();
+        }
+        for (int kt = 0; kt < num_k_tiles; ++kt, ++it) {
+          const int s = it % STAGES;
+          const long long w0 = clock64();
+          ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag, 2);
+          t_full += clock64() - w0;
+          if (!ok) break;
+          tcgen05_fence_after();
+          const uint32_t stage = base + s * S::kStage;
+          const int blocks = min(4, nkb - kt * 4);
+          for (int j = 0; j < blocks && !(args.debug & 4); ++j) {
+            tmem_copy_scales(tmem_base + kSfaCol + 4 * j, scale_desc(stage + S::kA + S::kB + j * 512));
+            tmem_copy_scales(tmem_base + kSfbCol + 8 * j, scale_desc(stage + S::kA + S::kB + S::kSFA + j * 512));
+            tmem_copy_scales(tmem_base + kSfbCol + 8 * j + 4,
+                             scale_desc(stage + S::kA + S::kB + S::kSFA + 2048 + j * 512));
+          }
+          const uint64_t adesc = operand_desc(stage), bdesc = operand_desc(stage + S::kA);
+          for (int j = 0; j < blocks && !(args.debug & 2); ++j)
+            mma_nvf4(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
+                     tmem_base + kSfbCol + 8 * j, (kt | j) != 0);
+          mma_commit(empty_bar(s));
+        }
+        if (ok) mma_commit(acc_full);
+      }
+      if (args.debug & 8) {
+        atomicAdd(&g_gemm_prof[2], static_cast<unsigned long long>(t_full));
+        atomicAdd(&g_gemm_prof[3], static_cast<unsigned long long>(t_acc));
+        atomicAdd(&g_gemm_prof[4], static_cast<unsigned long long>(clock64() - t0));
+      }
+    }
+  } else {
+    const int quarter = warp & 3;                        // accumulator lanes this warp may read
+    const int half = (warp - 2) >> 2;                    // 128-column half it drains
+    const float alpha = args.a_global[0] * args.b_global[0];
+    uint32_t local_tile = 0;
+    for (int pid = blockIdx.x; pid < num_tiles; pid += gridDim.x, ++local_tile) {
+      int tile_m, tile_n;
+      tile_coords(pid, tile_m, tile_n);
+      if (!mbar_wait(acc_full, local_tile & 1, abort_flag, 3)) break;
+      tcgen05_fence_after();
+      const int64_t row = static_cast<int64_t>(tile_m) * kBM + quarter * 32 + lane;
+#pragma unroll 1
+      for (int c = half * 128; c < half * 128 + 128; c += 32) {
+        uint32_t acc[32];
+        tmem_load32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c, acc);
+        if (c == half * 128 + 96) {                      // last read of this warp: hand the accumulator back
+          tcgen05_fence_before();
+          __syncwarp();
+          if (lane == 0) mbar_arrive(acc_empty);
+        }
+        const int64_t col = static_cast<int64_t>(tile_n) * BN + c;
         if (row < args.M && col < args.N) {
           const int64_t left = args.N - col;
           const int valid = left < 32 ? static_cast<int>(left) : 32;
@@ -377,6 +569,24 @@ static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, GemmArgs 
   return 0;
 }
 
+template <int STAGES>
+static int launch_persistent(const uint8_t* a_codes, const uint8_t* b_codes, GemmArgs args, int device, cudaStream_t st) {
+  using S = GemmSmem<256, STAGES>;
+  CUtensorMap map_a, map_b;
+  if (int rc = make_operand_map(&map_a, a_codes, args.M, args.K, kBM)) return rc;
+  if (int rc = make_operand_map(&map_b, b_codes, args.N, args.K, 256)) return rc;
+  args.num_m = static_cast<int>((args.M + kBM - 1) / kBM);
+  args.num_n = static_cast<int>((args.N + 255) / 256);
+  const int64_t tiles = static_cast<int64_t>(args.num_m) * args.num_n;
+  BL_REQUIRE(tiles <= 0x7FFFFFFF, "gemm: too many output tiles (%lld)", (long long)tiles);
+  BL_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+  const int sms = sm_count(device);
+  const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
+  gemm_persistent_kernel<STAGES><<<grid, kPersistThreads, S::kTotal, st>>>(map_a, map_b, args);
+  BL_CUDA(cudaGetLastError());
+  return 0;
+}
+
 }  // namespace blb
 
 using namespace blb;
@@ -406,11 +616,16 @@ extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const 
   args.ldc = ldc;
   args.out_dtype = out_dtype;
   args.num_m = args.num_n = 0;
+  {
+    const char* e = getenv("BL_GEMM_DEBUG");
+    args.debug = e ? atoi(e) : 0;
+  }
   static const int bn = [] {
     const char* e = getenv("BL_GEMM_BN");
     return e ? atoi(e) : 128;
   }();
   if (bn == 256) return launch_gemm<256, 4>(a_codes, b_codes, args, reinterpret_cast<cudaStream_t>(stream));
+  if (bn == 1) return launch_persistent<4>(a_codes, b_codes, args, device, reinterpret_cast<cudaStream_t>(stream));
   return launch_gemm<128, 3>(a_codes, b_codes, args, reinterpret_cast<cudaStream_t>(stream));
 }
 
@@ -422,5 +637,14 @@ extern "C" int bl_nvfp4_gemm_status(int* status, int device) {
   int zero = 0;
   BL_CUDA(cudaMemcpyFromSymbol(status, g_gemm_error, sizeof(int)));
   BL_CUDA(cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int)));
+  return 0;
+}
+
+// Experiments only: reads and clears the cycle counters of the persistent kernel (BL_GEMM_DEBUG bit 8).
+extern "C" BL_API int bl_nvfp4_gemm_prof(unsigned long long* out8, int device) {
+  BL_DEVICE(device);
+  unsigned long long zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
+  BL_CUDA(cudaMemcpyFromSymbol(out8, g_gemm_prof, sizeof(zero)));
+  BL_CUDA(cudaMemcpyToSymbol(g_gemm_prof, zero, sizeof(zero)));
   return 0;
 }

@@ -137,77 +137,65 @@ struct StepParams {
   uint32_t offset;   // RNG index of element (0, 0), low 32 bits
 };
 
+// ---- per-thread work unit: one scale group of 16 consecutive elements ------------------------------------------------
+// A thread loads the group's 8 code bytes, its phase bytes, its 16 gradient values and the scale byte, keeps its 16
+// columns while it walks down the rows, and needs no communication with other threads.
+//
+// Exactness notes (every shortcut below returns the reference's bits; the parity tests compare bit for bit):
+//  * (a, latent) of an element depend only on its code nibble and phase bits: a shared-memory table built with the
+//    reference's formula at kernel start replaces the per-element level / neighbour / latent arithmetic;
+//  * divisions sharing a divisor (the old and new group scale, a column's denominator, the RMS divisor) go through
+//    div_rn with one correctly rounded reciprocal per divisor;
+//  * the nearest level comes from the hardware E2M1 conversion (ties to even). The reference breaks ties to the lower
+//    level, but the projection is invariant to that choice: a target exactly half-way between levels L < U gives
+//    (U, phase -half) from either side (from L the phase code reaches +half and carries over), and with 0 phase bits
+//    both sides draw U with probability 1/2 from the same random number;
+//  * gaps between neighbouring levels are powers of two read off the exponent of the level, so dividing by a half
+//    gap is a multiplication by an exact reciprocal and (t - w) / width needs no clamp (|t - w| <= width).
+
+template <int PCB> struct PhaseWord;
+template <> struct PhaseWord<0> { using type = uint32_t; };
+template <> struct PhaseWord<1> { using type = uint16_t; };
+template <> struct PhaseWord<2> { using type = uint32_t; };
+template <> struct PhaseWord<4> { using type = uint2; };
+template <> struct PhaseWord<8> { using type = uint4; };
+
+// raw container value (PCB bits) of element i of the group
 template <int PCB>
-__device__ __forceinline__ void load_phase(const uint8_t* p, int pb, int ph[8]) {
-  if constexpr (PCB == 0) {
-#pragma unroll
-    for (int i = 0; i < 8; ++i) ph[i] = 0;
-  } else {
-    uint64_t v;
-    if constexpr (PCB == 1) v = *p;
-    else if constexpr (PCB == 2) v = *reinterpret_cast<const uint16_t*>(p);
-    else if constexpr (PCB == 4) v = *reinterpret_cast<const uint32_t*>(p);
-    else v = *reinterpret_cast<const uint64_t*>(p);
-    const int sh = 32 - pb;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      const uint32_t raw = static_cast<uint32_t>(v >> (i * PCB));
-      ph[i] = static_cast<int>(raw << sh) >> sh;      // sign-extend the low pb bits
-    }
+__device__ __forceinline__ uint32_t phase_raw(const typename PhaseWord<PCB>::type& w, int i) {
+  if constexpr (PCB == 0) return 0u;
+  else if constexpr (PCB == 1) return (static_cast<uint32_t>(w) >> i) & 1u;
+  else if constexpr (PCB == 2) return (w >> (2 * i)) & 3u;
+  else if constexpr (PCB == 4) return ((i < 8 ? w.x : w.y) >> (4 * (i & 7))) & 15u;
+  else {
+    const uint32_t word = i < 4 ? w.x : (i < 8 ? w.y : (i < 12 ? w.z : w.w));
+    return (word >> (8 * (i & 3))) & 255u;
   }
 }
 
 template <int PCB>
-__device__ __forceinline__ void store_phase(uint8_t* p, int pb, const int ph[8]) {
-  if constexpr (PCB != 0) {
-    const uint32_t mask = (1u << pb) - 1u;
-    uint64_t v = 0;
-#pragma unroll
-    for (int i = 0; i < 8; ++i) v |= static_cast<uint64_t>(static_cast<uint32_t>(ph[i]) & mask) << (i * PCB);
-    if constexpr (PCB == 1) *p = static_cast<uint8_t>(v);
-    else if constexpr (PCB == 2) *reinterpret_cast<uint16_t*>(p) = static_cast<uint16_t>(v);
-    else if constexpr (PCB == 4) *reinterpret_cast<uint32_t*>(p) = static_cast<uint32_t>(v);
-    else *reinterpret_cast<uint64_t*>(p) = v;
-  }
+__device__ __forceinline__ void phase_put(typename PhaseWord<PCB>::type& w, int i, uint32_t v) {
+  if constexpr (PCB == 1) w = static_cast<uint16_t>(w | (v << i));
+  else if constexpr (PCB == 2) w |= v << (2 * i);
+  else if constexpr (PCB == 4) (i < 8 ? w.x : w.y) |= v << (4 * (i & 7));
+  else if constexpr (PCB == 8) (i < 4 ? w.x : (i < 8 ? w.y : (i < 12 ? w.z : w.w))) |= v << (8 * (i & 3));
 }
 
-// latent position from the phase code (bitlattice/reference.py:277-281)
-__device__ __forceinline__ float latent(float w, float lo, float hi, int code, float inv_half) {
-  const float c = static_cast<float>(code) * inv_half;   // division by 2^(pb-1) is exact either way
-  return c < 0.0f ? w + c * (w - lo) * 0.5f : w + c * (hi - w) * 0.5f;
+// distance from level w to its neighbour on the side `up` (0 at the ends of the lattice): 0.5 below 2, 1 up to 4, 2
+// above, the interval being the one that contains the neighbour
+__device__ __forceinline__ float level_gap(float w, bool up) {
+  const float m = fabsf(w);
+  const bool outward = (w == 0.0f) || (up == (w > 0.0f));
+  const float x = outward ? m : m - 0.25f;
+  const uint32_t e = __float_as_uint(fmaxf(x, 1.0f)) & 0x7F800000u;
+  const float g = __uint_as_float(e - 0x00800000u);
+  return (outward && m == 6.0f) ? 0.0f : g;
 }
 
-// projection of target t around the nearest level w with neighbours lo/hi (bitlattice/reference.py:250-274);
-// returns the move (-1, 0, +1) and the new phase code
-__device__ __forceinline__ int project(float t, float w, float lo, float hi, float u, int pb, float half, int* code) {
-  if (pb == 0) {
-    const bool up = t >= w;
-    const float a = up ? w : lo, b = up ? hi : w;
-    const float gap = b - a;
-    const float p = gap > 0.0f ? (t - a) / gap : 0.0f;
-    const bool take_b = u < p;
-    *code = 0;
-    return up ? (take_b ? 1 : 0) : (take_b ? 0 : -1);
-  }
-  const bool left = t < w;
-  const float width = left ? (w - lo) * 0.5f : (hi - w) * 0.5f;
-  float c = width > 0.0f ? (t - w) / width : 0.0f;
-  c = fminf(fmaxf(c, -1.0f), 1.0f);
-  const float q = c * half;
-  const float fl = floorf(q);
-  float k = fl + ((u < (q - fl)) ? 1.0f : 0.0f);
-  int move = 0;
-  if (k >= half) {
-    if (hi > w) {
-      move = 1;
-      k = -half;
-    } else {
-      k = half - 1.0f;
-    }
-  }
-  *code = static_cast<int>(k);
-  return move;
-}
+// reciprocal of a power of two in the normal range
+__device__ __forceinline__ float rcp_pow2(float x) { return __uint_as_float(0x7F000000u - __float_as_uint(x)); }
+
+constexpr float kMagic = 12582912.0f;     // 1.5 * 2^23: adding it leaves the integer part in the low mantissa bits
 
 // DIR: 0 = D given as fp32, 1 = raw, 2 = sign, 3 = colnorm (the gradient is read as GT)
 template <int PCB, int DIR, typename GT>
@@ -217,100 +205,161 @@ __global__ void __launch_bounds__(kThreads) update_kernel(uint8_t* __restrict__ 
                                                           const GT* __restrict__ grad, const float* __restrict__ denom,
                                                           const float* __restrict__ stats, int64_t rows, int64_t cols,
                                                           StepParams P) {
-  const int64_t cc = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;   // 8-column chunk of this thread
-  const bool active = cc * 8 < cols;
+  using PW = typename PhaseWord<PCB>::type;
+  __shared__ float2 lut[16 << PCB];                 // (level a, latent) by code nibble | phase container << 4
+  {
+    const float inv_half = 1.0f / static_cast<float>(1 << (P.pb > 0 ? P.pb - 1 : 0));
+    const int sh = 32 - P.pb;
+    for (int e = threadIdx.y * blockDim.x + threadIdx.x; e < (16 << PCB); e += kThreads) {
+      const int rk = rank_of_code(e & 15);
+      const float av = level_of_rank(rk);
+      float lam = av;
+      if (PCB != 0) {
+        const int ph = static_cast<int>(static_cast<uint32_t>(e >> 4) << sh) >> sh;     // sign-extend pb bits
+        const float c = static_cast<float>(ph) * inv_half;
+        const float lo = level_of_rank(max(rk - 1, 0)), hi = level_of_rank(min(rk + 1, 14));
+        lam = c < 0.0f ? av + c * (av - lo) * 0.5f : av + c * (hi - av) * 0.5f;
+      }
+      lut[e] = make_float2(av, lam);
+    }
+  }
+  __syncthreads();
+
+  const int64_t cg = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;   // 16-column group of this thread
+  if (cg * 16 >= cols) return;
   const float gs = global_scale[0];
+  const float rgs = __frcp_rn(gs);
   const float div = stats != nullptr ? stats[1] : 1.0f;
-  const bool use_div = stats != nullptr;
-  float den[8];
-  if (DIR == 3 && active) {
-    const float4 a = reinterpret_cast<const float4*>(denom + cc * 8)[0];
-    const float4 b = reinterpret_cast<const float4*>(denom + cc * 8)[1];
-    den[0] = a.x; den[1] = a.y; den[2] = a.z; den[3] = a.w;
-    den[4] = b.x; den[5] = b.y; den[6] = b.z; den[7] = b.w;
+  const bool use_div = DIR != 0 && stats != nullptr && div != 1.0f;
+  const float rdiv = __frcp_rn(div);
+  float den[DIR == 3 ? 16 : 1], rden[DIR == 3 ? 16 : 1];
+  if constexpr (DIR == 3) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      den[i] = denom[cg * 16 + i];
+      rden[i] = __frcp_rn(den[i]);
+    }
   }
   const float half = static_cast<float>(1 << (P.pb > 0 ? P.pb - 1 : 0));
-  const float inv_half = 1.0f / half;
+  const uint32_t pmask = (1u << P.pb) - 1u;
   const int64_t code_stride = cols / 2, phase_stride = cols * PCB / 8, scale_stride = cols / 16;
   const int64_t row_step = static_cast<int64_t>(gridDim.y) * blockDim.y;
 
   for (int64_t r = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; r < rows; r += row_step) {
-    float a[8], tau[8], tf[8];
-    float s_old = 1.0f;
-    uint32_t sb_old = 0;
-    if (active) {
-      const uint32_t word = *reinterpret_cast<const uint32_t*>(codes + r * code_stride + cc * 4);
-      int ph[8];
-      load_phase<PCB>(phase + r * phase_stride + cc * PCB, P.pb, ph);
-      float gv[8];
-      load8(grad + r * cols + cc * 8, gv);
-      sb_old = scales_in[r * scale_stride + (cc >> 1)];
-      s_old = e4m3_decode(sb_old) * gs;
+    // ---- loads
+    const uint2 cw = *reinterpret_cast<const uint2*>(codes + r * code_stride + cg * 8);
+    PW pw{};
+    if constexpr (PCB != 0) pw = *reinterpret_cast<const PW*>(phase + r * phase_stride + cg * (2 * PCB));
+    float gv[16];
+    load8(grad + r * cols + cg * 16, gv);
+    load8(grad + r * cols + cg * 16 + 8, gv + 8);
+    const uint32_t sb_old = scales_in[r * scale_stride + cg];
+    const float s_old = e4m3_decode(sb_old) * gs;
+    const float inv_s = __frcp_rn(s_old);
+
+    // ---- latent target and the sums of the scale fit
+    float tau[16];
+    float saa[2] = {0.0f, 0.0f}, sat[2] = {0.0f, 0.0f}, stt[2] = {0.0f, 0.0f};
 #pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        const int rk = rank_of_code((word >> (4 * i)) & 0xFu);
-        const float av = level_of_rank(rk);
-        const float lo = level_of_rank(max(rk - 1, 0));
-        const float hi = level_of_rank(min(rk + 1, 14));
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t code = ((i < 8 ? cw.x : cw.y) >> (4 * (i & 7))) & 15u;
+      const float2 al = lut[code | (phase_raw<PCB>(pw, i) << 4)];
+      float d;
+      if (DIR == 2 && !use_div) {
+        d = gv[i] > 0.0f ? inv_s : (gv[i] < 0.0f ? -inv_s : 0.0f);        // (+-1) / s_old
+      } else {
         float u = gv[i];
         if (DIR == 2) u = static_cast<float>((u > 0.0f) - (u < 0.0f));
-        if (DIR == 3) u = u / den[i];
-        if (DIR != 0 && use_div) u = u / div;
-        const float d = u / s_old;
-        const float lam = P.pb == 0 ? av : latent(av, lo, hi, ph[i], inv_half);
-        a[i] = av;
-        tau[i] = lam * P.decay - P.lr * d;
-        tf[i] = P.rule == BL_RULE_FIT_LATENT ? tau[i] : av * P.decay - P.lr * d;
+        if (DIR == 3) u = div_rn(u, den[i], rden[i]);
+        if (use_div) u = div_rn(u, div, rdiv);
+        d = div_rn(u, s_old, inv_s);
       }
-    } else {
-#pragma unroll
-      for (int i = 0; i < 8; ++i) a[i] = tau[i] = tf[i] = 0.0f;
+      const float lrd = P.lr * d;
+      tau[i] = al.y * P.decay - lrd;
+      if (P.rule != BL_RULE_FIXED) {
+        const float tf = P.rule == BL_RULE_FIT_LATENT ? tau[i] : al.x * P.decay - lrd;
+        const int h = i >> 3;
+        saa[h] = saa[h] + al.x * al.x;
+        sat[h] = sat[h] + al.x * tf;
+        stt[h] = stt[h] + tf * tf;
+      }
     }
-    float s_new = s_old;
+
+    // ---- group scale inside the trust region (bitlattice/reference.py:307-321)
+    float s_new = s_old, inv_new = inv_s;
     uint32_t sb_new = sb_old;
     if (P.rule != BL_RULE_FIXED) {
-      float saa = 0.0f, sat = 0.0f, stt = 0.0f;
-#pragma unroll
-      for (int i = 0; i < 8; ++i) {
-        saa = saa + a[i] * a[i];
-        sat = sat + a[i] * tf[i];
-        stt = stt + tf[i] * tf[i];
-      }
-      saa = saa + __shfl_xor_sync(0xffffffffu, saa, 1);
-      sat = sat + __shfl_xor_sync(0xffffffffu, sat, 1);
-      stt = stt + __shfl_xor_sync(0xffffffffu, stt, 1);
-      float rr = saa > 0.0f ? sat / saa : 1.0f;
+      const float SAA = saa[0] + saa[1], SAT = sat[0] + sat[1], STT = stt[0] + stt[1];
+      float rr = SAA > 0.0f ? SAT / SAA : 1.0f;
       rr = fminf(fmaxf(rr, P.r_lo), P.r_hi);
-      const uint32_t bits = e4m3_encode(s_old * rr / gs);
+      const uint32_t bits = e4m3_encode(div_rn(s_old * rr, gs, rgs));
       const float cand = e4m3_decode(bits) * gs;
-      const float q = cand / s_old;
-      const float before = stt - 2.0f * sat + saa;
-      const float after = q * q * saa - 2.0f * q * sat + stt;
-      if ((after <= before) && isfinite(cand) && cand > 0.0f) {
+      const float q = div_rn(cand, s_old, inv_s);
+      const float before = STT - 2.0f * SAT + SAA;
+      const float after = q * q * SAA - 2.0f * q * SAT + STT;
+      if ((after <= before) && isfinite(cand) && cand > 0.0f && bits != sb_old) {
         s_new = cand;
         sb_new = bits;
+        inv_new = __frcp_rn(s_new);
       }
     }
-    if (!active) continue;
-    if ((threadIdx.x & 1) == 0) scales_out[r * scale_stride + (cc >> 1)] = static_cast<uint8_t>(sb_new);
-    const uint32_t idx0 = P.offset + static_cast<uint32_t>(static_cast<uint64_t>(r) * cols + cc * 8);
-    uint32_t word = 0;
-    int ph[8];
+    scales_out[r * scale_stride + cg] = static_cast<uint8_t>(sb_new);
+
+    // ---- projection back to (code, phase) (bitlattice/reference.py:250-274, 324-334)
+    const uint32_t idx0 = P.offset + static_cast<uint32_t>(static_cast<uint64_t>(r) * cols + cg * 16);
+    uint2 cout = make_uint2(0u, 0u);
+    PW pout{};
 #pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      float t = tau[i] * s_old / s_new;
-      t = fminf(fmaxf(t, -6.0f), 6.0f);
-      int rk = nearest_rank(t);
-      const float w = level_of_rank(rk);
-      const float lo = level_of_rank(max(rk - 1, 0));
-      const float hi = level_of_rank(min(rk + 1, 14));
-      const float u = rounding_u(P.rp, idx0 + i);
-      rk += project(t, w, lo, hi, u, P.pb, half, &ph[i]);
-      rk = min(max(rk, 0), 14);
-      word |= code_of_rank(rk) << (4 * i);
+    for (int i = 0; i < 16; i += 2) {
+      float fin[2];
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        float t = div_rn(tau[i + e] * s_old, s_new, inv_new);
+        t = fminf(fmaxf(t, -6.0f), 6.0f);
+        fin[e] = t;
+      }
+      // nearest levels of the pair through the hardware conversion and back
+      const uint32_t near2 = cvt_e2m1x2(fin[1], fin[0]);
+      float w2[2];
+      {
+        uint32_t h2;
+        asm("{\n\t.reg .b8 b;\n\tcvt.u8.u32 b, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b;\n\t}" : "=r"(h2) : "r"(near2));
+        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+        w2[0] = f.x;
+        w2[1] = f.y;
+      }
+#pragma unroll
+      for (int e = 0; e < 2; ++e) {
+        const float t = fin[e], w = w2[e];
+        const float u = rounding_u(P.rp, idx0 + i + e);
+        const bool up = !(t < w);
+        const float gap = level_gap(w, up);
+        float out;
+        if (PCB == 0) {
+          const float a = up ? w : w - gap;
+          const float p = gap > 0.0f ? (t - a) * rcp_pow2(gap) : 0.0f;
+          out = (u < p) ? a + gap : a;
+        } else {
+          const float width = gap * 0.5f;
+          const float c = width > 0.0f ? (t - w) * rcp_pow2(width) : 0.0f;
+          const float q = c * half;
+          const float flm = __fadd_rd(q, kMagic);                  // kMagic + floor(q), exact
+          const float fr = q - (flm - kMagic);
+          uint32_t k = __float_as_uint(flm) + ((u < fr) ? 1u : 0u);   // low bits: floor(q) + carry-in, two's complement
+          const bool carry = ((flm - kMagic) + ((u < fr) ? 1.0f : 0.0f)) >= half;
+          out = carry ? w + gap : w;                               // a carry implies gap > 0 (not the top level)
+          if (carry) k = static_cast<uint32_t>(-static_cast<int>(half));
+          phase_put<PCB>(pout, i + e, k & pmask);
+        }
+        fin[e] = out;
+      }
+      const uint32_t byte = cvt_e2m1x2(fin[1], fin[0]);            // exact: both are levels
+      (i < 8 ? cout.x : cout.y) |= byte << (4 * (i & 7));
     }
-    *reinterpret_cast<uint32_t*>(codes + r * code_stride + cc * 4) = word;
-    store_phase<PCB>(phase + r * phase_stride + cc * PCB, P.pb, ph);
+    cout.x = e2m1_drop_negative_zero(cout.x);
+    cout.y = e2m1_drop_negative_zero(cout.y);
+    *reinterpret_cast<uint2*>(codes + r * code_stride + cg * 8) = cout;
+    if constexpr (PCB != 0) *reinterpret_cast<PW*>(phase + r * phase_stride + cg * (2 * PCB)) = pout;
   }
 }
 
@@ -352,9 +401,9 @@ struct Geometry {
   dim3 block, grid;
 };
 
-// threads along x cover 8-column chunks (a power of two >= 32 so a warp never spans two rows), y covers rows
-static Geometry geometry(int64_t rows, int64_t cols, int device) {
-  const int64_t cpr = cols / 8;
+// threads along x cover `per`-column chunks (a power of two >= 32 so a warp never spans two rows), y covers rows
+static Geometry geometry(int64_t rows, int64_t cols, int device, int per = 16) {
+  const int64_t cpr = cols / per;
   int bx = 32;
   while (bx < 256 && bx < cpr) bx <<= 1;
   const int by = kThreads / bx;
@@ -470,7 +519,7 @@ static int direction_typed(const GT* grad, int64_t rows, int64_t cols, int direc
     denom = s.denom;
     stats = s.stats;
   }
-  const Geometry g = geometry(rows, cols, device);
+  const Geometry g = geometry(rows, cols, device, 8);
   if (direction == BL_DIR_RAW) direction_kernel<1, GT><<<g.grid, g.block, 0, st>>>(grad, denom, stats, rows, cols, D);
   else if (direction == BL_DIR_SIGN) direction_kernel<2, GT><<<g.grid, g.block, 0, st>>>(grad, denom, stats, rows, cols, D);
   else direction_kernel<3, GT><<<g.grid, g.block, 0, st>>>(grad, denom, stats, rows, cols, D);

@@ -92,6 +92,33 @@ def test_step_quantized_matches_oracle(bits, rule):
         assert (rs != scales).mean() > 0.05          # the refit is exercised
 
 
+@pytest.mark.parametrize("bits", [1, 2, 4, 8])
+def test_update_at_exact_ties_matches_oracle(bits):
+    """Phase codes of -half with a zero gradient put every target exactly half-way between two levels: the kernel
+    finds the nearest level with the hardware conversion (ties to even), the reference with ties to the lower level;
+    the projected (code, phase) must agree all the same. Mixed with +max phase codes and a few non-zero gradients."""
+    from bitlattice_b200.packing import pack
+    rows, cols = 64, 256
+    codes, scales, g = nvfp4_weights(rows, cols, 13)
+    half = 1 << (bits - 1)
+    raw = torch.full((rows, cols), -half, dtype=torch.int32)
+    raw[::3] = half - 1
+    cb = _ops.phase_container(bits)
+    ph = pack(raw & ((1 << bits) - 1), cb).numpy()
+    D = torch.zeros(rows, cols)
+    D[::5, ::7] = torch.randn(rows, cols, generator=gen(14))[::5, ::7]
+    for rule in ("fixed", "fit"):
+        kw = dict(lr=1e-3, weight_decay=0.0, phase_bits=bits, rounding="sr", seed=3, step=2, scale_rule=rule, trust=0.1,
+                  trust_lr=0.0)
+        rc, rp, rs = oracle.lattice_step(codes, ph, scales, g, D.numpy(), **kw)
+        packed, phase = dev(codes), dev(ph)
+        new_scales = _ops.step_quantized(packed, phase, dev(scales), dev(np.array([g], np.float32)), None, dev(D),
+                                         "nvfp4", rows, cols, phase_cb=cb, strata=16, **kw)
+        assert np.array_equal(host(new_scales), rs)
+        assert np.array_equal(host(packed), rc)
+        assert np.array_equal(host(phase), rp)
+
+
 @pytest.mark.parametrize("direction", ["sign", "raw", "colnorm"])
 @pytest.mark.parametrize("clip", [1.0, 0.25])
 @pytest.mark.parametrize("gdtype", [torch.bfloat16, torch.float32])
