@@ -31,6 +31,11 @@ _SIGNATURES = {
                                            _c.c_int, _c.c_double, _c.c_double, _c.c_int, _c.c_uint32, _c.c_uint32,
                                            _c.c_int, _c.c_int, _c.c_int, _c.c_double, _c.c_int, _c.c_double, _P,
                                            _c.c_size_t, _c.c_int, _P]),
+    "bl_update_fixed_scratch_capacity": (_c.c_size_t, []),
+    "bl_nvfp4_lattice_update_fixed_scratch": (_c.c_int, [_P, _P, _P, _P, _P, _c.c_int, _c.c_int64, _c.c_int64,
+                                                         _c.c_uint64, _c.c_int, _c.c_int, _c.c_double, _c.c_double,
+                                                         _c.c_int, _c.c_uint32, _c.c_uint32, _c.c_int, _c.c_int,
+                                                         _c.c_int, _c.c_double, _c.c_int, _c.c_double, _c.c_int, _P]),
     "bl_direction": (_c.c_int, [_P, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int, _c.c_double, _P, _P, _c.c_size_t,
                                 _c.c_int, _P]),
     "bl_nvfp4_dequantize": (_c.c_int, [_P, _P, _P, _c.c_int64, _c.c_int64, _P, _c.c_int, _c.c_int, _P]),
@@ -91,7 +96,8 @@ def check(status: int) -> None:
 
 # kernels each entry point launches (memsets not counted); the lattice update launches 3 when it needs column
 # statistics, the transposed quantizer 3 without a scale bound
-KERNELS_PER_CALL = {"bl_nvfp4_step_quantized": 1, "bl_nvfp4_lattice_update": 1, "bl_direction": 1,
+KERNELS_PER_CALL = {"bl_nvfp4_step_quantized": 1, "bl_nvfp4_lattice_update": 1,
+                    "bl_nvfp4_lattice_update_fixed_scratch": 1, "bl_direction": 1,
                     "bl_nvfp4_dequantize": 1, "bl_nvfp4_amax": 1, "bl_nvfp4_quantize": 1, "bl_nvfp4_quantize_t": 2,
                     "bl_nvfp4_requantize_t": 1, "bl_nvfp4_scales_to_blocked": 1, "bl_nvfp4_gemm": 1}
 

@@ -12,6 +12,8 @@
 // One thread owns 8 consecutive elements of a row (one 32-bit code word, cb bytes of phase, 16 or 32 bytes of
 // gradient); two neighbouring lanes share a 16-element scale group and exchange its three sums with one shuffle each.
 // A thread keeps its 8 columns while it walks down the rows, so per-column statistics (colnorm) stay in registers.
+#include <mutex>
+
 #include "common.cuh"
 
 namespace blb {
@@ -605,4 +607,68 @@ extern "C" int bl_direction(const void* grad, int grad_dtype, int64_t rows, int6
   if (grad_dtype == BL_F16)
     return direction_typed(static_cast<const __half*>(grad), rows, cols, direction, clip, D, scratch, device, st);
   return direction_typed(static_cast<const float*>(grad), rows, cols, direction, clip, D, scratch, device, st);
+}
+
+// ------------------------------------------------------------------------------------------------ fixed-scratch variant
+// The column statistics of the update live here instead of in a caller-provided buffer. The array is part of the
+// library image: every GPU that loads the library keeps these bytes until the process exits.
+constexpr size_t kFixedScratchBytes = size_t(4) << 20;
+static __device__ __align__(256) unsigned char g_fixed_scratch[kFixedScratchBytes];
+
+// In host code `g_fixed_scratch` is only a handle for the runtime, never an address a kernel may use: the device
+// address is asked for once per device, with that device current, and kept.
+static int fixed_scratch_address(int device, void** out) {
+  static std::mutex mu;
+  static void* cached[64];
+  BL_REQUIRE(device >= 0 && device < 64, "lattice_update_fixed_scratch: device index %d out of range", device);
+  std::lock_guard<std::mutex> lock(mu);
+  if (cached[device] == nullptr) {
+    void* p = nullptr;
+    BL_CUDA(cudaGetSymbolAddress(&p, g_fixed_scratch));
+    BL_REQUIRE(p != nullptr, "lattice_update_fixed_scratch: no device address for the scratch array");
+    cached[device] = p;
+  }
+  *out = cached[device];
+  return 0;
+}
+
+extern "C" size_t bl_update_fixed_scratch_capacity(void) { return kFixedScratchBytes; }
+
+extern "C" int bl_nvfp4_lattice_update_fixed_scratch(uint8_t* codes, uint8_t* phase, uint8_t* scales,
+                                                     const float* global_scale, const void* grad, int grad_dtype,
+                                                     int64_t rows, int64_t cols, uint64_t offset, int phase_bits,
+                                                     int phase_cb, double lr, double decay, int rounding,
+                                                     uint32_t seed, uint32_t step, int strat_j, int strat_k, int rule,
+                                                     double kappa, int direction, double clip, int device,
+                                                     bl_stream_t stream) {
+  if (int rc = check_common(rows, cols, phase_bits, phase_cb, phase, rounding, rule)) return rc;
+  BL_REQUIRE(codes && scales && global_scale && grad, "lattice_update_fixed_scratch: null buffer");
+  BL_REQUIRE(direction >= BL_DIR_RAW && direction <= BL_DIR_COLNORM,
+             "lattice_update_fixed_scratch: direction %d is not built (raw, sign and colnorm are)", direction);
+  BL_REQUIRE(clip > 0.0, "lattice_update_fixed_scratch: clip must be positive");
+  BL_REQUIRE(grad_dtype >= BL_F32 && grad_dtype <= BL_F16, "lattice_update_fixed_scratch: unknown gradient dtype %d",
+             grad_dtype);
+  BL_REQUIRE(aligned16(codes) && aligned16(grad) && (phase == nullptr || aligned16(phase)),
+             "lattice_update_fixed_scratch: codes, phase and gradient must be 16-byte aligned");
+  const size_t need = bl_update_scratch_bytes(rows, cols, direction, clip);
+  BL_REQUIRE(need <= kFixedScratchBytes,
+             "lattice_update_fixed_scratch: a %lld x %lld gradient needs %zu bytes of column statistics, the built-in "
+             "scratch holds %zu; use bl_nvfp4_lattice_update with a buffer of your own",
+             (long long)rows, (long long)cols, need, kFixedScratchBytes);
+  BL_DEVICE(device);
+  void* scratch = nullptr;
+  if (int rc = fixed_scratch_address(device, &scratch)) return rc;
+  const StepParams P = make_params(lr, decay, phase_bits, rule, kappa, rounding, seed, step, strat_j, strat_k, offset);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const int pcb = phase_bits ? phase_cb : 0;
+  // run_stats clears the arrival counter and overwrites every statistic it later reads, so what an earlier call left
+  // in the array does not matter
+  if (grad_dtype == BL_BF16)
+    return update_typed(codes, phase, scales, global_scale, static_cast<const __nv_bfloat16*>(grad), rows, cols, pcb, P,
+                        direction, clip, scratch, device, st);
+  if (grad_dtype == BL_F16)
+    return update_typed(codes, phase, scales, global_scale, static_cast<const __half*>(grad), rows, cols, pcb, P,
+                        direction, clip, scratch, device, st);
+  return update_typed(codes, phase, scales, global_scale, static_cast<const float*>(grad), rows, cols, pcb, P, direction,
+                      clip, scratch, device, st);
 }

@@ -80,6 +80,27 @@ BL_API int bl_nvfp4_lattice_update(uint8_t* codes, uint8_t* phase, uint8_t* scal
                             uint32_t step, int strat_j, int strat_k, int rule, double kappa, int direction,
                             double clip, void* scratch, size_t scratch_bytes, int device, bl_stream_t stream);
 
+/* No counterpart in the reference. The same update as bl_nvfp4_lattice_update for callers that have no way to hand
+ * over scratch memory: code running where cudaMalloc and the framework allocators are off limits -- a serving loop
+ * with a frozen memory plan, a host thread that must not take the allocator's locks or trigger its implicit device
+ * synchronisation, a plugin that only ever receives the tensors it works on. The column statistics go into an array
+ * that is part of the library image (bl_update_fixed_scratch_capacity() bytes, 4 MiB; every GPU that loads the
+ * library holds it until the process exits). Nothing is allocated or freed, here or in anything this calls.
+ *  - Shapes whose statistics do not fit (bl_update_scratch_bytes(...) above the capacity) are refused with an error;
+ *    4 MiB covers e.g. 12288 x 4096, 4096 x 12288 and 8192 x 8192.
+ *  - The first call on a device looks up the array's device address (cudaGetSymbolAddress, with that device
+ *    current) and keeps it; make that first call before any stream capture.
+ *  - All calls on a device share the one array. Each call resets the arrival counter it uses and overwrites every
+ *    statistic before reading it, so earlier contents never matter; two calls whose kernels may run at the same time
+ *    (different streams) race on it -- order them. */
+BL_API size_t bl_update_fixed_scratch_capacity(void);
+BL_API int bl_nvfp4_lattice_update_fixed_scratch(uint8_t* codes, uint8_t* phase, uint8_t* scales,
+                                                 const float* global_scale, const void* grad, int grad_dtype,
+                                                 int64_t rows, int64_t cols, uint64_t offset, int phase_bits,
+                                                 int phase_cb, double lr, double decay, int rounding, uint32_t seed,
+                                                 uint32_t step, int strat_j, int strat_k, int rule, double kappa,
+                                                 int direction, double clip, int device, bl_stream_t stream);
+
 /* Replaces torch.ops.bitlattice.direction for raw / sign / colnorm (csrc/bindings.cpp:90-92,
  * csrc/directions.cpp:145-191): writes the fp32 direction D [rows, cols]. */
 BL_API int bl_direction(const void* grad, int grad_dtype, int64_t rows, int64_t cols, int direction, double clip, float* D,
