@@ -58,11 +58,34 @@ __device__ __forceinline__ bool mbar_try_wait(uint32_t bar, uint32_t parity) {
   return ok != 0;
 }
 
+// mode 1: non-blocking test with cluster-scope acquire; mode 2: potentially blocking try with cluster-scope acquire
+__device__ __forceinline__ bool mbar_probe_cluster(uint32_t bar, uint32_t parity, int mode) {
+  uint32_t ok;
+  if (mode == 1)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.test_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n\t"
+        "selp.u32 %0, 1, 0, p;\n\t}"
+        : "=r"(ok)
+        : "r"(bar), "r"(parity)
+        : "memory");
+  return ok != 0;
+}
+
 // Bounded wait: returns false when the limit expires, or when another warp of this CTA (*abort_flag) or another CTA
 // (g_gemm_error) already gave up.
-__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code) {
+__device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
+                                          int mode = 0) {
   for (uint32_t i = 0; i < kSpinLimit; ++i) {
-    if (mbar_try_wait(bar, parity)) return true;
+    if (mode == 0 ? mbar_try_wait(bar, parity) : mbar_probe_cluster(bar, parity, mode)) return true;
     if ((i & 1023u) == 1023u && (*abort_flag != 0 || *reinterpret_cast<volatile int*>(&g_gemm_error) != 0))
       return false;
   }
@@ -140,7 +163,198 @@ __device__ __forceinline__ void tmem_load32(uint32_t taddr, uint32_t r[32]) {
   asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tmem_load32_async(uint32_t taddr, uint32_t* r) {
+  asm volatile(
+      "tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+      "{%0, %1, %2, %3, %4, %5, %6, %7, %8, %9, %10, %11, %12, %13, %14, %15, "
+      "%16, %17, %18, %19, %20, %21, %22, %23, %24, %25, %26, %27, %28, %29, %30, %31}, [%32];"
+      : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+        "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+        "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+        "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+      : "r"(taddr)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// Variants for a fully converged warp: every lane runs the same control flow with warp-uniform operands and one
+// elected lane issues the instruction.
+__device__ __forceinline__ void mbar_expect_tx_elect(uint32_t bar, uint32_t bytes) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_elect(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "@p cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n\t}"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void bulk_load_elect(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n\t}"
+      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void tmem_copy_scales_elect(uint32_t taddr, uint64_t sdesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "@p tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n\t}" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+__device__ __forceinline__ void mma_nvf4_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                               uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void mma_commit_elect(uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "@p tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar) : "memory");
+}
+
 // ------------------------------------------------------------------------------------------------ kernel
+
+// One election for a burst of instructions: q is 1 in the elected lane and 0 elsewhere; the *_if wrappers issue their
+// instruction under that predicate while the warp stays converged.
+__device__ __forceinline__ uint32_t elect_one() {
+  uint32_t q;
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "selp.u32 %0, 1, 0, p;\n\t}"
+      : "=r"(q));
+  return q;
+}
+
+__device__ __forceinline__ void mbar_expect_tx_if(uint32_t q, uint32_t bar, uint32_t bytes) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %0, 0;\n\t"
+      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%1], %2;\n\t}" ::"r"(q), "r"(bar), "r"(bytes) : "memory");
+}
+
+__device__ __forceinline__ void tma_load_2d_if(uint32_t q, uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %0, 0;\n\t"
+      "@p cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%1], [%2, {%3, %4}], [%5];\n\t}"
+      ::"r"(q), "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
+      : "memory");
+}
+
+__device__ __forceinline__ void bulk_load_if(uint32_t q, uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %0, 0;\n\t"
+      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%1], [%2], %3, [%4];\n\t}"
+      ::"r"(q), "r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
+      : "memory");
+}
+
+template <int CG>
+__device__ __forceinline__ void mma_commit_if(uint32_t q, uint32_t bar) {
+  if constexpr (CG == 1)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %0, 0;\n\t"
+        "@p tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}" ::"r"(q), "r"(bar)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %0, 0;\n\t"
+        "@p tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%1];\n\t}" ::"r"(q), "r"(bar)
+        : "memory");
+}
+
+template <int CG>
+__device__ __forceinline__ void tmem_copy_scales_if(uint32_t q, uint32_t taddr, uint64_t sdesc) {
+  if constexpr (CG == 1)
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %0, 0;\n\t"
+        "@p tcgen05.cp.cta_group::1.32x128b.warpx4 [%1], %2;\n\t}" ::"r"(q), "r"(taddr), "l"(sdesc) : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %0, 0;\n\t"
+        "@p tcgen05.cp.cta_group::2.32x128b.warpx4 [%1], %2;\n\t}" ::"r"(q), "r"(taddr), "l"(sdesc) : "memory");
+}
+
+template <int CG>
+__device__ __forceinline__ void mma_nvf4_if(uint32_t q, uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                            uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  if constexpr (CG == 1)
+    asm volatile(
+        "{\n\t.reg .pred p, a;\n\t"
+        "setp.ne.b32 p, %0, 0;\n\t"
+        "setp.ne.b32 a, %7, 0;\n\t"
+        "@p tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%1], %2, %3, %4, [%5], [%6], a;\n\t}"
+        ::"r"(q), "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+        : "memory");
+  else
+    asm volatile(
+        "{\n\t.reg .pred p, a;\n\t"
+        "setp.ne.b32 p, %0, 0;\n\t"
+        "setp.ne.b32 a, %7, 0;\n\t"
+        "@p tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%1], %2, %3, %4, [%5], [%6], a;\n\t}"
+        ::"r"(q), "r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+        : "memory");
+}
+
+// Scale copies and MMAs of one full k-tile (4 blocks of 64 along K) of a 256-wide tile, from one elected lane.
+//   sf_desc: descriptor of the stage's first A-scale blob; the B-scale blobs follow 2048 and 4096 bytes later
+//   ORDER 0: all copies, then all MMAs; 1: copies of block j right before MMA j; 2: copies one block ahead of the MMAs
+template <int CG, int ORDER>
+__device__ __forceinline__ void issue_k_tile(uint32_t q, uint32_t acc_t, uint32_t sfa_t, uint32_t sfb_t, uint64_t sf_desc,
+                                             uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+  auto copies = [&](int j) {
+    tmem_copy_scales_if<CG>(q, sfa_t + 4 * j, sf_desc + 32u * j);
+    tmem_copy_scales_if<CG>(q, sfb_t + 8 * j, sf_desc + 128u + 32u * j);
+    tmem_copy_scales_if<CG>(q, sfb_t + 8 * j + 4, sf_desc + 256u + 32u * j);
+  };
+  auto mma = [&](int j) {
+    mma_nvf4_if<CG>(q, acc_t, a_desc + 2u * j, b_desc + 2u * j, idesc, sfa_t + 4 * j, sfb_t + 8 * j,
+                    j == 0 ? accumulate : 1u);
+  };
+  if constexpr (ORDER == 0) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) copies(j);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) mma(j);
+  } else if constexpr (ORDER == 1) {
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      copies(j);
+      mma(j);
+    }
+  } else {
+    copies(0);
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      if (j < 3) copies(j + 1);
+      mma(j);
+    }
+  }
+}
 
 template <int BN, int STAGES>
 struct GemmSmem {
@@ -340,7 +554,7 @@ __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
-template <int STAGES>
+template <int STAGES, int ORDER>
 __global__ void __launch_bounds__(kPersistThreads, 1) gemm_persistent_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                              const __grid_constant__ CUtensorMap map_b,
                                                                              GemmArgs args) {
@@ -395,108 +609,432 @@ __global__ void __launch_bounds__(kPersistThreads, 1) gemm_persistent_kernel(con
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
+    // ------------------------------------------------------------------ producer: whole warp converged, one lane issues
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
-      uint32_t it = 0;                                   // k-tiles issued so far, over all tiles of this CTA
-      bool ok = true;
-      long long t_wait = 0, t0 = clock64();
-      for (int pid = blockIdx.x; pid < num_tiles && ok; pid += gridDim.x) {
-        int tile_m, tile_n;
-        tile_coords(pid, tile_m, tile_n);
-        const int b_blocks = min(BN / 128, nrb_b - tile_n * (BN / 128));
-        for (int kt = 0; kt < num_k_tiles; ++kt, ++it) {
-          const int s = it % STAGES;
-          const uint32_t round = it / STAGES;
-          const long long w0 = clock64();
-          if (round > 0 && !mbar_wait(empty_bar(s), (round - 1) & 1, abort_flag, 1)) {
-            ok = false;
-            break;
-          }
-          t_wait += clock64() - w0;
-          const uint32_t stage = base + s * S::kStage;
-          const int blobs = min(4, nkb - kt * 4);
-          const uint32_t sf_bytes = blobs * 512u;
-          mbar_expect_tx(full_bar(s), S::kA + S::kB + sf_bytes * (1 + b_blocks));
-          tma_load_2d(stage, &map_a, kt * (kBK / 2), tile_m * kBM, full_bar(s));
-          tma_load_2d(stage + S::kA, &map_b, kt * (kBK / 2), tile_n * BN, full_bar(s));
-          bulk_load(stage + S::kA + S::kB, args.a_sf + (static_cast<int64_t>(tile_m) * nkb + kt * 4) * 512, sf_bytes,
-                    full_bar(s));
-          for (int h = 0; h < b_blocks; ++h)
-            bulk_load(stage + S::kA + S::kB + S::kSFA + h * 2048,
-                      args.b_sf + ((static_cast<int64_t>(tile_n) * (BN / 128) + h) * nkb + kt * 4) * 512, sf_bytes,
-                      full_bar(s));
+    }
+    __syncwarp();
+    int s = 0;
+    uint32_t phase = 1;                                    // parity that means "stage is free" (free at the start)
+    bool ok = true;
+    for (int pid = blockIdx.x; pid < num_tiles && ok; pid += gridDim.x) {
+      int tile_m, tile_n;
+      tile_coords(pid, tile_m, tile_n);
+      const int b_blocks = min(BN / 128, nrb_b - tile_n * (BN / 128));
+      const uint8_t* sfa = args.a_sf + static_cast<int64_t>(tile_m) * nkb * 512;
+      const uint8_t* sfb = args.b_sf + static_cast<int64_t>(tile_n) * (BN / 128) * nkb * 512;
+      for (int kt = 0; kt < num_k_tiles; ++kt) {
+        ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), phase, abort_flag, 1));
+        if (!ok) break;
+        const uint32_t q = elect_one();
+        const uint32_t stage = base + s * S::kStage;
+        const int blobs = min(4, nkb - kt * 4);
+        const uint32_t sf_bytes = blobs * 512u;
+        mbar_expect_tx_if(q, full_bar(s), S::kA + S::kB + sf_bytes * (1 + b_blocks));
+        tma_load_2d_if(q, stage, &map_a, kt * (kBK / 2), tile_m * kBM, full_bar(s));
+        tma_load_2d_if(q, stage + S::kA, &map_b, kt * (kBK / 2), tile_n * BN, full_bar(s));
+        bulk_load_if(q, stage + S::kA + S::kB, sfa + kt * 2048, sf_bytes, full_bar(s));
+        bulk_load_if(q, stage + S::kA + S::kB + S::kSFA, sfb + kt * 2048, sf_bytes, full_bar(s));
+        if (b_blocks == 2)
+          bulk_load_if(q, stage + S::kA + S::kB + S::kSFA + 2048, sfb + (static_cast<int64_t>(nkb) + kt * 4) * 512, sf_bytes,
+                       full_bar(s));
+        if (++s == STAGES) {
+          s = 0;
+          phase ^= 1;
         }
-      }
-      if (args.debug & 8) {
-        atomicAdd(&g_gemm_prof[0], static_cast<unsigned long long>(t_wait));
-        atomicAdd(&g_gemm_prof[1], static_cast<unsigned long long>(clock64() - t0));
       }
     }
   } else if (warp == 1) {
+    // ------------------------------------------------------------------ MMA issue: whole warp converged, one lane issues
+    constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (8u << 24);
+    int s = 0;
+    uint32_t phase = 0, acc_phase = 1;                     // the accumulator starts out free
+    bool ok = true;
+    for (int pid = blockIdx.x; pid < num_tiles && ok; pid += gridDim.x) {
+      ok = __all_sync(0xffffffffu, mbar_wait(acc_empty, acc_phase, abort_flag, 4));
+      if (!ok) break;
+      acc_phase ^= 1;
+      tcgen05_fence_after();
+      for (int kt = 0; kt < num_k_tiles; ++kt) {
+        ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), phase, abort_flag, 2));
+        if (!ok) break;
+        tcgen05_fence_after();
+        const uint32_t q = elect_one();
+        const uint32_t stage = base + s * S::kStage;
+        const int blocks = min(4, nkb - kt * 4);
+        const uint64_t adesc = operand_desc(stage), bdesc = operand_desc(stage + S::kA);
+        const uint64_t sdesc = scale_desc(stage + S::kA + S::kB);
+        if (blocks == 4) {
+          issue_k_tile<1, ORDER>(q, tmem_base, tmem_base + kSfaCol, tmem_base + kSfbCol, sdesc, adesc, bdesc, idesc,
+                                 kt != 0);
+        } else {
+          for (int j = 0; j < blocks; ++j) {
+            tmem_copy_scales_if<1>(q, tmem_base + kSfaCol + 4 * j, sdesc + 32u * j);
+            tmem_copy_scales_if<1>(q, tmem_base + kSfbCol + 8 * j, sdesc + 128u + 32u * j);
+            tmem_copy_scales_if<1>(q, tmem_base + kSfbCol + 8 * j + 4, sdesc + 256u + 32u * j);
+          }
+          for (int j = 0; j < blocks; ++j)
+            mma_nvf4_if<1>(q, tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
+                           tmem_base + kSfbCol + 8 * j, (kt | j) != 0);
+        }
+        mma_commit_if<1>(q, empty_bar(s));
+        if (kt == num_k_tiles - 1) mma_commit_if<1>(q, acc_full);
+        if (++s == STAGES) {
+          s = 0;
+          phase ^= 1;
+        }
+      }
+    }
+  } else {
+    // ------------------------------------------------------------------ epilogue: 8 warps, a 32-lane x 128-column block each
+    const int quarter = warp & 3;                        // accumulator lanes this warp may read
+    const int half = (warp - 2) >> 2;                    // 128-column half it drains
+    const float alpha = args.a_global[0] * args.b_global[0];
+    uint32_t acc_phase = 0;
+    for (int pid = blockIdx.x; pid < num_tiles; pid += gridDim.x) {
+      int tile_m, tile_n;
+      tile_coords(pid, tile_m, tile_n);
+      if (!mbar_wait(acc_full, acc_phase, abort_flag, 3)) break;
+      acc_phase ^= 1;
+      tcgen05_fence_after();
+      // pull the whole block into registers first, so that the next tile's MMAs can start while this one is stored
+      uint32_t acc[4][32];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        tmem_load32_async(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 128 + i * 32, acc[i]);
+      tmem_load_wait();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(acc_empty);
+      const int64_t row = static_cast<int64_t>(tile_m) * kBM + quarter * 32 + lane;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int64_t col = static_cast<int64_t>(tile_n) * BN + half * 128 + i * 32;
+        if (row < args.M && col < args.N) {
+          const int64_t left = args.N - col;
+          const int valid = left < 32 ? static_cast<int>(left) : 32;
+          if (args.out_dtype == BL_BF16)
+            store_row32(static_cast<__nv_bfloat16*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
+          else if (args.out_dtype == BL_F16)
+            store_row32(static_cast<__half*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
+          else
+            store_row32(static_cast<float*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
+        }
+      }
+    }
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 1) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, kTmemCols);
+  }
+}
+
+// ------------------------------------------------------------------------------------------------ CTA-pair kernel
+// Two CTAs on neighbouring SMs (a cluster of 2) share one 256 x 256 output tile: CTA r holds rows [128 r, 128 r + 128)
+// of the A tile and of the accumulator, and half of the B tile (rows [128 r, 128 r + 128) of B); one
+// tcgen05.mma.cta_group::2 issued by CTA 0 multiplies the 256-row A by the 256-row B using both SMs' tensor cores and
+// both shared memories. Per flop this halves the operand bytes each SM pulls from L2, the number of MMA instructions
+// and the number of scale copies (tcgen05.cp.cta_group::2 copies in both CTAs at once).
+//
+// Synchronisation (all mbarriers; every wait bounded):
+//   full[s]       each CTA, its own loads of stage s (TMA + bulk copies, local)
+//   peer_full[s]  in CTA 0: CTA 1's relay thread arrives here (remote arrive) once CTA 1's full[s] completed
+//   empty[s]      each CTA: tcgen05.commit from CTA 0 after the MMAs that read stage s (one commit per CTA)
+//   acc_full      each CTA: tcgen05.commit from CTA 0 after the last MMA of a tile
+//   acc_empty     in CTA 0: 16 arrivals, one per epilogue warp of both CTAs, when the accumulator has been read
+// No load with cluster multicast is used; the only cross-CTA traffic is mbarrier arrivals.
+constexpr int kPairThreads = 320;
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+  uint32_t r;
+  asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) {   // shared::cluster address
+  uint32_t r;
+  asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(saddr), "r"(rank));
+  return r;
+}
+
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ void cluster_sync_all() {
+  asm volatile("barrier.cluster.arrive.release.aligned;" ::: "memory");
+  asm volatile("barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t smem_result, uint32_t ncols) {
+  asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_result), "r"(ncols) : "memory");
+  asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+  asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+__device__ __forceinline__ void tmem_copy_scales_pair(uint32_t taddr, uint64_t sdesc) {
+  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+__device__ __forceinline__ void mma_nvf4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                              uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+
+// arrives on the mbarrier at a shared::cluster address once all tcgen05 operations of this thread have completed
+__device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
+  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+__device__ __forceinline__ void tmem_copy_scales_pair_elect(uint32_t taddr, uint64_t sdesc) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "@p tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;\n\t}" ::"r"(taddr), "l"(sdesc) : "memory");
+}
+
+__device__ __forceinline__ void mma_nvf4_pair_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
+                                                    uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+  asm volatile(
+      "{\n\t.reg .pred p, q;\n\t"
+      "setp.ne.b32 p, %6, 0;\n\t"
+      "elect.sync _|q, 0xffffffff;\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
+      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      : "memory");
+}
+
+__device__ __forceinline__ void mma_commit_pair_elect(uint32_t cluster_addr) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "@p tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(cluster_addr)
+      : "memory");
+}
+
+// one commit that arrives on the mbarrier at the same offset in every CTA of the mask (no data moves: this is the
+// completion signal of the MMAs, not a load)
+__device__ __forceinline__ void mma_commit_pair_both_elect(uint32_t bar, uint16_t mask) {
+  asm volatile(
+      "{\n\t.reg .pred p;\n\t"
+      "elect.sync _|p, 0xffffffff;\n\t"
+      "@p tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}"
+      ::"r"(bar), "h"(mask)
+      : "memory");
+}
+
+template <int STAGES>
+struct PairSmem {
+  static constexpr uint32_t kA = 128 * (kBK / 2);       // this CTA's 128 rows of A
+  static constexpr uint32_t kB = 128 * (kBK / 2);       // this CTA's 128 rows of B
+  static constexpr uint32_t kSFA = 4 * 512;             // scales of its A rows
+  static constexpr uint32_t kSFB = 2 * 4 * 512;         // scales of all 256 B rows
+  static constexpr uint32_t kStage = kA + kB + kSFA + kSFB;
+  static constexpr uint32_t kTotal = STAGES * kStage + 1024 + 1024;
+};
+
+template <int STAGES>
+__global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
+                                                                    const __grid_constant__ CUtensorMap map_b,
+                                                                    GemmArgs args) {
+  using S = PairSmem<STAGES>;
+  extern __shared__ uint8_t smem_raw[];
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw_addr);
+  const uint32_t bars = base + STAGES * S::kStage;
+  uint8_t* bars_ptr = base_ptr + STAGES * S::kStage;
+  auto full_bar = [&](int s) { return bars + 8u * s; };
+  auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
+  auto peer_full_bar = [&](int s) { return bars + 8u * (2 * STAGES + s); };
+  const uint32_t acc_full = bars + 8u * (3 * STAGES);
+  const uint32_t acc_empty = bars + 8u * (3 * STAGES + 1);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 8 * (3 * STAGES + 2));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 8 * (3 * STAGES + 2) + 8);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int wmode = (args.debug >> 6) & 3;
+  const bool prof = (args.debug & 8) && blockIdx.x < 2;
+  long long waited[3] = {0, 0, 0};
+  const long long t_begin = clock64();
+  auto timed_wait = [&](int slot, uint32_t bar, uint32_t parity, int code) {
+    const long long t0 = prof ? clock64() : 0;
+    const bool r = mbar_wait(bar, parity, abort_flag, code, wmode);
+    if (prof) waited[slot] += clock64() - t0;
+    return r;
+  };
+  const uint32_t rank = cluster_ctarank();                 // 0: leader (issues the MMAs), 1: peer
+  const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
+  const int num_tiles = args.num_m * args.num_n;           // 256 x 256 tiles
+  const int num_k_tiles = static_cast<int>((args.K + kBK - 1) / kBK);
+  const int nkb = static_cast<int>((args.K + 63) / 64);
+  const int nrb_a = static_cast<int>((args.M + 127) / 128), nrb_b = static_cast<int>((args.N + 127) / 128);
+  constexpr uint32_t kTmemCols = 512, kSfaCol = 256, kSfbCol = 272;
+
+  constexpr int kGroup = 8;
+  auto tile_coords = [&](int pid, int& tile_m, int& tile_n) {
+    const int per_group = kGroup * args.num_n;
+    const int group = pid / per_group;
+    const int first_m = group * kGroup;
+    const int group_m = min(args.num_m - first_m, kGroup);
+    tile_m = first_m + (pid % per_group) % group_m;
+    tile_n = (pid % per_group) / group_m;
+  };
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) {
+      mbar_init(full_bar(s), 1);
+      mbar_init(empty_bar(s), 1);
+      mbar_init(peer_full_bar(s), 1);
+    }
+    mbar_init(acc_full, 1);
+    mbar_init(acc_empty, 16);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
+  tcgen05_fence_before();
+  __syncthreads();
+  cluster_sync_all();                                      // both CTAs' barriers exist before any remote arrival
+  tcgen05_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    // ---------------------------------------------------------------- producer (both CTAs, each for its own halves)
+    // the whole warp runs the loop; one elected lane issues each copy
     if (lane == 0) {
-      constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (8u << 24);
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+    }
+    __syncwarp();
+    uint32_t it = 0;
+    bool ok = true;
+    for (int pid = pair; pid < num_tiles && ok; pid += num_pairs) {
+      int tile_m, tile_n;
+      tile_coords(pid, tile_m, tile_n);
+      const int rb_a = tile_m * 2 + static_cast<int>(rank);             // 128-row block of A this CTA owns
+      const bool a_exists = rb_a < nrb_a;
+      const int b_blocks = min(2, nrb_b - tile_n * 2);
+      const uint8_t* sfa = args.a_sf + static_cast<int64_t>(rb_a) * nkb * 512;
+      const uint8_t* sfb = args.b_sf + static_cast<int64_t>(tile_n) * 2 * nkb * 512;
+      for (int kt = 0; kt < num_k_tiles; ++kt, ++it) {
+        const int s = it % STAGES;
+        const uint32_t round = it / STAGES;
+        if (round > 0) {
+          ok = __all_sync(0xffffffffu, timed_wait(0, empty_bar(s), (round - 1) & 1, 1));
+          if (!ok) break;
+        }
+        const uint32_t stage = base + s * S::kStage;
+        const int blobs = min(4, nkb - kt * 4);
+        const uint32_t sf_bytes = blobs * 512u;
+        mbar_expect_tx_elect(full_bar(s), S::kA + S::kB + sf_bytes * ((a_exists ? 1 : 0) + b_blocks));
+        tma_load_2d_elect(stage, &map_a, kt * (kBK / 2), rb_a * 128, full_bar(s));
+        tma_load_2d_elect(stage + S::kA, &map_b, kt * (kBK / 2), tile_n * 256 + static_cast<int>(rank) * 128, full_bar(s));
+        if (a_exists) bulk_load_elect(stage + S::kA + S::kB, sfa + kt * 2048, sf_bytes, full_bar(s));
+        for (int h = 0; h < b_blocks; ++h)
+          bulk_load_elect(stage + S::kA + S::kB + S::kSFA + h * 2048, sfb + (static_cast<int64_t>(h) * nkb + kt * 4) * 512,
+                          sf_bytes, full_bar(s));
+      }
+    }
+  } else if (warp == 1) {
+    if (rank == 1) {
+      // ---------------------------------------------------------------- peer: relay "my stage is loaded" to the leader
+      uint32_t it = 0;
+      bool ok = true;
+      for (int pid = pair; pid < num_tiles && ok; pid += num_pairs) {
+        for (int kt = 0; kt < num_k_tiles; ++kt, ++it) {
+          const int s = it % STAGES;
+          ok = __all_sync(0xffffffffu, timed_wait(0, full_bar(s), (it / STAGES) & 1, 5));
+          if (!ok) break;
+          if (lane == 0) mbar_arrive_cluster(map_to_cta(peer_full_bar(s), 0));
+          __syncwarp();
+        }
+      }
+    } else {
+      // ---------------------------------------------------------------- leader: scale copies + MMAs for the pair
+      // E2M1 x E2M1, UE4M3 scales, K-major, N = 256, M = 256 (two CTAs), dense K = 64
+      constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (32u << 17) | (16u << 24);
+      const uint32_t empty_peer0 = map_to_cta(empty_bar(0), 1);           // the peer's barriers, 8 bytes apart
+      const uint32_t acc_full_peer = map_to_cta(acc_full, 1);
       uint32_t it = 0, local_tile = 0;
       bool ok = true;
-      long long t_full = 0, t_acc = 0, t0 = clock64();
-      for (int pid = blockIdx.x; pid < num_tiles && ok; pid += gridDim.x, ++local_tile) {
+      for (int pid = pair; pid < num_tiles && ok; pid += num_pairs, ++local_tile) {
         if (local_tile > 0) {
-          const long long w0 = clock64();
-          ok = mbar_wait(acc_empty, (local_tile - 1) & 1, abort_flag, 4);
-          t_acc += clock64() - w0;
+          ok = __all_sync(0xffffffffu, timed_wait(2, acc_empty, (local_tile - 1) & 1, 4));
           if (!ok) break;
           tcgen05_fence_after();
         }
         for (int kt = 0; kt < num_k_tiles; ++kt, ++it) {
           const int s = it % STAGES;
-          const long long w0 = clock64();
-          ok = mbar_wait(full_bar(s), (it / STAGES) & 1, abort_flag, 2);
-          t_full += clock64() - w0;
+          const uint32_t parity = (it / STAGES) & 1;
+          ok = __all_sync(0xffffffffu, timed_wait(0, full_bar(s), parity, 2) &&
+                                           timed_wait(1, peer_full_bar(s), parity, 6));
           if (!ok) break;
           tcgen05_fence_after();
           const uint32_t stage = base + s * S::kStage;
           const int blocks = min(4, nkb - kt * 4);
           for (int j = 0; j < blocks && !(args.debug & 4); ++j) {
-            tmem_copy_scales(tmem_base + kSfaCol + 4 * j, scale_desc(stage + S::kA + S::kB + j * 512));
-            tmem_copy_scales(tmem_base + kSfbCol + 8 * j, scale_desc(stage + S::kA + S::kB + S::kSFA + j * 512));
-            tmem_copy_scales(tmem_base + kSfbCol + 8 * j + 4,
-                             scale_desc(stage + S::kA + S::kB + S::kSFA + 2048 + j * 512));
+            tmem_copy_scales_pair_elect(tmem_base + kSfaCol + 4 * j, scale_desc(stage + S::kA + S::kB + j * 512));
+            tmem_copy_scales_pair_elect(tmem_base + kSfbCol + 8 * j,
+                                        scale_desc(stage + S::kA + S::kB + S::kSFA + j * 512));
+            tmem_copy_scales_pair_elect(tmem_base + kSfbCol + 8 * j + 4,
+                                        scale_desc(stage + S::kA + S::kB + S::kSFA + 2048 + j * 512));
           }
           const uint64_t adesc = operand_desc(stage), bdesc = operand_desc(stage + S::kA);
           for (int j = 0; j < blocks && !(args.debug & 2); ++j)
-            mma_nvf4(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
-                     tmem_base + kSfbCol + 8 * j, (kt | j) != 0);
-          mma_commit(empty_bar(s));
+            mma_nvf4_pair_elect(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
+                                tmem_base + kSfbCol + 8 * j, (kt | j) != 0);
+          if (args.debug & 32) {
+            mma_commit_pair_both_elect(empty_bar(s), 3);
+          } else {
+            mma_commit_pair_elect(empty_bar(s));
+            mma_commit_pair_elect(empty_peer0 + 8u * s);
+          }
         }
-        if (ok) mma_commit(acc_full);
-      }
-      if (args.debug & 8) {
-        atomicAdd(&g_gemm_prof[2], static_cast<unsigned long long>(t_full));
-        atomicAdd(&g_gemm_prof[3], static_cast<unsigned long long>(t_acc));
-        atomicAdd(&g_gemm_prof[4], static_cast<unsigned long long>(clock64() - t0));
+        if (ok) {
+          if (args.debug & 32) {
+            mma_commit_pair_both_elect(acc_full, 3);
+          } else {
+            mma_commit_pair_elect(acc_full);
+            mma_commit_pair_elect(acc_full_peer);
+          }
+        }
       }
     }
   } else {
-    const int quarter = warp & 3;                        // accumulator lanes this warp may read
-    const int half = (warp - 2) >> 2;                    // 128-column half it drains
+    // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
+    const int quarter = warp & 3, half = (warp - 2) >> 2;
     const float alpha = args.a_global[0] * args.b_global[0];
+    const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
     uint32_t local_tile = 0;
-    for (int pid = blockIdx.x; pid < num_tiles; pid += gridDim.x, ++local_tile) {
+    for (int pid = pair; pid < num_tiles; pid += num_pairs, ++local_tile) {
       int tile_m, tile_n;
       tile_coords(pid, tile_m, tile_n);
-      if (!mbar_wait(acc_full, local_tile & 1, abort_flag, 3)) break;
+      if (!timed_wait(0, acc_full, local_tile & 1, 3)) break;
       tcgen05_fence_after();
-      const int64_t row = static_cast<int64_t>(tile_m) * kBM + quarter * 32 + lane;
+      const int64_t row = static_cast<int64_t>(tile_m) * 256 + rank * 128 + quarter * 32 + lane;
 #pragma unroll 1
       for (int c = half * 128; c < half * 128 + 128; c += 32) {
         uint32_t acc[32];
         tmem_load32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c, acc);
-        if (c == half * 128 + 96) {                      // last read of this warp: hand the accumulator back
+        if (c == half * 128 + 96) {
           tcgen05_fence_before();
           __syncwarp();
-          if (lane == 0) mbar_arrive(acc_empty);
+          if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
         }
-        const int64_t col = static_cast<int64_t>(tile_n) * BN + c;
+        const int64_t col = static_cast<int64_t>(tile_n) * 256 + c;
         if (row < args.M && col < args.N) {
           const int64_t left = args.N - col;
           const int valid = left < 32 ? static_cast<int>(left) : 32;
@@ -510,11 +1048,24 @@ __global__ void __launch_bounds__(kPersistThreads, 1) gemm_persistent_kernel(con
       }
     }
   }
+  if (prof && lane == 0 && warp <= 2) {
+    // slots: producer r0 (0), producer r1 (1), leader full/peer_full/acc_empty (2, 3, 4), relay (5), epilogue r0 (6)
+    if (warp == 0) g_gemm_prof[rank] = waited[0];
+    if (warp == 1 && rank == 0) {
+      g_gemm_prof[2] = waited[0];
+      g_gemm_prof[3] = waited[1];
+      g_gemm_prof[4] = waited[2];
+      g_gemm_prof[7] = clock64() - t_begin;
+    }
+    if (warp == 1 && rank == 1) g_gemm_prof[5] = waited[0];
+    if (warp == 2 && rank == 0) g_gemm_prof[6] = waited[0];
+  }
   tcgen05_fence_before();
   __syncthreads();
+  cluster_sync_all();                                      // no CTA frees tensor memory the pair's MMAs may still use
   if (warp == 1) {
     tcgen05_fence_after();
-    tmem_dealloc(tmem_base, kTmemCols);
+    tmem_dealloc_pair(tmem_base, kTmemCols);
   }
 }
 
@@ -569,7 +1120,7 @@ static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, GemmArgs 
   return 0;
 }
 
-template <int STAGES>
+template <int STAGES, int ORDER>
 static int launch_persistent(const uint8_t* a_codes, const uint8_t* b_codes, GemmArgs args, int device, cudaStream_t st) {
   using S = GemmSmem<256, STAGES>;
   CUtensorMap map_a, map_b;
@@ -579,11 +1130,57 @@ static int launch_persistent(const uint8_t* a_codes, const uint8_t* b_codes, Gem
   args.num_n = static_cast<int>((args.N + 255) / 256);
   const int64_t tiles = static_cast<int64_t>(args.num_m) * args.num_n;
   BL_REQUIRE(tiles <= 0x7FFFFFFF, "gemm: too many output tiles (%lld)", (long long)tiles);
-  BL_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+  BL_CUDA(cudaFuncSetAttribute(gemm_persistent_kernel<STAGES, ORDER>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
   const int sms = sm_count(device);
   const unsigned grid = static_cast<unsigned>(tiles < sms ? tiles : sms);
-  gemm_persistent_kernel<STAGES><<<grid, kPersistThreads, S::kTotal, st>>>(map_a, map_b, args);
+  gemm_persistent_kernel<STAGES, ORDER><<<grid, kPersistThreads, S::kTotal, st>>>(map_a, map_b, args);
   BL_CUDA(cudaGetLastError());
+  return 0;
+}
+
+template <int STAGES>
+static int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmArgs args, int device, cudaStream_t st) {
+  using S = PairSmem<STAGES>;
+  CUtensorMap map_a, map_b;
+  if (int rc = make_operand_map(&map_a, a_codes, args.M, args.K, 128)) return rc;
+  if (int rc = make_operand_map(&map_b, b_codes, args.N, args.K, 128)) return rc;
+  args.num_m = static_cast<int>((args.M + 255) / 256);
+  args.num_n = static_cast<int>((args.N + 255) / 256);
+  const int64_t tiles = static_cast<int64_t>(args.num_m) * args.num_n;
+  BL_REQUIRE(tiles <= 0x3FFFFFFF, "gemm: too many output tiles (%lld)", (long long)tiles);
+  BL_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3(sm_count(device) & ~1);
+  cfg.blockDim = dim3(kPairThreads);
+  cfg.dynamicSmemBytes = S::kTotal;
+  cfg.stream = st;
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeClusterDimension;
+  attr[0].val.clusterDim.x = 2;
+  attr[0].val.clusterDim.y = 1;
+  attr[0].val.clusterDim.z = 1;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  // The tile list is strided over the pairs, so every pair must be resident at once: ask how many clusters of two
+  // the device can hold (fewer than SMs / 2 where a GPC has an odd number of usable SMs).
+  static std::mutex mu;
+  static int resident[64] = {};
+  int max_pairs;
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    BL_REQUIRE(device >= 0 && device < 64, "gemm: device index %d out of range", device);
+    if (resident[device] == 0) {
+      int n = 0;
+      BL_CUDA(cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<STAGES>, &cfg));
+      BL_REQUIRE(n > 0, "gemm: the device cannot hold a cluster of two CTAs of the pair kernel");
+      resident[device] = n;
+      if (getenv("BL_GEMM_VERBOSE")) fprintf(stderr, "bitlattice_b200: %d resident CTA pairs on device %d\n", n, device);
+    }
+    max_pairs = resident[device];
+  }
+  const unsigned pairs = static_cast<unsigned>(tiles < max_pairs ? tiles : max_pairs);
+  cfg.gridDim = dim3(pairs * 2);
+  BL_CUDA(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<STAGES>, map_a, map_b, args));
   return 0;
 }
 
@@ -625,7 +1222,16 @@ extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const 
     return e ? atoi(e) : 128;
   }();
   if (bn == 256) return launch_gemm<256, 4>(a_codes, b_codes, args, reinterpret_cast<cudaStream_t>(stream));
-  if (bn == 1) return launch_persistent<4>(a_codes, b_codes, args, device, reinterpret_cast<cudaStream_t>(stream));
+  static const int order = [] {
+    const char* e = getenv("BL_GEMM_ORDER");
+    return e ? atoi(e) : 1;
+  }();
+  if (bn == 1 && order == 0)
+    return launch_persistent<4, 0>(a_codes, b_codes, args, device, reinterpret_cast<cudaStream_t>(stream));
+  if (bn == 1 && order == 2)
+    return launch_persistent<4, 2>(a_codes, b_codes, args, device, reinterpret_cast<cudaStream_t>(stream));
+  if (bn == 1) return launch_persistent<4, 1>(a_codes, b_codes, args, device, reinterpret_cast<cudaStream_t>(stream));
+  if (bn == 2) return launch_pair<5>(a_codes, b_codes, args, device, reinterpret_cast<cudaStream_t>(stream));
   return launch_gemm<128, 3>(a_codes, b_codes, args, reinterpret_cast<cudaStream_t>(stream));
 }
 
