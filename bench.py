@@ -293,7 +293,7 @@ def run_ours(a):
         "gpu_launches": launches,
         "gemm_error_flag": status,
         "clocks": clock_info,
-        "roofline": {"bound": "tensor", "kernel": "gemm_kernel (tcgen05 mxf4nvf4)", "achieved": gemm_tf,
+        "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel (tcgen05 mxf4nvf4, cta_group::2, 256x256 tiles)", "achieved": gemm_tf,
                      "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tf / fp4_peak if gemm_tf else None,
                      "traffic": None, "launches": gemm_calls,
                      "peak_note": f"4 x bf16 sustained cuBLAS ({peaks['source']}); nominal dense FP4 9000",

@@ -50,6 +50,7 @@ _SIGNATURES = {
     "bl_nvfp4_gemm": (_c.c_int, [_P, _P, _P, _P, _P, _P, _c.c_int64, _c.c_int64, _c.c_int64, _P, _c.c_int,
                                  _c.c_int64, _c.c_int, _P]),
     "bl_nvfp4_gemm_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.c_int]),
+    "bl_nvfp4_gemm_select": (_c.c_int, [_c.c_int]),
     "bl_selftest_division": (_c.c_int, [_c.c_uint64, _c.c_uint32, _c.POINTER(_c.c_uint64), _c.c_int]),
 }
 

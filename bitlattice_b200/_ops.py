@@ -302,6 +302,16 @@ def nvfp4_gemm(a_packed, a_sf, a_global, b_packed, b_sf, b_global, out_dtype=tor
     return out
 
 
+GEMM_KERNELS = {"auto": 0, "tile": 1, "persistent": 2, "pair": 3}
+
+
+def gemm_select(kernel: str = "auto") -> None:
+    """Force one of the GEMM kernels for every later nvfp4_gemm call of this process ("tile": 128 x 128 tiles,
+    "persistent": 128 x 256 tiles with one CTA per SM, "pair": 256 x 256 tiles on pairs of SMs), or hand the choice
+    back to the library ("auto"). All kernels give identical results; this exists for tests and experiments."""
+    _C.call("bl_nvfp4_gemm_select", GEMM_KERNELS[kernel])
+
+
 def gemm_status(device: int = 0) -> int:
     """Device-side error code of the GEMM kernels since the last call (0: none); synchronizes the device."""
     st = ctypes.c_int(0)

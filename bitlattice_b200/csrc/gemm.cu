@@ -20,6 +20,7 @@
 #include <cuda.h>
 
 #include <cstdlib>
+#include <atomic>
 #include <mutex>
 
 #include "common.cuh"
@@ -32,7 +33,6 @@ constexpr int kGemmThreads = 192;
 constexpr uint32_t kSpinLimit = 1u << 21;   // polls of one mbarrier wait before the kernel gives up
 
 __device__ int g_gemm_error = 0;  // 0 ok; otherwise the code of the wait that expired
-__device__ unsigned long long g_gemm_prof[8];   // cycle counters of the persistent kernel (debug bit 8)
 
 // ------------------------------------------------------------------------------------------------ PTX wrappers
 
@@ -178,60 +178,6 @@ __device__ __forceinline__ void tmem_load32_async(uint32_t taddr, uint32_t* r) {
 
 __device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
-// Variants for a fully converged warp: every lane runs the same control flow with warp-uniform operands and one
-// elected lane issues the instruction.
-__device__ __forceinline__ void mbar_expect_tx_elect(uint32_t bar, uint32_t bytes) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "@p mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;\n\t}" ::"r"(bar), "r"(bytes) : "memory");
-}
-
-__device__ __forceinline__ void tma_load_2d_elect(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "@p cp.async.bulk.tensor.2d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3}], [%4];\n\t}"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
-      : "memory");
-}
-
-__device__ __forceinline__ void bulk_load_elect(uint32_t dst, const void* src, uint32_t bytes, uint32_t bar) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "@p cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];\n\t}"
-      ::"r"(dst), "l"(reinterpret_cast<uint64_t>(src)), "r"(bytes), "r"(bar)
-      : "memory");
-}
-
-__device__ __forceinline__ void tmem_copy_scales_elect(uint32_t taddr, uint64_t sdesc) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "@p tcgen05.cp.cta_group::1.32x128b.warpx4 [%0], %1;\n\t}" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-
-__device__ __forceinline__ void mma_nvf4_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                               uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.b32 p, %6, 0;\n\t"
-      "elect.sync _|q, 0xffffffff;\n\t"
-      "@q tcgen05.mma.cta_group::1.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
-      : "memory");
-}
-
-__device__ __forceinline__ void mma_commit_elect(uint32_t bar) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "@p tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(bar) : "memory");
-}
-
-// ------------------------------------------------------------------------------------------------ kernel
-
 // One election for a burst of instructions: q is 1 in the elected lane and 0 elsewhere; the *_if wrappers issue their
 // instruction under that predicate while the warp stays converged.
 __device__ __forceinline__ uint32_t elect_one() {
@@ -376,7 +322,6 @@ struct GemmArgs {
   int64_t M, N, K, ldc;
   int out_dtype;
   int num_m, num_n;
-  int debug;      // experiments only: 1 skip stores, 2 skip MMAs, 4 skip scale copies
 };
 
 template <typename O>
@@ -493,7 +438,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_kernel(const __grid_constan
         tcgen05_fence_after();
         const uint32_t stage = base + s * S::kStage;
         const int blocks = min(4, nkb - kt * 4);
-        for (int j = 0; j < blocks && !(args.debug & 4); ++j) {
+        for (int j = 0; j < blocks; ++j) {
           tmem_copy_scales(tmem_base + kSfaCol + 4 * j, scale_desc(stage + S::kA + S::kB + j * 512));
 #pragma unroll
           for (int h = 0; h < BN / 128; ++h)
@@ -501,7 +446,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_kernel(const __grid_constan
                              scale_desc(stage + S::kA + S::kB + S::kSFA + h * 2048 + j * 512));
         }
         const uint64_t adesc = operand_desc(stage), bdesc = operand_desc(stage + S::kA);
-        for (int j = 0; j < blocks && !(args.debug & 2); ++j)
+        for (int j = 0; j < blocks; ++j)
           mma_nvf4(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
                    tmem_base + kSfbCol + (BN / 32) * j, (kt | j) != 0);
         mma_commit(empty_bar(s));
@@ -521,7 +466,7 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_kernel(const __grid_constan
         uint32_t acc[32];
         tmem_load32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c, acc);
         const int64_t col = n0 + c;
-        if (row < args.M && col < args.N && !(args.debug & 1)) {
+        if (row < args.M && col < args.N) {
           const int64_t left = args.N - col;
           const int valid = left < 32 ? static_cast<int>(left) : 32;
           if (args.out_dtype == BL_BF16)
@@ -736,16 +681,15 @@ __global__ void __launch_bounds__(kPersistThreads, 1) gemm_persistent_kernel(con
 // Two CTAs on neighbouring SMs (a cluster of 2) share one 256 x 256 output tile: CTA r holds rows [128 r, 128 r + 128)
 // of the A tile and of the accumulator, and half of the B tile (rows [128 r, 128 r + 128) of B); one
 // tcgen05.mma.cta_group::2 issued by CTA 0 multiplies the 256-row A by the 256-row B using both SMs' tensor cores and
-// both shared memories. Per flop this halves the operand bytes each SM pulls from L2, the number of MMA instructions
-// and the number of scale copies (tcgen05.cp.cta_group::2 copies in both CTAs at once).
+// both shared memories. Per flop this halves the operand bytes each SM pulls from L2.
 //
 // Synchronisation (all mbarriers; every wait bounded):
-//   full[s]       each CTA, its own loads of stage s (TMA + bulk copies, local)
-//   peer_full[s]  in CTA 0: CTA 1's relay thread arrives here (remote arrive) once CTA 1's full[s] completed
-//   empty[s]      each CTA: tcgen05.commit from CTA 0 after the MMAs that read stage s (one commit per CTA)
-//   acc_full      each CTA: tcgen05.commit from CTA 0 after the last MMA of a tile
-//   acc_empty     in CTA 0: 16 arrivals, one per epilogue warp of both CTAs, when the accumulator has been read
-// No load with cluster multicast is used; the only cross-CTA traffic is mbarrier arrivals.
+//   full[s]    in CTA 0 only: the TMA loads of BOTH CTAs for stage s complete their bytes here (the loads carry
+//              .cta_group::2, which lets a load signal the barrier of the other CTA of the pair)
+//   empty[s]   each CTA: tcgen05.commit from CTA 0 after the MMAs that read stage s (one commit per CTA)
+//   acc_full   each CTA: tcgen05.commit from CTA 0 after the last MMA of a tile
+//   acc_empty  in CTA 0: 16 arrivals, one per epilogue warp of both CTAs, when the accumulator is in registers
+// No load is multicast; the only cross-CTA traffic is barrier signalling.
 constexpr int kPairThreads = 320;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {
@@ -778,59 +722,26 @@ __device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols
   asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
 }
 
-__device__ __forceinline__ void tmem_copy_scales_pair(uint32_t taddr, uint64_t sdesc) {
-  asm volatile("tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-
-__device__ __forceinline__ void mma_nvf4_pair(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                              uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
+// TMA loads whose completion may be signalled on the other CTA of the pair (bar is a shared::cluster address)
+__device__ __forceinline__ void tma_pair_load_2d_if(uint32_t q, uint32_t dst, const CUtensorMap* map, int x, int y,
+                                                    uint32_t bar) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "setp.ne.b32 p, %6, 0;\n\t"
-      "tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
+      "setp.ne.b32 p, %0, 0;\n\t"
+      "@p cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%1], [%2, {%3, %4}], [%5];\n\t}"
+      ::"r"(q), "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(bar)
       : "memory");
 }
 
-// arrives on the mbarrier at a shared::cluster address once all tcgen05 operations of this thread have completed
-__device__ __forceinline__ void mma_commit_pair(uint32_t cluster_addr) {
-  asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(cluster_addr) : "memory");
-}
-
-__device__ __forceinline__ void tmem_copy_scales_pair_elect(uint32_t taddr, uint64_t sdesc) {
+__device__ __forceinline__ void tma_pair_load_3d_if(uint32_t q, uint32_t dst, const CUtensorMap* map, int x, int y, int z,
+                                                    uint32_t bar) {
   asm volatile(
       "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "@p tcgen05.cp.cta_group::2.32x128b.warpx4 [%0], %1;\n\t}" ::"r"(taddr), "l"(sdesc) : "memory");
-}
-
-__device__ __forceinline__ void mma_nvf4_pair_elect(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc,
-                                                    uint32_t sfa, uint32_t sfb, uint32_t accumulate) {
-  asm volatile(
-      "{\n\t.reg .pred p, q;\n\t"
-      "setp.ne.b32 p, %6, 0;\n\t"
-      "elect.sync _|q, 0xffffffff;\n\t"
-      "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%0], %1, %2, %3, [%4], [%5], p;\n\t}"
-      ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(sfa), "r"(sfb), "r"(accumulate)
-      : "memory");
-}
-
-__device__ __forceinline__ void mma_commit_pair_elect(uint32_t cluster_addr) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "@p tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];\n\t}" ::"r"(cluster_addr)
-      : "memory");
-}
-
-// one commit that arrives on the mbarrier at the same offset in every CTA of the mask (no data moves: this is the
-// completion signal of the MMAs, not a load)
-__device__ __forceinline__ void mma_commit_pair_both_elect(uint32_t bar, uint16_t mask) {
-  asm volatile(
-      "{\n\t.reg .pred p;\n\t"
-      "elect.sync _|p, 0xffffffff;\n\t"
-      "@p tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;\n\t}"
-      ::"r"(bar), "h"(mask)
+      "setp.ne.b32 p, %0, 0;\n\t"
+      "@p cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.tile.mbarrier::complete_tx::bytes "
+      "[%1], [%2, {%3, %4, %5}], [%6];\n\t}"
+      ::"r"(q), "r"(dst), "l"(reinterpret_cast<uint64_t>(map)), "r"(x), "r"(y), "r"(z), "r"(bar)
       : "memory");
 }
 
@@ -844,9 +755,11 @@ struct PairSmem {
   static constexpr uint32_t kTotal = STAGES * kStage + 1024 + 1024;
 };
 
-template <int STAGES>
+template <int STAGES, int ORDER>
 __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                     const __grid_constant__ CUtensorMap map_b,
+                                                                    const __grid_constant__ CUtensorMap map_sfa,
+                                                                    const __grid_constant__ CUtensorMap map_sfb,
                                                                     GemmArgs args) {
   using S = PairSmem<STAGES>;
   extern __shared__ uint8_t smem_raw[];
@@ -857,30 +770,19 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
   uint8_t* bars_ptr = base_ptr + STAGES * S::kStage;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  auto peer_full_bar = [&](int s) { return bars + 8u * (2 * STAGES + s); };
-  const uint32_t acc_full = bars + 8u * (3 * STAGES);
-  const uint32_t acc_empty = bars + 8u * (3 * STAGES + 1);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 8 * (3 * STAGES + 2));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 8 * (3 * STAGES + 2) + 8);
+  const uint32_t acc_full = bars + 8u * (2 * STAGES);
+  const uint32_t acc_empty = bars + 8u * (2 * STAGES + 1);
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 8 * (2 * STAGES + 2));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 8 * (2 * STAGES + 2) + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  const int wmode = (args.debug >> 6) & 3;
-  const bool prof = (args.debug & 8) && blockIdx.x < 2;
-  long long waited[3] = {0, 0, 0};
-  const long long t_begin = clock64();
-  auto timed_wait = [&](int slot, uint32_t bar, uint32_t parity, int code) {
-    const long long t0 = prof ? clock64() : 0;
-    const bool r = mbar_wait(bar, parity, abort_flag, code, wmode);
-    if (prof) waited[slot] += clock64() - t0;
-    return r;
-  };
   const uint32_t rank = cluster_ctarank();                 // 0: leader (issues the MMAs), 1: peer
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
   const int num_tiles = args.num_m * args.num_n;           // 256 x 256 tiles
   const int num_k_tiles = static_cast<int>((args.K + kBK - 1) / kBK);
   const int nkb = static_cast<int>((args.K + 63) / 64);
-  const int nrb_a = static_cast<int>((args.M + 127) / 128), nrb_b = static_cast<int>((args.N + 127) / 128);
   constexpr uint32_t kTmemCols = 512, kSfaCol = 256, kSfbCol = 272;
+  constexpr int kCluster = 2;                              // barriers signalled across the pair: cluster-scope acquire
 
   constexpr int kGroup = 8;
   auto tile_coords = [&](int pid, int& tile_m, int& tile_n) {
@@ -896,7 +798,6 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
     for (int s = 0; s < STAGES; ++s) {
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
-      mbar_init(peer_full_bar(s), 1);
     }
     mbar_init(acc_full, 1);
     mbar_init(acc_empty, 16);
@@ -907,158 +808,132 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
   if (warp == 1) tmem_alloc_pair(smem_u32(const_cast<uint32_t*>(tmem_slot)), kTmemCols);
   tcgen05_fence_before();
   __syncthreads();
-  cluster_sync_all();                                      // both CTAs' barriers exist before any remote arrival
+  cluster_sync_all();                                      // both CTAs' barriers exist before any remote signal
   tcgen05_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
   if (warp == 0) {
-    // ---------------------------------------------------------------- producer (both CTAs, each for its own halves)
-    // the whole warp runs the loop; one elected lane issues each copy
+    // ------------------------------------------------------------------ producer (both CTAs, each for its own halves)
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_a)) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_b)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_sfa)) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(reinterpret_cast<uint64_t>(&map_sfb)) : "memory");
     }
     __syncwarp();
-    uint32_t it = 0;
+    const uint32_t full_leader0 = map_to_cta(full_bar(0), 0);
+    int s = 0;
+    uint32_t phase = 1;
     bool ok = true;
     for (int pid = pair; pid < num_tiles && ok; pid += num_pairs) {
       int tile_m, tile_n;
       tile_coords(pid, tile_m, tile_n);
-      const int rb_a = tile_m * 2 + static_cast<int>(rank);             // 128-row block of A this CTA owns
-      const bool a_exists = rb_a < nrb_a;
-      const int b_blocks = min(2, nrb_b - tile_n * 2);
-      const uint8_t* sfa = args.a_sf + static_cast<int64_t>(rb_a) * nkb * 512;
-      const uint8_t* sfb = args.b_sf + static_cast<int64_t>(tile_n) * 2 * nkb * 512;
-      for (int kt = 0; kt < num_k_tiles; ++kt, ++it) {
-        const int s = it % STAGES;
-        const uint32_t round = it / STAGES;
-        if (round > 0) {
-          ok = __all_sync(0xffffffffu, timed_wait(0, empty_bar(s), (round - 1) & 1, 1));
-          if (!ok) break;
-        }
+      const int rb_a = tile_m * 2 + static_cast<int>(rank);               // 128-row block of A this CTA owns
+      const int row_b = tile_n * 256 + static_cast<int>(rank) * 128;      // its half of the B tile
+      for (int kt = 0; kt < num_k_tiles; ++kt) {
+        ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), phase, abort_flag, 1, kCluster));
+        if (!ok) break;
+        const uint32_t q = elect_one();
         const uint32_t stage = base + s * S::kStage;
-        const int blobs = min(4, nkb - kt * 4);
-        const uint32_t sf_bytes = blobs * 512u;
-        mbar_expect_tx_elect(full_bar(s), S::kA + S::kB + sf_bytes * ((a_exists ? 1 : 0) + b_blocks));
-        tma_load_2d_elect(stage, &map_a, kt * (kBK / 2), rb_a * 128, full_bar(s));
-        tma_load_2d_elect(stage + S::kA, &map_b, kt * (kBK / 2), tile_n * 256 + static_cast<int>(rank) * 128, full_bar(s));
-        if (a_exists) bulk_load_elect(stage + S::kA + S::kB, sfa + kt * 2048, sf_bytes, full_bar(s));
-        for (int h = 0; h < b_blocks; ++h)
-          bulk_load_elect(stage + S::kA + S::kB + S::kSFA + h * 2048, sfb + (static_cast<int64_t>(h) * nkb + kt * 4) * 512,
-                          sf_bytes, full_bar(s));
+        const uint32_t bar = full_leader0 + 8u * s;
+        // every load is a full box (bytes outside the tensors arrive as zeros), so the byte count is fixed
+        if (rank == 0) mbar_expect_tx_if(q, full_bar(s), 2 * S::kStage);
+        tma_pair_load_2d_if(q, stage, &map_a, kt * (kBK / 2), rb_a * 128, bar);
+        tma_pair_load_2d_if(q, stage + S::kA, &map_b, kt * (kBK / 2), row_b, bar);
+        tma_pair_load_3d_if(q, stage + S::kA + S::kB, &map_sfa, 0, kt * 4, rb_a, bar);
+        tma_pair_load_3d_if(q, stage + S::kA + S::kB + S::kSFA, &map_sfb, 0, kt * 4, tile_n * 2, bar);
+        if (++s == STAGES) {
+          s = 0;
+          phase ^= 1;
+        }
       }
     }
   } else if (warp == 1) {
-    if (rank == 1) {
-      // ---------------------------------------------------------------- peer: relay "my stage is loaded" to the leader
-      uint32_t it = 0;
-      bool ok = true;
-      for (int pid = pair; pid < num_tiles && ok; pid += num_pairs) {
-        for (int kt = 0; kt < num_k_tiles; ++kt, ++it) {
-          const int s = it % STAGES;
-          ok = __all_sync(0xffffffffu, timed_wait(0, full_bar(s), (it / STAGES) & 1, 5));
-          if (!ok) break;
-          if (lane == 0) mbar_arrive_cluster(map_to_cta(peer_full_bar(s), 0));
-          __syncwarp();
-        }
-      }
-    } else {
+    if (rank == 0) {
       // ---------------------------------------------------------------- leader: scale copies + MMAs for the pair
       // E2M1 x E2M1, UE4M3 scales, K-major, N = 256, M = 256 (two CTAs), dense K = 64
       constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (32u << 17) | (16u << 24);
       const uint32_t empty_peer0 = map_to_cta(empty_bar(0), 1);           // the peer's barriers, 8 bytes apart
       const uint32_t acc_full_peer = map_to_cta(acc_full, 1);
-      uint32_t it = 0, local_tile = 0;
+      int s = 0;
+      uint32_t phase = 0, acc_phase = 1;
       bool ok = true;
-      for (int pid = pair; pid < num_tiles && ok; pid += num_pairs, ++local_tile) {
-        if (local_tile > 0) {
-          ok = __all_sync(0xffffffffu, timed_wait(2, acc_empty, (local_tile - 1) & 1, 4));
+      for (int pid = pair; pid < num_tiles && ok; pid += num_pairs) {
+        ok = __all_sync(0xffffffffu, mbar_wait(acc_empty, acc_phase, abort_flag, 4, kCluster));
+        if (!ok) break;
+        acc_phase ^= 1;
+        tcgen05_fence_after();
+        for (int kt = 0; kt < num_k_tiles; ++kt) {
+          ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), phase, abort_flag, 2, kCluster));
           if (!ok) break;
           tcgen05_fence_after();
-        }
-        for (int kt = 0; kt < num_k_tiles; ++kt, ++it) {
-          const int s = it % STAGES;
-          const uint32_t parity = (it / STAGES) & 1;
-          ok = __all_sync(0xffffffffu, timed_wait(0, full_bar(s), parity, 2) &&
-                                           timed_wait(1, peer_full_bar(s), parity, 6));
-          if (!ok) break;
-          tcgen05_fence_after();
+          const uint32_t q = elect_one();
           const uint32_t stage = base + s * S::kStage;
           const int blocks = min(4, nkb - kt * 4);
-          for (int j = 0; j < blocks && !(args.debug & 4); ++j) {
-            tmem_copy_scales_pair_elect(tmem_base + kSfaCol + 4 * j, scale_desc(stage + S::kA + S::kB + j * 512));
-            tmem_copy_scales_pair_elect(tmem_base + kSfbCol + 8 * j,
-                                        scale_desc(stage + S::kA + S::kB + S::kSFA + j * 512));
-            tmem_copy_scales_pair_elect(tmem_base + kSfbCol + 8 * j + 4,
-                                        scale_desc(stage + S::kA + S::kB + S::kSFA + 2048 + j * 512));
-          }
           const uint64_t adesc = operand_desc(stage), bdesc = operand_desc(stage + S::kA);
-          for (int j = 0; j < blocks && !(args.debug & 2); ++j)
-            mma_nvf4_pair_elect(tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
-                                tmem_base + kSfbCol + 8 * j, (kt | j) != 0);
-          if (args.debug & 32) {
-            mma_commit_pair_both_elect(empty_bar(s), 3);
+          const uint64_t sdesc = scale_desc(stage + S::kA + S::kB);
+          if (blocks == 4) {
+            issue_k_tile<2, ORDER>(q, tmem_base, tmem_base + kSfaCol, tmem_base + kSfbCol, sdesc, adesc, bdesc, idesc,
+                                   kt != 0);
           } else {
-            mma_commit_pair_elect(empty_bar(s));
-            mma_commit_pair_elect(empty_peer0 + 8u * s);
+            for (int j = 0; j < blocks; ++j) {
+              tmem_copy_scales_if<2>(q, tmem_base + kSfaCol + 4 * j, sdesc + 32u * j);
+              tmem_copy_scales_if<2>(q, tmem_base + kSfbCol + 8 * j, sdesc + 128u + 32u * j);
+              tmem_copy_scales_if<2>(q, tmem_base + kSfbCol + 8 * j + 4, sdesc + 256u + 32u * j);
+            }
+            for (int j = 0; j < blocks; ++j)
+              mma_nvf4_if<2>(q, tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
+                             tmem_base + kSfbCol + 8 * j, (kt | j) != 0);
           }
-        }
-        if (ok) {
-          if (args.debug & 32) {
-            mma_commit_pair_both_elect(acc_full, 3);
-          } else {
-            mma_commit_pair_elect(acc_full);
-            mma_commit_pair_elect(acc_full_peer);
+          mma_commit_if<2>(q, empty_bar(s));
+          mma_commit_if<2>(q, empty_peer0 + 8u * s);
+          if (kt == num_k_tiles - 1) {
+            mma_commit_if<2>(q, acc_full);
+            mma_commit_if<2>(q, acc_full_peer);
+          }
+          if (++s == STAGES) {
+            s = 0;
+            phase ^= 1;
           }
         }
       }
     }
   } else {
-    // ---------------------------------------------------------------- epilogue (both CTAs, own 128 rows)
+    // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
     const int quarter = warp & 3, half = (warp - 2) >> 2;
     const float alpha = args.a_global[0] * args.b_global[0];
     const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
-    uint32_t local_tile = 0;
-    for (int pid = pair; pid < num_tiles; pid += num_pairs, ++local_tile) {
+    uint32_t acc_phase = 0;
+    for (int pid = pair; pid < num_tiles; pid += num_pairs) {
       int tile_m, tile_n;
       tile_coords(pid, tile_m, tile_n);
-      if (!timed_wait(0, acc_full, local_tile & 1, 3)) break;
+      if (!mbar_wait(acc_full, acc_phase, abort_flag, 3, kCluster)) break;
+      acc_phase ^= 1;
       tcgen05_fence_after();
+      uint32_t acc[4][32];
+#pragma unroll
+      for (int i = 0; i < 4; ++i)
+        tmem_load32_async(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 128 + i * 32, acc[i]);
+      tmem_load_wait();
+      tcgen05_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
       const int64_t row = static_cast<int64_t>(tile_m) * 256 + rank * 128 + quarter * 32 + lane;
-#pragma unroll 1
-      for (int c = half * 128; c < half * 128 + 128; c += 32) {
-        uint32_t acc[32];
-        tmem_load32(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + c, acc);
-        if (c == half * 128 + 96) {
-          tcgen05_fence_before();
-          __syncwarp();
-          if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
-        }
-        const int64_t col = static_cast<int64_t>(tile_n) * 256 + c;
+#pragma unroll
+      for (int i = 0; i < 4; ++i) {
+        const int64_t col = static_cast<int64_t>(tile_n) * 256 + half * 128 + i * 32;
         if (row < args.M && col < args.N) {
           const int64_t left = args.N - col;
           const int valid = left < 32 ? static_cast<int>(left) : 32;
           if (args.out_dtype == BL_BF16)
-            store_row32(static_cast<__nv_bfloat16*>(args.out) + row * args.ldc + col, acc, alpha, valid);
+            store_row32(static_cast<__nv_bfloat16*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
           else if (args.out_dtype == BL_F16)
-            store_row32(static_cast<__half*>(args.out) + row * args.ldc + col, acc, alpha, valid);
+            store_row32(static_cast<__half*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
           else
-            store_row32(static_cast<float*>(args.out) + row * args.ldc + col, acc, alpha, valid);
+            store_row32(static_cast<float*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
         }
       }
     }
-  }
-  if (prof && lane == 0 && warp <= 2) {
-    // slots: producer r0 (0), producer r1 (1), leader full/peer_full/acc_empty (2, 3, 4), relay (5), epilogue r0 (6)
-    if (warp == 0) g_gemm_prof[rank] = waited[0];
-    if (warp == 1 && rank == 0) {
-      g_gemm_prof[2] = waited[0];
-      g_gemm_prof[3] = waited[1];
-      g_gemm_prof[4] = waited[2];
-      g_gemm_prof[7] = clock64() - t_begin;
-    }
-    if (warp == 1 && rank == 1) g_gemm_prof[5] = waited[0];
-    if (warp == 2 && rank == 0) g_gemm_prof[6] = waited[0];
   }
   tcgen05_fence_before();
   __syncthreads();
@@ -1104,6 +979,24 @@ static int make_operand_map(CUtensorMap* map, const uint8_t* codes, int64_t rows
   return 0;
 }
 
+// Blocked scales seen as [row blocks][k blocks][512 bytes]; one box is 4 k blocks of box_row_blocks row blocks, landing
+// in shared memory as consecutive 512-byte blobs. Blocks outside the tensor arrive as zeros.
+static int make_scale_map(CUtensorMap* map, const uint8_t* sf, int64_t rows, int64_t K, int box_row_blocks) {
+  EncodeTiledFn enc = encode_tiled_fn();
+  BL_REQUIRE(enc != nullptr, "gemm: the CUDA driver does not provide cuTensorMapEncodeTiled");
+  const cuuint64_t nkb = static_cast<cuuint64_t>((K + 63) / 64), nrb = static_cast<cuuint64_t>((rows + 127) / 128);
+  const cuuint64_t dims[3] = {128u, nkb, nrb};                        // 32-bit words
+  const cuuint64_t strides[2] = {512u, nkb * 512u};
+  const cuuint32_t box[3] = {128u, 4u, static_cast<cuuint32_t>(box_row_blocks)};
+  const cuuint32_t elem[3] = {1u, 1u, 1u};
+  const CUresult rc = enc(map, CU_TENSOR_MAP_DATA_TYPE_UINT32, 3, const_cast<uint8_t*>(sf), dims, strides, box, elem,
+                          CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_NONE, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                          CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  BL_REQUIRE(rc == CUDA_SUCCESS, "gemm: cuTensorMapEncodeTiled failed with code %d for scales (rows %lld, K %lld)", (int)rc,
+             (long long)rows, (long long)K);
+  return 0;
+}
+
 template <int BN, int STAGES>
 static int launch_gemm(const uint8_t* a_codes, const uint8_t* b_codes, GemmArgs args, cudaStream_t st) {
   using S = GemmSmem<BN, STAGES>;
@@ -1138,17 +1031,20 @@ static int launch_persistent(const uint8_t* a_codes, const uint8_t* b_codes, Gem
   return 0;
 }
 
-template <int STAGES>
+template <int STAGES, int ORDER>
 static int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmArgs args, int device, cudaStream_t st) {
   using S = PairSmem<STAGES>;
   CUtensorMap map_a, map_b;
   if (int rc = make_operand_map(&map_a, a_codes, args.M, args.K, 128)) return rc;
   if (int rc = make_operand_map(&map_b, b_codes, args.N, args.K, 128)) return rc;
+  CUtensorMap map_sfa, map_sfb;
+  if (int rc = make_scale_map(&map_sfa, args.a_sf, args.M, args.K, 1)) return rc;
+  if (int rc = make_scale_map(&map_sfb, args.b_sf, args.N, args.K, 2)) return rc;
   args.num_m = static_cast<int>((args.M + 255) / 256);
   args.num_n = static_cast<int>((args.N + 255) / 256);
   const int64_t tiles = static_cast<int64_t>(args.num_m) * args.num_n;
   BL_REQUIRE(tiles <= 0x3FFFFFFF, "gemm: too many output tiles (%lld)", (long long)tiles);
-  BL_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+  BL_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<STAGES, ORDER>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(sm_count(device) & ~1);
   cfg.blockDim = dim3(kPairThreads);
@@ -1171,7 +1067,7 @@ static int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmArgs 
     BL_REQUIRE(device >= 0 && device < 64, "gemm: device index %d out of range", device);
     if (resident[device] == 0) {
       int n = 0;
-      BL_CUDA(cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<STAGES>, &cfg));
+      BL_CUDA(cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<STAGES, ORDER>, &cfg));
       BL_REQUIRE(n > 0, "gemm: the device cannot hold a cluster of two CTAs of the pair kernel");
       resident[device] = n;
       if (getenv("BL_GEMM_VERBOSE")) fprintf(stderr, "bitlattice_b200: %d resident CTA pairs on device %d\n", n, device);
@@ -1180,13 +1076,19 @@ static int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmArgs 
   }
   const unsigned pairs = static_cast<unsigned>(tiles < max_pairs ? tiles : max_pairs);
   cfg.gridDim = dim3(pairs * 2);
-  BL_CUDA(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<STAGES>, map_a, map_b, args));
+  BL_CUDA(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<STAGES, ORDER>, map_a, map_b, map_sfa, map_sfb, args));
   return 0;
 }
 
 }  // namespace blb
 
 using namespace blb;
+
+static std::atomic<int> g_kernel_choice{[] {
+  const char* e = getenv("BL_GEMM_KERNEL");     // same values as bl_nvfp4_gemm_select
+  const int v = e ? atoi(e) : 0;
+  return v >= BL_GEMM_AUTO && v <= BL_GEMM_PAIR ? v : 0;
+}()};
 
 extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const float* a_global, const uint8_t* b_codes,
                              const uint8_t* b_sf, const float* b_global, int64_t M, int64_t N, int64_t K, void* out,
@@ -1213,26 +1115,24 @@ extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const 
   args.ldc = ldc;
   args.out_dtype = out_dtype;
   args.num_m = args.num_n = 0;
-  {
-    const char* e = getenv("BL_GEMM_DEBUG");
-    args.debug = e ? atoi(e) : 0;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  int kernel = g_kernel_choice.load(std::memory_order_relaxed);
+  if (kernel == BL_GEMM_AUTO) {
+    // the pair kernel needs a full wave of 256 x 256 tiles to pay off; small problems spread better as 128 x 128 tiles
+    const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
+    kernel = tiles >= sm_count(device) / 2 ? BL_GEMM_PAIR : BL_GEMM_TILE;
   }
-  static const int bn = [] {
-    const char* e = getenv("BL_GEMM_BN");
-    return e ? atoi(e) : 128;
-  }();
-  if (bn == 256) return launch_gemm<256, 4>(a_codes, b_codes, args, reinterpret_cast<cudaStream_t>(stream));
-  static const int order = [] {
-    const char* e = getenv("BL_GEMM_ORDER");
-    return e ? atoi(e) : 1;
-  }();
-  if (bn == 1 && order == 0)
-    return launch_persistent<4, 0>(a_codes, b_codes, args, device, reinterpret_cast<cudaStream_t>(stream));
-  if (bn == 1 && order == 2)
-    return launch_persistent<4, 2>(a_codes, b_codes, args, device, reinterpret_cast<cudaStream_t>(stream));
-  if (bn == 1) return launch_persistent<4, 1>(a_codes, b_codes, args, device, reinterpret_cast<cudaStream_t>(stream));
-  if (bn == 2) return launch_pair<5>(a_codes, b_codes, args, device, reinterpret_cast<cudaStream_t>(stream));
-  return launch_gemm<128, 3>(a_codes, b_codes, args, reinterpret_cast<cudaStream_t>(stream));
+  if (kernel == BL_GEMM_PAIR) return launch_pair<5, 0>(a_codes, b_codes, args, device, st);
+  if (kernel == BL_GEMM_PERSISTENT) return launch_persistent<4, 0>(a_codes, b_codes, args, device, st);
+  return launch_gemm<128, 3>(a_codes, b_codes, args, st);
+}
+
+// Forces one of the GEMM kernels (BL_GEMM_TILE, BL_GEMM_PERSISTENT, BL_GEMM_PAIR) for every later bl_nvfp4_gemm call
+// of this process, or returns the choice to the library (BL_GEMM_AUTO). All kernels give identical results.
+extern "C" int bl_nvfp4_gemm_select(int kernel) {
+  BL_REQUIRE(kernel >= BL_GEMM_AUTO && kernel <= BL_GEMM_PAIR, "gemm_select: unknown kernel %d", kernel);
+  g_kernel_choice.store(kernel, std::memory_order_relaxed);
+  return 0;
 }
 
 // Reads (and clears) the device-side error flag of the GEMM kernels: 0 = no bounded wait expired so far.
@@ -1243,14 +1143,5 @@ extern "C" int bl_nvfp4_gemm_status(int* status, int device) {
   int zero = 0;
   BL_CUDA(cudaMemcpyFromSymbol(status, g_gemm_error, sizeof(int)));
   BL_CUDA(cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int)));
-  return 0;
-}
-
-// Experiments only: reads and clears the cycle counters of the persistent kernel (BL_GEMM_DEBUG bit 8).
-extern "C" BL_API int bl_nvfp4_gemm_prof(unsigned long long* out8, int device) {
-  BL_DEVICE(device);
-  unsigned long long zero[8] = {0, 0, 0, 0, 0, 0, 0, 0};
-  BL_CUDA(cudaMemcpyFromSymbol(out8, g_gemm_prof, sizeof(zero)));
-  BL_CUDA(cudaMemcpyToSymbol(g_gemm_prof, zero, sizeof(zero)));
   return 0;
 }

@@ -168,6 +168,14 @@ BL_API int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const floa
  * (0: none) in *status and clears it. No counterpart in the reference (cuBLASLt reports nothing of the kind). */
 BL_API int bl_nvfp4_gemm_status(int* status, int device);
 
+/* bl_nvfp4_gemm picks among three kernels by problem size: 128 x 128 tiles, one CTA per tile (small problems);
+ * persistent 128 x 256 tiles, one CTA per SM; persistent 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2), the
+ * fastest on problems with at least half as many such tiles as SMs. All give bit-identical results. This call forces
+ * one of them for the rest of the process (tests, experiments) or, with BL_GEMM_AUTO, hands the choice back.
+ * The environment variable BL_GEMM_KERNEL (same values) sets the initial choice. No counterpart in the reference. */
+enum { BL_GEMM_AUTO = 0, BL_GEMM_TILE = 1, BL_GEMM_PERSISTENT = 2, BL_GEMM_PAIR = 3 };
+BL_API int bl_nvfp4_gemm_select(int kernel);
+
 /* Diagnostic, no counterpart in the reference: the kernels replace fp32 divisions that share a divisor by a product
  * with its correctly rounded reciprocal plus two fused residual corrections. This runs that routine against the
  * plain division on n pseudo-random operand pairs (synchronously, with a temporary 8-byte device allocation) and

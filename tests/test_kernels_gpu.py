@@ -295,9 +295,21 @@ def _operand(rows, K, seed, scale):
     return codes, sf, float(g)
 
 
+@pytest.fixture
+def gemm_kernel(request):
+    """Runs a test once per GEMM kernel (the library's own choice included) and restores the choice afterwards."""
+    _ops.gemm_select(request.param)
+    yield request.param
+    _ops.gemm_select("auto")
+
+
+ALL_GEMM_KERNELS = pytest.mark.parametrize("gemm_kernel", ["auto", "tile", "persistent", "pair"], indirect=True)
+
+
+@ALL_GEMM_KERNELS
 @pytest.mark.parametrize("M,N,K", [(128, 128, 256), (128, 128, 64), (256, 384, 1024), (100, 136, 96), (48, 64, 128),
-                                   (1, 8, 32), (300, 520, 2048)])
-def test_gemm_matches_oracle(M, N, K):
+                                   (1, 8, 32), (300, 520, 2048), (520, 264, 352)])
+def test_gemm_matches_oracle(M, N, K, gemm_kernel):
     """Tolerance: the tensor core accumulates exact E2M1 x E2M1 x UE4M3 x UE4M3 products in fp32 and the result is
     rounded once to bf16 -> every element within 2^-8 relative (one bf16 ulp) of the double-precision contraction,
     plus an absolute term for cancellation inside the fp32 accumulation."""
@@ -316,7 +328,30 @@ def test_gemm_matches_oracle(M, N, K):
     np.testing.assert_allclose(yf.cpu().numpy(), ref, rtol=2e-5, atol=2e-5 * scale)
 
 
-def test_gemm_is_linear_in_row_blocks_at_scale():
+def test_gemm_kernels_agree_bit_for_bit():
+    """All kernels accumulate each output element over K in the same order on the same tensor-core path, so their
+    outputs are identical, ragged edges and a K that is not a multiple of the 256-element stage included."""
+    M, N, K = 2304 + 72, 2560 + 40, 1024 + 96
+    g0 = torch.Generator(device=DEV).manual_seed(3)
+    a = torch.randint(0, 256, (M, K // 2), device=DEV, dtype=torch.uint8, generator=g0)
+    b = torch.randint(0, 256, (N, K // 2), device=DEV, dtype=torch.uint8, generator=g0)
+    asf = _ops.to_blocked(torch.randint(40, 72, (M, K // 16), device=DEV, dtype=torch.uint8, generator=g0))
+    bsf = _ops.to_blocked(torch.randint(40, 72, (N, K // 16), device=DEV, dtype=torch.uint8, generator=g0))
+    one = torch.ones(1, device=DEV)
+    outs = {}
+    try:
+        for name in ("tile", "persistent", "pair"):
+            _ops.gemm_select(name)
+            outs[name] = _ops.nvfp4_gemm(a, asf, one, b, bsf, one, out_dtype=torch.float32)
+    finally:
+        _ops.gemm_select("auto")
+    assert _ops.gemm_status(0) == 0
+    assert torch.equal(outs["tile"], outs["persistent"]) and torch.equal(outs["tile"], outs["pair"])
+    assert torch.isfinite(outs["tile"]).all() and outs["tile"].abs().max() > 0
+
+
+@ALL_GEMM_KERNELS
+def test_gemm_is_linear_in_row_blocks_at_scale(gemm_kernel):
     """Size-independent property at a layer-sized problem: the product of stacked operands is the stack of products
     (bit for bit: tiles never mix rows), and equal inputs give equal outputs."""
     M, N, K = 2048, 3072, 4096
