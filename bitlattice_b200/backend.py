@@ -24,7 +24,7 @@ import torch
 from . import _ops
 from . import formats as F
 
-__all__ = ["FP4_RECIPES", "Fp4Operand", "Fp4Recipe", "as_recipe", "clear_shared", "drop_cached", "fp4_backward",
+__all__ = ["FP4_RECIPES", "Fp4Operand", "Fp4Recipe", "as_recipe", "clear_shared", "drop_cached", "fp4_backward", "fp4_dgrad", "fp4_wgrad",
            "fp4_forward_saving", "fp4_mm", "fp4_supported", "fp4_unfit", "is_nvfp4", "nvfp4_linear", "quantize_fp4",
            "rht_last", "set_sr_seed", "to_blocked", "weight_operand", "weight_t_operand"]
 
@@ -293,23 +293,34 @@ def fp4_forward_saving(x: torch.Tensor, w, bias, recipe: Fp4Recipe = Fp4Recipe()
     return y.reshape(*x.shape[:-1], w.shape[0]), xt
 
 
+def fp4_dgrad(gy: torch.Tensor, w, recipe: Fp4Recipe = Fp4Recipe()):
+    """gx = Q_sr(gy) Q(W^T)^T; also returns the padded 2-D gradient and its operand for fp4_wgrad."""
+    N = gy.shape[-1]
+    g2 = gy.reshape(-1, N)
+    g2p = _pad_rows(g2, 32).contiguous()
+    gq = quantize_fp4(g2p, stochastic=True)
+    return fp4_mm(gq, weight_t_operand(w), gy.dtype)[:g2.shape[0]], g2p, gq
+
+
+def fp4_wgrad(g2p: torch.Tensor, gq: Fp4Operand | None, xt: Fp4Operand, w, recipe: Fp4Recipe = Fp4Recipe()):
+    """gw = Q_sr(rot(gy^T)) Q(rot(x^T))^T for the padded 2-D gradient ``g2p``; ``gq`` (its row operand, if the input
+    gradient was computed) supplies the bound of the rotated operand's per-tensor scale."""
+    seed = _seed()
+    bound = gq.global_scale * 4.0 if gq is not None else None
+    gt = Fp4Operand(*_ops.quantize_nvfp4_t(g2p, _hadamard16(g2p.device, torch.float32), seed, 0, bound,
+                                           blocked=True), True)
+    return fp4_mm(gt, xt, w.dtype)
+
+
 def fp4_backward(gy: torch.Tensor, w, xt: Fp4Operand | None, need_x: bool, need_w: bool,
                  recipe: Fp4Recipe = Fp4Recipe()):
     """Input and weight gradients of y = x W^T on FP4 tensor cores (reference: backend.py:592-626):
     gx = Q_sr(gy) Q(W^T)^T, gw = Q_sr(rot(gy^T)) Q(rot(x^T))^T; the rotations cancel in the product."""
-    N = gy.shape[-1]
-    g2 = gy.reshape(-1, N)
-    M = g2.shape[0]
-    g2p = _pad_rows(g2, 32).contiguous()
-    gx = gw = None
-    gq = None
+    gx = gw = gq = g2p = None
     if need_x:
-        gq = quantize_fp4(g2p, stochastic=True)
-        gx = fp4_mm(gq, weight_t_operand(w), gy.dtype)[:M]
+        gx, g2p, gq = fp4_dgrad(gy, w, recipe)
     if need_w:
-        seed = _seed()
-        bound = gq.global_scale * 4.0 if gq is not None else None
-        gt = Fp4Operand(*_ops.quantize_nvfp4_t(g2p, _hadamard16(g2p.device, torch.float32), seed, 0, bound,
-                                               blocked=True), True)
-        gw = fp4_mm(gt, xt, w.dtype)
+        if g2p is None:
+            g2p = _pad_rows(gy.reshape(-1, gy.shape[-1]), 32).contiguous()
+        gw = fp4_wgrad(g2p, gq, xt, w, recipe)
     return gx, gw

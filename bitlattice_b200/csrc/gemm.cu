@@ -689,7 +689,7 @@ __global__ void __launch_bounds__(kPersistThreads, 1) gemm_persistent_kernel(con
 //   empty[s]   each CTA: tcgen05.commit from CTA 0 after the MMAs that read stage s (one commit per CTA)
 //   acc_full   each CTA: tcgen05.commit from CTA 0 after the last MMA of a tile
 //   acc_empty  in CTA 0: 16 arrivals, one per epilogue warp of both CTAs, when the accumulator is in registers
-// No load is multicast; the only cross-CTA traffic is barrier signalling.
+// Every CTA loads its own operand halves; the only cross-CTA traffic is barrier signalling.
 constexpr int kPairThreads = 320;
 
 __device__ __forceinline__ uint32_t cluster_ctarank() {

@@ -10,7 +10,11 @@ rank r holding rows ``[r*N/p, (r+1)*N/p)`` of codes, scales and optimizer phase,
     update    lattice update of shard r           local: no communication; ``_bl_row_offset`` makes the shard draw
                                                   the random numbers of the unsharded weight
 
-The two collectives are NCCL's (``torch.distributed``) over NVLink; gathered activations land in local HBM before any
+On the FP4 routes each rank quantizes only its own token shard (after an all-reduce of one float, the shard maxima,
+so that every rank derives the same per-tensor scale) and the ranks all-gather the packed operands instead of the
+bf16 activations: 0.5625 bytes per element instead of 2, and the quantization work shrinks with the world size.
+
+The collectives are NCCL's (``torch.distributed``) over NVLink; gathered operands land in local HBM before any
 kernel reads them. ``gloo`` works for CPU tests of the bookkeeping. With ``group=None`` or a world of one the layer
 degenerates to the plain lattice linear.
 """
@@ -21,7 +25,8 @@ import torch.distributed as dist
 
 from .tensor import LatticeTensor
 
-__all__ = ["ColumnParallelLinear", "column_parallel_linear", "shard_bounds", "shard_rows", "world"]
+__all__ = ["ColumnParallelFp4Linear", "ColumnParallelLinear", "column_parallel_linear", "column_parallel_linears",
+           "gathered_input_operands", "shard_bounds", "shard_rows", "world"]
 
 
 def world(group=None) -> tuple[int, int]:
@@ -104,9 +109,120 @@ class ColumnParallelLinear(torch.autograd.Function):
         return gx, gw, None, None
 
 
+def _gather_cat(local: torch.Tensor, group, size: int) -> torch.Tensor:
+    """all-gather of equally shaped contiguous tensors, stacked along a new leading dimension"""
+    out = torch.empty(size, *local.shape, dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(out, local.contiguous(), group=group)
+    return out
+
+
+def gathered_input_operands(x_shard: torch.Tensor, group, want_t: bool):
+    """NVFP4 GEMM operands of the full input x [M, K] from this rank's token shard [M/p, K] (M/p a multiple of 128):
+    the row operand Q(x) and, if asked, the rotated transposed operand Q(rot(x^T)) for the weight gradient. Codes and
+    scales equal those of the unsharded quantization bit for bit: the per-tensor scale comes from the maximum over all
+    shards, blocks of 16 never straddle shards, and 128-row scale tiles are whole."""
+    from . import _ops, backend
+    rank, size = world(group)
+    K = x_shard.shape[-1]
+    x2 = x_shard.reshape(-1, K).contiguous()
+    rows = x2.shape[0]
+    amax = _ops.amax_global(x2)[0:1].clone()
+    dist.all_reduce(amax, op=dist.ReduceOp.MAX, group=group)
+    g = _ops.amax_global(amax)[1:2]                       # the scale rule applied to the global maximum
+    packed, sf = _ops.quantize_nvfp4(x2, g, -1, 0, blocked=True)
+    xq = backend.Fp4Operand(_gather_cat(packed, group, size).view(size * rows, K // 2),
+                            _gather_cat(sf, group, size).view(-1), g, True)
+    xt = None
+    if want_t:
+        tp, ts, tg = _ops.quantize_nvfp4_t(x2, backend._hadamard16(x2.device, torch.float32), -1, 0, g * 4.0,
+                                           blocked=False)
+        # shards are column slices of the transposed operand: [p, K, m] -> [K, p * m]
+        tpf = _gather_cat(tp, group, size).permute(1, 0, 2).reshape(K, size * rows // 2)
+        tsf = _gather_cat(ts.view(torch.uint8), group, size).permute(1, 0, 2).reshape(K, size * rows // 16)
+        xt = backend.Fp4Operand(tpf, _ops.to_blocked(tsf.contiguous()), tg, True)
+    return xq, xt
+
+
+class ColumnParallelFp4Linear(torch.autograd.Function):
+    """The 'fp4_all' route of the column-parallel layer for one or more weights that read the same input (q/k/v,
+    gate/up): shard-local quantization and one packed all-gather for all of them; in the backward the partial input
+    gradients of all weights are summed locally, reduce-scattered once, and that collective runs while the weight
+    gradients are computed."""
+
+    @staticmethod
+    def forward(ctx, x_shard, group, recipe, *weights):
+        from . import backend
+        need_w = any(ctx.needs_input_grad[3:])
+        kind = f"cp:{id(group)}:{'fwd+t' if need_w else 'fwd'}"
+        xq, xt = backend._shared(x_shard, recipe, kind, lambda: gathered_input_operands(x_shard, group, need_w))
+        ctx.group, ctx.weights, ctx.recipe, ctx.xt = group, weights, recipe, xt
+        ctx.x_meta = (x_shard.shape, x_shard.dtype)
+        return tuple(backend.fp4_mm(xq, backend.weight_operand(w), x_shard.dtype) for w in weights)
+
+    @staticmethod
+    def backward(ctx, *gys):
+        from . import backend
+        shape, dtype = ctx.x_meta
+        rank, size = world(ctx.group)
+        need_x = ctx.needs_input_grad[0]
+        staged, gx_sum = [], None
+        for w, gy in zip(ctx.weights, gys):
+            if gy is None:
+                staged.append(None)
+                continue
+            if need_x:
+                gx, g2p, gq = backend.fp4_dgrad(gy, w, ctx.recipe)
+                gx_sum = gx if gx_sum is None else gx_sum.add_(gx)
+            else:
+                g2p, gq = backend._pad_rows(gy.reshape(-1, gy.shape[-1]), 32).contiguous(), None
+            staged.append((g2p, gq))
+        gx_out = work = None
+        if gx_sum is not None:
+            gx_sum = gx_sum.to(dtype).contiguous()
+            gx_out = torch.empty(gx_sum.shape[0] // size, gx_sum.shape[1], dtype=dtype, device=gx_sum.device)
+            work = dist.reduce_scatter_tensor(gx_out, gx_sum, op=dist.ReduceOp.SUM, group=ctx.group, async_op=True)
+        gws = []
+        for i, (w, st) in enumerate(zip(ctx.weights, staged)):
+            if st is None or not ctx.needs_input_grad[3 + i] or ctx.xt is None:
+                gws.append(None)
+                continue
+            gws.append(backend.fp4_wgrad(st[0], st[1], ctx.xt, w, ctx.recipe).to(w.dtype))
+        if work is not None:
+            work.wait()
+            gx_out = gx_out.reshape(shape)
+        return (gx_out, None, None, *gws)
+
+
+def _fp4_all_route(x_shard: torch.Tensor, w):
+    """The NVFP4 recipe when the layer would take the 'fp4_all' route and the shard shapes allow packed gathering."""
+    if not (isinstance(w, LatticeTensor) and x_shard.is_cuda and x_shard.dim() == 2):
+        return None
+    from .compute_policy import route
+    policy, comp = route(x_shard, w)
+    if policy != "fp4_all" or x_shard.shape[0] % 128 or x_shard.shape[1] % 64:
+        return None
+    return comp.nvfp4
+
+
 def column_parallel_linear(x_shard: torch.Tensor, w: torch.Tensor, group=None, linear=None) -> torch.Tensor:
     """Token-sharded input [M/p, K], row-sharded weight [N/p, K] -> feature-sharded output [M, N/p]."""
-    linear = linear or torch.nn.functional.linear
     if world(group)[1] == 1:
-        return linear(x_shard, w)
-    return ColumnParallelLinear.apply(x_shard, w, group, linear)
+        return (linear or torch.nn.functional.linear)(x_shard, w)
+    if linear is None:
+        recipe = _fp4_all_route(x_shard, w)
+        if recipe is not None:
+            return ColumnParallelFp4Linear.apply(x_shard, group, recipe, w)[0]
+    return ColumnParallelLinear.apply(x_shard, w, group, linear or torch.nn.functional.linear)
+
+
+def column_parallel_linears(x_shard: torch.Tensor, weights, group=None) -> tuple:
+    """Several column-parallel layers on one input (q/k/v, gate/up): the outputs of column_parallel_linear for each
+    weight. On the 'fp4_all' route they share one quantization and one all-gather of the input, and their input
+    gradients leave through a single reduce-scatter -- call backward on all outputs together
+    (``torch.autograd.backward(outputs, grads)``) to get that."""
+    weights = tuple(weights)
+    if world(group)[1] > 1:
+        recipes = [_fp4_all_route(x_shard, w) for w in weights]
+        if all(r is not None for r in recipes) and all(r == recipes[0] for r in recipes):
+            return ColumnParallelFp4Linear.apply(x_shard, group, recipes[0], *weights)
+    return tuple(column_parallel_linear(x_shard, w, group) for w in weights)

@@ -1,0 +1,92 @@
+"""Worker of tests/test_parallel_gpu.py: one process per GPU under torch.distributed.run (NCCL).
+
+Checks the column-parallel FP4 layer against the unsharded layer computed on the same rank:
+  * the gathered operands Q(x), Q(rot(x^T)) equal the unsharded quantization bit for bit,
+  * y_shard equals the matching columns of the unsharded y bit for bit,
+  * gx (reduce-scattered) and gw_shard stay within the reference's FP4 bound of the exact route
+    (their stochastic-rounding draws differ from the unsharded layer's by construction).
+Prints "OK <rank>" on success.
+"""
+import os
+import sys
+
+import torch
+import torch.distributed as dist
+
+sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
+import bitlattice_b200 as bl                                    # noqa: E402
+from bitlattice_b200 import backend                             # noqa: E402
+from bitlattice_b200.parallel import (column_parallel_linear, column_parallel_linears,     # noqa: E402
+                                      gathered_input_operands, shard_rows)
+
+
+def rel(a, b):
+    return float((a.float() - b.float()).norm() / b.float().norm())
+
+
+def main():
+    rank, world, local = int(os.environ["RANK"]), int(os.environ["WORLD_SIZE"]), int(os.environ["LOCAL_RANK"])
+    torch.cuda.set_device(local)
+    dev = torch.device("cuda", local)
+    dist.init_process_group("nccl", device_id=dev)
+    M, N, K = 256 * world, 512, 1024
+    gen = torch.Generator(device=dev).manual_seed(11)            # same stream on every rank
+    wd = torch.randn(N, K, device=dev, generator=gen) * 0.02
+    x = torch.randn(M, K, device=dev, generator=gen).to(torch.bfloat16)
+    gy = (torch.randn(M, N, device=dev, generator=gen) * 1e-2).to(torch.bfloat16)
+    w = bl.LatticeTensor.from_float(wd, "nvfp4", method="rtn", dtype=torch.bfloat16)
+    ws = shard_rows(w, rank, world)
+    rows = slice(rank * M // world, (rank + 1) * M // world)
+    cols = slice(rank * N // world, (rank + 1) * N // world)
+
+    # operands
+    xq, xt = gathered_input_operands(x[rows].contiguous(), None, True)
+    ref_q, ref_t = backend._input_operands(x, backend.Fp4Recipe())
+    for got, ref in ((xq, ref_q), (xt, ref_t)):
+        assert torch.equal(got.packed, ref.packed), "codes differ from the unsharded quantization"
+        assert torch.equal(got.scales.view(torch.uint8).reshape(-1), ref.scales.view(torch.uint8).reshape(-1))
+        assert torch.equal(got.global_scale, ref.global_scale)
+
+    with bl.compute("fp4_all"):
+        p_full = torch.nn.Parameter(w)
+        xf = x.detach().requires_grad_(True)
+        y_full = torch.nn.functional.linear(xf, p_full)
+        y_full.backward(gy)
+        p = torch.nn.Parameter(ws)
+        xs = x[rows].detach().contiguous().requires_grad_(True)
+        y = column_parallel_linear(xs, p, None)
+        assert torch.equal(y, y_full[:, cols]), "forward shard differs from the unsharded forward"
+        y.backward(gy[:, cols].contiguous())
+    W = w.dequantize(torch.float32)
+    gx_exact = gy.float() @ W
+    gw_exact = gy.float().t() @ x.float()
+    assert xs.grad.shape == (M // world, K) and p.grad.shape == (N // world, K)
+    # the reference's bound for FP4 gradients against the exact route (tests/test_backend.py:91-94)
+    assert rel(xs.grad, gx_exact[rows]) < 0.25, rel(xs.grad, gx_exact[rows])
+    assert rel(p.grad, gw_exact[cols]) < 0.25, rel(p.grad, gw_exact[cols])
+    # and as close to it as the unsharded layer is (same estimator, different draws)
+    assert rel(xs.grad, gx_exact[rows]) < 1.5 * rel(xf.grad, gx_exact) + 1e-3
+    assert rel(p.grad, gw_exact[cols]) < 1.5 * rel(p_full.grad, gw_exact) + 1e-3
+
+    # two layers on one input: one gather, one reduce-scatter of the summed input gradient
+    wd2 = torch.randn(N // 2, K, device=dev, generator=gen) * 0.02
+    gy2 = (torch.randn(M, N // 2, device=dev, generator=gen) * 1e-2).to(torch.bfloat16)
+    w2 = bl.LatticeTensor.from_float(wd2, "nvfp4", method="rtn", dtype=torch.bfloat16)
+    cols2 = slice(rank * N // 2 // world, (rank + 1) * N // 2 // world)
+    with bl.compute("fp4_all"):
+        pa, pb = torch.nn.Parameter(shard_rows(w, rank, world)), torch.nn.Parameter(shard_rows(w2, rank, world))
+        xs2 = x[rows].detach().contiguous().requires_grad_(True)
+        ya, yb = column_parallel_linears(xs2, (pa, pb), None)
+        assert torch.equal(ya, y_full[:, cols])
+        torch.autograd.backward((ya, yb), (gy[:, cols].contiguous(), gy2[:, cols2].contiguous()))
+    gx2_exact = gx_exact + gy2.float() @ w2.dequantize(torch.float32)
+    assert rel(xs2.grad, gx2_exact[rows]) < 0.25, rel(xs2.grad, gx2_exact[rows])
+    assert rel(pb.grad, (gy2.float().t() @ x.float())[cols2]) < 0.25
+    assert bl._ops.gemm_status(local) == 0
+    dist.barrier()
+    print(f"OK {rank}", flush=True)
+    dist.destroy_process_group()
+
+
+if __name__ == "__main__":
+    main()
