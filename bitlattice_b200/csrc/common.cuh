@@ -239,6 +239,88 @@ __device__ __forceinline__ uint32_t e2m1_sr_x8(const float v[8], float inv, uint
   return e2m1_drop_negative_zero(cvt_e2m1x8(r));
 }
 
+// ---------------------------------------------------------------------------------------------- device: blocks of 16
+// Whole 16-element blocks in one thread, written for few issue slots per element: packed fp32x2 multiplies, four
+// conversions merged into one register, and stochastic rounding decided in 2^-25 fixed point.
+
+// {a * s, b * s}: one packed multiply, each lane rounded to nearest like a scalar multiply
+__device__ __forceinline__ void mul2(float a, float b, float s, float& ra, float& rb) {
+  asm("{\n\t.reg .b64 p, q;\n\t"
+      "mov.b64 p, {%2, %3};\n\t"
+      "mov.b64 q, {%4, %4};\n\t"
+      "mul.rn.f32x2 p, p, q;\n\t"
+      "mov.b64 {%0, %1}, p;\n\t}"
+      : "=f"(ra), "=f"(rb)
+      : "f"(a), "f"(b), "f"(s));
+}
+
+// 8 floats -> 8 nibbles in one register (element i in nibble i), hardware rounding (nearest, ties to even)
+__device__ __forceinline__ uint32_t cvt_e2m1x8_merged(const float v[8]) {
+  uint32_t w;
+  asm("{\n\t.reg .b8 t0, t1, t2, t3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t0, %2, %1;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t1, %4, %3;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t2, %6, %5;\n\t"
+      "cvt.rn.satfinite.e2m1x2.f32 t3, %8, %7;\n\t"
+      "mov.b32 %0, {t0, t1, t2, t3};\n\t}"
+      : "=r"(w)
+      : "f"(v[0]), "f"(v[1]), "f"(v[2]), "f"(v[3]), "f"(v[4]), "f"(v[5]), "f"(v[6]), "f"(v[7]));
+  return w;
+}
+
+// Round-to-nearest codes (ties to the lower level) of (v[i] * pre) / se for 16 values, se > 0; pre is 1 or a power of
+// two folded into the bracket. inv approximates 1 / se to a few ulps; the bracket (1 -+ 2^-19) around it contains the
+// exact quotient, so equal conversions of both ends are the conversion of the quotient, which then is no tie;
+// otherwise (at or next to a midpoint) the exact ladder decides.
+__device__ __forceinline__ uint2 e2m1_rtn16(const float v[16], float pre, float se, float inv) {
+  const float lo = inv * pre * 0.99999809265136718750f, hi = inv * pre * 1.00000190734863281250f;
+  float a[16], b[16];
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    mul2(v[i], v[i + 1], lo, a[i], a[i + 1]);
+    mul2(v[i], v[i + 1], hi, b[i], b[i + 1]);
+  }
+  const uint32_t a0 = cvt_e2m1x8_merged(a), a1 = cvt_e2m1x8_merged(a + 8);
+  const uint32_t b0 = cvt_e2m1x8_merged(b), b1 = cvt_e2m1x8_merged(b + 8);
+  // (the reciprocal is only trusted for scales well inside the normal range)
+  if (__builtin_expect(a0 == b0 && a1 == b1 && se > 1e-30f && se < 1e30f, 1))
+    return make_uint2(e2m1_drop_negative_zero(a0), e2m1_drop_negative_zero(a1));
+  return make_uint2(e2m1_nearest_x8_exact(v[0] * pre, v[1] * pre, v[2] * pre, v[3] * pre, v[4] * pre, v[5] * pre,
+                                          v[6] * pre, v[7] * pre, se),
+                    e2m1_nearest_x8_exact(v[8] * pre, v[9] * pre, v[10] * pre, v[11] * pre, v[12] * pre, v[13] * pre,
+                                          v[14] * pre, v[15] * pre, se));
+}
+
+// Stochastic-rounding codes of x[i] = v[i] * inv for 16 values (bitlattice/fp4ref.py:71-78), u from hash(idx0 + i).
+// With a = min(|x|, 6) and A = ceil(a * 2^25) (exact for a >= 0.5), shifting A right by t = [a >= 2] + [a >= 4] puts
+// the level index below a in the bits above 24 and the position between the two neighbouring levels, as a fraction
+// of 2^24, in the bits below. The draw n = hash >> 8 rounds up iff n < that fraction, which is the carry of adding
+// (2^24 - 1 - n): so the code is ((A >> t) + (~hash >> 8) >> 24) + 2 t. Identical to comparing u * gap < a - lo in
+// real numbers, which is what the reference's fp32 expression evaluates without rounding.
+__device__ __forceinline__ uint2 e2m1_sr16(const float v[16], float inv, uint32_t key, uint32_t idx0) {
+  uint32_t w[2] = {0u, 0u};
+  const uint32_t h0 = idx0 * 0x27D4EB2Fu + key;
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) {
+    float x[2];
+    mul2(v[i], v[i + 1], inv, x[0], x[1]);
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const float a = fminf(fabsf(x[e]), 6.0f);
+      const uint32_t A = __float2uint_ru(a * 33554432.0f);
+      const uint32_t t = __byte_perm(0x02020100u, 0u, A >> 26);
+      uint32_t h = h0 + static_cast<uint32_t>(i + e) * 0x27D4EB2Fu;
+      h = (h ^ (h >> 16)) * 0x7FEB352Du;
+      h = (h ^ (h >> 15)) * 0x846CA68Bu;
+      h = ~(h ^ (h >> 16));
+      const uint32_t k = (((A >> t) + (h >> 8)) >> 24) + 2u * t;
+      const uint32_t nib = k | ((__float_as_uint(x[e]) >> 28) & 8u);
+      w[(i + e) >> 3] |= nib << (4 * ((i + e) & 7));
+    }
+  }
+  return make_uint2(e2m1_drop_negative_zero(w[0]), e2m1_drop_negative_zero(w[1]));
+}
+
 // ---------------------------------------------------------------------------------------------- device: dense loads
 
 template <typename T> __device__ __forceinline__ float to_f(T v);

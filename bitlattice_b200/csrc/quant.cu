@@ -183,12 +183,117 @@ __global__ void __launch_bounds__(kQThreads, 5) quantize_rows_kernel(const T* __
   }
 }
 
+// ---- rows, one thread per block of 16 ---------------------------------------------------------------------------------
+
+__device__ __forceinline__ float rcp_approx(float x) {
+  float r;
+  asm("rcp.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+// One block of 16 values v[i] * pre (pre: 1 or a power of two) -> 16 codes and the scale byte.
+// SR == false: reference.quantize 'rtn'. SR == true: fp4ref.quantize 'sr' (idx0 = flat index of v[0]).
+template <bool SR>
+__device__ __forceinline__ uint2 quantize_block(const float v[16], float pre, float g, float rg, uint32_t key,
+                                                uint32_t idx0, uint32_t* scale) {
+  float amax = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
+  amax *= pre;
+  if constexpr (!SR) {
+    const uint32_t sb = e4m3_encode(div_rn(fmaxf(div_rn(amax, 6.0f, kInv6), 1e-12f), g, rg));
+    const float se = e4m3_decode(sb) * g;
+    *scale = sb;
+    return e2m1_rtn16(v, pre, se, rcp_approx(se));
+  } else {
+    const uint32_t sb = e4m3_encode(div_rn(div_rn(amax, 6.0f, kInv6), g, rg));
+    const float t = e4m3_decode(sb) * g;
+    const float inv = t > 0.0f ? __frcp_rn(t) : 0.0f;
+    *scale = sb;
+    return e2m1_sr16(v, inv * pre, key, idx0);
+  }
+}
+
+template <typename T>
+struct Raw16 {                                       // 16 elements as loaded
+  uint4 q[sizeof(T) * 16 / 16];
+};
+
+template <typename T>
+__device__ __forceinline__ void load_raw16(const T* p, Raw16<T>& r) {
+#pragma unroll
+  for (int i = 0; i < static_cast<int>(sizeof(T)); ++i) r.q[i] = __ldcs(reinterpret_cast<const uint4*>(p) + i);
+}
+
+template <typename T>
+__device__ __forceinline__ void unpack_raw16(const Raw16<T>& r, float v[16]) {
+  const uint32_t* w = reinterpret_cast<const uint32_t*>(r.q);
+  if constexpr (sizeof(T) == 4) {
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(w[i]);
+  } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      v[2 * i] = __uint_as_float(w[i] << 16);
+      v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
+    }
+  } else {
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&w[i]));
+      v[2 * i] = f.x;
+      v[2 * i + 1] = f.y;
+    }
+  }
+}
+
+// block (bx, 256/bx): x covers the 16-element blocks of a row, y covers rows; a thread keeps its block column and walks
+// down the rows, kRowsUnroll rows in flight (their loads are issued before any arithmetic).
+template <typename T, bool SR>
+__global__ void __launch_bounds__(kQThreads, 3) quantize_rows16_kernel(const T* __restrict__ x, int64_t rows, int64_t cols,
+                                                                    const float* __restrict__ global, uint32_t key,
+                                                                    uint8_t* __restrict__ codes,
+                                                                    uint8_t* __restrict__ scales, int layout) {
+  const float g = global[0];
+  const float rg = __frcp_rn(g);
+  const int64_t cb = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;   // block column
+  const int64_t cols16 = cols / 16;
+  if (cb >= cols16) return;
+  const int64_t row_step = static_cast<int64_t>(gridDim.y) * blockDim.y;
+  // scale position: row-major r * cols16 + cb; blocked ((r >> 7) * nc + (cb >> 2)) * 512 + (r & 31) * 16 +
+  // ((r >> 5) & 3) * 4 + (cb & 3)
+  const int64_t nc = (cols16 + 3) >> 2;
+  const int64_t sf_col = layout == BL_SF_ROWMAJOR ? cb : (cb >> 2) * 512 + (cb & 3);
+  for (int64_t r0 = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; r0 < rows;
+       r0 += row_step * kRowsUnroll) {
+    Raw16<T> raw[kRowsUnroll];
+#pragma unroll
+    for (int u = 0; u < kRowsUnroll; ++u) {
+      const int64_t r = r0 + u * row_step;
+      if (r < rows) load_raw16(x + r * cols + cb * 16, raw[u]);
+    }
+#pragma unroll
+    for (int u = 0; u < kRowsUnroll; ++u) {
+      const int64_t r = r0 + u * row_step;
+      if (r >= rows) break;
+      float v[16];
+      unpack_raw16(raw[u], v);
+      uint32_t sb;
+      const uint2 out = quantize_block<SR>(v, 1.0f, g, rg, key, static_cast<uint32_t>(r * cols + cb * 16), &sb);
+      __stcs(reinterpret_cast<uint2*>(codes + r * (cols / 2)) + cb, out);
+      const int64_t sf_row = layout == BL_SF_ROWMAJOR ? r * cols16
+                                                      : (r >> 7) * nc * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4;
+      scales[sf_row + sf_col] = static_cast<uint8_t>(sb);
+    }
+  }
+}
+
 struct RowGeometry {
   dim3 block, grid;
 };
 
 static RowGeometry row_geometry(int64_t rows, int64_t cols, int device) {
-  const int64_t cpr = cols / 8;
+  const int64_t cpr = cols / 16;
   int bx = 32;
   while (bx < kQThreads && bx < cpr) bx <<= 1;
   const int by = kQThreads / bx;
@@ -461,6 +566,116 @@ __global__ void __launch_bounds__(kQThreads, 4) quantize_t2_kernel(const T* __re
   }
 }
 
+// v[j] = sum over i (ascending, every partial sum rounded to fp32: the reference's order) of p[i] * (-1)^popc(i & j),
+// p[i] = raw[i] * H[i][0], for H = diag(s) * Sylvester-Hadamard / 4. Outputs j and j' share every partial sum over
+// i < n when j = j' mod n, so the 16 sequential sums form a tree of 2 + 8 + 32 + 128 = 170 additions instead of 256.
+__device__ __forceinline__ void rotate16_tree(const float p[16], float v[16]) {
+  v[0] = p[0] + p[1];
+  v[1] = p[0] - p[1];
+#pragma unroll
+  for (int n = 2; n < 16; n <<= 1) {
+#pragma unroll
+    for (int j = 0; j < n; ++j) {
+      float a = v[j], b = v[j];
+#pragma unroll
+      for (int i = 0; i < n; ++i) {
+        if (__popc(i & j) & 1) {
+          a = a - p[n + i];
+          b = b + p[n + i];
+        } else {
+          a = a + p[n + i];
+          b = b - p[n + i];
+        }
+      }
+      v[j] = a;
+      v[n + j] = b;
+    }
+  }
+}
+
+// any 16 x 16 matrix: for each output the ascending sum over the inputs
+__device__ __forceinline__ void rotate16_generic(const float raw[16], const float* __restrict__ sH, float v[16]) {
+#pragma unroll
+  for (int j = 0; j < 16; ++j) {
+    float a = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) a = a + raw[i] * sH[i * 16 + j];
+    v[j] = a;
+  }
+}
+
+// Transposed quantizer, one thread per (block of 16 rows, pair of adjacent columns); adjacent lanes read adjacent column
+// pairs, so every row of the tile is read as full 128-byte lines; codes and scales of the 64 x 128 tile are staged in
+// shared memory and written out as rows of the transposed result.
+template <typename T, bool SR>
+__global__ void __launch_bounds__(kQThreads, 3) quantize_t3_kernel(const T* __restrict__ x, int64_t M, int64_t K,
+                                                                const float* __restrict__ H,
+                                                                const float* __restrict__ global, uint32_t key,
+                                                                uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
+                                                                int layout) {
+  __shared__ uint2 s_codes[kTK][kTM / 16 + 1];
+  __shared__ uint8_t s_scales[kTK][kTM / 16];
+  __shared__ float sH[256];
+  bool structured = false;
+  if (H != nullptr) {
+    sH[threadIdx.x] = H[threadIdx.x];
+    __syncthreads();
+    const int i = threadIdx.x >> 4, j = threadIdx.x & 15;
+    const float si = sH[i * 16];
+    const float expect = (__popc(i & j) & 1) ? -si : si;
+    structured = __syncthreads_and(fabsf(si) == 0.25f && sH[threadIdx.x] == expect) != 0;
+  }
+  const int64_t m0 = static_cast<int64_t>(blockIdx.y) * kTM, k0 = static_cast<int64_t>(blockIdx.x) * kTK;
+  const int kp = threadIdx.x & 31, mb = threadIdx.x >> 5;
+  const int64_t k = k0 + 2 * kp, m = m0 + mb * 16;
+  const bool active = k < K && m < M;                   // K is even and M a multiple of 16
+  if (active) {
+    float ra[16], rb[16];
+    const T* p = x + m * K + k;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) load2(p + i * K, ra[i], rb[i]);
+    const float g = global[0];
+    const float rg = __frcp_rn(g);
+    float va[16], vb[16];
+    if (H == nullptr) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) {
+        va[i] = ra[i];
+        vb[i] = rb[i];
+      }
+    } else if (structured) {
+#pragma unroll
+      for (int i = 0; i < 16; ++i) mul2(ra[i], rb[i], sH[i * 16], ra[i], rb[i]);
+      rotate16_tree(ra, va);
+      rotate16_tree(rb, vb);
+    } else {
+      rotate16_generic(ra, sH, va);
+      rotate16_generic(rb, sH, vb);
+    }
+    uint32_t sb;
+    s_codes[2 * kp][mb] =
+        quantize_block<SR>(va, 1.0f, g, rg, key, static_cast<uint32_t>(static_cast<uint64_t>(k) * M + m), &sb);
+    s_scales[2 * kp][mb] = static_cast<uint8_t>(sb);
+    s_codes[2 * kp + 1][mb] =
+        quantize_block<SR>(vb, 1.0f, g, rg, key, static_cast<uint32_t>(static_cast<uint64_t>(k + 1) * M + m), &sb);
+    s_scales[2 * kp + 1][mb] = static_cast<uint8_t>(sb);
+  }
+  __syncthreads();
+  // write-out: thread -> (row of the transposed tile, two of its eight blocks)
+  const int row = threadIdx.x >> 2, b0 = (threadIdx.x & 3) * 2;
+  const int64_t kr = k0 + row;
+  if (kr < K) {
+#pragma unroll
+    for (int e = 0; e < 2; ++e) {
+      const int64_t mm = m0 + (b0 + e) * 16;
+      if (mm < M) {
+        *reinterpret_cast<uint2*>(codes + kr * (M / 2) + mm / 2) = s_codes[row][b0 + e];
+        scales[scale_index(layout, kr, mm / 16, M / 16)] = s_scales[row][b0 + e];
+      }
+    }
+  }
+}
+
 // NVFP4 W [N, K] -> NVFP4 of W^T [K, N]; same tiling, the tile holds (level*scale)*global
 __global__ void __launch_bounds__(kQThreads) requantize_t_kernel(const uint8_t* __restrict__ wcodes,
                                                                  const uint8_t* __restrict__ wscales,
@@ -592,9 +807,9 @@ static int quantize_rows_typed(const T* x, int64_t rows, int64_t cols, const flo
                                uint8_t* codes, uint8_t* scales, int layout, int device, cudaStream_t st) {
   const RowGeometry geo = row_geometry(rows, cols, device);
   if (seed < 0)
-    quantize_rows_kernel<T, false><<<geo.grid, geo.block, 0, st>>>(x, rows, cols, g, 0u, codes, scales, layout);
+    quantize_rows16_kernel<T, false><<<geo.grid, geo.block, 0, st>>>(x, rows, cols, g, 0u, codes, scales, layout);
   else
-    quantize_rows_kernel<T, true><<<geo.grid, geo.block, 0, st>>>(x, rows, cols, g,
+    quantize_rows16_kernel<T, true><<<geo.grid, geo.block, 0, st>>>(x, rows, cols, g,
                                                                   hash_key(static_cast<uint32_t>(seed), step), codes,
                                                                   scales, layout);
   BL_CUDA(cudaGetLastError());
@@ -637,8 +852,8 @@ static int quantize_t_typed(const T* x, int64_t M, int64_t K, const float* H, in
   const dim3 grid(static_cast<unsigned>((K + kTK - 1) / kTK), static_cast<unsigned>((M + kTM - 1) / kTM));
   const uint32_t key = seed < 0 ? 0u : hash_key(static_cast<uint32_t>(seed), step);
   const bool pairs = K % 2 == 0 && (reinterpret_cast<uintptr_t>(x) % (2 * sizeof(T))) == 0;
-  if (pairs && seed < 0) quantize_t2_kernel<T, false><<<grid, kQThreads, 0, st>>>(x, M, K, H, gout, key, codes, scales, layout);
-  else if (pairs) quantize_t2_kernel<T, true><<<grid, kQThreads, 0, st>>>(x, M, K, H, gout, key, codes, scales, layout);
+  if (pairs && seed < 0) quantize_t3_kernel<T, false><<<grid, kQThreads, 0, st>>>(x, M, K, H, gout, key, codes, scales, layout);
+  else if (pairs) quantize_t3_kernel<T, true><<<grid, kQThreads, 0, st>>>(x, M, K, H, gout, key, codes, scales, layout);
   else if (seed < 0) quantize_t_kernel<T, false><<<grid, kQThreads, 0, st>>>(x, M, K, H, gout, key, codes, scales, layout);
   else quantize_t_kernel<T, true><<<grid, kQThreads, 0, st>>>(x, M, K, H, gout, key, codes, scales, layout);
   BL_CUDA(cudaGetLastError());
