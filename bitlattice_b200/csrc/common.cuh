@@ -272,6 +272,9 @@ __device__ __forceinline__ uint32_t cvt_e2m1x8_merged(const float v[8]) {
 // two folded into the bracket. inv approximates 1 / se to a few ulps; the bracket (1 -+ 2^-19) around it contains the
 // exact quotient, so equal conversions of both ends are the conversion of the quotient, which then is no tie;
 // otherwise (at or next to a midpoint) the exact ladder decides.
+// exact code of one value, out of line: the per-element repair of e2m1_rtn16
+static __device__ __noinline__ uint32_t e2m1_nearest_exact(float v, float se) { return e2m1_code_nearest(v / se); }
+
 __device__ __forceinline__ uint2 e2m1_rtn16(const float v[16], float pre, float se, float inv) {
   const float lo = inv * pre * 0.99999809265136718750f, hi = inv * pre * 1.00000190734863281250f;
   float a[16], b[16];
@@ -280,15 +283,20 @@ __device__ __forceinline__ uint2 e2m1_rtn16(const float v[16], float pre, float 
     mul2(v[i], v[i + 1], lo, a[i], a[i + 1]);
     mul2(v[i], v[i + 1], hi, b[i], b[i + 1]);
   }
-  const uint32_t a0 = cvt_e2m1x8_merged(a), a1 = cvt_e2m1x8_merged(a + 8);
-  const uint32_t b0 = cvt_e2m1x8_merged(b), b1 = cvt_e2m1x8_merged(b + 8);
+  uint32_t w[2] = {cvt_e2m1x8_merged(a), cvt_e2m1x8_merged(a + 8)};
+  uint32_t d[2] = {w[0] ^ cvt_e2m1x8_merged(b), w[1] ^ cvt_e2m1x8_merged(b + 8)};
   // (the reciprocal is only trusted for scales well inside the normal range)
-  if (__builtin_expect(a0 == b0 && a1 == b1 && se > 1e-30f && se < 1e30f, 1))
-    return make_uint2(e2m1_drop_negative_zero(a0), e2m1_drop_negative_zero(a1));
-  return make_uint2(e2m1_nearest_x8_exact(v[0] * pre, v[1] * pre, v[2] * pre, v[3] * pre, v[4] * pre, v[5] * pre,
-                                          v[6] * pre, v[7] * pre, se),
-                    e2m1_nearest_x8_exact(v[8] * pre, v[9] * pre, v[10] * pre, v[11] * pre, v[12] * pre, v[13] * pre,
-                                          v[14] * pre, v[15] * pre, se));
+  if (!(se > 1e-30f && se < 1e30f)) d[0] = d[1] = 0xFFFFFFFFu;
+  if (__builtin_expect((d[0] | d[1]) != 0u, 0)) {
+    // Values at a midpoint between two levels are common with 8-bit inputs and few-bit scales: repair only the
+    // elements whose two conversions differ.
+#pragma unroll
+    for (int i = 0; i < 16; ++i) {
+      const uint32_t m = 0xFu << (4 * (i & 7));
+      if (d[i >> 3] & m) w[i >> 3] = (w[i >> 3] & ~m) | (e2m1_nearest_exact(v[i] * pre, se) << (4 * (i & 7)));
+    }
+  }
+  return make_uint2(e2m1_drop_negative_zero(w[0]), e2m1_drop_negative_zero(w[1]));
 }
 
 // Stochastic-rounding codes of x[i] = v[i] * inv for 16 values (bitlattice/fp4ref.py:71-78), u from hash(idx0 + i).

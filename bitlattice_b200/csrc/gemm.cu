@@ -1118,9 +1118,10 @@ extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int kernel = g_kernel_choice.load(std::memory_order_relaxed);
   if (kernel == BL_GEMM_AUTO) {
-    // the pair kernel needs a full wave of 256 x 256 tiles to pay off; small problems spread better as 128 x 128 tiles
+    // the pair kernel needs most of a wave of 256 x 256 tiles to pay off; small problems spread better as 128 x 128
+    // tiles
     const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
-    kernel = tiles >= sm_count(device) / 2 ? BL_GEMM_PAIR : BL_GEMM_TILE;
+    kernel = tiles >= sm_count(device) / 4 ? BL_GEMM_PAIR : BL_GEMM_TILE;
   }
   if (kernel == BL_GEMM_PAIR) return launch_pair<5, 0>(a_codes, b_codes, args, device, st);
   if (kernel == BL_GEMM_PERSISTENT) return launch_persistent<4, 0>(a_codes, b_codes, args, device, st);
