@@ -161,14 +161,18 @@ __device__ __forceinline__ uint32_t e2m1_code_sr(float v, float u) {
 // quotients: one product and two residual corrections with fused multiply-adds (the sequence compilers emit for an
 // fp32 division, minus the reciprocal and the range checks). The residuals are exact, so the result is the correctly
 // rounded quotient whenever no intermediate leaves the normal range; outside it the plain division is used.
+static __device__ __noinline__ float div_general(float x, float y) { return x / y; }
+
 __device__ __forceinline__ float div_rn(float x, float y, float ry) {
-  float q = x * ry;
-  const float aq = fabsf(q);
-  if (!(aq > 1e-30f && aq < 1e30f)) return x / y;      // zero, tiny, huge or non-finite: the general path
-  float e = fmaf(-y, q, x);
-  q = fmaf(e, ry, q);
+  const float q0 = x * ry;
+  float e = fmaf(-y, q0, x);
+  float q = fmaf(e, ry, q0);
   e = fmaf(-y, q, x);
-  return fmaf(e, ry, q);
+  q = fmaf(e, ry, q);
+  const float aq = fabsf(q0);
+  // zero, tiny, huge or non-finite: the general path, kept out of line so that it costs nothing when not taken
+  if (__builtin_expect(!(aq > 1e-30f && aq < 1e30f), 0)) return div_general(x, y);
+  return q;
 }
 
 // ---------------------------------------------------------------------------------------------- device: fast E2M1

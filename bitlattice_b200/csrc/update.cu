@@ -201,7 +201,7 @@ constexpr float kMagic = 12582912.0f;     // 1.5 * 2^23: adding it leaves the in
 
 // DIR: 0 = D given as fp32, 1 = raw, 2 = sign, 3 = colnorm (the gradient is read as GT)
 template <int PCB, int DIR, typename GT>
-__global__ void __launch_bounds__(kThreads) update_kernel(uint8_t* __restrict__ codes, uint8_t* __restrict__ phase,
+__global__ void __launch_bounds__(kThreads, 3) update_kernel(uint8_t* __restrict__ codes, uint8_t* __restrict__ phase,
                                                           const uint8_t* scales_in, uint8_t* scales_out,
                                                           const float* __restrict__ global_scale,
                                                           const GT* __restrict__ grad, const float* __restrict__ denom,
