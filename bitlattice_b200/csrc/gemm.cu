@@ -268,17 +268,20 @@ __device__ __forceinline__ void mma_nvf4_if(uint32_t q, uint32_t d_tmem, uint64_
 
 // Scale copies and MMAs of one full k-tile (4 blocks of 64 along K) of a 256-wide tile, from one elected lane.
 //   sf_desc: descriptor of the stage's first A-scale blob; the B-scale blobs follow 2048 and 4096 bytes later
+//   (two 128-row blobs of B scales per k block, whatever the tile width up to 256)
 //   ORDER 0: all copies, then all MMAs; 1: copies of block j right before MMA j; 2: copies one block ahead of the MMAs
-template <int CG, int ORDER>
+template <int CG, int ORDER, int NB = 2>
 __device__ __forceinline__ void issue_k_tile(uint32_t q, uint32_t acc_t, uint32_t sfa_t, uint32_t sfb_t, uint64_t sf_desc,
-                                             uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+                                             uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate,
+                                             uint32_t sfb_first = 0u) {
   auto copies = [&](int j) {
     tmem_copy_scales_if<CG>(q, sfa_t + 4 * j, sf_desc + 32u * j);
-    tmem_copy_scales_if<CG>(q, sfb_t + 8 * j, sf_desc + 128u + 32u * j);
-    tmem_copy_scales_if<CG>(q, sfb_t + 8 * j + 4, sf_desc + 256u + 32u * j);
+    tmem_copy_scales_if<CG>(q, sfb_t + 4 * NB * j, sf_desc + 128u + 32u * j);
+    if constexpr (NB == 2) tmem_copy_scales_if<CG>(q, sfb_t + 8 * j + 4, sf_desc + 256u + 32u * j);
   };
   auto mma = [&](int j) {
-    mma_nvf4_if<CG>(q, acc_t, a_desc + 2u * j, b_desc + 2u * j, idesc, sfa_t + 4 * j, sfb_t + 8 * j,
+    // sfb_first: column, inside the copied blobs, of the tile's first 32 rows of B (tiles that start inside a blob)
+    mma_nvf4_if<CG>(q, acc_t, a_desc + 2u * j, b_desc + 2u * j, idesc, sfa_t + 4 * j, sfb_t + 4 * NB * j + sfb_first,
                     j == 0 ? accumulate : 1u);
   };
   if constexpr (ORDER == 0) {
@@ -745,23 +748,32 @@ __device__ __forceinline__ void tma_pair_load_3d_if(uint32_t q, uint32_t dst, co
       : "memory");
 }
 
-template <int STAGES>
+// BN = 256 (the one in use): one accumulator of 256 columns; a second one plus the scale columns would not fit the 512
+// columns of tensor memory, so a tile's MMAs wait for the epilogue of the tile before it. The kernel is written for
+// narrower tiles with two accumulators as well (BN = 192: a 192-row tile of B starts at row 0 or 64 of a 128-row
+// scale blob, so the MMA is pointed two columns into the copied blobs for odd tiles; BN = 128: one blob). Both gave
+// the same bits but were slower on B200 and are not instantiated: an MMA of N = 192 takes as long as one of N = 256
+// (3.9 PFLOP/s against 4.6-5.1), and 256 x 128 tiles are bound by L2 -> shared-memory traffic (3.1 PFLOP/s).
+template <int BN, int STAGES>
 struct PairSmem {
   static constexpr uint32_t kA = 128 * (kBK / 2);       // this CTA's 128 rows of A
-  static constexpr uint32_t kB = 128 * (kBK / 2);       // this CTA's 128 rows of B
+  static constexpr uint32_t kB = (BN / 2) * (kBK / 2);  // this CTA's half of the B tile
   static constexpr uint32_t kSFA = 4 * 512;             // scales of its A rows
-  static constexpr uint32_t kSFB = 2 * 4 * 512;         // scales of all 256 B rows
+  static constexpr int kBlobsB = BN > 128 ? 2 : 1;      // 128-row scale blobs the B tile touches
+  static constexpr uint32_t kSFB = kBlobsB * 4 * 512;
   static constexpr uint32_t kStage = kA + kB + kSFA + kSFB;
   static constexpr uint32_t kTotal = STAGES * kStage + 1024 + 1024;
 };
 
-template <int STAGES, int ORDER>
+template <int BN, int STAGES>
 __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid_constant__ CUtensorMap map_a,
                                                                     const __grid_constant__ CUtensorMap map_b,
                                                                     const __grid_constant__ CUtensorMap map_sfa,
                                                                     const __grid_constant__ CUtensorMap map_sfb,
                                                                     GemmArgs args) {
-  using S = PairSmem<STAGES>;
+  using S = PairSmem<BN, STAGES>;
+  constexpr int NACC = BN == 256 ? 1 : 2;                  // accumulator buffers
+  constexpr int kHalf = BN / 2;                            // columns one epilogue warp drains
   extern __shared__ uint8_t smem_raw[];
   const uint32_t raw_addr = smem_u32(smem_raw);
   const uint32_t base = (raw_addr + 1023u) & ~1023u;
@@ -770,18 +782,19 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
   uint8_t* bars_ptr = base_ptr + STAGES * S::kStage;
   auto full_bar = [&](int s) { return bars + 8u * s; };
   auto empty_bar = [&](int s) { return bars + 8u * (STAGES + s); };
-  const uint32_t acc_full = bars + 8u * (2 * STAGES);
-  const uint32_t acc_empty = bars + 8u * (2 * STAGES + 1);
-  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 8 * (2 * STAGES + 2));
-  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 8 * (2 * STAGES + 2) + 8);
+  auto acc_full = [&](int a) { return bars + 8u * (2 * STAGES + a); };
+  auto acc_empty = [&](int a) { return bars + 8u * (2 * STAGES + 2 + a); };
+  volatile uint32_t* tmem_slot = reinterpret_cast<volatile uint32_t*>(bars_ptr + 8 * (2 * STAGES + 4));
+  volatile int* abort_flag = reinterpret_cast<volatile int*>(bars_ptr + 8 * (2 * STAGES + 4) + 8);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const uint32_t rank = cluster_ctarank();                 // 0: leader (issues the MMAs), 1: peer
   const int pair = blockIdx.x >> 1, num_pairs = gridDim.x >> 1;
-  const int num_tiles = args.num_m * args.num_n;           // 256 x 256 tiles
+  const int num_tiles = args.num_m * args.num_n;           // 256 x BN tiles
   const int num_k_tiles = static_cast<int>((args.K + kBK - 1) / kBK);
   const int nkb = static_cast<int>((args.K + 63) / 64);
-  constexpr uint32_t kTmemCols = 512, kSfaCol = 256, kSfbCol = 272;
+  constexpr uint32_t kTmemCols = 512, kSfaCol = NACC * BN, kSfbCol = kSfaCol + 16;
+  static_assert(kSfbCol + 32 <= kTmemCols, "tensor memory budget");
   constexpr int kCluster = 2;                              // barriers signalled across the pair: cluster-scope acquire
 
   constexpr int kGroup = 8;
@@ -799,8 +812,10 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
       mbar_init(full_bar(s), 1);
       mbar_init(empty_bar(s), 1);
     }
-    mbar_init(acc_full, 1);
-    mbar_init(acc_empty, 16);
+    for (int a = 0; a < 2; ++a) {
+      mbar_init(acc_full(a), 1);
+      mbar_init(acc_empty(a), 16);
+    }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
@@ -829,7 +844,8 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
       int tile_m, tile_n;
       tile_coords(pid, tile_m, tile_n);
       const int rb_a = tile_m * 2 + static_cast<int>(rank);               // 128-row block of A this CTA owns
-      const int row_b = tile_n * 256 + static_cast<int>(rank) * 128;      // its half of the B tile
+      const int row_b = tile_n * BN + static_cast<int>(rank) * (BN / 2);  // its half of the B tile
+      const int blob_b = (tile_n * BN) >> 7;                              // first scale blob the B tile touches
       for (int kt = 0; kt < num_k_tiles; ++kt) {
         ok = __all_sync(0xffffffffu, mbar_wait(empty_bar(s), phase, abort_flag, 1, kCluster));
         if (!ok) break;
@@ -841,7 +857,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
         tma_pair_load_2d_if(q, stage, &map_a, kt * (kBK / 2), rb_a * 128, bar);
         tma_pair_load_2d_if(q, stage + S::kA, &map_b, kt * (kBK / 2), row_b, bar);
         tma_pair_load_3d_if(q, stage + S::kA + S::kB, &map_sfa, 0, kt * 4, rb_a, bar);
-        tma_pair_load_3d_if(q, stage + S::kA + S::kB + S::kSFA, &map_sfb, 0, kt * 4, tile_n * 2, bar);
+        tma_pair_load_3d_if(q, stage + S::kA + S::kB + S::kSFA, &map_sfb, 0, kt * 4, blob_b, bar);
         if (++s == STAGES) {
           s = 0;
           phase ^= 1;
@@ -851,17 +867,22 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
   } else if (warp == 1) {
     if (rank == 0) {
       // ---------------------------------------------------------------- leader: scale copies + MMAs for the pair
-      // E2M1 x E2M1, UE4M3 scales, K-major, N = 256, M = 256 (two CTAs), dense K = 64
-      constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (32u << 17) | (16u << 24);
+      // E2M1 x E2M1, UE4M3 scales, K-major, N = BN, M = 256 (two CTAs), dense K = 64
+      constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (16u << 24);
       const uint32_t empty_peer0 = map_to_cta(empty_bar(0), 1);           // the peer's barriers, 8 bytes apart
-      const uint32_t acc_full_peer = map_to_cta(acc_full, 1);
-      int s = 0;
-      uint32_t phase = 0, acc_phase = 1;
+      const uint32_t acc_full_peer0 = map_to_cta(acc_full(0), 1);
+      int s = 0, ab = 0;
+      uint32_t phase = 0, acc_phases = 3u;                                // bit a: parity to wait for on accumulator a
+                                                                          // (both start out free)
       bool ok = true;
       for (int pid = pair; pid < num_tiles && ok; pid += num_pairs) {
-        ok = __all_sync(0xffffffffu, mbar_wait(acc_empty, acc_phase, abort_flag, 4, kCluster));
+        int tile_m, tile_n;
+        tile_coords(pid, tile_m, tile_n);
+        const uint32_t sfb_first = static_cast<uint32_t>(((tile_n * BN) & 127) >> 5);
+        const uint32_t acc_t = tmem_base + static_cast<uint32_t>(ab * BN);
+        ok = __all_sync(0xffffffffu, mbar_wait(acc_empty(ab), (acc_phases >> ab) & 1u, abort_flag, 4, kCluster));
         if (!ok) break;
-        acc_phase ^= 1;
+        acc_phases ^= 1u << ab;
         tcgen05_fence_after();
         for (int kt = 0; kt < num_k_tiles; ++kt) {
           ok = __all_sync(0xffffffffu, mbar_wait(full_bar(s), phase, abort_flag, 2, kCluster));
@@ -873,55 +894,58 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
           const uint64_t adesc = operand_desc(stage), bdesc = operand_desc(stage + S::kA);
           const uint64_t sdesc = scale_desc(stage + S::kA + S::kB);
           if (blocks == 4) {
-            issue_k_tile<2, ORDER>(q, tmem_base, tmem_base + kSfaCol, tmem_base + kSfbCol, sdesc, adesc, bdesc, idesc,
-                                   kt != 0);
+            issue_k_tile<2, 0, S::kBlobsB>(q, acc_t, tmem_base + kSfaCol, tmem_base + kSfbCol, sdesc, adesc, bdesc, idesc, kt != 0,
+                               sfb_first);
           } else {
             for (int j = 0; j < blocks; ++j) {
               tmem_copy_scales_if<2>(q, tmem_base + kSfaCol + 4 * j, sdesc + 32u * j);
-              tmem_copy_scales_if<2>(q, tmem_base + kSfbCol + 8 * j, sdesc + 128u + 32u * j);
-              tmem_copy_scales_if<2>(q, tmem_base + kSfbCol + 8 * j + 4, sdesc + 256u + 32u * j);
+              tmem_copy_scales_if<2>(q, tmem_base + kSfbCol + 4 * S::kBlobsB * j, sdesc + 128u + 32u * j);
+              if (S::kBlobsB == 2) tmem_copy_scales_if<2>(q, tmem_base + kSfbCol + 8 * j + 4, sdesc + 256u + 32u * j);
             }
             for (int j = 0; j < blocks; ++j)
-              mma_nvf4_if<2>(q, tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
-                             tmem_base + kSfbCol + 8 * j, (kt | j) != 0);
+              mma_nvf4_if<2>(q, acc_t, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
+                             tmem_base + kSfbCol + 4 * S::kBlobsB * j + sfb_first, (kt | j) != 0);
           }
           mma_commit_if<2>(q, empty_bar(s));
           mma_commit_if<2>(q, empty_peer0 + 8u * s);
           if (kt == num_k_tiles - 1) {
-            mma_commit_if<2>(q, acc_full);
-            mma_commit_if<2>(q, acc_full_peer);
+            mma_commit_if<2>(q, acc_full(ab));
+            mma_commit_if<2>(q, acc_full_peer0 + 8u * ab);
           }
           if (++s == STAGES) {
             s = 0;
             phase ^= 1;
           }
         }
+        if (NACC == 2) ab ^= 1;
       }
     }
   } else {
     // ------------------------------------------------------------------ epilogue (both CTAs, own 128 rows)
     const int quarter = warp & 3, half = (warp - 2) >> 2;
     const float alpha = args.a_global[0] * args.b_global[0];
-    const uint32_t acc_empty_leader = map_to_cta(acc_empty, 0);
-    uint32_t acc_phase = 0;
+    const uint32_t acc_empty_leader0 = map_to_cta(acc_empty(0), 0);
+    int ab = 0;
+    uint32_t acc_phases = 0u;
     for (int pid = pair; pid < num_tiles; pid += num_pairs) {
       int tile_m, tile_n;
       tile_coords(pid, tile_m, tile_n);
-      if (!mbar_wait(acc_full, acc_phase, abort_flag, 3, kCluster)) break;
-      acc_phase ^= 1;
+      if (!mbar_wait(acc_full(ab), (acc_phases >> ab) & 1u, abort_flag, 3, kCluster)) break;
+      acc_phases ^= 1u << ab;
       tcgen05_fence_after();
-      uint32_t acc[4][32];
+      uint32_t acc[kHalf / 32][32];
 #pragma unroll
-      for (int i = 0; i < 4; ++i)
-        tmem_load32_async(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + half * 128 + i * 32, acc[i]);
+      for (int i = 0; i < kHalf / 32; ++i)
+        tmem_load32_async(tmem_base + (static_cast<uint32_t>(quarter * 32) << 16) + ab * BN + half * kHalf + i * 32,
+                          acc[i]);
       tmem_load_wait();
       tcgen05_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive_cluster(acc_empty_leader);
+      if (lane == 0) mbar_arrive_cluster(acc_empty_leader0 + 8u * ab);
       const int64_t row = static_cast<int64_t>(tile_m) * 256 + rank * 128 + quarter * 32 + lane;
 #pragma unroll
-      for (int i = 0; i < 4; ++i) {
-        const int64_t col = static_cast<int64_t>(tile_n) * 256 + half * 128 + i * 32;
+      for (int i = 0; i < kHalf / 32; ++i) {
+        const int64_t col = static_cast<int64_t>(tile_n) * BN + half * kHalf + i * 32;
         if (row < args.M && col < args.N) {
           const int64_t left = args.N - col;
           const int valid = left < 32 ? static_cast<int>(left) : 32;
@@ -933,6 +957,7 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
             store_row32(static_cast<float*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
         }
       }
+      if (NACC == 2) ab ^= 1;
     }
   }
   tcgen05_fence_before();
@@ -1031,20 +1056,20 @@ static int launch_persistent(const uint8_t* a_codes, const uint8_t* b_codes, Gem
   return 0;
 }
 
-template <int STAGES, int ORDER>
+template <int BN, int STAGES>
 static int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmArgs args, int device, cudaStream_t st) {
-  using S = PairSmem<STAGES>;
+  using S = PairSmem<BN, STAGES>;
   CUtensorMap map_a, map_b;
   if (int rc = make_operand_map(&map_a, a_codes, args.M, args.K, 128)) return rc;
-  if (int rc = make_operand_map(&map_b, b_codes, args.N, args.K, 128)) return rc;
+  if (int rc = make_operand_map(&map_b, b_codes, args.N, args.K, BN / 2)) return rc;
   CUtensorMap map_sfa, map_sfb;
   if (int rc = make_scale_map(&map_sfa, args.a_sf, args.M, args.K, 1)) return rc;
-  if (int rc = make_scale_map(&map_sfb, args.b_sf, args.N, args.K, 2)) return rc;
+  if (int rc = make_scale_map(&map_sfb, args.b_sf, args.N, args.K, S::kBlobsB)) return rc;
   args.num_m = static_cast<int>((args.M + 255) / 256);
-  args.num_n = static_cast<int>((args.N + 255) / 256);
+  args.num_n = static_cast<int>((args.N + BN - 1) / BN);
   const int64_t tiles = static_cast<int64_t>(args.num_m) * args.num_n;
   BL_REQUIRE(tiles <= 0x3FFFFFFF, "gemm: too many output tiles (%lld)", (long long)tiles);
-  BL_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<STAGES, ORDER>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
+  BL_CUDA(cudaFuncSetAttribute(gemm_pair_kernel<BN, STAGES>, cudaFuncAttributeMaxDynamicSharedMemorySize, S::kTotal));
   cudaLaunchConfig_t cfg = {};
   cfg.gridDim = dim3(sm_count(device) & ~1);
   cfg.blockDim = dim3(kPairThreads);
@@ -1067,16 +1092,15 @@ static int launch_pair(const uint8_t* a_codes, const uint8_t* b_codes, GemmArgs 
     BL_REQUIRE(device >= 0 && device < 64, "gemm: device index %d out of range", device);
     if (resident[device] == 0) {
       int n = 0;
-      BL_CUDA(cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<STAGES, ORDER>, &cfg));
+      BL_CUDA(cudaOccupancyMaxActiveClusters(&n, gemm_pair_kernel<BN, STAGES>, &cfg));
       BL_REQUIRE(n > 0, "gemm: the device cannot hold a cluster of two CTAs of the pair kernel");
       resident[device] = n;
-      if (getenv("BL_GEMM_VERBOSE")) fprintf(stderr, "bitlattice_b200: %d resident CTA pairs on device %d\n", n, device);
     }
     max_pairs = resident[device];
   }
   const unsigned pairs = static_cast<unsigned>(tiles < max_pairs ? tiles : max_pairs);
   cfg.gridDim = dim3(pairs * 2);
-  BL_CUDA(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<STAGES, ORDER>, map_a, map_b, map_sfa, map_sfb, args));
+  BL_CUDA(cudaLaunchKernelEx(&cfg, gemm_pair_kernel<BN, STAGES>, map_a, map_b, map_sfa, map_sfb, args));
   return 0;
 }
 
@@ -1123,7 +1147,7 @@ extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const 
     const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
     kernel = tiles >= sm_count(device) / 4 ? BL_GEMM_PAIR : BL_GEMM_TILE;
   }
-  if (kernel == BL_GEMM_PAIR) return launch_pair<5, 0>(a_codes, b_codes, args, device, st);
+  if (kernel == BL_GEMM_PAIR) return launch_pair<256, 5>(a_codes, b_codes, args, device, st);
   if (kernel == BL_GEMM_PERSISTENT) return launch_persistent<4, 0>(a_codes, b_codes, args, device, st);
   return launch_gemm<128, 3>(a_codes, b_codes, args, st);
 }
