@@ -116,11 +116,33 @@ def _gather_cat(local: torch.Tensor, group, size: int) -> torch.Tensor:
     return out
 
 
+class _PendingTransposed:
+    """The rotated transposed operand of the gathered input while its all-gathers are in flight; ``get`` waits for
+    them (once), permutes the shards into place and re-tiles the scales."""
+
+    def __init__(self, works, codes, scales, g, K, cols):
+        self.works, self.codes, self.scales, self.g, self.K, self.cols = works, codes, scales, g, K, cols
+        self.operand = None
+
+    def get(self):
+        if self.operand is None:
+            from . import _ops, backend
+            for w in self.works:
+                w.wait()
+            # shards are column slices of the transposed operand: [p, K, m] -> [K, p * m]
+            tpf = self.codes.permute(1, 0, 2).reshape(self.K, self.cols // 2)
+            tsf = self.scales.permute(1, 0, 2).reshape(self.K, self.cols // 16)
+            self.operand = backend.Fp4Operand(tpf, _ops.to_blocked(tsf.contiguous()), self.g, True)
+            self.works = self.codes = self.scales = None
+        return self.operand
+
+
 def gathered_input_operands(x_shard: torch.Tensor, group, want_t: bool):
     """NVFP4 GEMM operands of the full input x [M, K] from this rank's token shard [M/p, K] (M/p a multiple of 128):
-    the row operand Q(x) and, if asked, the rotated transposed operand Q(rot(x^T)) for the weight gradient. Codes and
-    scales equal those of the unsharded quantization bit for bit: the per-tensor scale comes from the maximum over all
-    shards, blocks of 16 never straddle shards, and 128-row scale tiles are whole."""
+    the row operand Q(x) and, if asked, the rotated transposed operand Q(rot(x^T)) for the weight gradient, returned as
+    an object whose ``get()`` yields it: its all-gathers run asynchronously, so they overlap the forward GEMMs. Codes
+    and scales equal those of the unsharded quantization bit for bit: the per-tensor scale comes from the maximum over
+    all shards, blocks of 16 never straddle shards, and 128-row scale tiles are whole."""
     from . import _ops, backend
     rank, size = world(group)
     K = x_shard.shape[-1]
@@ -136,10 +158,12 @@ def gathered_input_operands(x_shard: torch.Tensor, group, want_t: bool):
     if want_t:
         tp, ts, tg = _ops.quantize_nvfp4_t(x2, backend._hadamard16(x2.device, torch.float32), -1, 0, g * 4.0,
                                            blocked=False)
-        # shards are column slices of the transposed operand: [p, K, m] -> [K, p * m]
-        tpf = _gather_cat(tp, group, size).permute(1, 0, 2).reshape(K, size * rows // 2)
-        tsf = _gather_cat(ts.view(torch.uint8), group, size).permute(1, 0, 2).reshape(K, size * rows // 16)
-        xt = backend.Fp4Operand(tpf, _ops.to_blocked(tsf.contiguous()), tg, True)
+        ts = ts.view(torch.uint8)
+        codes = torch.empty(size, *tp.shape, dtype=tp.dtype, device=tp.device)
+        scales = torch.empty(size, *ts.shape, dtype=ts.dtype, device=ts.device)
+        works = [dist.all_gather_into_tensor(codes, tp, group=group, async_op=True),
+                 dist.all_gather_into_tensor(scales, ts.contiguous(), group=group, async_op=True)]
+        xt = _PendingTransposed(works, codes, scales, tg, K, size * rows)
     return xq, xt
 
 
@@ -186,7 +210,7 @@ class ColumnParallelFp4Linear(torch.autograd.Function):
             if st is None or not ctx.needs_input_grad[3 + i] or ctx.xt is None:
                 gws.append(None)
                 continue
-            gws.append(backend.fp4_wgrad(st[0], st[1], ctx.xt, w, ctx.recipe).to(w.dtype))
+            gws.append(backend.fp4_wgrad(st[0], st[1], ctx.xt.get(), w, ctx.recipe).to(w.dtype))
         if work is not None:
             work.wait()
             gx_out = gx_out.reshape(shape)

@@ -42,7 +42,7 @@ def main():
     # operands
     xq, xt = gathered_input_operands(x[rows].contiguous(), None, True)
     ref_q, ref_t = backend._input_operands(x, backend.Fp4Recipe())
-    for got, ref in ((xq, ref_q), (xt, ref_t)):
+    for got, ref in ((xq, ref_q), (xt.get(), ref_t)):
         assert torch.equal(got.packed, ref.packed), "codes differ from the unsharded quantization"
         assert torch.equal(got.scales.view(torch.uint8).reshape(-1), ref.scales.view(torch.uint8).reshape(-1))
         assert torch.equal(got.global_scale, ref.global_scale)
