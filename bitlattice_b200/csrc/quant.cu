@@ -86,20 +86,6 @@ __device__ __forceinline__ uint32_t quantize_half_block(const float v[8], float 
   return out;
 }
 
-// the reference kernel's own block rule for W^T (csrc/act_quant.cu:66-86): scale amax/6/g, s > 0 ? v/s : 0
-__device__ __forceinline__ uint32_t requantize_half_block(const float v[8], float g, float rg, uint32_t* scale) {
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 8; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  amax = fmaxf(amax, __shfl_xor_sync(0xffffffffu, amax, 1));
-  const uint32_t sb = e4m3_encode(div_rn(div_rn(amax, 6.0f, kInv6), g, rg));
-  const float s = e4m3_decode(sb) * g;
-  *scale = sb;
-  if (!(s > 0.0f)) return 0u;
-  const float inv = __frcp_rn(s);
-  return e2m1_nearest_x8(v, s, inv * 0.99999904632568359375f, inv * 1.00000095367431640625f);
-}
-
 __device__ __forceinline__ int64_t scale_index(int layout, int64_t r, int64_t c16, int64_t cols16) {
   if (layout == BL_SF_ROWMAJOR) return r * cols16 + c16;
   const int64_t nc = (cols16 + 3) >> 2;
@@ -108,80 +94,9 @@ __device__ __forceinline__ int64_t scale_index(int layout, int64_t r, int64_t c1
 
 // ------------------------------------------------------------------------------------------------ rows
 
-// x [rows, cols] -> codes [rows, cols/2], scales; one thread per 8 elements, lane pairs share a block. Every thread
-// has kRowsUnroll independent chunks in flight (their loads are issued before any arithmetic).
+// x [rows, cols] -> codes [rows, cols/2], scales. Every thread has kRowsUnroll independent blocks in flight (their
+// loads are issued before any arithmetic).
 constexpr int kRowsUnroll = 2;
-
-template <typename T>
-struct Raw8 {                                        // 8 elements as loaded
-  uint4 a, b;                                        // b only for 4-byte types
-};
-
-template <typename T>
-__device__ __forceinline__ void load_raw8(const T* p, Raw8<T>& r) {
-  r.a = __ldcs(reinterpret_cast<const uint4*>(p));
-  if constexpr (sizeof(T) == 4) r.b = __ldcs(reinterpret_cast<const uint4*>(p) + 1);
-}
-
-template <typename T>
-__device__ __forceinline__ void unpack_raw8(const Raw8<T>& r, float v[8]) {
-  if constexpr (sizeof(T) == 4) {
-    v[0] = __uint_as_float(r.a.x); v[1] = __uint_as_float(r.a.y); v[2] = __uint_as_float(r.a.z); v[3] = __uint_as_float(r.a.w);
-    v[4] = __uint_as_float(r.b.x); v[5] = __uint_as_float(r.b.y); v[6] = __uint_as_float(r.b.z); v[7] = __uint_as_float(r.b.w);
-  } else if constexpr (std::is_same<T, __nv_bfloat16>::value) {
-    const uint32_t w[4] = {r.a.x, r.a.y, r.a.z, r.a.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      v[2 * i] = __uint_as_float(w[i] << 16);
-      v[2 * i + 1] = __uint_as_float(w[i] & 0xFFFF0000u);
-    }
-  } else {
-    const __half2* h = reinterpret_cast<const __half2*>(&r.a);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const float2 f = __half22float2(h[i]);
-      v[2 * i] = f.x;
-      v[2 * i + 1] = f.y;
-    }
-  }
-}
-
-// block (bx, 256/bx): x covers 8-element chunks of a row (bx a power of two >= 32: a warp stays inside one row), y
-// covers rows; a thread keeps its columns and walks down the rows, kRowsUnroll rows in flight.
-template <typename T, bool SR>
-__global__ void __launch_bounds__(kQThreads, 5) quantize_rows_kernel(const T* __restrict__ x, int64_t rows, int64_t cols,
-                                                                  const float* __restrict__ global, uint32_t key,
-                                                                  uint8_t* __restrict__ codes,
-                                                                  uint8_t* __restrict__ scales, int layout) {
-  const float g = global[0];
-  const float rg = __frcp_rn(g);
-  const int64_t cc = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;
-  const bool in_row = cc * 8 < cols;               // cols is a multiple of 16: lane pairs are in or out together
-  const int64_t row_step = static_cast<int64_t>(gridDim.y) * blockDim.y;
-  const int64_t cols16 = cols / 16, cols2 = cols / 2;
-  for (int64_t r0 = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; r0 < rows;
-       r0 += row_step * kRowsUnroll) {
-    Raw8<T> raw[kRowsUnroll];
-#pragma unroll
-    for (int u = 0; u < kRowsUnroll; ++u) {
-      const int64_t r = r0 + u * row_step;
-      if (in_row && r < rows) load_raw8(x + r * cols + cc * 8, raw[u]);
-      else raw[u].a = raw[u].b = make_uint4(0u, 0u, 0u, 0u);
-    }
-#pragma unroll
-    for (int u = 0; u < kRowsUnroll; ++u) {
-      const int64_t r = r0 + u * row_step;
-      if (r >= rows) break;                        // uniform over the warp (one row per warp)
-      float v[8];
-      unpack_raw8(raw[u], v);
-      uint32_t sb;
-      const uint32_t out = quantize_half_block<SR>(v, g, rg, key, static_cast<uint32_t>(r * cols + cc * 8), &sb);
-      if (!in_row) continue;
-      __stcs(reinterpret_cast<uint32_t*>(codes + r * cols2) + cc, out);
-      if ((threadIdx.x & 1) == 0) scales[scale_index(layout, r, cc >> 1, cols16)] = static_cast<uint8_t>(sb);
-    }
-  }
-}
 
 // ---- rows, one thread per block of 16 ---------------------------------------------------------------------------------
 
@@ -409,8 +324,6 @@ __global__ void __launch_bounds__(kQThreads) quantize_t_kernel(const T* __restri
 }
 
 // ---- transposed quantizer, one thread per (block of 16 rows, pair of adjacent columns) ------------------------------
-// Adjacent lanes read adjacent column pairs, so every row of the tile is read as full 128-byte lines; codes and
-// scales of the 64 x 128 tile are staged in shared memory and written out as rows of the transposed result.
 
 template <typename T>
 __device__ __forceinline__ void load2(const T* p, float& a, float& b) {
@@ -426,143 +339,6 @@ __device__ __forceinline__ void load2(const T* p, float& a, float& b) {
     const float2 v = __half22float2(*reinterpret_cast<const __half2*>(p));
     a = v.x;
     b = v.y;
-  }
-}
-
-// Exponent spread (in bits) up to which every partial sum of +-raw[i]/4 over 16 inputs is exact in fp32, so that any
-// summation order gives the reference's sequential result: inputs with p significant bits and exponents within
-// [emin, emax] are multiples of 2^(emin - p - 1) and their partial sums stay below 2^(emax + 3).
-template <typename T> struct ExactSpread { static constexpr int value = -1000; };          // fp32 input: never
-template <> struct ExactSpread<__nv_bfloat16> { static constexpr int value = 11; };        // 8 significant bits
-template <> struct ExactSpread<__half> { static constexpr int value = 8; };                // 11 significant bits
-
-// v <- raw H for H = diag(s) * Sylvester-Hadamard / 4. Fast path (exact, hence order-free): sign flips, four
-// butterfly stages, one scaling. Otherwise the reference order: for each output the ascending sum over the inputs.
-template <int SPREAD>
-__device__ __forceinline__ void rotate16(const float raw[16], const float* __restrict__ sH, bool structured,
-                                         float v[16]) {
-  uint32_t mx = 0u, mn = 0x7FFFFFFFu;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) {
-    const uint32_t b = __float_as_uint(raw[i]) & 0x7FFFFFFFu;
-    mx = max(mx, b);
-    mn = min(mn, b ? b : 0x7FFFFFFFu);
-  }
-  const int spread = static_cast<int>(mx >> 23) - static_cast<int>(mn >> 23);
-  if (structured && spread <= SPREAD && (mn >> 23) != 0u) {
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = sH[i * 16] < 0.0f ? -raw[i] : raw[i];
-#pragma unroll
-    for (int len = 1; len < 16; len <<= 1) {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) {
-        if ((i & len) == 0) {
-          const float a = v[i], b = v[i + len];
-          v[i] = a + b;
-          v[i + len] = a - b;
-        }
-      }
-    }
-#pragma unroll
-    for (int i = 0; i < 16; ++i) v[i] = v[i] * 0.25f;
-  } else {
-#pragma unroll
-    for (int j = 0; j < 16; ++j) {
-      float a = 0.0f;
-#pragma unroll
-      for (int i = 0; i < 16; ++i) a = a + raw[i] * sH[i * 16 + j];
-      v[j] = a;
-    }
-  }
-}
-
-// one whole block of 16 values -> 16 codes and the scale byte
-template <bool SR>
-__device__ __forceinline__ uint2 quantize_block16(const float v[16], float g, float rg, uint32_t key,
-                                                  uint32_t idx0, uint32_t* scale) {
-  float amax = 0.0f;
-#pragma unroll
-  for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
-  uint2 out;
-  if constexpr (!SR) {
-    const uint32_t sb = e4m3_encode(div_rn(fmaxf(div_rn(amax, 6.0f, kInv6), 1e-12f), g, rg));
-    const float se = e4m3_decode(sb) * g;
-    const float inv = __frcp_rn(se);
-    const float lo = inv * 0.99999904632568359375f, hi = inv * 1.00000095367431640625f;
-    out.x = e2m1_nearest_x8(v, se, lo, hi);
-    out.y = e2m1_nearest_x8(v + 8, se, lo, hi);
-    *scale = sb;
-  } else {
-    const uint32_t sb = e4m3_encode(div_rn(div_rn(amax, 6.0f, kInv6), g, rg));
-    const float t = e4m3_decode(sb) * g;
-    const float inv = t > 0.0f ? __frcp_rn(t) : 0.0f;
-    out.x = e2m1_sr_x8(v, inv, key, idx0);
-    out.y = e2m1_sr_x8(v + 8, inv, key, idx0 + 8);
-    *scale = sb;
-  }
-  return out;
-}
-
-template <typename T, bool SR>
-__global__ void __launch_bounds__(kQThreads, 4) quantize_t2_kernel(const T* __restrict__ x, int64_t M, int64_t K,
-                                                                const float* __restrict__ H,
-                                                                const float* __restrict__ global, uint32_t key,
-                                                                uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
-                                                                int layout) {
-  __shared__ uint2 s_codes[kTK][kTM / 16 + 1];
-  __shared__ uint8_t s_scales[kTK][kTM / 16];
-  __shared__ float sH[256];
-  bool structured = false;
-  if (H != nullptr) {
-    sH[threadIdx.x] = H[threadIdx.x];
-    __syncthreads();
-    const int i = threadIdx.x >> 4, j = threadIdx.x & 15;
-    const float si = sH[i * 16];
-    const float expect = (__popc(i & j) & 1) ? -si : si;
-    structured = __syncthreads_and(fabsf(si) == 0.25f && sH[threadIdx.x] == expect) != 0;
-  }
-  const int64_t m0 = static_cast<int64_t>(blockIdx.y) * kTM, k0 = static_cast<int64_t>(blockIdx.x) * kTK;
-  const int kp = threadIdx.x & 31, mb = threadIdx.x >> 5;
-  const int64_t k = k0 + 2 * kp, m = m0 + mb * 16;
-  const bool active = k < K && m < M;                   // K is even and M a multiple of 16
-  if (active) {
-    float ra[16], rb[16];
-    const T* p = x + m * K + k;
-#pragma unroll
-    for (int i = 0; i < 16; ++i) load2(p + i * K, ra[i], rb[i]);
-    const float g = global[0];
-    const float rg = __frcp_rn(g);
-    float v[16];
-    uint32_t sb;
-    if (H != nullptr) rotate16<ExactSpread<T>::value>(ra, sH, structured, v);
-    else {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = ra[i];
-    }
-    s_codes[2 * kp][mb] = quantize_block16<SR>(v, g, rg, key, static_cast<uint32_t>(static_cast<uint64_t>(k) * M + m), &sb);
-    s_scales[2 * kp][mb] = static_cast<uint8_t>(sb);
-    if (H != nullptr) rotate16<ExactSpread<T>::value>(rb, sH, structured, v);
-    else {
-#pragma unroll
-      for (int i = 0; i < 16; ++i) v[i] = rb[i];
-    }
-    s_codes[2 * kp + 1][mb] =
-        quantize_block16<SR>(v, g, rg, key, static_cast<uint32_t>(static_cast<uint64_t>(k + 1) * M + m), &sb);
-    s_scales[2 * kp + 1][mb] = static_cast<uint8_t>(sb);
-  }
-  __syncthreads();
-  // write-out: thread -> (row of the transposed tile, two of its eight blocks)
-  const int row = threadIdx.x >> 2, b0 = (threadIdx.x & 3) * 2;
-  const int64_t kr = k0 + row;
-  if (kr < K) {
-#pragma unroll
-    for (int e = 0; e < 2; ++e) {
-      const int64_t mm = m0 + (b0 + e) * 16;
-      if (mm < M) {
-        *reinterpret_cast<uint2*>(codes + kr * (M / 2) + mm / 2) = s_codes[row][b0 + e];
-        scales[scale_index(layout, kr, mm / 16, M / 16)] = s_scales[row][b0 + e];
-      }
-    }
   }
 }
 
@@ -701,21 +477,29 @@ __global__ void __launch_bounds__(kQThreads) requantize_t_kernel(const uint8_t* 
     }
   }
   __syncthreads();
-  for (int it = 0; it < 4; ++it) {
+  // one thread per (column k of W, block of 16 rows): lanes walk k, so tile reads are conflict-free
+  const float rg = __frcp_rn(g);
+  for (int it = 0; it < 2; ++it) {
     const int w = it * kQThreads + threadIdx.x;
-    const int half = w & 1, kk = (w >> 1) & (kTK - 1), nb = w >> 7;
+    const int kk = w & (kTK - 1), nb = w >> 6;
     const int64_t k = k0 + kk, n = n0 + nb * 16;
-    const bool active = k < K && n < N;
-    float v[8];
+    if (!(k < K && n < N)) continue;
+    float v[16];
+    float amax = 0.0f;
 #pragma unroll
-    for (int i = 0; i < 8; ++i) v[i] = tile[nb * 16 + half * 8 + i][kk];
-    uint32_t sb;
-    const uint32_t out = requantize_half_block(v, g, __frcp_rn(g), &sb);
-    if (!active) continue;
-    *reinterpret_cast<uint32_t*>(codes + k * (N / 2) + (n + half * 8) / 2) = out;
-    if (half == 0) scales[scale_index(layout, k, n / 16, N / 16)] = static_cast<uint8_t>(sb);
+    for (int i = 0; i < 16; ++i) {
+      v[i] = tile[nb * 16 + i][kk];
+      amax = fmaxf(amax, fabsf(v[i]));
+    }
+    // the reference kernel's own block rule for W^T (csrc/act_quant.cu:66-86): scale amax/6/g, s > 0 ? v/s : 0
+    const uint32_t sb = e4m3_encode(div_rn(div_rn(amax, 6.0f, kInv6), g, rg));
+    const float se = e4m3_decode(sb) * g;
+    const uint2 out = se > 0.0f ? e2m1_rtn16(v, 1.0f, se, rcp_approx(se)) : make_uint2(0u, 0u);
+    *reinterpret_cast<uint2*>(codes + k * (N / 2) + n / 2) = out;
+    scales[scale_index(layout, k, n / 16, N / 16)] = static_cast<uint8_t>(sb);
   }
 }
+
 
 // ------------------------------------------------------------------------------------------------ dequantize, layout
 
