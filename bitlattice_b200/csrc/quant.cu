@@ -384,7 +384,7 @@ __device__ __forceinline__ void rotate16_generic(const float raw[16], const floa
 // pairs, so every row of the tile is read as full 128-byte lines; codes and scales of the 64 x 128 tile are staged in
 // shared memory and written out as rows of the transposed result.
 template <typename T, bool SR>
-__global__ void __launch_bounds__(kQThreads, 3) quantize_t3_kernel(const T* __restrict__ x, int64_t M, int64_t K,
+__global__ void __launch_bounds__(kQThreads, 4) quantize_t3_kernel(const T* __restrict__ x, int64_t M, int64_t K,
                                                                 const float* __restrict__ H,
                                                                 const float* __restrict__ global, uint32_t key,
                                                                 uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
