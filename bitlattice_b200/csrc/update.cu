@@ -200,7 +200,8 @@ __device__ __forceinline__ float rcp_pow2(float x) { return __uint_as_float(0x7F
 constexpr float kMagic = 12582912.0f;     // 1.5 * 2^23: adding it leaves the integer part in the low mantissa bits
 
 // DIR: 0 = D given as fp32, 1 = raw, 2 = sign, 3 = colnorm (the gradient is read as GT)
-template <int PCB, int DIR, typename GT>
+// SRMODE: the rounding mode is known to be 'sr' (the draw needs no mode switch)
+template <int PCB, int DIR, typename GT, bool SRMODE>
 __global__ void __launch_bounds__(kThreads, 3) update_kernel(uint8_t* __restrict__ codes, uint8_t* __restrict__ phase,
                                                           const uint8_t* scales_in, uint8_t* scales_out,
                                                           const float* __restrict__ global_scale,
@@ -224,6 +225,19 @@ __global__ void __launch_bounds__(kThreads, 3) update_kernel(uint8_t* __restrict
       }
       lut[e] = make_float2(av, lam);
     }
+  }
+  // by code nibble: the level w, half / (half the distance to the next level above / below) -- 0 at the ends of the
+  // lattice -- and the next level above: (t - w) times one of the two factors is the phase coordinate of a target t
+  // whose nearest level is w
+  __shared__ float4 plut[16];
+  if (threadIdx.y * blockDim.x + threadIdx.x < 16) {
+    const int c = threadIdx.y * blockDim.x + threadIdx.x;
+    const int rk = rank_of_code(c);
+    const float w = level_of_rank(rk);
+    const float hf = static_cast<float>(1 << (P.pb > 0 ? P.pb - 1 : 0));
+    const float wu = rk < 14 ? level_of_rank(rk + 1) : w, wd = rk > 0 ? level_of_rank(rk - 1) : w;
+    const float su = rk < 14 ? hf / ((wu - w) * 0.5f) : 0.0f, sd = rk > 0 ? hf / ((w - wd) * 0.5f) : 0.0f;
+    plut[c] = make_float4(w, su, sd, wu);
   }
   __syncthreads();
 
@@ -320,36 +334,35 @@ __global__ void __launch_bounds__(kThreads, 3) update_kernel(uint8_t* __restrict
         t = fminf(fmaxf(t, -6.0f), 6.0f);
         fin[e] = t;
       }
-      // nearest levels of the pair through the hardware conversion and back
+      // nearest levels of the pair through the hardware conversion (ties to even: see the notes above)
       const uint32_t near2 = cvt_e2m1x2(fin[1], fin[0]);
-      float w2[2];
-      {
-        uint32_t h2;
-        asm("{\n\t.reg .b8 b;\n\tcvt.u8.u32 b, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b;\n\t}" : "=r"(h2) : "r"(near2));
-        const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
-        w2[0] = f.x;
-        w2[1] = f.y;
-      }
 #pragma unroll
       for (int e = 0; e < 2; ++e) {
-        const float t = fin[e], w = w2[e];
-        const float u = rounding_u(P.rp, idx0 + i + e);
-        const bool up = !(t < w);
-        const float gap = level_gap(w, up);
+        const float t = fin[e];
+        const float u = SRMODE ? hash_uniform(idx0 + i + e, P.rp.key) : rounding_u(P.rp, idx0 + i + e);
         float out;
         if (PCB == 0) {
+          float w;
+          {
+            uint32_t h2;
+            asm("{\n\t.reg .b8 b;\n\tcvt.u8.u32 b, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b;\n\t}" : "=r"(h2) : "r"(near2));
+            const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+            w = e == 0 ? f.x : f.y;
+          }
+          const bool up = !(t < w);
+          const float gap = level_gap(w, up);
           const float a = up ? w : w - gap;
           const float p = gap > 0.0f ? (t - a) * rcp_pow2(gap) : 0.0f;
           out = (u < p) ? a + gap : a;
         } else {
-          const float width = gap * 0.5f;
-          const float c = width > 0.0f ? (t - w) * rcp_pow2(width) : 0.0f;
-          const float q = c * half;
+          const float4 L = plut[(near2 >> (4 * e)) & 15u];
+          const float q = (t - L.x) * (t < L.x ? L.z : L.y);       // phase coordinate times half; exact scaling
           const float flm = __fadd_rd(q, kMagic);                  // kMagic + floor(q), exact
-          const float fr = q - (flm - kMagic);
-          uint32_t k = __float_as_uint(flm) + ((u < fr) ? 1u : 0u);   // low bits: floor(q) + carry-in, two's complement
-          const bool carry = ((flm - kMagic) + ((u < fr) ? 1.0f : 0.0f)) >= half;
-          out = carry ? w + gap : w;                               // a carry implies gap > 0 (not the top level)
+          const float flo = flm - kMagic;
+          const bool ci = u < q - flo;
+          uint32_t k = __float_as_uint(flm) + (ci ? 1u : 0u);      // low bits: floor(q) + carry-in, two's complement
+          const bool carry = flo + (ci ? 1.0f : 0.0f) >= half;
+          out = carry ? L.w : L.x;                                 // a carry implies a level above (not the top one)
           if (carry) k = static_cast<uint32_t>(-static_cast<int>(half));
           phase_put<PCB>(pout, i + e, k & pmask);
         }
@@ -453,17 +466,27 @@ static StepParams make_params(double lr, double decay, int pb, int rule, double 
   return P;
 }
 
+template <int DIR, typename GT, bool SRMODE>
+static void launch_update_mode(int pcb, const Geometry& g, cudaStream_t st, uint8_t* codes, uint8_t* phase,
+                               const uint8_t* sin, uint8_t* sout, const float* gs, const GT* grad, const float* denom,
+                               const float* stats, int64_t rows, int64_t cols, const StepParams& P) {
+  switch (pcb) {
+    case 0: update_kernel<0, DIR, GT, SRMODE><<<g.grid, g.block, 0, st>>>(codes, phase, sin, sout, gs, grad, denom, stats, rows, cols, P); break;
+    case 1: update_kernel<1, DIR, GT, SRMODE><<<g.grid, g.block, 0, st>>>(codes, phase, sin, sout, gs, grad, denom, stats, rows, cols, P); break;
+    case 2: update_kernel<2, DIR, GT, SRMODE><<<g.grid, g.block, 0, st>>>(codes, phase, sin, sout, gs, grad, denom, stats, rows, cols, P); break;
+    case 4: update_kernel<4, DIR, GT, SRMODE><<<g.grid, g.block, 0, st>>>(codes, phase, sin, sout, gs, grad, denom, stats, rows, cols, P); break;
+    default: update_kernel<8, DIR, GT, SRMODE><<<g.grid, g.block, 0, st>>>(codes, phase, sin, sout, gs, grad, denom, stats, rows, cols, P); break;
+  }
+}
+
 template <int DIR, typename GT>
 static void launch_update(int pcb, const Geometry& g, cudaStream_t st, uint8_t* codes, uint8_t* phase,
                           const uint8_t* sin, uint8_t* sout, const float* gs, const GT* grad, const float* denom,
                           const float* stats, int64_t rows, int64_t cols, const StepParams& P) {
-  switch (pcb) {
-    case 0: update_kernel<0, DIR, GT><<<g.grid, g.block, 0, st>>>(codes, phase, sin, sout, gs, grad, denom, stats, rows, cols, P); break;
-    case 1: update_kernel<1, DIR, GT><<<g.grid, g.block, 0, st>>>(codes, phase, sin, sout, gs, grad, denom, stats, rows, cols, P); break;
-    case 2: update_kernel<2, DIR, GT><<<g.grid, g.block, 0, st>>>(codes, phase, sin, sout, gs, grad, denom, stats, rows, cols, P); break;
-    case 4: update_kernel<4, DIR, GT><<<g.grid, g.block, 0, st>>>(codes, phase, sin, sout, gs, grad, denom, stats, rows, cols, P); break;
-    default: update_kernel<8, DIR, GT><<<g.grid, g.block, 0, st>>>(codes, phase, sin, sout, gs, grad, denom, stats, rows, cols, P); break;
-  }
+  if (P.rp.mode == BL_ROUND_SR)
+    launch_update_mode<DIR, GT, true>(pcb, g, st, codes, phase, sin, sout, gs, grad, denom, stats, rows, cols, P);
+  else
+    launch_update_mode<DIR, GT, false>(pcb, g, st, codes, phase, sin, sout, gs, grad, denom, stats, rows, cols, P);
 }
 
 // column statistics + finalize into scratch; returns pointers for the consumer kernel
