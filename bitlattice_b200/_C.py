@@ -51,6 +51,9 @@ _SIGNATURES = {
                                  _c.c_int64, _c.c_int, _P]),
     "bl_nvfp4_gemm_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.c_int]),
     "bl_nvfp4_gemm_select": (_c.c_int, [_c.c_int]),
+    "bl_swiglu_fwd": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int, _c.c_void_p]),
+    "bl_swiglu_bwd": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64,
+                                  _c.c_int, _c.c_void_p]),
     "bl_selftest_division": (_c.c_int, [_c.c_uint64, _c.c_uint32, _c.POINTER(_c.c_uint64), _c.c_int]),
 }
 
@@ -100,7 +103,8 @@ def check(status: int) -> None:
 KERNELS_PER_CALL = {"bl_nvfp4_step_quantized": 1, "bl_nvfp4_lattice_update": 1,
                     "bl_nvfp4_lattice_update_fixed_scratch": 1, "bl_direction": 1,
                     "bl_nvfp4_dequantize": 1, "bl_nvfp4_amax": 1, "bl_nvfp4_quantize": 1, "bl_nvfp4_quantize_t": 2,
-                    "bl_nvfp4_requantize_t": 1, "bl_nvfp4_scales_to_blocked": 1, "bl_nvfp4_gemm": 1}
+                    "bl_nvfp4_requantize_t": 1, "bl_nvfp4_scales_to_blocked": 1, "bl_nvfp4_gemm": 1,
+                    "bl_swiglu_fwd": 1, "bl_swiglu_bwd": 1}
 
 
 class Counters:

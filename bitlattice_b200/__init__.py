@@ -21,9 +21,10 @@ from .compute_policy import PRESETS as COMPUTE_PRESETS  # noqa: E402
 from .compute_policy import Compute, compute  # noqa: E402
 from .formats import Format, TableFormat  # noqa: E402
 from .optim import Lattice  # noqa: E402
+from .swiglu import swiglu  # noqa: E402
 from .tensor import LatticeTensor, is_lattice  # noqa: E402
 
 __version__ = "0.1.0"
 
 __all__ = ["COMPUTE_PRESETS", "HAVE_EXT", "Compute", "Format", "Lattice", "LatticeTensor", "TableFormat", "backend",
-           "compute", "formats", "is_lattice", "optim", "packing", "parallel"]
+           "compute", "formats", "is_lattice", "optim", "packing", "parallel", "swiglu"]

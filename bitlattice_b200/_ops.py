@@ -302,6 +302,34 @@ def nvfp4_gemm(a_packed, a_sf, a_global, b_packed, b_sf, b_global, out_dtype=tor
     return out
 
 
+def swiglu_fwd(g: torch.Tensor, u: torch.Tensor) -> torch.Tensor:
+    """a = T(T(silu(g)) * u), the bits of ``F.silu(g) * u`` under autograd (reference:
+    torch.ops.bitlattice.swiglu_fwd)."""
+    _require(g, "g")
+    _require(u, "u", g.dtype)
+    if g.dtype not in (torch.bfloat16, torch.float16) or g.shape != u.shape:
+        raise RuntimeError("swiglu: g and u must be bf16 or fp16 tensors of one shape")
+    a = torch.empty_like(g)
+    if g.numel():
+        _C.call("bl_swiglu_fwd", _C.ptr(g), _C.ptr(u), _C.ptr(a), _C.DTYPE[g.dtype], g.numel(), _C.device_of(g),
+                _C.stream_of(g))
+    return a
+
+
+def swiglu_bwd(g: torch.Tensor, u: torch.Tensor, da: torch.Tensor):
+    """(dg, du) of swiglu_fwd for the upstream gradient ``da`` (reference: torch.ops.bitlattice.swiglu_bwd)."""
+    _require(g, "g")
+    _require(u, "u", g.dtype)
+    _require(da, "da", g.dtype)
+    if g.dtype not in (torch.bfloat16, torch.float16) or g.shape != u.shape or g.shape != da.shape:
+        raise RuntimeError("swiglu: g, u and da must be bf16 or fp16 tensors of one shape")
+    dg, du = torch.empty_like(g), torch.empty_like(g)
+    if g.numel():
+        _C.call("bl_swiglu_bwd", _C.ptr(g), _C.ptr(u), _C.ptr(da), _C.ptr(dg), _C.ptr(du), _C.DTYPE[g.dtype], g.numel(),
+                _C.device_of(g), _C.stream_of(g))
+    return dg, du
+
+
 GEMM_KERNELS = {"auto": 0, "tile": 1, "persistent": 2, "pair": 3}
 
 

@@ -2,7 +2,7 @@
 
     python bitlattice_b200/csrc/build.py [--force] [--verbose]
 
-The kernels that must reproduce the reference's fp32 rounding bit for bit (update.cu, quant.cu) are compiled with
+The kernels that must reproduce the reference's fp32 rounding bit for bit (update.cu, quant.cu, swiglu.cu) are compiled with
 --fmad=false, as the reference's extension is (its setup.py:21-22); the GEMM keeps fused multiply-adds.
 """
 from __future__ import annotations
@@ -24,6 +24,7 @@ SOURCES = {
     "update.cu": ["--fmad=false"],
     "quant.cu": ["--fmad=false"],
     "gemm.cu": [],
+    "swiglu.cu": ["--fmad=false"],
 }
 
 

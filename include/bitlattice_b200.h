@@ -168,6 +168,16 @@ BL_API int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const floa
  * (0: none) in *status and clears it. No counterpart in the reference (cuBLASLt reports nothing of the kind). */
 BL_API int bl_nvfp4_gemm_status(int* status, int device);
 
+/* SwiGLU glue between the gate/up and the down projection, every intermediate rounded to the activation type as
+ * PyTorch autograd rounds F.silu(g) * u. Replaces torch.ops.bitlattice.swiglu_fwd / swiglu_bwd
+ * (csrc/bindings.cpp:126-129, csrc/swiglu.cu:20-80):
+ *   forward   a  = T(T(silu(g)) * u)
+ *   backward  du = T(da * T(silu(g))),  dg = T(T(da * u) * sig * (1 + g * (1 - sig))),  sig = 1 / (1 + exp(-g))
+ * g, u, da, a, dg, du: n contiguous elements of dtype BL_BF16 or BL_F16, 16-byte aligned. */
+BL_API int bl_swiglu_fwd(const void* g, const void* u, void* a, int dtype, int64_t n, int device, bl_stream_t stream);
+BL_API int bl_swiglu_bwd(const void* g, const void* u, const void* da, void* dg, void* du, int dtype, int64_t n,
+                  int device, bl_stream_t stream);
+
 /* bl_nvfp4_gemm picks among three kernels by problem size: 128 x 128 tiles, one CTA per tile (small problems);
  * persistent 128 x 256 tiles, one CTA per SM; persistent 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2), the
  * fastest on problems with at least a quarter as many such tiles as SMs. All give bit-identical results. This call forces
