@@ -1142,10 +1142,15 @@ extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const 
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int kernel = g_kernel_choice.load(std::memory_order_relaxed);
   if (kernel == BL_GEMM_AUTO) {
-    // the pair kernel needs most of a wave of 256 x 256 tiles to pay off; small problems spread better as 128 x 128
-    // tiles
+    // Measured on B200: the pair kernel wins from two waves of 256 x 256 tiles, or from a quarter wave when K is long
+    // enough to amortise its start-up; below that 128 x 256 tiles on single SMs fill the machine better, and small
+    // problems spread best as 128 x 128 tiles.
     const int64_t tiles = ((M + 255) / 256) * ((N + 255) / 256);
-    kernel = tiles >= sm_count(device) / 4 ? BL_GEMM_PAIR : BL_GEMM_TILE;
+    const int64_t tiles_1sm = ((M + 127) / 128) * ((N + 255) / 256);
+    const int sms = sm_count(device);
+    if (tiles >= sms || (tiles >= sms / 4 && K >= 16384)) kernel = BL_GEMM_PAIR;
+    else if (tiles_1sm >= sms / 2) kernel = BL_GEMM_PERSISTENT;
+    else kernel = BL_GEMM_TILE;
   }
   if (kernel == BL_GEMM_PAIR) return launch_pair<256, 5>(a_codes, b_codes, args, device, st);
   if (kernel == BL_GEMM_PERSISTENT) return launch_persistent<4, 0>(a_codes, b_codes, args, device, st);

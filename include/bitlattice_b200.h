@@ -180,7 +180,7 @@ BL_API int bl_swiglu_bwd(const void* g, const void* u, const void* da, void* dg,
 
 /* bl_nvfp4_gemm picks among three kernels by problem size: 128 x 128 tiles, one CTA per tile (small problems);
  * persistent 128 x 256 tiles, one CTA per SM; persistent 256 x 256 tiles on pairs of SMs (tcgen05 cta_group::2), the
- * fastest on problems with at least a quarter as many such tiles as SMs. All give bit-identical results. This call forces
+ * fastest on problems with at least as many such tiles as SMs (a quarter as many when K >= 16384). All give bit-identical results. This call forces
  * one of them for the rest of the process (tests, experiments) or, with BL_GEMM_AUTO, hands the choice back.
  * The environment variable BL_GEMM_KERNEL (same values) sets the initial choice. No counterpart in the reference. */
 enum { BL_GEMM_AUTO = 0, BL_GEMM_TILE = 1, BL_GEMM_PERSISTENT = 2, BL_GEMM_PAIR = 3 };
