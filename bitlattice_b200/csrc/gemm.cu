@@ -498,8 +498,11 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_kernel(const __grid_constan
 //   quarter, each taking one 128-column half of the accumulator)
 constexpr int kPersistThreads = 320;
 
+// The "accumulator drained" arrivals carry no data through memory (tensor-memory reads are ordered by
+// tcgen05.wait::ld and the tcgen05 fences on both sides), so they are relaxed: a release would first wait for the
+// epilogue's outstanding global stores of the previous tile, about a microsecond per tile.
 __device__ __forceinline__ void mbar_arrive(uint32_t bar) {
-  asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
+  asm volatile("mbarrier.arrive.relaxed.cta.shared::cta.b64 _, [%0];" ::"r"(bar) : "memory");
 }
 
 template <int STAGES, int ORDER>
@@ -707,8 +710,8 @@ __device__ __forceinline__ uint32_t map_to_cta(uint32_t saddr, uint32_t rank) { 
   return r;
 }
 
-__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
-  asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {   // relaxed: see mbar_arrive
+  asm volatile("mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
 }
 
 __device__ __forceinline__ void cluster_sync_all() {
