@@ -7,7 +7,14 @@
 // delegates to cuBLASLt through torch._scaled_mm (bitlattice/backend.py:267-290); forward, input-gradient and
 // weight-gradient GEMMs of the layer are all of this form (bitlattice/backend.py:502-510, 606-624).
 //
-// Kernel structure (one CTA per 128 x BN output tile, 192 threads):
+// Three kernels compute it with identical results, chosen by problem size (bl_nvfp4_gemm): gemm_kernel (below; one
+// CTA per 128 x 128 tile), gemm_persistent_kernel (one CTA per SM walking 128 x 256 tiles) and gemm_pair_kernel (a
+// cluster of two CTAs per SM pair walking 256 x 256 tiles with tcgen05.mma.cta_group::2). In the two persistent
+// kernels the producer and MMA warps stay fully converged and issue each k-tile's burst of instructions under one
+// elect.sync predicate: issued from a single lane of a diverged warp, every tcgen05 / TMA instruction cost about 90
+// cycles and bounded the kernel.
+//
+// Structure of gemm_kernel (one CTA per 128 x BN output tile, 192 threads):
 //   warp 0      producer: TMA loads of the A and B code tiles (128-byte swizzle) and bulk copies of their scale
 //               blobs into a ring of shared-memory stages, signalled through mbarriers (full / empty)
 //   warp 1      MMA issuer: owns the tensor-memory allocation; per stage copies the scale blobs into tensor memory

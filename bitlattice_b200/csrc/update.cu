@@ -9,9 +9,9 @@
 //
 // Data layout in HBM (all row-major over the weight's [rows, cols] view, cols % 16 == 0):
 //   codes  [rows, cols/2] bytes, phase [rows, cols*cb/8] bytes, scales [rows, cols/16] bytes, grad [rows, cols].
-// One thread owns 8 consecutive elements of a row (one 32-bit code word, cb bytes of phase, 16 or 32 bytes of
-// gradient); two neighbouring lanes share a 16-element scale group and exchange its three sums with one shuffle each.
-// A thread keeps its 8 columns while it walks down the rows, so per-column statistics (colnorm) stay in registers.
+// One thread owns one 16-element scale group of a row (two 32-bit code words, 2 cb bytes of phase, 32 or 64 bytes of
+// gradient, one scale byte) and needs no communication with other threads. A thread keeps its 16 columns while it
+// walks down the rows, so per-column statistics (colnorm) stay in registers.
 #include <mutex>
 
 #include "common.cuh"
