@@ -287,6 +287,33 @@ def test_weight_transpose_requantization():
     assert np.array_equal(host(scales), rs) and np.array_equal(host(packed), rc)
 
 
+def test_quantizers_index_beyond_2_31_elements():
+    """Size-independent property at a tensor of 2^31 + 2^27 elements: round-to-nearest quantization is local to rows
+    (row operand) and to 16-row blocks (transposed operand), so quantizing the two halves of the rows separately with
+    the same per-tensor scale reproduces the whole, bit for bit -- which it would not if an index wrapped at 32
+    bits."""
+    M, K = 139264, 16384
+    x = torch.empty(M, K, device=DEV, dtype=torch.bfloat16)
+    gen = torch.Generator(device=DEV).manual_seed(9)
+    for r0 in range(0, M, 8192):                                   # filled in slabs to bound temporary memory
+        x[r0:r0 + 8192] = torch.randn(8192, K, device=DEV, generator=gen).to(torch.bfloat16)
+    g = _ops.amax_global(x)[1:2]
+    h = M // 2
+    codes, sf = _ops.quantize_nvfp4(x, g)
+    for lo in (0, h):
+        c2, s2 = _ops.quantize_nvfp4(x[lo:lo + h], g)
+        assert torch.equal(codes[lo:lo + h], c2) and torch.equal(sf.view(torch.uint8)[lo:lo + h], s2.view(torch.uint8))
+    assert int(codes[-1].max()) > 0
+    del codes, sf, c2, s2
+    from bitlattice_b200.backend import _hadamard16
+    H = _hadamard16(torch.device(DEV), torch.float32)
+    tc, ts, _ = _ops.quantize_nvfp4_t(x, H, -1, 0, g * 4.0)
+    for lo in (0, h):
+        c2, s2, _ = _ops.quantize_nvfp4_t(x[lo:lo + h], H, -1, 0, g * 4.0)
+        assert torch.equal(tc[:, lo // 2:(lo + h) // 2], c2)
+        assert torch.equal(ts.view(torch.uint8)[:, lo // 16:(lo + h) // 16], s2.view(torch.uint8))
+
+
 # ------------------------------------------------------------------------------------------------ GEMM
 
 def _operand(rows, K, seed, scale):
