@@ -195,7 +195,8 @@ def blocked_scale_bytes(rows: int, cols16: int) -> int:
 
 def amax_global(x: torch.Tensor) -> torch.Tensor:
     """fp32 [4]: [0] = max|x|, [1] = the per-tensor NVFP4 scale max(amax/(6*448), 1e-12)
-    (reference: bitlattice/backend.py:240-241)."""
+    (reference: bitlattice/backend.py:240-241), [3] = max(amax/(6*256), 1e-12), the per-tensor scale of the
+    four-over-six recipe."""
     _require(x, "x")
     out = torch.empty(4, dtype=torch.float32, device=x.device)
     _C.call("bl_nvfp4_amax", _C.ptr(x), _C.DTYPE[x.dtype], x.numel(), _C.ptr(out), _C.device_of(x), _C.stream_of(x))
@@ -221,6 +222,26 @@ def quantize_nvfp4(x: torch.Tensor, global_scale: torch.Tensor, seed: int = -1, 
     scales = _scale_buffer(rows, cols // 16, blocked, x.device)
     _C.call("bl_nvfp4_quantize", _C.ptr(x), _C.DTYPE[x.dtype], rows, cols, _C.ptr(global_scale), int(seed),
             int(step) & 0xFFFFFFFF, _C.ptr(packed), _C.ptr(scales), int(blocked), _C.device_of(x), _C.stream_of(x))
+    return packed, scales if blocked else scales.view(torch.float8_e4m3fn)
+
+
+def quantize_nvfp4_4over6(x: torch.Tensor, global_scale: torch.Tensor, select: str = "mse", blocked: bool = False):
+    """The four-over-six round-to-nearest quantizer of forward activations: every block keeps the better of "maximum
+    mapped to 6" and "maximum mapped to 4" (``select``: 'mse' or 'mae'). ``global_scale``: amax / (6 * 256), i.e.
+    ``amax_global(x)[3:4]`` (reference: torch.ops.bitlattice.nvfp4_quantize with four_over_six; Python twin
+    bitlattice/fp4ref.py:103-135)."""
+    _require(x, "x")
+    _require(global_scale, "global_scale", torch.float32)
+    if x.dtype not in _C.DTYPE:
+        raise RuntimeError("x must be bf16, fp16 or fp32")
+    if select not in ("mse", "mae"):
+        raise ValueError("select must be 'mse' or 'mae'")
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    packed = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
+    scales = _scale_buffer(rows, cols // 16, blocked, x.device)
+    _C.call("bl_nvfp4_quantize_4over6", _C.ptr(x), _C.DTYPE[x.dtype], rows, cols, _C.ptr(global_scale),
+            1 if select == "mae" else 0, _C.ptr(packed), _C.ptr(scales), int(blocked), _C.device_of(x), _C.stream_of(x))
     return packed, scales if blocked else scales.view(torch.float8_e4m3fn)
 
 

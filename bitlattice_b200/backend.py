@@ -31,8 +31,10 @@ __all__ = ["FP4_RECIPES", "Fp4Operand", "Fp4Recipe", "as_recipe", "clear_shared"
 
 @dataclass(frozen=True)
 class Fp4Recipe:
-    """Quantization of the GEMM operands (reference: bitlattice/backend.py:57-121). Only the default values -- the
-    NVIDIA NVFP4 training recipe -- are built."""
+    """Quantization of the GEMM operands (reference: bitlattice/backend.py:57-121). Built: the default values (the
+    NVIDIA NVFP4 training recipe) and ``activations='4over6'`` (four-over-six block scales for the forward input,
+    criterion ``select``), everything else as in the NVIDIA recipe. The 128-point rotation, MS-EDEN gradients and
+    delayed scales are not."""
 
     activations: str = "rtn"
     gradients: str = "sr"
@@ -46,18 +48,24 @@ class Fp4Recipe:
     scale_margin: float = 2.0
 
     def __post_init__(self):
-        if astuple(self) != _NVIDIA:
-            raise ValueError("only the 'nvidia' FP4 recipe (round-to-nearest activations, stochastically rounded "
-                             "gradients, 16-point rotation) is built; the four-over-six / quartet2 recipes are not")
+        if self.activations not in ("rtn", "4over6"):
+            raise ValueError("activations must be 'rtn' or '4over6'")
+        if self.select not in ("mse", "mae"):
+            raise ValueError("select must be 'mse' or 'mae'")
+        if astuple(self)[1:5] + astuple(self)[6:] != _NVIDIA[1:5] + _NVIDIA[6:]:
+            raise ValueError("only the 'nvidia' and '4over6' FP4 recipes (stochastically rounded gradients, 16-point "
+                             "rotation) are built; the quartet2 recipes (128-point rotation, MS-EDEN, cached or "
+                             "delayed scales) are not")
 
     @property
     def legacy(self) -> bool:
-        return True
+        """True for the NVIDIA recipe."""
+        return astuple(self) == _NVIDIA
 
 
 _NVIDIA = ("rtn", "sr", 16, False, False, "mse", "requantize", "current", "current", 2.0)
 
-FP4_RECIPES: dict[str, Fp4Recipe] = {"nvidia": Fp4Recipe()}
+FP4_RECIPES: dict[str, Fp4Recipe] = {"nvidia": Fp4Recipe(), "4over6": Fp4Recipe(activations="4over6")}
 
 
 def as_recipe(r) -> Fp4Recipe:
@@ -138,6 +146,15 @@ def quantize_fp4(x2: torch.Tensor, stochastic: bool = False, blocked: bool = Tru
     seed = _seed() if stochastic else -1
     packed, scales = _ops.quantize_nvfp4(x2, g, seed, 0, blocked=blocked)
     return Fp4Operand(packed, scales, g, blocked)
+
+
+def _act_operand(x2: torch.Tensor, recipe: Fp4Recipe) -> Fp4Operand:
+    """Forward operand of the activations under ``recipe`` (reference: backend.py `_act_operand`)."""
+    if recipe.activations != "4over6":
+        return quantize_fp4(x2)
+    g = _ops.amax_global(x2)[3:4]
+    packed, scales = _ops.quantize_nvfp4_4over6(x2, g, recipe.select, blocked=True)
+    return Fp4Operand(packed, scales, g, True)
 
 
 def fp4_mm(a: Fp4Operand, b: Fp4Operand, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
@@ -264,8 +281,10 @@ def _input_operands(x: torch.Tensor, recipe: Fp4Recipe, row: bool = True):
     backend.py:519-546, legacy branch): the global scale of x bounds the rotated one by a factor 4."""
     K = x.shape[-1]
     x2 = _pad_rows(x.reshape(-1, K), 32).contiguous()
-    xq = quantize_fp4(x2)
-    bound = xq.global_scale * 4.0
+    xq = _act_operand(x2, recipe)
+    # |x H/4| <= 4 max|x| for the orthogonal 16 x 16 rotation: the row-wise per-tensor scale bounds the rotated one
+    # (brought back to the 448 convention when the row operand used 256; reference: backend.py:541-544)
+    bound = xq.global_scale * (4.0 * (256.0 / 448.0 if recipe.activations == "4over6" else 1.0))
     xt = Fp4Operand(*_ops.quantize_nvfp4_t(x2, _hadamard16(x2.device, torch.float32), -1, 0, bound, blocked=True), True)
     return (xq if row else None), xt
 
@@ -275,7 +294,7 @@ def nvfp4_linear(x: torch.Tensor, w, bias: torch.Tensor | None = None, recipe: F
     """y = Q(x) W^T (+ bias) with x quantized to NVFP4 on the fly; W must be an NVFP4 LatticeTensor."""
     K = x.shape[-1]
     M = x.numel() // K
-    xq = _shared(x, recipe, "fwd", lambda: quantize_fp4(_pad_rows(x.reshape(-1, K), 16).contiguous()))
+    xq = _shared(x, recipe, "fwd", lambda: _act_operand(_pad_rows(x.reshape(-1, K), 16).contiguous(), recipe))
     y = fp4_mm(xq, weight_operand(w), x.dtype)[:M]
     if bias is not None:
         y += bias.to(y.dtype)

@@ -22,7 +22,8 @@ __device__ __forceinline__ void atomic_max_pos(float* addr, float v) {   // v >=
   atomicMax(reinterpret_cast<int*>(addr), __float_as_int(v));
 }
 
-// out[0] = max|x| (out must start at zero), out[1] = max(out[0]/2688, 1e-12) written by the last block to finish
+// out[0] = max|x| (out must start at zero); the last block to finish writes out[1] = max(out[0] / 2688, 1e-12) and
+// out[3] = max(out[0] / 1536, 1e-12); out[2] is the ticket counter
 template <typename T>
 __global__ void __launch_bounds__(kQThreads) amax_kernel(const T* __restrict__ x, int64_t n, float* __restrict__ out) {
   constexpr int per = 16 / sizeof(T);
@@ -50,6 +51,7 @@ __global__ void __launch_bounds__(kQThreads) amax_kernel(const T* __restrict__ x
       __threadfence();
       const float a = *reinterpret_cast<volatile float*>(out);
       out[1] = fmaxf(a / 2688.0f, 1e-12f);
+      out[3] = fmaxf(a / 1536.0f, 1e-12f);      // the four-over-six recipe: amax / (6 * 256)
     }
   }
 }
@@ -106,26 +108,74 @@ __device__ __forceinline__ float rcp_approx(float x) {
   return r;
 }
 
+// block quantization modes
+constexpr int kModeRtn = 0, kModeSr = 1, kModeFosMse = 2, kModeFosMae = 3;
+
+// levels of 8 codes (one register of nibbles) times se, through the hardware E2M1 -> fp16 conversion
+__device__ __forceinline__ void e2m1_values8(uint32_t w, float se, float out[8]) {
+#pragma unroll
+  for (int k = 0; k < 4; ++k) {
+    uint32_t h2;
+    asm("{\n\t.reg .b8 b;\n\tcvt.u8.u32 b, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b;\n\t}" : "=r"(h2) : "r"(w >> (8 * k)));
+    const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
+    out[2 * k] = f.x * se;
+    out[2 * k + 1] = f.y * se;
+  }
+}
+
+// One candidate of the four-over-six choice: codes of v / se (one reciprocal per block, nearest level with ties to the
+// even code: the hardware conversion) and the error of the dequantized block, summed over the elements in ascending
+// order (bitlattice/fp4ref.py:117-131; the reference's kernel: csrc/nvfp4.cu:176-195)
+template <bool MAE>
+__device__ __forceinline__ float fos_candidate(const float v[16], float se, uint2& codes) {
+  const float inv = se > 0.0f ? __frcp_rn(se) : 0.0f;
+  float q[16];
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) mul2(v[i], v[i + 1], inv, q[i], q[i + 1]);
+  codes = make_uint2(cvt_e2m1x8_merged(q), cvt_e2m1x8_merged(q + 8));
+  float d[16];
+  e2m1_values8(codes.x, se, d);
+  e2m1_values8(codes.y, se, d + 8);
+  float err = 0.0f;
+#pragma unroll
+  for (int i = 0; i < 16; ++i) {
+    const float e = d[i] - v[i];
+    err = err + (MAE ? fabsf(e) : e * e);
+  }
+  return err;
+}
+
 // One block of 16 values v[i] * pre (pre: 1 or a power of two) -> 16 codes and the scale byte.
-// SR == false: reference.quantize 'rtn'. SR == true: fp4ref.quantize 'sr' (idx0 = flat index of v[0]).
-template <bool SR>
+// kModeRtn: reference.quantize 'rtn'. kModeSr: fp4ref.quantize 'sr' (idx0 = flat index of v[0]). kModeFosMse /
+// kModeFosMae: fp4ref.quantize 'rtn' with four_over_six (pre must be 1).
+template <int MODE>
 __device__ __forceinline__ uint2 quantize_block(const float v[16], float pre, float g, float rg, uint32_t key,
                                                 uint32_t idx0, uint32_t* scale) {
   float amax = 0.0f;
 #pragma unroll
   for (int i = 0; i < 16; ++i) amax = fmaxf(amax, fabsf(v[i]));
   amax *= pre;
-  if constexpr (!SR) {
+  if constexpr (MODE == kModeRtn) {
     const uint32_t sb = e4m3_encode(div_rn(fmaxf(div_rn(amax, 6.0f, kInv6), 1e-12f), g, rg));
     const float se = e4m3_decode(sb) * g;
     *scale = sb;
     return e2m1_rtn16(v, pre, se, rcp_approx(se));
-  } else {
+  } else if constexpr (MODE == kModeSr) {
     const uint32_t sb = e4m3_encode(div_rn(div_rn(amax, 6.0f, kInv6), g, rg));
     const float t = e4m3_decode(sb) * g;
     const float inv = t > 0.0f ? __frcp_rn(t) : 0.0f;
     *scale = sb;
     return e2m1_sr16(v, inv * pre, key, idx0);
+  } else {
+    const uint32_t b6 = e4m3_encode(div_rn(div_rn(amax, 6.0f, kInv6), g, rg));
+    const uint32_t b4 = e4m3_encode(div_rn(amax * 0.25f, g, rg));
+    uint2 c6, c4;
+    const float e6 = fos_candidate<MODE == kModeFosMae>(v, e4m3_decode(b6) * g, c6);
+    const float e4 = fos_candidate<MODE == kModeFosMae>(v, e4m3_decode(b4) * g, c4);
+    const bool pick4 = e4 < e6;
+    *scale = pick4 ? b4 : b6;
+    const uint2 c = pick4 ? c4 : c6;
+    return make_uint2(e2m1_drop_negative_zero(c.x), e2m1_drop_negative_zero(c.y));
   }
 }
 
@@ -164,7 +214,7 @@ __device__ __forceinline__ void unpack_raw16(const Raw16<T>& r, float v[16]) {
 
 // block (bx, 256/bx): x covers the 16-element blocks of a row, y covers rows; a thread keeps its block column and walks
 // down the rows, kRowsUnroll rows in flight (their loads are issued before any arithmetic).
-template <typename T, bool SR>
+template <typename T, int MODE>
 __global__ void __launch_bounds__(kQThreads, 3) quantize_rows16_kernel(const T* __restrict__ x, int64_t rows, int64_t cols,
                                                                     const float* __restrict__ global, uint32_t key,
                                                                     uint8_t* __restrict__ codes,
@@ -194,7 +244,7 @@ __global__ void __launch_bounds__(kQThreads, 3) quantize_rows16_kernel(const T* 
       float v[16];
       unpack_raw16(raw[u], v);
       uint32_t sb;
-      const uint2 out = quantize_block<SR>(v, 1.0f, g, rg, key, static_cast<uint32_t>(r * cols + cb * 16), &sb);
+      const uint2 out = quantize_block<MODE>(v, 1.0f, g, rg, key, static_cast<uint32_t>(r * cols + cb * 16), &sb);
       __stcs(reinterpret_cast<uint2*>(codes + r * (cols / 2)) + cb, out);
       const int64_t sf_row = layout == BL_SF_ROWMAJOR ? r * cols16
                                                       : (r >> 7) * nc * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4;
@@ -430,10 +480,10 @@ __global__ void __launch_bounds__(kQThreads, 4) quantize_t3_kernel(const T* __re
     }
     uint32_t sb;
     s_codes[2 * kp][mb] =
-        quantize_block<SR>(va, 1.0f, g, rg, key, static_cast<uint32_t>(static_cast<uint64_t>(k) * M + m), &sb);
+        quantize_block<SR ? kModeSr : kModeRtn>(va, 1.0f, g, rg, key, static_cast<uint32_t>(static_cast<uint64_t>(k) * M + m), &sb);
     s_scales[2 * kp][mb] = static_cast<uint8_t>(sb);
     s_codes[2 * kp + 1][mb] =
-        quantize_block<SR>(vb, 1.0f, g, rg, key, static_cast<uint32_t>(static_cast<uint64_t>(k + 1) * M + m), &sb);
+        quantize_block<SR ? kModeSr : kModeRtn>(vb, 1.0f, g, rg, key, static_cast<uint32_t>(static_cast<uint64_t>(k + 1) * M + m), &sb);
     s_scales[2 * kp + 1][mb] = static_cast<uint8_t>(sb);
   }
   __syncthreads();
@@ -586,16 +636,22 @@ extern "C" int bl_nvfp4_amax(const void* x, int dtype, int64_t n, float* out, in
   return 0;
 }
 
+constexpr int64_t kSeedFosMse = -2, kSeedFosMae = -3;   // internal mode selectors of quantize_rows_typed
+
 template <typename T>
 static int quantize_rows_typed(const T* x, int64_t rows, int64_t cols, const float* g, int64_t seed, uint32_t step,
                                uint8_t* codes, uint8_t* scales, int layout, int device, cudaStream_t st) {
   const RowGeometry geo = row_geometry(rows, cols, device);
-  if (seed < 0)
-    quantize_rows16_kernel<T, false><<<geo.grid, geo.block, 0, st>>>(x, rows, cols, g, 0u, codes, scales, layout);
+  if (seed == kSeedFosMse)
+    quantize_rows16_kernel<T, kModeFosMse><<<geo.grid, geo.block, 0, st>>>(x, rows, cols, g, 0u, codes, scales, layout);
+  else if (seed == kSeedFosMae)
+    quantize_rows16_kernel<T, kModeFosMae><<<geo.grid, geo.block, 0, st>>>(x, rows, cols, g, 0u, codes, scales, layout);
+  else if (seed < 0)
+    quantize_rows16_kernel<T, kModeRtn><<<geo.grid, geo.block, 0, st>>>(x, rows, cols, g, 0u, codes, scales, layout);
   else
-    quantize_rows16_kernel<T, true><<<geo.grid, geo.block, 0, st>>>(x, rows, cols, g,
-                                                                  hash_key(static_cast<uint32_t>(seed), step), codes,
-                                                                  scales, layout);
+    quantize_rows16_kernel<T, kModeSr><<<geo.grid, geo.block, 0, st>>>(x, rows, cols, g,
+                                                                       hash_key(static_cast<uint32_t>(seed), step),
+                                                                       codes, scales, layout);
   BL_CUDA(cudaGetLastError());
   return 0;
 }
@@ -611,6 +667,7 @@ extern "C" int bl_nvfp4_quantize(const void* x, int dtype, int64_t rows, int64_t
   BL_REQUIRE(aligned16(x) && aligned16(codes), "quantize_nvfp4: x and codes must be 16-byte aligned");
   BL_DEVICE(device);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (seed < 0) seed = -1;                              // any negative seed: round to nearest
   if (sf_layout == BL_SF_BLOCKED && blocked_needs_padding(rows, cols / 16))
     BL_CUDA(cudaMemsetAsync(scales, 0, bl_blocked_scale_bytes(rows, cols / 16), st));
   if (dtype == BL_BF16)
@@ -618,6 +675,28 @@ extern "C" int bl_nvfp4_quantize(const void* x, int dtype, int64_t rows, int64_t
   if (dtype == BL_F16)
     return quantize_rows_typed(static_cast<const __half*>(x), rows, cols, global_scale, seed, step, codes, scales, sf_layout, device, st);
   return quantize_rows_typed(static_cast<const float*>(x), rows, cols, global_scale, seed, step, codes, scales, sf_layout, device, st);
+}
+
+extern "C" int bl_nvfp4_quantize_4over6(const void* x, int dtype, int64_t rows, int64_t cols, const float* global_scale,
+                                        int select, uint8_t* codes, uint8_t* scales, int sf_layout, int device,
+                                        bl_stream_t stream) {
+  BL_REQUIRE(x && global_scale && codes && scales, "quantize_4over6: null buffer");
+  BL_REQUIRE(rows > 0 && cols > 0 && cols % 16 == 0,
+             "quantize_4over6: last dimension must be a multiple of 16, got %lld x %lld", (long long)rows, (long long)cols);
+  BL_REQUIRE(dtype >= BL_F32 && dtype <= BL_F16, "quantize_4over6: unknown dtype %d", dtype);
+  BL_REQUIRE(select == BL_SELECT_MSE || select == BL_SELECT_MAE, "quantize_4over6: unknown selection rule %d", select);
+  BL_REQUIRE(sf_layout == BL_SF_ROWMAJOR || sf_layout == BL_SF_BLOCKED, "quantize_4over6: unknown scale layout %d", sf_layout);
+  BL_REQUIRE(aligned16(x) && aligned16(codes), "quantize_4over6: x and codes must be 16-byte aligned");
+  BL_DEVICE(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (sf_layout == BL_SF_BLOCKED && blocked_needs_padding(rows, cols / 16))
+    BL_CUDA(cudaMemsetAsync(scales, 0, bl_blocked_scale_bytes(rows, cols / 16), st));
+  const int64_t mode = select == BL_SELECT_MAE ? kSeedFosMae : kSeedFosMse;
+  if (dtype == BL_BF16)
+    return quantize_rows_typed(static_cast<const __nv_bfloat16*>(x), rows, cols, global_scale, mode, 0u, codes, scales, sf_layout, device, st);
+  if (dtype == BL_F16)
+    return quantize_rows_typed(static_cast<const __half*>(x), rows, cols, global_scale, mode, 0u, codes, scales, sf_layout, device, st);
+  return quantize_rows_typed(static_cast<const float*>(x), rows, cols, global_scale, mode, 0u, codes, scales, sf_layout, device, st);
 }
 
 template <typename T>

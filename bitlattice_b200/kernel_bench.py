@@ -79,6 +79,7 @@ def quant():
         g = am[1:2]
         cases = [("amax", lambda: _ops.amax_global(x)),
                  ("rows rtn", lambda: _ops.quantize_nvfp4(x, g, blocked=True)),
+                 ("rows 4over6", lambda: _ops.quantize_nvfp4_4over6(x, am[3:4], "mse", blocked=True)),
                  ("rows sr", lambda: _ops.quantize_nvfp4(x, g, seed=3, blocked=True)),
                  ("transposed rtn", lambda: _ops.quantize_nvfp4_t(x, H, -1, 0, g * 4, blocked=True)),
                  ("transposed sr", lambda: _ops.quantize_nvfp4_t(x, H, 5, 0, g * 4, blocked=True))]

@@ -47,6 +47,8 @@ enum { BL_RULE_FIXED = 0, BL_RULE_FIT = 1, BL_RULE_FIT_LATENT = 2 };
 enum { BL_DIR_RAW = 0, BL_DIR_SIGN = 1, BL_DIR_COLNORM = 2 };
 /* layout of block-scale outputs */
 enum { BL_SF_ROWMAJOR = 0, BL_SF_BLOCKED = 1 };
+/* four-over-six selection criterion: squared or absolute error of the dequantized block */
+enum { BL_SELECT_MSE = 0, BL_SELECT_MAE = 1 };
 
 BL_API int bl_version(void);
 BL_API const char* bl_last_error(void);
@@ -116,7 +118,8 @@ BL_API int bl_nvfp4_dequantize(const uint8_t* codes, const uint8_t* scales, cons
 /* ---- operand quantizers --------------------------------------------------------------------------------------- */
 
 /* The amax pass of bitlattice/backend.py:240-241: out[0] = max|x|, out[1] = max(out[0] / (6*448), 1e-12) (the
- * per-tensor scale), out[2..3] are used as a counter. out: 4 floats. */
+ * per-tensor scale), out[2] is used as a counter, out[3] = max(out[0] / (6*256), 1e-12) (the per-tensor scale of the
+ * four-over-six recipe, bitlattice/fp4ref.py:110-113). out: 4 floats. */
 BL_API int bl_nvfp4_amax(const void* x, int dtype, int64_t n, float* out, int device, bl_stream_t stream);
 
 /* Replaces torch.ops.bitlattice.quantize_nvfp4 (csrc/bindings.cpp:96, csrc/act_quant.cu:180-225): x [rows, cols]
@@ -127,6 +130,15 @@ BL_API int bl_nvfp4_amax(const void* x, int dtype, int64_t n, float* out, int de
  * bl_blocked_scale_bytes(rows, cols/16) bytes and receives the zero padding too. cols % 16 == 0. */
 BL_API int bl_nvfp4_quantize(const void* x, int dtype, int64_t rows, int64_t cols, const float* global_scale, int64_t seed,
                       uint32_t step, uint8_t* codes, uint8_t* scales, int sf_layout, int device, bl_stream_t stream);
+
+/* The forward-activation quantizer of the '4over6' recipe (bitlattice/backend.py:131, the general quantizer
+ * torch.ops.bitlattice.nvfp4_quantize with four_over_six, csrc/nvfp4.cu:553-600; Python twin bitlattice/fp4ref.py:103-135):
+ * round to nearest with ties to the even code, v * (1 / (scale*global)); every block is quantized with its maximum
+ * mapped to 6 and to 4 and keeps the candidate with the smaller error (select: BL_SELECT_MSE / BL_SELECT_MAE; six on
+ * equality; error sums in element order). *global_scale is amax / (6 * 256) (out[3] of bl_nvfp4_amax). */
+BL_API int bl_nvfp4_quantize_4over6(const void* x, int dtype, int64_t rows, int64_t cols, const float* global_scale,
+                             int select, uint8_t* codes, uint8_t* scales, int sf_layout, int device,
+                             bl_stream_t stream);
 
 /* Replaces torch.ops.bitlattice.quantize_nvfp4_t (csrc/bindings.cpp:97-98, csrc/act_quant.cu:100-148,230-270):
  * x [M, K] -> NVFP4 of x^T, codes [K, M/2] + scales over [K, M/16], blocks of 16 along M, each block optionally

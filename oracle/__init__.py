@@ -61,6 +61,9 @@ def lib() -> ctypes.CDLL:
         L.blo_global_from_bound.argtypes = [c.c_float]
         L.blo_quantize_rows.argtypes = [f32p, c.c_int64, c.c_int64, c.c_float, c.c_int, c.c_uint32, c.c_uint32, u8p,
                                         u8p]
+        L.blo_global_fos.argtypes = [c.c_float]
+        L.blo_global_fos.restype = c.c_float
+        L.blo_quantize_rows_fos.argtypes = [f32p, c.c_int64, c.c_int64, c.c_float, c.c_int, u8p, u8p]
         L.blo_quantize_t.argtypes = [f32p, c.c_int64, c.c_int64, f32p, c.c_float, c.c_int, c.c_uint32, c.c_uint32,
                                      u8p, u8p]
         L.blo_requantize_t.argtypes = [u8p, u8p, c.c_float, c.c_int64, c.c_int64, u8p, u8p]
@@ -141,6 +144,20 @@ def quantize_rows(x, g: float | None = None, mode: str = "rtn", seed: int = 0, s
     scales = np.empty((rows, cols // 16), np.uint8)
     lib().blo_quantize_rows(_p(x, ctypes.c_float), rows, cols, np.float32(g), 0 if mode == "rtn" else 1,
                             seed & 0xFFFFFFFF, step & 0xFFFFFFFF, _p(codes, ctypes.c_uint8), _p(scales, ctypes.c_uint8))
+    return codes, scales, np.float32(g)
+
+
+def quantize_rows_fos(x, g: float | None = None, select: str = "mse"):
+    """Four-over-six round-to-nearest quantizer of the forward activations (bitlattice/fp4ref.py:103-135 with
+    four_over_six=True): x [rows, cols] -> (codes, scale bytes, global). ``g`` None: amax / (6 * 256)."""
+    x = _f32(x)
+    rows, cols = x.shape
+    if g is None:
+        g = lib().blo_global_fos(np.float32(amax(x)))
+    codes = np.empty((rows, cols // 2), np.uint8)
+    scales = np.empty((rows, cols // 16), np.uint8)
+    lib().blo_quantize_rows_fos(_p(x, ctypes.c_float), rows, cols, np.float32(g), 1 if select == "mae" else 0,
+                                _p(codes, ctypes.c_uint8), _p(scales, ctypes.c_uint8))
     return codes, scales, np.float32(g)
 
 

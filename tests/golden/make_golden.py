@@ -2,7 +2,7 @@
 
 Run where the reference checkout is importable (it is read-only, so no bytecode is written):
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/reference [file names ...]
 
 Every array below is an OUTPUT OF THE REFERENCE (bitlattice.reference, bitlattice.fp4ref, bitlattice._ops CPU
 fallbacks, bitlattice.optim.Lattice on CPU) on seeded inputs; the inputs are stored next to them. The oracle and the
@@ -91,6 +91,23 @@ def quantize_cases():
     sc = torch.randint(0, 127, (200, 9), generator=gen(3), dtype=torch.uint8)
     out["blk_in"] = sc.numpy()
     out["blk_out"] = bl.backend.to_blocked(sc).numpy()
+    return out
+
+
+def fos_cases():
+    """Four-over-six round-to-nearest quantizer of the forward activations (the '4over6' recipe): fp4ref.quantize
+    with four_over_six=True, both selection criteria, bf16-valued and fp32-valued inputs, an all-zero block."""
+    out = {}
+    x = torch.randn(64, 256, generator=gen(11)).to(torch.bfloat16).float()
+    x[0, :16] = 0.0
+    xf = torch.randn(48, 128, generator=gen(12)) * 3.0
+    for tag, inp in (("bf", x), ("f32", xf)):
+        out[f"{tag}_x"] = inp.numpy()
+        for select in ("mse", "mae"):
+            vals, s, g = fp4ref.quantize(inp, mode="rtn", four_over_six=True, select=select)
+            out[f"{tag}_{select}_codes"] = values_to_codes(vals).numpy()
+            out[f"{tag}_{select}_scales"] = u8(s.to(torch.float8_e4m3fn))
+            out[f"{tag}_{select}_g"] = g.reshape(1).numpy()
     return out
 
 
@@ -229,7 +246,9 @@ def main():
     torch.set_num_threads(4)
     for name, fn in (("hash", hash_cases), ("e4m3", e4m3_cases), ("quantize", quantize_cases),
                      ("transposed", transposed_cases), ("step", step_cases), ("direction", direction_cases),
-                     ("optimizer", optimizer_cases), ("linear", linear_cases)):
+                     ("optimizer", optimizer_cases), ("linear", linear_cases), ("fos", fos_cases)):
+        if len(sys.argv) > 2 and name not in sys.argv[2:]:
+            continue                                   # optional: names of the files to (re)generate
         data = fn()
         path = os.path.join(OUT, f"{name}.npz")
         np.savez_compressed(path, **data)

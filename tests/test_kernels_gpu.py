@@ -235,6 +235,34 @@ def test_row_quantizer_matches_oracle(dtype, mode):
     assert np.array_equal(host(_ops.to_blocked(scales.view(torch.uint8))), oracle.to_blocked(rs))
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float32, torch.float16])
+@pytest.mark.parametrize("select", ["mse", "mae"])
+def test_four_over_six_quantizer_matches_oracle(dtype, select):
+    rows, cols = 77, 1040
+    x = torch.randn(rows, cols, generator=gen(12)).to(dtype)
+    x[5, 32:48] = 0.0
+    xf = x.float().numpy()
+    rc, rs, g = oracle.quantize_rows_fos(xf, None, select)
+    am = _ops.amax_global(dev(x))
+    assert host(am)[3] == g
+    packed, scales = _ops.quantize_nvfp4_4over6(dev(x), am[3:4], select)
+    assert np.array_equal(host(scales), rs)
+    assert np.array_equal(host(packed), rc)
+    packed_b, blocked = _ops.quantize_nvfp4_4over6(dev(x), am[3:4], select, blocked=True)
+    assert torch.equal(packed_b, packed)
+    assert np.array_equal(host(blocked), oracle.to_blocked(rs))
+
+
+def test_four_over_six_quantizer_matches_reference_golden():
+    g = golden("fos")
+    for tag in ("bf", "f32"):
+        for select in ("mse", "mae"):
+            x = dev(g[f"{tag}_x"], torch.bfloat16 if tag == "bf" else torch.float32)
+            packed, scales = _ops.quantize_nvfp4_4over6(x, dev(g[f"{tag}_{select}_g"]), select)
+            assert np.array_equal(host(packed), g[f"{tag}_{select}_codes"])
+            assert np.array_equal(host(scales), g[f"{tag}_{select}_scales"])
+
+
 def test_blocked_layout_matches_reference_golden():
     g = golden("quantize")
     assert np.array_equal(host(_ops.to_blocked(dev(g["blk_in"]))), g["blk_out"])

@@ -67,6 +67,36 @@ def test_fp4_linear_matches_quantized_reference(M):
     assert bl._ops.gemm_status(0) == 0
 
 
+def test_four_over_six_recipe_forward_and_backward():
+    """The '4over6' recipe: the forward follows dequant(Q_4over6(x)) @ dequant(W)^T within the reference's forward bound
+    (1e-2), is at least as close to the exact layer as the NVIDIA recipe on Gaussian inputs, and the backward stays
+    within the 0.25 bound of the exact route."""
+    x = torch.randn(512, 512, generator=gen(1)).to(torch.bfloat16)
+    w = bl.LatticeTensor.from_float((torch.randn(384, 512, generator=gen(2)) * 0.05).to(DEV), "nvfp4", method="rtn",
+                                    dtype=torch.bfloat16)
+    W = w.dequantize(torch.float32).cpu()
+    xc, xs, xg = oracle.quantize_rows_fos(x.float().numpy(), None, "mse")
+    ref = torch.from_numpy(oracle.dequantize(xc, xs, xg)) @ W.T
+    exact = x.float() @ W.T
+    gy = (torch.randn(512, 384, generator=gen(3)) * 1e-2).to(DEV, torch.bfloat16)
+    errs = {}
+    for name in ("nvidia", "4over6"):
+        p = torch.nn.Parameter(w)
+        xin = x.to(DEV).requires_grad_(True)
+        with bl.compute(bl.Compute("nvfp4", nvfp4=name)):
+            y = torch.nn.functional.linear(xin, p)
+            y.backward(gy)
+        errs[name] = rel(y.cpu(), exact)
+        if name == "4over6":
+            assert rel(y.cpu(), ref) < 1e-2
+        assert rel(xin.grad.cpu(), gy.float().cpu() @ W) < 0.25
+        assert rel(p.grad.cpu(), gy.float().cpu().T @ x.float()) < 0.25
+    assert errs["4over6"] <= errs["nvidia"] * 1.02, errs
+    assert bl._ops.gemm_status(0) == 0
+    with pytest.raises(ValueError, match="quartet2"):
+        bl.backend.Fp4Recipe(rotation=128)
+
+
 @pytest.mark.parametrize("M", [5, 96, 512])
 def test_fp4_all_gradients_close_to_exact(M):
     """The reference's bound (tests/test_backend.py:77-94): y, dx, dw within 0.25 relative error of the exact route."""

@@ -48,6 +48,23 @@ def test_quantize_sr(seed):
     assert np.array_equal(codes, g[f"sr{seed}_codes"])
 
 
+@pytest.mark.parametrize("tag", ["bf", "f32"])
+@pytest.mark.parametrize("select", ["mse", "mae"])
+def test_quantize_four_over_six(tag, select):
+    """fp4ref.quantize(mode='rtn', four_over_six=True): codes, scale bytes and the per-tensor scale amax / (6 * 256).
+    The candidate errors are summed in element order here and by torch's reduction in fp4ref; on these vectors the two
+    agree in every block."""
+    g = golden("fos")
+    codes, scales, gs = oracle.quantize_rows_fos(g[f"{tag}_x"], None, select)
+    assert gs == g[f"{tag}_{select}_g"][0]
+    assert np.array_equal(scales, g[f"{tag}_{select}_scales"])
+    assert np.array_equal(codes, g[f"{tag}_{select}_codes"])
+    # the choice matters: some blocks keep the four-mapping, some the six-mapping
+    _, six_scales, _ = oracle.quantize_rows(g[f"{tag}_x"], float(gs), "sr", seed=0)    # scale bytes of amax / 6 / g
+    frac = float((scales != six_scales).mean())
+    assert 0.05 < frac < 0.95, frac
+
+
 def test_blocked_scale_layout():
     g = golden("quantize")
     assert np.array_equal(oracle.to_blocked(g["blk_in"]), g["blk_out"])
