@@ -11,8 +11,8 @@ Direction, scale refit and projection run as ONE pass over codes, phase and grad
 Same constructor, option names, validation errors, per-parameter seeds (``seed + 7919 * index``), step counters and
 state layout (``state[p]["phase"]``: uint8 [rows, cols * container_bits / 8]) as the reference, so optimizer state
 interchanges. Not built, and refused with NotImplementedError: Newton-Schulz / factored / sinkhorn directions,
-momentum, neuron-wise normalization, row-sparse gradients, native-format (non-lattice) parameters, host-memory state
-and the overlap worker.
+low-precision momentum (momentum='fp32' is built), neuron-wise normalization, row-sparse gradients, native-format
+(non-lattice) parameters, host-memory state and the overlap worker.
 """
 from __future__ import annotations
 
@@ -44,6 +44,7 @@ def defer_fused_updates(delta: int) -> None:
 DIRECTIONS = ("muon_block", "muon", "factored", "sinkhorn", "colnorm", "sign", "raw")
 BUILT_DIRECTIONS = ("colnorm", "sign", "raw")
 MOMENTA = ("none", "fp32", "ternary", "bf16", "int8", "fp8", "nvfp4")
+BUILT_MOMENTA = ("none", "fp32")
 ROUNDINGS = ("sr", "strat", "rtn")
 SCALE_RULES = ("fit", "fit_latent", "fixed")
 
@@ -70,8 +71,8 @@ def _validate(g: dict) -> None:
     if g["direction"] not in BUILT_DIRECTIONS:
         raise NotImplementedError(f"direction={g['direction']!r} is outside this build; built: {BUILT_DIRECTIONS} "
                                   "(pass direction= explicitly: the reference's default 'muon_block' is not built)")
-    if g["momentum"] != "none":
-        raise NotImplementedError("momentum is outside this build (momentum='none' is built)")
+    if g["momentum"] not in BUILT_MOMENTA:
+        raise NotImplementedError(f"momentum={g['momentum']!r} is outside this build; built: {BUILT_MOMENTA}")
     if g["normalize"] != "none":
         raise NotImplementedError("neuron-wise normalization is outside this build")
     for p in g["params"]:
@@ -213,6 +214,13 @@ class Lattice(torch.optim.Optimizer):
         if bits and "phase" not in st:
             st["phase"] = torch.zeros(rows, packed_cols(cols, cb), dtype=torch.uint8, device=p.packed.device)
         G2 = G.reshape(rows, cols)
+        if g["momentum"] == "fp32":
+            # exponential average of the gradient in fp32, which then takes the gradient's place
+            # (reference: lattice.py:396-405: m <- beta1 * m, m <- m + (1 - beta1) * G, in place)
+            if "m" not in st:
+                st["m"] = torch.zeros(rows, cols, dtype=torch.float32, device=G2.device)
+            st["m"].mul_(g["beta1"]).add_(G2.float(), alpha=1 - g["beta1"])
+            G2 = st["m"]
         if G2.dtype not in (torch.bfloat16, torch.float16, torch.float32):
             G2 = G2.float()
         _ops.lattice_update(p.packed, st.get("phase") if bits else None, p.scales, p.global_scale, None,
@@ -223,11 +231,12 @@ class Lattice(torch.optim.Optimizer):
                             offset=int(getattr(p, "_bl_row_offset", 0)) * cols)
 
     def state_bits(self) -> dict[str, float]:
-        """Logical optimizer state in bits, by component (only the phase exists in this build)."""
+        """Logical optimizer state in bits, by component (phase and, with momentum='fp32', the fp32 average)."""
         out = {"phase": 0.0, "factors": 0.0, "momentum": 0.0}
         for g in self.param_groups:
             for p in g["params"]:
                 out["phase"] += p.numel() * g["phase_bits"]
+                out["momentum"] += p.numel() * (32 if g["momentum"] == "fp32" else 0)
         out["total"] = sum(out.values())
         return out
 

@@ -227,6 +227,36 @@ def optimizer_cases():
     return out
 
 
+def momentum_cases():
+    """bl.optim.Lattice on CPU with momentum='fp32' (lattice.py:396-405): three steps, so that the averaged gradient
+    differs from every single one; the final momentum buffers are stored too."""
+    out = {}
+    names = []
+    for direction, bits, rule in (("sign", 4, "fit"), ("raw", 2, "fixed")):
+        ws = [torch.randn(32, 64, generator=gen(50)) * 0.02, torch.randn(16, 128, generator=gen(51)) * 0.02]
+        ps = [torch.nn.Parameter(bl.LatticeTensor.from_float(w, "nvfp4", method="rtn", dtype=torch.bfloat16))
+              for w in ws]
+        key = f"{direction}_b{bits}_{rule}"
+        names.append(key)
+        for i, p in enumerate(ps):
+            out[f"{key}_p{i}_codes0"], out[f"{key}_p{i}_scales0"] = p.packed.numpy().copy(), u8(p.scales)
+            out[f"{key}_p{i}_g"] = p.global_scale.numpy().copy()
+        opt = bl.optim.Lattice(ps, lr=3e-3, direction=direction, phase_bits=bits, scale_rule=rule, seed=4321,
+                               trust=0.1, trust_lr=0.0, momentum="fp32", beta1=0.9)
+        for s in range(3):
+            for i, p in enumerate(ps):
+                G = (torch.randn(p.shape, generator=gen(60 + 2 * s + i)) * 1e-2).to(torch.bfloat16)
+                out[f"{key}_p{i}_G{s}"] = G.float().numpy()
+                p.grad = G
+            opt.step()
+        for i, p in enumerate(ps):
+            out[f"{key}_p{i}_codes"], out[f"{key}_p{i}_scales"] = p.packed.numpy().copy(), u8(p.scales)
+            out[f"{key}_p{i}_phase"] = opt.state[p]["phase"].numpy().copy()
+            out[f"{key}_p{i}_m"] = opt.state[p]["m"].numpy().copy()
+    out["names"] = np.array(names)
+    return out
+
+
 def linear_cases():
     """'exact' route forward / backward of one layer (the GEMM oracle), config-1-like but small."""
     M, K, N = 48, 128, 64
@@ -246,7 +276,8 @@ def main():
     torch.set_num_threads(4)
     for name, fn in (("hash", hash_cases), ("e4m3", e4m3_cases), ("quantize", quantize_cases),
                      ("transposed", transposed_cases), ("step", step_cases), ("direction", direction_cases),
-                     ("optimizer", optimizer_cases), ("linear", linear_cases), ("fos", fos_cases)):
+                     ("optimizer", optimizer_cases), ("linear", linear_cases), ("fos", fos_cases),
+                     ("momentum", momentum_cases)):
         if len(sys.argv) > 2 and name not in sys.argv[2:]:
             continue                                   # optional: names of the files to (re)generate
         data = fn()

@@ -206,6 +206,30 @@ def test_optimizer_matches_reference_golden(key):
     assert opt.state_bits()["phase"] == bits * sum(p.numel() for p in ps)
 
 
+@pytest.mark.parametrize("key", [str(n) for n in golden("momentum")["names"]])
+def test_fp32_momentum_matches_reference_golden(key):
+    """Three steps with momentum='fp32': codes, scale bytes, phase bytes and the momentum buffer itself equal the
+    reference's CPU run bit for bit (the average is one rounded multiply and one fused multiply-add per element on both
+    sides)."""
+    g = golden("momentum")
+    direction, bits, rule = key.split("_")[0], int(key.split("_")[1][1:]), key.split("_", 2)[2]
+    shapes = [(32, 64), (16, 128)]
+    ps = [torch.nn.Parameter(lattice_from(g[f"{key}_p{i}_codes0"], g[f"{key}_p{i}_scales0"], g[f"{key}_p{i}_g"], s))
+          for i, s in enumerate(shapes)]
+    opt = bl.optim.Lattice(ps, lr=3e-3, direction=direction, phase_bits=bits, scale_rule=rule, seed=4321, trust=0.1,
+                           trust_lr=0.0, momentum="fp32", beta1=0.9)
+    for s in range(3):
+        for i, p in enumerate(ps):
+            p.grad = torch.from_numpy(g[f"{key}_p{i}_G{s}"]).to(DEV, torch.bfloat16)
+        opt.step()
+    for i, p in enumerate(ps):
+        assert np.array_equal(opt.state[p]["m"].cpu().numpy(), g[f"{key}_p{i}_m"]), (key, i)
+        assert np.array_equal(p.scales.view(torch.uint8).cpu().numpy(), g[f"{key}_p{i}_scales"]), (key, i)
+        assert np.array_equal(p.packed.cpu().numpy(), g[f"{key}_p{i}_codes"]), (key, i)
+        assert np.array_equal(opt.state[p]["phase"].cpu().numpy(), g[f"{key}_p{i}_phase"]), (key, i)
+    assert opt.state_bits()["momentum"] == 32 * sum(p.numel() for p in ps)
+
+
 def _make_params(seed=11):
     return [torch.nn.Parameter(bl.LatticeTensor.from_float((torch.randn(s, generator=gen(seed + i)) * 0.05).to(DEV),
                                                            "nvfp4", method="rtn", dtype=torch.bfloat16))
