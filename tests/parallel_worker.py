@@ -82,6 +82,23 @@ def main():
     gx2_exact = gx_exact + gy2.float() @ w2.dequantize(torch.float32)
     assert rel(xs2.grad, gx2_exact[rows]) < 0.25, rel(xs2.grad, gx2_exact[rows])
     assert rel(pb.grad, (gy2.float().t() @ x.float())[cols2]) < 0.25
+
+    # a token shard that is not a multiple of 128 rows takes the generic route (bf16 all-gather, the layer's own
+    # autograd function, reduce-scatter): same forward bits, gradients within the same bounds
+    Mo = 96 * world
+    xo, gyo = x[:Mo].contiguous(), gy[:Mo].contiguous()
+    ro = slice(rank * 96, (rank + 1) * 96)
+    with bl.compute("fp4_all"):
+        pf = torch.nn.Parameter(w)
+        xf2 = xo.detach().requires_grad_(True)
+        yo_full = torch.nn.functional.linear(xf2, pf)
+        po = torch.nn.Parameter(shard_rows(w, rank, world))
+        xso = xo[ro].detach().contiguous().requires_grad_(True)
+        yo = column_parallel_linear(xso, po, None)
+        assert torch.equal(yo, yo_full[:, cols]), "generic route: forward shard differs from the unsharded forward"
+        yo.backward(gyo[:, cols].contiguous())
+    assert rel(xso.grad, (gyo.float() @ W)[ro]) < 0.25
+    assert rel(po.grad, (gyo.float().t() @ xo.float())[cols]) < 0.25
     assert bl._ops.gemm_status(local) == 0
     dist.barrier()
     print(f"OK {rank}", flush=True)
