@@ -15,7 +15,7 @@ from . import _C
 
 _C.lib()          # fail loudly here, not at the first kernel call, when the CUDA library is missing
 
-from . import backend, formats, optim, packing, parallel  # noqa: E402
+from . import backend, formats, io, optim, packing, parallel  # noqa: E402
 from ._ops import HAVE_EXT  # noqa: E402
 from .compute_policy import PRESETS as COMPUTE_PRESETS  # noqa: E402
 from .compute_policy import Compute, compute  # noqa: E402
@@ -27,4 +27,4 @@ from .tensor import LatticeTensor, is_lattice  # noqa: E402
 __version__ = "0.1.0"
 
 __all__ = ["COMPUTE_PRESETS", "HAVE_EXT", "Compute", "Format", "Lattice", "LatticeTensor", "TableFormat", "backend",
-           "compute", "formats", "is_lattice", "optim", "packing", "parallel", "swiglu"]
+           "compute", "formats", "io", "is_lattice", "optim", "packing", "parallel", "swiglu"]
