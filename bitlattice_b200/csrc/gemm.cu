@@ -312,6 +312,107 @@ __device__ __forceinline__ void issue_k_tile(uint32_t q, uint32_t acc_t, uint32_
   }
 }
 
+// One asm block for the whole burst of a full k-tile of the pair kernel, so that the operand arithmetic of all 16
+// instructions can be scheduled ahead of them: 12 scale copies, 4 MMAs, and the two commits that hand the stage back
+// to the producers of both CTAs. Descriptors differ only in their low
+// words (sf_lo, a_lo, b_lo); sf_hi / op_hi are the constant high words.
+__device__ __forceinline__ void issue_k_tile_pair_block(uint32_t q, uint32_t acc_t, uint32_t sfa_t, uint32_t sfb_t,
+                                                        uint32_t sf_lo, uint32_t a_lo, uint32_t b_lo, uint32_t idesc,
+                                                        uint32_t accumulate, uint32_t sf_hi, uint32_t op_hi,
+                                                        uint32_t sfb_mma_t, uint32_t empty_local, uint32_t empty_peer) {
+  asm volatile(
+      "{\n\t"
+      ".reg .pred q, p, one;\n\t"
+      ".reg .b32 t0, t1, lo;\n\t"
+      ".reg .b64 d0, d1;\n\t"
+      "setp.ne.b32 q, %0, 0;\n\t"
+      "setp.ne.b32 p, %8, 0;\n\t"
+      "setp.eq.b32 one, 0, 0;\n\t"
+      "add.u32 t0, %2, 0;\n\t"
+      "add.u32 lo, %4, 0;\n\t"
+      "mov.b64 d0, {lo, %9};\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [t0], d0;\n\t"
+      "add.u32 t0, %3, 0;\n\t"
+      "add.u32 lo, %4, 128;\n\t"
+      "mov.b64 d0, {lo, %9};\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [t0], d0;\n\t"
+      "add.u32 t0, %3, 4;\n\t"
+      "add.u32 lo, %4, 256;\n\t"
+      "mov.b64 d0, {lo, %9};\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [t0], d0;\n\t"
+      "add.u32 t0, %2, 4;\n\t"
+      "add.u32 lo, %4, 32;\n\t"
+      "mov.b64 d0, {lo, %9};\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [t0], d0;\n\t"
+      "add.u32 t0, %3, 8;\n\t"
+      "add.u32 lo, %4, 160;\n\t"
+      "mov.b64 d0, {lo, %9};\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [t0], d0;\n\t"
+      "add.u32 t0, %3, 12;\n\t"
+      "add.u32 lo, %4, 288;\n\t"
+      "mov.b64 d0, {lo, %9};\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [t0], d0;\n\t"
+      "add.u32 t0, %2, 8;\n\t"
+      "add.u32 lo, %4, 64;\n\t"
+      "mov.b64 d0, {lo, %9};\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [t0], d0;\n\t"
+      "add.u32 t0, %3, 16;\n\t"
+      "add.u32 lo, %4, 192;\n\t"
+      "mov.b64 d0, {lo, %9};\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [t0], d0;\n\t"
+      "add.u32 t0, %3, 20;\n\t"
+      "add.u32 lo, %4, 320;\n\t"
+      "mov.b64 d0, {lo, %9};\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [t0], d0;\n\t"
+      "add.u32 t0, %2, 12;\n\t"
+      "add.u32 lo, %4, 96;\n\t"
+      "mov.b64 d0, {lo, %9};\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [t0], d0;\n\t"
+      "add.u32 t0, %3, 24;\n\t"
+      "add.u32 lo, %4, 224;\n\t"
+      "mov.b64 d0, {lo, %9};\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [t0], d0;\n\t"
+      "add.u32 t0, %3, 28;\n\t"
+      "add.u32 lo, %4, 352;\n\t"
+      "mov.b64 d0, {lo, %9};\n\t"
+      "@q tcgen05.cp.cta_group::2.32x128b.warpx4 [t0], d0;\n\t"
+      "add.u32 t0, %2, 0;\n\t"
+      "add.u32 t1, %11, 0;\n\t"
+      "add.u32 lo, %5, 0;\n\t"
+      "mov.b64 d0, {lo, %10};\n\t"
+      "add.u32 lo, %6, 0;\n\t"
+      "mov.b64 d1, {lo, %10};\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%1], d0, d1, %7, [t0], [t1], p;\n\t"
+      "add.u32 t0, %2, 4;\n\t"
+      "add.u32 t1, %11, 8;\n\t"
+      "add.u32 lo, %5, 2;\n\t"
+      "mov.b64 d0, {lo, %10};\n\t"
+      "add.u32 lo, %6, 2;\n\t"
+      "mov.b64 d1, {lo, %10};\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%1], d0, d1, %7, [t0], [t1], one;\n\t"
+      "add.u32 t0, %2, 8;\n\t"
+      "add.u32 t1, %11, 16;\n\t"
+      "add.u32 lo, %5, 4;\n\t"
+      "mov.b64 d0, {lo, %10};\n\t"
+      "add.u32 lo, %6, 4;\n\t"
+      "mov.b64 d1, {lo, %10};\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%1], d0, d1, %7, [t0], [t1], one;\n\t"
+      "add.u32 t0, %2, 12;\n\t"
+      "add.u32 t1, %11, 24;\n\t"
+      "add.u32 lo, %5, 6;\n\t"
+      "mov.b64 d0, {lo, %10};\n\t"
+      "add.u32 lo, %6, 6;\n\t"
+      "mov.b64 d1, {lo, %10};\n\t"
+      "@q tcgen05.mma.cta_group::2.kind::mxf4nvf4.block_scale.scale_vec::4X [%1], d0, d1, %7, [t0], [t1], one;\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%12];\n\t"
+      "@q tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%13];\n\t"
+      "}"
+      ::"r"(q), "r"(acc_t), "r"(sfa_t), "r"(sfb_t), "r"(sf_lo), "r"(a_lo), "r"(b_lo), "r"(idesc), "r"(accumulate),
+        "r"(sf_hi), "r"(op_hi), "r"(sfb_mma_t), "r"(empty_local), "r"(empty_peer)
+      : "memory");
+}
+
+
 template <int BN, int STAGES>
 struct GemmSmem {
   static constexpr uint32_t kA = kBM * (kBK / 2);          // 16 KiB
@@ -903,21 +1004,28 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
           const int blocks = min(4, nkb - kt * 4);
           const uint64_t adesc = operand_desc(stage), bdesc = operand_desc(stage + S::kA);
           const uint64_t sdesc = scale_desc(stage + S::kA + S::kB);
-          if (blocks == 4) {
-            issue_k_tile<2, 0, S::kBlobsB>(q, acc_t, tmem_base + kSfaCol, tmem_base + kSfbCol, sdesc, adesc, bdesc, idesc, kt != 0,
-                               sfb_first);
+          if (blocks == 4 && S::kBlobsB == 2) {
+            issue_k_tile_pair_block(q, acc_t, tmem_base + kSfaCol, tmem_base + kSfbCol, static_cast<uint32_t>(sdesc),
+                                    static_cast<uint32_t>(adesc), static_cast<uint32_t>(bdesc), idesc, kt != 0,
+                                    static_cast<uint32_t>(sdesc >> 32), static_cast<uint32_t>(adesc >> 32),
+                                    tmem_base + kSfbCol + sfb_first, empty_bar(s), empty_peer0 + 8u * s);
           } else {
-            for (int j = 0; j < blocks; ++j) {
-              tmem_copy_scales_if<2>(q, tmem_base + kSfaCol + 4 * j, sdesc + 32u * j);
-              tmem_copy_scales_if<2>(q, tmem_base + kSfbCol + 4 * S::kBlobsB * j, sdesc + 128u + 32u * j);
-              if (S::kBlobsB == 2) tmem_copy_scales_if<2>(q, tmem_base + kSfbCol + 8 * j + 4, sdesc + 256u + 32u * j);
+            if (blocks == 4) {
+              issue_k_tile<2, 0, S::kBlobsB>(q, acc_t, tmem_base + kSfaCol, tmem_base + kSfbCol, sdesc, adesc, bdesc, idesc,
+                                             kt != 0, sfb_first);
+            } else {
+              for (int j = 0; j < blocks; ++j) {
+                tmem_copy_scales_if<2>(q, tmem_base + kSfaCol + 4 * j, sdesc + 32u * j);
+                tmem_copy_scales_if<2>(q, tmem_base + kSfbCol + 4 * S::kBlobsB * j, sdesc + 128u + 32u * j);
+                if (S::kBlobsB == 2) tmem_copy_scales_if<2>(q, tmem_base + kSfbCol + 8 * j + 4, sdesc + 256u + 32u * j);
+              }
+              for (int j = 0; j < blocks; ++j)
+                mma_nvf4_if<2>(q, acc_t, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
+                               tmem_base + kSfbCol + 4 * S::kBlobsB * j + sfb_first, (kt | j) != 0);
             }
-            for (int j = 0; j < blocks; ++j)
-              mma_nvf4_if<2>(q, acc_t, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
-                             tmem_base + kSfbCol + 4 * S::kBlobsB * j + sfb_first, (kt | j) != 0);
+            mma_commit_if<2>(q, empty_bar(s));
+            mma_commit_if<2>(q, empty_peer0 + 8u * s);
           }
-          mma_commit_if<2>(q, empty_bar(s));
-          mma_commit_if<2>(q, empty_peer0 + 8u * s);
           if (kt == num_k_tiles - 1) {
             mma_commit_if<2>(q, acc_full(ab));
             mma_commit_if<2>(q, acc_full_peer0 + 8u * ab);
