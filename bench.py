@@ -11,8 +11,13 @@ gate, up: 12288x4096; down: 4096x12288} NVFP4 weights, `--tokens` tokens (defaul
 ~ N(0,1), upstream gradients ~ N(0, 1e-2^2), weights ~ N(0, 0.02^2), all synthetic and seeded. One step = for every
 linear: y = F.linear(x, W) under compute("fp4_all"), y.backward(gy) -> dgrad + wgrad, and the lattice update of W
 (colnorm direction, 4-bit phase, stochastic projection, scale refit with trust region 0.1) from the gradient hook.
-With N > 1 every weight is sharded along N (rows) over the ranks: activations are all-gathered, input gradients
-reduce-scattered (NCCL), the update is local; total work is fixed (strong scaling).
+With N > 1 every weight (codes, scales, optimizer phase) is sharded along N (rows) over the ranks and the update is
+local; total work is fixed (strong scaling). Two exchange patterns over that storage (`--parallel`):
+  column  activations all-gathered (packed), input gradients reduce-scattered, each rank computes its N/p columns;
+  token   packed weights all-gathered, weight-gradient partials reduce-scattered, each rank computes its M/p tokens;
+  auto    (default) the one that moves fewer bytes for the workload: `token` when a step has more tokens than the
+          weights have rows (65,536 tokens against 1024-12288 rows here). The line then also carries the other
+          pattern's throughput from a short run (`other_parallelism`).
 
 Prints one JSON line (rank 0). `value` is whole-job TFLOP/s with inputs resident in HBM; `e2e` is the same step with
 the step's inputs copied from pinned host memory and a checksum read back inside the timed region.
@@ -55,6 +60,8 @@ def parse():
     ap.add_argument("--tokens", type=int, default=16 * 4096)
     ap.add_argument("--layers", type=int, default=36)
     ap.add_argument("--cpu-tokens", type=int, default=16384, help="tokens of the bounded CPU sample")
+    ap.add_argument("--parallel", default="auto", choices=["auto", "column", "token"],
+                    help="exchange pattern of the N-sharded weights at N > 1")
     return ap.parse_args()
 
 
@@ -178,12 +185,15 @@ def run_ours(a):
     import torch
     import torch.distributed as dist
     import bitlattice_b200 as bl
-    from bitlattice_b200 import _C
-    from bitlattice_b200.parallel import column_parallel_linears, shard_rows
+    from bitlattice_b200 import _C, backend
+    from bitlattice_b200.parallel import GatheredWeights, column_parallel_linears, shard_rows, token_parallel_linears
 
     world = int(os.environ.get("WORLD_SIZE", "1"))
     rank = int(os.environ.get("RANK", "0"))
     local = int(os.environ.get("LOCAL_RANK", "0"))
+    # backward (and the update hooks) on the calling thread: with a few hundred launches per layer the hand-over to
+    # autograd's device thread and back costs more host time than it hides
+    torch.autograd.set_multithreading_enabled(False)
     torch.cuda.set_device(local)
     dev = torch.device("cuda", local)
     if world > 1:
@@ -208,94 +218,116 @@ def run_ours(a):
             params.append(p)
             meta.append((name, N, K))
     opt = bl.Lattice(params, fused_backward=True, **OPT)
-
-    # inputs: token shard of x per distinct K, feature shard of gy per distinct N
-    gen = torch.Generator(device=dev).manual_seed(7 + rank)
-    xs = {name: torch.randn(Ms, K, device=dev, generator=gen).to(torch.bfloat16) for name, K in INPUT_WIDTH.items()}
-    gys = {N: (torch.randn(M, N // world, device=dev, generator=gen) * 1e-2).to(torch.bfloat16)
-           for N in (4096, 1024, 12288)}
-    host = {k: v.cpu().pin_memory() for k, v in {**{("x", name): t for name, t in xs.items()},
-                                                 **{("g", N): t for N, t in gys.items()}}.items()}
-    h2d_bytes = sum(t.numel() * t.element_size() for t in host.values())
     flops = sum(6.0 * M * N * K for _, N, K in meta)
     weights = sum(N * K for _, N, K in meta)
     group = dist.group.WORLD if world > 1 else None
-
-    # End to end, the inputs of step i + 1 are copied from pinned host memory on a second stream while step i
-    # computes (two sets of device buffers); the first step's copy has nothing to hide behind.
-    sets = [(xs, gys)]
+    # bytes crossing NVLink per step and rank, to pick the pattern: activations (column) against weights (token)
+    moved = {"column": sum(3.125 * M * K for _, N, K in meta), "token": sum(3.125 * N * K for _, N, K in meta)}
+    mode = a.parallel if a.parallel != "auto" else min(moved, key=moved.get)
+    backend.set_sr_seed(1 + (rank << 20))               # ranks draw different stochastic-rounding streams
     copy_stream = torch.cuda.Stream(device=dev)
+    order = [[params[li * len(LAYER) + INDEX[n]] for n in names] for li in range(a.layers) for names in GROUPS]
 
-    def copy_in(k):
-        while len(sets) <= k:
-            sets.append(({n: torch.empty_like(t) for n, t in xs.items()}, {n: torch.empty_like(t) for n, t in gys.items()}))
-        with torch.cuda.stream(copy_stream):
-            for name, t in sets[k][0].items():
-                t.copy_(host[("x", name)], non_blocking=True)
-            for N, t in sets[k][1].items():
-                t.copy_(host[("g", N)], non_blocking=True)
-            ev = torch.cuda.Event()
-            ev.record(copy_stream)
-        return ev
+    def measure(mode, steps, warmup, clocks=None):
+        """Warm up, time `steps` steps with inputs resident in HBM, then the same end to end from pinned host memory."""
+        # inputs: this rank's tokens of x per distinct K; gy as the layer's output is laid out under `mode`
+        gen = torch.Generator(device=dev).manual_seed(7 + rank)
+        xs = {name: torch.randn(Ms, K, device=dev, generator=gen).to(torch.bfloat16) for name, K in INPUT_WIDTH.items()}
+        gshape = (lambda N: (M, N // world)) if mode == "column" else (lambda N: (Ms, N))
+        gys = {N: (torch.randn(*gshape(N), device=dev, generator=gen) * 1e-2).to(torch.bfloat16)
+               for N in (4096, 1024, 12288)}
+        host = {k: v.cpu().pin_memory() for k, v in {**{("x", name): t for name, t in xs.items()},
+                                                     **{("g", N): t for N, t in gys.items()}}.items()}
+        h2d_bytes = sum(t.numel() * t.element_size() for t in host.values())
+        gathered = GatheredWeights(group, limit_bytes=1 << 30) if mode == "token" and world > 1 else None
 
-    def step(from_host: bool, bufs=None):
-        cur_x, cur_g = bufs or sets[0]
-        check = torch.zeros((), device=dev)
-        with bl.compute("fp4_all"):
-            for li in range(a.layers):
-                xin = {name: t.detach().requires_grad_(True) for name, t in cur_x.items()}
-                for names in GROUPS:                   # forward + backward of the projections that share an input
-                    ps = [params[li * len(LAYER) + INDEX[n]] for n in names]
-                    ys = column_parallel_linears(xin[INPUT_OF[names[0]]], ps, group)
-                    torch.autograd.backward(ys, [cur_g[SHAPE[n][0]] for n in names])
-                if from_host:
-                    check = check + xin["attn_in"].grad[0, :8].float().sum()
-        opt.step()
-        return float(check.item()) if from_host else 0.0      # the device -> host read of the step's result
+        # End to end, the inputs of step i + 1 are copied from pinned host memory on a second stream while step i
+        # computes (two sets of device buffers); the first step's copy has nothing to hide behind.
+        sets = [(xs, gys)]
 
-    def run_steps(n, from_host):
-        if not from_host:
-            for _ in range(n):
-                step(False)
-            return
-        ev = copy_in(0)
-        for i in range(n):
-            torch.cuda.current_stream().wait_event(ev)
-            if i + 1 < n:
-                ev = copy_in((i + 1) % 2)                   # safe: step i - 1, the last user of that set, has ended
-            step(True, sets[i % 2])
+        def copy_in(k):
+            while len(sets) <= k:
+                sets.append(({n: torch.empty_like(t) for n, t in xs.items()},
+                             {n: torch.empty_like(t) for n, t in gys.items()}))
+            with torch.cuda.stream(copy_stream):
+                for name, t in sets[k][0].items():
+                    t.copy_(host[("x", name)], non_blocking=True)
+                for N, t in sets[k][1].items():
+                    t.copy_(host[("g", N)], non_blocking=True)
+                ev = torch.cuda.Event()
+                ev.record(copy_stream)
+            return ev
 
-    def timed(n, from_host):
-        if world > 1:
-            dist.barrier()
-        torch.cuda.synchronize()
-        s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
-        s.record()
-        run_steps(n, from_host)
-        e.record()
-        torch.cuda.synchronize()
-        if world > 1:
-            dist.barrier()
-        t = torch.tensor([s.elapsed_time(e)], device=dev)
-        if world > 1:
-            dist.all_reduce(t, op=dist.ReduceOp.MAX)
-        return t.item() / 1e3
+        def step(from_host: bool, bufs=None):
+            cur_x, cur_g = bufs or sets[0]
+            check = torch.zeros((), device=dev)
+            with bl.compute("fp4_all"):
+                for li in range(a.layers):
+                    xin = {name: t.detach().requires_grad_(True) for name, t in cur_x.items()}
+                    for gi, names in enumerate(GROUPS):    # forward + backward of the projections sharing an input
+                        ps = order[li * len(GROUPS) + gi]
+                        if gathered is not None:
+                            # the next group's weights (already updated in this or the previous step) are gathered
+                            # while this group computes
+                            gathered.prefetch(order[(li * len(GROUPS) + gi + 1) % len(order)])
+                            ys = token_parallel_linears(xin[INPUT_OF[names[0]]], ps, gathered)
+                        else:
+                            ys = column_parallel_linears(xin[INPUT_OF[names[0]]], ps, group)
+                        torch.autograd.backward(ys, [cur_g[SHAPE[n][0]] for n in names])
+                    if from_host:
+                        check = check + xin["attn_in"].grad[0, :8].float().sum()
+            opt.step()
+            return float(check.item()) if from_host else 0.0      # the device -> host read of the step's result
 
-    for _ in range(max(a.warmup, 3)):
-        step(False)
-    clocks = Clocks(local)
-    if rank == 0:
-        clocks.start()
-    _C.Counters.reset(timed={"bl_nvfp4_gemm", "bl_nvfp4_lattice_update"})
-    secs = timed(a.steps, False)
-    launches = _C.Counters.launches
-    gemm_ms, gemm_calls = _C.Counters.elapsed_ms("bl_nvfp4_gemm")
-    upd_ms, upd_calls = _C.Counters.elapsed_ms("bl_nvfp4_lattice_update")
-    _C.Counters.reset()
-    clock_info = clocks.stop() if rank == 0 else None
-    run_steps(2, True)
-    e2e_steps = max(2, min(a.steps, 5))
-    e2e_secs = timed(e2e_steps, True)
+        def run_steps(n, from_host):
+            if not from_host:
+                for _ in range(n):
+                    step(False)
+                return
+            ev = copy_in(0)
+            for i in range(n):
+                torch.cuda.current_stream().wait_event(ev)
+                if i + 1 < n:
+                    ev = copy_in((i + 1) % 2)               # safe: step i - 1, the last user of that set, has ended
+                step(True, sets[i % 2])
+
+        def timed(n, from_host):
+            if world > 1:
+                dist.barrier()
+            torch.cuda.synchronize()
+            s, e = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            s.record()
+            run_steps(n, from_host)
+            e.record()
+            torch.cuda.synchronize()
+            if world > 1:
+                dist.barrier()
+            t = torch.tensor([s.elapsed_time(e)], device=dev)
+            if world > 1:
+                dist.all_reduce(t, op=dist.ReduceOp.MAX)
+            return t.item() / 1e3
+
+        for _ in range(warmup):
+            step(False)
+        if clocks is not None:
+            clocks.start()
+        _C.Counters.reset(timed={"bl_nvfp4_gemm", "bl_nvfp4_lattice_update"})
+        secs = timed(steps, False)
+        r = {"secs": secs, "steps": steps, "launches": _C.Counters.launches, "h2d_bytes": h2d_bytes}
+        r["gemm_ms"], r["gemm_calls"] = _C.Counters.elapsed_ms("bl_nvfp4_gemm")
+        r["upd_ms"], r["upd_calls"] = _C.Counters.elapsed_ms("bl_nvfp4_lattice_update")
+        _C.Counters.reset()
+        r["clocks"] = clocks.stop() if clocks is not None else None
+        run_steps(2, True)
+        r["e2e_steps"] = max(2, min(steps, 5))
+        r["e2e_secs"] = timed(r["e2e_steps"], True)
+        return r
+
+    res = measure(mode, a.steps, max(a.warmup, 3), Clocks(local) if rank == 0 else None)
+    other = None
+    if world > 1 and a.parallel == "auto":
+        other_mode = "column" if mode == "token" else "token"
+        other = measure(other_mode, 1, 3)
     status = bl._ops.gemm_status(local)
     if world > 1:
         dist.barrier()
@@ -305,12 +337,17 @@ def run_ours(a):
         return
 
     peaks = measured_peaks()
-    per_step = secs / a.steps
+    per_step = res["secs"] / a.steps
     fp4_peak = 4.0 * peaks["bf16_sustained"]
+    gemm_ms, upd_ms = res["gemm_ms"], res["upd_ms"]
     gemm_flops_rank = a.steps * flops / world                     # this rank's share of the contraction work
     gemm_tf = gemm_flops_rank / (gemm_ms / 1e3) / 1e12 if gemm_ms else None
     upd_bytes_rank = a.steps * weights * BYTES_PER_WEIGHT / world
     upd_gbs = upd_bytes_rank / (upd_ms / 1e3) / 1e9 if upd_ms else None
+    names = {"column": "N-sharded weights, column-parallel compute: packed activations all-gathered, input gradients "
+                       "reduce-scattered",
+             "token": "N-sharded weights, token-parallel compute: packed weights all-gathered, weight-gradient "
+                      "partials reduce-scattered"}
     out = {
         "metric": "nvfp4_linear_fwd_bwd_tflops", "value": flops / per_step / 1e12, "unit": "TFLOP/s",
         "n_gpus": world, "steps": a.steps, "warmup": max(a.warmup, 3), "ms_per_step": per_step * 1e3,
@@ -320,24 +357,31 @@ def run_ours(a):
                    "linears_per_layer": [f"{n}:{N}x{K}" for n, N, K in LAYER],
                    "activations_per_layer": "4 distinct (q/k/v share one, gate/up share one, o and down their own)",
                    "update": OPT,
-                   "parallelism": f"N-sharded x{world}" if world > 1 else "single GPU",
-                   "l2": "inputs larger than L2 (weights, activations and gradients of a step exceed 126 MB)"},
-        "e2e": {"value": flops / (e2e_secs / e2e_steps) / 1e12, "unit": "TFLOP/s", "h2d_bytes_per_step": h2d_bytes,
-                "d2h_bytes_per_step": 4, "steps": e2e_steps},
-        "gpu_launches": launches,
+                   "parallelism": f"x{world}: {names[mode]}" if world > 1 else "single GPU",
+                   "nvlink_bytes_per_step_per_rank": {k: v * (world - 1) / world for k, v in moved.items()}
+                   if world > 1 else None,
+                   "l2": "inputs larger than L2 (weights, activations and gradients of a step exceed 126 MB)",
+                   "host": "one Python thread per rank (autograd multithreading off)"},
+        "e2e": {"value": flops / (res["e2e_secs"] / res["e2e_steps"]) / 1e12, "unit": "TFLOP/s",
+                "h2d_bytes_per_step": res["h2d_bytes"], "d2h_bytes_per_step": 4, "steps": res["e2e_steps"]},
+        "gpu_launches": res["launches"],
         "gemm_error_flag": status,
-        "clocks": clock_info,
+        "clocks": res["clocks"],
         "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel (tcgen05 mxf4nvf4, cta_group::2, 256x256 tiles)", "achieved": gemm_tf,
                      "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tf / fp4_peak if gemm_tf else None,
-                     "traffic": None, "launches": gemm_calls,
+                     "traffic": None, "launches": res["gemm_calls"],
                      "peak_note": f"4 x bf16 sustained cuBLAS ({peaks['source']}); nominal dense FP4 9000",
                      "frac_of_nominal": gemm_tf / 9000.0 if gemm_tf else None},
-        "update": {"metric": "lattice_update_hbm_gbs", "value": upd_gbs, "unit": "GB/s", "calls": upd_calls,
+        "update": {"metric": "lattice_update_hbm_gbs", "value": upd_gbs, "unit": "GB/s", "calls": res["upd_calls"],
                    "bytes_per_weight": BYTES_PER_WEIGHT,
                    "roofline": {"bound": "hbm", "achieved": upd_gbs, "peak": peaks["hbm"], "unit": "GB/s",
                                 "frac": upd_gbs / peaks["hbm"] if upd_gbs else None, "traffic": None,
                                 "peak_note": f"copy bandwidth ({peaks['source']}); nominal 8000"}},
     }
+    if other is not None:
+        out["other_parallelism"] = {"parallelism": names[other_mode], "steps": other["steps"],
+                                    "value": flops / (other["secs"] / other["steps"]) / 1e12, "unit": "TFLOP/s",
+                                    "ms_per_step": other["secs"] / other["steps"] * 1e3}
     if world == 1:
         t, cflops, _, threads = cpu_sample(a.cpu_tokens)
         out["cpu_baseline"] = {"value": cflops / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",

@@ -82,11 +82,20 @@ def lib() -> ctypes.CDLL:
 
 
 def ptr(t: torch.Tensor | None):
-    return None if t is None else ctypes.c_void_p(t.data_ptr())
+    """Device address as a plain int (ctypes converts it for a void* parameter), None for an absent tensor."""
+    return None if t is None else t.data_ptr()
 
 
-def stream_of(t: torch.Tensor) -> ctypes.c_void_p:
-    return ctypes.c_void_p(torch.cuda.current_stream(t.device).cuda_stream)
+_raw_stream = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+
+
+def stream_of(t: torch.Tensor):
+    """The current CUDA stream of the tensor's device as a raw handle. These wrappers run a few hundred times per
+    training step, so the handle comes from torch's raw query where it exists instead of a Stream object."""
+    index = t.device.index
+    if _raw_stream is not None and index is not None:
+        return _raw_stream(index)
+    return torch.cuda.current_stream(t.device).cuda_stream
 
 
 def device_of(t: torch.Tensor) -> int:

@@ -190,7 +190,8 @@ def direction(G, kind: str, r=None, c=None, k: int = 1, beta2: float = 0.95, blo
 # ------------------------------------------------------------------------------------------------ operand quantizers
 
 def blocked_scale_bytes(rows: int, cols16: int) -> int:
-    return int(_C.lib().bl_blocked_scale_bytes(rows, cols16))
+    """Bytes of the 128x4-tiled scale layout (== bl_blocked_scale_bytes of the library; tests compare the two)."""
+    return ((rows + 127) // 128) * ((cols16 + 3) // 4) * 512
 
 
 def amax_global(x: torch.Tensor) -> torch.Tensor:
@@ -264,7 +265,10 @@ def quantize_nvfp4_t(x: torch.Tensor, hadamard: torch.Tensor | None, seed: int =
     gout = torch.empty(1, dtype=torch.float32, device=x.device)
     bound = amax = None
     if global_scale is not None:
-        bound = _require(global_scale.to(torch.float32).reshape(1).contiguous(), "global_scale")
+        bound = global_scale
+        if bound.dtype != torch.float32 or bound.numel() != 1 or not bound.is_contiguous():
+            bound = bound.to(torch.float32).reshape(1).contiguous()
+        _require(bound, "global_scale")
     else:
         amax = torch.empty(4, dtype=torch.float32, device=x.device)
     _C.call("bl_nvfp4_quantize_t", _C.ptr(x), _C.DTYPE[x.dtype], M, K, _C.ptr(hadamard), int(seed),
@@ -278,7 +282,10 @@ def requantize_nvfp4_t(packed: torch.Tensor, scales: torch.Tensor, global_scale:
     (reference: torch.ops.bitlattice.requantize_nvfp4_t)."""
     _require(packed, "packed", torch.uint8)
     _require(scales, "scales")
-    g = _require(global_scale.to(torch.float32).reshape(1).contiguous(), "global_scale")
+    g = global_scale
+    if g.dtype != torch.float32 or g.numel() != 1 or not g.is_contiguous():
+        g = g.to(torch.float32).reshape(1).contiguous()
+    _require(g, "global_scale")
     N, K = packed.shape[0], packed.shape[1] * 2
     out = torch.empty(K, N // 2, dtype=torch.uint8, device=packed.device)
     osc = _scale_buffer(K, N // 16, blocked, packed.device)
@@ -314,8 +321,8 @@ def nvfp4_gemm(a_packed, a_sf, a_global, b_packed, b_sf, b_global, out_dtype=tor
         raise RuntimeError(f"operand K mismatch: {K} vs {b_packed.shape[1] * 2}")
     if a_sf.numel() < blocked_scale_bytes(M, K // 16) or b_sf.numel() < blocked_scale_bytes(N, K // 16):
         raise RuntimeError("scale buffers are smaller than the blocked layout of their operands")
-    ga = _require(a_global.reshape(-1), "a_global", torch.float32)
-    gb = _require(b_global.reshape(-1), "b_global", torch.float32)
+    ga = _require(a_global, "a_global", torch.float32)
+    gb = _require(b_global, "b_global", torch.float32)
     if out is None:
         out = torch.empty(M, N, dtype=out_dtype, device=a_packed.device)
     _C.call("bl_nvfp4_gemm", _C.ptr(a_packed), _C.ptr(a_sf), _C.ptr(ga), _C.ptr(b_packed), _C.ptr(b_sf), _C.ptr(gb),

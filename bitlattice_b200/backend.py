@@ -162,7 +162,9 @@ def fp4_mm(a: Fp4Operand, b: Fp4Operand, out_dtype: torch.dtype = torch.bfloat16
     ``out_dtype`` output, both per-tensor scales applied in the epilogue (reference: backend.py:280-290)."""
     sa = a.scales if a.blocked else to_blocked(a.scales)
     sb = b.scales if b.blocked else to_blocked(b.scales)
-    return _ops.nvfp4_gemm(a.packed, sa, a.global_scale.float(), b.packed, sb, b.global_scale.float(), out_dtype)
+    ga, gb = a.global_scale, b.global_scale
+    return _ops.nvfp4_gemm(a.packed, sa, ga if ga.dtype == torch.float32 else ga.float(), b.packed, sb,
+                           gb if gb.dtype == torch.float32 else gb.float(), out_dtype)
 
 
 # per-weight operands, kept while the weight is unchanged (the role of the reference's backend.py:293-342)

@@ -17,16 +17,36 @@ bf16 activations: 0.5625 bytes per element instead of 2, and the quantization wo
 The collectives are NCCL's (``torch.distributed``) over NVLink; gathered operands land in local HBM before any
 kernel reads them. ``gloo`` works for CPU tests of the bookkeeping. With ``group=None`` or a world of one the layer
 degenerates to the plain lattice linear.
+
+A second exchange pattern over the SAME storage (weights and optimizer state sharded along N, communication-free
+update) is ``token_parallel_linear(s)``: every rank keeps its tokens and runs the whole layer on them against the
+all-gathered packed weight, and the weight-gradient partials are reduce-scattered to the shard owners,
+
+    forward   W_r codes + scales  --all-gather (0.5625 B/weight)-->  W [N, K];      y = x_r W^T   [M/p, N]
+    dgrad     re-quantized W_r^T  --all-gather-->  W^T [K, N];                       gx_r = gy_r W  [M/p, K]
+    wgrad     gw_partial_r = gy_r^T x_r  [N, K]    --reduce-scatter (sum)-->          gw [N/p, K]
+    update    as above
+
+which moves weight-sized instead of activation-sized messages (about 3.1 N K bytes per layer and step -- 1.125 N K
+of packed operands gathered, 2 N K of bf16 partials scattered -- against 3.1 M K): the better choice when a step has
+more tokens M than the weight has rows N. A rank's layer is exactly the single-GPU layer on
+its tokens -- its own per-tensor scales and stochastic-rounding draws, i.e. the ranks are the micro-batches of the
+reference's gradient accumulation (``Lattice.accumulate``: the gradient is the sum over micro-batches in the
+weight's dtype).
 """
 from __future__ import annotations
+
+import weakref
+from collections import OrderedDict
 
 import torch
 import torch.distributed as dist
 
 from .tensor import LatticeTensor
 
-__all__ = ["ColumnParallelFp4Linear", "ColumnParallelLinear", "column_parallel_linear", "column_parallel_linears",
-           "gathered_input_operands", "shard_bounds", "shard_rows", "world"]
+__all__ = ["ColumnParallelFp4Linear", "ColumnParallelLinear", "GatheredWeights", "TokenParallelFp4Linear",
+           "TokenParallelLinear", "column_parallel_linear", "column_parallel_linears", "gathered_input_operands",
+           "shard_bounds", "shard_rows", "token_parallel_linear", "token_parallel_linears", "world"]
 
 
 def world(group=None) -> tuple[int, int]:
@@ -250,3 +270,253 @@ def column_parallel_linears(x_shard: torch.Tensor, weights, group=None) -> tuple
         if all(r is not None for r in recipes) and all(r == recipes[0] for r in recipes):
             return ColumnParallelFp4Linear.apply(x_shard, group, recipes[0], *weights)
     return tuple(column_parallel_linear(x_shard, w, group) for w in weights)
+
+
+# ------------------------------------------------------------------------------------ token-parallel, gathered weights
+
+class _GatheredEntry:
+    __slots__ = ("version", "ref", "work", "row", "t_parts", "t", "nbytes")
+
+
+class _Coalesced:
+    """Several collectives of one kind issued as a single NCCL group (one launch, one host call); ``wait`` makes the
+    current stream wait for all of them. Falls back to one call per collective on backends without the fast path."""
+
+    def __init__(self, fn, pairs, group, **kw):
+        self.works = []
+        if len(pairs) > 1 and pairs[0][0].is_cuda and hasattr(dist, "_coalescing_manager"):
+            with dist._coalescing_manager(group, async_ops=True) as cm:
+                for out, inp in pairs:
+                    fn(out, inp, group=group, **kw)
+            self.works.append(cm)
+        else:
+            self.works = [fn(out, inp, group=group, async_op=True, **kw) for out, inp in pairs]
+        self.keep = pairs                                   # inputs stay alive until the wait
+
+    def wait(self) -> None:
+        for w in self.works:
+            w.wait()
+        self.works, self.keep = [], None
+
+
+class GatheredWeights:
+    """GEMM operands of the full weight assembled from the ranks' row shards: W [N, K] for the forward and the
+    re-quantized W^T [K, N] for the input gradient, valid for one weight version (``_bl_version``). The all-gathers run
+    asynchronously, those of the weights of one ``prefetch`` call as a single NCCL group; prefetching the weights
+    needed next lets them finish under other work. Entries are dropped least recently used beyond ``limit_bytes``;
+    weights are held weakly."""
+
+    def __init__(self, group=None, limit_bytes: int = 4 << 30):
+        self.group, self.limit, self.used = group, limit_bytes, 0
+        self.entries: OrderedDict = OrderedDict()
+
+    def _remove(self, key) -> None:
+        self.used -= self.entries.pop(key).nbytes
+
+    def clear(self) -> None:
+        self.entries.clear()
+        self.used = 0
+
+    def _current(self, w):
+        e = self.entries.get(id(w))
+        if e is not None:
+            if e.version == getattr(w, "_bl_version", 0) and e.ref() is w:
+                self.entries.move_to_end(id(w))
+                return e
+            self._remove(id(w))
+        return None
+
+    def prefetch(self, weights) -> None:
+        """Start the gathers of every weight of ``weights`` whose current version is not here yet."""
+        from . import _ops, backend
+        todo = [w for w in weights if self._current(w) is None]
+        if not todo:
+            return
+        size = world(self.group)[1]
+        pairs, made = [], []
+        for w in todo:
+            n, K = w.shape
+            if n % 128 or K % 64:
+                raise ValueError(f"a [{n}, {K}] shard cannot be gathered as packed operands (rows % 128, cols % 64)")
+            dev = w.packed.device
+            local = backend.weight_operand(w)                  # 128-row scale tiles are whole: shards concatenate
+            lsf = local.scales.view(torch.uint8).reshape(-1)
+            codes = torch.empty(size * n, K // 2, dtype=torch.uint8, device=dev)
+            sf = torch.empty(size * lsf.numel(), dtype=torch.uint8, device=dev)
+            # W_r^T [K, n] is a column slice of W^T: gathered as [p, K, n/2] and [p, K, n/16], permuted into place
+            # on first use
+            tp, ts, tg = _ops.requantize_nvfp4_t(w.packed, w.scales, w.global_scale, blocked=False)
+            ts = ts.view(torch.uint8)
+            tcodes = torch.empty(size, *tp.shape, dtype=torch.uint8, device=dev)
+            tsf = torch.empty(size, *ts.shape, dtype=torch.uint8, device=dev)
+            pairs += [(codes, w.packed), (sf, lsf), (tcodes, tp), (tsf, ts)]
+            e = _GatheredEntry()
+            e.version, e.ref = getattr(w, "_bl_version", 0), weakref.ref(w)
+            e.row = backend.Fp4Operand(codes, sf, w.global_scale.float(), True)
+            e.t_parts, e.t = (tcodes, tsf, tg, K, size * n), None
+            e.nbytes = 2 * (codes.numel() + sf.numel())
+            made.append((w, e))
+        work = _Coalesced(dist.all_gather_into_tensor, pairs, self.group)
+        for w, e in made:
+            e.work = work
+            self.entries[id(w)] = e
+            self.used += e.nbytes
+        while self.used > self.limit and len(self.entries) > len(made):
+            self._remove(next(iter(self.entries)))
+
+    def _entry(self, w) -> _GatheredEntry:
+        e = self._current(w)
+        if e is None:
+            self.prefetch((w,))
+            e = self.entries[id(w)]
+        if e.work is not None:
+            e.work.wait()
+            e.work = None
+        return e
+
+    def operand(self, w):
+        """W [N, K] of the current version as a GEMM operand."""
+        return self._entry(w).row
+
+    def t_operand(self, w):
+        """W^T [K, N], re-quantized along N, of the current version as a GEMM operand."""
+        from . import _ops, backend
+        e = self._entry(w)
+        if e.t is None:
+            tcodes, tsf, tg, K, N = e.t_parts
+            e.t = backend.Fp4Operand(tcodes.permute(1, 0, 2).reshape(K, N // 2),
+                                     _ops.to_blocked(tsf.permute(1, 0, 2).reshape(K, N // 16)), tg, True)
+            e.t_parts = None
+        return e.t
+
+
+class TokenParallelFp4Linear(torch.autograd.Function):
+    """The 'fp4_all' route of one or more N-sharded weights that read the same input, on this rank's tokens: the plain
+    layer's quantizers and GEMMs against the gathered weight operands; the weight-gradient partials leave through
+    asynchronous reduce-scatters that run under the input-gradient GEMMs."""
+
+    @staticmethod
+    def forward(ctx, x, gathered, recipe, *weights):
+        from . import backend
+        need_w = any(ctx.needs_input_grad[3:])
+        K = x.shape[-1]
+        M = x.numel() // K
+        if need_w:
+            xq, xt = backend._shared(x, recipe, "fwd+t", lambda: backend._input_operands(x, recipe))
+        else:
+            xq = backend._shared(x, recipe, "fwd", lambda: backend._act_operand(
+                backend._pad_rows(x.reshape(-1, K), 16).contiguous(), recipe))
+            xt = None
+        ctx.gathered, ctx.weights, ctx.recipe, ctx.xt = gathered, weights, recipe, xt
+        ctx.x_meta = (x.shape, x.dtype)
+        size = world(gathered.group)[1]
+        return tuple(backend.fp4_mm(xq, gathered.operand(w), x.dtype)[:M].reshape(*x.shape[:-1], size * w.shape[0])
+                     for w in weights)
+
+    @staticmethod
+    def backward(ctx, *gys):
+        from . import backend
+        shape, dtype = ctx.x_meta
+        group = ctx.gathered.group
+        size = world(group)[1]
+        need_x = ctx.needs_input_grad[0]
+        staged, gws, pairs = [], [], []
+        for i, (w, gy) in enumerate(zip(ctx.weights, gys)):
+            need_w = gy is not None and ctx.needs_input_grad[3 + i] and ctx.xt is not None
+            if gy is None or not (need_x or need_w):
+                staged.append(None)
+                gws.append(None)
+                continue
+            N = gy.shape[-1]
+            g2 = gy.reshape(-1, N)
+            g2p = backend._pad_rows(g2, 32).contiguous()
+            gq = backend.quantize_fp4(g2p, stochastic=True) if need_x else None
+            staged.append((gq, g2.shape[0]))
+            if not need_w:
+                gws.append(None)
+                continue
+            part = backend.fp4_wgrad(g2p, gq, ctx.xt, w, ctx.recipe).to(w.dtype).contiguous()      # [N, K]
+            out = torch.empty(N // size, part.shape[1], dtype=part.dtype, device=part.device)
+            pairs.append((out, part))
+            gws.append(out)
+        # the partials of all weights leave as one NCCL group and are summed while the input gradients are computed
+        work = _Coalesced(dist.reduce_scatter_tensor, pairs, group, op=dist.ReduceOp.SUM) if pairs else None
+        gx = None
+        if need_x:
+            for w, st in zip(ctx.weights, staged):
+                if st is None:
+                    continue
+                gi = backend.fp4_mm(st[0], ctx.gathered.t_operand(w), dtype)[:st[1]]
+                gx = gi if gx is None else gx.add_(gi)
+            if gx is not None:
+                gx = gx.reshape(shape)
+        if work is not None:
+            work.wait()
+        return (gx, None, None, *gws)
+
+
+def _gather_weight_rows(w, group, requires_grad: bool):
+    """The full weight from the ranks' row shards as a fresh leaf: a dense tensor, or a LatticeTensor built from the
+    gathered parts."""
+    if not isinstance(w, LatticeTensor):
+        return _all_gather_rows(w.detach(), group).requires_grad_(requires_grad)
+    packed = _all_gather_rows(w.packed, group)
+    scales = _all_gather_rows(w.scales.view(torch.uint8), group).view(w.scales.dtype)
+    full = LatticeTensor(packed, scales, w.global_scale, None, w.fmt, (packed.shape[0], *w.shape[1:]), w.dtype,
+                         requires_grad=requires_grad)
+    full.compute = w.compute
+    return full
+
+
+class TokenParallelLinear(torch.autograd.Function):
+    """y = x_r all_gather(W)^T on this rank's tokens with the matching backward (the weight gradient is
+    reduce-scattered to the shard owners); ``linear`` is the local layer."""
+
+    @staticmethod
+    def forward(ctx, x, w, group, linear):
+        wf = _gather_weight_rows(w, group, w.requires_grad)
+        with torch.enable_grad():
+            xin = x.detach().requires_grad_(x.requires_grad)
+            y = linear(xin, wf)
+        ctx.group, ctx.xin, ctx.wf, ctx.y = group, xin, wf, y
+        return y.detach()
+
+    @staticmethod
+    def backward(ctx, gy):
+        inputs = [t for t in (ctx.xin, ctx.wf) if t.requires_grad]
+        grads = torch.autograd.grad(ctx.y, inputs, gy, allow_unused=True) if inputs else ()
+        it = iter(grads)
+        gx = next(it) if ctx.xin.requires_grad else None
+        gw = next(it) if ctx.wf.requires_grad else None
+        if gw is not None:
+            gw = _reduce_scatter_rows(gw, ctx.group)
+        return gx, gw, None, None
+
+
+def token_parallel_linear(x: torch.Tensor, w: torch.Tensor, gathered: GatheredWeights | None = None, group=None,
+                          linear=None) -> torch.Tensor:
+    """This rank's tokens [M/p, K], row-sharded weight [N/p, K] -> this rank's outputs [M/p, N]. ``gathered`` keeps the
+    gathered operands of the FP4 route between calls (and carries the process group)."""
+    return token_parallel_linears(x, (w,), gathered, group, linear)[0]
+
+
+def token_parallel_linears(x: torch.Tensor, weights, gathered: GatheredWeights | None = None, group=None,
+                           linear=None) -> tuple:
+    """Several token-parallel layers on one input (q/k/v, gate/up). On the 'fp4_all' route they share one quantization
+    of the input; call backward on all outputs together so that the reduce-scatters of their weight gradients run
+    under the input-gradient GEMMs."""
+    weights = tuple(weights)
+    if gathered is not None:
+        group = gathered.group
+    fn = linear or torch.nn.functional.linear
+    if world(group)[1] == 1:
+        return tuple(fn(x, w) for w in weights)
+    if linear is None and x.is_cuda and all(isinstance(w, LatticeTensor) for w in weights):
+        from .compute_policy import route
+        routes = [route(x, w) for w in weights]
+        if all(r[0] == "fp4_all" for r in routes) and all(r[1].nvfp4 == routes[0][1].nvfp4 for r in routes) \
+                and all(w.shape[0] % 128 == 0 and w.shape[1] % 64 == 0 for w in weights):
+            if gathered is None:
+                gathered = GatheredWeights(group)
+            return TokenParallelFp4Linear.apply(x, gathered, routes[0][1].nvfp4, *weights)
+    return tuple(TokenParallelLinear.apply(x, w, group, fn) for w in weights)

@@ -20,6 +20,10 @@ from . import formats as F
 __all__ = ["LatticeTensor", "is_lattice", "to_parameter"]
 
 _PARTS = ("packed", "scales", "global_scale")
+# torch's own "no override" implementation of __torch_function__ (what nn.Parameter uses): attribute reads such as
+# .shape or .grad on a lattice parameter happen dozens of times per layer call and should cost what they cost on a
+# plain tensor
+_plain_torch_function = torch._C._disabled_torch_function_impl
 
 
 def is_lattice(t) -> bool:
@@ -119,8 +123,7 @@ class LatticeTensor(torch.Tensor):
             b = args[2] if len(args) > 2 else kwargs.get("bias")
             if isinstance(w, LatticeTensor) and not isinstance(x, LatticeTensor):
                 return _LatticeLinear.apply(x, w, b)
-        with torch._C.DisableTorchFunctionSubclass():
-            return func(*args, **kwargs)
+        return _plain_torch_function(func, types, args, kwargs)     # everything else: as for a plain tensor
 
     @classmethod
     def __torch_dispatch__(cls, func, types, args=(), kwargs=None):

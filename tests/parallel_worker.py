@@ -16,12 +16,69 @@ import torch.distributed as dist
 sys.path.insert(0, os.path.dirname(os.path.dirname(os.path.abspath(__file__))))
 import bitlattice_b200 as bl                                    # noqa: E402
 from bitlattice_b200 import backend                             # noqa: E402
-from bitlattice_b200.parallel import (column_parallel_linear, column_parallel_linears,     # noqa: E402
-                                      gathered_input_operands, shard_rows)
+from bitlattice_b200.parallel import (GatheredWeights, column_parallel_linear, column_parallel_linears,   # noqa: E402
+                                      gathered_input_operands, shard_rows, token_parallel_linear,
+                                      token_parallel_linears)
 
 
 def rel(a, b):
     return float((a.float() - b.float()).norm() / b.float().norm())
+
+
+def token_parallel_checks(rank, world, dev, w, x, gy, w2, gy2):
+    M, N = gy.shape
+    rows = slice(rank * M // world, (rank + 1) * M // world)
+    cols = slice(rank * N // world, (rank + 1) * N // world)
+    xr, gr = x[rows].contiguous(), gy[rows].contiguous()
+    gathered = GatheredWeights(None)
+    p = torch.nn.Parameter(shard_rows(w, rank, world))
+    p._bl_row_offset = rank * N // world
+    for got, ref in ((gathered.operand(p), backend.weight_operand(w)), (gathered.t_operand(p), backend.weight_t_operand(w))):
+        assert torch.equal(got.packed, ref.packed), "gathered weight codes differ from the unsharded operand"
+        assert torch.equal(got.scales.view(torch.uint8).reshape(-1), ref.scales.view(torch.uint8).reshape(-1))
+        assert torch.equal(got.global_scale, ref.global_scale)
+    with bl.compute("fp4_all"):
+        backend.set_sr_seed(500 + 64 * rank)
+        pf = torch.nn.Parameter(w)
+        xf = xr.detach().requires_grad_(True)
+        yf = torch.nn.functional.linear(xf, pf)
+        yf.backward(gr)
+        backend.set_sr_seed(500 + 64 * rank)
+        xs = xr.detach().requires_grad_(True)
+        y = token_parallel_linear(xs, p, gathered)
+        assert y.shape == (M // world, N) and torch.equal(y, yf), "token-parallel forward differs"
+        y.backward(gr)
+    assert torch.equal(xs.grad, xf.grad), "token-parallel input gradient differs from the single-GPU layer's"
+    parts = [torch.empty_like(pf.grad) for _ in range(world)]
+    dist.all_gather(parts, pf.grad.contiguous())
+    assert p.grad.shape == (N // world, x.shape[1])
+    if world == 2:
+        assert torch.equal(p.grad, (parts[0] + parts[1])[cols]), "weight gradient is not the sum of the partials"
+    total = sum(t.float() for t in parts)[cols]
+    assert rel(p.grad, total) < 1e-2
+    assert rel(p.grad, (gy.float().t() @ x.float())[cols]) < 0.25
+
+    # the update changes the shard: the gathered operands must follow the new version
+    opt = bl.Lattice([p], lr=3e-3, direction="sign", phase_bits=4, seed=77, fused_backward=False)
+    opt.step()
+    full = torch.empty(N, p.packed.shape[1], dtype=torch.uint8, device=dev)
+    dist.all_gather_into_tensor(full, p.packed.contiguous())
+    assert torch.equal(gathered.operand(p).packed, full) and not torch.equal(full, w.packed)
+    assert gathered.t_operand(p).packed.shape == (x.shape[1], N // 2)
+
+    # two layers on one input, gathers prefetched
+    pa, pb = torch.nn.Parameter(shard_rows(w, rank, world)), torch.nn.Parameter(shard_rows(w2, rank, world))
+    gathered.prefetch((pa, pb))
+    with bl.compute("fp4_all"):
+        xs2 = xr.detach().requires_grad_(True)
+        ya, yb = token_parallel_linears(xs2, (pa, pb), gathered)
+        assert torch.equal(ya, yf)
+        torch.autograd.backward((ya, yb), (gr, gy2[rows].contiguous()))
+    W, W2 = w.dequantize(torch.float32), w2.dequantize(torch.float32)
+    assert rel(xs2.grad, gr.float() @ W + gy2[rows].float() @ W2) < 0.25
+    cols2 = slice(rank * w2.shape[0] // world, (rank + 1) * w2.shape[0] // world)
+    assert rel(pb.grad, (gy2.float().t() @ x.float())[cols2]) < 0.25
+    assert rel(pa.grad, (gy.float().t() @ x.float())[cols]) < 0.25
 
 
 def main():
@@ -99,6 +156,7 @@ def main():
         yo.backward(gyo[:, cols].contiguous())
     assert rel(xso.grad, (gyo.float() @ W)[ro]) < 0.25
     assert rel(po.grad, (gyo.float().t() @ xo.float())[cols]) < 0.25
+    token_parallel_checks(rank, world, dev, w, x, gy, w2, gy2)
     assert bl._ops.gemm_status(local) == 0
     dist.barrier()
     print(f"OK {rank}", flush=True)

@@ -27,6 +27,9 @@ def test_host_side_helpers_run_without_a_device():
     L = _C.lib()
     assert L.bl_version() >= 1
     assert L.bl_blocked_scale_bytes(200, 9) == 2 * 3 * 512
+    from bitlattice_b200 import _ops
+    for rows, cols16 in ((1, 1), (128, 4), (129, 5), (200, 9), (65536, 256), (12288, 768), (32, 2)):
+        assert _ops.blocked_scale_bytes(rows, cols16) == L.bl_blocked_scale_bytes(rows, cols16)
     assert L.bl_update_scratch_bytes(4096, 4096, 1, 1.0) == 0            # sign with clip >= 1 needs no statistics
     assert L.bl_update_scratch_bytes(4096, 4096, 2, 1.0) >= 32 * 4096 * 4
     # argument validation happens before any CUDA call

@@ -1,5 +1,6 @@
 """The N-sharded layer's bookkeeping on two gloo ranks (CPU): gathered input, feature-sharded output, reduce-scattered
-input gradient and local weight-gradient shards agree with the unsharded layer."""
+input gradient and local weight-gradient shards agree with the unsharded layer; so do the token-parallel layer's
+gathered weight, token-sharded output and reduce-scattered weight gradient."""
 import os
 import socket
 
@@ -8,7 +9,7 @@ import torch
 import torch.distributed as dist
 import torch.multiprocessing as mp
 
-from bitlattice_b200.parallel import column_parallel_linear, shard_bounds, world
+from bitlattice_b200.parallel import column_parallel_linear, shard_bounds, token_parallel_linear, world
 
 
 def _free_port():
@@ -40,6 +41,16 @@ def _worker(rank, size, port, out):
         ok = (torch.allclose(y, (x @ W.t())[:, lo:hi], atol=1e-5)
               and torch.allclose(xs.grad, xr.grad[rank * rows:(rank + 1) * rows], atol=1e-4)
               and torch.allclose(Ws.grad, Wr.grad[lo:hi], atol=1e-4))
+        # the other exchange pattern over the same row shards: the rank keeps its tokens, the weight is gathered and
+        # the weight-gradient partials are reduce-scattered to the shard owners
+        xt = x[rank * rows:(rank + 1) * rows].clone().requires_grad_(True)
+        Wt = W[lo:hi].clone().requires_grad_(True)
+        yt = token_parallel_linear(xt, Wt)
+        assert yt.shape == (rows, N)
+        yt.backward(gy[rank * rows:(rank + 1) * rows].contiguous())
+        ok = (ok and torch.allclose(yt, (x @ W.t())[rank * rows:(rank + 1) * rows], atol=1e-5)
+              and torch.allclose(xt.grad, xr.grad[rank * rows:(rank + 1) * rows], atol=1e-4)
+              and torch.allclose(Wt.grad, Wr.grad[lo:hi], atol=1e-4))
         out[rank] = bool(ok)
     finally:
         dist.destroy_process_group()
@@ -77,6 +88,7 @@ def test_shard_bounds():
 def test_single_process_degenerates_to_plain_linear():
     x, W = torch.randn(4, 8), torch.randn(6, 8)
     assert torch.equal(column_parallel_linear(x, W), torch.nn.functional.linear(x, W))
+    assert torch.equal(token_parallel_linear(x, W), torch.nn.functional.linear(x, W))
 
 
 def _io_worker(rank, size, port, out, ckpt, tmp):
