@@ -274,6 +274,15 @@ def column_parallel_linears(x_shard: torch.Tensor, weights, group=None) -> tuple
 
 # ------------------------------------------------------------------------------------ token-parallel, gathered weights
 
+def _place_columns(parts: torch.Tensor) -> torch.Tensor:
+    """Column slices gathered as [p, K, m] bytes -> the matrix [K, p * m] they are slices of, moved as 8-byte words
+    when m allows (shards of a multiple of 128 rows make both the code and the scale pieces multiples of 8 bytes)."""
+    p, K, m = parts.shape
+    if m % 8 == 0:
+        return parts.view(torch.int64).permute(1, 0, 2).reshape(K, p * m // 8).contiguous().view(torch.uint8)
+    return parts.permute(1, 0, 2).reshape(K, p * m).contiguous()
+
+
 class _GatheredEntry:
     __slots__ = ("version", "ref", "work", "row", "t_parts", "t", "nbytes")
 
@@ -384,8 +393,7 @@ class GatheredWeights:
         e = self._entry(w)
         if e.t is None:
             tcodes, tsf, tg, K, N = e.t_parts
-            e.t = backend.Fp4Operand(tcodes.permute(1, 0, 2).reshape(K, N // 2),
-                                     _ops.to_blocked(tsf.permute(1, 0, 2).reshape(K, N // 16)), tg, True)
+            e.t = backend.Fp4Operand(_place_columns(tcodes), _ops.to_blocked(_place_columns(tsf)), tg, True)
             e.t_parts = None
         return e.t
 

@@ -143,3 +143,12 @@ def test_sharded_checkpoint_round_trip_on_gloo(tmp_path):
         p.join(180)
         assert p.exitcode == 0
     assert all(out.get(r) for r in range(size)), dict(out)
+
+
+@pytest.mark.parametrize("p,K,m", [(8, 64, 64), (8, 64, 8), (2, 32, 128), (4, 48, 12), (1, 16, 8)])
+def test_gathered_column_slices_are_put_in_place(p, K, m):
+    from bitlattice_b200.parallel import _place_columns
+    full = torch.randint(0, 256, (K, p * m), dtype=torch.uint8)
+    parts = torch.stack([full[:, r * m:(r + 1) * m] for r in range(p)]).contiguous()
+    out = _place_columns(parts)
+    assert out.is_contiguous() and out.dtype == torch.uint8 and torch.equal(out, full)
