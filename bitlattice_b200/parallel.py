@@ -275,16 +275,48 @@ def column_parallel_linears(x_shard: torch.Tensor, weights, group=None) -> tuple
 # ------------------------------------------------------------------------------------ token-parallel, gathered weights
 
 def _place_columns(parts: torch.Tensor) -> torch.Tensor:
-    """Column slices gathered as [p, K, m] bytes -> the matrix [K, p * m] they are slices of, moved as 8-byte words
-    when m allows (shards of a multiple of 128 rows make both the code and the scale pieces multiples of 8 bytes)."""
+    """Column slices gathered as [p, K, m] (possibly strided between the p slices) -> the byte matrix [K, p * m *
+    itemsize] they are slices of. Bytes are moved as 8-byte words when m allows (shards of a multiple of 128 rows make
+    both the code and the scale pieces multiples of 8 bytes); a tensor of 8-byte words is taken as is."""
     p, K, m = parts.shape
-    if m % 8 == 0:
-        return parts.view(torch.int64).permute(1, 0, 2).reshape(K, p * m // 8).contiguous().view(torch.uint8)
-    return parts.permute(1, 0, 2).reshape(K, p * m).contiguous()
+    if parts.dtype == torch.uint8 and m % 8 == 0 and parts.stride(2) == 1 and parts.is_contiguous():
+        parts, m = parts.view(torch.int64), m // 8
+    return parts.permute(1, 0, 2).reshape(K, p * m).contiguous().view(torch.uint8)
+
+
+def _row_pieces(words: torch.Tensor, span) -> torch.Tensor:
+    """Piece ``span`` = (first word, words) of every rank's buffer in ``words`` [p, words per rank], concatenated in
+    rank order (= row order of a row-sharded matrix), as flat bytes."""
+    first, count = span
+    return words[:, first:first + count].contiguous().view(torch.uint8).view(-1)
+
+
+def _column_pieces(words: torch.Tensor, span, K: int) -> torch.Tensor:
+    """Piece ``span`` of every rank's buffer taken as that rank's [K, m] column slice: the byte matrix [K, p * m]."""
+    first, count = span
+    return _place_columns(words[:, first:first + count].unflatten(1, (K, count // K)))
 
 
 class _GatheredEntry:
-    __slots__ = ("version", "ref", "work", "row", "t_parts", "t", "nbytes")
+    __slots__ = ("version", "ref", "batch", "spans", "meta", "row", "t", "nbytes")
+
+
+class _GatherBatch:
+    """One all-gather carrying every piece (codes, tiled scales, transposed codes and scales) of the weights of one
+    ``prefetch`` call: each rank sends a single packed buffer, so a group of projections costs one collective."""
+
+    def __init__(self, pieces, group, size):
+        send = torch.cat([t.reshape(-1) for t in pieces])                   # one launch; every piece is 8-byte sized
+        self.recv = torch.empty(size, send.numel(), dtype=torch.uint8, device=send.device)
+        self.work = dist.all_gather_into_tensor(self.recv, send, group=group, async_op=True)
+        self.send = send
+
+    def words(self) -> torch.Tensor:
+        """The gathered buffers as [p, bytes / 8] 8-byte words, after the current stream has been made to wait."""
+        if self.work is not None:
+            self.work.wait()
+            self.work = self.send = None
+        return self.recv.view(torch.int64)
 
 
 class _Coalesced:
@@ -310,10 +342,10 @@ class _Coalesced:
 
 class GatheredWeights:
     """GEMM operands of the full weight assembled from the ranks' row shards: W [N, K] for the forward and the
-    re-quantized W^T [K, N] for the input gradient, valid for one weight version (``_bl_version``). The all-gathers run
-    asynchronously, those of the weights of one ``prefetch`` call as a single NCCL group; prefetching the weights
-    needed next lets them finish under other work. Entries are dropped least recently used beyond ``limit_bytes``;
-    weights are held weakly."""
+    re-quantized W^T [K, N] for the input gradient, valid for one weight version (``_bl_version``). The all-gather runs
+    asynchronously, one collective for all the weights of a ``prefetch`` call; prefetching the weights needed next
+    lets it finish under other work. Entries are dropped least recently used beyond ``limit_bytes``; weights are held
+    weakly."""
 
     def __init__(self, group=None, limit_bytes: int = 4 << 30):
         self.group, self.limit, self.used = group, limit_bytes, 0
@@ -336,38 +368,36 @@ class GatheredWeights:
         return None
 
     def prefetch(self, weights) -> None:
-        """Start the gathers of every weight of ``weights`` whose current version is not here yet."""
+        """Start the gather of every weight of ``weights`` whose current version is not here yet."""
         from . import _ops, backend
         todo = [w for w in weights if self._current(w) is None]
         if not todo:
             return
         size = world(self.group)[1]
-        pairs, made = [], []
+        pieces, made, off = [], [], 0
         for w in todo:
             n, K = w.shape
             if n % 128 or K % 64:
                 raise ValueError(f"a [{n}, {K}] shard cannot be gathered as packed operands (rows % 128, cols % 64)")
-            dev = w.packed.device
             local = backend.weight_operand(w)                  # 128-row scale tiles are whole: shards concatenate
-            lsf = local.scales.view(torch.uint8).reshape(-1)
-            codes = torch.empty(size * n, K // 2, dtype=torch.uint8, device=dev)
-            sf = torch.empty(size * lsf.numel(), dtype=torch.uint8, device=dev)
-            # W_r^T [K, n] is a column slice of W^T: gathered as [p, K, n/2] and [p, K, n/16], permuted into place
-            # on first use
+            # W_r^T [K, n] is a column slice of W^T: its pieces arrive as [p, K, n/2] and [p, K, n/16] and are
+            # permuted into place on first use
             tp, ts, tg = _ops.requantize_nvfp4_t(w.packed, w.scales, w.global_scale, blocked=False)
-            ts = ts.view(torch.uint8)
-            tcodes = torch.empty(size, *tp.shape, dtype=torch.uint8, device=dev)
-            tsf = torch.empty(size, *ts.shape, dtype=torch.uint8, device=dev)
-            pairs += [(codes, w.packed), (sf, lsf), (tcodes, tp), (tsf, ts)]
+            parts = [w.packed, local.scales.view(torch.uint8), tp, ts.view(torch.uint8)]
             e = _GatheredEntry()
             e.version, e.ref = getattr(w, "_bl_version", 0), weakref.ref(w)
-            e.row = backend.Fp4Operand(codes, sf, w.global_scale.float(), True)
-            e.t_parts, e.t = (tcodes, tsf, tg, K, size * n), None
-            e.nbytes = 2 * (codes.numel() + sf.numel())
+            e.spans = []
+            for t in parts:
+                e.spans.append((off // 8, t.numel() // 8))
+                off += t.numel()
+            e.meta = (n, K, w.global_scale.float(), tg)
+            e.row = e.t = None
+            e.nbytes = 2 * sum(t.numel() for t in parts) * size
+            pieces += parts
             made.append((w, e))
-        work = _Coalesced(dist.all_gather_into_tensor, pairs, self.group)
+        batch = _GatherBatch(pieces, self.group, size)
         for w, e in made:
-            e.work = work
+            e.batch = batch
             self.entries[id(w)] = e
             self.used += e.nbytes
         while self.used > self.limit and len(self.entries) > len(made):
@@ -378,23 +408,32 @@ class GatheredWeights:
         if e is None:
             self.prefetch((w,))
             e = self.entries[id(w)]
-        if e.work is not None:
-            e.work.wait()
-            e.work = None
         return e
 
     def operand(self, w):
         """W [N, K] of the current version as a GEMM operand."""
-        return self._entry(w).row
+        from . import backend
+        e = self._entry(w)
+        if e.row is None:
+            words = e.batch.words()
+            n, K, g, _ = e.meta
+            e.row = backend.Fp4Operand(_row_pieces(words, e.spans[0]).view(-1, K // 2),
+                                       _row_pieces(words, e.spans[1]), g, True)
+            if e.t is not None:
+                e.batch = None                                  # both operands built: the gathered buffer can go
+        return e.row
 
     def t_operand(self, w):
         """W^T [K, N], re-quantized along N, of the current version as a GEMM operand."""
         from . import _ops, backend
         e = self._entry(w)
         if e.t is None:
-            tcodes, tsf, tg, K, N = e.t_parts
-            e.t = backend.Fp4Operand(_place_columns(tcodes), _ops.to_blocked(_place_columns(tsf)), tg, True)
-            e.t_parts = None
+            words = e.batch.words()
+            n, K, _, tg = e.meta
+            e.t = backend.Fp4Operand(_column_pieces(words, e.spans[2], K),
+                                     _ops.to_blocked(_column_pieces(words, e.spans[3], K)), tg, True)
+            if e.row is not None:
+                e.batch = None
         return e.t
 
 
