@@ -62,6 +62,9 @@ def parse():
     ap.add_argument("--cpu-tokens", type=int, default=16384, help="tokens of the bounded CPU sample")
     ap.add_argument("--parallel", default="auto", choices=["auto", "column", "token"],
                     help="exchange pattern of the N-sharded weights at N > 1")
+    ap.add_argument("--kernel-summary", default=None, metavar="FILE",
+                    help="after the measurements, run 2 more steps under torch.profiler on rank 0 and write per-kernel "
+                         "launch counts and device time (text) to FILE")
     return ap.parse_args()
 
 
@@ -228,7 +231,7 @@ def run_ours(a):
     copy_stream = torch.cuda.Stream(device=dev)
     order = [[params[li * len(LAYER) + INDEX[n]] for n in names] for li in range(a.layers) for names in GROUPS]
 
-    def measure(mode, steps, warmup, clocks=None):
+    def measure(mode, steps, warmup, clocks=None, summary_to=None):
         """Warm up, time `steps` steps with inputs resident in HBM, then the same end to end from pinned host memory."""
         # inputs: this rank's tokens of x per distinct K; gy as the layer's output is laid out under `mode`
         gen = torch.Generator(device=dev).manual_seed(7 + rank)
@@ -321,9 +324,46 @@ def run_ours(a):
         run_steps(2, True)
         r["e2e_steps"] = max(2, min(steps, 5))
         r["e2e_secs"] = timed(r["e2e_steps"], True)
+        if summary_to:
+            kernel_summary(lambda: run_steps(2, False), summary_to)
         return r
 
-    res = measure(mode, a.steps, max(a.warmup, 3), Clocks(local) if rank == 0 else None)
+    def kernel_summary(run, path):
+        """Per-kernel launch counts and device time of `run()` from torch.profiler (CUPTI), written by rank 0. Times
+        under a profiler are for shares and overlap, never for throughput."""
+        from torch.profiler import ProfilerActivity, profile
+        if world > 1:
+            dist.barrier()
+        torch.cuda.synchronize()
+        with profile(activities=[ProfilerActivity.CUDA]) as prof:
+            run()
+            torch.cuda.synchronize()
+        if rank != 0:
+            return
+        rows, spans = {}, []
+        for e in prof.events():
+            if e.device_type != torch.autograd.DeviceType.CUDA:
+                continue
+            n, d = rows.get(e.name, (0, 0.0))
+            rows[e.name] = (n + 1, d + e.time_range.elapsed_us())
+            spans.append((e.time_range.start, e.time_range.end, e.name.startswith("nccl")))
+        if not spans:
+            return
+        t0, t1 = min(s[0] for s in spans), max(s[1] for s in spans)
+        busy, end = 0.0, t0                                   # union of the non-NCCL kernels' intervals
+        for a0, a1, comm in sorted(spans):
+            if comm:
+                continue
+            if a1 > end:
+                busy += a1 - max(a0, end)
+                end = a1
+        with open(path, "w") as f:
+            f.write(f"window {(t1 - t0) / 1e3:.2f} ms, 2 steps of {a.layers} layers, rank 0 of {world}; compute "
+                    f"kernels busy {busy / 1e3:.2f} ms ({100 * busy / (t1 - t0):.1f} %)\n")
+            for name, (n, d) in sorted(rows.items(), key=lambda kv: -kv[1][1]):
+                f.write(f"{name[:90]:90s} n={n:5d} total {d / 1e3:9.3f} ms  avg {d / n:8.1f} us\n")
+
+    res = measure(mode, a.steps, max(a.warmup, 3), Clocks(local) if rank == 0 else None, a.kernel_summary)
     other = None
     if world > 1 and a.parallel == "auto":
         other_mode = "column" if mode == "token" else "token"

@@ -49,6 +49,8 @@ _SIGNATURES = {
     "bl_nvfp4_requantize_t": (_c.c_int, [_P, _P, _P, _c.c_int64, _c.c_int64, _P, _P, _P, _c.c_int, _c.c_int, _P]),
     "bl_blocked_scale_bytes": (_c.c_size_t, [_c.c_int64, _c.c_int64]),
     "bl_nvfp4_scales_to_blocked": (_c.c_int, [_P, _c.c_int64, _c.c_int64, _P, _c.c_int, _P]),
+    "bl_nvfp4_assemble_gathered": (_c.c_int, [_P, _c.c_int64, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int64, _c.c_int64,
+                                              _c.c_int64, _c.c_int64, _P, _P, _P, _P, _c.c_int, _P]),
     "bl_nvfp4_gemm": (_c.c_int, [_P, _P, _P, _P, _P, _P, _c.c_int64, _c.c_int64, _c.c_int64, _P, _c.c_int,
                                  _c.c_int64, _c.c_int, _P]),
     "bl_nvfp4_gemm_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.c_int]),
@@ -110,12 +112,13 @@ def check(status: int) -> None:
 
 
 # kernels each entry point launches (memsets not counted); the lattice update launches 3 when it needs column
-# statistics, the transposed quantizer 3 without a scale bound
+# statistics, the transposed quantizer 2 without a scale bound
 KERNELS_PER_CALL = {"bl_nvfp4_step_quantized": 1, "bl_nvfp4_lattice_update": 1,
                     "bl_nvfp4_lattice_update_fixed_scratch": 1, "bl_direction": 1,
-                    "bl_nvfp4_dequantize": 1, "bl_nvfp4_amax": 1, "bl_nvfp4_quantize": 1, "bl_nvfp4_quantize_t": 2,
+                    "bl_nvfp4_dequantize": 1, "bl_nvfp4_amax": 1, "bl_nvfp4_quantize": 1, "bl_nvfp4_quantize_t": 1,
                     "bl_nvfp4_quantize_4over6": 1,
                     "bl_nvfp4_requantize_t": 1, "bl_nvfp4_scales_to_blocked": 1, "bl_nvfp4_gemm": 1,
+                    "bl_nvfp4_assemble_gathered": 1,
                     "bl_swiglu_fwd": 1, "bl_swiglu_bwd": 1}
 
 

@@ -305,6 +305,22 @@ def to_blocked(scales: torch.Tensor) -> torch.Tensor:
     return out
 
 
+def assemble_gathered(recv: torch.Tensor, n: int, K: int, offsets):
+    """recv [p, bytes] uint8: the all-gathered per-rank buffers holding, at byte ``offsets`` = (codes, blocked scales,
+    transposed codes, transposed row-major scales), the pieces of a weight's row shard [n, K]. Returns the operands of
+    the full weight, ((codes [p*n, K/2], blocked scales), (W^T codes [K, p*n/2], blocked scales)), in one launch."""
+    _require(recv, "recv", torch.uint8)
+    p = recv.shape[0]
+    dev = recv.device
+    codes = torch.empty(p * n, K // 2, dtype=torch.uint8, device=dev)
+    sf = torch.empty(p * blocked_scale_bytes(n, K // 16), dtype=torch.uint8, device=dev)
+    tcodes = torch.empty(K, p * n // 2, dtype=torch.uint8, device=dev)
+    tsf = torch.empty(blocked_scale_bytes(K, p * n // 16), dtype=torch.uint8, device=dev)
+    _C.call("bl_nvfp4_assemble_gathered", _C.ptr(recv), recv.stride(0), p, n, K, *[int(o) for o in offsets],
+            _C.ptr(codes), _C.ptr(sf), _C.ptr(tcodes), _C.ptr(tsf), _C.device_of(recv), _C.stream_of(recv))
+    return (codes, sf), (tcodes, tsf)
+
+
 # ------------------------------------------------------------------------------------------------ GEMM
 
 def nvfp4_gemm(a_packed, a_sf, a_global, b_packed, b_sf, b_global, out_dtype=torch.bfloat16,

@@ -25,6 +25,7 @@ SOURCES = {
     "quant.cu": ["--fmad=false"],
     "gemm.cu": [],
     "swiglu.cu": ["--fmad=false"],
+    "gather.cu": [],
 }
 
 

@@ -324,10 +324,18 @@ __global__ void __launch_bounds__(kQThreads) amax_t_kernel(const T* __restrict__
   if ((threadIdx.x & 31) == 0) atomic_max_pos(out, m);
 }
 
-// global scale of the transposed operand: from a bound (given == 1: in[0] is the bound) or from an amax (in[0])
-__global__ void global_t_kernel(const float* __restrict__ in, int given, float* __restrict__ global_out) {
+// global scale of the transposed operand: from a bound (given == 1: in[0] is the bound), from an amax (given == 0),
+// or as is (given == 2: in[0] already is the scale). The quantizers evaluate it themselves and their first thread
+// publishes it, which saves a launch per operand; the one-thread kernel remains for callers whose output aliases the
+// input.
+__device__ __forceinline__ float global_t(const float* __restrict__ in, int given) {
+  if (given == 2) return in[0];
   const float amax = given ? in[0] * 2688.0f : in[0];
-  global_out[0] = fmaxf(amax / 2688.0f, 1e-12f);
+  return fmaxf(amax / 2688.0f, 1e-12f);
+}
+
+__global__ void global_t_kernel(const float* __restrict__ in, int given, float* __restrict__ global_out) {
+  global_out[0] = global_t(in, given);
 }
 
 // x [M, K] -> NVFP4 of x^T. A CTA stages a [128, 64] tile of x in shared memory with coalesced row reads; the work
@@ -335,7 +343,8 @@ __global__ void global_t_kernel(const float* __restrict__ in, int given, float* 
 template <typename T, bool SR>
 __global__ void __launch_bounds__(kQThreads) quantize_t_kernel(const T* __restrict__ x, int64_t M, int64_t K,
                                                                const float* __restrict__ H,
-                                                               const float* __restrict__ global, uint32_t key,
+                                                               const float* __restrict__ global, int given,
+                                                               float* __restrict__ global_out, uint32_t key,
                                                                uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
                                                                int layout) {
   __shared__ float tile[kTM][kTK + 1];
@@ -348,7 +357,8 @@ __global__ void __launch_bounds__(kQThreads) quantize_t_kernel(const T* __restri
     tile[rr][cc] = (m < M && k < K) ? to_f<T>(x[m * K + k]) : 0.0f;
   }
   __syncthreads();
-  const float g = global[0];
+  const float g = global_t(global, given);
+  if (global_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) global_out[0] = g;
   // 64 columns x 8 blocks x 2 halves = 1024 work items, 4 per thread; lanes (2j, 2j+1) = halves of one block
   for (int it = 0; it < 4; ++it) {
     const int w = it * kQThreads + threadIdx.x;
@@ -436,7 +446,8 @@ __device__ __forceinline__ void rotate16_generic(const float raw[16], const floa
 template <typename T, bool SR>
 __global__ void __launch_bounds__(kQThreads, 4) quantize_t3_kernel(const T* __restrict__ x, int64_t M, int64_t K,
                                                                 const float* __restrict__ H,
-                                                                const float* __restrict__ global, uint32_t key,
+                                                                const float* __restrict__ global, int given,
+                                                                float* __restrict__ global_out, uint32_t key,
                                                                 uint8_t* __restrict__ codes, uint8_t* __restrict__ scales,
                                                                 int layout) {
   __shared__ uint2 s_codes[kTK][kTM / 16 + 1];
@@ -460,7 +471,8 @@ __global__ void __launch_bounds__(kQThreads, 4) quantize_t3_kernel(const T* __re
     const T* p = x + m * K + k;
 #pragma unroll
     for (int i = 0; i < 16; ++i) load2(p + i * K, ra[i], rb[i]);
-    const float g = global[0];
+    const float g = global_t(global, given);
+    if (global_out != nullptr && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) global_out[0] = g;
     const float rg = __frcp_rn(g);
     float va[16], vb[16];
     if (H == nullptr) {
@@ -707,18 +719,24 @@ static int quantize_t_typed(const T* x, int64_t M, int64_t K, const float* H, in
     BL_CUDA(cudaMemsetAsync(amax_scratch, 0, 16, st));
     amax_t_kernel<<<grid_for((M / 16) * K, kQThreads, device), kQThreads, 0, st>>>(x, M, K, H, amax_scratch);
     BL_CUDA(cudaGetLastError());
-    global_t_kernel<<<1, 1, 0, st>>>(amax_scratch, 0, gout);
-  } else {
-    global_t_kernel<<<1, 1, 0, st>>>(bound, 1, gout);
   }
-  BL_CUDA(cudaGetLastError());
+  const float* src = bound == nullptr ? amax_scratch : bound;
+  int given = bound == nullptr ? 0 : 1;
+  float* publish = gout;
+  if (static_cast<const void*>(gout) == static_cast<const void*>(src)) {     // in-place: settle the scale first
+    global_t_kernel<<<1, 1, 0, st>>>(src, given, gout);
+    BL_CUDA(cudaGetLastError());
+    src = gout;
+    given = 2;
+    publish = nullptr;
+  }
   const dim3 grid(static_cast<unsigned>((K + kTK - 1) / kTK), static_cast<unsigned>((M + kTM - 1) / kTM));
   const uint32_t key = seed < 0 ? 0u : hash_key(static_cast<uint32_t>(seed), step);
   const bool pairs = K % 2 == 0 && (reinterpret_cast<uintptr_t>(x) % (2 * sizeof(T))) == 0;
-  if (pairs && seed < 0) quantize_t3_kernel<T, false><<<grid, kQThreads, 0, st>>>(x, M, K, H, gout, key, codes, scales, layout);
-  else if (pairs) quantize_t3_kernel<T, true><<<grid, kQThreads, 0, st>>>(x, M, K, H, gout, key, codes, scales, layout);
-  else if (seed < 0) quantize_t_kernel<T, false><<<grid, kQThreads, 0, st>>>(x, M, K, H, gout, key, codes, scales, layout);
-  else quantize_t_kernel<T, true><<<grid, kQThreads, 0, st>>>(x, M, K, H, gout, key, codes, scales, layout);
+  if (pairs && seed < 0) quantize_t3_kernel<T, false><<<grid, kQThreads, 0, st>>>(x, M, K, H, src, given, publish, key, codes, scales, layout);
+  else if (pairs) quantize_t3_kernel<T, true><<<grid, kQThreads, 0, st>>>(x, M, K, H, src, given, publish, key, codes, scales, layout);
+  else if (seed < 0) quantize_t_kernel<T, false><<<grid, kQThreads, 0, st>>>(x, M, K, H, src, given, publish, key, codes, scales, layout);
+  else quantize_t_kernel<T, true><<<grid, kQThreads, 0, st>>>(x, M, K, H, src, given, publish, key, codes, scales, layout);
   BL_CUDA(cudaGetLastError());
   return 0;
 }

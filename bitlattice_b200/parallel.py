@@ -274,36 +274,14 @@ def column_parallel_linears(x_shard: torch.Tensor, weights, group=None) -> tuple
 
 # ------------------------------------------------------------------------------------ token-parallel, gathered weights
 
-def _place_columns(parts: torch.Tensor) -> torch.Tensor:
-    """Column slices gathered as [p, K, m] (possibly strided between the p slices) -> the byte matrix [K, p * m *
-    itemsize] they are slices of. Bytes are moved as 8-byte words when m allows (shards of a multiple of 128 rows make
-    both the code and the scale pieces multiples of 8 bytes); a tensor of 8-byte words is taken as is."""
-    p, K, m = parts.shape
-    if parts.dtype == torch.uint8 and m % 8 == 0 and parts.stride(2) == 1 and parts.is_contiguous():
-        parts, m = parts.view(torch.int64), m // 8
-    return parts.permute(1, 0, 2).reshape(K, p * m).contiguous().view(torch.uint8)
-
-
-def _row_pieces(words: torch.Tensor, span) -> torch.Tensor:
-    """Piece ``span`` = (first word, words) of every rank's buffer in ``words`` [p, words per rank], concatenated in
-    rank order (= row order of a row-sharded matrix), as flat bytes."""
-    first, count = span
-    return words[:, first:first + count].contiguous().view(torch.uint8).view(-1)
-
-
-def _column_pieces(words: torch.Tensor, span, K: int) -> torch.Tensor:
-    """Piece ``span`` of every rank's buffer taken as that rank's [K, m] column slice: the byte matrix [K, p * m]."""
-    first, count = span
-    return _place_columns(words[:, first:first + count].unflatten(1, (K, count // K)))
-
-
 class _GatheredEntry:
     __slots__ = ("version", "ref", "batch", "spans", "meta", "row", "t", "nbytes")
 
 
 class _GatherBatch:
     """One all-gather carrying every piece (codes, tiled scales, transposed codes and scales) of the weights of one
-    ``prefetch`` call: each rank sends a single packed buffer, so a group of projections costs one collective."""
+    ``prefetch`` call: each rank sends a single packed buffer, so a group of projections costs one collective; one
+    kernel per weight (``_ops.assemble_gathered``) cuts the stacked buffers back into the two GEMM operands."""
 
     def __init__(self, pieces, group, size):
         send = torch.cat([t.reshape(-1) for t in pieces])                   # one launch; every piece is 8-byte sized
@@ -311,12 +289,12 @@ class _GatherBatch:
         self.work = dist.all_gather_into_tensor(self.recv, send, group=group, async_op=True)
         self.send = send
 
-    def words(self) -> torch.Tensor:
-        """The gathered buffers as [p, bytes / 8] 8-byte words, after the current stream has been made to wait."""
+    def buffers(self) -> torch.Tensor:
+        """The gathered buffers [p, bytes], after the current stream has been made to wait for them."""
         if self.work is not None:
             self.work.wait()
             self.work = self.send = None
-        return self.recv.view(torch.int64)
+        return self.recv
 
 
 class _Coalesced:
@@ -388,7 +366,7 @@ class GatheredWeights:
             e.version, e.ref = getattr(w, "_bl_version", 0), weakref.ref(w)
             e.spans = []
             for t in parts:
-                e.spans.append((off // 8, t.numel() // 8))
+                e.spans.append(off)                            # byte offset of the piece in every rank's buffer
                 off += t.numel()
             e.meta = (n, K, w.global_scale.float(), tg)
             e.row = e.t = None
@@ -410,31 +388,24 @@ class GatheredWeights:
             e = self.entries[id(w)]
         return e
 
-    def operand(self, w):
-        """W [N, K] of the current version as a GEMM operand."""
-        from . import backend
+    def _assembled(self, w) -> _GatheredEntry:
+        from . import _ops, backend
         e = self._entry(w)
         if e.row is None:
-            words = e.batch.words()
-            n, K, g, _ = e.meta
-            e.row = backend.Fp4Operand(_row_pieces(words, e.spans[0]).view(-1, K // 2),
-                                       _row_pieces(words, e.spans[1]), g, True)
-            if e.t is not None:
-                e.batch = None                                  # both operands built: the gathered buffer can go
-        return e.row
+            n, K, g, tg = e.meta
+            (codes, sf), (tcodes, tsf) = _ops.assemble_gathered(e.batch.buffers(), n, K, e.spans)
+            e.row = backend.Fp4Operand(codes, sf, g, True)
+            e.t = backend.Fp4Operand(tcodes, tsf, tg, True)
+            e.batch = None                                      # the gathered buffer goes with the last weight cut out
+        return e
+
+    def operand(self, w):
+        """W [N, K] of the current version as a GEMM operand."""
+        return self._assembled(w).row
 
     def t_operand(self, w):
         """W^T [K, N], re-quantized along N, of the current version as a GEMM operand."""
-        from . import _ops, backend
-        e = self._entry(w)
-        if e.t is None:
-            words = e.batch.words()
-            n, K, _, tg = e.meta
-            e.t = backend.Fp4Operand(_column_pieces(words, e.spans[2], K),
-                                     _ops.to_blocked(_column_pieces(words, e.spans[3], K)), tg, True)
-            if e.row is not None:
-                e.batch = None
-        return e.t
+        return self._assembled(w).t
 
 
 class TokenParallelFp4Linear(torch.autograd.Function):

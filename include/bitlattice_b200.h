@@ -164,6 +164,16 @@ BL_API size_t bl_blocked_scale_bytes(int64_t rows, int64_t cols16);
 BL_API int bl_nvfp4_scales_to_blocked(const uint8_t* scales, int64_t rows, int64_t cols16, uint8_t* out, int device,
                                bl_stream_t stream);
 
+/* No counterpart in the reference (it has no tensor parallelism): GEMM operands of a full weight W [p*n, K] from the
+ * p row shards an all-gather delivered. recv holds p buffers rank_stride bytes apart; inside each, at the given byte
+ * offsets, the shard's codes [n, K/2], its blocked scales (bl_blocked_scale_bytes(n, K/16) bytes), the codes [K, n/2]
+ * and the row-major scales [K, n/16] of its re-quantized W^T slice (bl_nvfp4_requantize_t of the shard). Outputs:
+ * codes [p*n, K/2], sf (p blocked buffers in rank order = the blocked scales of W), tcodes [K, p*n/2], tsf (blocked
+ * scales of W^T, bl_blocked_scale_bytes(K, p*n/16) bytes). n % 128 == 0, K % 64 == 0, offsets % 16 == 0. */
+BL_API int bl_nvfp4_assemble_gathered(const uint8_t* recv, int64_t rank_stride, int p, int64_t n, int64_t K,
+                               int64_t off_codes, int64_t off_sf, int64_t off_tcodes, int64_t off_tsf, uint8_t* codes,
+                               uint8_t* sf, uint8_t* tcodes, uint8_t* tsf, int device, bl_stream_t stream);
+
 /* ---- GEMM ----------------------------------------------------------------------------------------------------- */
 
 /* Replaces bitlattice.backend.fp4_mm, i.e. torch._scaled_mm / F.scaled_mm on NVFP4 operands plus the per-tensor

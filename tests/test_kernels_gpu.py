@@ -446,3 +446,42 @@ def test_shared_reciprocal_division_is_exact():
     for seed in (1, 77777):
         _C.call("bl_selftest_division", 1 << 29, seed, ctypes.byref(bad), 0)
         assert bad.value == 0
+
+
+@pytest.mark.parametrize("p,N,K", [(2, 512, 1024), (8, 1024, 4096), (4, 1024, 192), (1, 128, 64)])
+def test_assembled_gathered_operands_equal_the_unsharded_weight(p, N, K):
+    """p ranks' send buffers (codes, tiled scales, re-quantized W^T slice of each row shard) stacked as an all-gather
+    stacks them: the assembly kernel must return exactly the operands of the unsharded weight (K = 192 leaves a
+    partial 128-row tile in the W^T scales, whose padding must read as zero)."""
+    import bitlattice_b200 as bl
+    from bitlattice_b200 import backend
+    from bitlattice_b200.parallel import shard_rows
+    wd = (torch.randn(N, K, generator=gen(5)) * 0.02).to(DEV)
+    w = bl.LatticeTensor.from_float(wd, "nvfp4", method="rtn", dtype=torch.bfloat16)
+    ref_row, ref_t = backend.weight_operand(w), backend.weight_t_operand(w)
+    n = N // p
+    sends, offsets = [], None
+    filler = torch.full((48,), 0xAB, dtype=torch.uint8, device=DEV)           # another weight's pieces come first
+    for r in range(p):
+        s = shard_rows(w, r, p)
+        tp, ts, _ = _ops.requantize_nvfp4_t(s.packed, s.scales, s.global_scale, blocked=False)
+        pieces = [filler, s.packed, _ops.to_blocked(s.scales.view(torch.uint8)), tp, ts.view(torch.uint8)]
+        offsets, off = [], 0
+        for t in pieces:
+            offsets.append(off)
+            off += t.numel()
+        sends.append(torch.cat([t.reshape(-1) for t in pieces]))
+    recv = torch.stack(sends).contiguous()
+    (codes, sf), (tcodes, tsf) = _ops.assemble_gathered(recv, n, K, offsets[1:])
+    assert torch.equal(codes, ref_row.packed)
+    assert torch.equal(sf, ref_row.scales.view(torch.uint8).reshape(-1))
+    assert torch.equal(tcodes, ref_t.packed)
+    assert torch.equal(tsf, ref_t.scales.view(torch.uint8).reshape(-1))
+
+
+def test_assemble_gathered_rejects_unaligned_pieces():
+    recv = torch.zeros(2, 128 * 64 * 2, dtype=torch.uint8, device=DEV)
+    with pytest.raises(RuntimeError, match="multiples of 16"):
+        _ops.assemble_gathered(recv, 128, 64, [8, 4096, 8192, 12288])
+    with pytest.raises(RuntimeError, match="rows % 128"):
+        _ops.assemble_gathered(recv, 64, 64, [0, 4096, 8192, 12288])

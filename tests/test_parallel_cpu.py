@@ -143,40 +143,3 @@ def test_sharded_checkpoint_round_trip_on_gloo(tmp_path):
         p.join(180)
         assert p.exitcode == 0
     assert all(out.get(r) for r in range(size)), dict(out)
-
-
-@pytest.mark.parametrize("p,K,m", [(8, 64, 64), (8, 64, 8), (2, 32, 128), (4, 48, 12), (1, 16, 8)])
-def test_gathered_column_slices_are_put_in_place(p, K, m):
-    from bitlattice_b200.parallel import _place_columns
-    full = torch.randint(0, 256, (K, p * m), dtype=torch.uint8)
-    parts = torch.stack([full[:, r * m:(r + 1) * m] for r in range(p)]).contiguous()
-    out = _place_columns(parts)
-    assert out.is_contiguous() and out.dtype == torch.uint8 and torch.equal(out, full)
-
-
-@pytest.mark.parametrize("p", [2, 8])
-def test_pieces_of_a_gathered_batch_are_found_again(p):
-    """Every rank sends one buffer holding, per weight, its rows of the codes and its column slice of the transposed
-    codes; the receiver must cut the stacked buffers back into the full matrices."""
-    from bitlattice_b200.parallel import _column_pieces, _row_pieces
-    g = torch.Generator().manual_seed(p)
-    shapes = [(128 * p, 64), (256 * p, 128)]                       # (N, K) of two weights
-    full_rows = [torch.randint(0, 256, (N, K // 2), dtype=torch.uint8, generator=g) for N, K in shapes]
-    full_cols = [torch.randint(0, 256, (K, N // 16), dtype=torch.uint8, generator=g) for N, K in shapes]
-    sends, spans = [], None
-    for r in range(p):
-        pieces, sp, off = [], [], 0
-        for (N, K), fr, fc in zip(shapes, full_rows, full_cols):
-            n = N // p
-            for t in (fr[r * n:(r + 1) * n], fc[:, r * n // 16:(r + 1) * n // 16]):
-                t = t.contiguous()
-                sp.append((off // 8, t.numel() // 8))
-                off += t.numel()
-                pieces.append(t.reshape(-1))
-        sends.append(torch.cat(pieces))
-        spans = sp
-    words = torch.stack(sends).view(torch.int64)
-    for i, ((N, K), fr, fc) in enumerate(zip(shapes, full_rows, full_cols)):
-        assert torch.equal(_row_pieces(words, spans[2 * i]).view(N, K // 2), fr)
-        got = _column_pieces(words, spans[2 * i + 1], K)
-        assert got.is_contiguous() and torch.equal(got, fc)
