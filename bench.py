@@ -62,6 +62,8 @@ def parse():
     ap.add_argument("--cpu-tokens", type=int, default=16384, help="tokens of the bounded CPU sample")
     ap.add_argument("--parallel", default="auto", choices=["auto", "column", "token"],
                     help="exchange pattern of the N-sharded weights at N > 1")
+    ap.add_argument("--overlap", type=int, default=1, choices=[0, 1],
+                    help="1: the optimizer issues its updates on a side stream (Lattice(overlap=True)); 0: in line")
     ap.add_argument("--kernel-summary", default=None, metavar="FILE",
                     help="after the measurements, run 2 more steps under torch.profiler on rank 0 and write per-kernel "
                          "launch counts and device time (text) to FILE")
@@ -220,7 +222,7 @@ def run_ours(a):
             p._bl_row_offset = getattr(w, "_bl_row_offset", 0)
             params.append(p)
             meta.append((name, N, K))
-    opt = bl.Lattice(params, fused_backward=True, **OPT)
+    opt = bl.Lattice(params, fused_backward=True, overlap=bool(a.overlap), **OPT)
     flops = sum(6.0 * M * N * K for _, N, K in meta)
     weights = sum(N * K for _, N, K in meta)
     group = dist.group.WORLD if world > 1 else None
@@ -270,9 +272,10 @@ def run_ours(a):
                     for gi, names in enumerate(GROUPS):    # forward + backward of the projections sharing an input
                         ps = order[li * len(GROUPS) + gi]
                         if gathered is not None:
-                            # the next group's weights (already updated in this or the previous step) are gathered
-                            # while this group computes
-                            gathered.prefetch(order[(li * len(GROUPS) + gi + 1) % len(order)])
+                            # the next group's weights (last updated in the previous step, which step() has
+                            # joined) are gathered while this group computes
+                            if li * len(GROUPS) + gi + 1 < len(order):
+                                gathered.prefetch(order[li * len(GROUPS) + gi + 1])
                             ys = token_parallel_linears(xin[INPUT_OF[names[0]]], ps, gathered)
                         else:
                             ys = column_parallel_linears(xin[INPUT_OF[names[0]]], ps, group)
@@ -401,7 +404,8 @@ def run_ours(a):
                    "nvlink_bytes_per_step_per_rank": {k: v * (world - 1) / world for k, v in moved.items()}
                    if world > 1 else None,
                    "l2": "inputs larger than L2 (weights, activations and gradients of a step exceed 126 MB)",
-                   "host": "one Python thread per rank (autograd multithreading off)"},
+                   "host": "one Python thread per rank (autograd multithreading off)",
+                   "updates": "side stream (overlap=True)" if a.overlap else "in line"},
         "e2e": {"value": flops / (res["e2e_secs"] / res["e2e_steps"]) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": res["h2d_bytes"], "d2h_bytes_per_step": 4, "steps": res["e2e_steps"]},
         "gpu_launches": res["launches"],

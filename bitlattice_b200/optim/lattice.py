@@ -12,7 +12,13 @@ Same constructor, option names, validation errors, per-parameter seeds (``seed +
 state layout (``state[p]["phase"]``: uint8 [rows, cols * container_bits / 8]) as the reference, so optimizer state
 interchanges. Not built, and refused with NotImplementedError: Newton-Schulz / factored / sinkhorn directions,
 low-precision momentum (momentum='fp32' is built), neuron-wise normalization, row-sparse gradients, native-format
-(non-lattice) parameters, host-memory state and the overlap worker.
+(non-lattice) parameters and host-memory state.
+
+``overlap=True`` (reference: lattice.py:225-253 hands each update to a worker thread that issues it on a side stream)
+is built without the thread: the hook itself issues the update on a per-device side stream that waits for the
+gradient's event, so the caller's stream goes on with the rest of the backward pass while the update runs; ``wait()``
+(called by ``step()``) makes the current stream wait for the update streams. A second Python thread would only take
+turns with the first one on the interpreter lock.
 """
 from __future__ import annotations
 
@@ -117,14 +123,14 @@ class Lattice(torch.optim.Optimizer):
             raise ValueError("state must be 'gpu', 'ram' or 'auto'")
         if state != "gpu":
             raise NotImplementedError("optimizer state in host memory is outside this build (state='gpu' is built)")
-        if overlap:
-            raise NotImplementedError("the overlap worker is outside this build")
         for g in self.param_groups:
             _validate(g)
         self.state_placement = "gpu"
         self.seed = int(seed)
         self.fused_backward = fused_backward
-        self.overlap = False
+        self.overlap = bool(overlap)
+        self._update_streams: dict = {}
+        self._scratch: dict = {}
         self._pid = {}
         for g in self.param_groups:
             for p in g["params"]:
@@ -143,10 +149,29 @@ class Lattice(torch.optim.Optimizer):
     def _on_grad(self, p: torch.Tensor) -> None:
         if p.grad is None or self._defer or _deferred:
             return
-        with torch.no_grad():
-            self._update(p, self._group_of[p])
+        if self.overlap and p.is_cuda:
+            self._update_aside(p, self._group_of[p])
+        else:
+            with torch.no_grad():
+                self._update(p, self._group_of[p])
         p.grad = None
         self._done.add(p)
+
+    def _update_stream(self, device: torch.device) -> torch.cuda.Stream:
+        s = self._update_streams.get(device)
+        if s is None:
+            s = self._update_streams[device] = torch.cuda.Stream(device=device)
+        return s
+
+    def _update_aside(self, p: torch.Tensor, g: dict) -> None:
+        """Issue the update of ``p`` on the device's update stream, behind everything the caller's stream holds so far
+        (the gradient is complete there)."""
+        G = p.grad
+        side = self._update_stream(p.device)
+        side.wait_stream(torch.cuda.current_stream(p.device))
+        with torch.cuda.device(p.device), torch.cuda.stream(side), torch.no_grad():
+            self._update(p, g, G)
+        G.record_stream(side)                        # the gradient's memory is reused only after the update has run
 
     @staticmethod
     def _invalidate(p: torch.Tensor) -> None:
@@ -155,7 +180,11 @@ class Lattice(torch.optim.Optimizer):
         drop_cached(p)
 
     def wait(self) -> None:
-        """Updates are issued on the caller's stream, in order: nothing to wait for."""
+        """Make the current stream of every device wait (on the GPU) for the updates issued so far on the update
+        streams (``overlap``); without ``overlap`` updates are issued on the caller's stream and there is nothing to
+        wait for."""
+        for dev, s in self._update_streams.items():
+            torch.cuda.current_stream(dev).wait_stream(s)
 
     def synchronize(self) -> None:
         for dev in {p.device for p in self._pid if p.is_cuda}:
@@ -171,11 +200,15 @@ class Lattice(torch.optim.Optimizer):
             for p in g["params"]:
                 if p in self._done or p.grad is None:
                     continue
-                with torch.cuda.device(p.device):
-                    self._update(p, g)
+                if self.overlap and p.is_cuda:
+                    self._update_aside(p, g)
+                else:
+                    with torch.cuda.device(p.device):
+                        self._update(p, g)
                 if self.fused_backward:
                     p.grad = None
         self._done.clear()
+        self.wait()
         return loss
 
     @contextlib.contextmanager
@@ -223,12 +256,18 @@ class Lattice(torch.optim.Optimizer):
             G2 = st["m"]
         if G2.dtype not in (torch.bfloat16, torch.float16, torch.float32):
             G2 = G2.float()
+        scratch = None
+        if self.overlap:                             # column statistics of updates that run beside the caller's stream
+            need = _ops.update_scratch_bytes(rows, cols, g["direction"], g["clip"])
+            scratch = self._scratch.get(p.device)
+            if need and (scratch is None or scratch.numel() < need):
+                scratch = self._scratch[p.device] = torch.empty(need, dtype=torch.uint8, device=p.device)
         _ops.lattice_update(p.packed, st.get("phase") if bits else None, p.scales, p.global_scale, None,
                             G2.contiguous(), p.fmt, rows, cols, lr=g["lr"], weight_decay=g["weight_decay"],
                             phase_bits=bits, phase_cb=cb, rounding=g["rounding"], seed=seed, step=st["step"],
                             strata=g["strata"], scale_rule=g["scale_rule"], trust=g["trust"], trust_lr=g["trust_lr"],
                             direction=g["direction"], clip=g["clip"],
-                            offset=int(getattr(p, "_bl_row_offset", 0)) * cols)
+                            offset=int(getattr(p, "_bl_row_offset", 0)) * cols, scratch=scratch)
 
     def state_bits(self) -> dict[str, float]:
         """Logical optimizer state in bits, by component (phase and, with momentum='fp32', the fp32 average)."""

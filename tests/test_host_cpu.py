@@ -109,7 +109,7 @@ def test_optimizer_options_validated_like_the_reference():
     with pytest.raises(KeyError):
         bl.Lattice([p], "nonexistent")
     for kw in (dict(), dict(direction="muon"), dict(direction="sign", momentum="bf16"),
-               dict(direction="sign", state="ram"), dict(direction="sign", overlap=True)):
+               dict(direction="sign", state="ram")):
         with pytest.raises(NotImplementedError):
             bl.Lattice([p], **kw)
     with pytest.raises(NotImplementedError):

@@ -264,6 +264,27 @@ def test_fused_backward_matches_step():
         assert torch.equal(o1.state[p]["phase"], o2.state[q]["phase"])
 
 
+def test_overlapped_updates_match_step():
+    """``overlap=True`` issues the updates on a side stream behind the gradient (the reference's worker thread and
+    update stream, lattice.py:225-253); after ``step()`` has joined the streams the weights and the optimizer state
+    are those of the plain optimizer, and forward passes in between read the updated weights."""
+    a, b, c = _make_params(), _make_params(), _make_params()
+    o1 = bl.Lattice(a, lr=5e-3, direction="colnorm", phase_bits=4, seed=3)
+    o2 = bl.Lattice(b, lr=5e-3, direction="colnorm", phase_bits=4, seed=3, fused_backward=True, overlap=True)
+    o3 = bl.Lattice(c, lr=5e-3, direction="colnorm", phase_bits=4, seed=3, overlap=True)
+    _run(a, o1, 3)
+    _run(b, o2, 3)
+    _run(c, o3, 3)
+    torch.cuda.synchronize()
+    assert all(p.grad is None for p in b)
+    for p, q, r in zip(a, b, c):
+        for t in (q, r):
+            assert torch.equal(p.packed, t.packed)
+            assert torch.equal(p.scales.view(torch.uint8), t.scales.view(torch.uint8))
+        assert torch.equal(o1.state[p]["phase"], o2.state[q]["phase"])
+        assert torch.equal(o1.state[p]["phase"], o3.state[r]["phase"])
+
+
 def test_accumulate_equals_summed_gradient():
     """Reference identity (tests/test_parallel.py:131-156): with fused_backward, micro-batches inside accumulate()
     are summed and applied once."""
