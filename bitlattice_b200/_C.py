@@ -31,6 +31,9 @@ _SIGNATURES = {
                                            _c.c_int, _c.c_double, _c.c_double, _c.c_int, _c.c_uint32, _c.c_uint32,
                                            _c.c_int, _c.c_int, _c.c_int, _c.c_double, _c.c_int, _c.c_double, _P,
                                            _c.c_size_t, _c.c_int, _P]),
+    "bl_nvfp4_lattice_update_many": (_c.c_int, [_c.c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _c.c_int, _c.c_int,
+                                                _c.c_int, _c.c_double, _c.c_double, _c.c_int, _c.c_int, _c.c_int,
+                                                _c.c_double, _c.c_int, _c.c_double, _P, _c.c_size_t, _c.c_int, _P]),
     "bl_update_fixed_scratch_capacity": (_c.c_size_t, []),
     "bl_nvfp4_lattice_update_fixed_scratch": (_c.c_int, [_P, _P, _P, _P, _P, _c.c_int, _c.c_int64, _c.c_int64,
                                                          _c.c_uint64, _c.c_int, _c.c_int, _c.c_double, _c.c_double,
@@ -113,7 +116,7 @@ def check(status: int) -> None:
 
 # kernels each entry point launches (memsets not counted); the lattice update launches 3 when it needs column
 # statistics, the transposed quantizer 2 without a scale bound
-KERNELS_PER_CALL = {"bl_nvfp4_step_quantized": 1, "bl_nvfp4_lattice_update": 1,
+KERNELS_PER_CALL = {"bl_nvfp4_step_quantized": 1, "bl_nvfp4_lattice_update": 1, "bl_nvfp4_lattice_update_many": 0,
                     "bl_nvfp4_lattice_update_fixed_scratch": 1, "bl_direction": 1,
                     "bl_nvfp4_dequantize": 1, "bl_nvfp4_amax": 1, "bl_nvfp4_quantize": 1, "bl_nvfp4_quantize_t": 1,
                     "bl_nvfp4_quantize_4over6": 1,

@@ -168,6 +168,50 @@ def lattice_update(packed, phase, scales, global_scale, zeros, G, fmt, rows: int
             extra_kernels=2 if need else 0)
 
 
+def lattice_update_many(items, fmt, *, lr: float, weight_decay: float, phase_bits: int, phase_cb: int, rounding: str,
+                        strata: int, scale_rule: str, trust: float, trust_lr: float, direction: str, clip: float = 1.0,
+                        scratch: torch.Tensor | None = None) -> None:
+    """``lattice_update`` for many tensors of one parameter group in one library call (no interpreter between their
+    launches). ``items``: dicts with packed, phase (or None), scales, global_scale, grad, rows, cols, offset, seed,
+    step; all gradients of one dtype, everything on one device."""
+    import ctypes
+    if not _is_nvfp4(fmt):
+        raise RuntimeError("only NVFP4 tensors (no zero points) are built")
+    if direction not in _DIRECTION:
+        raise RuntimeError(f"direction {direction!r} is outside this build (raw, sign, colnorm are built)")
+    n = len(items)
+    if n == 0:
+        return
+    gdtype = items[0]["grad"].dtype
+    need = 0
+    for it in items:
+        _require(it["packed"], "packed", torch.uint8)
+        _require(it["scales"], "scales")
+        _require(it["global_scale"], "global_scale", torch.float32)
+        _require(it["grad"], "gradient", gdtype)
+        if gdtype not in _C.DTYPE or it["grad"].numel() != it["rows"] * it["cols"]:
+            raise RuntimeError("gradient: bf16, fp16 or fp32 with rows*cols elements")
+        if phase_bits > 0:
+            _require(it["phase"], "phase", torch.uint8)
+        need = max(need, update_scratch_bytes(it["rows"], it["cols"], direction, clip))
+    dev = items[0]["packed"]
+    if scratch is None:
+        scratch = _scratch_for(dev.device, need)
+    ptrs = lambda key: (ctypes.c_void_p * n)(*[(it[key].data_ptr() if it[key] is not None else None) for it in items])
+    i64 = lambda key: (ctypes.c_int64 * n)(*[int(it[key]) for it in items])
+    u64 = lambda key: (ctypes.c_uint64 * n)(*[int(it[key]) & 0xFFFFFFFFFFFFFFFF for it in items])
+    u32 = lambda key: (ctypes.c_uint32 * n)(*[int(it[key]) & 0xFFFFFFFF for it in items])
+    jk = [strat_args(rounding, it["step"], strata) for it in items]
+    sj = (ctypes.c_int * n)(*[j for j, _ in jk])
+    launches = n * (3 if need else 1)
+    _C.call("bl_nvfp4_lattice_update_many", n, ptrs("packed"), ptrs("phase") if phase_bits > 0 else None,
+            ptrs("scales"), ptrs("global_scale"), ptrs("grad"), i64("rows"), i64("cols"), u64("offset"), u32("seed"),
+            u32("step"), sj, _C.DTYPE[gdtype], phase_bits, phase_cb, float(lr), float(1.0 - lr * weight_decay),
+            _ROUNDING[rounding], jk[0][1], _RULE[scale_rule], float(kappa(trust, trust_lr, lr)), _DIRECTION[direction],
+            float(clip), _C.ptr(scratch), scratch.numel() if scratch is not None else 0, _C.device_of(dev),
+            _C.stream_of(dev), extra_kernels=launches)
+
+
 def direction(G, kind: str, r=None, c=None, k: int = 1, beta2: float = 0.95, block=0, ns_steps: int = 5,
               ns_dtype: str = "bf16", sinkhorn_iters: int = 2, clip: float = 1.0, **unused) -> torch.Tensor:
     """Update direction as float32 [rows, cols], RMS clipped to ``clip`` (reference: bitlattice/_ops.py:110-144).

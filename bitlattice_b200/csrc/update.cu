@@ -610,6 +610,34 @@ extern "C" int bl_nvfp4_lattice_update(uint8_t* codes, uint8_t* phase, uint8_t* 
                       clip, scratch, device, st);
 }
 
+extern "C" int bl_nvfp4_lattice_update_many(int count, uint8_t* const* codes, uint8_t* const* phase,
+                                            uint8_t* const* scales, const float* const* global_scale,
+                                            const void* const* grad, const int64_t* rows, const int64_t* cols,
+                                            const uint64_t* offset, const uint32_t* seed, const uint32_t* step,
+                                            const int* strat_j, int grad_dtype, int phase_bits, int phase_cb, double lr,
+                                            double decay, int rounding, int strat_k, int rule, double kappa,
+                                            int direction, double clip, void* scratch, size_t scratch_bytes, int device,
+                                            bl_stream_t stream) {
+  BL_REQUIRE(count >= 0, "lattice_update_many: negative count");
+  BL_REQUIRE(count == 0 || (codes && scales && global_scale && grad && rows && cols && offset && seed && step),
+             "lattice_update_many: null array");
+  BL_REQUIRE(phase_bits == 0 || phase != nullptr, "lattice_update_many: null phase array");
+  // the tensors are updated one after the other on the stream and share the scratch, whose size must cover the largest
+  for (int i = 0; i < count; ++i) {
+    const size_t need = bl_update_scratch_bytes(rows[i], cols[i], direction, clip);
+    BL_REQUIRE(need == 0 || (scratch != nullptr && scratch_bytes >= need),
+               "lattice_update_many: tensor %d needs %zu bytes of scratch, got %zu", i, need, scratch_bytes);
+  }
+  for (int i = 0; i < count; ++i) {
+    const int rc = bl_nvfp4_lattice_update(codes[i], phase_bits ? phase[i] : nullptr, scales[i], global_scale[i], grad[i],
+                                           grad_dtype, rows[i], cols[i], offset[i], phase_bits, phase_cb, lr, decay,
+                                           rounding, seed[i], step[i], strat_j ? strat_j[i] : 0, strat_k, rule, kappa,
+                                           direction, clip, scratch, scratch_bytes, device, stream);
+    if (rc != 0) return rc;
+  }
+  return 0;
+}
+
 extern "C" int bl_direction(const void* grad, int grad_dtype, int64_t rows, int64_t cols, int direction, double clip,
                             float* D, void* scratch, size_t scratch_bytes, int device, bl_stream_t stream) {
   BL_REQUIRE(rows > 0 && cols > 0 && cols % 8 == 0, "direction: [rows, cols] with cols a multiple of 8, got %lld x %lld",

@@ -197,9 +197,26 @@ class Lattice(torch.optim.Optimizer):
             with torch.enable_grad():
                 loss = closure()
         for g in self.param_groups:
-            for p in g["params"]:
-                if p in self._done or p.grad is None:
-                    continue
+            todo = [p for p in g["params"] if p not in self._done and p.grad is not None]
+            batch = [p for p in todo if self._batchable(p, g, todo[0])]
+            if len(batch) > 1:
+                # the tensors of the group in one library call: small shards are paced by the GPU, not the interpreter
+                if self.overlap:
+                    side = self._update_stream(batch[0].device)
+                    side.wait_stream(torch.cuda.current_stream(batch[0].device))
+                    with torch.cuda.device(batch[0].device), torch.cuda.stream(side):
+                        self._update_many(batch, g)
+                    for p in batch:
+                        p.grad.record_stream(side)
+                else:
+                    with torch.cuda.device(batch[0].device):
+                        self._update_many(batch, g)
+                batched = {id(p) for p in batch}
+                todo = [p for p in todo if id(p) not in batched]
+                if self.fused_backward:
+                    for p in batch:
+                        p.grad = None
+            for p in todo:
                 if self.overlap and p.is_cuda:
                     self._update_aside(p, g)
                 else:
@@ -210,6 +227,42 @@ class Lattice(torch.optim.Optimizer):
         self._done.clear()
         self.wait()
         return loss
+
+    @staticmethod
+    def _batchable(p, g: dict, first) -> bool:
+        G = p.grad
+        return (g["momentum"] == "none" and p.is_cuda and p.device == first.device and p.fmt == first.fmt
+                and not G.is_sparse
+                and G.dtype == first.grad.dtype and G.dtype in (torch.bfloat16, torch.float16, torch.float32)
+                and G.is_contiguous())
+
+    def _update_many(self, ps, g: dict) -> None:
+        bits = g["phase_bits"]
+        cb = _ops.phase_container(bits)
+        items, need = [], 0
+        for p in ps:
+            self._invalidate(p)
+            st = self.state[p]
+            st["step"] = st.get("step", 0) + 1
+            rows, cols = p.rows, p.cols
+            if bits and "phase" not in st:
+                st["phase"] = torch.zeros(rows, packed_cols(cols, cb), dtype=torch.uint8, device=p.packed.device)
+            items.append(dict(packed=p.packed, phase=st.get("phase") if bits else None, scales=p.scales,
+                              global_scale=p.global_scale, grad=p.grad.reshape(rows, cols), rows=rows, cols=cols,
+                              offset=int(getattr(p, "_bl_row_offset", 0)) * cols,
+                              seed=(self.seed + 7919 * self._pid[p]) & 0xFFFFFFFF, step=st["step"]))
+            if self.overlap:
+                need = max(need, _ops.update_scratch_bytes(rows, cols, g["direction"], g["clip"]))
+        scratch = None
+        if self.overlap:
+            dev = ps[0].device
+            scratch = self._scratch.get(dev)
+            if need and (scratch is None or scratch.numel() < need):
+                scratch = self._scratch[dev] = torch.empty(need, dtype=torch.uint8, device=dev)
+        _ops.lattice_update_many(items, ps[0].fmt, lr=g["lr"], weight_decay=g["weight_decay"], phase_bits=bits,
+                                 phase_cb=cb, rounding=g["rounding"], strata=g["strata"], scale_rule=g["scale_rule"],
+                                 trust=g["trust"], trust_lr=g["trust_lr"], direction=g["direction"], clip=g["clip"],
+                                 scratch=scratch)
 
     @contextlib.contextmanager
     def accumulate(self):

@@ -82,6 +82,20 @@ BL_API int bl_nvfp4_lattice_update(uint8_t* codes, uint8_t* phase, uint8_t* scal
                             uint32_t step, int strat_j, int strat_k, int rule, double kappa, int direction,
                             double clip, void* scratch, size_t scratch_bytes, int device, bl_stream_t stream);
 
+/* bl_nvfp4_lattice_update for `count` tensors in one call, issued back to back on the stream without returning to the
+ * caller in between: the role of the reference's native tile loop (csrc/update.cpp:30-53, which exists so that the
+ * loop runs without the interpreter lock), applied across the tensors of a parameter group, whose shards can be so
+ * small that the interpreter, not the GPU, sets the pace. Per-tensor arrays of length count (phase may be NULL when
+ * phase_bits == 0, strat_j when rounding is not BL_ROUND_STRAT); the other settings are shared. The tensors share
+ * `scratch`, which must cover the largest bl_update_scratch_bytes among them. Stops at the first error. */
+BL_API int bl_nvfp4_lattice_update_many(int count, uint8_t* const* codes, uint8_t* const* phase, uint8_t* const* scales,
+                                 const float* const* global_scale, const void* const* grad, const int64_t* rows,
+                                 const int64_t* cols, const uint64_t* offset, const uint32_t* seed,
+                                 const uint32_t* step, const int* strat_j, int grad_dtype, int phase_bits, int phase_cb,
+                                 double lr, double decay, int rounding, int strat_k, int rule, double kappa,
+                                 int direction, double clip, void* scratch, size_t scratch_bytes, int device,
+                                 bl_stream_t stream);
+
 /* No counterpart in the reference. The same update as bl_nvfp4_lattice_update for callers that have no way to hand
  * over scratch memory: code running where cudaMalloc and the framework allocators are off limits -- a serving loop
  * with a frozen memory plan, a host thread that must not take the allocator's locks or trigger its implicit device
