@@ -10,6 +10,11 @@ so a checkpoint written here loads in the reference and the other way round. Bui
 parameters plus ordinary tensors of a module; model skeletons, Hugging Face configs and third-party quantized layouts
 (ModelOpt, compressed-tensors, GPTQ, AWQ) stay with the reference's loader.
 
+Third-party NVFP4 layouts convert without touching a code or a scale byte (reference: ``bitlattice/io/convert.py:40-54,
+155-160``): compressed-tensors 'nvfp4-pack-quantized' (``weight_packed``, ``weight_scale``, ``weight_global_scale``
+stored as a divisor) and ModelOpt NVFP4 (``weight``, ``weight_scale``, ``weight_scale_2`` stored as a multiplier)
+share the byte layout of ``packed`` / ``scales``; only the per-tensor scale changes its convention.
+
 N-sharded weights (``parallel.shard_rows``): ``save`` called by every rank of ``group`` gathers the row shards of each
 lattice parameter on rank 0, which writes the checkpoint of the unsharded model; ``load_into`` gives each rank its rows.
 """
@@ -25,7 +30,8 @@ import torch.distributed as dist
 from . import formats as F
 from .tensor import LatticeTensor
 
-__all__ = ["format_from_spec", "format_spec", "load_into", "load_state", "save"]
+__all__ = ["format_from_spec", "format_spec", "from_ct_nvfp4", "from_mo_nvfp4", "load_into", "load_state", "save",
+           "to_ct_nvfp4"]
 
 _PARTS = ("packed", "scales", "global_scale")
 
@@ -215,3 +221,37 @@ def load_into(module: torch.nn.Module, path: str, device=None, group=None) -> No
         if name in rows:
             new._bl_row_offset = rows[name][0]
         mod._parameters[leaf] = new
+
+
+# ------------------------------------------------------------------------------------ third-party NVFP4 layouts
+
+def _as_lattice(codes: torch.Tensor, scales: torch.Tensor, global_scale: torch.Tensor, dtype, device) -> LatticeTensor:
+    rows, half = codes.shape
+    if scales.shape != (rows, half // 8):
+        raise ValueError(f"scales {tuple(scales.shape)} do not match codes {tuple(codes.shape)} (one per 16 values)")
+    sc = scales.to(device).contiguous()
+    sc = sc if sc.dtype == torch.float8_e4m3fn else sc.view(torch.float8_e4m3fn)
+    return LatticeTensor(codes.to(device, torch.uint8).contiguous(), sc,
+                         global_scale.to(device, torch.float32).reshape(1), None, F.get("nvfp4"), (rows, 2 * half),
+                         dtype)
+
+
+def from_ct_nvfp4(tensors: dict, dtype=torch.bfloat16, device="cuda") -> LatticeTensor:
+    """compressed-tensors NVFP4 (value = e2m1 * weight_scale / weight_global_scale) as a lattice weight: the stored
+    divisor becomes the per-tensor multiplier 1 / weight_global_scale (fp32 division)."""
+    return _as_lattice(tensors["weight_packed"], tensors["weight_scale"],
+                       1.0 / tensors["weight_global_scale"].float(), dtype, device)
+
+
+def from_mo_nvfp4(tensors: dict, dtype=torch.bfloat16, device="cuda") -> LatticeTensor:
+    """ModelOpt NVFP4 (value = e2m1 * weight_scale * weight_scale_2) as a lattice weight."""
+    return _as_lattice(tensors["weight"], tensors["weight_scale"], tensors["weight_scale_2"].float(), dtype, device)
+
+
+def to_ct_nvfp4(w: LatticeTensor) -> dict[str, torch.Tensor]:
+    """The compressed-tensors NVFP4 tensors of a lattice weight (the inverse of ``from_ct_nvfp4`` up to the rounding of
+    the reciprocal)."""
+    if w.fmt.name != "nvfp4":
+        raise ValueError("only nvfp4 tensors are exported to compressed-tensors")
+    return {"weight_packed": w.packed.contiguous(), "weight_scale": w.scales.contiguous(),
+            "weight_global_scale": (1.0 / w.global_scale.float()).reshape(1)}

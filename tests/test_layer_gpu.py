@@ -327,3 +327,23 @@ def test_row_shard_update_equals_whole_update():
         os_.step()
         assert torch.equal(sh.packed, whole.packed[rank * 64:(rank + 1) * 64])
         assert torch.equal(os_.state[sh]["phase"], ow.state[whole]["phase"][rank * 64:(rank + 1) * 64])
+
+
+def test_converted_third_party_weights_dequantize_as_in_the_reference():
+    """compressed-tensors / ModelOpt NVFP4 tensors converted to lattice weights decode to the reference's values
+    (tests/golden/convert.npz, written by the reference's bitlattice.io.convert)."""
+    import os
+    g = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "convert.npz"))
+    t = lambda k: torch.from_numpy(g[k])
+    ct = {"weight_packed": t("ct_weight_packed"), "weight_scale": t("ct_weight_scale").view(torch.float8_e4m3fn),
+          "weight_global_scale": t("ct_weight_global_scale")}
+    mo = {"weight": t("mo_weight"), "weight_scale": t("mo_weight_scale").view(torch.float8_e4m3fn),
+          "weight_scale_2": t("mo_weight_scale_2")}
+    for w, key in ((bl.io.from_ct_nvfp4(ct, torch.bfloat16, DEV), "ct_dequant"),
+                   (bl.io.from_mo_nvfp4(mo, torch.bfloat16, DEV), "mo_dequant")):
+        assert torch.equal(w.dequantize(torch.float32).cpu(), t(key))
+        x = torch.randn(32, 128, generator=gen(4)).to(DEV, torch.bfloat16)
+        with bl.compute("fp4"):
+            y = torch.nn.functional.linear(x, w)
+        ref = x.float() @ t(key).to(DEV).t()
+        assert float((y.float() - ref).norm() / ref.norm()) < 0.1
