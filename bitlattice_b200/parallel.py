@@ -514,7 +514,9 @@ class TokenParallelLinear(torch.autograd.Function):
 def token_parallel_linear(x: torch.Tensor, w: torch.Tensor, gathered: GatheredWeights | None = None, group=None,
                           linear=None) -> torch.Tensor:
     """This rank's tokens [M/p, K], row-sharded weight [N/p, K] -> this rank's outputs [M/p, N]. ``gathered`` keeps the
-    gathered operands of the FP4 route between calls (and carries the process group)."""
+    gathered operands of the FP4 route between calls (and carries the process group). The ranks are independent
+    micro-batches: give each its own stochastic-rounding stream (``backend.set_sr_seed`` with a rank-dependent
+    start), or their rounding errors are drawn from the same numbers."""
     return token_parallel_linears(x, (w,), gathered, group, linear)[0]
 
 
