@@ -52,6 +52,12 @@ SHAPE = {n: (N, K) for n, N, K in LAYER}
 OPT = dict(lr=3e-3, direction="colnorm", phase_bits=4, rounding="sr", scale_rule="fit", trust=0.1, trust_lr=0.0,
            seed=1234)
 BYTES_PER_WEIGHT = 4.125      # codes r+w 1.0, 4-bit phase r+w 1.0, bf16 gradient 2.0, E4M3 scales r+w 0.125
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu capture of a small case summarised in
+# profiles/pair_gemm_quantizers_update_tokens8192_ncu_full.md, scaled by the units a launch processes:
+#   update_kernel 12288 x 4096: 181.5 MB for 50.3 M weights (the gradient partly still in L2 from the statistics pass)
+#   gemm_pair_kernel 8192 x 12288 x K 4096: 157.3 MB for 0.825 TFLOP (operands stream from L2, the output is written)
+NCU_UPDATE_BYTES_PER_WEIGHT = 181.5e6 / (12288 * 4096)
+NCU_GEMM_BYTES_PER_FLOP = 157.3e6 / (2.0 * 8192 * 12288 * 4096)
 
 
 def parse():
@@ -452,7 +458,10 @@ def run_ours(a):
         "clocks": res["clocks"],
         "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel (tcgen05 mxf4nvf4, cta_group::2, 256x256 tiles)", "achieved": gemm_tf,
                      "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tf / fp4_peak if gemm_tf else None,
-                     "traffic": None, "launches": res["gemm_calls"],
+                     "traffic": NCU_GEMM_BYTES_PER_FLOP * gemm_flops_rank / max(res["gemm_calls"], 1),
+                     "traffic_note": "bytes per average launch, scaled by flops from the ncu capture of a small case "
+                                     "(profiles/pair_gemm_quantizers_update_tokens8192_ncu_full.md)",
+                     "launches": res["gemm_calls"],
                      "peak_note": f"4 x bf16 sustained cuBLAS ({peaks['source']}); nominal dense FP4 9000",
                      "frac_of_nominal": gemm_tf / 9000.0 if gemm_tf else None},
         # the update alone over the whole weight set (BASELINE configs[2]): whole-job GB/s = all ranks' bytes / time;
@@ -463,7 +472,10 @@ def run_ours(a):
                    "phase, sr, scale refit (trust 0.1), sharded along N",
                    "in_step": {"value": upd_gbs, "unit": "GB/s per GPU", "calls": res["upd_calls"]},
                    "roofline": {"bound": "hbm", "achieved": upd_alone_gbs / world, "peak": peaks["hbm"],
-                                "unit": "GB/s", "frac": upd_alone_gbs / world / peaks["hbm"], "traffic": None,
+                                "unit": "GB/s", "frac": upd_alone_gbs / world / peaks["hbm"],
+                                "traffic": NCU_UPDATE_BYTES_PER_WEIGHT * weights / world,
+                                "traffic_note": "bytes per pass and GPU, scaled by weights from the ncu capture of "
+                                                "one 12288 x 4096 update (same profile)",
                                 "peak_note": f"per GPU against copy bandwidth ({peaks['source']}); nominal 8000"}},
     }
     if other is not None:
