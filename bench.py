@@ -281,10 +281,9 @@ def run_ours(a):
                     for gi, names in enumerate(GROUPS):    # forward + backward of the projections sharing an input
                         ps = order[li * len(GROUPS) + gi]
                         if gathered is not None:
-                            # the next group's weights (last updated in the previous step, which step() has
-                            # joined) are gathered while this group computes
-                            if li * len(GROUPS) + gi + 1 < len(order):
-                                gathered.prefetch(order[li * len(GROUPS) + gi + 1])
+                            # the next group's weights are gathered while this group computes (after the last
+                            # group: the first group of the next step; the gather waits for that group's update)
+                            gathered.prefetch(order[(li * len(GROUPS) + gi + 1) % len(order)])
                             ys = token_parallel_linears(xin[INPUT_OF[names[0]]], ps, gathered)
                         else:
                             ys = column_parallel_linears(xin[INPUT_OF[names[0]]], ps, group)

@@ -23,6 +23,7 @@ import torch
 
 from . import _ops
 from . import formats as F
+from .tensor import wait_for_update
 
 __all__ = ["FP4_RECIPES", "Fp4Operand", "Fp4Recipe", "as_recipe", "clear_shared", "drop_cached", "fp4_backward", "fp4_dgrad", "fp4_wgrad",
            "fp4_forward_saving", "fp4_mm", "fp4_supported", "fp4_unfit", "is_nvfp4", "nvfp4_linear", "quantize_fp4",
@@ -187,6 +188,7 @@ class _WeightOperands:
                 self.entries.move_to_end(key)
                 return entry[2]
             self._remove(key)
+        wait_for_update(w)                              # an update issued on another stream finishes before we read
         operand = make()
         nbytes = sum(t.numel() * t.element_size() for t in operand if isinstance(t, torch.Tensor))
         self.entries[key] = (version, weakref.ref(w), operand, nbytes)

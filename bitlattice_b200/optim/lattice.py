@@ -171,7 +171,16 @@ class Lattice(torch.optim.Optimizer):
         side.wait_stream(torch.cuda.current_stream(p.device))
         with torch.cuda.device(p.device), torch.cuda.stream(side), torch.no_grad():
             self._update(p, g, G)
+            self._mark_updated((p,), side)
         G.record_stream(side)                        # the gradient's memory is reused only after the update has run
+
+    @staticmethod
+    def _mark_updated(ps, side) -> None:
+        """Leave the event readers of the storage wait for (``tensor.wait_for_update``)."""
+        ev = torch.cuda.Event()
+        ev.record(side)
+        for p in ps:
+            p._bl_updated = ev
 
     @staticmethod
     def _invalidate(p: torch.Tensor) -> None:
@@ -206,6 +215,7 @@ class Lattice(torch.optim.Optimizer):
                     side.wait_stream(torch.cuda.current_stream(batch[0].device))
                     with torch.cuda.device(batch[0].device), torch.cuda.stream(side):
                         self._update_many(batch, g)
+                        self._mark_updated(batch, side)
                     for p in batch:
                         p.grad.record_stream(side)
                 else:

@@ -42,7 +42,7 @@ from collections import OrderedDict
 import torch
 import torch.distributed as dist
 
-from .tensor import LatticeTensor
+from .tensor import LatticeTensor, wait_for_update
 
 __all__ = ["ColumnParallelFp4Linear", "ColumnParallelLinear", "GatheredWeights", "TokenParallelFp4Linear",
            "TokenParallelLinear", "column_parallel_linear", "column_parallel_linears", "gathered_input_operands",
@@ -357,6 +357,7 @@ class GatheredWeights:
             n, K = w.shape
             if n % 128 or K % 64:
                 raise ValueError(f"a [{n}, {K}] shard cannot be gathered as packed operands (rows % 128, cols % 64)")
+            wait_for_update(w)                                 # an update on another stream finishes before we read
             local = backend.weight_operand(w)                  # 128-row scale tiles are whole: shards concatenate
             # W_r^T [K, n] is a column slice of W^T: its pieces arrive as [p, K, n/2] and [p, K, n/16] and are
             # permuted into place on first use

@@ -17,7 +17,7 @@ from torch.utils._pytree import tree_map
 from . import _ops
 from . import formats as F
 
-__all__ = ["LatticeTensor", "is_lattice", "to_parameter"]
+__all__ = ["LatticeTensor", "is_lattice", "to_parameter", "wait_for_update"]
 
 _PARTS = ("packed", "scales", "global_scale")
 # torch's own "no override" implementation of __torch_function__ (what nn.Parameter uses): attribute reads such as
@@ -28,6 +28,15 @@ _plain_torch_function = torch._C._disabled_torch_function_impl
 
 def is_lattice(t) -> bool:
     return isinstance(t, LatticeTensor)
+
+
+def wait_for_update(t) -> None:
+    """Make the current stream wait for the last update of ``t`` that an optimizer issued on another stream
+    (``Lattice(overlap=True)`` leaves its event in ``t._bl_updated``). Every reader of the storage calls this first, so
+    an update that is still running beside the caller's stream is never raced, whatever the order of calls."""
+    ev = getattr(t, "_bl_updated", None)
+    if ev is not None:
+        torch.cuda.current_stream(t.packed.device).wait_event(ev)
 
 
 class LatticeTensor(torch.Tensor):
@@ -88,6 +97,7 @@ class LatticeTensor(torch.Tensor):
 
     def dequantize(self, dtype: torch.dtype | None = None) -> torch.Tensor:
         dtype = dtype or self.dtype
+        wait_for_update(self)
         kd = dtype if dtype in (torch.float32, torch.bfloat16, torch.float16) else torch.float32
         w = _ops.dequantize(self.packed, self.scales, self.global_scale, None, self.fmt, self.rows, self.cols, kd)
         return w.to(dtype).reshape(self.shape)

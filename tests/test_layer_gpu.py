@@ -285,6 +285,33 @@ def test_overlapped_updates_match_step():
         assert torch.equal(o1.state[p]["phase"], o3.state[r]["phase"])
 
 
+def test_readers_wait_for_overlapped_updates():
+    """With ``overlap=True`` an update may still be running on the update stream when the weight is read again;
+    every reader (GEMM operands, dequantize) first waits for the update's event, so reading right after backward --
+    without step() in between -- sees the updated weight, as with the in-line optimizer."""
+    a, b = _make_params(40), _make_params(40)
+    o1 = bl.Lattice(a, lr=5e-3, direction="colnorm", phase_bits=4, seed=9, fused_backward=True)
+    o2 = bl.Lattice(b, lr=5e-3, direction="colnorm", phase_bits=4, seed=9, fused_backward=True, overlap=True)
+    outs = []
+    for ps in (a, b):
+        loss = 0
+        for p in ps:
+            x = torch.randn(16, p.shape[1], generator=gen(77)).to(DEV, torch.bfloat16)
+            loss = loss + torch.nn.functional.linear(x, p).float().square().mean()
+        loss.backward()                                     # hooks issue the updates; no step() yet
+        got = []
+        for p in ps:
+            x = torch.randn(32, p.shape[1], generator=gen(78)).to(DEV, torch.bfloat16)
+            with bl.compute("fp4"):
+                got.append(torch.nn.functional.linear(x, p))
+            got.append(p.dequantize(torch.float32))
+        outs.append(got)
+    assert all(hasattr(p, "_bl_updated") for p in b)
+    for u, v in zip(*outs):
+        assert torch.equal(u, v)
+    o1.step(), o2.step()
+
+
 def test_accumulate_equals_summed_gradient():
     """Reference identity (tests/test_parallel.py:131-156): with fused_backward, micro-batches inside accumulate()
     are summed and applied once."""
