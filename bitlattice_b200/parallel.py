@@ -284,7 +284,7 @@ class _GatherBatch:
     kernel per weight (``_ops.assemble_gathered``) cuts the stacked buffers back into the two GEMM operands."""
 
     def __init__(self, pieces, group, size):
-        send = torch.cat([t.reshape(-1) for t in pieces])                   # one launch; every piece is 8-byte sized
+        send = torch.cat([t.reshape(-1) for t in pieces])                   # one launch; piece sizes are multiples of 16 bytes
         self.recv = torch.empty(size, send.numel(), dtype=torch.uint8, device=send.device)
         self.work = dist.all_gather_into_tensor(self.recv, send, group=group, async_op=True)
         self.send = send
@@ -359,8 +359,8 @@ class GatheredWeights:
                 raise ValueError(f"a [{n}, {K}] shard cannot be gathered as packed operands (rows % 128, cols % 64)")
             wait_for_update(w)                                 # an update on another stream finishes before we read
             local = backend.weight_operand(w)                  # 128-row scale tiles are whole: shards concatenate
-            # W_r^T [K, n] is a column slice of W^T: its pieces arrive as [p, K, n/2] and [p, K, n/16] and are
-            # permuted into place on first use
+            # W_r^T [K, n] is a column slice of W^T: its pieces arrive as [p, K, n/2] and [p, K, n/16] and the
+            # assembly kernel puts them side by side on first use
             tp, ts, tg = _ops.requantize_nvfp4_t(w.packed, w.scales, w.global_scale, blocked=False)
             parts = [w.packed, local.scales.view(torch.uint8), tp, ts.view(torch.uint8)]
             e = _GatheredEntry()
