@@ -228,7 +228,6 @@ def run_ours(a):
             if world > 1:
                 w = shard_rows(w, rank, world)
             p = torch.nn.Parameter(w)
-            p._bl_row_offset = getattr(w, "_bl_row_offset", 0)
             params.append(p)
             meta.append((name, N, K))
     opt = bl.Lattice(params, fused_backward=True, overlap=bool(a.overlap), **OPT)

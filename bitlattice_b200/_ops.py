@@ -124,12 +124,19 @@ _scratch: dict = {}
 
 
 def _scratch_for(device: torch.device, nbytes: int) -> torch.Tensor | None:
-    """A per-device scratch buffer that only grows (column statistics of the fused update)."""
+    """The scratch buffer (column statistics of the fused update) of the calling stream: one per (device, current
+    stream), growing on demand. Kernels of one stream run in order, so they can share a buffer; callers on different
+    streams of a device (two optimizers, a user stream beside autograd's) each get their own and never race on the
+    statistics. A buffer that is outgrown is released to torch's allocator by the stream that used it, which only
+    hands the memory out again behind that stream's work."""
     if nbytes == 0:
         return None
-    buf = _scratch.get(device)
+    key = (device, _C._raw_stream(device.index) if _C._raw_stream is not None and device.index is not None
+           else torch.cuda.current_stream(device).cuda_stream)
+    buf = _scratch.get(key)
     if buf is None or buf.numel() < nbytes:
-        buf = _scratch[device] = torch.empty(nbytes, dtype=torch.uint8, device=device)
+        with torch.cuda.device(device):
+            buf = _scratch[key] = torch.empty(nbytes, dtype=torch.uint8, device=device)
     return buf
 
 
@@ -426,6 +433,24 @@ def gemm_select(kernel: str = "auto") -> None:
     "persistent": 128 x 256 tiles with one CTA per SM, "pair": 256 x 256 tiles on pairs of SMs), or hand the choice
     back to the library ("auto"). All kernels give identical results; this exists for tests and experiments."""
     _C.call("bl_nvfp4_gemm_select", GEMM_KERNELS[kernel])
+
+
+def gemm_status_async(host_flag: torch.Tensor, device: int, stream=None) -> None:
+    """Enqueue, behind the work already on the current stream of ``device``, a copy of the GEMM kernels' error flag
+    (not cleared) into ``host_flag``: a pinned int32 CPU tensor, to be read after that stream has passed the copy."""
+    if host_flag.dtype != torch.int32 or host_flag.is_cuda or not host_flag.is_pinned():
+        raise RuntimeError("gemm_status_async needs a pinned int32 host tensor")
+    st = stream if stream is not None else torch.cuda.current_stream(device).cuda_stream
+    _C.call("bl_nvfp4_gemm_status_async", host_flag.data_ptr(), int(device), st)
+
+
+def selftest_bounded_wait(device: int = 0) -> tuple[int, int]:
+    """(recorded code, kernel-returned marker) of the give-up path of the kernels' bounded waits run in isolation:
+    (9, 2) when a wait that expires records its code and the kernel still runs to its end."""
+    st, ret = ctypes.c_int(0), ctypes.c_int(0)
+    scratch = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", device))
+    _C.call("bl_selftest_bounded_wait", ctypes.byref(st), ctypes.byref(ret), scratch.data_ptr(), int(device))
+    return st.value, ret.value
 
 
 def gemm_status(device: int = 0) -> int:

@@ -90,8 +90,8 @@ __device__ __forceinline__ bool mbar_probe_cluster(uint32_t bar, uint32_t parity
 // Bounded wait: returns false when the limit expires, or when another warp of this CTA (*abort_flag) or another CTA
 // (g_gemm_error) already gave up.
 __device__ __forceinline__ bool mbar_wait(uint32_t bar, uint32_t parity, volatile int* abort_flag, int code,
-                                          int mode = 0) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+                                          int mode = 0, uint32_t limit = kSpinLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mode == 0 ? mbar_try_wait(bar, parity) : mbar_probe_cluster(bar, parity, mode)) return true;
     if ((i & 1023u) == 1023u && (*abort_flag != 0 || *reinterpret_cast<volatile int*>(&g_gemm_error) != 0))
       return false;
@@ -1087,6 +1087,25 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
   }
 }
 
+// The give-up path of mbar_wait on its own: one warp, one mbarrier that nothing ever arrives on, a short limit. No
+// TMA copy or tensor-memory operation is in flight, so the kernel simply records the code and returns.
+constexpr int kSelftestWaitCode = 9;
+
+__global__ void selftest_bounded_wait_kernel(int* returned) {
+  __shared__ uint64_t bar;
+  __shared__ int abort_flag;
+  if (threadIdx.x == 0) {
+    mbar_init(smem_u32(&bar), 1);
+    abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  __syncwarp();
+  bool ok = true;
+  if (threadIdx.x == 0) ok = mbar_wait(smem_u32(&bar), 0, &abort_flag, kSelftestWaitCode, 0, 4096u);
+  __syncwarp();
+  if (threadIdx.x == 0) *returned = ok ? 1 : 2;            // 2: the wait gave up and the kernel still reached its end
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1289,6 +1308,35 @@ extern "C" int bl_nvfp4_gemm_status(int* status, int device) {
   BL_REQUIRE(status != nullptr, "gemm_status: null output");
   BL_DEVICE(device);
   int zero = 0;
+  BL_CUDA(cudaMemcpyFromSymbol(status, g_gemm_error, sizeof(int)));
+  BL_CUDA(cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int)));
+  return 0;
+}
+
+// Copies the error flag (without clearing it) to `host_status`, which must be page-locked host memory, behind the
+// work already enqueued on `stream`; the caller reads it after a later synchronisation of that stream. This is how a
+// training loop watches the flag without a device synchronisation of its own.
+extern "C" int bl_nvfp4_gemm_status_async(int* host_status, int device, bl_stream_t stream) {
+  BL_REQUIRE(host_status != nullptr, "gemm_status_async: null output");
+  BL_DEVICE(device);
+  BL_CUDA(cudaMemcpyFromSymbolAsync(host_status, g_gemm_error, sizeof(int), 0, cudaMemcpyDeviceToHost,
+                                    reinterpret_cast<cudaStream_t>(stream)));
+  return 0;
+}
+
+// Runs the give-up path of the kernels' bounded waits in isolation (see selftest_bounded_wait_kernel) and reports
+// what bl_nvfp4_gemm_status would: *status receives the recorded code (9 when the path works), *returned 2 when the
+// kernel ran to its end after giving up. Synchronous; clears the flag; `scratch`: 4 bytes of device memory.
+extern "C" int bl_selftest_bounded_wait(int* status, int* returned, int* scratch, int device) {
+  BL_REQUIRE(status != nullptr && returned != nullptr && scratch != nullptr, "selftest_bounded_wait: null argument");
+  BL_DEVICE(device);
+  int zero = 0;
+  BL_CUDA(cudaDeviceSynchronize());
+  BL_CUDA(cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int)));
+  BL_CUDA(cudaMemcpy(scratch, &zero, sizeof(int), cudaMemcpyHostToDevice));
+  selftest_bounded_wait_kernel<<<1, 32>>>(scratch);
+  BL_CUDA(cudaGetLastError());
+  BL_CUDA(cudaMemcpy(returned, scratch, sizeof(int), cudaMemcpyDeviceToHost));
   BL_CUDA(cudaMemcpyFromSymbol(status, g_gemm_error, sizeof(int)));
   BL_CUDA(cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int)));
   return 0;

@@ -28,7 +28,7 @@ import torch
 import torch.distributed as dist
 
 from . import formats as F
-from .tensor import LatticeTensor
+from .tensor import LatticeTensor, wait_for_update
 
 __all__ = ["format_from_spec", "format_spec", "from_ct_nvfp4", "from_mo_nvfp4", "load_into", "load_state", "save",
            "to_ct_nvfp4"]
@@ -92,7 +92,6 @@ def _named_tensors(obj):
 def save(obj, path: str, max_shard_bytes: int = 4 << 30, group=None) -> None:
     """Write the parameters and buffers of ``obj`` (a module, or a mapping name -> tensor) to ``path``. With an
     initialised process group every rank calls it; rank 0 writes."""
-    from safetensors.torch import save_file
     rank, size = _world(group)
     meta: dict[str, Any] = {"version": 1, "tensors": {}}
     flat: dict[str, torch.Tensor] = {}
@@ -101,6 +100,7 @@ def save(obj, path: str, max_shard_bytes: int = 4 << 30, group=None) -> None:
             meta.setdefault("tied", {})[name] = t
             continue
         if isinstance(t, LatticeTensor):
+            wait_for_update(t)                 # an optimizer update still running on another stream finishes first
             sharded = size > 1 and hasattr(t, "_bl_row_offset")
             shape = list(t.shape)
             parts = {}
@@ -122,6 +122,15 @@ def save(obj, path: str, max_shard_bytes: int = 4 << 30, group=None) -> None:
         if size > 1:
             dist.barrier(group=group)
         return
+    try:
+        _write(path, flat, meta, max_shard_bytes)
+    finally:
+        if size > 1:                           # the other ranks wait here: reach it even when writing failed
+            dist.barrier(group=group)
+
+
+def _write(path: str, flat: dict, meta: dict, max_shard_bytes: int) -> None:
+    from safetensors.torch import save_file
     os.makedirs(path, exist_ok=True)
     shards, cur, used = [], {}, 0
     for k, v in flat.items():
@@ -141,8 +150,6 @@ def save(obj, path: str, max_shard_bytes: int = 4 << 30, group=None) -> None:
         json.dump({"metadata": {}, "weight_map": weight_map}, f, indent=1)
     with open(os.path.join(path, "bitlattice.json"), "w") as f:
         json.dump(meta, f, indent=1)
-    if size > 1:
-        dist.barrier(group=group)
 
 
 def _shard_files(path: str) -> list[str]:

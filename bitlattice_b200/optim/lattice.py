@@ -131,6 +131,7 @@ class Lattice(torch.optim.Optimizer):
         self.overlap = bool(overlap)
         self._update_streams: dict = {}
         self._scratch: dict = {}
+        self._gemm_flags: dict = {}                 # device -> (pinned int32 [1], event after its last async copy)
         self._pid = {}
         for g in self.param_groups:
             for p in g["params"]:
@@ -198,6 +199,40 @@ class Lattice(torch.optim.Optimizer):
     def synchronize(self) -> None:
         for dev in {p.device for p in self._pid if p.is_cuda}:
             torch.cuda.synchronize(dev)
+        self.check_gemm_status(wait=True)
+
+    # The GEMM kernels bound every wait; one that expires leaves a partial output and a sticky flag on the device
+    # (bl_nvfp4_gemm_status). Gradients computed from such an output must not be trained on, so the optimizer watches
+    # the flag: every step() enqueues an asynchronous copy of it into pinned host memory behind the step's work and
+    # the next step() -- or synchronize() / state_dict() -- reads the copy and raises. No host synchronisation is
+    # added to the step.
+
+    def _watch_gemm_status(self) -> None:
+        for dev in {p.device for p in self._pid if p.is_cuda}:
+            entry = self._gemm_flags.get(dev)
+            if entry is None:
+                entry = self._gemm_flags[dev] = (torch.zeros(1, dtype=torch.int32).pin_memory(), torch.cuda.Event())
+            flag, ev = entry
+            with torch.cuda.device(dev):
+                _ops.gemm_status_async(flag, dev.index if dev.index is not None else torch.cuda.current_device())
+                ev.record(torch.cuda.current_stream(dev))
+
+    def check_gemm_status(self, wait: bool = False) -> None:
+        """Raise if a GEMM kernel of an earlier step gave up on a bounded wait (its output, and any update applied
+        from it, is invalid). ``wait``: block until the copies enqueued by the last ``step()`` have arrived. The
+        device flag is cleared when the error is raised; weights updated from the failed step are not restored."""
+        for dev, (flag, ev) in self._gemm_flags.items():
+            if wait:
+                ev.synchronize()
+            elif not ev.query():
+                continue
+            code = int(flag.item())
+            if code:
+                flag.zero_()
+                _ops.gemm_status(dev.index if dev.index is not None else torch.cuda.current_device())   # clears it
+                raise RuntimeError(f"an NVFP4 GEMM kernel on {dev} gave up on a bounded wait (code {code}: 1 operand "
+                                   "loads, 2 MMA issue, 3 epilogue, 4 accumulator hand-over); outputs since then are "
+                                   "partial and updates applied from them are invalid")
 
     @torch.no_grad()
     def step(self, closure=None):
@@ -205,6 +240,7 @@ class Lattice(torch.optim.Optimizer):
         if closure is not None:
             with torch.enable_grad():
                 loss = closure()
+        self.check_gemm_status()                   # a failed GEMM of an earlier step: raise before updating further
         for g in self.param_groups:
             todo = [p for p in g["params"] if p not in self._done and p.grad is not None]
             batch = [p for p in todo if self._batchable(p, g, todo[0])]
@@ -236,6 +272,7 @@ class Lattice(torch.optim.Optimizer):
                     p.grad = None
         self._done.clear()
         self.wait()
+        self._watch_gemm_status()
         return loss
 
     @staticmethod

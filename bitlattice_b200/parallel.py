@@ -479,6 +479,7 @@ def _gather_weight_rows(w, group, requires_grad: bool):
     gathered parts."""
     if not isinstance(w, LatticeTensor):
         return _all_gather_rows(w.detach(), group).requires_grad_(requires_grad)
+    wait_for_update(w)                         # an update still running on another stream finishes first
     packed = _all_gather_rows(w.packed, group)
     scales = _all_gather_rows(w.scales.view(torch.uint8), group).view(w.scales.dtype)
     full = LatticeTensor(packed, scales, w.global_scale, None, w.fmt, (packed.shape[0], *w.shape[1:]), w.dtype,

@@ -117,10 +117,18 @@ class LatticeTensor(torch.Tensor):
         fmt, shape, dtype = ctx
         return LatticeTensor(inner["packed"], inner["scales"], inner["global_scale"], None, fmt, shape, dtype)
 
-    def _map(self, fn, shape=None, dtype=None) -> "LatticeTensor":
+    def _map(self, fn, shape=None, dtype=None, shares_storage: bool = False) -> "LatticeTensor":
+        """A LatticeTensor over ``fn`` of every part. The side attributes travel with it: a row shard stays a row
+        shard (``_bl_row_offset``: the optimizer's RNG offset and the checkpoint writer's gather depend on it), and a
+        result that shares the storage (detach, alias: what ``nn.Parameter(t)`` is made of) also keeps the weight
+        version and the event of an update still running on another stream."""
         t = LatticeTensor(fn(self.packed), fn(self.scales), fn(self.global_scale), None, self.fmt,
                           shape or self.shape, dtype or self.dtype)
         t.compute = self.compute
+        keep = ("_bl_row_offset", "_bl_version", "_bl_updated") if shares_storage else ("_bl_row_offset",)
+        for name in keep:
+            if name in self.__dict__:
+                setattr(t, name, self.__dict__[name])
         return t
 
     # operator interception
@@ -140,17 +148,22 @@ class LatticeTensor(torch.Tensor):
         kwargs = kwargs or {}
         aten = torch.ops.aten
         if func in (aten.detach.default, aten.alias.default):
-            return args[0]._map(lambda t: t)
+            return args[0]._map(lambda t: t, shares_storage=True)
         if func is aten.clone.default:
+            wait_for_update(args[0])
             return args[0]._map(lambda t: t.clone())
         if func is aten._to_copy.default:
             src = args[0]
             device = kwargs.get("device", src.device)
             dtype = kwargs.get("dtype", src.dtype)
             keep = dtype if dtype is not None and dtype.is_floating_point else src.dtype
+            wait_for_update(src)
             return src._map(lambda t: t.to(device), dtype=keep)
         if func is aten.copy_.default:
             dst, src = args[0], args[1]
+            wait_for_update(dst)                       # an update still running on another stream finishes first
+            if isinstance(src, LatticeTensor):
+                wait_for_update(src)
             dst._bl_version = getattr(dst, "_bl_version", 0) + 1          # invalidates derived GEMM operands
             if not (isinstance(src, LatticeTensor) and src.fmt == dst.fmt):
                 dense = src.dequantize(torch.float32) if isinstance(src, LatticeTensor) else src

@@ -6,7 +6,9 @@
  * the reference's csrc/bindings.cpp:75-134) for the NVFP4 format only. Conventions shared by all of them:
  *   - plain device pointers and sizes; the library never allocates or frees device memory (the caller owns every
  *     buffer, outputs included) -- scratch memory, where an operation needs some, is passed in and its size comes
- *     from the matching *_scratch_bytes function;
+ *     from the matching *_scratch_bytes function. Two exceptions, both stated at their declarations:
+ *     bl_nvfp4_lattice_update_fixed_scratch keeps its scratch in an array inside the library image, and the
+ *     diagnostic bl_selftest_division makes a temporary 8-byte allocation;
  *   - all buffers are contiguous and 16-byte aligned; shapes are validated before anything is launched;
  *   - work is enqueued on `stream` of CUDA device `device` and the call returns without synchronizing;
  *   - the return value is 0 on success, non-zero on failure; bl_last_error() then describes the failure
@@ -203,6 +205,20 @@ BL_API int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const floa
  * 3 epilogue), frees its tensor memory and returns. This call synchronizes `device`, stores the recorded code
  * (0: none) in *status and clears it. No counterpart in the reference (cuBLASLt reports nothing of the kind). */
 BL_API int bl_nvfp4_gemm_status(int* status, int device);
+
+/* The flag is sticky: once a wait has expired, every GEMM on the device gives up on its waits early (and leaves a
+ * partial output) until bl_nvfp4_gemm_status has read and cleared it, so results are not to be trusted before that.
+ * bl_nvfp4_gemm_status_async lets a training loop watch the flag without a synchronisation of its own: it enqueues,
+ * behind the work already on `stream`, a copy of the flag (not cleared) into *host_status, which must be page-locked
+ * host memory; read it once the stream has passed that point. The Python optimizer does this every step and raises
+ * before applying updates computed from a failed GEMM. No counterpart in the reference. */
+BL_API int bl_nvfp4_gemm_status_async(int* host_status, int device, bl_stream_t stream);
+
+/* Diagnostic, no counterpart in the reference: runs the give-up path of the kernels' bounded waits in isolation -- one
+ * warp waits, with a short limit, on a barrier nothing arrives on; no copy or tensor-memory operation is in flight.
+ * *status receives the code the wait recorded (9), *returned 2 when the kernel ran to its end afterwards. Synchronous;
+ * clears the error flag before and after; scratch: 4 bytes of device memory. */
+BL_API int bl_selftest_bounded_wait(int* status, int* returned, int* scratch, int device);
 
 /* SwiGLU glue between the gate/up and the down projection, every intermediate rounded to the activation type as
  * PyTorch autograd rounds F.silu(g) * u. Replaces torch.ops.bitlattice.swiglu_fwd / swiglu_bwd

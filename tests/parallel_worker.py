@@ -32,7 +32,7 @@ def token_parallel_checks(rank, world, dev, w, x, gy, w2, gy2):
     xr, gr = x[rows].contiguous(), gy[rows].contiguous()
     gathered = GatheredWeights(None)
     p = torch.nn.Parameter(shard_rows(w, rank, world))
-    p._bl_row_offset = rank * N // world
+    assert p._bl_row_offset == rank * N // world          # the shard's first row travels into the Parameter
     for got, ref in ((gathered.operand(p), backend.weight_operand(w)), (gathered.t_operand(p), backend.weight_t_operand(w))):
         assert torch.equal(got.packed, ref.packed), "gathered weight codes differ from the unsharded operand"
         assert torch.equal(got.scales.view(torch.uint8).reshape(-1), ref.scales.view(torch.uint8).reshape(-1))

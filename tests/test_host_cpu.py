@@ -134,3 +134,24 @@ def test_lattice_tensor_container_semantics():
     assert names == ["packed", "scales", "global_scale"]
     r = bl.LatticeTensor.__tensor_unflatten__(p.parts(), ctx, None, None)
     assert torch.equal(r.scales.view(torch.uint8), p.scales.view(torch.uint8))
+
+
+def test_side_attributes_travel_with_views_and_copies():
+    """A row shard stays a row shard through Parameter / detach / clone / to (the optimizer's RNG offset and the
+    checkpoint gather read ``_bl_row_offset``); storage-sharing results also keep the weight version."""
+    from bitlattice_b200.parallel import shard_rows
+    from bitlattice_b200.tensor import to_parameter
+    w = cpu_weight(rows=64, requires_grad=False)
+    for rank in range(2):
+        sh = shard_rows(w, rank, 2)
+        lo = rank * 32
+        assert sh._bl_row_offset == lo
+        sh._bl_version = 3
+        p = to_parameter(sh)
+        assert p._bl_row_offset == lo and p._bl_version == 3
+        assert torch.nn.Parameter(sh)._bl_row_offset == lo
+        assert p.detach()._bl_row_offset == lo and p.detach()._bl_version == 3
+        c = p.detach().clone()
+        assert c._bl_row_offset == lo and not hasattr(c, "_bl_version")       # fresh storage: fresh version
+        assert p.detach().to(torch.float16)._bl_row_offset == lo
+    assert not hasattr(to_parameter(w), "_bl_row_offset")

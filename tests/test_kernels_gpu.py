@@ -485,3 +485,43 @@ def test_assemble_gathered_rejects_unaligned_pieces():
         _ops.assemble_gathered(recv, 128, 64, [8, 4096, 8192, 12288])
     with pytest.raises(RuntimeError, match="rows % 128"):
         _ops.assemble_gathered(recv, 64, 64, [0, 4096, 8192, 12288])
+
+
+# ------------------------------------------------------------------------------------------------ bounded waits
+
+def test_bounded_wait_gives_up_records_its_code_and_returns():
+    """The give-up path of the GEMM kernels' waits, run alone: a warp waits on a barrier nothing arrives on, the wait
+    expires after its (short) limit, records its code in the device flag, and the kernel runs to its end. The flag
+    reads back through the status call and is clear afterwards."""
+    code, returned = _ops.selftest_bounded_wait(0)
+    assert code == 9 and returned == 2
+    assert _ops.gemm_status(0) == 0
+    # the GEMM still works after the flag has been raised and cleared
+    a = torch.randint(0, 256, (128, 64), dtype=torch.uint8, device=DEV)
+    sf = torch.full((_ops.blocked_scale_bytes(128, 8),), 56, dtype=torch.uint8, device=DEV)
+    one = torch.ones(1, device=DEV)
+    _ops.nvfp4_gemm(a, sf, one, a, sf, one)
+    assert _ops.gemm_status(0) == 0
+
+
+def test_optimizer_raises_on_a_recorded_gemm_failure():
+    """Lattice.step() copies the GEMM error flag to pinned memory behind each step and the next step (or
+    synchronize / state_dict) raises when it was set, instead of training on partial outputs."""
+    import bitlattice_b200 as bl
+    w = bl.LatticeTensor.from_float((torch.randn(64, 64, generator=gen(3)) * 0.02).to(DEV), "nvfp4", method="rtn",
+                                    dtype=torch.bfloat16)
+    p = torch.nn.Parameter(w)
+    opt = bl.Lattice([p], lr=3e-3, direction="sign", phase_bits=2)
+    p.grad = torch.randn(64, 64, device=DEV).to(torch.bfloat16)
+    opt.step()
+    opt.synchronize()                                         # flag copied and read: clean
+    flag, _ = opt._gemm_flags[p.device]
+    assert int(flag.item()) == 0
+    flag.fill_(2)                                             # what the copy would have delivered after a failure
+    p.grad = torch.randn(64, 64, device=DEV).to(torch.bfloat16)
+    before = p.packed.clone()
+    with pytest.raises(RuntimeError, match="gave up on a bounded wait"):
+        opt.step()
+    assert torch.equal(p.packed, before)                      # raised before any update was applied
+    p.grad = None
+    opt.step()                                                # reported once, cleared

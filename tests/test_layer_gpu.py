@@ -348,7 +348,7 @@ def test_row_shard_update_equals_whole_update():
     ow.step()
     for rank in range(2):
         sh = torch.nn.Parameter(shard_rows(w, rank, 2))
-        sh._bl_row_offset = sh.data._bl_row_offset if hasattr(sh.data, "_bl_row_offset") else rank * 64
+        assert sh._bl_row_offset == rank * 64              # Parameter(shard) keeps the shard's first global row
         os_ = bl.Lattice([sh], lr=3e-3, direction="sign", phase_bits=4, seed=9)
         sh.grad = G[rank * 64:(rank + 1) * 64].contiguous()
         os_.step()

@@ -115,9 +115,7 @@ def _io_worker(rank, size, port, out, ckpt, tmp):
                 self.down = torch.nn.Linear(64, 32)
                 self.register_buffer("steps", torch.zeros(5, dtype=torch.int64))
         m = Tiny().to(torch.bfloat16)
-        shard = torch.nn.Parameter(state["up.weight"])
-        shard._bl_row_offset = state["up.weight"]._bl_row_offset
-        m.up.weight = shard
+        m.up.weight = torch.nn.Parameter(state["up.weight"])           # the row offset travels with the shard
         m.up.bias = torch.nn.Parameter(full["up.bias"].clone())
         m.up.weight.packed.zero_()
         bl.io.load_into(m, tmp)

@@ -63,3 +63,41 @@ def test_fixed_scratch_update_refuses_what_does_not_fit():
     with pytest.raises(RuntimeError, match="built-in scratch holds"):
         _call("bl_nvfp4_lattice_update_fixed_scratch", one, one, one, gs, torch.zeros(8, device=DEV,
               dtype=torch.bfloat16), rows, cols, 2, 1.0, 1)
+
+
+def test_fixed_scratch_update_allocates_no_device_memory():
+    """What the entry point is for: after the first call on the device (which looks up the built-in array's address),
+    further calls leave the device's free memory and torch's allocator exactly as they were -- nothing is allocated,
+    cached or freed by the library."""
+    rows, cols = 384, 1024
+    st = _state(rows, cols, 7)
+    G = (torch.randn(rows, cols, device=DEV, generator=torch.Generator(device=DEV).manual_seed(8)) * 1e-3
+         ).to(torch.bfloat16)
+    _call("bl_nvfp4_lattice_update_fixed_scratch", *st, G, rows, cols, 2, 1.0, 1)        # first call: set-up
+    torch.cuda.synchronize()
+    before = (torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
+    for step in (2, 3, 4):
+        _call("bl_nvfp4_lattice_update_fixed_scratch", *st, G, rows, cols, 2, 1.0, step)
+    torch.cuda.synchronize()
+    after = (torch.cuda.mem_get_info()[0], torch.cuda.memory_allocated(), torch.cuda.memory_reserved())
+    assert after == before
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_fixed_scratch_update_on_a_device_that_is_not_current():
+    """The array's address is per device: a call for device 1 while device 0 is current uses device 1's copy."""
+    rows, cols = 256, 512
+    torch.cuda.set_device(0)
+    with torch.cuda.device(0):
+        ref = _state(rows, cols, 9)
+        G = (torch.randn(rows, cols, device=DEV, generator=torch.Generator(device=DEV).manual_seed(10)) * 1e-3
+             ).to(torch.bfloat16)
+        _call("bl_nvfp4_lattice_update_fixed_scratch", *ref, G, rows, cols, 2, 1.0, 1)
+    other = tuple(t.to("cuda:1") for t in _state(rows, cols, 9))
+    G1 = G.to("cuda:1")
+    torch.cuda.synchronize(1)
+    assert torch.cuda.current_device() == 0
+    _call("bl_nvfp4_lattice_update_fixed_scratch", *other, G1, rows, cols, 2, 1.0, 1)
+    torch.cuda.synchronize(1)
+    for a, b in zip(ref[:3], other[:3]):
+        assert torch.equal(a.cpu(), b.cpu())
