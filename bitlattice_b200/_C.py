@@ -31,9 +31,12 @@ _SIGNATURES = {
                                            _c.c_int, _c.c_double, _c.c_double, _c.c_int, _c.c_uint32, _c.c_uint32,
                                            _c.c_int, _c.c_int, _c.c_int, _c.c_double, _c.c_int, _c.c_double, _P,
                                            _c.c_size_t, _c.c_int, _P]),
+    "bl_update_many_scratch_bytes": (_c.c_size_t, [_c.c_int, _P, _P, _c.c_int, _c.c_double]),
     "bl_nvfp4_lattice_update_many": (_c.c_int, [_c.c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _c.c_int, _c.c_int,
                                                 _c.c_int, _c.c_double, _c.c_double, _c.c_int, _c.c_int, _c.c_int,
-                                                _c.c_double, _c.c_int, _c.c_double, _P, _c.c_size_t, _c.c_int, _P]),
+                                                _c.c_double, _c.c_int, _c.c_double, _P, _c.c_size_t, _c.c_int, _P,
+                                                _c.POINTER(_c.c_int)]),
+    "bl_update_select": (_c.c_int, [_c.c_int]),
     "bl_update_fixed_scratch_capacity": (_c.c_size_t, []),
     "bl_nvfp4_lattice_update_fixed_scratch": (_c.c_int, [_P, _P, _P, _P, _P, _c.c_int, _c.c_int64, _c.c_int64,
                                                          _c.c_uint64, _c.c_int, _c.c_int, _c.c_double, _c.c_double,

@@ -175,13 +175,29 @@ def lattice_update(packed, phase, scales, global_scale, zeros, G, fmt, rows: int
             extra_kernels=2 if need else 0)
 
 
+def update_select(route: str = "auto") -> None:
+    """Send every later lattice update of this process through the general route of the update kernel ("general") or
+    hand the choice back ("auto": the fast route where it applies). Identical results; for tests and experiments."""
+    _C.call("bl_update_select", {"auto": 0, "general": 1}[route])
+
+
+def update_many_scratch_bytes(shapes, direction: str, clip: float) -> int:
+    """Scratch with which ``lattice_update_many`` runs tensors of the given (rows, cols) in the fewest launches."""
+    n = len(shapes)
+    if n == 0:
+        return 0
+    rows = (ctypes.c_int64 * n)(*[int(r) for r, _ in shapes])
+    cols = (ctypes.c_int64 * n)(*[int(c) for _, c in shapes])
+    return int(_C.lib().bl_update_many_scratch_bytes(n, rows, cols, _DIRECTION[direction], float(clip)))
+
+
 def lattice_update_many(items, fmt, *, lr: float, weight_decay: float, phase_bits: int, phase_cb: int, rounding: str,
                         strata: int, scale_rule: str, trust: float, trust_lr: float, direction: str, clip: float = 1.0,
                         scratch: torch.Tensor | None = None) -> None:
-    """``lattice_update`` for many tensors of one parameter group in one library call (no interpreter between their
-    launches). ``items``: dicts with packed, phase (or None), scales, global_scale, grad, rows, cols, offset, seed,
-    step; all gradients of one dtype, everything on one device."""
-    import ctypes
+    """``lattice_update`` for many tensors of one parameter group in one library call: the library packs them into
+    batches of up to 40 and runs each batch as one chain of launches (statistics, their reduction, the update), so
+    small shards are not paced by launches. ``items``: dicts with packed, phase (or None), scales, global_scale, grad,
+    rows, cols, offset, seed, step; all gradients of one dtype, everything on one device."""
     if not _is_nvfp4(fmt):
         raise RuntimeError("only NVFP4 tensors (no zero points) are built")
     if direction not in _DIRECTION:
@@ -190,7 +206,6 @@ def lattice_update_many(items, fmt, *, lr: float, weight_decay: float, phase_bit
     if n == 0:
         return
     gdtype = items[0]["grad"].dtype
-    need = 0
     for it in items:
         _require(it["packed"], "packed", torch.uint8)
         _require(it["scales"], "scales")
@@ -200,23 +215,24 @@ def lattice_update_many(items, fmt, *, lr: float, weight_decay: float, phase_bit
             raise RuntimeError("gradient: bf16, fp16 or fp32 with rows*cols elements")
         if phase_bits > 0:
             _require(it["phase"], "phase", torch.uint8)
-        need = max(need, update_scratch_bytes(it["rows"], it["cols"], direction, clip))
     dev = items[0]["packed"]
     if scratch is None:
-        scratch = _scratch_for(dev.device, need)
+        scratch = _scratch_for(dev.device, update_many_scratch_bytes([(it["rows"], it["cols"]) for it in items],
+                                                                     direction, clip))
     ptrs = lambda key: (ctypes.c_void_p * n)(*[(it[key].data_ptr() if it[key] is not None else None) for it in items])
     i64 = lambda key: (ctypes.c_int64 * n)(*[int(it[key]) for it in items])
     u64 = lambda key: (ctypes.c_uint64 * n)(*[int(it[key]) & 0xFFFFFFFFFFFFFFFF for it in items])
     u32 = lambda key: (ctypes.c_uint32 * n)(*[int(it[key]) & 0xFFFFFFFF for it in items])
     jk = [strat_args(rounding, it["step"], strata) for it in items]
     sj = (ctypes.c_int * n)(*[j for j, _ in jk])
-    launches = n * (3 if need else 1)
+    launches = ctypes.c_int(0)
     _C.call("bl_nvfp4_lattice_update_many", n, ptrs("packed"), ptrs("phase") if phase_bits > 0 else None,
             ptrs("scales"), ptrs("global_scale"), ptrs("grad"), i64("rows"), i64("cols"), u64("offset"), u32("seed"),
             u32("step"), sj, _C.DTYPE[gdtype], phase_bits, phase_cb, float(lr), float(1.0 - lr * weight_decay),
             _ROUNDING[rounding], jk[0][1], _RULE[scale_rule], float(kappa(trust, trust_lr, lr)), _DIRECTION[direction],
             float(clip), _C.ptr(scratch), scratch.numel() if scratch is not None else 0, _C.device_of(dev),
-            _C.stream_of(dev), extra_kernels=launches)
+            _C.stream_of(dev), ctypes.byref(launches))
+    _C.Counters.launches += launches.value
 
 
 def direction(G, kind: str, r=None, c=None, k: int = 1, beta2: float = 0.95, block=0, ns_steps: int = 5,

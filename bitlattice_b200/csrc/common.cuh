@@ -175,6 +175,42 @@ __device__ __forceinline__ float div_rn(float x, float y, float ry) {
   return q;
 }
 
+// ---------------------------------------------------------------------------------------------- device: fp32 pairs
+// Two independent fp32 operations per instruction, each lane rounded to nearest like the scalar operation (the fused
+// multiply-add is written out only where a single rounding is wanted: the residuals of the divisions).
+
+using f32x2 = unsigned long long;
+
+__device__ __forceinline__ f32x2 pk(float lo, float hi) {
+  f32x2 r;
+  asm("mov.b64 %0, {%1, %2};" : "=l"(r) : "f"(lo), "f"(hi));
+  return r;
+}
+__device__ __forceinline__ void upk(f32x2 p, float& lo, float& hi) { asm("mov.b64 {%0, %1}, %2;" : "=f"(lo), "=f"(hi) : "l"(p)); }
+__device__ __forceinline__ f32x2 mul2p(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("mul.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 add2p(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(r) : "l"(a), "l"(b));
+  return r;
+}
+__device__ __forceinline__ f32x2 fma2p(f32x2 a, f32x2 b, f32x2 c) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
+  return r;
+}
+// x / y per lane from ny = -y and ry = rcp_rn(y): div_rn without its range check (the caller establishes the range)
+__device__ __forceinline__ f32x2 div2p(f32x2 x, f32x2 ny, f32x2 ry) {
+  const f32x2 q0 = mul2p(x, ry);
+  f32x2 e = fma2p(ny, q0, x);
+  f32x2 q = fma2p(e, ry, q0);
+  e = fma2p(ny, q, x);
+  return fma2p(e, ry, q);
+}
+
 // ---------------------------------------------------------------------------------------------- device: fast E2M1
 // The hardware conversion cvt.rn.satfinite.e2m1x2.f32 rounds two floats to E2M1 nibbles (ties to even, -0 kept).
 // It gives the reference's code (ties to the lower level, +0 only) whenever its input is not at, or within rounding

@@ -611,6 +611,30 @@ __global__ void selftest_division_kernel(uint64_t n, uint32_t seed, unsigned lon
     const float y = __uint_as_float((b & 0x807FFFFFu) | (eb << 23));
     const float q = div_rn(x, y, __frcp_rn(y));
     bad += __float_as_uint(q) != __float_as_uint(x / y);
+    // the packed sequence (no range check of its own): both lanes, inside the range its callers establish
+    const float x2 = __uint_as_float(__float_as_uint(x) ^ 0x00155555u);
+    float q0, q1;
+    upk(div2p(pk(x, x2), pk(-y, -y), pk(__frcp_rn(y), __frcp_rn(y))), q0, q1);
+    const float qa = fabsf(x / y), qb = fabsf(x2 / y);
+    if (qa > 3.2e-30f && qa < 3.1e29f && fabsf(x) > 3.2e-30f)
+      bad += __float_as_uint(q0) != __float_as_uint(x / y);
+    if (qb > 3.2e-30f && qb < 3.1e29f && fabsf(x2) > 3.2e-30f)
+      bad += __float_as_uint(q1) != __float_as_uint(x2 / y);
+    // packed multiply and add against the scalar operations
+    float m0, m1, s0, s1;
+    upk(mul2p(pk(x, x2), pk(y, x)), m0, m1);
+    upk(add2p(pk(x, x2), pk(y, -x)), s0, s1);
+    bad += __float_as_uint(m0) != __float_as_uint(x * y);
+    bad += __float_as_uint(m1) != __float_as_uint(x2 * x);
+    bad += __float_as_uint(s0) != __float_as_uint(x + y);
+    bad += __float_as_uint(s1) != __float_as_uint(x2 - x);
+    // A packed product must not feed a packed sum: the assembler contracts that pair into one fused multiply-add
+    // even under --fmad=false. Products that feed sums are therefore formed by the scalar round-to-nearest multiply,
+    // which is never contracted, and only then packed; that pattern is checked here.
+    float c0, c1;
+    upk(add2p(pk(__fmul_rn(x, y), __fmul_rn(x2, y)), pk(x2, x)), c0, c1);
+    bad += __float_as_uint(c0) != __float_as_uint(__fadd_rn(__fmul_rn(x, y), x2));
+    bad += __float_as_uint(c1) != __float_as_uint(__fadd_rn(__fmul_rn(x2, y), x));
   }
   if (bad) atomicAdd(mismatches, bad);
 }

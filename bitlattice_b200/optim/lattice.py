@@ -286,7 +286,7 @@ class Lattice(torch.optim.Optimizer):
     def _update_many(self, ps, g: dict) -> None:
         bits = g["phase_bits"]
         cb = _ops.phase_container(bits)
-        items, need = [], 0
+        items = []
         for p in ps:
             self._invalidate(p)
             st = self.state[p]
@@ -298,10 +298,9 @@ class Lattice(torch.optim.Optimizer):
                               global_scale=p.global_scale, grad=p.grad.reshape(rows, cols), rows=rows, cols=cols,
                               offset=int(getattr(p, "_bl_row_offset", 0)) * cols,
                               seed=(self.seed + 7919 * self._pid[p]) & 0xFFFFFFFF, step=st["step"]))
-            if self.overlap:
-                need = max(need, _ops.update_scratch_bytes(rows, cols, g["direction"], g["clip"]))
         scratch = None
-        if self.overlap:
+        if self.overlap:                             # updates that run beside the caller's stream: a buffer of their own
+            need = _ops.update_many_scratch_bytes([(it["rows"], it["cols"]) for it in items], g["direction"], g["clip"])
             dev = ps[0].device
             scratch = self._scratch.get(dev)
             if need and (scratch is None or scratch.numel() < need):

@@ -77,26 +77,38 @@ BL_API size_t bl_update_scratch_bytes(int64_t rows, int64_t cols, int direction,
  * kernel and the fp32 direction is never written to memory. D = U / max(rms(U)/clip, 1) with U = G, sign(G) or
  * G / (sqrt(mean_rows(G^2)) + 1e-30) (bitlattice/_ops.py:135-144, bitlattice/reference.py:488-490). Scales are
  * updated in place. Directions other than sign with clip >= 1 first reduce column statistics into `scratch`
- * (fixed reduction order: 128-row panels summed sequentially, then panels in ascending order). */
+ * (fixed reduction order: 16 rows summed sequentially, eight such sums in ascending order per 128-row panel, then the
+ * panels in ascending order). */
 BL_API int bl_nvfp4_lattice_update(uint8_t* codes, uint8_t* phase, uint8_t* scales, const float* global_scale,
                             const void* grad, int grad_dtype, int64_t rows, int64_t cols, uint64_t offset,
                             int phase_bits, int phase_cb, double lr, double decay, int rounding, uint32_t seed,
                             uint32_t step, int strat_j, int strat_k, int rule, double kappa, int direction,
                             double clip, void* scratch, size_t scratch_bytes, int device, bl_stream_t stream);
 
-/* bl_nvfp4_lattice_update for `count` tensors in one call, issued back to back on the stream without returning to the
- * caller in between: the role of the reference's native tile loop (csrc/update.cpp:30-53, which exists so that the
- * loop runs without the interpreter lock), applied across the tensors of a parameter group, whose shards can be so
- * small that the interpreter, not the GPU, sets the pace. Per-tensor arrays of length count (phase may be NULL when
- * phase_bits == 0, strat_j when rounding is not BL_ROUND_STRAT); the other settings are shared. The tensors share
- * `scratch`, which must cover the largest bl_update_scratch_bytes among them. Stops at the first error. */
+/* bl_nvfp4_lattice_update for `count` tensors in one call: the role of the reference's native tile loop
+ * (csrc/update.cpp:30-53, which exists so that the loop runs without the interpreter lock), applied across the tensors
+ * of a parameter group, whose shards can be so small that launches, not the GPU, set the pace. The tensors are
+ * packed, in order, into batches of up to 40; a batch is ONE chain of launches (column statistics of all its tensors,
+ * their reduction, the update of all its tensors), each kernel finding its tensor from a descriptor list passed in the
+ * kernel parameters. Per-tensor arrays of length count (phase may be NULL when phase_bits == 0, strat_j when rounding
+ * is not BL_ROUND_STRAT); the other settings are shared. `scratch` must cover the largest single
+ * bl_update_scratch_bytes among the tensors; with bl_update_many_scratch_bytes(...) bytes every batch is full, with
+ * less a batch closes when the next tensor's statistics would not fit beside those in it. launches (nullable) receives
+ * the number of kernels launched. Results are identical to calling bl_nvfp4_lattice_update per tensor. */
+BL_API size_t bl_update_many_scratch_bytes(int count, const int64_t* rows, const int64_t* cols, int direction, double clip);
 BL_API int bl_nvfp4_lattice_update_many(int count, uint8_t* const* codes, uint8_t* const* phase, uint8_t* const* scales,
                                  const float* const* global_scale, const void* const* grad, const int64_t* rows,
                                  const int64_t* cols, const uint64_t* offset, const uint32_t* seed,
                                  const uint32_t* step, const int* strat_j, int grad_dtype, int phase_bits, int phase_cb,
                                  double lr, double decay, int rounding, int strat_k, int rule, double kappa,
                                  int direction, double clip, void* scratch, size_t scratch_bytes, int device,
-                                 bl_stream_t stream);
+                                 bl_stream_t stream, int* launches);
+
+/* The update kernel has two routes with identical results: a fast one (stochastic rounding, 1..7 phase bits: packed
+ * fp32 pairs, one range check per element instead of one per division; single groups whose values leave that range
+ * fall back) and a general one. 1 forces the general route for every later update of this process (tests,
+ * experiments), 0 hands the choice back. No counterpart in the reference. */
+BL_API int bl_update_select(int route);
 
 /* No counterpart in the reference. The same update as bl_nvfp4_lattice_update for callers that have no way to hand
  * over scratch memory: code running where cudaMalloc and the framework allocators are off limits -- a serving loop

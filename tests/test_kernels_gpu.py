@@ -143,6 +143,139 @@ def test_fused_update_matches_oracle(direction, clip, gdtype):
     assert np.array_equal(host(Dg), D)
 
 
+@pytest.mark.parametrize("direction", ["sign", "raw", "colnorm"])
+@pytest.mark.parametrize("clip", [1.0, 0.25])
+def test_fused_update_with_extreme_gradient_values(direction, clip):
+    """Zeros (single, a whole row, a whole column), values next to and inside the subnormal range, and very large
+    values: the groups that hold them leave the range in which the update's unchecked divisions are exact and take
+    the general route; results stay bit-identical to the oracle's, for those groups and for their neighbours."""
+    rows, cols = 200, 256
+    codes, scales, g = nvfp4_weights(rows, cols, 44)
+    G = torch.randn(rows, cols, generator=gen(45)) * 1e-3
+    G[3, 5] = 0.0
+    G[7] = 0.0
+    G[:, 33] = 0.0
+    G[11, 64:80] = torch.tensor([1e-30, -1e-38, 1e-42, -1e-45, 3e-39, 1e-20, -1e-25, 2e-33] * 2)
+    G[13, 100] = 1e15
+    G[17, 200] = -3e12
+    G[19, 16:32] = 1e-12
+    D, _ = oracle.direction(G.numpy(), direction, clip)
+    kw = dict(lr=3e-3, weight_decay=0.0, phase_bits=4, rounding="sr", seed=77, step=5, scale_rule="fit", trust=0.1,
+              trust_lr=0.0)
+    ph0 = np.zeros((rows, cols // 2), np.uint8)
+    rc, rp, rs = oracle.lattice_step(codes, ph0, scales, g, D, **kw)
+    packed, phase, sc = dev(codes), dev(ph0), dev(scales)
+    _ops.lattice_update(packed, phase, sc, dev(np.array([g], np.float32)), None, dev(G), "nvfp4", rows, cols,
+                        phase_cb=4, strata=16, direction=direction, clip=clip, **kw)
+    assert np.array_equal(host(sc), rs)
+    assert np.array_equal(host(packed), rc)
+    assert np.array_equal(host(phase), rp)
+
+
+@pytest.mark.parametrize("lr,wd", [(1e-12, 0.0), (300.0, 0.0), (3e-3, 0.3)])
+def test_fused_update_with_unusual_step_sizes(lr, wd):
+    """Learning rates outside the fast route's window (every group takes the general route) and a weight decay."""
+    rows, cols = 64, 128
+    codes, scales, g = nvfp4_weights(rows, cols, 46)
+    G = (torch.randn(rows, cols, generator=gen(47)) * 1e-3).to(torch.bfloat16)
+    D, _ = oracle.direction(G.float().numpy(), "colnorm", 1.0)
+    kw = dict(lr=lr, weight_decay=wd, phase_bits=4, rounding="sr", seed=5, step=1, scale_rule="fit", trust=0.1,
+              trust_lr=0.0)
+    ph0 = np.zeros((rows, cols // 2), np.uint8)
+    rc, rp, rs = oracle.lattice_step(codes, ph0, scales, g, D, **kw)
+    packed, phase, sc = dev(codes), dev(ph0), dev(scales)
+    _ops.lattice_update(packed, phase, sc, dev(np.array([g], np.float32)), None, dev(G), "nvfp4", rows, cols,
+                        phase_cb=4, strata=16, direction="colnorm", clip=1.0, **kw)
+    assert np.array_equal(host(sc), rs) and np.array_equal(host(packed), rc) and np.array_equal(host(phase), rp)
+
+
+@pytest.mark.parametrize("bits", [1, 2, 3, 4, 6, 7, 8])
+@pytest.mark.parametrize("rule", ["fixed", "fit", "fit_latent"])
+def test_fused_update_matches_oracle_for_every_phase_width(bits, rule):
+    """Two steps from a random phase state: 1..7 bits run the packed fast route, 8 bits the general one."""
+    from bitlattice_b200.packing import pack
+    rows, cols = 96, 256
+    codes, scales, g = nvfp4_weights(rows, cols, 50 + bits)
+    cb = _ops.phase_container(bits)
+    raw = torch.randint(0, 1 << bits, (rows, cols), generator=gen(60 + bits), dtype=torch.int32)
+    phase = pack(raw, cb).numpy()
+    packed, ph, sc = dev(codes), dev(phase), dev(scales)
+    gs = dev(np.array([g], np.float32))
+    for step in (1, 2):
+        G = (torch.randn(rows, cols, generator=gen(70 + step)) * 1e-3).to(torch.bfloat16)
+        D, _ = oracle.direction(G.float().numpy(), "colnorm", 1.0)
+        kw = dict(lr=3e-2, weight_decay=0.01, phase_bits=bits, rounding="sr", seed=9, step=step, scale_rule=rule,
+                  trust=0.1, trust_lr=0.0)
+        codes, phase, scales = oracle.lattice_step(codes, phase, scales, g, D, **kw)
+        _ops.lattice_update(packed, ph, sc, gs, None, dev(G), "nvfp4", rows, cols, phase_cb=cb, strata=16,
+                            direction="colnorm", clip=1.0, **kw)
+        assert np.array_equal(host(sc), scales) and np.array_equal(host(packed), codes)
+        assert np.array_equal(host(ph), phase)
+
+
+@pytest.mark.parametrize("direction,clip", [("colnorm", 1.0), ("sign", 1.0), ("raw", 0.5)])
+def test_update_many_equals_one_call_per_tensor(direction, clip):
+    """bl_nvfp4_lattice_update_many packs its tensors into batches that share every launch; with ample scratch (full
+    batches of 40), with the minimum (a batch closes early) and tensor by tensor the results are identical."""
+    shapes = [(32, 64), (128, 256), (300, 512), (16, 16), (257, 1024)] * 9 + [(64, 4096)]          # 46 tensors
+    def fresh():
+        items = []
+        for i, (r, c) in enumerate(shapes):
+            codes, scales, g = nvfp4_weights(r, c, 100 + (i % 5))
+            G = (torch.randn(r, c, generator=gen(200 + i)) * (3.0 if direction == "raw" else 1e-3)).to(torch.bfloat16)
+            items.append(dict(packed=dev(codes), phase=torch.zeros(r, c // 2, dtype=torch.uint8, device=DEV),
+                              scales=dev(scales), global_scale=dev(np.array([g], np.float32)), grad=dev(G), rows=r,
+                              cols=c, offset=i * 1000, seed=11 + i, step=1 + i % 3))
+        return items
+    kw = dict(lr=3e-3, weight_decay=0.0, phase_bits=4, phase_cb=4, rounding="sr", strata=16, scale_rule="fit", trust=0.1,
+              trust_lr=0.0, direction=direction, clip=clip)
+    one = fresh()
+    for it in one:
+        _ops.lattice_update(it["packed"], it["phase"], it["scales"], it["global_scale"], None, it["grad"], "nvfp4",
+                            it["rows"], it["cols"], seed=it["seed"], step=it["step"], offset=it["offset"], **kw)
+    full = fresh()
+    _ops.lattice_update_many(full, "nvfp4", **kw)
+    tight = fresh()
+    need = max(_ops.update_scratch_bytes(r, c, direction, clip) for r, c in shapes)
+    scratch = torch.empty(max(need, 16), dtype=torch.uint8, device=DEV) if need else None
+    _ops.lattice_update_many(tight, "nvfp4", scratch=scratch, **kw)
+    for a, b, c in zip(one, full, tight):
+        for k in ("packed", "phase", "scales"):
+            assert torch.equal(a[k], b[k]) and torch.equal(a[k], c[k]), (k, a["rows"], a["cols"])
+
+
+@pytest.mark.parametrize("direction", ["colnorm", "sign", "raw"])
+@pytest.mark.parametrize("bits,wd,lr", [(4, 0.0, 3e-3), (4, 0.01, 3e-2), (7, 0.01, 3e-2), (2, 0.1, 1e-1)])
+def test_update_routes_agree_at_scale(direction, bits, wd, lr):
+    """The fast route of the update kernel (packed pairs, one range check per element) against its general route on
+    16.7 M weights with a random phase state: identical codes, phase and scale bytes. (With a weight decay and a large
+    step every product feeds a sum with cancellation: a single contracted multiply-add would show here.)"""
+    rows, cols = 4096, 4096
+    dg = lambda s: torch.Generator(device=DEV).manual_seed(s)
+    w = torch.randn(rows, cols, device=DEV, generator=dg(0)) * 0.02
+    gs = _ops.amax_global(w)[1:2].clone()
+    packed0, scales0 = _ops.quantize_nvfp4(w, gs)
+    cb = _ops.phase_container(bits)
+    per = 8 // cb
+    vals = torch.randint(0, 1 << bits, (rows, cols // per, per), device=DEV, dtype=torch.int32, generator=dg(1))
+    phase0 = sum(vals[..., j] << (cb * j) for j in range(per)).to(torch.uint8)
+    G = (torch.randn(rows, cols, device=DEV, generator=dg(2)) * (3.0 if direction == "raw" else 1e-3)).to(torch.bfloat16)
+    out = {}
+    try:
+        for route in ("general", "auto"):
+            _ops.update_select(route)
+            st = [packed0.clone(), phase0.clone(), scales0.view(torch.uint8).clone()]
+            _ops.lattice_update(st[0], st[1], st[2], gs, None, G, "nvfp4", rows, cols, lr=lr, weight_decay=wd,
+                                phase_bits=bits, phase_cb=cb, rounding="sr", seed=9, step=1, strata=16,
+                                scale_rule="fit", trust=0.1, trust_lr=0.0, direction=direction, clip=1.0)
+            out[route] = st
+    finally:
+        _ops.update_select("auto")
+    for a, b in zip(out["general"], out["auto"]):
+        assert torch.equal(a, b)
+    assert not torch.equal(out["auto"][0], packed0)
+
+
 def test_direction_close_to_reference_golden():
     g = golden("direction")
     for kind in ("raw", "sign", "colnorm"):
