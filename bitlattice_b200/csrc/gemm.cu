@@ -1106,6 +1106,77 @@ __global__ void selftest_bounded_wait_kernel(int* returned) {
   if (threadIdx.x == 0) *returned = ok ? 1 : 2;            // 2: the wait gave up and the kernel still reached its end
 }
 
+// Tensor-pipe ceiling: every SM issues block-scaled FP4 MMAs (M 128, N 256, K 64, the persistent kernel's shape) on
+// one resident pair of operand tiles filled with pseudo-random codes, with nothing else in the loop -- no loads, no
+// scale copies, no epilogue. The result is meaningless; the time is what the MMA pipe alone needs, under the power cap,
+// and serves as the measured peak the GEMM kernels are compared with.
+__global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* status) {
+  extern __shared__ uint8_t smem_raw[];
+  __shared__ uint64_t bar_storage;
+  __shared__ uint32_t tmem_slot_storage;
+  __shared__ int abort_storage;
+  const uint32_t raw_addr = smem_u32(smem_raw);
+  const uint32_t base = (raw_addr + 1023u) & ~1023u;
+  uint8_t* base_ptr = smem_raw + (base - raw_addr);
+  constexpr uint32_t kA = 128 * 128, kB = 256 * 128, kSF = 3 * 2048;      // A tile, B tile, scale blobs (A, B lo, B hi)
+  const uint32_t bar = smem_u32(&bar_storage);
+  volatile int* abort_flag = &abort_storage;
+  const int warp = threadIdx.x >> 5;
+  for (uint32_t i = threadIdx.x; i < (kA + kB) / 4; i += blockDim.x) {
+    uint32_t h = (i + blockIdx.x * 7919u) * 0x9E3779B1u;
+    h = (h ^ (h >> 15)) * 0x85EBCA77u;
+    reinterpret_cast<uint32_t*>(base_ptr)[i] = h ^ (h >> 13);
+  }
+  for (uint32_t i = threadIdx.x; i < kSF / 4; i += blockDim.x)
+    reinterpret_cast<uint32_t*>(base_ptr + kA + kB)[i] = 0x38383838u;      // UE4M3 1.0
+  if (threadIdx.x == 0) {
+    mbar_init(bar, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  asm volatile("fence.proxy.async.shared::cta;" ::: "memory");
+  if (warp == 0) tmem_alloc(smem_u32(&tmem_slot_storage), 512);
+  tcgen05_fence_before();
+  __syncthreads();
+  tcgen05_fence_after();
+  const uint32_t tmem_base = tmem_slot_storage;
+  if (warp == 0) {
+    constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(256 >> 3) << 17) | (8u << 24);
+    constexpr uint32_t kSfaCol = 256, kSfbCol = 272;
+    const uint64_t adesc = operand_desc(base), bdesc = operand_desc(base + kA);
+    const uint64_t sdesc = scale_desc(base + kA + kB);
+    uint32_t q = elect_one();
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      tmem_copy_scales_if<1>(q, tmem_base + kSfaCol + 4 * j, sdesc + 32u * j);
+      tmem_copy_scales_if<1>(q, tmem_base + kSfbCol + 8 * j, sdesc + 128u + 32u * j);
+      tmem_copy_scales_if<1>(q, tmem_base + kSfbCol + 8 * j + 4, sdesc + 256u + 32u * j);
+    }
+    uint32_t parity = 0;
+    bool ok = true;
+    for (int it = 0; it < iters && ok; ++it) {
+      q = elect_one();
+#pragma unroll
+      for (int j = 0; j < 4; ++j)
+        mma_nvf4_if<1>(q, tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
+                       tmem_base + kSfbCol + 8 * j, (it | j) != 0);
+      if ((it & 63) == 63 || it == iters - 1) {               // bound the work in flight; every wait has a limit
+        mma_commit_if<1>(q, bar);
+        ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, 8));
+        parity ^= 1u;
+        tcgen05_fence_after();
+      }
+    }
+    if (!ok && (threadIdx.x & 31) == 0) *status = 8;
+  }
+  tcgen05_fence_before();
+  __syncthreads();
+  if (warp == 0) {
+    tcgen05_fence_after();
+    tmem_dealloc(tmem_base, 512);
+  }
+}
+
 // ------------------------------------------------------------------------------------------------ host side
 
 typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
@@ -1339,5 +1410,37 @@ extern "C" int bl_selftest_bounded_wait(int* status, int* returned, int* scratch
   BL_CUDA(cudaMemcpy(returned, scratch, sizeof(int), cudaMemcpyDeviceToHost));
   BL_CUDA(cudaMemcpyFromSymbol(status, g_gemm_error, sizeof(int)));
   BL_CUDA(cudaMemcpyToSymbol(g_gemm_error, &zero, sizeof(int)));
+  return 0;
+}
+
+// Measures the tensor-pipe ceiling with mma_peak_kernel: `iters` k-tiles (4 MMAs of 128 x 256 x 64 each) per SM, timed
+// with CUDA events after one warm-up launch. *ms receives the duration, *flops the work (2 * 128 * 256 * 256 * iters
+// * SMs). Synchronous; scratch: 4 bytes of device memory for the kernel's give-up code (returned as an error).
+extern "C" int bl_selftest_mma_peak(int iters, float* ms, double* flops, int* scratch, int device) {
+  BL_REQUIRE(iters > 0 && iters <= (1 << 20) && ms && flops && scratch, "selftest_mma_peak: bad argument");
+  BL_DEVICE(device);
+  constexpr int kSmem = 128 * 128 + 256 * 128 + 3 * 2048 + 1024;
+  BL_CUDA(cudaFuncSetAttribute(mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+  const int sms = sm_count(device);
+  cudaEvent_t a, b;
+  BL_CUDA(cudaEventCreate(&a));
+  BL_CUDA(cudaEventCreate(&b));
+  int zero = 0, code = 0;
+  cudaError_t rc = cudaMemcpy(scratch, &zero, sizeof(int), cudaMemcpyHostToDevice);
+  if (rc == cudaSuccess) {
+    mma_peak_kernel<<<sms, 128, kSmem>>>(64, scratch);
+    cudaEventRecord(a);
+    mma_peak_kernel<<<sms, 128, kSmem>>>(iters, scratch);
+    cudaEventRecord(b);
+    rc = cudaEventSynchronize(b);
+  }
+  if (rc == cudaSuccess) rc = cudaGetLastError();
+  if (rc == cudaSuccess) rc = cudaEventElapsedTime(ms, a, b);
+  if (rc == cudaSuccess) rc = cudaMemcpy(&code, scratch, sizeof(int), cudaMemcpyDeviceToHost);
+  cudaEventDestroy(a);
+  cudaEventDestroy(b);
+  BL_CUDA(rc);
+  BL_REQUIRE(code == 0, "selftest_mma_peak: a bounded wait expired (code %d)", code);
+  *flops = 2.0 * 128.0 * 256.0 * 256.0 * static_cast<double>(iters) * static_cast<double>(sms);
   return 0;
 }
