@@ -19,11 +19,18 @@ local; total work is fixed (strong scaling). Two exchange patterns over that sto
           weights have rows (65,536 tokens against 1024-12288 rows here). The line then also carries the other
           pattern's throughput from a short run (`other_parallelism`).
 
-After the step measurements the lattice update alone is timed over the whole weight set (BASELINE configs[2]: bf16
-gradients ~ N(0, 1e-3^2), every rank its shards, nothing else on the GPU): `update.value` is its whole-job HBM GB/s.
+After the step measurements the lattice update alone is timed over the whole weight set (the 8B-class update workload:
+one distinct bf16 gradient ~ N(0, 1e-3^2) per parameter, resident in HBM, every rank its shards, nothing else on the
+GPU): `update.value` is its whole-job HBM GB/s. Then, on the same GPU, the GEMM kernel is timed against cuBLASLt
+(`torch._scaled_mm`, the reference's Blackwell GEMM) on the workload's GEMM shapes (`vs_cublaslt`), the 32B-class GEMM
+sweep runs (`gemm_sweep_32b`: hidden 5120 / intermediate 25600, N-sharded over the ranks) and an MMA-only kernel
+measures the tensor-pipe ceiling the roofline fractions are quoted against (`roofline.peak`).
 
 Prints one JSON line (rank 0). `value` is whole-job TFLOP/s with inputs resident in HBM; `e2e` is the same step with
-the step's inputs copied from pinned host memory and a checksum read back inside the timed region.
+the step's inputs copied from pinned host memory and a checksum read back inside the timed region. `cpu_baseline` and
+`--impl reference` time the reference's own CPU path (its Python package staged by oracle/stage_reference.py when a
+checkout was present at build time, else the C restatement in oracle/) on a bounded sample and extrapolate to the
+workload: GEMM time by flops, update time by weights.
 """
 from __future__ import annotations
 
@@ -52,11 +59,12 @@ SHAPE = {n: (N, K) for n, N, K in LAYER}
 OPT = dict(lr=3e-3, direction="colnorm", phase_bits=4, rounding="sr", scale_rule="fit", trust=0.1, trust_lr=0.0,
            seed=1234)
 BYTES_PER_WEIGHT = 4.125      # codes r+w 1.0, 4-bit phase r+w 1.0, bf16 gradient 2.0, E4M3 scales r+w 0.125
-# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from the ncu capture of a small case summarised in
-# profiles/pair_gemm_quantizers_update_tokens8192_ncu_full.md, scaled by the units a launch processes:
-#   update_kernel 12288 x 4096: 181.5 MB for 50.3 M weights (the gradient partly still in L2 from the statistics pass)
+# DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from ncu captures of small cases, scaled by the units a
+# launch processes (the summaries of those captures are kept with the other profiles of this repository):
+#   update of 12288 x 4096, colnorm: update_kernel 180.6 MB + colstats_kernel 100.9 MB + finalize 1.6 MB for 50.3 M
+#     weights (the update kernel finds part of the gradient in L2 after the statistics pass)
 #   gemm_pair_kernel 8192 x 12288 x K 4096: 157.3 MB for 0.825 TFLOP (operands stream from L2, the output is written)
-NCU_UPDATE_BYTES_PER_WEIGHT = 181.5e6 / (12288 * 4096)
+NCU_UPDATE_BYTES_PER_WEIGHT = (180.6e6 + 100.9e6 + 1.6e6) / (12288 * 4096)
 NCU_GEMM_BYTES_PER_FLOP = 157.3e6 / (2.0 * 8192 * 12288 * 4096)
 
 
@@ -68,7 +76,10 @@ def parse():
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
     ap.add_argument("--tokens", type=int, default=16 * 4096)
     ap.add_argument("--layers", type=int, default=36)
-    ap.add_argument("--cpu-tokens", type=int, default=16384, help="tokens of the bounded CPU sample")
+    ap.add_argument("--cpu-tokens", type=int, default=4096, help="tokens of the bounded CPU sample")
+    ap.add_argument("--extras", type=int, default=1, choices=[0, 1],
+                    help="1: after the step measurements also run the cuBLASLt comparison, the 32B-class GEMM sweep and "
+                         "the MMA-only ceiling; 0: skip them")
     ap.add_argument("--parallel", default="auto", choices=["auto", "column", "token"],
                     help="exchange pattern of the N-sharded weights at N > 1")
     ap.add_argument("--overlap", type=int, default=1, choices=[0, 1],
@@ -134,62 +145,143 @@ class Clocks:
 
 # ---------------------------------------------------------------------------------------------------- CPU arm
 
-def cpu_sample(tokens: int, repeats: int = 1):
-    """The reference's CPU path for one q-projection (4096 x 4096) on `tokens` tokens, restated by the oracle:
-    exact-route forward / dgrad / wgrad (dequantize to bf16, bf16 x bf16 -> fp32 contractions) and one lattice update
-    (colnorm direction + step). Returns (seconds per repeat, flops, weights, threads)."""
-    import numpy as np
-    import torch
-    import oracle
+FULL_FLOPS = lambda tokens, layers: sum(6.0 * tokens * N * K for _, N, K in LAYER) * layers      # noqa: E731
+FULL_WEIGHTS = lambda layers: sum(N * K for _, N, K in LAYER) * layers                            # noqa: E731
+
+
+def _host_threads() -> int:
+    """All host threads this process may use (torch.distributed.run exports OMP_NUM_THREADS=1 to its workers: the
+    thread counts are set explicitly, after import)."""
+    try:
+        return max(1, len(os.sched_getaffinity(0)))
+    except AttributeError:
+        return os.cpu_count() or 1
+
+
+def _reference_package():
+    """The reference's own Python package when oracle/stage_reference.py staged it at build time, else None."""
+    ref = os.path.join(ROOT, "oracle", "_ref")
+    if not os.path.isfile(os.path.join(ref, "bitlattice", "__init__.py")):
+        return None
+    if ref not in sys.path:
+        sys.path.insert(0, ref)
+    try:
+        import bitlattice
+        return bitlattice
+    except Exception as ex:                          # a dependency of the package missing on this machine
+        sys.stderr.write(f"staged reference package not importable ({type(ex).__name__}: {ex}); timing the C port\n")
+        return None
+
+
+class CpuSample:
+    """One q-projection (4096 x 4096 NVFP4 weight) on `tokens` tokens on the host cores: exact-route forward + dgrad +
+    wgrad (dequantize to bf16, bf16 GEMMs) and one lattice update with the workload's optimizer settings. `step()`
+    returns (seconds of the three GEMMs, seconds of the update). kind 'reference': the reference's own
+    F.linear / backward / bitlattice.optim.Lattice.step(); kind 'port': the C restatement of the same arithmetic."""
+
     N = K = 4096
-    g = torch.Generator().manual_seed(0)
-    w = (torch.randn(N, K, generator=g) * 0.02).numpy()
-    x = torch.randn(tokens, K, generator=g).to(torch.bfloat16)
-    gy = (torch.randn(tokens, N, generator=g) * 1e-2).to(torch.bfloat16)
-    codes, scales, gs = oracle.quantize_rows(w, None, "rtn")
-    phase = np.zeros((N, K // 2), np.uint8)
-    bits = lambda t: t.contiguous().view(torch.int16).numpy().view(np.uint16)
-    times = []
-    for _ in range(repeats):
+
+    def __init__(self, tokens: int):
+        import torch
+        self.tokens = tokens
+        self.threads = _host_threads()
+        torch.set_num_threads(self.threads)
+        self.torch = torch
+        g = torch.Generator().manual_seed(0)
+        w = torch.randn(self.N, self.K, generator=g) * 0.02
+        self.x = torch.randn(tokens, self.K, generator=g).to(torch.bfloat16)
+        self.gy = (torch.randn(tokens, self.N, generator=g) * 1e-2).to(torch.bfloat16)
+        rb = _reference_package()
+        if rb is not None:
+            self.kind = "reference"
+            self.p = torch.nn.Parameter(rb.LatticeTensor.from_float(w, "nvfp4", method="rtn", dtype=torch.bfloat16))
+            self.opt = rb.optim.Lattice([self.p], **OPT)
+        else:
+            import numpy as np
+            import oracle
+            oracle.set_num_threads(self.threads)
+            self.kind, self.np, self.oracle = "port", np, oracle
+            self.codes, self.scales, self.gs = oracle.quantize_rows(w.numpy(), None, "rtn")
+            self.phase = np.zeros((self.N, self.K // 2), np.uint8)
+            self.nstep = 0
+        self.flops = 6.0 * tokens * self.N * self.K
+        self.weights = self.N * self.K
+
+    def describe(self) -> str:
+        how = ("the reference's own Python package on CPU: F.linear exact route + backward, bitlattice.optim.Lattice.step()"
+               if self.kind == "reference" else "C restatement of the reference's CPU path (oracle/bl_oracle.c)")
+        return (f"one q-projection 4096x4096 at {self.tokens} tokens, fwd+dgrad+wgrad + colnorm lattice update, {how}; "
+                "extrapolated to the workload: GEMM seconds by flops, update seconds by weights")
+
+    def step(self):
+        torch = self.torch
+        if self.kind == "reference":
+            x = self.x.clone().requires_grad_(True)
+            t0 = time.perf_counter()
+            y = torch.nn.functional.linear(x, self.p)
+            y.backward(self.gy)
+            t1 = time.perf_counter()
+            self.opt.step()
+            self.opt.zero_grad()
+            t2 = time.perf_counter()
+            return t1 - t0, t2 - t1
+        np, oracle = self.np, self.oracle
+        bits = lambda t: t.contiguous().view(torch.int16).numpy().view(np.uint16)      # noqa: E731
         t0 = time.perf_counter()
-        wd = torch.from_numpy(oracle.dequantize(codes, scales, gs)).to(torch.bfloat16)
-        y = oracle.gemm_bf16_nt(bits(x), bits(wd))                                  # [M, N]
-        gx = oracle.gemm_bf16_nt(bits(gy), bits(wd.t()))                            # [M, K]
-        gw = oracle.gemm_bf16_nt(bits(gy.t()), bits(x.t()))                         # [N, K]
+        wd = torch.from_numpy(oracle.dequantize(self.codes, self.scales, self.gs)).to(torch.bfloat16)
+        y = oracle.gemm_bf16_nt(bits(self.x), bits(wd))                                  # [M, N]
+        gx = oracle.gemm_bf16_nt(bits(self.gy), bits(wd.t()))                            # [M, K]
+        gw = oracle.gemm_bf16_nt(bits(self.gy.t()), bits(self.x.t()))                    # [N, K]
+        del y, gx
+        t1 = time.perf_counter()
         G = torch.from_numpy(gw).to(torch.bfloat16).float().numpy()
         D, _ = oracle.direction(G, "colnorm", 1.0)
-        codes, phase, scales = oracle.lattice_step(codes, phase, scales, gs, D, lr=OPT["lr"], phase_bits=4,
-                                                   rounding="sr", seed=OPT["seed"], step=1, scale_rule="fit",
-                                                   trust=0.1, trust_lr=0.0)
-        times.append(time.perf_counter() - t0)
-        del y, gx
-    return min(times), 6.0 * tokens * N * K, N * K, oracle.num_threads()
+        self.nstep += 1
+        self.codes, self.phase, self.scales = oracle.lattice_step(
+            self.codes, self.phase, self.scales, self.gs, D, lr=OPT["lr"], phase_bits=4, rounding="sr",
+            seed=OPT["seed"], step=self.nstep, scale_rule="fit", trust=0.1, trust_lr=0.0)
+        t2 = time.perf_counter()
+        return t1 - t0, t2 - t1
+
+    def extrapolate(self, t_gemm: float, t_update: float, tokens: int, layers: int):
+        """Seconds of one full workload step on these host cores and the two factors used."""
+        fg = FULL_FLOPS(tokens, layers) / self.flops
+        fu = FULL_WEIGHTS(layers) / self.weights
+        return t_gemm * fg + t_update * fu, fg, fu
+
+
+def cpu_baseline(a, steps: int, warmup: int) -> dict:
+    """Times `steps` sample steps after `warmup`, returns the JSON fields of the CPU arm."""
+    smp = CpuSample(a.cpu_tokens)
+    for _ in range(warmup):
+        smp.step()
+    ts = [smp.step() for _ in range(max(steps, 1))]
+    tg = sum(t[0] for t in ts) / len(ts)
+    tu = sum(t[1] for t in ts) / len(ts)
+    full_s, fg, fu = smp.extrapolate(tg, tu, a.tokens, a.layers)
+    val = FULL_FLOPS(a.tokens, a.layers) / full_s / 1e12
+    return {"value": val, "unit": "TFLOP/s", "cores": smp.threads, "kind": smp.kind, "sample": smp.describe(),
+            "sample_gemm_s": tg, "sample_update_s": tu, "sample_gemm_tflops": smp.flops / tg / 1e12,
+            "sample_update_mweights_per_s": smp.weights / tu / 1e6, "extrapolation": {"gemm_by_flops": fg,
+                                                                                       "update_by_weights": fu},
+            "ms_per_step_extrapolated": full_s * 1e3, "ms_per_sample_step": (tg + tu) * 1e3}
 
 
 def run_reference(a):
-    """`--impl reference`: the reference's own CPU implementation of the path (its pure-PyTorch code cannot travel
-    to the GPU box, so the oracle -- the port pinned to it by the golden vectors -- is what runs), all host threads,
-    each step a bounded sample of the workload."""
-    rank = int(os.environ.get("RANK", "0"))
-    if rank != 0:
+    """`--impl reference`: the reference's own CPU implementation of the path on this machine's host cores (all of
+    them), each step a bounded sample of the workload. Rank 0 alone works; the other ranks exit at once."""
+    if int(os.environ.get("RANK", "0")) != 0:
         return
-    for _ in range(max(a.warmup, 0) and 1):
-        cpu_sample(a.cpu_tokens)
-    ts = []
-    for _ in range(a.steps):
-        t, flops, weights, threads = cpu_sample(a.cpu_tokens)
-        ts.append(t)
-    t = sum(ts) / len(ts)
-    sample = (f"one q-projection 4096x4096, {a.cpu_tokens} tokens: exact-route fwd+dgrad+wgrad (bf16 operands, fp32 "
-              f"accumulate) + colnorm lattice update, per step")
-    val = flops / t / 1e12
+    cb = cpu_baseline(a, a.steps, max(a.warmup, 0))
     print(json.dumps({
-        "impl": "reference", "metric": "nvfp4_linear_fwd_bwd_tflops", "value": val, "unit": "TFLOP/s",
-        "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": t * 1e3, "higher_is_better": True,
-        "scaling": "strong", "vs_baseline": None, "dtype": "bf16 (CPU exact route)", "data": "synthetic",
-        "config": {"workload": "cfg4_8b_linear_stack", "sample": sample},
-        "cpu_baseline": {"value": val, "unit": "TFLOP/s", "cores": threads, "kind": "port", "sample": sample},
-        "e2e": {"value": val, "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "impl": "reference", "metric": "nvfp4_linear_fwd_bwd_tflops", "value": cb["value"], "unit": "TFLOP/s",
+        "n_gpus": a.gpus, "steps": a.steps, "warmup": a.warmup, "ms_per_step": cb["ms_per_sample_step"],
+        "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
+        "dtype": "bf16 (CPU exact route: dequantize to bf16, fp32 accumulate)", "data": "synthetic",
+        "config": {"workload": "cfg4_8b_linear_stack", "layers": a.layers, "tokens": a.tokens,
+                   "sample": cb["sample"], "update": OPT},
+        "cpu_baseline": cb,
+        "e2e": {"value": cb["value"], "unit": "TFLOP/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }))
 
 
@@ -324,11 +416,12 @@ def run_ours(a):
             step(False)
         if clocks is not None:
             clocks.start()
-        _C.Counters.reset(timed={"bl_nvfp4_gemm", "bl_nvfp4_lattice_update"})
+        _C.Counters.reset(timed={"bl_nvfp4_gemm", "bl_nvfp4_lattice_update", "bl_nvfp4_lattice_update_many"})
         secs = timed(steps, False)
         r = {"secs": secs, "steps": steps, "launches": _C.Counters.launches, "h2d_bytes": h2d_bytes}
         r["gemm_ms"], r["gemm_calls"] = _C.Counters.elapsed_ms("bl_nvfp4_gemm")
-        r["upd_ms"], r["upd_calls"] = _C.Counters.elapsed_ms("bl_nvfp4_lattice_update")
+        u1, u2 = _C.Counters.elapsed_ms("bl_nvfp4_lattice_update"), _C.Counters.elapsed_ms("bl_nvfp4_lattice_update_many")
+        r["upd_ms"], r["upd_calls"] = u1[0] + u2[0], u1[1] + u2[1]
         _C.Counters.reset()
         r["clocks"] = clocks.stop() if clocks is not None else None
         run_steps(2, True)
@@ -374,18 +467,14 @@ def run_ours(a):
                 f.write(f"{name[:90]:90s} n={n:5d} total {d / 1e3:9.3f} ms  avg {d / n:8.1f} us\n")
 
     def update_only(passes, warm):
-        """BASELINE configs[2]: the lattice update alone over the whole weight set (every rank its shards), gradients
-        bf16 ~ N(0, 1e-3^2) resident in HBM, nothing else on the GPU. Returns seconds per pass (max over ranks)."""
+        """The 8B-class update workload: the lattice update alone over the whole weight set (every rank its shards),
+        one distinct bf16 gradient ~ N(0, 1e-3^2) per parameter resident in HBM (so that no matrix finds a gradient in
+        L2 that an earlier one pulled in), nothing else on the GPU. Returns seconds per pass (max over ranks)."""
         plain = bl.Lattice(params, fused_backward=False, **OPT)         # in-line updates, own phase state
         gen = torch.Generator(device=dev).manual_seed(99 + rank)
-        pool = {}
-        for p in params:
-            shape = tuple(p.shape)
-            if shape not in pool:
-                pool[shape] = (torch.randn(*shape, device=dev, generator=gen) * 1e-3).to(torch.bfloat16)
         with torch.no_grad():
             for p in params:
-                p.grad = pool[tuple(p.shape)]
+                p.grad = (torch.randn(*p.shape, device=dev, generator=gen) * 1e-3).to(torch.bfloat16)
 
             def run(n):
                 if world > 1:
@@ -402,17 +491,41 @@ def run_ours(a):
                     dist.all_reduce(t, op=dist.ReduceOp.MAX)
                 return t.item() / 1e3 / n
             run(warm)
+            _C.Counters.reset()
             secs = run(passes)
+            launches = _C.Counters.launches // passes
             for p in params:
                 p.grad = None
-        return secs
+        return secs, launches
+
+    def extras():
+        """Measurements beside the step, on this rank's GPU: the GEMM against cuBLASLt on the workload's shapes (this
+        rank's tokens), the 32B-class sweep on this rank's N-shard, and the MMA-only ceiling (a burst, and the average
+        over about a second of back-to-back calls: the figure for a kernel timed inside a long step)."""
+        import kernel_bench as kb
+        out = {}
+        burst = max(bl._ops.mma_peak_tflops(local, 16384) for _ in range(3))
+        t0, vals = time.perf_counter(), []
+        while time.perf_counter() - t0 < 1.0:
+            vals.append(bl._ops.mma_peak_tflops(local, 16384))
+        out["mma_only"] = {"burst": burst, "sustained": sum(vals[len(vals) // 2:]) / max(len(vals) - len(vals) // 2, 1),
+                           "unit": "TFLOP/s", "calls": len(vals)}
+        shapes = [tuple(Ms if d == 65536 else d for d in shp) for shp in kb.CFG4_GEMMS]
+        out["vs_cublaslt"] = {k: {kk: (round(vv, 3) if isinstance(vv, float) else vv) for kk, vv in r.items()}
+                              for k, r in kb.gemm_vs_cublaslt(shapes, reps=10).items()}
+        sweep = kb.gemm32b_sweep(world=world)
+        out["gemm_sweep_32b"] = {k: {kk: round(vv, 1) for kk, vv in r.items()} for k, r in sweep.items()}
+        return out
 
     res = measure(mode, a.steps, max(a.warmup, 3), Clocks(local) if rank == 0 else None, a.kernel_summary)
     other = None
     if world > 1 and a.parallel == "auto":
         other_mode = "column" if mode == "token" else "token"
         other = measure(other_mode, 1, 3)
-    upd_alone = update_only(3, 3)
+    upd_alone, upd_launches = update_only(3, 3)
+    backend._OPERANDS.clear()
+    torch.cuda.empty_cache()
+    extra = extras() if a.extras else None
     status = bl._ops.gemm_status(local)
     if world > 1:
         dist.barrier()
@@ -423,7 +536,9 @@ def run_ours(a):
 
     peaks = measured_peaks()
     per_step = res["secs"] / a.steps
-    fp4_peak = 4.0 * peaks["bf16_sustained"]
+    proxy_peak = 4.0 * peaks["bf16_sustained"]
+    mma = extra["mma_only"] if extra else None
+    fp4_peak = mma["sustained"] if mma else proxy_peak
     gemm_ms, upd_ms = res["gemm_ms"], res["upd_ms"]
     gemm_flops_rank = a.steps * flops / world                     # this rank's share of the contraction work
     gemm_tf = gemm_flops_rank / (gemm_ms / 1e3) / 1e12 if gemm_ms else None
@@ -454,37 +569,51 @@ def run_ours(a):
         "gpu_launches": res["launches"],
         "gemm_error_flag": status,
         "clocks": res["clocks"],
-        "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel (tcgen05 mxf4nvf4, cta_group::2, 256x256 tiles)", "achieved": gemm_tf,
-                     "peak": fp4_peak, "unit": "TFLOP/s", "frac": gemm_tf / fp4_peak if gemm_tf else None,
+        "whole_step": {"frac_of_mma_only_peak": flops / world / per_step / 1e12 / fp4_peak,
+                       "frac_of_nominal": flops / world / per_step / 1e12 / 9000.0,
+                       "note": "per-GPU whole-step TFLOP/s (GEMMs, quantizers, update) against the tensor ceilings"},
+        "roofline": {"bound": "tensor", "kernel": "gemm_pair_kernel (tcgen05 mxf4nvf4, cta_group::2, 256x256 tiles)",
+                     "achieved": gemm_tf, "peak": fp4_peak, "unit": "TFLOP/s",
+                     "frac": gemm_tf / fp4_peak if gemm_tf else None,
                      "traffic": NCU_GEMM_BYTES_PER_FLOP * gemm_flops_rank / max(res["gemm_calls"], 1),
-                     "traffic_note": "bytes per average launch, scaled by flops from the ncu capture of a small case "
-                                     "(profiles/pair_gemm_quantizers_update_tokens8192_ncu_full.md)",
+                     "traffic_note": "bytes per average launch, scaled by flops from the ncu capture of a small case",
                      "launches": res["gemm_calls"],
-                     "peak_note": f"4 x bf16 sustained cuBLAS ({peaks['source']}); nominal dense FP4 9000",
+                     "peak_note": ("measured on this GPU in this run: a kernel that only issues block-scaled FP4 MMAs "
+                                   "(no loads, scale copies or epilogue), averaged over about a second of back-to-back "
+                                   f"calls; burst {mma['burst']:.0f}" if mma else
+                                   f"4 x bf16 sustained cuBLAS ({peaks['source']}); the MMA-only ceiling was not run")
+                                  + f"; 4 x bf16 sustained cuBLAS ({peaks['source']}) {proxy_peak:.0f}; nominal dense "
+                                    "FP4 9000",
+                     "frac_of_4x_bf16_sustained": gemm_tf / proxy_peak if gemm_tf else None,
                      "frac_of_nominal": gemm_tf / 9000.0 if gemm_tf else None},
-        # the update alone over the whole weight set (BASELINE configs[2]): whole-job GB/s = all ranks' bytes / time;
-        # `in_step` is the same kernel timed inside the step, where (with overlap) it shares the GPU with the GEMMs
+        # the update alone over the whole weight set (the 8B-class update workload): whole-job GB/s = all ranks' bytes
+        # / time; `in_step` is the same kernel timed inside the step, where (with overlap) it shares the GPU with the GEMMs
         "update": {"metric": "lattice_update_hbm_gbs", "value": upd_alone_gbs, "unit": "GB/s", "n_gpus": world,
                    "per_gpu": upd_alone_gbs / world, "ms_per_pass": upd_alone * 1e3, "weights": weights,
+                   "launches_per_pass": upd_launches,
+                   "gradients": "one distinct bf16 tensor per parameter (none shared, none resident in L2)",
                    "bytes_per_weight": BYTES_PER_WEIGHT, "workload": f"cfg3: {a.layers} x 7 NVFP4 matrices, colnorm, 4-bit "
                    "phase, sr, scale refit (trust 0.1), sharded along N",
                    "in_step": {"value": upd_gbs, "unit": "GB/s per GPU", "calls": res["upd_calls"]},
                    "roofline": {"bound": "hbm", "achieved": upd_alone_gbs / world, "peak": peaks["hbm"],
                                 "unit": "GB/s", "frac": upd_alone_gbs / world / peaks["hbm"],
                                 "traffic": NCU_UPDATE_BYTES_PER_WEIGHT * weights / world,
-                                "traffic_note": "bytes per pass and GPU, scaled by weights from the ncu capture of "
-                                                "one 12288 x 4096 update (same profile)",
+                                "traffic_note": "bytes per pass and GPU (update, column statistics and their "
+                                                "reduction), scaled by weights from the ncu capture of one "
+                                                "12288 x 4096 update",
                                 "peak_note": f"per GPU against copy bandwidth ({peaks['source']}); nominal 8000"}},
     }
+    if extra:
+        out["vs_cublaslt"] = extra["vs_cublaslt"]
+        out["gemm_sweep_32b"] = {"unit": "TFLOP/s per GPU", "sharding": f"N / {world}", "peak": fp4_peak,
+                                 "cases": extra["gemm_sweep_32b"]}
+        out["mma_only"] = mma
     if other is not None:
         out["other_parallelism"] = {"parallelism": names[other_mode], "steps": other["steps"],
                                     "value": flops / (other["secs"] / other["steps"]) / 1e12, "unit": "TFLOP/s",
                                     "ms_per_step": other["secs"] / other["steps"] * 1e3}
     if world == 1:
-        t, cflops, _, threads = cpu_sample(a.cpu_tokens)
-        out["cpu_baseline"] = {"value": cflops / t / 1e12, "unit": "TFLOP/s", "cores": threads, "kind": "port",
-                               "sample": f"one q-projection 4096x4096 at {a.cpu_tokens} tokens (exact route fwd+dgrad+"
-                                         f"wgrad + colnorm lattice update), {t:.2f} s"}
+        out["cpu_baseline"] = cpu_baseline(a, 3, 1)
     print(json.dumps(out))
     if world > 1:
         dist.destroy_process_group()

@@ -7,7 +7,7 @@ input saved as transposed NVFP4. Where the reference calls ``torch.ops.bitlattic
 ``torch._scaled_mm`` (cuBLASLt), this module calls the kernels of ``libbitlattice_b200.so``; block scales are produced
 directly in the GEMM's tiled layout and the per-tensor scales are applied in the GEMM epilogue.
 
-Not built (the reference's other recipes): four-over-six, MS-EDEN / 128-point rotations, delayed scales, deferred
+Not built (the reference's other recipes): MS-EDEN / 128-point rotations, delayed scales, deferred
 weight gradients, MXFP8. Asking for them raises.
 """
 from __future__ import annotations

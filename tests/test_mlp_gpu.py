@@ -1,4 +1,4 @@
-"""The SwiGLU glue and the MLP block of BASELINE.json's second configuration (hidden 1024, intermediate 3072,
+"""The SwiGLU glue and the SwiGLU MLP block benchmark configuration (hidden 1024, intermediate 3072,
 8192 tokens): gate/up -> SwiGLU -> down with NVFP4 weights, all nine GEMMs on the FP4 tensor cores."""
 import pytest
 import torch
