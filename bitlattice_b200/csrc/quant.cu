@@ -429,6 +429,33 @@ __device__ __forceinline__ void rotate16_tree(const float p[16], float v[16]) {
   }
 }
 
+// The same tree for two columns at once, one in each lane of packed fp32 pairs: half the instructions. (p holds
+// products by +-1/4, which are exact, so it does not matter that a packed product feeding a packed sum is contracted
+// into one fused multiply-add.)
+__device__ __forceinline__ void rotate16_tree2(const f32x2 p[16], f32x2 v[16]) {
+  v[0] = add2p(p[0], p[1]);
+  v[1] = sub2p(p[0], p[1]);
+#pragma unroll
+  for (int n = 2; n < 16; n <<= 1) {
+#pragma unroll
+    for (int j = 0; j < n; ++j) {
+      f32x2 a = v[j], b = v[j];
+#pragma unroll
+      for (int i = 0; i < n; ++i) {
+        if (__popc(i & j) & 1) {
+          a = sub2p(a, p[n + i]);
+          b = add2p(b, p[n + i]);
+        } else {
+          a = add2p(a, p[n + i]);
+          b = sub2p(b, p[n + i]);
+        }
+      }
+      v[j] = a;
+      v[n + j] = b;
+    }
+  }
+}
+
 // any 16 x 16 matrix: for each output the ascending sum over the inputs
 __device__ __forceinline__ void rotate16_generic(const float raw[16], const float* __restrict__ sH, float v[16]) {
 #pragma unroll
@@ -482,10 +509,12 @@ __global__ void __launch_bounds__(kQThreads, 4) quantize_t3_kernel(const T* __re
         vb[i] = rb[i];
       }
     } else if (structured) {
+      f32x2 p2[16], v2[16];
 #pragma unroll
-      for (int i = 0; i < 16; ++i) mul2(ra[i], rb[i], sH[i * 16], ra[i], rb[i]);
-      rotate16_tree(ra, va);
-      rotate16_tree(rb, vb);
+      for (int i = 0; i < 16; ++i) p2[i] = mul2p(pk(ra[i], rb[i]), pk(sH[i * 16], sH[i * 16]));
+      rotate16_tree2(p2, v2);
+#pragma unroll
+      for (int i = 0; i < 16; ++i) upk(v2[i], va[i], vb[i]);
     } else {
       rotate16_generic(ra, sH, va);
       rotate16_generic(rb, sH, vb);
