@@ -521,7 +521,7 @@ def run_ours(a):
     other = None
     if world > 1 and a.parallel == "auto":
         other_mode = "column" if mode == "token" else "token"
-        other = measure(other_mode, 1, 3)
+        other = measure(other_mode, max(2, a.steps // 2), 3)     # the other exchange pattern over the same storage
     upd_alone, upd_launches = update_only(3, 3)
     backend._OPERANDS.clear()
     torch.cuda.empty_cache()
@@ -609,9 +609,12 @@ def run_ours(a):
                                  "cases": extra["gemm_sweep_32b"]}
         out["mma_only"] = mma
     if other is not None:
-        out["other_parallelism"] = {"parallelism": names[other_mode], "steps": other["steps"],
+        out["other_parallelism"] = {"parallelism": names[other_mode], "steps": other["steps"], "warmup": 3,
                                     "value": flops / (other["secs"] / other["steps"]) / 1e12, "unit": "TFLOP/s",
-                                    "ms_per_step": other["secs"] / other["steps"] * 1e3}
+                                    "ms_per_step": other["secs"] / other["steps"] * 1e3,
+                                    "e2e": flops / (other["e2e_secs"] / other["e2e_steps"]) / 1e12,
+                                    "gemm_tflops_per_gpu": (other["steps"] * flops / world / (other["gemm_ms"] / 1e3)
+                                                            / 1e12 if other["gemm_ms"] else None)}
     if world == 1:
         out["cpu_baseline"] = cpu_baseline(a, 3, 1)
     print(json.dumps(out))
