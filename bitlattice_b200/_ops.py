@@ -96,9 +96,10 @@ def dequantize(packed, scales, global_scale, zeros, fmt, rows: int, cols: int, d
 
 def step_quantized(packed, phase, scales, global_scale, zeros, D, fmt, rows: int, cols: int, *, lr: float,
                    weight_decay: float, phase_bits: int, phase_cb: int, rounding: str, seed: int, step: int,
-                   strata: int, scale_rule: str, trust: float, trust_lr: float, offset: int = 0) -> torch.Tensor:
+                   strata: int, scale_rule: str, trust: float, trust_lr: float, offset: int = 0,
+                   inplace_scales: bool = False) -> torch.Tensor:
     """In-place update of ``packed`` (and ``phase``) given the fp32 direction ``D``; returns the new scales tensor
-    (reference: bitlattice/_ops.py:76-86)."""
+    (reference: bitlattice/_ops.py:76-86), or, with ``inplace_scales``, writes them into ``scales`` itself."""
     if zeros is not None or not _is_nvfp4(fmt):
         raise RuntimeError("only NVFP4 tensors (no zero points) are built")
     _require(packed, "packed", torch.uint8)
@@ -110,7 +111,7 @@ def step_quantized(packed, phase, scales, global_scale, zeros, D, fmt, rows: int
         raise RuntimeError("D: float32 [rows*cols]")
     if phase_bits > 0:
         _require(phase, "phase", torch.uint8)
-    new_scales = torch.empty_like(scales)
+    new_scales = scales if inplace_scales else torch.empty_like(scales)
     j, k = strat_args(rounding, step, strata)
     _C.call("bl_nvfp4_step_quantized", _C.ptr(packed), _C.ptr(phase) if phase_bits > 0 else None, _C.ptr(scales),
             _C.ptr(new_scales), _C.ptr(global_scale), _C.ptr(Df), rows, cols, int(offset) & 0xFFFFFFFFFFFFFFFF,

@@ -2,16 +2,19 @@
 weights (mirror of the reference's ``bitlattice/optim/lattice.py`` for the part on the hot path).
 
 One step of a parameter W with gradient G:
-    D = direction(G), RMS-clipped          sign | colnorm | raw
+    D = direction(G), RMS-clipped
     t = latent(W, phase) * (1 - lr*wd) - lr*D
     refit the group scales inside the trust region, then project t back to (code, phase) with unbiased rounding.
-Direction, scale refit and projection run as ONE pass over codes, phase and gradient on the GPU
-(``bl_nvfp4_lattice_update``); the fp32 direction is never materialised and no row tiling is needed.
+For the directions sign, colnorm and raw, direction, scale refit and projection run as ONE pass over codes, phase and
+gradient on the GPU (``bl_nvfp4_lattice_update``): the fp32 direction is never materialised and no row tiling is
+needed. The other directions of the reference (Newton-Schulz ``muon`` / ``muon_block``, ``factored``, ``sinkhorn``,
+neuron-wise normalisation) write D first (``optim/directions.py``) and hand it to the same kernel
+(``bl_nvfp4_step_quantized``). Momentum (fp32, bf16, int8, fp8, ternary) replaces the gradient by its running average.
 
-Same constructor, option names, validation errors, per-parameter seeds (``seed + 7919 * index``), step counters and
-state layout (``state[p]["phase"]``: uint8 [rows, cols * container_bits / 8]) as the reference, so optimizer state
-interchanges. Not built, and refused with NotImplementedError: Newton-Schulz / factored / sinkhorn directions,
-low-precision momentum (momentum='fp32' is built), neuron-wise normalization, row-sparse gradients, native-format
+Same constructor, option names, presets, validation errors, per-parameter seeds (``seed + 7919 * index``), step
+counters and state layout (``state[p]["phase"]``: uint8 [rows, cols * container_bits / 8]; factored ``r`` / ``c`` /
+``k``; momentum ``m`` / ``mb`` / ``m8`` + ``m8s`` / ``mq`` + ``ms``) as the reference, so optimizer state interchanges.
+Not built, and refused with NotImplementedError: NVFP4-format momentum, row-sparse gradients, native-format
 (non-lattice) parameters and host-memory state.
 
 ``overlap=True`` (reference: lattice.py:225-253 hands each update to a worker thread that issues it on a side stream)
@@ -29,6 +32,7 @@ from typing import Any
 import torch
 
 from .. import _ops
+from . import directions as D_
 from ..packing import packed_cols
 from ..tensor import LatticeTensor
 
@@ -48,9 +52,9 @@ def defer_fused_updates(delta: int) -> None:
 
 
 DIRECTIONS = ("muon_block", "muon", "factored", "sinkhorn", "colnorm", "sign", "raw")
-BUILT_DIRECTIONS = ("colnorm", "sign", "raw")
+FUSED_DIRECTIONS = ("colnorm", "sign", "raw")        # computed inside the update kernel; the others write D first
 MOMENTA = ("none", "fp32", "ternary", "bf16", "int8", "fp8", "nvfp4")
-BUILT_MOMENTA = ("none", "fp32")
+BUILT_MOMENTA = ("none", "fp32", "ternary", "bf16", "int8", "fp8")
 ROUNDINGS = ("sr", "strat", "rtn")
 SCALE_RULES = ("fit", "fit_latent", "fixed")
 
@@ -74,13 +78,15 @@ def _validate(g: dict) -> None:
         raise ValueError("vector_direction cannot be a matrix direction")
     if g["normalize"] not in ("none", "row"):
         raise ValueError("normalize must be 'none' or 'row'")
-    if g["direction"] not in BUILT_DIRECTIONS:
-        raise NotImplementedError(f"direction={g['direction']!r} is outside this build; built: {BUILT_DIRECTIONS} "
-                                  "(pass direction= explicitly: the reference's default 'muon_block' is not built)")
     if g["momentum"] not in BUILT_MOMENTA:
-        raise NotImplementedError(f"momentum={g['momentum']!r} is outside this build; built: {BUILT_MOMENTA}")
-    if g["normalize"] != "none":
-        raise NotImplementedError("neuron-wise normalization is outside this build")
+        raise NotImplementedError(f"momentum={g['momentum']!r} is outside this build (it needs the reference's general "
+                                  f"NVFP4 quantizer); built: {BUILT_MOMENTA}")
+    if g["ns_dtype"] not in ("bf16", "fp16", "fp32"):
+        raise ValueError("ns_dtype must be 'bf16', 'fp16' or 'fp32'")
+    if g["ns_coeffs"] not in ("muon", "polar_express"):
+        raise ValueError("ns_coeffs must be 'muon' or 'polar_express'")
+    if g["ns_algo"] not in ("auto", "standard", "gram"):
+        raise ValueError("ns_algo must be 'auto', 'standard' or 'gram'")
     for p in g["params"]:
         if not isinstance(p, LatticeTensor):
             raise NotImplementedError("only NVFP4 LatticeTensor parameters are built; native-format parameters "
@@ -104,10 +110,8 @@ class Lattice(torch.optim.Optimizer):
     def __init__(self, params, preset: str | None = None, *, lr: float = DEFAULTS["lr"], state: str = "gpu",
                  fused_backward: bool = False, seed: int = 0, weight_decay: float = 0.0, overlap: bool = False,
                  **options):
-        from .presets import PRESETS, REFERENCE_PRESETS
+        from .presets import PRESETS
         if preset is not None:
-            if preset in REFERENCE_PRESETS:
-                raise NotImplementedError(f"preset {preset!r} uses directions outside this build")
             if preset not in PRESETS:
                 raise KeyError(f"unknown preset {preset!r}; known: {sorted(PRESETS)}")
             options = {**PRESETS[preset], **options}
@@ -132,6 +136,7 @@ class Lattice(torch.optim.Optimizer):
         self._update_streams: dict = {}
         self._scratch: dict = {}
         self._gemm_flags: dict = {}                 # device -> (pinned int32 [1], event after its last async copy)
+        self._gens: dict = {}                       # device -> torch.Generator of the bf16 / int8 momentum rounding
         self._pid = {}
         for g in self.param_groups:
             for p in g["params"]:
@@ -276,9 +281,21 @@ class Lattice(torch.optim.Optimizer):
         return loss
 
     @staticmethod
+    def _kind(p, g: dict) -> str:
+        """The direction of ``p``: matrices use ``direction``, vectors ``vector_direction`` (reference: lattice.py:472-473)."""
+        matrix = p.dim() >= 2 and min(p.shape[0], p.numel() // p.shape[0]) > 1
+        return g["direction"] if matrix else g["vector_direction"]
+
+    @staticmethod
+    def _fused(p, g: dict) -> bool:
+        """Whether the direction of ``p`` is computed inside the update kernel."""
+        return Lattice._kind(p, g) in FUSED_DIRECTIONS and g["normalize"] != "row"
+
+    @staticmethod
     def _batchable(p, g: dict, first) -> bool:
         G = p.grad
-        return (g["momentum"] == "none" and p.is_cuda and p.device == first.device and p.fmt == first.fmt
+        return (g["momentum"] == "none" and Lattice._fused(p, g) and Lattice._kind(p, g) == Lattice._kind(first, g)
+                and p.is_cuda and p.device == first.device and p.fmt == first.fmt
                 and not G.is_sparse
                 and G.dtype == first.grad.dtype and G.dtype in (torch.bfloat16, torch.float16, torch.float32)
                 and G.is_contiguous())
@@ -300,15 +317,16 @@ class Lattice(torch.optim.Optimizer):
                               seed=(self.seed + 7919 * self._pid[p]) & 0xFFFFFFFF, step=st["step"]))
         scratch = None
         if self.overlap:                             # updates that run beside the caller's stream: a buffer of their own
-            need = _ops.update_many_scratch_bytes([(it["rows"], it["cols"]) for it in items], g["direction"], g["clip"])
+            need = _ops.update_many_scratch_bytes([(it["rows"], it["cols"]) for it in items], self._kind(ps[0], g),
+                                                  g["clip"])
             dev = ps[0].device
             scratch = self._scratch.get(dev)
             if need and (scratch is None or scratch.numel() < need):
                 scratch = self._scratch[dev] = torch.empty(need, dtype=torch.uint8, device=dev)
         _ops.lattice_update_many(items, ps[0].fmt, lr=g["lr"], weight_decay=g["weight_decay"], phase_bits=bits,
                                  phase_cb=cb, rounding=g["rounding"], strata=g["strata"], scale_rule=g["scale_rule"],
-                                 trust=g["trust"], trust_lr=g["trust_lr"], direction=g["direction"], clip=g["clip"],
-                                 scratch=scratch)
+                                 trust=g["trust"], trust_lr=g["trust_lr"], direction=self._kind(ps[0], g),
+                                 clip=g["clip"], scratch=scratch)
 
     @contextlib.contextmanager
     def accumulate(self):
@@ -346,27 +364,45 @@ class Lattice(torch.optim.Optimizer):
         if bits and "phase" not in st:
             st["phase"] = torch.zeros(rows, packed_cols(cols, cb), dtype=torch.uint8, device=p.packed.device)
         G2 = G.reshape(rows, cols)
-        if g["momentum"] == "fp32":
-            # exponential average of the gradient in fp32, which then takes the gradient's place
-            # (reference: lattice.py:396-405: m <- beta1 * m, m <- m + (1 - beta1) * G, in place)
-            if "m" not in st:
-                st["m"] = torch.zeros(rows, cols, dtype=torch.float32, device=G2.device)
-            st["m"].mul_(g["beta1"]).add_(G2.float(), alpha=1 - g["beta1"])
-            G2 = st["m"]
+        if g["momentum"] != "none":
+            # an exponential average of the gradient, kept in the chosen format between steps, takes the gradient's place
+            G2 = D_.momentum(G2, st, g["momentum"], g["beta1"], self.seed, self._pid[p], self._gens)
         if G2.dtype not in (torch.bfloat16, torch.float16, torch.float32):
             G2 = G2.float()
+        matrix = p.dim() >= 2 and min(rows, cols) > 1
+        kind = self._kind(p, g)
+        common = dict(lr=g["lr"], weight_decay=g["weight_decay"], phase_bits=bits, phase_cb=cb, rounding=g["rounding"],
+                      seed=seed, step=st["step"], strata=g["strata"], scale_rule=g["scale_rule"], trust=g["trust"],
+                      trust_lr=g["trust_lr"], offset=int(getattr(p, "_bl_row_offset", 0)) * cols)
+        if not self._fused(p, g):
+            # directions outside the update kernel: D is written out, then the kernel takes it as given
+            r = c = None
+            if kind == "factored":
+                if "r" not in st:
+                    st["r"] = torch.zeros(rows, device=G2.device)
+                    st["c"] = torch.zeros(cols, device=G2.device)
+                    st["k"] = 0
+                st["k"] += 1
+                r, c = st["r"], st["c"]
+            row = {}
+            if g["normalize"] == "row" and matrix and kind != "factored":       # factored is adaptive already
+                if "nv" not in st:
+                    st["nv"] = torch.zeros(rows, device=G2.device)
+                row = dict(row_state=st["nv"], row_k=st["step"], row_beta=g["row_beta"], row_eps=g["row_eps"])
+            D = D_.direction(G2, kind, r, c, st.get("k", 1), g["beta2"], g["block"], g["ns_steps"], g["ns_dtype"],
+                             g["sinkhorn_iters"], g["clip"], g["ns_coeffs"], g["ns_algo"], **row)
+            _ops.step_quantized(p.packed, st.get("phase") if bits else None, p.scales, p.global_scale, None, D, p.fmt,
+                                rows, cols, inplace_scales=True, **common)
+            return
         scratch = None
         if self.overlap:                             # column statistics of updates that run beside the caller's stream
-            need = _ops.update_scratch_bytes(rows, cols, g["direction"], g["clip"])
+            need = _ops.update_scratch_bytes(rows, cols, kind, g["clip"])
             scratch = self._scratch.get(p.device)
             if need and (scratch is None or scratch.numel() < need):
                 scratch = self._scratch[p.device] = torch.empty(need, dtype=torch.uint8, device=p.device)
         _ops.lattice_update(p.packed, st.get("phase") if bits else None, p.scales, p.global_scale, None,
-                            G2.contiguous(), p.fmt, rows, cols, lr=g["lr"], weight_decay=g["weight_decay"],
-                            phase_bits=bits, phase_cb=cb, rounding=g["rounding"], seed=seed, step=st["step"],
-                            strata=g["strata"], scale_rule=g["scale_rule"], trust=g["trust"], trust_lr=g["trust_lr"],
-                            direction=g["direction"], clip=g["clip"],
-                            offset=int(getattr(p, "_bl_row_offset", 0)) * cols, scratch=scratch)
+                            G2.contiguous(), p.fmt, rows, cols, direction=kind, clip=g["clip"], scratch=scratch,
+                            **common)
 
     def state_bits(self) -> dict[str, float]:
         """Logical optimizer state in bits, by component (phase and, with momentum='fp32', the fp32 average)."""
@@ -374,7 +410,12 @@ class Lattice(torch.optim.Optimizer):
         for g in self.param_groups:
             for p in g["params"]:
                 out["phase"] += p.numel() * g["phase_bits"]
-                out["momentum"] += p.numel() * (32 if g["momentum"] == "fp32" else 0)
+                out["momentum"] += p.numel() * {"none": 0, "fp32": 32, "bf16": 16, "int8": 8 + 32 / D_.MOM_BLOCK,
+                                                "fp8": 8 + 32 / D_.MOM_BLOCK, "ternary": 8}[g["momentum"]]
+                if not self._fused(p, g):
+                    kind = g["direction"] if p.dim() >= 2 else g["vector_direction"]
+                    if kind == "factored":
+                        out["factors"] += 32 * (p.rows + p.cols)
         out["total"] = sum(out.values())
         return out
 

@@ -257,6 +257,86 @@ def momentum_cases():
     return out
 
 
+def directions2_cases():
+    """The reference's other directions on CPU (bitlattice/_ops.py:110-144 fallbacks -> reference.py:398-499): whole-
+    matrix and blocked Newton-Schulz in fp32 (standard and Gram iteration, both coefficient sets), the factored
+    direction over two steps with its running state, sinkhorn, and the neuron-wise normalisation over two steps."""
+    out = {}
+    G = (torch.randn(96, 160, generator=gen(70)) * 1e-3).to(torch.bfloat16)
+    G2 = (torch.randn(96, 160, generator=gen(71)) * 1e-3).to(torch.bfloat16)
+    out["G"], out["G2"] = G.float().numpy(), G2.float().numpy()
+    kw = dict(ns_steps=5, ns_dtype="fp32", clip=1.0)
+    out["muon"] = _ops.direction(G, "muon", **kw).numpy()
+    out["muon_tall"] = _ops.direction(G.t().contiguous(), "muon", **kw).numpy()
+    out["muon_block32"] = _ops.direction(G, "muon_block", block=32, **kw).numpy()
+    out["muon_band32_gram_pe"] = _ops.direction(G, "muon_block", block=(32, None), ns_coeffs="polar_express",
+                                                ns_algo="gram", **kw).numpy()
+    out["muon_block64x48"] = _ops.direction(G, "muon_block", block=(64, 48), ns_algo="standard", **kw).numpy()
+    out["sinkhorn"] = _ops.direction(G, "sinkhorn", sinkhorn_iters=2, clip=0.5).numpy()
+    r, c = torch.zeros(96), torch.zeros(160)
+    out["factored_1"] = _ops.direction(G, "factored", r, c, 1, 0.95, clip=1.0).numpy()
+    out["factored_2"] = _ops.direction(G2, "factored", r, c, 2, 0.95, clip=1.0).numpy()
+    out["factored_r"], out["factored_c"] = r.numpy().copy(), c.numpy().copy()
+    v = torch.zeros(96)
+    out["normuon_1"] = _ops.direction(G, "muon", row_state=v, row_k=1, **kw).numpy()
+    out["normuon_2"] = _ops.direction(G2, "muon", row_state=v, row_k=2, **kw).numpy()
+    out["normuon_v"] = v.numpy().copy()
+    return out
+
+
+def momentum2_cases():
+    """bl.optim.Lattice on CPU with the deterministic low-precision momenta (lattice.py:396-431): 'ternary' (hash-based
+    stochastic rounding) and 'fp8' (round to nearest), three steps with the sign direction; final weights, phase and
+    momentum state."""
+    out = {}
+    for mode in ("ternary", "fp8"):
+        ws = [torch.randn(32, 64, generator=gen(80)) * 0.02, torch.randn(16, 128, generator=gen(81)) * 0.02]
+        ps = [torch.nn.Parameter(bl.LatticeTensor.from_float(w, "nvfp4", method="rtn", dtype=torch.bfloat16))
+              for w in ws]
+        for i, p in enumerate(ps):
+            out[f"{mode}_p{i}_codes0"], out[f"{mode}_p{i}_scales0"] = p.packed.numpy().copy(), u8(p.scales)
+            out[f"{mode}_p{i}_g"] = p.global_scale.numpy().copy()
+        opt = bl.optim.Lattice(ps, lr=3e-3, direction="sign", phase_bits=4, scale_rule="fit", seed=777, trust=0.1,
+                               trust_lr=0.0, momentum=mode, beta1=0.9)
+        for s in range(3):
+            for i, p in enumerate(ps):
+                G = (torch.randn(p.shape, generator=gen(90 + 2 * s + i)) * 1e-2).to(torch.bfloat16)
+                out[f"{mode}_p{i}_G{s}"] = G.float().numpy()
+                p.grad = G
+            opt.step()
+        for i, p in enumerate(ps):
+            st = opt.state[p]
+            out[f"{mode}_p{i}_codes"], out[f"{mode}_p{i}_scales"] = p.packed.numpy().copy(), u8(p.scales)
+            out[f"{mode}_p{i}_phase"] = st["phase"].numpy().copy()
+            if mode == "ternary":
+                out[f"{mode}_p{i}_mq"], out[f"{mode}_p{i}_ms"] = st["mq"].numpy().copy(), st["ms"].numpy().copy()
+            else:
+                out[f"{mode}_p{i}_m8"], out[f"{mode}_p{i}_m8s"] = u8(st["m8"]), st["m8s"].numpy().copy()
+    return out
+
+
+def presets_cases():
+    """bl.optim.Lattice on CPU under presets whose directions are written out before the step ('balanced': factored;
+    'stateless': sinkhorn, no phase; 'muon' with fp32 Newton-Schulz on 32 x 32 blocks): two steps; final weights."""
+    out = {}
+    for name, extra in (("balanced", {}), ("stateless", {}), ("muon", dict(block=32, ns_dtype="fp32"))):
+        ws = [torch.randn(64, 96, generator=gen(100)) * 0.02]
+        ps = [torch.nn.Parameter(bl.LatticeTensor.from_float(w, "nvfp4", method="rtn", dtype=torch.bfloat16))
+              for w in ws]
+        out[f"{name}_codes0"], out[f"{name}_scales0"] = ps[0].packed.numpy().copy(), u8(ps[0].scales)
+        out[f"{name}_g"] = ps[0].global_scale.numpy().copy()
+        opt = bl.optim.Lattice(ps, name, lr=3e-3, seed=55, trust=0.1, trust_lr=0.0, **extra)
+        for s in range(2):
+            G = (torch.randn(64, 96, generator=gen(110 + s)) * 1e-2).to(torch.bfloat16)
+            out[f"{name}_G{s}"] = G.float().numpy()
+            ps[0].grad = G
+            opt.step()
+        out[f"{name}_codes"], out[f"{name}_scales"] = ps[0].packed.numpy().copy(), u8(ps[0].scales)
+        if "phase" in opt.state[ps[0]]:
+            out[f"{name}_phase"] = opt.state[ps[0]]["phase"].numpy().copy()
+    return out
+
+
 def linear_cases():
     """'exact' route forward / backward of one layer (the GEMM oracle), config-1-like but small."""
     M, K, N = 48, 128, 64
@@ -277,7 +357,8 @@ def main():
     for name, fn in (("hash", hash_cases), ("e4m3", e4m3_cases), ("quantize", quantize_cases),
                      ("transposed", transposed_cases), ("step", step_cases), ("direction", direction_cases),
                      ("optimizer", optimizer_cases), ("linear", linear_cases), ("fos", fos_cases),
-                     ("momentum", momentum_cases)):
+                     ("momentum", momentum_cases), ("directions2", directions2_cases),
+                     ("momentum2", momentum2_cases), ("presets", presets_cases)):
         if len(sys.argv) > 2 and name not in sys.argv[2:]:
             continue                                   # optional: names of the files to (re)generate
         data = fn()

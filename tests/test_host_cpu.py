@@ -108,12 +108,15 @@ def test_optimizer_options_validated_like_the_reference():
         bl.Lattice([p], direction="sign", state="disk")
     with pytest.raises(KeyError):
         bl.Lattice([p], "nonexistent")
-    for kw in (dict(), dict(direction="muon"), dict(direction="sign", momentum="bf16"),
-               dict(direction="sign", state="ram")):
+    for kw in (dict(direction="sign", momentum="nvfp4"), dict(direction="sign", state="ram")):
         with pytest.raises(NotImplementedError):
             bl.Lattice([p], **kw)
-    with pytest.raises(NotImplementedError):
-        bl.Lattice([p], "muon")
+    with pytest.raises(ValueError):
+        bl.Lattice([p], direction="muon", ns_dtype="fp64")
+    with pytest.raises(ValueError):
+        bl.Lattice([p], vector_direction="muon")
+    assert set(bl.optim.PRESETS) == {"muon", "muon_fast", "normuon", "normuon_fast", "muon_precise", "light", "balanced",
+                                     "precise", "stateless"}
     with pytest.raises(NotImplementedError):
         bl.Lattice([torch.nn.Parameter(torch.zeros(4, 16))], direction="sign")
     with pytest.raises(RuntimeError, match="CUDA device"):
@@ -155,3 +158,22 @@ def test_side_attributes_travel_with_views_and_copies():
         assert c._bl_row_offset == lo and not hasattr(c, "_bl_version")       # fresh storage: fresh version
         assert p.detach().to(torch.float16)._bl_row_offset == lo
     assert not hasattr(to_parameter(w), "_bl_row_offset")
+
+
+def test_newton_schulz_orthogonalises_and_matches_its_coefficients():
+    """The polar-factor iteration on CPU tensors (pure matrix products): singular values move toward 1, the Gram
+    variant agrees with the standard one, and tall inputs are handled through the transpose."""
+    from bitlattice_b200.optim.directions import newton_schulz, ns_coefficients
+    g = torch.randn(48, 96, generator=torch.Generator().manual_seed(0))
+    x = newton_schulz(g, steps=5)
+    sv = torch.linalg.svdvals(x)
+    assert 0.6 < sv.min() and sv.max() < 1.3
+    y = newton_schulz(g, steps=5, algo="gram")
+    assert torch.allclose(x, y, atol=2e-3)
+    t = newton_schulz(g.t().contiguous(), steps=5)
+    assert torch.allclose(t, x.t(), atol=1e-5)
+    assert ns_coefficients("muon", 3) == (3.4445, -4.7750, 2.0315)
+    a, b, c = ns_coefficients("polar_express", 9)
+    assert abs(a - 2.300652019954817 / 1.05) < 1e-12 and b < 0 < c
+    with pytest.raises(ValueError):
+        ns_coefficients("cubic", 0)
