@@ -605,10 +605,26 @@ __global__ void __launch_bounds__(kThreads, 2) update_kernel(const __grid_consta
       // ---- latent target and the sums of the scale fit
       f32x2 tau2[8];
       f32x2 sat2 = pk(0.0f, 0.0f), stt2 = pk(0.0f, 0.0f);
+      // table indices (code | phase << 4). With 4-bit containers the nibbles of a code word and of a phase word are
+      // interleaved into index bytes four at a time: even elements (c & 0x0F0F0F0F) | ((p << 4) & 0xF0F0F0F0), odd
+      // elements ((c >> 4) & 0x0F0F0F0F) | (p & 0xF0F0F0F0); an index is then one byte extraction.
+      [[maybe_unused]] uint32_t ev[2], od[2];
+      if constexpr (PCB == 4) {
+        ev[0] = (cw.x & 0x0F0F0F0Fu) | ((pw.x << 4) & 0xF0F0F0F0u);
+        od[0] = ((cw.x >> 4) & 0x0F0F0F0Fu) | (pw.x & 0xF0F0F0F0u);
+        ev[1] = (cw.y & 0x0F0F0F0Fu) | ((pw.y << 4) & 0xF0F0F0F0u);
+        od[1] = ((cw.y >> 4) & 0x0F0F0F0Fu) | (pw.y & 0xF0F0F0F0u);
+      }
 #pragma unroll
       for (int i = 0; i < 8; ++i) {
-        const uint32_t ia = ((cw.x >> (4 * i)) & 15u) | (phase_raw<PCB>(pw, i) << 4);
-        const uint32_t ib = ((cw.y >> (4 * i)) & 15u) | (phase_raw<PCB>(pw, i + 8) << 4);
+        uint32_t ia, ib;
+        if constexpr (PCB == 4) {
+          ia = __byte_perm((i & 1) ? od[0] : ev[0], 0u, 0x4440u | static_cast<uint32_t>(i >> 1));
+          ib = __byte_perm((i & 1) ? od[1] : ev[1], 0u, 0x4440u | static_cast<uint32_t>(i >> 1));
+        } else {
+          ia = ((cw.x >> (4 * i)) & 15u) | (phase_raw<PCB>(pw, i) << 4);
+          ib = ((cw.y >> (4 * i)) & 15u) | (phase_raw<PCB>(pw, i + 8) << 4);
+        }
         const float a0 = lutA[ia], a1 = lutA[ib], l0 = lutL[ia], l1 = lutL[ib];
         // Products that feed a sum are scalar (__fmul_rn is never contracted; a packed product followed by a packed
         // sum would be turned into one fused multiply-add, with one rounding instead of the reference's two).
