@@ -62,7 +62,8 @@ _SIGNATURES = {
     "bl_nvfp4_gemm_status": (_c.c_int, [_c.POINTER(_c.c_int), _c.c_int]),
     "bl_nvfp4_gemm_status_async": (_c.c_int, [_P, _c.c_int, _P]),
     "bl_selftest_bounded_wait": (_c.c_int, [_c.POINTER(_c.c_int), _c.POINTER(_c.c_int), _P, _c.c_int]),
-    "bl_selftest_mma_peak": (_c.c_int, [_c.c_int, _c.POINTER(_c.c_float), _c.POINTER(_c.c_double), _P, _c.c_int]),
+    "bl_selftest_mma_peak": (_c.c_int, [_c.c_int, _c.c_int, _c.POINTER(_c.c_float), _c.POINTER(_c.c_double), _P,
+                                        _c.c_int]),
     "bl_nvfp4_gemm_select": (_c.c_int, [_c.c_int]),
     "bl_swiglu_fwd": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64, _c.c_int, _c.c_void_p]),
     "bl_swiglu_bwd": (_c.c_int, [_c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_void_p, _c.c_int, _c.c_int64,

@@ -470,12 +470,13 @@ def selftest_bounded_wait(device: int = 0) -> tuple[int, int]:
     return st.value, ret.value
 
 
-def mma_peak_tflops(device: int = 0, iters: int = 4096) -> float:
+def mma_peak_tflops(device: int = 0, iters: int = 4096, mma_n: int = 256) -> float:
     """The tensor-pipe ceiling for block-scaled FP4 on this GPU: TFLOP/s of a kernel that only issues MMAs (no loads,
     no scale copies, no epilogue), a few hundred microseconds of work per call, timed with CUDA events."""
     ms, flops = ctypes.c_float(0.0), ctypes.c_double(0.0)
     scratch = torch.zeros(1, dtype=torch.int32, device=torch.device("cuda", device))
-    _C.call("bl_selftest_mma_peak", int(iters), ctypes.byref(ms), ctypes.byref(flops), scratch.data_ptr(), int(device))
+    _C.call("bl_selftest_mma_peak", int(iters), int(mma_n), ctypes.byref(ms), ctypes.byref(flops), scratch.data_ptr(),
+            int(device))
     return flops.value / (ms.value * 1e-3) / 1e12
 
 

@@ -1110,6 +1110,7 @@ __global__ void selftest_bounded_wait_kernel(int* returned) {
 // one resident pair of operand tiles filled with pseudo-random codes, with nothing else in the loop -- no loads, no
 // scale copies, no epilogue. The result is meaningless; the time is what the MMA pipe alone needs, under the power cap,
 // and serves as the measured peak the GEMM kernels are compared with.
+template <int BN>
 __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* status) {
   extern __shared__ uint8_t smem_raw[];
   __shared__ uint64_t bar_storage;
@@ -1141,7 +1142,7 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* status
   tcgen05_fence_after();
   const uint32_t tmem_base = tmem_slot_storage;
   if (warp == 0) {
-    constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(256 >> 3) << 17) | (8u << 24);
+    constexpr uint32_t idesc = (1u << 7) | (1u << 10) | (static_cast<uint32_t>(BN >> 3) << 17) | (8u << 24);
     constexpr uint32_t kSfaCol = 256, kSfbCol = 272;
     const uint64_t adesc = operand_desc(base), bdesc = operand_desc(base + kA);
     const uint64_t sdesc = scale_desc(base + kA + kB);
@@ -1157,9 +1158,17 @@ __global__ void __launch_bounds__(128, 1) mma_peak_kernel(int iters, int* status
     for (int it = 0; it < iters && ok; ++it) {
       q = elect_one();
 #pragma unroll
-      for (int j = 0; j < 4; ++j)
-        mma_nvf4_if<1>(q, tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
-                       tmem_base + kSfbCol + 8 * j, (it | j) != 0);
+      for (int j = 0; j < 4; ++j) {
+        if constexpr (BN == 256) {
+          mma_nvf4_if<1>(q, tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
+                         tmem_base + kSfbCol + 8 * j, (it | j) != 0);
+        } else {                                    // the same work as two MMAs of 128 columns (B rows 128 apart)
+          mma_nvf4_if<1>(q, tmem_base, adesc + 2u * j, bdesc + 2u * j, idesc, tmem_base + kSfaCol + 4 * j,
+                         tmem_base + kSfbCol + 8 * j, (it | j) != 0);
+          mma_nvf4_if<1>(q, tmem_base + 128, adesc + 2u * j, bdesc + 1024u + 2u * j, idesc,
+                         tmem_base + kSfaCol + 4 * j, tmem_base + kSfbCol + 8 * j + 4, (it | j) != 0);
+        }
+      }
       if ((it & 63) == 63 || it == iters - 1) {               // bound the work in flight; every wait has a limit
         mma_commit_if<1>(q, bar);
         ok = __all_sync(0xffffffffu, mbar_wait(bar, parity, abort_flag, 8));
@@ -1413,14 +1422,17 @@ extern "C" int bl_selftest_bounded_wait(int* status, int* returned, int* scratch
   return 0;
 }
 
-// Measures the tensor-pipe ceiling with mma_peak_kernel: `iters` k-tiles (4 MMAs of 128 x 256 x 64 each) per SM, timed
+// Measures the tensor-pipe ceiling with mma_peak_kernel: `iters` k-tiles (4 MMAs of 128 x 256 x 64 each, or with
+// mma_n = 128 the same work as 8 MMAs of 128 x 128 x 64) per SM, timed
 // with CUDA events after one warm-up launch. *ms receives the duration, *flops the work (2 * 128 * 256 * 256 * iters
 // * SMs). Synchronous; scratch: 4 bytes of device memory for the kernel's give-up code (returned as an error).
-extern "C" int bl_selftest_mma_peak(int iters, float* ms, double* flops, int* scratch, int device) {
+extern "C" int bl_selftest_mma_peak(int iters, int mma_n, float* ms, double* flops, int* scratch, int device) {
   BL_REQUIRE(iters > 0 && iters <= (1 << 20) && ms && flops && scratch, "selftest_mma_peak: bad argument");
+  BL_REQUIRE(mma_n == 256 || mma_n == 128, "selftest_mma_peak: the MMA width is 256 or 128 columns");
+  auto kernel = mma_n == 256 ? mma_peak_kernel<256> : mma_peak_kernel<128>;
   BL_DEVICE(device);
   constexpr int kSmem = 128 * 128 + 256 * 128 + 3 * 2048 + 1024;
-  BL_CUDA(cudaFuncSetAttribute(mma_peak_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
+  BL_CUDA(cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmem));
   const int sms = sm_count(device);
   cudaEvent_t a, b;
   BL_CUDA(cudaEventCreate(&a));
@@ -1428,9 +1440,9 @@ extern "C" int bl_selftest_mma_peak(int iters, float* ms, double* flops, int* sc
   int zero = 0, code = 0;
   cudaError_t rc = cudaMemcpy(scratch, &zero, sizeof(int), cudaMemcpyHostToDevice);
   if (rc == cudaSuccess) {
-    mma_peak_kernel<<<sms, 128, kSmem>>>(64, scratch);
+    kernel<<<sms, 128, kSmem>>>(64, scratch);
     cudaEventRecord(a);
-    mma_peak_kernel<<<sms, 128, kSmem>>>(iters, scratch);
+    kernel<<<sms, 128, kSmem>>>(iters, scratch);
     cudaEventRecord(b);
     rc = cudaEventSynchronize(b);
   }

@@ -234,10 +234,11 @@ BL_API int bl_selftest_bounded_wait(int* status, int* returned, int* scratch, in
 
 /* Diagnostic, no counterpart in the reference: the tensor-pipe ceiling for block-scaled FP4. Every SM issues `iters`
  * k-tiles of four 128 x 256 x 64 MMAs on one resident pair of operand tiles, with no loads, scale copies or epilogue in
- * the loop; *ms receives the CUDA-event duration (after a warm-up launch), *flops the work done. The GEMM kernels'
+ * the loop (mma_n = 128: the same work issued as MMAs of 128 columns); *ms receives the CUDA-event duration (after a
+ * warm-up launch), *flops the work done. The GEMM kernels'
  * roofline fraction is quoted against flops / ms measured this way on the same GPU. Synchronous; scratch: 4 bytes of
  * device memory. */
-BL_API int bl_selftest_mma_peak(int iters, float* ms, double* flops, int* scratch, int device);
+BL_API int bl_selftest_mma_peak(int iters, int mma_n, float* ms, double* flops, int* scratch, int device);
 
 /* SwiGLU glue between the gate/up and the down projection, every intermediate rounded to the activation type as
  * PyTorch autograd rounds F.silu(g) * u. Replaces torch.ops.bitlattice.swiglu_fwd / swiglu_bwd
