@@ -392,9 +392,10 @@ def assemble_gathered(recv: torch.Tensor, n: int, K: int, offsets):
 # ------------------------------------------------------------------------------------------------ GEMM
 
 def nvfp4_gemm(a_packed, a_sf, a_global, b_packed, b_sf, b_global, out_dtype=torch.bfloat16,
-               out: torch.Tensor | None = None) -> torch.Tensor:
+               out: torch.Tensor | None = None, accumulate: bool = False) -> torch.Tensor:
     """(A B^T) * ga * gb for NVFP4 A [M, K], B [N, K] with blocked scales; fp32 accumulation on FP4 tensor cores
-    (reference: bitlattice/backend.py:280-290)."""
+    (reference: bitlattice/backend.py:280-290). ``accumulate``: add the product to ``out`` (the bits of
+    ``out + product`` as an add of two tensors of out's type)."""
     _require(a_packed, "a_packed", torch.uint8)
     _require(b_packed, "b_packed", torch.uint8)
     _require(a_sf, "a_sf")
@@ -408,8 +409,12 @@ def nvfp4_gemm(a_packed, a_sf, a_global, b_packed, b_sf, b_global, out_dtype=tor
     ga = _require(a_global, "a_global", torch.float32)
     gb = _require(b_global, "b_global", torch.float32)
     if out is None:
+        if accumulate:
+            raise RuntimeError("accumulate needs the tensor to add to (out=)")
         out = torch.empty(M, N, dtype=out_dtype, device=a_packed.device)
-    _C.call("bl_nvfp4_gemm", _C.ptr(a_packed), _C.ptr(a_sf), _C.ptr(ga), _C.ptr(b_packed), _C.ptr(b_sf), _C.ptr(gb),
+    elif out.shape != (M, N) or not out.is_cuda or out.stride(1) != 1:
+        raise RuntimeError(f"out must be a CUDA tensor [{M}, {N}] with unit column stride")
+    _C.call("bl_nvfp4_gemm_accumulate" if accumulate else "bl_nvfp4_gemm", _C.ptr(a_packed), _C.ptr(a_sf), _C.ptr(ga), _C.ptr(b_packed), _C.ptr(b_sf), _C.ptr(gb),
             M, N, K, _C.ptr(out), _C.DTYPE[out.dtype], out.stride(0), _C.device_of(a_packed), _C.stream_of(a_packed))
     return out
 

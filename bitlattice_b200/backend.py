@@ -158,14 +158,18 @@ def _act_operand(x2: torch.Tensor, recipe: Fp4Recipe) -> Fp4Operand:
     return Fp4Operand(packed, scales, g, True)
 
 
-def fp4_mm(a: Fp4Operand, b: Fp4Operand, out_dtype: torch.dtype = torch.bfloat16) -> torch.Tensor:
+def fp4_mm(a: Fp4Operand, b: Fp4Operand, out_dtype: torch.dtype = torch.bfloat16,
+           add_to: torch.Tensor | None = None) -> torch.Tensor:
     """A B^T for NVFP4 operands A [M, K], B [N, K] (K: multiple of 32), fp32 accumulation in tensor memory,
-    ``out_dtype`` output, both per-tensor scales applied in the epilogue (reference: backend.py:280-290)."""
+    ``out_dtype`` output, both per-tensor scales applied in the epilogue (reference: backend.py:280-290).
+    ``add_to`` [M, N]: the product is added to it in the GEMM's epilogue (same bits as ``add_to + product``) and it is
+    returned: how the input gradients of projections sharing an input are summed without a pass of their own."""
     sa = a.scales if a.blocked else to_blocked(a.scales)
     sb = b.scales if b.blocked else to_blocked(b.scales)
     ga, gb = a.global_scale, b.global_scale
     return _ops.nvfp4_gemm(a.packed, sa, ga if ga.dtype == torch.float32 else ga.float(), b.packed, sb,
-                           gb if gb.dtype == torch.float32 else gb.float(), out_dtype)
+                           gb if gb.dtype == torch.float32 else gb.float(), out_dtype, out=add_to,
+                           accumulate=add_to is not None)
 
 
 # per-weight operands, kept while the weight is unchanged (the role of the reference's backend.py:293-342)
@@ -316,12 +320,16 @@ def fp4_forward_saving(x: torch.Tensor, w, bias, recipe: Fp4Recipe = Fp4Recipe()
     return y.reshape(*x.shape[:-1], w.shape[0]), xt
 
 
-def fp4_dgrad(gy: torch.Tensor, w, recipe: Fp4Recipe = Fp4Recipe()):
-    """gx = Q_sr(gy) Q(W^T)^T; also returns the padded 2-D gradient and its operand for fp4_wgrad."""
+def fp4_dgrad(gy: torch.Tensor, w, recipe: Fp4Recipe = Fp4Recipe(), add_to: torch.Tensor | None = None):
+    """gx = Q_sr(gy) Q(W^T)^T; also returns the padded 2-D gradient and its operand for fp4_wgrad. ``add_to``: the
+    padded [Mp, K] buffer of an earlier projection's input gradient, to which this one is added in the epilogue (the
+    padded buffer is then what is returned)."""
     N = gy.shape[-1]
     g2 = gy.reshape(-1, N)
     g2p = _pad_rows(g2, 32).contiguous()
     gq = quantize_fp4(g2p, stochastic=True)
+    if add_to is not None:
+        return fp4_mm(gq, weight_t_operand(w), gy.dtype, add_to=add_to), g2p, gq
     return fp4_mm(gq, weight_t_operand(w), gy.dtype)[:g2.shape[0]], g2p, gq
 
 

@@ -433,6 +433,7 @@ struct GemmArgs {
   int64_t M, N, K, ldc;
   int out_dtype;
   int num_m, num_n;
+  int accumulate;          // 1: out += result, the sum rounded as a dense add of two tensors of the output type
 };
 
 // 32 bytes in one store instruction (a whole sector per lane); dst must be 32-byte aligned
@@ -442,9 +443,17 @@ __device__ __forceinline__ void store32B(void* dst, const uint32_t w[8]) {
                : "memory");
 }
 
-template <typename O>
-__device__ __forceinline__ void store_row32(O* dst, const uint32_t acc[32], float alpha, int ncols_valid) {
-  // 32 consecutive outputs of one row; ncols_valid is a multiple of 8
+__device__ __forceinline__ void load32B(const void* src, uint32_t w[8]) {
+  asm volatile("ld.global.v8.b32 {%0, %1, %2, %3, %4, %5, %6, %7}, [%8];"
+               : "=r"(w[0]), "=r"(w[1]), "=r"(w[2]), "=r"(w[3]), "=r"(w[4]), "=r"(w[5]), "=r"(w[6]), "=r"(w[7])
+               : "l"(src)
+               : "memory");
+}
+
+// 32 consecutive outputs of one row; ncols_valid is a multiple of 8. ACC: the result is added to what dst holds, as
+// torch adds two tensors of type O: the product is rounded to O first, then the fp32 sum of the two is rounded to O.
+template <typename O, bool ACC>
+__device__ __forceinline__ void store_row32_impl(O* dst, const uint32_t acc[32], float alpha, int ncols_valid) {
   if constexpr (sizeof(O) == 2) {
     // full width and a 32-byte aligned row: two 32-byte stores instead of four 16-byte ones. Every lane writes its
     // own row, so a warp's store instruction touches 32 different sectors either way; filling each sector with one
@@ -455,6 +464,12 @@ __device__ __forceinline__ void store_row32(O* dst, const uint32_t acc[32], floa
         O o[16];
 #pragma unroll
         for (int j = 0; j < 16; ++j) o[j] = from_f<O>(__uint_as_float(acc[c + j]) * alpha);
+        if constexpr (ACC) {
+          O old[16];
+          load32B(dst + c, reinterpret_cast<uint32_t*>(old));
+#pragma unroll
+          for (int j = 0; j < 16; ++j) o[j] = from_f<O>(to_f<O>(old[j]) + to_f<O>(o[j]));
+        }
         store32B(dst + c, reinterpret_cast<const uint32_t*>(o));
       }
       return;
@@ -468,15 +483,33 @@ __device__ __forceinline__ void store_row32(O* dst, const uint32_t acc[32], floa
                               __uint_as_float(acc[c + 2]) * alpha, __uint_as_float(acc[c + 3]) * alpha);
       float4 v1 = make_float4(__uint_as_float(acc[c + 4]) * alpha, __uint_as_float(acc[c + 5]) * alpha,
                               __uint_as_float(acc[c + 6]) * alpha, __uint_as_float(acc[c + 7]) * alpha);
+      if constexpr (ACC) {      // (explicitly rounded adds: this file is compiled with fused multiply-adds allowed)
+        const float4 p0 = reinterpret_cast<const float4*>(dst + c)[0], p1 = reinterpret_cast<const float4*>(dst + c)[1];
+        v0 = make_float4(__fadd_rn(p0.x, v0.x), __fadd_rn(p0.y, v0.y), __fadd_rn(p0.z, v0.z), __fadd_rn(p0.w, v0.w));
+        v1 = make_float4(__fadd_rn(p1.x, v1.x), __fadd_rn(p1.y, v1.y), __fadd_rn(p1.z, v1.z), __fadd_rn(p1.w, v1.w));
+      }
       reinterpret_cast<float4*>(dst + c)[0] = v0;
       reinterpret_cast<float4*>(dst + c)[1] = v1;
     } else {
       O o[8];
 #pragma unroll
       for (int j = 0; j < 8; ++j) o[j] = from_f<O>(__uint_as_float(acc[c + j]) * alpha);
+      if constexpr (ACC) {
+        const uint4 raw = *reinterpret_cast<const uint4*>(dst + c);
+        const O* old = reinterpret_cast<const O*>(&raw);
+#pragma unroll
+        for (int j = 0; j < 8; ++j) o[j] = from_f<O>(to_f<O>(old[j]) + to_f<O>(o[j]));
+      }
       *reinterpret_cast<uint4*>(dst + c) = *reinterpret_cast<const uint4*>(o);
     }
   }
+}
+
+template <typename O>
+__device__ __forceinline__ void store_row32(O* dst, const uint32_t acc[32], float alpha, int ncols_valid,
+                                            int accumulate = 0) {
+  if (accumulate) store_row32_impl<O, true>(dst, acc, alpha, ncols_valid);
+  else store_row32_impl<O, false>(dst, acc, alpha, ncols_valid);
 }
 
 template <int BN, int STAGES>
@@ -603,11 +636,11 @@ __global__ void __launch_bounds__(kGemmThreads) gemm_kernel(const __grid_constan
           const int64_t left = args.N - col;
           const int valid = left < 32 ? static_cast<int>(left) : 32;
           if (args.out_dtype == BL_BF16)
-            store_row32(static_cast<__nv_bfloat16*>(args.out) + row * args.ldc + col, acc, alpha, valid);
+            store_row32(static_cast<__nv_bfloat16*>(args.out) + row * args.ldc + col, acc, alpha, valid, args.accumulate);
           else if (args.out_dtype == BL_F16)
-            store_row32(static_cast<__half*>(args.out) + row * args.ldc + col, acc, alpha, valid);
+            store_row32(static_cast<__half*>(args.out) + row * args.ldc + col, acc, alpha, valid, args.accumulate);
           else
-            store_row32(static_cast<float*>(args.out) + row * args.ldc + col, acc, alpha, valid);
+            store_row32(static_cast<float*>(args.out) + row * args.ldc + col, acc, alpha, valid, args.accumulate);
         }
       }
     }
@@ -796,11 +829,11 @@ __global__ void __launch_bounds__(kPersistThreads, 1) gemm_persistent_kernel(con
           const int64_t left = args.N - col;
           const int valid = left < 32 ? static_cast<int>(left) : 32;
           if (args.out_dtype == BL_BF16)
-            store_row32(static_cast<__nv_bfloat16*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
+            store_row32(static_cast<__nv_bfloat16*>(args.out) + row * args.ldc + col, acc[i], alpha, valid, args.accumulate);
           else if (args.out_dtype == BL_F16)
-            store_row32(static_cast<__half*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
+            store_row32(static_cast<__half*>(args.out) + row * args.ldc + col, acc[i], alpha, valid, args.accumulate);
           else
-            store_row32(static_cast<float*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
+            store_row32(static_cast<float*>(args.out) + row * args.ldc + col, acc[i], alpha, valid, args.accumulate);
         }
       }
     }
@@ -1090,11 +1123,11 @@ __global__ void __launch_bounds__(kPairThreads, 1) gemm_pair_kernel(const __grid
           const int64_t left = args.N - col;
           const int valid = left < 32 ? static_cast<int>(left) : 32;
           if (args.out_dtype == BL_BF16)
-            store_row32(static_cast<__nv_bfloat16*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
+            store_row32(static_cast<__nv_bfloat16*>(args.out) + row * args.ldc + col, acc[i], alpha, valid, args.accumulate);
           else if (args.out_dtype == BL_F16)
-            store_row32(static_cast<__half*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
+            store_row32(static_cast<__half*>(args.out) + row * args.ldc + col, acc[i], alpha, valid, args.accumulate);
           else
-            store_row32(static_cast<float*>(args.out) + row * args.ldc + col, acc[i], alpha, valid);
+            store_row32(static_cast<float*>(args.out) + row * args.ldc + col, acc[i], alpha, valid, args.accumulate);
         }
       }
       if (NACC == 2) ab ^= 1;
@@ -1353,9 +1386,9 @@ static std::atomic<int> g_kernel_choice{[] {
   return v >= BL_GEMM_AUTO && v <= BL_GEMM_PAIR ? v : 0;
 }()};
 
-extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const float* a_global, const uint8_t* b_codes,
-                             const uint8_t* b_sf, const float* b_global, int64_t M, int64_t N, int64_t K, void* out,
-                             int out_dtype, int64_t ldc, int device, bl_stream_t stream) {
+static int gemm_entry(const uint8_t* a_codes, const uint8_t* a_sf, const float* a_global, const uint8_t* b_codes,
+                      const uint8_t* b_sf, const float* b_global, int64_t M, int64_t N, int64_t K, void* out,
+                      int out_dtype, int64_t ldc, int accumulate, int device, bl_stream_t stream) {
   BL_REQUIRE(a_codes && a_sf && a_global && b_codes && b_sf && b_global && out, "gemm: null buffer");
   BL_REQUIRE(M > 0 && N > 0 && K > 0, "gemm: empty problem %lld x %lld x %lld", (long long)M, (long long)N, (long long)K);
   BL_REQUIRE(K % 32 == 0, "gemm: K = %lld is not a multiple of 32", (long long)K);
@@ -1378,6 +1411,7 @@ extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const 
   args.ldc = ldc;
   args.out_dtype = out_dtype;
   args.num_m = args.num_n = 0;
+  args.accumulate = accumulate ? 1 : 0;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   int kernel = g_kernel_choice.load(std::memory_order_relaxed);
   if (kernel == BL_GEMM_AUTO) {
@@ -1394,6 +1428,21 @@ extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const 
   if (kernel == BL_GEMM_PAIR) return launch_pair<256, 5>(a_codes, b_codes, args, device, st);
   if (kernel == BL_GEMM_PERSISTENT) return launch_persistent<4, 0>(a_codes, b_codes, args, device, st);
   return launch_gemm<128, 3>(a_codes, b_codes, args, st);
+}
+
+extern "C" int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const float* a_global, const uint8_t* b_codes,
+                             const uint8_t* b_sf, const float* b_global, int64_t M, int64_t N, int64_t K, void* out,
+                             int out_dtype, int64_t ldc, int device, bl_stream_t stream) {
+  return gemm_entry(a_codes, a_sf, a_global, b_codes, b_sf, b_global, M, N, K, out, out_dtype, ldc, 0, device, stream);
+}
+
+// out += (A B^T) * ga * gb: the sum of the input gradients of projections that read one input (q / k / v, gate / up)
+// without a separate pass over the gradient. Bits of `out + product` as a dense add of two tensors of the output type.
+extern "C" int bl_nvfp4_gemm_accumulate(const uint8_t* a_codes, const uint8_t* a_sf, const float* a_global,
+                                        const uint8_t* b_codes, const uint8_t* b_sf, const float* b_global, int64_t M,
+                                        int64_t N, int64_t K, void* out, int out_dtype, int64_t ldc, int device,
+                                        bl_stream_t stream) {
+  return gemm_entry(a_codes, a_sf, a_global, b_codes, b_sf, b_global, M, N, K, out, out_dtype, ldc, 1, device, stream);
 }
 
 // Forces one of the GEMM kernels (BL_GEMM_TILE, BL_GEMM_PERSISTENT, BL_GEMM_PAIR) for every later bl_nvfp4_gemm call

@@ -215,8 +215,14 @@ class ColumnParallelFp4Linear(torch.autograd.Function):
                 staged.append(None)
                 continue
             if need_x:
-                gx, g2p, gq = backend.fp4_dgrad(gy, w, ctx.recipe)
-                gx_sum = gx if gx_sum is None else gx_sum.add_(gx)
+                # the partial input gradients of the projections are summed in the GEMM's epilogue (same bits as adding
+                # the tensors) whenever the rows need no padding; otherwise by a dense add
+                rows = gy.numel() // gy.shape[-1]
+                if gx_sum is not None and rows % 32 == 0 and gx_sum.shape[0] == rows and gx_sum.is_contiguous():
+                    _, g2p, gq = backend.fp4_dgrad(gy, w, ctx.recipe, add_to=gx_sum)
+                else:
+                    gx, g2p, gq = backend.fp4_dgrad(gy, w, ctx.recipe)
+                    gx_sum = gx if gx_sum is None else gx_sum.add_(gx)
             else:
                 g2p, gq = backend._pad_rows(gy.reshape(-1, gy.shape[-1]), 32).contiguous(), None
             staged.append((g2p, gq))
@@ -465,8 +471,12 @@ class TokenParallelFp4Linear(torch.autograd.Function):
             for w, st in zip(ctx.weights, staged):
                 if st is None:
                     continue
-                gi = backend.fp4_mm(st[0], ctx.gathered.t_operand(w), dtype)[:st[1]]
-                gx = gi if gx is None else gx.add_(gi)
+                wt = ctx.gathered.t_operand(w)
+                if gx is not None and st[1] % 32 == 0 and gx.shape[0] == st[1] and gx.is_contiguous():
+                    backend.fp4_mm(st[0], wt, dtype, add_to=gx)        # summed in the epilogue: no pass of its own
+                else:
+                    gi = backend.fp4_mm(st[0], wt, dtype)[:st[1]]
+                    gx = gi if gx is None else gx.add_(gi)
             if gx is not None:
                 gx = gx.reshape(shape)
         if work is not None:

@@ -213,6 +213,15 @@ BL_API int bl_nvfp4_gemm(const uint8_t* a_codes, const uint8_t* a_sf, const floa
                   const uint8_t* b_sf, const float* b_global, int64_t M, int64_t N, int64_t K, void* out,
                   int out_dtype, int64_t ldc, int device, bl_stream_t stream);
 
+/* out += (A B^T) * (*a_global * *b_global), same operands and rules as bl_nvfp4_gemm. Replaces the dense add autograd
+ * performs when several projections read one input (the reference sums their input gradients as separate tensors,
+ * bitlattice/tensor.py:269 + autograd): the product is rounded to out_dtype, then the fp32 sum of the old value and the
+ * product is rounded to out_dtype -- the bits of `out + product` computed as two tensors. */
+BL_API int bl_nvfp4_gemm_accumulate(const uint8_t* a_codes, const uint8_t* a_sf, const float* a_global,
+                                    const uint8_t* b_codes, const uint8_t* b_sf, const float* b_global, int64_t M,
+                                    int64_t N, int64_t K, void* out, int out_dtype, int64_t ldc, int device,
+                                    bl_stream_t stream);
+
 /* Every wait inside the GEMM kernel is bounded; when one expires the kernel records which (1 producer, 2 MMA issuer,
  * 3 epilogue), frees its tensor memory and returns. This call synchronizes `device`, stores the recorded code
  * (0: none) in *status and clears it. No counterpart in the reference (cuBLASLt reports nothing of the kind). */

@@ -562,6 +562,26 @@ def test_gemm_is_linear_in_row_blocks_at_scale(gemm_kernel):
     assert torch.isfinite(full.float()).all() and full.float().abs().max() > 0
 
 
+@ALL_GEMM_KERNELS
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16, torch.float32])
+def test_gemm_accumulate_equals_adding_the_tensors(gemm_kernel, dtype):
+    """out += product in the epilogue gives the bits of torch's `out + product` (the product rounded to the output type
+    first), on full tiles and on ragged edges (N not a multiple of 32, rows not a multiple of 128)."""
+    for M, N, K in ((256, 512, 256), (300, 520, 320)):
+        g0 = torch.Generator(device=DEV).manual_seed(5)
+        a = torch.randint(0, 256, (M, K // 2), device=DEV, dtype=torch.uint8, generator=g0)
+        b = torch.randint(0, 256, (N, K // 2), device=DEV, dtype=torch.uint8, generator=g0)
+        asf = _ops.to_blocked(torch.randint(40, 72, (M, K // 16), device=DEV, dtype=torch.uint8, generator=g0))
+        bsf = _ops.to_blocked(torch.randint(40, 72, (N, K // 16), device=DEV, dtype=torch.uint8, generator=g0))
+        one = torch.full((1,), 1e-3, device=DEV)
+        base = (torch.randn(M, N, device=DEV, generator=g0) * 50).to(dtype)
+        prod = _ops.nvfp4_gemm(a, asf, one, b, bsf, one, out_dtype=dtype)
+        out = base.clone()
+        _ops.nvfp4_gemm(a, asf, one, b, bsf, one, out=out, accumulate=True)
+        assert torch.equal(out, base + prod)
+    assert _ops.gemm_status(0) == 0
+
+
 def test_gemm_rejects_bad_shapes():
     one = torch.ones(1, device=DEV)
     a = torch.zeros(16, 24, device=DEV, dtype=torch.uint8)      # K = 48
