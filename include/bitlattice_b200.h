@@ -243,7 +243,8 @@ BL_API int bl_selftest_bounded_wait(int* status, int* returned, int* scratch, in
 
 /* Diagnostic, no counterpart in the reference: the tensor-pipe ceiling for block-scaled FP4. Every SM issues `iters`
  * k-tiles of four 128 x 256 x 64 MMAs on one resident pair of operand tiles, with no loads, scale copies or epilogue in
- * the loop (mma_n = 128: the same work issued as MMAs of 128 columns); *ms receives the CUDA-event duration (after a
+ * the loop (mma_n = 128: the same work issued as MMAs of 128 columns; mma_n = 1256: 256 columns with the twelve scale
+ * copies of a k-tile issued in order before its MMAs); *ms receives the CUDA-event duration (after a
  * warm-up launch), *flops the work done. The GEMM kernels'
  * roofline fraction is quoted against flops / ms measured this way on the same GPU. Synchronous; scratch: 4 bytes of
  * device memory. */

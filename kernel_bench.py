@@ -151,6 +151,9 @@ def mma_peak():
         vals = [_ops.mma_peak_tflops(0, iters, n) for iters in (1024, 4096, 16384, 16384, 16384)]
         print(f"mma-only block-scaled FP4 (128 x {n} x 64 MMAs on resident tiles), TFLOP/s per call: " +
               ", ".join(f"{v:.0f}" for v in vals), flush=True)
+    vals = [_ops.mma_peak_tflops(0, iters, 1256) for iters in (1024, 4096, 16384, 16384, 16384)]
+    print("the same with the 12 scale copies of every k-tile issued in order before its MMAs, TFLOP/s per call: " +
+          ", ".join(f"{v:.0f}" for v in vals), flush=True)
 
 
 def quant():
