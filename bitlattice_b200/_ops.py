@@ -314,6 +314,67 @@ def quantize_nvfp4_4over6(x: torch.Tensor, global_scale: torch.Tensor, select: s
     return packed, scales if blocked else scales.view(torch.float8_e4m3fn)
 
 
+Q_MODES = {"rtn": 0, "sr": 1, "eden": 2}
+
+
+def nvfp4_quantize_general(x: torch.Tensor, *, transpose: bool = False, mode: str = "rtn", four_over_six: bool = False,
+                           select: str = "mse", rotate: bool = False, seed: int = 0, rotate_seed: int = -1,
+                           given: torch.Tensor | None = None, pow2: bool = False, w_scales: torch.Tensor | None = None,
+                           w_global: torch.Tensor | None = None, blocked: bool = False):
+    """The general quantizer of the 128-rotation recipes (reference: torch.ops.bitlattice.nvfp4_quantize; Python twin
+    bitlattice/fp4ref.py:103-150): x [R, C] dense, or the packed codes of an NVFP4 matrix with ``w_scales`` /
+    ``w_global`` (transposed only) -> (packed, scales, global [1]) of x or x^T; ``mode`` 'rtn' | 'sr' | 'eden';
+    ``rotate``: randomized 128-point Hadamard rotation along the quantized dimension with ``rotate_seed`` (< 0:
+    ``seed``); ``given``: the per-tensor scale to use; ``pow2``: the computed per-tensor scale rounded up to a power
+    of two."""
+    _require(x, "x")
+    if x.dim() != 2:
+        raise RuntimeError("x must be a contiguous 2-D CUDA tensor")
+    if mode not in Q_MODES:
+        raise ValueError("mode must be 'rtn', 'sr' or 'eden'")
+    if select not in ("mse", "mae"):
+        raise ValueError("select must be 'mse' or 'mae'")
+    packed_in = w_scales is not None
+    if packed_in:
+        _require(w_scales, "w_scales")
+        _require(w_global, "w_global", torch.float32)
+        R, C = x.shape[0], x.shape[1] * 2
+        dtype = 0
+    else:
+        if x.dtype not in _C.DTYPE:
+            raise RuntimeError("x must be bf16, fp16 or fp32")
+        R, C = x.shape
+        dtype = _C.DTYPE[x.dtype]
+    if given is not None:
+        _require(given, "given", torch.float32)
+    rows, cols = (C, R) if transpose else (R, C)
+    packed = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
+    scales = _scale_buffer(rows, cols // 16, blocked, x.device)
+    out = torch.empty(2, dtype=torch.float32, device=x.device)           # [0]: the per-tensor scale, [1]: amax scratch
+    _C.call("bl_nvfp4_quantize_general", _C.ptr(x), dtype, R, C, int(transpose), Q_MODES[mode], int(four_over_six),
+            1 if select == "mae" else 0, int(rotate), int(seed), int(rotate_seed),
+            _C.ptr(given) if given is not None else None, int(pow2),
+            _C.ptr(_bytes(w_scales)) if packed_in else None, _C.ptr(w_global) if packed_in else None, _C.ptr(packed),
+            _C.ptr(scales), int(blocked), _C.ptr(out), _C.ptr(out[1:]), _C.device_of(x), _C.stream_of(x))
+    return packed, scales if blocked else scales.view(torch.float8_e4m3fn), out[:1]
+
+
+def fp4_fold_scales(scales: torch.Tensor, row_tiles: int, piece: torch.Tensor, g: torch.Tensor, rounded: torch.Tensor
+                    ) -> torch.Tensor:
+    """In place: the blocked scale bytes ``scales`` (row_tiles x len(piece) tiles of 512 bytes) of operands
+    concatenated along K are brought to the common per-tensor scale max(g); ``piece`` int32: the piece of every column
+    tile, ``g`` fp32: the pieces' power-of-two scales, ``rounded`` int64 [1]: counter of inexact products. Returns
+    max(g) [1] (reference: torch.ops.bitlattice.fp4_fold_scales)."""
+    _require(scales, "scales", torch.uint8)
+    _require(piece, "piece", torch.int32)
+    _require(g, "g", torch.float32)
+    _require(rounded, "rounded", torch.int64)
+    g_max = torch.empty(1, dtype=torch.float32, device=scales.device)
+    _C.call("bl_fp4_fold_scales", _C.ptr(scales), int(row_tiles), piece.numel(), _C.ptr(piece), _C.ptr(g), g.numel(),
+            _C.ptr(g_max), _C.ptr(rounded), _C.device_of(scales), _C.stream_of(scales))
+    return g_max
+
+
 def quantize_nvfp4_t(x: torch.Tensor, hadamard: torch.Tensor | None, seed: int = -1, step: int = 0,
                      global_scale: torch.Tensor | None = None, blocked: bool = False):
     """x [M, K] -> NVFP4 of x^T (rotated by ``hadamard`` along M): (packed [K, M/2], scales, global [1])

@@ -23,6 +23,7 @@ SOURCES = {
     "abi.cu": [],
     "update.cu": ["--fmad=false"],
     "quant.cu": ["--fmad=false"],
+    "quant_general.cu": ["--fmad=false"],
     "gemm.cu": [],
     "swiglu.cu": ["--fmad=false"],
     "gather.cu": [],

@@ -51,6 +51,7 @@ enum { BL_DIR_RAW = 0, BL_DIR_SIGN = 1, BL_DIR_COLNORM = 2 };
 enum { BL_SF_ROWMAJOR = 0, BL_SF_BLOCKED = 1 };
 /* four-over-six selection criterion: squared or absolute error of the dequantized block */
 enum { BL_SELECT_MSE = 0, BL_SELECT_MAE = 1 };
+enum { BL_Q_RTN = 0, BL_Q_SR = 1, BL_Q_EDEN = 2 };    /* modes of bl_nvfp4_quantize_general */
 
 BL_API int bl_version(void);
 BL_API const char* bl_last_error(void);
@@ -167,6 +168,39 @@ BL_API int bl_nvfp4_quantize(const void* x, int dtype, int64_t rows, int64_t col
 BL_API int bl_nvfp4_quantize_4over6(const void* x, int dtype, int64_t rows, int64_t cols, const float* global_scale,
                              int select, uint8_t* codes, uint8_t* scales, int sf_layout, int device,
                              bl_stream_t stream);
+
+/* Replaces torch.ops.bitlattice.nvfp4_quantize (csrc/bindings.cpp schema "nvfp4_quantize", csrc/nvfp4.cu:553-600; Python
+ * twin bitlattice/fp4ref.py:103-150): the quantizer of the 128-rotation recipes. x: dense [R, C] of `dtype`, or -- with
+ * w_scales / w_global given -- the packed codes [R, C/2] of an NVFP4 matrix with its row-major scale bytes and
+ * per-tensor scale (then transpose must be set; values are formed as (level * scale) * global). Output: codes and
+ * scales of x (transpose = 0) or of x^T [C, R] (transpose = 1), blocks of 16 along the output's last dimension.
+ *   mode           BL_Q_RTN: round to nearest, ties to the even code, v * (1 / (scale*global));
+ *                  BL_Q_SR: stochastic rounding, u = hash(flat output index, seed, 0);
+ *                  BL_Q_EDEN: round-to-nearest codes; per 128 elements S = <x,x> / <x,x_rtn>, every block scale times
+ *                  S rounded stochastically to E4M3, u = hash(flat block index, seed ^ 0x9E3779B9, 0); needs rotate
+ *   four_over_six  every block keeps the better (select: BL_SELECT_MSE / BL_SELECT_MAE) of "maximum mapped to 6" and
+ *                  "maximum mapped to 4"; the per-tensor scale then uses 256 instead of 448
+ *   rotate         x <- (x * signs) H_128 / sqrt(128) over consecutive 128-element blocks of the output's last
+ *                  dimension (a multiple of 128), signs = hash(j, rotate_seed, 0x5151) < 0.5 ? -1 : 1 (rotate_seed < 0:
+ *                  seed)
+ *   given_global   device pointer to the per-tensor scale to use, or NULL: max|rotated x| / (6 * 448 or 256), at
+ *                  least 1e-12, rounded up to a power of two when pow2 is set
+ * Summation orders (the reference fixes none; its test allows 2e-3 of codes and scales to differ): butterflies with
+ * strides 1 .. 64 then the normalisation; error and MS-EDEN sums over groups of four elements, then pairwise.
+ * out_global: 1 float (written); scratch: 1 float of device memory (the amax). sf_layout as bl_nvfp4_quantize. */
+BL_API int bl_nvfp4_quantize_general(const void* x, int dtype, int64_t R, int64_t C, int transpose, int mode,
+                              int four_over_six, int select, int rotate, int64_t seed, int64_t rotate_seed,
+                              const float* given_global, int pow2, const uint8_t* w_scales, const float* w_global,
+                              uint8_t* codes, uint8_t* scales, int sf_layout, float* out_global, float* scratch,
+                              int device, bl_stream_t stream);
+
+/* Replaces torch.ops.bitlattice.fp4_fold_scales (csrc/fold.cu:12-33; Python twin bitlattice/backend.py:688-697): the
+ * blocked scale buffer of operands concatenated along K -- row_tiles x tiles_per_row tiles of 512 bytes, column tile t
+ * belonging to piece piece[t] (device int32 [tiles_per_row]) whose per-tensor scale is the power of two g[piece] -- is
+ * brought to the common scale max(g): every byte times g[piece] / max(g), rounded to E4M3. *g_max receives max(g);
+ * *rounded (device, 64-bit) is incremented by the number of non-zero products below 2^-6 (rounded, not exact). */
+BL_API int bl_fp4_fold_scales(uint8_t* scales, int64_t row_tiles, int64_t tiles_per_row, const int* piece, const float* g,
+                       int pieces, float* g_max, unsigned long long* rounded, int device, bl_stream_t stream);
 
 /* Replaces torch.ops.bitlattice.quantize_nvfp4_t (csrc/bindings.cpp:97-98, csrc/act_quant.cu:100-148,230-270):
  * x [M, K] -> NVFP4 of x^T, codes [K, M/2] + scales over [K, M/16], blocks of 16 along M, each block optionally

@@ -111,6 +111,38 @@ def fos_cases():
     return out
 
 
+def general_cases():
+    """The general quantizer (fp4ref.quantize): rows and transposed, round to nearest / stochastic / MS-EDEN, with and
+    without four-over-six, with and without the 128-point rotation (MS-EDEN always rotated), on the input
+    distribution of the reference's own kernel test (tests/test_nvfp4.py:22-27: per-row log-normal magnitudes, one
+    outlier column, bf16). Stored: packed codes of the returned levels, scale bytes, global scale. Also the rotation
+    itself and the E4M3 stochastic rounding on a value grid."""
+    out = {}
+    g = gen(0)
+    x = torch.randn(128, 256, generator=g) * torch.exp(torch.randn(128, 1, generator=g))
+    x[:, 3] *= 25
+    x = x.to(torch.bfloat16).float()
+    out["x"] = x.numpy()
+    for transpose in (False, True):
+        src = x.t().contiguous() if transpose else x
+        for mode in ("rtn", "sr", "eden"):
+            for fos in (False, True):
+                for rotate in ((True,) if mode == "eden" else (False, True)):
+                    vals, s, gg = fp4ref.quantize(src, mode=mode, four_over_six=fos, seed=11, rotate=rotate,
+                                                  rotate_seed=21)
+                    tag = f"{'t' if transpose else 'r'}_{mode}_{int(fos)}_{int(rotate)}"
+                    out[tag + "_codes"] = values_to_codes(vals).numpy()
+                    out[tag + "_scales"] = u8(s.to(torch.float8_e4m3fn))
+                    out[tag + "_g"] = gg.reshape(1).numpy()
+    out["rht_seed21"] = fp4ref.rht128(x[:8], 21).numpy()
+    out["signs_seed21"] = fp4ref.hadamard_signs(21).numpy()
+    v = torch.cat([torch.logspace(-10, 9.5, 300, base=2.0), torch.tensor([2.0 ** -9, 448.0, 500.0, 1e-4])])
+    u = fp4ref.uniform_u(v.numel(), 5, "cpu")
+    out["sr_e4m3_v"], out["sr_e4m3_u"] = v.numpy(), u.numpy()
+    out["sr_e4m3_out"] = u8(fp4ref._sr_e4m3(v, u).to(torch.float8_e4m3fn))
+    return out
+
+
 def rotate_t(x: torch.Tensor, H: torch.Tensor) -> torch.Tensor:
     """x [M, K] -> rotated x^T [K, M]: every 16-block along M times H, summed sequentially over i (the order of
     csrc/act_quant.cu:110-116; products by +-0.25 are exact, so this equals the kernel's fmaf chain)."""
@@ -358,7 +390,7 @@ def main():
                      ("transposed", transposed_cases), ("step", step_cases), ("direction", direction_cases),
                      ("optimizer", optimizer_cases), ("linear", linear_cases), ("fos", fos_cases),
                      ("momentum", momentum_cases), ("directions2", directions2_cases),
-                     ("momentum2", momentum2_cases), ("presets", presets_cases)):
+                     ("momentum2", momentum2_cases), ("presets", presets_cases), ("general", general_cases)):
         if len(sys.argv) > 2 and name not in sys.argv[2:]:
             continue                                   # optional: names of the files to (re)generate
         data = fn()
