@@ -1,17 +1,23 @@
 """GEMM back end of NVFP4 lattice linear layers on B200: operand quantization + the block-scaled FP4 GEMM.
 
-Mirrors the NVIDIA-recipe part of the reference's ``bitlattice/backend.py`` (same names, argument meaning and tensor
-layouts): round-to-nearest activations, stochastically rounded gradients, a 16-point Hadamard rotation of the
+Mirrors the NVFP4 part of the reference's ``bitlattice/backend.py`` (same names, argument meaning and tensor layouts).
+The NVIDIA recipe: round-to-nearest activations, stochastically rounded gradients, a 16-point Hadamard rotation of the
 weight-gradient operands, the transposed weight re-quantized once per weight version for the input gradient, the layer
-input saved as transposed NVFP4. Where the reference calls ``torch.ops.bitlattice.*`` quantizers and
+input saved as transposed NVFP4. The quartet2 recipes: four-over-six activations, MS-EDEN (or stochastic) gradients,
+a randomized 128-point rotation of the token axis of the weight-gradient GEMM and of the output-feature axis of the
+input-gradient GEMM, the rotated W^T re-quantized per backward or cached per weight version (with a current or a
+bounded per-tensor scale), and deferred weight gradients (operands with power-of-two per-tensor scales kept per
+micro-batch, folded and multiplied in one GEMM). Where the reference calls ``torch.ops.bitlattice.*`` quantizers and
 ``torch._scaled_mm`` (cuBLASLt), this module calls the kernels of ``libbitlattice_b200.so``; block scales are produced
 directly in the GEMM's tiled layout and the per-tensor scales are applied in the GEMM epilogue.
 
-Not built (the reference's other recipes): MS-EDEN / 128-point rotations, delayed scales, deferred
-weight gradients, MXFP8. Asking for them raises.
+Not built: delayed per-tensor scales (``scale_source='delayed'``), seeds mixed with a device epoch for CUDA-graph
+replay, MXFP8. Asking for them raises. The reference's one-read kernel for both layouts of an operand
+(``nvfp4_quantize2``) is two calls of the general quantizer here: same results, one more read.
 """
 from __future__ import annotations
 
+import contextlib
 import itertools
 import weakref
 from collections import OrderedDict
@@ -25,17 +31,30 @@ from . import _ops
 from . import formats as F
 from .tensor import wait_for_update
 
-__all__ = ["FP4_RECIPES", "Fp4Operand", "Fp4Recipe", "as_recipe", "clear_shared", "drop_cached", "fp4_backward", "fp4_dgrad", "fp4_wgrad",
-           "fp4_forward_saving", "fp4_mm", "fp4_supported", "fp4_unfit", "is_nvfp4", "nvfp4_linear", "quantize_fp4",
-           "rht_last", "set_sr_seed", "to_blocked", "weight_operand", "weight_t_operand"]
+__all__ = ["FP4_RECIPES", "Fp4Operand", "Fp4Recipe", "as_recipe", "clear_shared", "defer_wgrad", "drop_cached",
+           "flush_wgrad", "fold_rounded", "fp4_backward", "fp4_dgrad", "fp4_wgrad", "fp4_forward_saving", "fp4_mm",
+           "fp4_supported", "fp4_unfit", "is_nvfp4", "nvfp4_linear", "pending_wgrad", "quantize_fp4", "rht_last",
+           "set_sr_seed", "to_blocked", "weight_operand", "weight_t_operand", "weight_t_rotated_operand"]
 
 
 @dataclass(frozen=True)
 class Fp4Recipe:
-    """Quantization of the GEMM operands (reference: bitlattice/backend.py:57-121). Built: the default values (the
-    NVIDIA NVFP4 training recipe) and ``activations='4over6'`` (four-over-six block scales for the forward input,
-    criterion ``select``), everything else as in the NVIDIA recipe. The 128-point rotation, MS-EDEN gradients and
-    delayed scales are not."""
+    """Quantization of the GEMM operands under the FP4 policies (reference: bitlattice/backend.py:57-121).
+
+    activations      'rtn' | '4over6'   forward input: round to nearest, with four-over-six block scales or not
+    gradients        'sr' | 'eden'      output gradient in backward: stochastic rounding, or MS-EDEN (round to nearest
+                                        plus stochastically rounded, bias-correcting block scales; needs rotation=128)
+    rotation         16 | 128           randomized Hadamard block along the token axis of the weight-gradient GEMM
+    rotate_dgrad     bool               also rotate (128) the output-feature axis of the input-gradient GEMM
+    backward_4over6  bool               four-over-six block scales for the backward operands too
+    select           'mse' | 'mae'      four-over-six criterion
+    dgrad_weight     'requantize' | 'cached'   with rotate_dgrad: the rotated W^T re-quantized in every backward, or
+                                        once per weight version (round to nearest, one rotation per version)
+    dgrad_scale      'current' | 'bound'   cached W^T per-tensor scale: from an amax pass over the rotated weight, or
+                                        the bound sqrt(128) * W.global_scale
+    scale_source     'current'          ('delayed' is not built)
+    scale_margin     float              kept for the reference's signature
+    """
 
     activations: str = "rtn"
     gradients: str = "sr"
@@ -51,27 +70,60 @@ class Fp4Recipe:
     def __post_init__(self):
         if self.activations not in ("rtn", "4over6"):
             raise ValueError("activations must be 'rtn' or '4over6'")
+        if self.gradients not in ("sr", "eden"):
+            raise ValueError("gradients must be 'sr' or 'eden'")
+        if self.rotation not in (16, 128):
+            raise ValueError("rotation must be 16 or 128")
+        if self.gradients == "eden" and self.rotation != 128:
+            raise ValueError("MS-EDEN gradients need rotation=128")
         if self.select not in ("mse", "mae"):
             raise ValueError("select must be 'mse' or 'mae'")
-        if astuple(self)[1:5] + astuple(self)[6:] != _NVIDIA[1:5] + _NVIDIA[6:]:
-            raise ValueError("only the 'nvidia' and '4over6' FP4 recipes (stochastically rounded gradients, 16-point "
-                             "rotation) are built; the quartet2 recipes (128-point rotation, MS-EDEN, cached or "
-                             "delayed scales) are not")
+        if self.dgrad_weight not in ("requantize", "cached"):
+            raise ValueError("dgrad_weight must be 'requantize' or 'cached'")
+        if self.dgrad_scale not in ("current", "bound"):
+            raise ValueError("dgrad_scale must be 'current' or 'bound'")
+        if self.dgrad_scale == "bound" and not (self.dgrad_weight == "cached" and self.rotate_dgrad
+                                                and self.rotation == 128):
+            raise ValueError("dgrad_scale='bound' needs cached weights and the 128-element dgrad rotation")
+        if self.scale_source == "delayed":
+            raise ValueError("delayed per-tensor scales (scale_source='delayed') are not built")
+        if self.scale_source != "current":
+            raise ValueError("scale_source must be 'current' or 'delayed'")
+        if not self.scale_margin >= 1.0:
+            raise ValueError("scale_margin must be >= 1")
 
     @property
     def legacy(self) -> bool:
         """True for the NVIDIA recipe."""
         return astuple(self) == _NVIDIA
 
+    @property
+    def packed_exchange(self) -> bool:
+        """True when the operands are those of the NVIDIA recipe up to the forward activations' block scales: what the
+        multi-GPU layers that exchange packed operands are written for."""
+        return astuple(self)[1:5] + astuple(self)[6:] == _NVIDIA[1:5] + _NVIDIA[6:]
+
 
 _NVIDIA = ("rtn", "sr", 16, False, False, "mse", "requantize", "current", "current", 2.0)
 
-FP4_RECIPES: dict[str, Fp4Recipe] = {"nvidia": Fp4Recipe(), "4over6": Fp4Recipe(activations="4over6")}
+FP4_RECIPES: dict[str, Fp4Recipe] = {
+    "nvidia": Fp4Recipe(),
+    "4over6": Fp4Recipe(activations="4over6"),
+    "quartet2": Fp4Recipe(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True),
+    "quartet2_4o6": Fp4Recipe(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True,
+                              backward_4over6=True),
+    "quartet2_fast": Fp4Recipe(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True,
+                               dgrad_weight="cached"),
+    "quartet2_bound": Fp4Recipe(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True,
+                                dgrad_weight="cached", dgrad_scale="bound"),
+}
 
 
 def as_recipe(r) -> Fp4Recipe:
     if isinstance(r, Fp4Recipe):
         return r
+    if r == "quartet2_delayed":
+        raise ValueError("FP4 recipe 'quartet2_delayed' (delayed per-tensor scales) is not built")
     if r not in FP4_RECIPES:
         raise ValueError(f"unknown FP4 recipe {r!r}; built: {sorted(FP4_RECIPES)}")
     return FP4_RECIPES[r]
@@ -239,6 +291,27 @@ def weight_t_operand(w) -> Fp4Operand:
     return _cached(w, "wt", make)
 
 
+def weight_t_rotated_operand(w, four_over_six: bool = False, seed: int | None = None,
+                             scale_source: str = "current") -> Fp4Operand:
+    """W^T [K, N] rotated along N (128-blocks) and re-quantized from the codes once per weight version (round to
+    nearest); the rotation seed (``rotate_seed`` of the result) is fixed per version, or ``seed`` (then not cached).
+    ``scale_source='bound'``: per-tensor scale sqrt(128) * W.global_scale instead of an amax pass over the rotated
+    weight (reference: bitlattice/backend.py:345-362)."""
+    if scale_source not in ("current", "bound"):
+        raise ValueError("scale_source must be 'current' or 'bound'")
+
+    def make(seed):
+        # |W H_128| <= sqrt(128) * 6 * 448 * W.global_scale; block scales still use the current block maxima
+        given = ((w.global_scale.float() * (128 ** 0.5) * (448.0 / 256.0 if four_over_six else 1.0)).reshape(1)
+                 if scale_source == "bound" else None)
+        return _q(None, mode="rtn", four_over_six=four_over_six, rotate_seed=seed, seed=0, w=w, given=given)
+    if seed is not None:
+        return make(seed)
+    ver = getattr(w, "_bl_version", 0)
+    seed = (id(w) * 2654435761 + ver * 40503 + 1) & 0x7FFFFFFF
+    return _cached(w, ("wt128_4o6" if four_over_six else "wt128") + "_" + scale_source, lambda: make(seed))
+
+
 @cache
 def _hadamard16(device: torch.device, dtype: torch.dtype) -> torch.Tensor:
     """Orthogonal 16x16 matrix diag(s) H / 4 with the reference's fixed sign vector (backend.py:365-372; the signs
@@ -259,6 +332,31 @@ def rht_last(x: torch.Tensor) -> torch.Tensor:
 def _pad_rows(x2: torch.Tensor, multiple: int) -> torch.Tensor:
     pad = (-x2.shape[0]) % multiple
     return torch.nn.functional.pad(x2, (0, 0, 0, pad)) if pad else x2
+
+
+def _pad_to(recipe: Fp4Recipe) -> int:
+    return 128 if recipe.rotation == 128 else 32
+
+
+def _q(x2: torch.Tensor | None, *, transpose: bool = False, mode: str = "rtn", four_over_six: bool = False,
+       recipe: Fp4Recipe | None = None, rotate_seed: int = -1, seed: int = 0, w=None, pow2: bool = False,
+       given: torch.Tensor | None = None) -> Fp4Operand:
+    """NVFP4 operand from the general quantizer: rows of x2 (or of x2^T), optionally rotated (128) with
+    ``rotate_seed``; ``w``: an NVFP4 weight given by its codes (transposed re-quantization); ``pow2``: per-tensor scale
+    rounded up to a power of two (reference: bitlattice/backend.py:398-416)."""
+    select = recipe.select if recipe is not None else "mse"
+    rot = rotate_seed >= 0
+    if w is not None:
+        wait_for_update(w)
+        packed, scales, g = _ops.nvfp4_quantize_general(
+            w.packed, transpose=True, mode=mode, four_over_six=four_over_six, select=select, rotate=rot, seed=seed,
+            rotate_seed=rotate_seed if rot else -1, given=given, pow2=pow2, w_scales=w.scales,
+            w_global=w.global_scale.float().reshape(1), blocked=True)
+    else:
+        packed, scales, g = _ops.nvfp4_quantize_general(
+            x2, transpose=transpose, mode=mode, four_over_six=four_over_six, select=select, rotate=rot, seed=seed,
+            rotate_seed=rotate_seed if rot else -1, given=given, pow2=pow2, blocked=True)
+    return Fp4Operand(packed, scales, g, True, rotate_seed)
 
 
 # one quantization per input shared by its consumers (q / k / v, gate / up); reference: backend.py:471-499
@@ -285,16 +383,29 @@ def clear_shared() -> None:
 
 
 def _input_operands(x: torch.Tensor, recipe: Fp4Recipe, row: bool = True):
-    """Forward operand of x and its rotated transposed operand for the weight gradient (reference:
-    backend.py:519-546, legacy branch): the global scale of x bounds the rotated one by a factor 4."""
+    """Forward operand of x (None with ``row=False``) and its rotated transposed operand for the weight gradient
+    (reference: bitlattice/backend.py:519-557)."""
     K = x.shape[-1]
-    x2 = _pad_rows(x.reshape(-1, K), 32).contiguous()
-    xq = _act_operand(x2, recipe)
-    # |x H/4| <= 4 max|x| for the orthogonal 16 x 16 rotation: the row-wise per-tensor scale bounds the rotated one
-    # (brought back to the 448 convention when the row operand used 256; reference: backend.py:541-544)
-    bound = xq.global_scale * (4.0 * (256.0 / 448.0 if recipe.activations == "4over6" else 1.0))
-    xt = Fp4Operand(*_ops.quantize_nvfp4_t(x2, _hadamard16(x2.device, torch.float32), -1, 0, bound, blocked=True), True)
-    return (xq if row else None), xt
+    x2 = _pad_rows(x.reshape(-1, K), _pad_to(recipe)).contiguous()
+    if recipe.rotation == 16:
+        xq = _act_operand(x2, recipe)
+        # |x H/4| <= 4 max|x| for the orthogonal 16 x 16 rotation: the row-wise per-tensor scale bounds the rotated
+        # one (brought back to the 448 convention when the row operand used 256; reference: backend.py:541-544)
+        bound = xq.global_scale * (4.0 * (256.0 / 448.0 if recipe.activations == "4over6" else 1.0))
+        xt = Fp4Operand(*_ops.quantize_nvfp4_t(x2, _hadamard16(x2.device, torch.float32), -1, 0, bound, blocked=True),
+                        True)
+        return (xq if row else None), xt
+    mode = "eden" if recipe.gradients == "eden" else "rtn"
+    fos = recipe.backward_4over6 or (mode == "rtn" and recipe.activations == "4over6")
+    rseed, seed = _seed(), _seed()
+    # the weight-gradient operands get power-of-two per-tensor scales: micro-batches can then be concatenated exactly
+    # into one GEMM (deferred weight gradients)
+    xt = _q(x2, transpose=True, mode=mode, four_over_six=fos, recipe=recipe, rotate_seed=rseed, seed=seed, pow2=True)
+    xq = None
+    if row:
+        xq = (_q(x2, four_over_six=recipe.activations == "4over6", recipe=recipe) if K % 128 == 0
+              else _act_operand(x2, recipe))
+    return xq, xt
 
 
 def nvfp4_linear(x: torch.Tensor, w, bias: torch.Tensor | None = None, recipe: Fp4Recipe = Fp4Recipe()
@@ -344,14 +455,179 @@ def fp4_wgrad(g2p: torch.Tensor, gq: Fp4Operand | None, xt: Fp4Operand, w, recip
 
 
 def fp4_backward(gy: torch.Tensor, w, xt: Fp4Operand | None, need_x: bool, need_w: bool,
-                 recipe: Fp4Recipe = Fp4Recipe()):
-    """Input and weight gradients of y = x W^T on FP4 tensor cores (reference: backend.py:592-626):
-    gx = Q_sr(gy) Q(W^T)^T, gw = Q_sr(rot(gy^T)) Q(rot(x^T))^T; the rotations cancel in the product."""
-    gx = gw = gq = g2p = None
+                 recipe: Fp4Recipe = Fp4Recipe(), *, wt: Fp4Operand | None = None, keep: list | None = None):
+    """Input and weight gradients of y = x W^T on FP4 tensor cores (reference: bitlattice/backend.py:560-634).
+    NVIDIA recipe: gx = Q_sr(gy) Q(W^T)^T, gw = Q_sr(rot16(gy^T)) Q(rot16(x^T))^T. 128-rotation recipes: the output
+    gradient is quantized rotated along N for the input gradient (against W^T rotated with the same signs) and
+    rotated along the tokens, with the rotation of the saved x^T, for the weight gradient; the rotations cancel in
+    the products.
+
+    wt     the rotated W^T operand to use (``dgrad_weight='cached'`` recipes; default: the per-version cache)
+    keep   the weight-gradient operands (g^T, x^T) are appended here instead of being multiplied or deferred"""
+    if (wt is not None or keep is not None) and not (
+            recipe.rotation == 128 and recipe.rotate_dgrad and recipe.dgrad_weight == "cached"
+            and gy.shape[-1] % 128 == 0 and (xt is None or xt.rotate_seed >= 0)):
+        raise RuntimeError("explicit W^T / kept operands need a 'quartet2_fast'-like recipe and output features in "
+                           "multiples of 128")
+    if recipe.rotation == 16 and not recipe.backward_4over6 and recipe.gradients == "sr" and not _defer_wgrad[0]:
+        gx = gw = gq = g2p = None
+        if need_x:
+            gx, g2p, gq = fp4_dgrad(gy, w, recipe)
+        if need_w:
+            if g2p is None:
+                g2p = _pad_rows(gy.reshape(-1, gy.shape[-1]), 32).contiguous()
+            gw = fp4_wgrad(g2p, gq, xt, w, recipe)
+        return gx, gw
+    N = gy.shape[-1]
+    g2 = gy.reshape(-1, N)
+    M = g2.shape[0]
+    g2p = _pad_rows(g2, _pad_to(recipe)).contiguous()
+    gx = gw = gq = None
+    b46 = recipe.backward_4over6
+    rotated_w = need_w and xt.rotate_seed >= 0
+    mode = "eden" if recipe.gradients == "eden" else "sr"
+    if N % 128 == 0 and (rotated_w or not need_w) and (recipe.rotate_dgrad or not need_x):
+        if need_x and recipe.dgrad_weight == "cached" and wt is None:
+            wt = weight_t_rotated_operand(w, b46, scale_source=recipe.dgrad_scale)
+        r = wt.rotate_seed if wt is not None else _seed()
+        seed_row, seed_col = _seed(), _seed()
+        if need_x:
+            gq = _q(g2p, mode=mode, four_over_six=b46, recipe=recipe, rotate_seed=r, seed=seed_row)
+            if wt is None:      # W^T: MS-EDEN with MS-EDEN gradients (both factors unbiased), else round to nearest
+                wt = _q(None, mode="eden" if mode == "eden" else "rtn", four_over_six=b46, recipe=recipe,
+                        rotate_seed=r, seed=_seed(), w=w)
+            gx = fp4_mm(gq, wt, gy.dtype)[:M]
+        if need_w:
+            gt = _q(g2p, transpose=True, mode=mode, four_over_six=b46, recipe=recipe, rotate_seed=xt.rotate_seed,
+                    seed=seed_col, pow2=True)
+            if keep is not None:
+                keep.append((gt, xt))
+            else:
+                gw = _weight_grad(w, gt, xt)
+        return gx, gw
     if need_x:
-        gx, g2p, gq = fp4_dgrad(gy, w, recipe)
+        if recipe.rotate_dgrad and N % 128 == 0:
+            wt = (weight_t_rotated_operand(w, b46, scale_source=recipe.dgrad_scale)
+                  if recipe.dgrad_weight == "cached" else None)
+            r = wt.rotate_seed if wt is not None else _seed()
+            gq = _q(g2p, mode=mode, four_over_six=b46, recipe=recipe, rotate_seed=r, seed=_seed())
+            if wt is None:
+                wt = _q(None, mode="eden" if mode == "eden" else "rtn", four_over_six=b46, recipe=recipe,
+                        rotate_seed=r, seed=_seed(), w=w)
+            gx = fp4_mm(gq, wt, gy.dtype)[:M]
+            gq = None                                     # rotated: its per-tensor scale does not bound g^T
+        else:
+            gq = (_q(g2p, mode="sr", four_over_six=True, recipe=recipe, seed=_seed()) if b46
+                  else quantize_fp4(g2p, stochastic=True))
+            gx = fp4_mm(gq, weight_t_operand(w), gy.dtype)[:M]
     if need_w:
-        if g2p is None:
-            g2p = _pad_rows(gy.reshape(-1, gy.shape[-1]), 32).contiguous()
-        gw = fp4_wgrad(g2p, gq, xt, w, recipe)
+        if xt.rotate_seed >= 0:                                                        # g^T rotated (128), [N, Mp]
+            gt = _q(g2p, transpose=True, mode=mode, four_over_six=b46, recipe=recipe, rotate_seed=xt.rotate_seed,
+                    seed=_seed(), pow2=True)
+        else:
+            if _defer_wgrad[0]:
+                name = getattr(w, "_bl_name", None) or f"weight {tuple(w.shape)}"
+                raise RuntimeError(f"{name}: deferred weight gradients need a recipe with the 128-element rotation "
+                                   "(e.g. 'quartet2_fast'); this layer's recipe rotates by 16 and its weight-gradient "
+                                   "operands cannot be folded")
+            seed = _seed()                                                             # g^T rotated (16), [N, Mp]
+            bound = gq.global_scale * (4.0 * (256.0 / 448.0 if b46 else 1.0)) if gq is not None else None
+            gt = Fp4Operand(*_ops.quantize_nvfp4_t(g2p, _hadamard16(g2p.device, torch.float32), seed, 0, bound,
+                                                   blocked=True), True)
+            return gx, fp4_mm(gt, xt, w.dtype)                  # not power-of-two scaled: never deferred
+        gw = _weight_grad(w, gt, xt)
     return gx, gw
+
+
+# deferred weight gradients (reference: bitlattice/backend.py:637-746)
+# With micro-batches, every backward of a layer adds its weight gradient to .grad from a GEMM over that micro-batch's
+# tokens only. Inside ``defer_wgrad()`` the 128-rotation recipes keep the quantized operands (E^T, x^T: power-of-two
+# per-tensor scales) instead; ``flush_wgrad`` folds their block scales to a common per-tensor scale (exact: powers of
+# two shift E4M3 exponents), concatenates them along the token axis and runs one GEMM over all micro-batches.
+
+_defer_wgrad = [0]
+_PENDING: OrderedDict = OrderedDict()             # id(param) -> (weakref(param), [(gt, xt), ...])
+_FOLD_ROUNDED: dict = {}                          # device -> int64 counter of block scales that were rounded
+_PIECES: dict = {}
+
+
+@contextlib.contextmanager
+def defer_wgrad():
+    """Keep the weight-gradient operands of FP4 layers instead of computing their gradients (see flush_wgrad)."""
+    _defer_wgrad[0] += 1
+    try:
+        yield
+    finally:
+        _defer_wgrad[0] -= 1
+
+
+def _weight_grad(w, gt: Fp4Operand, xt: Fp4Operand):
+    if not _defer_wgrad[0]:
+        return fp4_mm(gt, xt, w.dtype)
+    entry = _PENDING.get(id(w))
+    if entry is None or entry[0]() is not w:
+        entry = _PENDING[id(w)] = (weakref.ref(w), [])
+    entry[1].append((gt, xt))
+    return None
+
+
+def _concat(ops: list) -> Fp4Operand:
+    """Operands [rows, K_j] with power-of-two per-tensor scales and tiled block scales -> one operand [rows, sum K_j]
+    with the largest per-tensor scale; the others' block scales are multiplied by g_j / g_max = 2^-k. Exact while the
+    products stay in E4M3's normal range; smaller products are rounded and counted (``fold_rounded``)."""
+    if len(ops) == 1:
+        return ops[0]
+    packed = torch.cat([o.packed for o in ops], 1)
+    rows = ops[0].packed.shape[0]
+    nr = -(-rows // 128)
+    dev = packed.device
+    count = _FOLD_ROUNDED.get(dev)
+    if count is None:
+        count = _FOLD_ROUNDED[dev] = torch.zeros(1, dtype=torch.int64, device=dev)
+    tiles = [o.scales.view(torch.uint8).view(nr, -1, 512) for o in ops]
+    g = torch.cat([o.global_scale.reshape(1).float() for o in ops])
+    scales = torch.cat(tiles, 1).contiguous()
+    widths = tuple(t.shape[1] for t in tiles)
+    piece = _PIECES.get((widths, dev))
+    if piece is None:
+        piece = _PIECES[(widths, dev)] = torch.tensor([j for j, n in enumerate(widths) for _ in range(n)],
+                                                      dtype=torch.int32, device=dev)
+    g_max = _ops.fp4_fold_scales(scales.view(-1), nr, piece, g, count)
+    return Fp4Operand(packed, scales.view(-1), g_max, True)
+
+
+def fold_rounded(reset: bool = False) -> int:
+    """Number of NVFP4 blocks whose scale was rounded when deferred weight-gradient operands of micro-batches with
+    different magnitudes were folded into one GEMM (0: the deferred gradients were exact). Synchronizes."""
+    n = int(sum(int(c.item()) for c in _FOLD_ROUNDED.values()))
+    if reset:
+        for c in _FOLD_ROUNDED.values():
+            c.zero_()
+    return n
+
+
+def pending_wgrad() -> list:
+    """Parameters with deferred weight gradients."""
+    return [ref() for ref, _ in _PENDING.values() if ref() is not None]
+
+
+def flush_wgrad(params=None, optimizer=None) -> int:
+    """Compute deferred weight gradients (all, or of ``params``) with one GEMM per parameter, add them to ``.grad``
+    and, for a fused-backward optimizer, apply its update. Returns the number of parameters flushed."""
+    keys = list(_PENDING) if params is None else [id(p) for p in params if id(p) in _PENDING]
+    n = 0
+    for k in keys:
+        ref, items = _PENDING.pop(k)
+        p = ref()
+        if p is None or not items:
+            continue
+        gt = _concat([a for a, _ in items])
+        xt = _concat([b for _, b in items])
+        items.clear()
+        gw = fp4_mm(gt, xt, p.dtype)
+        del gt, xt
+        p.grad = gw if p.grad is None else p.grad.add_(gw)
+        if optimizer is not None and getattr(optimizer, "fused_backward", False):
+            optimizer._on_grad(p)
+        n += 1
+    return n

@@ -51,6 +51,7 @@ PRESETS: dict[str, Compute] = {
     "exact": Compute(),
     "fp4": Compute("nvfp4", backward=False),
     "fp4_all": Compute("nvfp4"),
+    **{name: Compute("nvfp4", nvfp4=r) for name, r in FP4_RECIPES.items() if name != "nvidia"},
 }
 
 

@@ -249,8 +249,8 @@ def _fp4_all_route(x_shard: torch.Tensor, w):
         return None
     from .compute_policy import route
     policy, comp = route(x_shard, w)
-    if policy != "fp4_all" or x_shard.shape[0] % 128 or x_shard.shape[1] % 64:
-        return None
+    if policy != "fp4_all" or not comp.nvfp4.packed_exchange or x_shard.shape[0] % 128 or x_shard.shape[1] % 64:
+        return None                             # (the 128-rotation recipes take the generic route: local layers)
     return comp.nvfp4
 
 
@@ -547,6 +547,7 @@ def token_parallel_linears(x: torch.Tensor, weights, gathered: GatheredWeights |
         from .compute_policy import route
         routes = [route(x, w) for w in weights]
         if all(r[0] == "fp4_all" for r in routes) and all(r[1].nvfp4 == routes[0][1].nvfp4 for r in routes) \
+                and routes[0][1].nvfp4.packed_exchange \
                 and all(w.shape[0] % 128 == 0 and w.shape[1] % 64 == 0 for w in weights):
             if gathered is None:
                 gathered = GatheredWeights(group)

@@ -75,10 +75,17 @@ def test_compute_policy_routes_and_requirements():
     assert bl.COMPUTE_PRESETS["fp4"].route == "fp4" and bl.COMPUTE_PRESETS["fp4_all"].route == "fp4_all"
     with pytest.raises(ValueError):
         bl.Compute("mxfp8")
-    with pytest.raises(ValueError):
-        bl.backend.Fp4Recipe(rotation=128)
-    with pytest.raises(ValueError):
-        bl.compute_policy.as_compute("quartet2")
+    with pytest.raises(ValueError, match="not built"):
+        bl.backend.Fp4Recipe(scale_source="delayed")
+    with pytest.raises(ValueError, match="not built"):
+        bl.backend.as_recipe("quartet2_delayed")
+    with pytest.raises(ValueError, match="rotation=128"):
+        bl.backend.Fp4Recipe(gradients="eden")
+    with pytest.raises(ValueError, match="bound"):
+        bl.backend.Fp4Recipe(dgrad_scale="bound")
+    assert bl.compute_policy.as_compute("quartet2_fast").nvfp4 == bl.backend.FP4_RECIPES["quartet2_fast"]
+    assert bl.compute_policy.as_compute("quartet2_fast").route == "fp4_all"
+    assert not bl.backend.FP4_RECIPES["quartet2_fast"].packed_exchange and bl.backend.FP4_RECIPES["4over6"].packed_exchange
     bad = cpu_weight(rows=24, cols=64)
     assert "multiple of 32" in bl.backend.fp4_unfit(bad, 0, True)
     assert "multiple of 16" in bl.backend.fp4_unfit(bad, 0, False)

@@ -93,8 +93,8 @@ def test_four_over_six_recipe_forward_and_backward():
         assert rel(p.grad.cpu(), gy.float().cpu().T @ x.float()) < 0.25
     assert errs["4over6"] <= errs["nvidia"] * 1.02, errs
     assert bl._ops.gemm_status(0) == 0
-    with pytest.raises(ValueError, match="quartet2"):
-        bl.backend.Fp4Recipe(rotation=128)
+    with pytest.raises(ValueError, match="not built"):
+        bl.backend.Fp4Recipe(scale_source="delayed")
 
 
 @pytest.mark.parametrize("M", [5, 96, 512])
