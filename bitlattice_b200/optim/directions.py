@@ -176,12 +176,20 @@ def load_momentum(st: dict, mode: str, X: torch.Tensor) -> torch.Tensor:
     rows, cols = X.shape
     if mode == "bf16":
         return st["mb"].float() if "mb" in st else torch.zeros_like(X)
+    if mode == "nvfp4":
+        if "m4p" not in st:
+            return torch.zeros_like(X)
+        return _ops.dequantize(st["m4p"], st["m4s"], st["m4g"], None, "nvfp4", rows, cols, torch.float32)
     if "m8" not in st:
         return torch.zeros_like(X)
     return (st["m8"].float() * st["m8s"][:, None]).reshape(-1)[:X.numel()].view(rows, cols)
 
 
 def store_momentum(st: dict, mode: str, m: torch.Tensor, seed: int, gens: dict) -> None:
+    if mode == "nvfp4":             # stochastic rounding with four-over-six block scales (the general quantizer)
+        st["m4p"], st["m4s"], st["m4g"] = _ops.nvfp4_quantize_general(m.contiguous(), mode="sr", four_over_six=True,
+                                                                      seed=seed)
+        return
     gen = gens.get(m.device)
     if gen is None:
         gen = gens[m.device] = torch.Generator(device=m.device)
@@ -215,7 +223,9 @@ def momentum(G2: torch.Tensor, st: dict, mode: str, beta1: float, seed: int, pid
             st["m"] = torch.zeros_like(X)
         st["m"].mul_(beta1).add_(X, alpha=1 - beta1)
         return st["m"]
-    if mode in ("bf16", "int8", "fp8"):
+    if mode in ("bf16", "int8", "fp8", "nvfp4"):
+        if mode == "nvfp4" and X.shape[1] % 16:
+            mode = "int8"                            # rows not made of 16-element blocks keep int8 momentum
         m = load_momentum(st, mode, X)
         m.mul_(beta1).add_(X, alpha=1 - beta1)
         store_momentum(st, mode, m, (seed + 7919 * pid + 104729 * st["step"]) & 0x7FFFFFFF, gens)

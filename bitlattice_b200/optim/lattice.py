@@ -9,11 +9,12 @@ For the directions sign, colnorm and raw, direction, scale refit and projection 
 gradient on the GPU (``bl_nvfp4_lattice_update``): the fp32 direction is never materialised and no row tiling is
 needed. The other directions of the reference (Newton-Schulz ``muon`` / ``muon_block``, ``factored``, ``sinkhorn``,
 neuron-wise normalisation) write D first (``optim/directions.py``) and hand it to the same kernel
-(``bl_nvfp4_step_quantized``). Momentum (fp32, bf16, int8, fp8, ternary) replaces the gradient by its running average.
+(``bl_nvfp4_step_quantized``). Momentum (fp32, bf16, int8, fp8, nvfp4, ternary) replaces the gradient by its running
+average.
 
 Same constructor, option names, presets, validation errors, per-parameter seeds (``seed + 7919 * index``), step
 counters and state layout (``state[p]["phase"]``: uint8 [rows, cols * container_bits / 8]; factored ``r`` / ``c`` /
-``k``; momentum ``m`` / ``mb`` / ``m8`` + ``m8s`` / ``mq`` + ``ms``) as the reference, so optimizer state interchanges.
+``k``; momentum ``m`` / ``mb`` / ``m8`` + ``m8s`` / ``m4p`` + ``m4s`` + ``m4g`` / ``mq`` + ``ms``) as the reference, so optimizer state interchanges.
 Not built, and refused with NotImplementedError: NVFP4-format momentum, row-sparse gradients, native-format
 (non-lattice) parameters and host-memory state.
 
@@ -54,7 +55,6 @@ def defer_fused_updates(delta: int) -> None:
 DIRECTIONS = ("muon_block", "muon", "factored", "sinkhorn", "colnorm", "sign", "raw")
 FUSED_DIRECTIONS = ("colnorm", "sign", "raw")        # computed inside the update kernel; the others write D first
 MOMENTA = ("none", "fp32", "ternary", "bf16", "int8", "fp8", "nvfp4")
-BUILT_MOMENTA = ("none", "fp32", "ternary", "bf16", "int8", "fp8")
 ROUNDINGS = ("sr", "strat", "rtn")
 SCALE_RULES = ("fit", "fit_latent", "fixed")
 
@@ -78,9 +78,6 @@ def _validate(g: dict) -> None:
         raise ValueError("vector_direction cannot be a matrix direction")
     if g["normalize"] not in ("none", "row"):
         raise ValueError("normalize must be 'none' or 'row'")
-    if g["momentum"] not in BUILT_MOMENTA:
-        raise NotImplementedError(f"momentum={g['momentum']!r} is outside this build (it needs the reference's general "
-                                  f"NVFP4 quantizer); built: {BUILT_MOMENTA}")
     if g["ns_dtype"] not in ("bf16", "fp16", "fp32"):
         raise ValueError("ns_dtype must be 'bf16', 'fp16' or 'fp32'")
     if g["ns_coeffs"] not in ("muon", "polar_express"):
@@ -410,8 +407,11 @@ class Lattice(torch.optim.Optimizer):
         for g in self.param_groups:
             for p in g["params"]:
                 out["phase"] += p.numel() * g["phase_bits"]
+                mode = g["momentum"]
+                if mode == "nvfp4" and p.shape[-1] % 16:
+                    mode = "int8"
                 out["momentum"] += p.numel() * {"none": 0, "fp32": 32, "bf16": 16, "int8": 8 + 32 / D_.MOM_BLOCK,
-                                                "fp8": 8 + 32 / D_.MOM_BLOCK, "ternary": 8}[g["momentum"]]
+                                                "fp8": 8 + 32 / D_.MOM_BLOCK, "ternary": 8, "nvfp4": 4.5}[mode]
                 if not self._fused(p, g):
                     kind = g["direction"] if p.dim() >= 2 else g["vector_direction"]
                     if kind == "factored":

@@ -118,6 +118,29 @@ def test_generator_rounded_momentum_keeps_its_average(mode):
     assert torch.equal(p.packed, p2.packed)
 
 
+def test_nvfp4_momentum_is_the_general_quantizer_of_the_average():
+    """momentum='nvfp4' (reference: bitlattice/optim/lattice.py:419-423,455-458; needs the reference's CUDA
+    extension, so no fixture): the stored average is the stochastically rounded four-over-six NVFP4 of the fp32
+    average, with the seed (seed + 7919 pid + 104729 step) & 0x7FFFFFFF, and the next step starts from its values."""
+    from oracle import fp4_general as G
+    w = bl.LatticeTensor.from_float((torch.randn(32, 256, generator=torch.Generator().manual_seed(0)) * 0.02).to(DEV),
+                                    "nvfp4", method="rtn", dtype=torch.bfloat16)
+    p = torch.nn.Parameter(w)
+    opt = bl.Lattice([p], lr=3e-3, direction="sign", phase_bits=4, seed=5, momentum="nvfp4", beta1=0.9)
+    m = np.zeros((32, 256), np.float32)
+    for s in range(1, 4):
+        grad = (torch.randn(32, 256, generator=torch.Generator().manual_seed(10 + s)) * 1e-2).to(torch.bfloat16)
+        p.grad = grad.to(DEV)
+        opt.step()
+        m = (m * np.float32(0.9)).astype(np.float32) + (grad.float().numpy() * np.float32(1 - 0.9)).astype(np.float32)
+        codes, sb, g = G.quantize(m, mode="sr", four_over_six=True, seed=(5 + 104729 * s) & 0x7FFFFFFF)
+        st = opt.state[p]
+        assert np.array_equal(st["m4p"].cpu().numpy(), G.pack(codes))
+        assert np.array_equal(st["m4s"].view(torch.uint8).cpu().numpy(), sb) and float(st["m4g"].item()) == float(g)
+        m = G.dequantize(codes, sb, g).astype(np.float32)
+    assert opt.state_bits()["momentum"] == 4.5 * p.numel()
+
+
 @pytest.mark.parametrize("name,extra", [("balanced", {}), ("stateless", {}), ("muon", dict(block=32, ns_dtype="fp32"))])
 def test_presets_follow_the_reference_optimizer(name, extra):
     g = golden("presets")
