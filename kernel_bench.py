@@ -201,8 +201,35 @@ def swiglu():
         print(f"swiglu backward {M}x{I}: {t * 1e6:.0f} us, {10 * M * I / t / 1e9:.0f} GB/s", flush=True)
 
 
+def recipes():
+    """The general quantizer of the 128-rotation recipes (amax pass + quantization pass per call) and one linear
+    layer, forward + backward, under every FP4 recipe (65,536 tokens, 4096 -> 4096)."""
+    import bitlattice_b200 as bl
+    x = torch.randn(65536, 4096, device=DEV).to(torch.bfloat16)
+    for name, kw in [("rows rtn 4/6", dict(four_over_six=True)),
+                     ("rows eden rotated", dict(mode="eden", rotate=True, seed=1)),
+                     ("rows sr rotated", dict(mode="sr", rotate=True, seed=1)),
+                     ("transposed eden rotated", dict(mode="eden", rotate=True, seed=1, transpose=True, pow2=True))]:
+        t = timeit(lambda: _ops.nvfp4_quantize_general(x, blocked=True, **kw))
+        print(f"general quantizer 65536x4096 bf16 {name}: {t * 1e6:.0f} us, {x.numel() * 2 / t / 1e9:.0f} GB/s of input",
+              flush=True)
+    w = torch.nn.Parameter(bl.LatticeTensor.from_float(torch.randn(4096, 4096, device=DEV) * 0.02, "nvfp4",
+                                                       method="rtn", dtype=torch.bfloat16))
+    gy = (torch.randn(65536, 4096, device=DEV) * 1e-2).to(torch.bfloat16)
+    for name in bl.backend.FP4_RECIPES:
+        def step():
+            xi = x.detach().requires_grad_(True)
+            with bl.compute(bl.Compute("nvfp4", nvfp4=name)):
+                torch.nn.functional.linear(xi, w).backward(gy)
+            w.grad = None
+        t = timeit(step, reps=5)
+        print(f"linear 65536 x 4096 -> 4096 fwd+bwd, recipe {name}: {t * 1e3:.2f} ms, "
+              f"{6.0 * 65536 * 4096 * 4096 / t / 1e12:.0f} TFLOP/s", flush=True)
+    print("gemm error flag", _ops.gemm_status(0), flush=True)
+
+
 if __name__ == "__main__":
-    which = sys.argv[1:] or ["mma_peak", "gemm", "gemm32b", "quant", "update", "swiglu"]
+    which = sys.argv[1:] or ["mma_peak", "gemm", "gemm32b", "quant", "update", "swiglu", "recipes"]
     for name in which:
         {"gemm": gemm, "gemm32b": gemm32b, "mma_peak": mma_peak, "quant": quant, "update": update,
-         "swiglu": swiglu}[name]()
+         "swiglu": swiglu, "recipes": recipes}[name]()
