@@ -192,47 +192,99 @@ def update_many_scratch_bytes(shapes, direction: str, clip: float) -> int:
     return int(_C.lib().bl_update_many_scratch_bytes(n, rows, cols, _DIRECTION[direction], float(clip)))
 
 
+class UpdatePlan:
+    """The per-tensor arguments of ``lattice_update_many`` that do not change from step to step (shapes, offsets,
+    seeds, the weights' and the phase buffers' addresses), validated and marshalled once: a step then only fills in the
+    gradients' addresses and the step counters. ``items`` as for ``lattice_update_many`` (``grad`` / ``step`` are read
+    for validation only). The plan keeps the tensors alive; build a new one when a parameter's storage is replaced
+    (``stale`` tells)."""
+
+    def __init__(self, items, fmt, phase_bits: int):
+        if not _is_nvfp4(fmt):
+            raise RuntimeError("only NVFP4 tensors (no zero points) are built")
+        n = self.n = len(items)
+        self.phase_bits = phase_bits
+        self.gdtype = items[0]["grad"].dtype
+        for it in items:
+            _require(it["packed"], "packed", torch.uint8)
+            _require(it["scales"], "scales")
+            _require(it["global_scale"], "global_scale", torch.float32)
+            if phase_bits > 0:
+                _require(it["phase"], "phase", torch.uint8)
+        self.tensors = [(it["packed"], it["phase"] if phase_bits > 0 else None, it["scales"], it["global_scale"])
+                        for it in items]
+        self.numel = [int(it["rows"]) * int(it["cols"]) for it in items]
+        self.shapes = [(int(it["rows"]), int(it["cols"])) for it in items]
+        self.rows = (ctypes.c_int64 * n)(*[int(it["rows"]) for it in items])
+        self.cols = (ctypes.c_int64 * n)(*[int(it["cols"]) for it in items])
+        self.offset = (ctypes.c_uint64 * n)(*[int(it["offset"]) & 0xFFFFFFFFFFFFFFFF for it in items])
+        self.seed = (ctypes.c_uint32 * n)(*[int(it["seed"]) & 0xFFFFFFFF for it in items])
+        self.addr = [tuple(t.data_ptr() if t is not None else 0 for t in ts) for ts in self.tensors]
+        col = lambda k: (ctypes.c_void_p * n)(*[a[k] or None for a in self.addr])
+        self.packed, self.phase, self.scales, self.gs = col(0), (col(1) if phase_bits > 0 else None), col(2), col(3)
+        self.grad = (ctypes.c_void_p * n)()
+        self.step = (ctypes.c_uint32 * n)()
+        self.strat_j = (ctypes.c_int * n)()
+        self.device = items[0]["packed"]
+        self.scratch_need: dict = {}
+
+    def stale(self, tensors) -> bool:
+        """True when one of ``tensors`` (per parameter: packed, phase or None, scales, global_scale) is not the
+        storage the plan was built for."""
+        return any(tuple(t.data_ptr() if t is not None else 0 for t in ts) != a for ts, a in zip(tensors, self.addr))
+
+    def scratch_bytes(self, direction: str, clip: float) -> int:
+        key = (direction, float(clip))
+        need = self.scratch_need.get(key)
+        if need is None:
+            need = self.scratch_need[key] = update_many_scratch_bytes(self.shapes, direction, clip)
+        return need
+
+
 def lattice_update_many(items, fmt, *, lr: float, weight_decay: float, phase_bits: int, phase_cb: int, rounding: str,
                         strata: int, scale_rule: str, trust: float, trust_lr: float, direction: str, clip: float = 1.0,
-                        scratch: torch.Tensor | None = None) -> None:
+                        scratch: torch.Tensor | None = None, plan: UpdatePlan | None = None, grads=None,
+                        steps=None) -> None:
     """``lattice_update`` for many tensors of one parameter group in one library call: the library packs them into
     batches of up to 40 and runs each batch as one chain of launches (statistics, their reduction, the update), so
     small shards are not paced by launches. ``items``: dicts with packed, phase (or None), scales, global_scale, grad,
-    rows, cols, offset, seed, step; all gradients of one dtype, everything on one device."""
-    if not _is_nvfp4(fmt):
-        raise RuntimeError("only NVFP4 tensors (no zero points) are built")
+    rows, cols, offset, seed, step; all gradients of one dtype, everything on one device. With a ``plan``
+    (:class:`UpdatePlan`) ``items`` is ignored and only ``grads`` (contiguous tensors of the plan's gradient dtype)
+    and ``steps`` are read."""
     if direction not in _DIRECTION:
         raise RuntimeError(f"direction {direction!r} is outside this build (raw, sign, colnorm are built)")
-    n = len(items)
-    if n == 0:
-        return
-    gdtype = items[0]["grad"].dtype
-    for it in items:
-        _require(it["packed"], "packed", torch.uint8)
-        _require(it["scales"], "scales")
-        _require(it["global_scale"], "global_scale", torch.float32)
-        _require(it["grad"], "gradient", gdtype)
-        if gdtype not in _C.DTYPE or it["grad"].numel() != it["rows"] * it["cols"]:
-            raise RuntimeError("gradient: bf16, fp16 or fp32 with rows*cols elements")
-        if phase_bits > 0:
-            _require(it["phase"], "phase", torch.uint8)
-    dev = items[0]["packed"]
+    if plan is None:
+        if len(items) == 0:
+            return
+        plan = UpdatePlan(items, fmt, phase_bits)
+        grads = [it["grad"] for it in items]
+        steps = [it["step"] for it in items]
+    n = plan.n
+    gdtype = plan.gdtype
+    if gdtype not in _C.DTYPE:
+        raise RuntimeError("gradient: bf16, fp16 or fp32 with rows*cols elements")
+    grad, step, sj = plan.grad, plan.step, plan.strat_j
+    strat_k = 1
+    for i in range(n):
+        G = grads[i]
+        if G.dtype != gdtype or G.numel() != plan.numel[i] or not G.is_cuda or not G.is_contiguous():
+            raise RuntimeError("gradient: a contiguous CUDA tensor of the group's dtype with rows*cols elements")
+        grad[i] = G.data_ptr()
+        step[i] = int(steps[i]) & 0xFFFFFFFF
+        if rounding == "strat":
+            sj[i], strat_k = strat_args(rounding, steps[i], strata)
+    if rounding != "strat":
+        strat_k = strat_args(rounding, steps[0], strata)[1]
+    dev = plan.device
     if scratch is None:
-        scratch = _scratch_for(dev.device, update_many_scratch_bytes([(it["rows"], it["cols"]) for it in items],
-                                                                     direction, clip))
-    ptrs = lambda key: (ctypes.c_void_p * n)(*[(it[key].data_ptr() if it[key] is not None else None) for it in items])
-    i64 = lambda key: (ctypes.c_int64 * n)(*[int(it[key]) for it in items])
-    u64 = lambda key: (ctypes.c_uint64 * n)(*[int(it[key]) & 0xFFFFFFFFFFFFFFFF for it in items])
-    u32 = lambda key: (ctypes.c_uint32 * n)(*[int(it[key]) & 0xFFFFFFFF for it in items])
-    jk = [strat_args(rounding, it["step"], strata) for it in items]
-    sj = (ctypes.c_int * n)(*[j for j, _ in jk])
+        scratch = _scratch_for(dev.device, plan.scratch_bytes(direction, clip))
     launches = ctypes.c_int(0)
-    _C.call("bl_nvfp4_lattice_update_many", n, ptrs("packed"), ptrs("phase") if phase_bits > 0 else None,
-            ptrs("scales"), ptrs("global_scale"), ptrs("grad"), i64("rows"), i64("cols"), u64("offset"), u32("seed"),
-            u32("step"), sj, _C.DTYPE[gdtype], phase_bits, phase_cb, float(lr), float(1.0 - lr * weight_decay),
-            _ROUNDING[rounding], jk[0][1], _RULE[scale_rule], float(kappa(trust, trust_lr, lr)), _DIRECTION[direction],
-            float(clip), _C.ptr(scratch), scratch.numel() if scratch is not None else 0, _C.device_of(dev),
-            _C.stream_of(dev), ctypes.byref(launches))
+    _C.call("bl_nvfp4_lattice_update_many", n, plan.packed, plan.phase, plan.scales, plan.gs, grad, plan.rows,
+            plan.cols, plan.offset, plan.seed, step, sj, _C.DTYPE[gdtype], phase_bits, phase_cb, float(lr),
+            float(1.0 - lr * weight_decay), _ROUNDING[rounding], strat_k, _RULE[scale_rule],
+            float(kappa(trust, trust_lr, lr)), _DIRECTION[direction], float(clip), _C.ptr(scratch),
+            scratch.numel() if scratch is not None else 0, _C.device_of(dev), _C.stream_of(dev),
+            ctypes.byref(launches))
     _C.Counters.launches += launches.value
 
 

@@ -19,6 +19,7 @@ from __future__ import annotations
 
 import contextlib
 import itertools
+import os
 import weakref
 from collections import OrderedDict
 from dataclasses import astuple, dataclass
@@ -210,6 +211,22 @@ def _act_operand(x2: torch.Tensor, recipe: Fp4Recipe) -> Fp4Operand:
     return Fp4Operand(packed, scales, g, True)
 
 
+NVTX = bool(os.environ.get("BL_NVTX"))       # name the GEMMs and the update in profiler timelines (off by default)
+
+
+@contextlib.contextmanager
+def nvtx(name: str):
+    """An NVTX range around a piece of the hot path when BL_NVTX is set in the environment (else nothing)."""
+    if not NVTX:
+        yield
+        return
+    torch.cuda.nvtx.range_push(name)
+    try:
+        yield
+    finally:
+        torch.cuda.nvtx.range_pop()
+
+
 def fp4_mm(a: Fp4Operand, b: Fp4Operand, out_dtype: torch.dtype = torch.bfloat16,
            add_to: torch.Tensor | None = None) -> torch.Tensor:
     """A B^T for NVFP4 operands A [M, K], B [N, K] (K: multiple of 32), fp32 accumulation in tensor memory,
@@ -235,6 +252,7 @@ class _WeightOperands:
         self.limit = limit_bytes
         self.used = 0
         self.entries: OrderedDict = OrderedDict()      # (id(weight), kind) -> (version, weakref, operand, bytes)
+        self.kinds: dict = {}                           # id(weight) -> kinds present (drop() without a scan)
 
     def get(self, w, kind: str, make):
         key, version = (id(w), kind), getattr(w, "_bl_version", 0)
@@ -248,6 +266,7 @@ class _WeightOperands:
         operand = make()
         nbytes = sum(t.numel() * t.element_size() for t in operand if isinstance(t, torch.Tensor))
         self.entries[key] = (version, weakref.ref(w), operand, nbytes)
+        self.kinds.setdefault(key[0], set()).add(kind)
         self.used += nbytes
         while self.used > self.limit and len(self.entries) > 1:
             self._remove(next(iter(self.entries)))
@@ -255,13 +274,19 @@ class _WeightOperands:
 
     def _remove(self, key) -> None:
         self.used -= self.entries.pop(key)[3]
+        kinds = self.kinds.get(key[0])
+        if kinds is not None:
+            kinds.discard(key[1])
+            if not kinds:
+                del self.kinds[key[0]]
 
     def drop(self, w) -> None:
-        for key in [k for k in self.entries if k[0] == id(w)]:
-            self._remove(key)
+        for kind in tuple(self.kinds.get(id(w), ())):
+            self._remove((id(w), kind))
 
     def clear(self) -> None:
         self.entries.clear()
+        self.kinds.clear()
         self.used = 0
 
 
@@ -425,7 +450,8 @@ def fp4_forward_saving(x: torch.Tensor, w, bias, recipe: Fp4Recipe = Fp4Recipe()
     K = x.shape[-1]
     M = x.numel() // K
     xq, xt = _shared(x, recipe, "fwd+t", lambda: _input_operands(x, recipe))
-    y = fp4_mm(xq, weight_operand(w), x.dtype)[:M]
+    with nvtx("bl.fwd_gemm"):
+        y = fp4_mm(xq, weight_operand(w), x.dtype)[:M]
     if bias is not None:
         y += bias.to(y.dtype)
     return y.reshape(*x.shape[:-1], w.shape[0]), xt
@@ -439,9 +465,10 @@ def fp4_dgrad(gy: torch.Tensor, w, recipe: Fp4Recipe = Fp4Recipe(), add_to: torc
     g2 = gy.reshape(-1, N)
     g2p = _pad_rows(g2, 32).contiguous()
     gq = quantize_fp4(g2p, stochastic=True)
-    if add_to is not None:
-        return fp4_mm(gq, weight_t_operand(w), gy.dtype, add_to=add_to), g2p, gq
-    return fp4_mm(gq, weight_t_operand(w), gy.dtype)[:g2.shape[0]], g2p, gq
+    with nvtx("bl.dgrad_gemm"):
+        if add_to is not None:
+            return fp4_mm(gq, weight_t_operand(w), gy.dtype, add_to=add_to), g2p, gq
+        return fp4_mm(gq, weight_t_operand(w), gy.dtype)[:g2.shape[0]], g2p, gq
 
 
 def fp4_wgrad(g2p: torch.Tensor, gq: Fp4Operand | None, xt: Fp4Operand, w, recipe: Fp4Recipe = Fp4Recipe()):
@@ -451,7 +478,8 @@ def fp4_wgrad(g2p: torch.Tensor, gq: Fp4Operand | None, xt: Fp4Operand, w, recip
     bound = gq.global_scale * 4.0 if gq is not None else None
     gt = Fp4Operand(*_ops.quantize_nvfp4_t(g2p, _hadamard16(g2p.device, torch.float32), seed, 0, bound,
                                            blocked=True), True)
-    return fp4_mm(gt, xt, w.dtype)
+    with nvtx("bl.wgrad_gemm"):
+        return fp4_mm(gt, xt, w.dtype)
 
 
 def fp4_backward(gy: torch.Tensor, w, xt: Fp4Operand | None, need_x: bool, need_w: bool,

@@ -1270,8 +1270,56 @@ static EncodeTiledFn encode_tiled_fn() {
   return fn;
 }
 
+// Encoded tensor maps are a function of (address, shape, box) alone, so they are kept: a training step multiplies
+// the same operands (weights of a version, cached activations) and the same shapes at the same addresses again and
+// again, and the driver call costs more than the look-up. Direct-mapped, a few hundred KiB, one lock.
+struct MapKey {
+  const void* ptr;
+  int64_t rows, K;
+  int box, kind;
+  bool operator==(const MapKey& o) const {
+    return ptr == o.ptr && rows == o.rows && K == o.K && box == o.box && kind == o.kind;
+  }
+};
+
+struct MapSlot {
+  MapKey key;
+  CUtensorMap map;
+  bool used;
+};
+
+constexpr size_t kMapSlots = 2048;
+static MapSlot g_map_cache[kMapSlots];
+static std::mutex g_map_mutex;
+
+static size_t map_slot(const MapKey& k) {
+  uint64_t h = reinterpret_cast<uintptr_t>(k.ptr) * 0x9E3779B97F4A7C15ull;
+  h ^= static_cast<uint64_t>(k.rows) * 0xC2B2AE3D27D4EB4Full + static_cast<uint64_t>(k.K) * 0x165667B19E3779F9ull +
+       static_cast<uint64_t>(k.box * 4 + k.kind);
+  h ^= h >> 29;
+  return static_cast<size_t>(h % kMapSlots);
+}
+
+static bool cached_map(const MapKey& k, CUtensorMap* out) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  const MapSlot& s = g_map_cache[map_slot(k)];
+  if (!s.used || !(s.key == k)) return false;
+  *out = s.map;
+  return true;
+}
+
+static void keep_map(const MapKey& k, const CUtensorMap& m) {
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  MapSlot& s = g_map_cache[map_slot(k)];
+  s.key = k;
+  s.map = m;
+  s.used = true;
+}
+
 // [rows, K/2] bytes, box of 128 bytes x box_rows rows, 128-byte swizzle, zero fill outside the tensor
 static int make_operand_map(CUtensorMap* map, const uint8_t* codes, int64_t rows, int64_t K, int box_rows) {
+  const MapKey key{codes, rows, K, box_rows, 0};
+  if (cached_map(key, map)) return 0;
   EncodeTiledFn enc = encode_tiled_fn();
   BL_REQUIRE(enc != nullptr, "gemm: the CUDA driver does not provide cuTensorMapEncodeTiled");
   const cuuint64_t dims[2] = {static_cast<cuuint64_t>(K / 2), static_cast<cuuint64_t>(rows)};
@@ -1283,12 +1331,15 @@ static int make_operand_map(CUtensorMap* map, const uint8_t* codes, int64_t rows
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   BL_REQUIRE(rc == CUDA_SUCCESS, "gemm: cuTensorMapEncodeTiled failed with code %d (rows %lld, K %lld)", (int)rc,
              (long long)rows, (long long)K);
+  keep_map(key, *map);
   return 0;
 }
 
 // Blocked scales seen as [row blocks][k blocks][512 bytes]; one box is 4 k blocks of box_row_blocks row blocks, landing
 // in shared memory as consecutive 512-byte blobs. Blocks outside the tensor arrive as zeros.
 static int make_scale_map(CUtensorMap* map, const uint8_t* sf, int64_t rows, int64_t K, int box_row_blocks) {
+  const MapKey key{sf, rows, K, box_row_blocks, 1};
+  if (cached_map(key, map)) return 0;
   EncodeTiledFn enc = encode_tiled_fn();
   BL_REQUIRE(enc != nullptr, "gemm: the CUDA driver does not provide cuTensorMapEncodeTiled");
   const cuuint64_t nkb = static_cast<cuuint64_t>((K + 63) / 64), nrb = static_cast<cuuint64_t>((rows + 127) / 128);
@@ -1301,6 +1352,7 @@ static int make_scale_map(CUtensorMap* map, const uint8_t* sf, int64_t rows, int
                           CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   BL_REQUIRE(rc == CUDA_SUCCESS, "gemm: cuTensorMapEncodeTiled failed with code %d for scales (rows %lld, K %lld)", (int)rc,
              (long long)rows, (long long)K);
+  keep_map(key, *map);
   return 0;
 }
 

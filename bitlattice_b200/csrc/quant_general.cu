@@ -9,10 +9,10 @@
 //   4/6 error  per block: sequential sums over elements 4q .. 4q + 3, then (s0 + s1) + (s2 + s3)
 //   MS-EDEN    <x, x> and <x, x_rtn> per 128: sequential sums over 4 elements, then a pairwise tree (neighbours first)
 //
-// Thread mapping (not the reference's thread-per-block mapping): a warp owns one 128-element segment of an output row;
-// lane l holds elements 4l .. 4l + 3, so strides 1 and 2 of the rotation are in registers, strides 4 .. 64 are
-// shuffles over lane distances 1 .. 16, a 16-element block is four neighbouring lanes, and the warp writes 64
-// contiguous bytes of codes. A CTA covers 128 output columns x 64 output rows; for transposed output it first stages
+// Thread mapping: a lane owns one 16-element block, eight neighbouring lanes one 128-element segment of an output row,
+// a warp four rows' segments at a time. Strides 1 .. 8 of the rotation run in registers, strides 16 .. 64 are shuffles
+// over lane distances 1, 2, 4; block scales, four-over-six errors and stochastic draws need no exchange, the MS-EDEN
+// sums three shuffle steps. A CTA covers 128 output columns x 64 output rows; for transposed output it first stages
 // the 128 x 64 source tile (dense values, or NVFP4 codes decoded as (level * scale) * global) in shared memory.
 #include <type_traits>
 
@@ -53,10 +53,10 @@ __device__ __forceinline__ float general_global(const GenArgs& A) {
   return g;
 }
 
-// levels of the four codes in the low 16 bits of w
-__device__ __forceinline__ void e2m1_values4(uint32_t w, float out[4]) {
+// levels of the eight codes of w (element i in nibble i)
+__device__ __forceinline__ void e2m1_levels8(uint32_t w, float out[8]) {
 #pragma unroll
-  for (int k = 0; k < 2; ++k) {
+  for (int k = 0; k < 4; ++k) {
     uint32_t h2;
     asm("{\n\t.reg .b8 b;\n\tcvt.u8.u32 b, %1;\n\tcvt.rn.f16x2.e2m1x2 %0, b;\n\t}" : "=r"(h2) : "r"(w >> (8 * k)));
     const float2 f = __half22float2(*reinterpret_cast<const __half2*>(&h2));
@@ -65,9 +65,32 @@ __device__ __forceinline__ void e2m1_values4(uint32_t w, float out[4]) {
   }
 }
 
-// round-to-nearest codes (ties to the even code, saturating) of v[i] * inv, element i in nibble i
-__device__ __forceinline__ uint32_t e2m1_nearest4(const float v[4], float inv) {
-  return cvt_e2m1x2(v[1] * inv, v[0] * inv) | (cvt_e2m1x2(v[3] * inv, v[2] * inv) << 8);
+// round-to-nearest codes (ties to the even code, saturating) of v[i] * inv for a block of 16
+__device__ __forceinline__ uint2 e2m1_nearest16(const float v[16], float inv) {
+  float q[16];
+#pragma unroll
+  for (int i = 0; i < 16; i += 2) mul2(v[i], v[i + 1], inv, q[i], q[i + 1]);
+  return make_uint2(cvt_e2m1x8_merged(q), cvt_e2m1x8_merged(q + 8));
+}
+
+// error of a candidate: sum over the block of (level * t - v)^2 (or | |), four sequential sums over elements
+// 4q .. 4q + 3, then (s0 + s1) + (s2 + s3)
+__device__ __forceinline__ float candidate_error(const float v[16], uint2 codes, float t, bool mae) {
+  float d[16];
+  e2m1_levels8(codes.x, d);
+  e2m1_levels8(codes.y, d + 8);
+  float s[4];
+#pragma unroll
+  for (int q = 0; q < 4; ++q) {
+    float acc = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const float e = d[4 * q + i] * t - v[4 * q + i];
+      acc = acc + (mae ? fabsf(e) : e * e);
+    }
+    s[q] = acc;
+  }
+  return (s[0] + s[1]) + (s[2] + s[3]);
 }
 
 // stochastic rounding to E4M3 of a positive value (bitlattice/fp4ref.py:81-88)
@@ -85,24 +108,13 @@ __device__ __forceinline__ uint32_t e4m3_sr(float v, float u) {
   return u < p ? hb : b;
 }
 
-template <typename T>
-__device__ __forceinline__ void load4(const T* p, float v[4]) {
-  if constexpr (sizeof(T) == 4) {
-    const float4 a = *reinterpret_cast<const float4*>(p);
-    v[0] = a.x; v[1] = a.y; v[2] = a.z; v[3] = a.w;
-  } else {
-    const uint2 raw = *reinterpret_cast<const uint2*>(p);
-    const T* e = reinterpret_cast<const T*>(&raw);
-#pragma unroll
-    for (int i = 0; i < 4; ++i) v[i] = to_f<T>(e[i]);
-  }
-}
-
 // PASS 0: max |value| of the (rotated) output into A.amax[0] (zeroed by the host). PASS 1: codes and scales.
+// A warp works on four output rows at a time: lanes 8c .. 8c + 7 hold the eight 16-element blocks of row c's segment.
 template <typename T, int SRC, int PASS>
 __global__ void __launch_bounds__(kGenThreads) general_kernel(GenArgs A) {
   __shared__ float tile[SRC == kSrcRows ? 1 : 128 * 65];
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int sub = lane >> 3, blk = lane & 7;               // row of the warp's group of four, block of the segment
   const int64_t col0 = static_cast<int64_t>(blockIdx.x) * 128;         // first output column of the segment
   const int64_t row0 = static_cast<int64_t>(blockIdx.y) * kGenTileRows;  // first output row of the tile
 
@@ -143,74 +155,82 @@ __global__ void __launch_bounds__(kGenThreads) general_kernel(GenArgs A) {
     __syncthreads();
   }
 
-  const bool valid = col0 + 4 * lane < A.cols;             // cols is a multiple of 16: all four or none
+  const bool valid_col = col0 + 16 * blk < A.cols;         // cols is a multiple of 16: a whole block or none
   uint32_t neg = 0;                                        // bit i: the rotation negates element i of this lane
   if (A.rotate) {
 #pragma unroll
-    for (int i = 0; i < 4; ++i) neg |= (hash_uniform(static_cast<uint32_t>(4 * lane + i), A.rot_key) < 0.5f ? 1u : 0u) << i;
+    for (int i = 0; i < 16; ++i)
+      neg |= (hash_uniform(static_cast<uint32_t>(16 * blk + i), A.rot_key) < 0.5f ? 1u : 0u) << i;
   }
   const float g = PASS == 1 ? general_global(A) : 1.0f;
   if (PASS == 1 && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) A.out_global[0] = g;
   float wmax = 0.0f;
 
-  for (int j = 0; j < kGenTileRows / 8; ++j) {
-    const int rr = warp + 8 * j;
+  for (int j = 0; j < kGenTileRows / 32; ++j) {
+    const int rr = 4 * (warp + 8 * j) + sub;
     const int64_t r = row0 + rr;
-    if (r >= A.rows) break;                                // the same for every lane of the warp
-    float v[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+    if (row0 + 4 * (warp + 8 * j) >= A.rows) break;        // the same for every lane of the warp
+    const bool valid = valid_col && r < A.rows;
+    float v[16];
+#pragma unroll
+    for (int i = 0; i < 16; ++i) v[i] = 0.0f;
     if (valid) {
       if constexpr (SRC == kSrcRows) {
-        load4(static_cast<const T*>(A.x) + r * A.C + col0 + 4 * lane, v);
+        const T* p = static_cast<const T*>(A.x) + r * A.C + col0 + 16 * blk;
+        if ((A.C % 8) == 0) {
+          load8(p, v);
+          load8(p + 8, v + 8);
+        } else {
+#pragma unroll
+          for (int i = 0; i < 16; ++i) v[i] = to_f<T>(p[i]);
+        }
       } else {
 #pragma unroll
-        for (int i = 0; i < 4; ++i) v[i] = tile[(4 * lane + i) * 65 + rr];
+        for (int i = 0; i < 16; ++i) v[i] = tile[(16 * blk + i) * 65 + rr];
       }
     }
     if (A.rotate) {
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] = (neg >> i) & 1u ? -v[i] : v[i];
-      float a = v[0] + v[1], b = v[0] - v[1], c = v[2] + v[3], d = v[2] - v[3];        // stride 1
-      v[0] = a + c; v[2] = a - c; v[1] = b + d; v[3] = b - d;                          // stride 2
+      for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(__float_as_uint(v[i]) ^ (((neg >> i) & 1u) << 31));
 #pragma unroll
-      for (int m = 1; m < 32; m <<= 1) {                                               // strides 4 .. 64
+      for (int h = 1; h < 16; h <<= 1) {                                               // strides 1 .. 8
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float p = __shfl_xor_sync(0xffffffffu, v[i], m);
-          v[i] = (lane & m) ? p - v[i] : v[i] + p;
+        for (int i = 0; i < 16; ++i) {
+          if ((i & h) == 0) {
+            const float a = v[i], b = v[i + h];
+            v[i] = a + b;
+            v[i + h] = a - b;
+          }
         }
       }
 #pragma unroll
-      for (int i = 0; i < 4; ++i) v[i] *= kInvSqrt128;
+      for (int m = 1; m < 8; m <<= 1) {                                                // strides 16 .. 64
+        const float sgn = (blk & m) ? -1.0f : 1.0f;
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float p = __shfl_xor_sync(0xffffffffu, v[i], m);
+          v[i] = fmaf(v[i], sgn, p);                       // a + b below, a - b above: one rounding either way
+        }
+      }
+#pragma unroll
+      for (int i = 0; i < 16; i += 2) mul2(v[i], v[i + 1], kInvSqrt128, v[i], v[i + 1]);
     }
-    float am = fmaxf(fmaxf(fabsf(v[0]), fabsf(v[1])), fmaxf(fabsf(v[2]), fabsf(v[3])));
+    float am = 0.0f;
+#pragma unroll
+    for (int i = 0; i < 16; ++i) am = fmaxf(am, fabsf(v[i]));
     if constexpr (PASS == 0) {
       wmax = fmaxf(wmax, am);
     } else {
-      am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 1));
-      am = fmaxf(am, __shfl_xor_sync(0xffffffffu, am, 2));
       uint32_t sb = e4m3_encode(am / 6.0f / g);
       float t = e4m3_decode(sb) * g;
       float inv = t > 0.0f ? 1.0f / t : 0.0f;
-      uint32_t codes = e2m1_nearest4(v, inv);
+      uint2 codes = e2m1_nearest16(v, inv);
       if (A.fos) {
         const uint32_t sb4 = e4m3_encode(am / 4.0f / g);
         const float t4 = e4m3_decode(sb4) * g;
         const float inv4 = t4 > 0.0f ? 1.0f / t4 : 0.0f;
-        const uint32_t codes4 = e2m1_nearest4(v, inv4);
-        float d6[4], d4[4];
-        e2m1_values4(codes, d6);
-        e2m1_values4(codes4, d4);
-        float e6 = 0.0f, e4 = 0.0f;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          const float a6 = d6[i] * t - v[i], a4 = d4[i] * t4 - v[i];
-          e6 = e6 + (A.mae ? fabsf(a6) : a6 * a6);
-          e4 = e4 + (A.mae ? fabsf(a4) : a4 * a4);
-        }
-        e6 = e6 + __shfl_xor_sync(0xffffffffu, e6, 1);
-        e4 = e4 + __shfl_xor_sync(0xffffffffu, e4, 1);
-        e6 = e6 + __shfl_xor_sync(0xffffffffu, e6, 2);
-        e4 = e4 + __shfl_xor_sync(0xffffffffu, e4, 2);
+        const uint2 codes4 = e2m1_nearest16(v, inv4);
+        const float e6 = candidate_error(v, codes, t, A.mae != 0), e4 = candidate_error(v, codes4, t4, A.mae != 0);
         if (e4 < e6) {
           sb = sb4;
           t = t4;
@@ -220,41 +240,46 @@ __global__ void __launch_bounds__(kGenThreads) general_kernel(GenArgs A) {
       }
       if (A.mode == BL_Q_SR) {
         const uint32_t idx0 = static_cast<uint32_t>(static_cast<uint64_t>(r) * static_cast<uint64_t>(A.cols) +
-                                                    static_cast<uint64_t>(col0 + 4 * lane));
-        codes = 0;
-#pragma unroll
-        for (int i = 0; i < 4; ++i) codes |= e2m1_code_sr(v[i] * inv, hash_uniform(idx0 + i, A.key)) << (4 * i);
+                                                    static_cast<uint64_t>(col0 + 16 * blk));
+        codes = e2m1_sr16(v, inv, A.key, idx0);
       } else if (A.mode == BL_Q_EDEN) {
-        float d[4];
-        e2m1_values4(codes, d);
-        float xx = 0.0f, xr = 0.0f;
+        float d[16];
+        e2m1_levels8(codes.x, d);
+        e2m1_levels8(codes.y, d + 8);
+        float sx[4], sr[4];
 #pragma unroll
-        for (int i = 0; i < 4; ++i) {
-          xx = xx + v[i] * v[i];
-          xr = xr + v[i] * (d[i] * t);
+        for (int q = 0; q < 4; ++q) {
+          float ax = 0.0f, ar = 0.0f;
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            ax = ax + v[4 * q + i] * v[4 * q + i];
+            ar = ar + v[4 * q + i] * (d[4 * q + i] * t);
+          }
+          sx[q] = ax;
+          sr[q] = ar;
         }
+        float xx = (sx[0] + sx[1]) + (sx[2] + sx[3]), xr = (sr[0] + sr[1]) + (sr[2] + sr[3]);
 #pragma unroll
-        for (int m = 1; m < 32; m <<= 1) {
+        for (int m = 1; m < 8; m <<= 1) {
           xx = xx + __shfl_xor_sync(0xffffffffu, xx, m);
           xr = xr + __shfl_xor_sync(0xffffffffu, xr, m);
         }
         const float S = xr != 0.0f ? xx / xr : 1.0f;
         const uint32_t block = static_cast<uint32_t>(static_cast<uint64_t>(r) * static_cast<uint64_t>(A.cols / 16) +
-                                                     static_cast<uint64_t>((col0 + 4 * lane) / 16));
+                                                     static_cast<uint64_t>((col0 + 16 * blk) / 16));
         sb = e4m3_sr(e4m3_decode(sb) * S, hash_uniform(block, A.eden_key));
       }
       if (valid) {
-        codes = e2m1_drop_negative_zero(codes) & 0xFFFFu;
-        reinterpret_cast<uint16_t*>(A.codes + r * (A.cols / 2) + col0 / 2)[lane] = static_cast<uint16_t>(codes);
-        if ((lane & 3) == 0) {
-          const int64_t c16 = (col0 + 4 * lane) / 16, cols16 = A.cols / 16;
-          int64_t at = r * cols16 + c16;
-          if (A.layout != BL_SF_ROWMAJOR) {
-            const int64_t nc = (cols16 + 3) >> 2;
-            at = ((r >> 7) * nc + (c16 >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (c16 & 3);
-          }
-          A.scales[at] = static_cast<uint8_t>(sb);
+        codes.x = e2m1_drop_negative_zero(codes.x);
+        codes.y = e2m1_drop_negative_zero(codes.y);
+        *reinterpret_cast<uint2*>(A.codes + r * (A.cols / 2) + (col0 + 16 * blk) / 2) = codes;
+        const int64_t c16 = (col0 + 16 * blk) / 16, cols16 = A.cols / 16;
+        int64_t at = r * cols16 + c16;
+        if (A.layout != BL_SF_ROWMAJOR) {
+          const int64_t nc = (cols16 + 3) >> 2;
+          at = ((r >> 7) * nc + (c16 >> 2)) * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4 + (c16 & 3);
         }
+        A.scales[at] = static_cast<uint8_t>(sb);
       }
     }
   }

@@ -291,15 +291,14 @@ __device__ __forceinline__ float level_gap(float w, bool up) {
 __device__ __forceinline__ float rcp_pow2(float x) { return __uint_as_float(0x7F000000u - __float_as_uint(x)); }
 
 constexpr float kMagic = 12582912.0f;     // 1.5 * 2^23: adding it leaves the integer part in the low mantissa bits
-constexpr uint32_t kMagicBits = 0x4B400000u;
 
 // Shared-memory tables of a CTA:
-//   lutA / lutL [16 << PCB]  level a and latent value by (code nibble | phase container << 4)
+//   lutAL [16 << PCB]        (level a, latent value) by (code nibble | phase container << 4)
 //   plut [16]                by code nibble: the level w, half / (half the distance to the next level above / below)
 //                            -- 0 at the ends of the lattice -- and the code of the next level above: (t - w) times
 //                            one of the two factors is the phase coordinate of a target t whose nearest level is w
 template <int PCB>
-__device__ __forceinline__ void build_tables(float* lutA, float* lutL, float4* plut, int pb, int tid) {
+__device__ __forceinline__ void build_tables(float2* lutAL, float4* plut, int pb, int tid, float4* plut24 = nullptr) {
   const float inv_half = 1.0f / static_cast<float>(1 << (pb > 0 ? pb - 1 : 0));
   const int sh = 32 - pb;
   for (int e = tid; e < (16 << PCB); e += kThreads) {
@@ -312,8 +311,7 @@ __device__ __forceinline__ void build_tables(float* lutA, float* lutL, float4* p
       const float lo = level_of_rank(max(rk - 1, 0)), hi = level_of_rank(min(rk + 1, 14));
       lam = c < 0.0f ? av + c * (av - lo) * 0.5f : av + c * (hi - av) * 0.5f;
     }
-    lutA[e] = av;
-    lutL[e] = lam;
+    lutAL[e] = make_float2(av, lam);
   }
   if (tid < 16) {
     const int rk = rank_of_code(tid);
@@ -322,6 +320,9 @@ __device__ __forceinline__ void build_tables(float* lutA, float* lutL, float4* p
     const float wu = rk < 14 ? level_of_rank(rk + 1) : w, wd = rk > 0 ? level_of_rank(rk - 1) : w;
     const float su = rk < 14 ? hf / ((wu - w) * 0.5f) : 0.0f, sd = rk > 0 ? hf / ((w - wd) * 0.5f) : 0.0f;
     plut[tid] = make_float4(w, su, sd, __uint_as_float(code_of_rank(min(rk + 1, 14))));
+    // the same with the two factors times 2^24 (powers of two: exact): the phase coordinate in 2^-24 fixed point
+    if (plut24) plut24[tid] = make_float4(w, su * 16777216.0f, sd * 16777216.0f,
+                                          __uint_as_float(code_of_rank(min(rk + 1, 14))));
   }
 }
 
@@ -341,7 +342,7 @@ __device__ __forceinline__ float draw_u(int mode, uint32_t idx, uint32_t key, fl
 template <int PCB, int DIR, typename GT>
 static __device__ __noinline__ void update_group_general(const TensorDesc& T, int64_t r, int64_t cg,
                                                          const float* __restrict__ denom, float div, bool use_div,
-                                                         const float* lutA, const float* lutL, const float4* plut,
+                                                         const float2* lutAL, const float4* plut,
                                                          const StepParams& P) {
   using PW = typename PhaseWord<PCB>::type;
   const int64_t cols = T.cols;
@@ -370,7 +371,8 @@ static __device__ __noinline__ void update_group_general(const TensorDesc& T, in
   for (int i = 0; i < 16; ++i) {
     const uint32_t code = ((i < 8 ? cw.x : cw.y) >> (4 * (i & 7))) & 15u;
     const uint32_t li = code | (phase_raw<PCB>(pw, i) << 4);
-    const float a = lutA[li], lam = lutL[li];
+    const float2 al = lutAL[li];
+    const float a = al.x, lam = al.y;
     float d;
     if (DIR == 2 && !use_div) {
       d = gv[i] > 0.0f ? inv_s : (gv[i] < 0.0f ? -inv_s : 0.0f);        // (+-1) / s_old
@@ -507,10 +509,10 @@ template <int PCB, int DIR, typename GT, bool FAST>
 __global__ void __launch_bounds__(kThreads, 2) update_kernel(const __grid_constant__ Batch B, unsigned char* __restrict__ scratch, int has_stats,
                                                             StepParams P) {
   using PW = typename PhaseWord<PCB>::type;
-  __shared__ float lutA[16 << PCB];
-  __shared__ float lutL[16 << PCB];
+  __shared__ float2 lutAL[16 << PCB];                       // (level, latent) pairs: one load per element
   __shared__ float4 plut[16];
-  build_tables<PCB>(lutA, lutL, plut, P.pb, threadIdx.x);
+  __shared__ float4 plut24[FAST ? 16 : 1];
+  build_tables<PCB>(lutAL, plut, P.pb, threadIdx.x, FAST ? plut24 : nullptr);
   __syncthreads();
 
   int ti = 0;
@@ -541,7 +543,7 @@ __global__ void __launch_bounds__(kThreads, 2) update_kernel(const __grid_consta
 
   if constexpr (!FAST) {
     for (int64_t r = row_first; r < rows; r += row_step)
-      update_group_general<PCB, DIR, GT>(T, r, cg, denom, div, use_div, lutA, lutL, plut, P);
+      update_group_general<PCB, DIR, GT>(T, r, cg, denom, div, use_div, lutAL, plut, P);
     return;
   } else {
     const float gs = T.gs[0];
@@ -549,7 +551,7 @@ __global__ void __launch_bounds__(kThreads, 2) update_kernel(const __grid_consta
     const GT* grad = static_cast<const GT*>(T.grad);
     const int64_t code_stride = cols / 2, phase_stride = cols * PCB / 8, scale_stride = cols / 16;
     const uint32_t pmask = (1u << P.pb) - 1u;
-    const uint32_t carry_bits = kMagicBits + (1u << (P.pb - 1));
+    const int half_i = 1 << (P.pb - 1);
     const bool fit = P.rule != BL_RULE_FIXED, latent = P.rule == BL_RULE_FIT_LATENT;
     const bool decay_one = P.decay == 1.0f;                   // no weight decay: the products by it are exact copies
     const f32x2 ndiv2 = pk(-div, -div), rdiv2 = pk(__frcp_rn(div), __frcp_rn(div));
@@ -625,7 +627,8 @@ __global__ void __launch_bounds__(kThreads, 2) update_kernel(const __grid_consta
           ia = ((cw.x >> (4 * i)) & 15u) | (phase_raw<PCB>(pw, i) << 4);
           ib = ((cw.y >> (4 * i)) & 15u) | (phase_raw<PCB>(pw, i + 8) << 4);
         }
-        const float a0 = lutA[ia], a1 = lutA[ib], l0 = lutL[ia], l1 = lutL[ib];
+        const float2 al0 = lutAL[ia], al1 = lutAL[ib];
+        const float a0 = al0.x, a1 = al1.x, l0 = al0.y, l1 = al1.y;
         // Products that feed a sum are scalar (__fmul_rn is never contracted; a packed product followed by a packed
         // sum would be turned into one fused multiply-add, with one rounding instead of the reference's two).
         float nl0, nl1;                                          // -(lr * d) of the pair
@@ -683,7 +686,7 @@ __global__ void __launch_bounds__(kThreads, 2) update_kernel(const __grid_consta
       }
       ok = ok && s_new <= 4.0f * s_old && s_old <= 4.0f * s_new;
       if (!ok) {                                                // rare: values outside the unchecked divisions' range
-        update_group_general<PCB, DIR, GT>(T, r, cg, denom, div, use_div, lutA, lutL, plut, P);
+        update_group_general<PCB, DIR, GT>(T, r, cg, denom, div, use_div, lutAL, plut, P);
         continue;
       }
       T.scales_out[r * scale_stride + cg] = static_cast<uint8_t>(sb_new);
@@ -698,28 +701,28 @@ __global__ void __launch_bounds__(kThreads, 2) update_kernel(const __grid_consta
       for (int i = 0; i < 8; ++i) {
         float tv[2];
         upk(div2p(mul2p(tau2[i], sold2), nsnew2, rsnew2), tv[0], tv[1]);
-        tv[0] = fminf(fmaxf(tv[0], -6.0f), 6.0f);
-        tv[1] = fminf(fmaxf(tv[1], -6.0f), 6.0f);
-        // nearest levels of the pair through the hardware conversion (ties to even: see the notes above)
+        // nearest levels of the pair through the hardware conversion (ties to even: see the notes above). It
+        // saturates, and beyond the last level the table's factor is 0, so a target outside [-6, 6] needs no clamp
+        // (the range check has made it finite): its phase coordinate is 0 either way.
         const uint32_t near2 = cvt_e2m1x2(tv[1], tv[0]);
 #pragma unroll
         for (int e = 0; e < 2; ++e) {
           const float t = tv[e];
           const uint32_t nib = e == 0 ? (near2 & 15u) : (near2 >> 4);
-          const float4 L = plut[nib];
-          const float q = (t - L.x) * (t < L.x ? L.z : L.y);     // phase coordinate times half; exact scaling
-          const float flm = __fadd_rd(q, kMagic);                // kMagic + floor(q), exact
-          const float flo = flm - kMagic;
+          const float4 L = plut24[nib];
+          // phase coordinate times half, in 2^-24 fixed point (exact scaling; |q| <= 64, so it fits 31 bits); the
+          // draw n = hash >> 8 rounds up iff n * 2^-24 < frac(q), i.e. iff n < ceil(frac(q) * 2^24): the carry of
+          // adding 2^24 - 1 - n to ceil(q * 2^24). k = floor(q) + carry, two's complement.
+          const int q24 = __float2int_ru((t - L.x) * (t < L.x ? L.z : L.y));
           uint32_t h = h0 + static_cast<uint32_t>(i + 8 * e) * 0x27D4EB2Fu;
           h = (h ^ (h >> 16)) * 0x7FEB352Du;
           h = (h ^ (h >> 15)) * 0x846CA68Bu;
-          h ^= h >> 16;
-          const float u = static_cast<float>(h >> 8) * 5.9604644775390625e-08f;
-          const uint32_t k = __float_as_uint(flm) + (u < q - flo ? 1u : 0u);   // floor(q) + carry-in, two's complement
-          const uint32_t code = k == carry_bits ? __float_as_uint(L.w) : nib;  // +half: the level above, phase -half
+          h = ~(h ^ (h >> 16));
+          const int k = (q24 + static_cast<int>(h >> 8)) >> 24;
+          const uint32_t code = k == half_i ? __float_as_uint(L.w) : nib;      // +half: the level above, phase -half
           if (e == 0) cout.x += code << (4 * i);
           else cout.y += code << (4 * i);
-          phase_put<PCB>(pout, i + 8 * e, k & pmask);
+          phase_put<PCB>(pout, i + 8 * e, static_cast<uint32_t>(k) & pmask);
         }
       }
       cout.x = e2m1_drop_negative_zero(cout.x);

@@ -33,6 +33,7 @@ from typing import Any
 import torch
 
 from .. import _ops
+from ..backend import nvtx as _nvtx
 from . import directions as D_
 from ..packing import packed_cols
 from ..tensor import LatticeTensor
@@ -132,6 +133,7 @@ class Lattice(torch.optim.Optimizer):
         self.overlap = bool(overlap)
         self._update_streams: dict = {}
         self._scratch: dict = {}
+        self._plans: dict = {}            # (phase bits, ids of a batch of parameters) -> _ops.UpdatePlan
         self._gemm_flags: dict = {}                 # device -> (pinned int32 [1], event after its last async copy)
         self._gens: dict = {}                       # device -> torch.Generator of the bf16 / int8 momentum rounding
         self._pid = {}
@@ -300,30 +302,39 @@ class Lattice(torch.optim.Optimizer):
     def _update_many(self, ps, g: dict) -> None:
         bits = g["phase_bits"]
         cb = _ops.phase_container(bits)
-        items = []
+        kind = self._kind(ps[0], g)
+        state, invalidate = self.state, self._invalidate
+        steps, grads, tensors = [], [], []
         for p in ps:
-            self._invalidate(p)
-            st = self.state[p]
-            st["step"] = st.get("step", 0) + 1
-            rows, cols = p.rows, p.cols
+            invalidate(p)
+            st = state[p]
+            step = st["step"] = st.get("step", 0) + 1
+            steps.append(step)
             if bits and "phase" not in st:
-                st["phase"] = torch.zeros(rows, packed_cols(cols, cb), dtype=torch.uint8, device=p.packed.device)
-            items.append(dict(packed=p.packed, phase=st.get("phase") if bits else None, scales=p.scales,
-                              global_scale=p.global_scale, grad=p.grad.reshape(rows, cols), rows=rows, cols=cols,
-                              offset=int(getattr(p, "_bl_row_offset", 0)) * cols,
-                              seed=(self.seed + 7919 * self._pid[p]) & 0xFFFFFFFF, step=st["step"]))
+                st["phase"] = torch.zeros(p.rows, packed_cols(p.cols, cb), dtype=torch.uint8, device=p.packed.device)
+            grads.append(p.grad)
+            tensors.append((p.packed, st["phase"] if bits else None, p.scales, p.global_scale))
+        # shapes, offsets, seeds and the weights' addresses are marshalled once per set of parameters
+        key = (bits, tuple(map(id, ps)))
+        plan = self._plans.get(key)
+        if plan is None or plan.gdtype != grads[0].dtype or plan.stale(tensors):
+            items = [dict(packed=t[0], phase=t[1], scales=t[2], global_scale=t[3], grad=G, rows=p.rows, cols=p.cols,
+                          offset=int(getattr(p, "_bl_row_offset", 0)) * p.cols,
+                          seed=(self.seed + 7919 * self._pid[p]) & 0xFFFFFFFF, step=s)
+                     for p, t, G, s in zip(ps, tensors, grads, steps)]
+            plan = self._plans[key] = _ops.UpdatePlan(items, ps[0].fmt, bits)
         scratch = None
         if self.overlap:                             # updates that run beside the caller's stream: a buffer of their own
-            need = _ops.update_many_scratch_bytes([(it["rows"], it["cols"]) for it in items], self._kind(ps[0], g),
-                                                  g["clip"])
+            need = plan.scratch_bytes(kind, g["clip"])
             dev = ps[0].device
             scratch = self._scratch.get(dev)
             if need and (scratch is None or scratch.numel() < need):
                 scratch = self._scratch[dev] = torch.empty(need, dtype=torch.uint8, device=dev)
-        _ops.lattice_update_many(items, ps[0].fmt, lr=g["lr"], weight_decay=g["weight_decay"], phase_bits=bits,
-                                 phase_cb=cb, rounding=g["rounding"], strata=g["strata"], scale_rule=g["scale_rule"],
-                                 trust=g["trust"], trust_lr=g["trust_lr"], direction=self._kind(ps[0], g),
-                                 clip=g["clip"], scratch=scratch)
+        with _nvtx("bl.lattice_update"):
+            _ops.lattice_update_many(None, ps[0].fmt, lr=g["lr"], weight_decay=g["weight_decay"], phase_bits=bits,
+                                     phase_cb=cb, rounding=g["rounding"], strata=g["strata"], scale_rule=g["scale_rule"],
+                                     trust=g["trust"], trust_lr=g["trust_lr"], direction=kind, clip=g["clip"],
+                                     scratch=scratch, plan=plan, grads=grads, steps=steps)
 
     @contextlib.contextmanager
     def accumulate(self):
@@ -397,9 +408,10 @@ class Lattice(torch.optim.Optimizer):
             scratch = self._scratch.get(p.device)
             if need and (scratch is None or scratch.numel() < need):
                 scratch = self._scratch[p.device] = torch.empty(need, dtype=torch.uint8, device=p.device)
-        _ops.lattice_update(p.packed, st.get("phase") if bits else None, p.scales, p.global_scale, None,
-                            G2.contiguous(), p.fmt, rows, cols, direction=kind, clip=g["clip"], scratch=scratch,
-                            **common)
+        with _nvtx("bl.lattice_update"):
+            _ops.lattice_update(p.packed, st.get("phase") if bits else None, p.scales, p.global_scale, None,
+                                G2.contiguous(), p.fmt, rows, cols, direction=kind, clip=g["clip"], scratch=scratch,
+                                **common)
 
     def state_bits(self) -> dict[str, float]:
         """Logical optimizer state in bits, by component (phase and, with momentum='fp32', the fp32 average)."""
