@@ -84,6 +84,9 @@ def parse():
                     help="exchange pattern of the N-sharded weights at N > 1")
     ap.add_argument("--overlap", type=int, default=1, choices=[0, 1],
                     help="1: the optimizer issues its updates on a side stream (Lattice(overlap=True)); 0: in line")
+    ap.add_argument("--hook-batch", type=int, default=7,
+                    help="gradients the optimizer's backward hooks collect before their updates go out as one batch "
+                         "(Lattice(hook_batch=...)); 7 = the projections of one layer, 1 = every parameter on its own")
     ap.add_argument("--kernel-summary", default=None, metavar="FILE",
                     help="after the measurements, run 2 more steps under torch.profiler on rank 0 and write per-kernel "
                          "launch counts and device time (text) to FILE")
@@ -322,7 +325,7 @@ def run_ours(a):
             p = torch.nn.Parameter(w)
             params.append(p)
             meta.append((name, N, K))
-    opt = bl.Lattice(params, fused_backward=True, overlap=bool(a.overlap), **OPT)
+    opt = bl.Lattice(params, fused_backward=True, overlap=bool(a.overlap), hook_batch=a.hook_batch, **OPT)
     flops = sum(6.0 * M * N * K for _, N, K in meta)
     weights = sum(N * K for _, N, K in meta)
     group = dist.group.WORLD if world > 1 else None
@@ -563,7 +566,8 @@ def run_ours(a):
                    if world > 1 else None,
                    "l2": "inputs larger than L2 (weights, activations and gradients of a step exceed 126 MB)",
                    "host": "one Python thread per rank (autograd multithreading off)",
-                   "updates": "side stream (overlap=True)" if a.overlap else "in line"},
+                   "updates": ("side stream (overlap=True)" if a.overlap else "in line") +
+                              (f", issued {a.hook_batch} parameters at a time" if a.hook_batch > 1 else "")},
         "e2e": {"value": flops / (res["e2e_secs"] / res["e2e_steps"]) / 1e12, "unit": "TFLOP/s",
                 "h2d_bytes_per_step": res["h2d_bytes"], "d2h_bytes_per_step": 4, "steps": res["e2e_steps"]},
         "gpu_launches": res["launches"],

@@ -52,7 +52,7 @@ _SIGNATURES = {
                                             _c.c_int, _P]),
     "bl_nvfp4_quantize_general": (_c.c_int, [_P, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
                                              _c.c_int, _c.c_int64, _c.c_int64, _P, _c.c_int, _P, _P, _P, _P, _c.c_int,
-                                             _P, _P, _c.c_int, _P]),
+                                             _P, _P, _P, _c.c_int, _P]),
     "bl_fp4_fold_scales": (_c.c_int, [_P, _c.c_int64, _c.c_int64, _P, _P, _c.c_int, _P, _P, _c.c_int, _P]),
     "bl_nvfp4_quantize_t": (_c.c_int, [_P, _c.c_int, _c.c_int64, _c.c_int64, _P, _c.c_int64, _c.c_uint32, _P, _P, _P,
                                        _P, _P, _c.c_int, _c.c_int, _P]),

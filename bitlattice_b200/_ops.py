@@ -372,13 +372,14 @@ Q_MODES = {"rtn": 0, "sr": 1, "eden": 2}
 def nvfp4_quantize_general(x: torch.Tensor, *, transpose: bool = False, mode: str = "rtn", four_over_six: bool = False,
                            select: str = "mse", rotate: bool = False, seed: int = 0, rotate_seed: int = -1,
                            given: torch.Tensor | None = None, pow2: bool = False, w_scales: torch.Tensor | None = None,
-                           w_global: torch.Tensor | None = None, blocked: bool = False):
+                           w_global: torch.Tensor | None = None, blocked: bool = False,
+                           amax_out: torch.Tensor | None = None):
     """The general quantizer of the 128-rotation recipes (reference: torch.ops.bitlattice.nvfp4_quantize; Python twin
     bitlattice/fp4ref.py:103-150): x [R, C] dense, or the packed codes of an NVFP4 matrix with ``w_scales`` /
     ``w_global`` (transposed only) -> (packed, scales, global [1]) of x or x^T; ``mode`` 'rtn' | 'sr' | 'eden';
     ``rotate``: randomized 128-point Hadamard rotation along the quantized dimension with ``rotate_seed`` (< 0:
     ``seed``); ``given``: the per-tensor scale to use; ``pow2``: the computed per-tensor scale rounded up to a power
-    of two."""
+    of two; ``amax_out`` fp32 [1]: receives max|rotated x| (given scale or not)."""
     _require(x, "x")
     if x.dim() != 2:
         raise RuntimeError("x must be a contiguous 2-D CUDA tensor")
@@ -407,7 +408,9 @@ def nvfp4_quantize_general(x: torch.Tensor, *, transpose: bool = False, mode: st
             1 if select == "mae" else 0, int(rotate), int(seed), int(rotate_seed),
             _C.ptr(given) if given is not None else None, int(pow2),
             _C.ptr(_bytes(w_scales)) if packed_in else None, _C.ptr(w_global) if packed_in else None, _C.ptr(packed),
-            _C.ptr(scales), int(blocked), _C.ptr(out), _C.ptr(out[1:]), _C.device_of(x), _C.stream_of(x))
+            _C.ptr(scales), int(blocked), _C.ptr(out), _C.ptr(out[1:]),
+            _C.ptr(_require(amax_out, "amax_out", torch.float32)) if amax_out is not None else None,
+            _C.device_of(x), _C.stream_of(x))
     return packed, scales if blocked else scales.view(torch.float8_e4m3fn), out[:1]
 
 

@@ -11,8 +11,7 @@ micro-batch, folded and multiplied in one GEMM). Where the reference calls ``tor
 ``torch._scaled_mm`` (cuBLASLt), this module calls the kernels of ``libbitlattice_b200.so``; block scales are produced
 directly in the GEMM's tiled layout and the per-tensor scales are applied in the GEMM epilogue.
 
-Not built: delayed per-tensor scales (``scale_source='delayed'``), seeds mixed with a device epoch for CUDA-graph
-replay, MXFP8. Asking for them raises. The reference's one-read kernel for both layouts of an operand
+Not built: seeds mixed with a device epoch for CUDA-graph replay, MXFP8. Asking for them raises. The reference's one-read kernel for both layouts of an operand
 (``nvfp4_quantize2``) is two calls of the general quantizer here: same results, one more read.
 """
 from __future__ import annotations
@@ -53,8 +52,11 @@ class Fp4Recipe:
                                         once per weight version (round to nearest, one rotation per version)
     dgrad_scale      'current' | 'bound'   cached W^T per-tensor scale: from an amax pass over the rotated weight, or
                                         the bound sqrt(128) * W.global_scale
-    scale_source     'current'          ('delayed' is not built)
-    scale_margin     float              kept for the reference's signature
+    scale_source     'current' | 'delayed'   per-tensor scales from an amax pass over the operand (exact), or from
+                                        the amax the previous call of the same layer saw (times scale_margin; no
+                                        extra pass; values beyond the range saturate). Applies to the operands of
+                                        the 128-rotation recipes; the first call of a layer is exact
+    scale_margin     float              headroom of delayed scales
     """
 
     activations: str = "rtn"
@@ -86,9 +88,7 @@ class Fp4Recipe:
         if self.dgrad_scale == "bound" and not (self.dgrad_weight == "cached" and self.rotate_dgrad
                                                 and self.rotation == 128):
             raise ValueError("dgrad_scale='bound' needs cached weights and the 128-element dgrad rotation")
-        if self.scale_source == "delayed":
-            raise ValueError("delayed per-tensor scales (scale_source='delayed') are not built")
-        if self.scale_source != "current":
+        if self.scale_source not in ("current", "delayed"):
             raise ValueError("scale_source must be 'current' or 'delayed'")
         if not self.scale_margin >= 1.0:
             raise ValueError("scale_margin must be >= 1")
@@ -115,6 +115,8 @@ FP4_RECIPES: dict[str, Fp4Recipe] = {
                               backward_4over6=True),
     "quartet2_fast": Fp4Recipe(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True,
                                dgrad_weight="cached"),
+    "quartet2_delayed": Fp4Recipe(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True,
+                                  dgrad_weight="cached", scale_source="delayed"),
     "quartet2_bound": Fp4Recipe(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True,
                                 dgrad_weight="cached", dgrad_scale="bound"),
 }
@@ -123,8 +125,6 @@ FP4_RECIPES: dict[str, Fp4Recipe] = {
 def as_recipe(r) -> Fp4Recipe:
     if isinstance(r, Fp4Recipe):
         return r
-    if r == "quartet2_delayed":
-        raise ValueError("FP4 recipe 'quartet2_delayed' (delayed per-tensor scales) is not built")
     if r not in FP4_RECIPES:
         raise ValueError(f"unknown FP4 recipe {r!r}; built: {sorted(FP4_RECIPES)}")
     return FP4_RECIPES[r]
@@ -365,7 +365,7 @@ def _pad_to(recipe: Fp4Recipe) -> int:
 
 def _q(x2: torch.Tensor | None, *, transpose: bool = False, mode: str = "rtn", four_over_six: bool = False,
        recipe: Fp4Recipe | None = None, rotate_seed: int = -1, seed: int = 0, w=None, pow2: bool = False,
-       given: torch.Tensor | None = None) -> Fp4Operand:
+       given: torch.Tensor | None = None, amax_out: torch.Tensor | None = None) -> Fp4Operand:
     """NVFP4 operand from the general quantizer: rows of x2 (or of x2^T), optionally rotated (128) with
     ``rotate_seed``; ``w``: an NVFP4 weight given by its codes (transposed re-quantization); ``pow2``: per-tensor scale
     rounded up to a power of two (reference: bitlattice/backend.py:398-416)."""
@@ -380,8 +380,50 @@ def _q(x2: torch.Tensor | None, *, transpose: bool = False, mode: str = "rtn", f
     else:
         packed, scales, g = _ops.nvfp4_quantize_general(
             x2, transpose=transpose, mode=mode, four_over_six=four_over_six, select=select, rotate=rot, seed=seed,
-            rotate_seed=rotate_seed if rot else -1, given=given, pow2=pow2, blocked=True)
+            rotate_seed=rotate_seed if rot else -1, given=given, pow2=pow2, blocked=True, amax_out=amax_out)
     return Fp4Operand(packed, scales, g, True, rotate_seed)
+
+
+def _site(w, role: str) -> dict:
+    """Per-weight state of an operand site (delayed scales): the amax its row and column operands saw last."""
+    sites = w.__dict__.setdefault("_bl_sites", {})
+    return sites.setdefault(role, {})
+
+
+def _q2(x2: torch.Tensor, row: dict | None, col: dict | None, recipe: Fp4Recipe, site: dict | None = None):
+    """Row and column (x2^T) operands of x2; ``row`` / ``col``: keyword arguments of ``_q`` for that side, or None.
+    With ``scale_source='delayed'`` and a ``site`` the per-tensor scales come from the amax the site's previous call
+    saw, times the margin (the first call, and a side first used later, are exact), and the amax seen now is kept
+    (reference: bitlattice/backend.py:419-443; there one kernel makes both layouts from one read, here the general
+    quantizer runs once per side)."""
+    sides = (row, col)
+    on = (row is not None, col is not None)
+    given = [None, None]
+    seen = None
+    if recipe.scale_source == "delayed" and site is not None:
+        hist, known = site.get("amax"), site.get("known", (False, False))
+        if hist is not None and all(known[i] for i in range(2) if on[i]):
+            for i in range(2):
+                if on[i]:
+                    f = recipe.scale_margin / (6.0 * (256.0 if sides[i].get("four_over_six") else 448.0))
+                    gv = (hist[i:i + 1] * f).clamp_min(1e-30)               # device ops only, no synchronisation
+                    if sides[i].get("pow2"):                                # concatenated operands: powers of two
+                        gv = torch.exp2(torch.ceil(torch.log2(gv)))
+                    given[i] = gv
+        seen = torch.zeros(2, dtype=torch.float32, device=x2.device)
+    ops = []
+    for i, kw in enumerate(sides):
+        if kw is None:
+            ops.append(None)
+            continue
+        ops.append(_q(x2, transpose=i == 1, recipe=recipe, given=given[i],
+                      amax_out=seen[i:i + 1] if seen is not None else None, **kw))
+    if seen is not None:
+        hist = site.get("amax")
+        site["amax"] = seen if hist is None else torch.stack([seen[i] if on[i] else hist[i] for i in range(2)])
+        known = site.get("known", (False, False))
+        site["known"] = (known[0] or on[0], known[1] or on[1])
+    return ops[0], ops[1]
 
 
 # one quantization per input shared by its consumers (q / k / v, gate / up); reference: backend.py:471-499
@@ -407,7 +449,7 @@ def clear_shared() -> None:
     _SHARED.clear()
 
 
-def _input_operands(x: torch.Tensor, recipe: Fp4Recipe, row: bool = True):
+def _input_operands(x: torch.Tensor, recipe: Fp4Recipe, row: bool = True, site: dict | None = None):
     """Forward operand of x (None with ``row=False``) and its rotated transposed operand for the weight gradient
     (reference: bitlattice/backend.py:519-557)."""
     K = x.shape[-1]
@@ -425,12 +467,11 @@ def _input_operands(x: torch.Tensor, recipe: Fp4Recipe, row: bool = True):
     rseed, seed = _seed(), _seed()
     # the weight-gradient operands get power-of-two per-tensor scales: micro-batches can then be concatenated exactly
     # into one GEMM (deferred weight gradients)
-    xt = _q(x2, transpose=True, mode=mode, four_over_six=fos, recipe=recipe, rotate_seed=rseed, seed=seed, pow2=True)
-    xq = None
-    if row:
-        xq = (_q(x2, four_over_six=recipe.activations == "4over6", recipe=recipe) if K % 128 == 0
-              else _act_operand(x2, recipe))
-    return xq, xt
+    col = dict(mode=mode, four_over_six=fos, rotate_seed=rseed, seed=seed, pow2=True)
+    if K % 128 == 0:
+        return _q2(x2, dict(four_over_six=recipe.activations == "4over6") if row else None, col, recipe, site)
+    xt = _q(x2, transpose=True, recipe=recipe, **col)
+    return (_act_operand(x2, recipe) if row else None), xt
 
 
 def nvfp4_linear(x: torch.Tensor, w, bias: torch.Tensor | None = None, recipe: Fp4Recipe = Fp4Recipe()
@@ -449,7 +490,7 @@ def fp4_forward_saving(x: torch.Tensor, w, bias, recipe: Fp4Recipe = Fp4Recipe()
     """Forward of 'fp4_all': returns (y, saved), saved = x^T (rotated, NVFP4) for the weight gradient."""
     K = x.shape[-1]
     M = x.numel() // K
-    xq, xt = _shared(x, recipe, "fwd+t", lambda: _input_operands(x, recipe))
+    xq, xt = _shared(x, recipe, "fwd+t", lambda: _input_operands(x, recipe, site=_site(w, "x")))
     with nvtx("bl.fwd_gemm"):
         y = fp4_mm(xq, weight_operand(w), x.dtype)[:M]
     if bias is not None:
@@ -519,15 +560,16 @@ def fp4_backward(gy: torch.Tensor, w, xt: Fp4Operand | None, need_x: bool, need_
             wt = weight_t_rotated_operand(w, b46, scale_source=recipe.dgrad_scale)
         r = wt.rotate_seed if wt is not None else _seed()
         seed_row, seed_col = _seed(), _seed()
+        gq, gt = _q2(g2p,
+                     dict(mode=mode, four_over_six=b46, rotate_seed=r, seed=seed_row) if need_x else None,
+                     dict(mode=mode, four_over_six=b46, rotate_seed=xt.rotate_seed, seed=seed_col, pow2=True)
+                     if need_w else None, recipe, _site(w, "g"))
         if need_x:
-            gq = _q(g2p, mode=mode, four_over_six=b46, recipe=recipe, rotate_seed=r, seed=seed_row)
             if wt is None:      # W^T: MS-EDEN with MS-EDEN gradients (both factors unbiased), else round to nearest
                 wt = _q(None, mode="eden" if mode == "eden" else "rtn", four_over_six=b46, recipe=recipe,
                         rotate_seed=r, seed=_seed(), w=w)
             gx = fp4_mm(gq, wt, gy.dtype)[:M]
         if need_w:
-            gt = _q(g2p, transpose=True, mode=mode, four_over_six=b46, recipe=recipe, rotate_seed=xt.rotate_seed,
-                    seed=seed_col, pow2=True)
             if keep is not None:
                 keep.append((gt, xt))
             else:

@@ -36,6 +36,7 @@ struct GenArgs {
   uint32_t key, eden_key, rot_key;
   const float* given;         // per-tensor scale to use, or null: from amax[0]
   float* amax;                // max |value| after the rotation (pass 0 writes, pass 1 reads)
+  float* amax_out;            // or null: receives that maximum also when the per-tensor scale is given (delayed scales)
   float* out_global;
   uint8_t* codes;
   uint8_t* scales;
@@ -163,7 +164,11 @@ __global__ void __launch_bounds__(kGenThreads) general_kernel(GenArgs A) {
       neg |= (hash_uniform(static_cast<uint32_t>(16 * blk + i), A.rot_key) < 0.5f ? 1u : 0u) << i;
   }
   const float g = PASS == 1 ? general_global(A) : 1.0f;
-  if (PASS == 1 && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) A.out_global[0] = g;
+  if (PASS == 1 && blockIdx.x == 0 && blockIdx.y == 0 && threadIdx.x == 0) {
+    A.out_global[0] = g;
+    if (A.amax_out && !A.given) A.amax_out[0] = A.amax[0];
+  }
+  const bool observe = PASS == 1 && A.amax_out && A.given;     // no amax pass ran: observe the maximum here
   float wmax = 0.0f;
 
   for (int j = 0; j < kGenTileRows / 32; ++j) {
@@ -221,6 +226,7 @@ __global__ void __launch_bounds__(kGenThreads) general_kernel(GenArgs A) {
     if constexpr (PASS == 0) {
       wmax = fmaxf(wmax, am);
     } else {
+      if (observe) wmax = fmaxf(wmax, am);
       uint32_t sb = e4m3_encode(am / 6.0f / g);
       float t = e4m3_decode(sb) * g;
       float inv = t > 0.0f ? 1.0f / t : 0.0f;
@@ -283,10 +289,10 @@ __global__ void __launch_bounds__(kGenThreads) general_kernel(GenArgs A) {
       }
     }
   }
-  if constexpr (PASS == 0) {
+  if (PASS == 0 || observe) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) wmax = fmaxf(wmax, __shfl_xor_sync(0xffffffffu, wmax, o));
-    if (lane == 0 && wmax > 0.0f) atomicMax(reinterpret_cast<int*>(A.amax), __float_as_int(wmax));
+    if (lane == 0 && wmax > 0.0f) atomicMax(reinterpret_cast<int*>(PASS == 0 ? A.amax : A.amax_out), __float_as_int(wmax));
   }
 }
 
@@ -340,7 +346,8 @@ extern "C" int bl_nvfp4_quantize_general(const void* x, int dtype, int64_t R, in
                                          int four_over_six, int select, int rotate, int64_t seed, int64_t rotate_seed,
                                          const float* given_global, int pow2, const uint8_t* w_scales,
                                          const float* w_global, uint8_t* codes, uint8_t* scales, int sf_layout,
-                                         float* out_global, float* scratch, int device, bl_stream_t stream) {
+                                         float* out_global, float* scratch, float* amax_out, int device,
+                                         bl_stream_t stream) {
   BL_REQUIRE(x && codes && scales && out_global && scratch, "quantize_general: null buffer");
   BL_REQUIRE(R > 0 && C > 0 && R < (1ll << 31) && C < (1ll << 31), "quantize_general: bad shape %lld x %lld",
              (long long)R, (long long)C);
@@ -382,6 +389,7 @@ extern "C" int bl_nvfp4_quantize_general(const void* x, int dtype, int64_t R, in
   A.rot_key = hash_key(r32, 0x5151u);
   A.given = given_global;
   A.amax = scratch;
+  A.amax_out = amax_out;
   A.out_global = out_global;
   A.codes = codes;
   A.scales = scales;
@@ -389,6 +397,7 @@ extern "C" int bl_nvfp4_quantize_general(const void* x, int dtype, int64_t R, in
   if (sf_layout == BL_SF_BLOCKED && ((rows % 128) != 0 || ((cols / 16) % 4) != 0))
     BL_CUDA(cudaMemsetAsync(scales, 0, bl_blocked_scale_bytes(rows, cols / 16), st));
   const bool need_amax = given_global == nullptr;
+  if (amax_out && !need_amax) BL_CUDA(cudaMemsetAsync(amax_out, 0, sizeof(float), st));
   if (packed || dtype == BL_BF16) return general_typed<__nv_bfloat16>(A, packed, transpose != 0, need_amax, st);
   if (dtype == BL_F16) return general_typed<__half>(A, packed, transpose != 0, need_amax, st);
   return general_typed<float>(A, packed, transpose != 0, need_amax, st);

@@ -100,6 +100,9 @@ class Lattice(torch.optim.Optimizer):
     ``params``          an iterable of LatticeTensor parameters or param-group dicts (any key of ``DEFAULTS`` per group)
     ``fused_backward``  apply each parameter's update as soon as its gradient is accumulated and free the gradient
                         (the step then only advances); peak memory holds one gradient
+    ``hook_batch``      with ``fused_backward``: gradients are collected until this many are ready (or the backward
+                        pass ends) and their updates go to the GPU as one batch; 1 updates every parameter on its
+                        own. Same results; fewer, larger launches, and up to ``hook_batch`` gradients held
     ``seed``            base of the per-parameter RNG seeds: parameter number i uses (seed + 7919 * i) mod 2^32
     A parameter that is a row shard of a larger weight sets ``p._bl_row_offset`` to its first global row: the update
     then draws the random numbers of the unsharded tensor (as the reference's row tiles do, csrc/update.cpp:50).
@@ -107,7 +110,7 @@ class Lattice(torch.optim.Optimizer):
 
     def __init__(self, params, preset: str | None = None, *, lr: float = DEFAULTS["lr"], state: str = "gpu",
                  fused_backward: bool = False, seed: int = 0, weight_decay: float = 0.0, overlap: bool = False,
-                 **options):
+                 hook_batch: int = 1, **options):
         from .presets import PRESETS
         if preset is not None:
             if preset not in PRESETS:
@@ -143,6 +146,9 @@ class Lattice(torch.optim.Optimizer):
         self._group_of = {p: g for g in self.param_groups for p in g["params"]}
         self._done: set = set()
         self._defer = 0
+        self.hook_batch = max(1, int(hook_batch))
+        self._pending: list = []                    # parameters whose gradient is ready and whose update is not issued
+        self._pending_lock = threading.Lock()
         self._hooks = []
         if fused_backward:
             for p in self._pid:
@@ -154,6 +160,16 @@ class Lattice(torch.optim.Optimizer):
     def _on_grad(self, p: torch.Tensor) -> None:
         if p.grad is None or self._defer or _deferred:
             return
+        if self.hook_batch > 1:
+            with self._pending_lock:
+                self._pending.append(p)
+                first, full = len(self._pending) == 1, len(self._pending) >= self.hook_batch
+            self._done.add(p)
+            if first:                                # whatever is left when the backward pass ends goes out then
+                torch.autograd.Variable._execution_engine.queue_callback(self._flush_pending)
+            if full:
+                self._flush_pending()
+            return
         if self.overlap and p.is_cuda:
             self._update_aside(p, self._group_of[p])
         else:
@@ -161,6 +177,46 @@ class Lattice(torch.optim.Optimizer):
                 self._update(p, self._group_of[p])
         p.grad = None
         self._done.add(p)
+
+    def _flush_pending(self) -> None:
+        """Issue the updates of the parameters collected by the hooks (``hook_batch``), batched per parameter group."""
+        with self._pending_lock:
+            ps, self._pending = self._pending, []
+        if not ps:
+            return
+        with torch.no_grad():
+            for g in self.param_groups:
+                mine = [p for p in ps if self._group_of[p] is g]
+                if mine:
+                    self._apply(mine, g)
+        for p in ps:
+            p.grad = None
+
+    def _apply(self, todo: list, g: dict) -> None:
+        """Update the parameters ``todo`` of group ``g`` from their gradients: those that can share a library call
+        (same device, gradient dtype, fused direction, no momentum) in one batch, the others one by one."""
+        batch = [p for p in todo if self._batchable(p, g, todo[0])]
+        if len(batch) > 1:
+            # the tensors of the group in one library call: small shards are paced by the GPU, not the interpreter
+            if self.overlap:
+                side = self._update_stream(batch[0].device)
+                side.wait_stream(torch.cuda.current_stream(batch[0].device))
+                with torch.cuda.device(batch[0].device), torch.cuda.stream(side):
+                    self._update_many(batch, g)
+                    self._mark_updated(batch, side)
+                for p in batch:
+                    p.grad.record_stream(side)
+            else:
+                with torch.cuda.device(batch[0].device):
+                    self._update_many(batch, g)
+            batched = {id(p) for p in batch}
+            todo = [p for p in todo if id(p) not in batched]
+        for p in todo:
+            if self.overlap and p.is_cuda:
+                self._update_aside(p, g)
+            else:
+                with torch.cuda.device(p.device):
+                    self._update(p, g)
 
     def _update_stream(self, device: torch.device) -> torch.cuda.Stream:
         s = self._update_streams.get(device)
@@ -201,6 +257,7 @@ class Lattice(torch.optim.Optimizer):
             torch.cuda.current_stream(dev).wait_stream(s)
 
     def synchronize(self) -> None:
+        self._flush_pending()
         for dev in {p.device for p in self._pid if p.is_cuda}:
             torch.cuda.synchronize(dev)
         self.check_gemm_status(wait=True)
@@ -245,35 +302,14 @@ class Lattice(torch.optim.Optimizer):
             with torch.enable_grad():
                 loss = closure()
         self.check_gemm_status()                   # a failed GEMM of an earlier step: raise before updating further
+        self._flush_pending()
         for g in self.param_groups:
             todo = [p for p in g["params"] if p not in self._done and p.grad is not None]
-            batch = [p for p in todo if self._batchable(p, g, todo[0])]
-            if len(batch) > 1:
-                # the tensors of the group in one library call: small shards are paced by the GPU, not the interpreter
-                if self.overlap:
-                    side = self._update_stream(batch[0].device)
-                    side.wait_stream(torch.cuda.current_stream(batch[0].device))
-                    with torch.cuda.device(batch[0].device), torch.cuda.stream(side):
-                        self._update_many(batch, g)
-                        self._mark_updated(batch, side)
-                    for p in batch:
-                        p.grad.record_stream(side)
-                else:
-                    with torch.cuda.device(batch[0].device):
-                        self._update_many(batch, g)
-                batched = {id(p) for p in batch}
-                todo = [p for p in todo if id(p) not in batched]
+            if todo:
+                self._apply(todo, g)
                 if self.fused_backward:
-                    for p in batch:
+                    for p in todo:
                         p.grad = None
-            for p in todo:
-                if self.overlap and p.is_cuda:
-                    self._update_aside(p, g)
-                else:
-                    with torch.cuda.device(p.device):
-                        self._update(p, g)
-                if self.fused_backward:
-                    p.grad = None
         self._done.clear()
         self.wait()
         self._watch_gemm_status()

@@ -187,12 +187,14 @@ BL_API int bl_nvfp4_quantize_4over6(const void* x, int dtype, int64_t rows, int6
  *                  least 1e-12, rounded up to a power of two when pow2 is set
  * Summation orders (the reference fixes none; its test allows 2e-3 of codes and scales to differ): butterflies with
  * strides 1 .. 64 then the normalisation; error and MS-EDEN sums over groups of four elements, then pairwise.
- * out_global: 1 float (written); scratch: 1 float of device memory (the amax). sf_layout as bl_nvfp4_quantize. */
+ * out_global: 1 float (written); scratch: 1 float of device memory (the amax). amax_out (nullable, 1 float): receives
+ * max|rotated x| whether the per-tensor scale was given or computed -- the "seen" amax of the reference's delayed
+ * scales (csrc/nvfp4.cu:435, 459-460). sf_layout as bl_nvfp4_quantize. */
 BL_API int bl_nvfp4_quantize_general(const void* x, int dtype, int64_t R, int64_t C, int transpose, int mode,
                               int four_over_six, int select, int rotate, int64_t seed, int64_t rotate_seed,
                               const float* given_global, int pow2, const uint8_t* w_scales, const float* w_global,
                               uint8_t* codes, uint8_t* scales, int sf_layout, float* out_global, float* scratch,
-                              int device, bl_stream_t stream);
+                              float* amax_out, int device, bl_stream_t stream);
 
 /* Replaces torch.ops.bitlattice.fp4_fold_scales (csrc/fold.cu:12-33; Python twin bitlattice/backend.py:688-697): the
  * blocked scale buffer of operands concatenated along K -- row_tiles x tiles_per_row tiles of 512 bytes, column tile t

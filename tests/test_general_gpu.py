@@ -86,6 +86,20 @@ def test_packed_weight_input_equals_dense_input(shape, rotate, fos, mode):
     assert g2 == g and np.array_equal(p2, packed) and np.array_equal(s2, sb)
 
 
+def test_observed_amax_with_and_without_a_given_scale():
+    """amax_out receives the maximum of the rotated values whether the per-tensor scale is computed (the amax pass
+    found it) or given (the quantization pass observes it): the 'seen' amax of delayed scales."""
+    x = torch.from_numpy(GOLD["x"]).to(DEV).to(torch.bfloat16)
+    for transpose in (False, True):
+        src = GOLD["x"].T if transpose else GOLD["x"]
+        want = np.abs(G.rht128(np.ascontiguousarray(src), 21)).max()
+        for given in (None, torch.tensor([0.02], device=DEV)):
+            seen = torch.zeros(1, device=DEV)
+            _ops.nvfp4_quantize_general(x, transpose=transpose, mode="eden", rotate=True, seed=11, rotate_seed=21,
+                                        given=given, amax_out=seen)
+            assert float(seen.item()) == float(want)
+
+
 def test_blocked_scale_layout_and_ragged_rows():
     x = torch.randn(200, 256, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(DEV)
     p0, s0, g0 = _ops.nvfp4_quantize_general(x, mode="eden", rotate=True, seed=3)

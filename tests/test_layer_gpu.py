@@ -93,8 +93,8 @@ def test_four_over_six_recipe_forward_and_backward():
         assert rel(p.grad.cpu(), gy.float().cpu().T @ x.float()) < 0.25
     assert errs["4over6"] <= errs["nvidia"] * 1.02, errs
     assert bl._ops.gemm_status(0) == 0
-    with pytest.raises(ValueError, match="not built"):
-        bl.backend.Fp4Recipe(scale_source="delayed")
+    with pytest.raises(ValueError, match="scale_source"):
+        bl.backend.Fp4Recipe(scale_source="sometimes")
 
 
 @pytest.mark.parametrize("M", [5, 96, 512])
@@ -283,6 +283,62 @@ def test_overlapped_updates_match_step():
             assert torch.equal(p.scales.view(torch.uint8), t.scales.view(torch.uint8))
         assert torch.equal(o1.state[p]["phase"], o2.state[q]["phase"])
         assert torch.equal(o1.state[p]["phase"], o3.state[r]["phase"])
+
+
+def test_batched_step_reuses_its_plan_and_notices_new_storage():
+    """step() marshals the static arguments of a batch of parameters once (an update plan) and reuses them; when a
+    parameter's state or storage is replaced between steps the plan is rebuilt. Either way the result is that of the
+    optimizer updating one tensor at a time."""
+    a, b = _make_params(21), _make_params(21)
+    o1 = bl.Lattice(a, lr=5e-3, direction="colnorm", phase_bits=4, seed=3)
+    o2 = bl.Lattice(b, lr=5e-3, direction="colnorm", phase_bits=4, seed=3)
+    o2._batchable = lambda *args: False                      # one library call per tensor
+    _run(a, o1, 2)
+    assert len(o1._plans) == 1
+    plan = next(iter(o1._plans.values()))
+    _run(a, o1, 1)
+    assert next(iter(o1._plans.values())) is plan            # reused
+    for p in a:                                              # new phase storage, as load_state_dict leaves it
+        o1.state[p]["phase"] = o1.state[p]["phase"].clone()
+    _run(a, o1, 2)
+    assert next(iter(o1._plans.values())) is not plan        # rebuilt for the new addresses
+    for n in (2, 1, 2):                                      # the same inputs as above, one tensor at a time
+        _run(b, o2, n)
+    assert not o2._plans
+    torch.cuda.synchronize()
+    for p, q in zip(a, b):
+        assert torch.equal(p.packed, q.packed)
+        assert torch.equal(p.scales.view(torch.uint8), q.scales.view(torch.uint8))
+        assert torch.equal(o1.state[p]["phase"], o2.state[q]["phase"])
+
+
+@pytest.mark.parametrize("overlap", [False, True])
+def test_hook_batches_match_immediate_updates(overlap):
+    """``hook_batch``: the backward hooks collect gradients and issue their updates several at a time (the rest when
+    the backward pass ends, before anything reads the weights again); same weights and state as updating each
+    parameter from its own hook, gradients freed either way."""
+    def params():
+        return [torch.nn.Parameter(bl.LatticeTensor.from_float((torch.randn(s, generator=gen(40 + i)) * 0.05).to(DEV),
+                                                               "nvfp4", method="rtn", dtype=torch.bfloat16))
+                for i, s in enumerate([(64, 128), (32, 256), (48, 128), (32, 128), (64, 256)])]
+    a, b = params(), params()
+    o1 = bl.Lattice(a, lr=5e-3, direction="colnorm", phase_bits=4, seed=3, fused_backward=True)
+    o2 = bl.Lattice(b, lr=5e-3, direction="colnorm", phase_bits=4, seed=3, fused_backward=True, overlap=overlap,
+                    hook_batch=2)
+    for ps, opt in ((a, o1), (b, o2)):
+        for s in range(3):
+            loss = 0
+            for p in ps:
+                x = torch.randn(16, p.shape[1], generator=gen(200 + s)).to(DEV, torch.bfloat16)
+                loss = loss + torch.nn.functional.linear(x, p).float().square().mean()
+            loss.backward()
+            assert all(p.grad is None for p in ps) and not opt._pending       # 5 parameters: 2 + 2 + the last one
+            opt.step()
+    torch.cuda.synchronize()
+    for p, q in zip(a, b):
+        assert torch.equal(p.packed, q.packed)
+        assert torch.equal(p.scales.view(torch.uint8), q.scales.view(torch.uint8))
+        assert torch.equal(o1.state[p]["phase"], o2.state[q]["phase"])
 
 
 def test_readers_wait_for_overlapped_updates():

@@ -1,4 +1,4 @@
-"""The 128-rotation FP4 recipes (quartet2, quartet2_4o6, quartet2_fast, quartet2_bound) and deferred weight gradients
+"""The 128-rotation FP4 recipes (quartet2, quartet2_4o6, quartet2_fast, quartet2_delayed, quartet2_bound) and deferred weight gradients
 end to end through F.linear, with the criteria of the reference's own tests (tests/test_backend.py:159-201,318-334):
 outputs and gradients within 0.25 relative of the exact route, MS-EDEN gradients unbiased (the mean over repeated
 backward passes at most 0.35 of one pass's error), deferred weight gradients equal to the accumulated ones within
@@ -14,7 +14,7 @@ from oracle import fp4_general as G
 
 pytestmark = pytest.mark.gpu
 DEV = "cuda"
-RECIPES = ("nvidia", "4over6", "quartet2", "quartet2_4o6", "quartet2_fast", "quartet2_bound")
+RECIPES = ("nvidia", "4over6", "quartet2", "quartet2_4o6", "quartet2_fast", "quartet2_delayed", "quartet2_bound")
 
 
 def _C(policy, recipe="nvidia"):
@@ -146,6 +146,62 @@ def test_deferred_weight_gradients_match_accumulated(recipe):
     assert rel(p.grad.float(), ref) < 0.25
     assert not backend.pending_wgrad()
     assert backend.fold_rounded() >= 0
+
+
+def test_delayed_scales_follow_the_previous_call():
+    """'quartet2_delayed' (reference: tests/test_backend.py:298-316): the first call of a layer computes its
+    per-tensor scales, later calls take them from the amax the previous call saw times the margin -- also when the
+    new input exceeds it within the margin -- and stay within 0.25 of the exact gradients. The kept amax is the one
+    the oracle finds for the rotated operands, and a given scale is the previous amax * margin / (6 * 448), rounded
+    up to a power of two for the weight-gradient side."""
+    g = torch.Generator().manual_seed(11)
+    w = _weight(seed=11)
+    p = torch.nn.Parameter(w.detach())
+    rels, seen_x = [], []
+    backend.set_sr_seed(500)
+    for i, scale in enumerate((1.0, 1.0, 1.0, 1.5)):
+        x = (torch.randn(256, 256, generator=g) * scale).to(torch.bfloat16).to(DEV)
+        gy = torch.randn(256, 128, generator=g).to(torch.bfloat16).to(DEV)
+        _, rdx, rdw = _grads(x, w, gy, "exact", "nvidia")
+        p.grad = None
+        xi = x.clone().requires_grad_(True)
+        with bl.compute(_C("fp4_all", "quartet2_delayed")):
+            y = torch.nn.functional.linear(xi, p)
+            xt_global = float(y.grad_fn.saved_tensors[2].item())
+            y.backward(gy)
+        rels.append(max(rel(xi.grad.float(), rdx), rel(p.grad.float(), rdw)))
+        amax = p._bl_sites["x"]["amax"].cpu().numpy()
+        xf = x.float().cpu().numpy()
+        assert amax[0] == np.abs(xf).max()                                   # row side: not rotated
+        rot = G.rht128(np.ascontiguousarray(xf.T), 500 + 4 * i)              # the call's first seed rotates x^T
+        assert amax[1] == np.abs(rot).max()
+        if seen_x:                                                           # the scale came from the previous amax
+            want = np.float32(seen_x[-1][1]) * np.float32(2.0 / (6.0 * 448.0))      # MS-EDEN side: no four-over-six
+            assert xt_global == float(G.pow2_up(np.float32(want)))
+        seen_x.append(amax)
+    assert p._bl_sites["x"]["known"] == (True, True) and p._bl_sites["g"]["known"] == (True, True)
+    assert max(rels) < 0.25, rels
+
+
+def test_deferred_weight_gradients_with_delayed_scales():
+    g = torch.Generator().manual_seed(14)
+    w = _weight(seed=14)
+    p = torch.nn.Parameter(w.detach())
+    for step in range(3):                              # the first step is exact; later ones use delayed scales
+        xs = [(torch.randn(128, 256, generator=g) * s).to(torch.bfloat16).to(DEV) for s in (1.0, 1.3)]
+        gys = [torch.randn(128, 128, generator=g).to(torch.bfloat16).to(DEV) for _ in xs]
+        ref = sum(_grads(x, w, gy, "exact", "nvidia")[2] for x, gy in zip(xs, gys))
+        p.grad = None
+        with bl.compute(_C("fp4_all", "quartet2_delayed")):
+            with backend.defer_wgrad():
+                for x, gy in zip(xs, gys):
+                    torch.nn.functional.linear(x.clone().requires_grad_(True), p).backward(gy)
+            for _, items in backend._PENDING.values():   # the operands to concatenate: power-of-two scales
+                for gt, xt in items:
+                    for gs in (gt.global_scale, xt.global_scale):
+                        assert torch.equal(gs, torch.exp2(torch.round(torch.log2(gs))))
+            backend.flush_wgrad()
+        assert rel(p.grad.float(), ref) < 0.25, step
 
 
 def test_deferred_weight_gradients_need_the_128_rotation():
