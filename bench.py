@@ -325,7 +325,7 @@ def run_ours(a):
             p = torch.nn.Parameter(w)
             params.append(p)
             meta.append((name, N, K))
-    opt = bl.Lattice(params, fused_backward=True, overlap=bool(a.overlap), hook_batch=a.hook_batch, **OPT)
+    opt = bl.Lattice(params, fused_backward=True, overlap=bool(a.overlap), hook_batch=a.hook_batch, hook_flush="reader", **OPT)
     flops = sum(6.0 * M * N * K for _, N, K in meta)
     weights = sum(N * K for _, N, K in meta)
     group = dist.group.WORLD if world > 1 else None

@@ -255,6 +255,9 @@ class _WeightOperands:
         self.kinds: dict = {}                           # id(weight) -> kinds present (drop() without a scan)
 
     def get(self, w, kind: str, make):
+        opt = getattr(w, "_bl_pending", None)
+        if opt is not None:                             # an update held back by its optimizer goes out first (it
+            opt._flush_pending()                        # bumps the version)
         key, version = (id(w), kind), getattr(w, "_bl_version", 0)
         entry = self.entries.get(key)
         if entry is not None:

@@ -28,6 +28,7 @@ from __future__ import annotations
 
 import contextlib
 import threading
+import weakref
 from typing import Any
 
 import torch
@@ -103,6 +104,11 @@ class Lattice(torch.optim.Optimizer):
     ``hook_batch``      with ``fused_backward``: gradients are collected until this many are ready (or the backward
                         pass ends) and their updates go to the GPU as one batch; 1 updates every parameter on its
                         own. Same results; fewer, larger launches, and up to ``hook_batch`` gradients held
+    ``hook_flush``      when an incomplete batch goes out: 'backward' -- at the end of the backward pass that produced
+                        it; 'reader' -- when the batch fills up, at ``step()`` / ``synchronize()``, or as soon as
+                        anything in this package reads one of its weights (GEMM operands, dequantize, copies, save):
+                        batches then fill across several backward calls. Code that reads ``p.packed`` itself
+                        between backward and step must use 'backward'
     ``seed``            base of the per-parameter RNG seeds: parameter number i uses (seed + 7919 * i) mod 2^32
     A parameter that is a row shard of a larger weight sets ``p._bl_row_offset`` to its first global row: the update
     then draws the random numbers of the unsharded tensor (as the reference's row tiles do, csrc/update.cpp:50).
@@ -110,7 +116,7 @@ class Lattice(torch.optim.Optimizer):
 
     def __init__(self, params, preset: str | None = None, *, lr: float = DEFAULTS["lr"], state: str = "gpu",
                  fused_backward: bool = False, seed: int = 0, weight_decay: float = 0.0, overlap: bool = False,
-                 hook_batch: int = 1, **options):
+                 hook_batch: int = 1, hook_flush: str = "backward", **options):
         from .presets import PRESETS
         if preset is not None:
             if preset not in PRESETS:
@@ -147,6 +153,9 @@ class Lattice(torch.optim.Optimizer):
         self._done: set = set()
         self._defer = 0
         self.hook_batch = max(1, int(hook_batch))
+        if hook_flush not in ("backward", "reader"):
+            raise ValueError("hook_flush must be 'backward' or 'reader'")
+        self.hook_flush = hook_flush
         self._pending: list = []                    # parameters whose gradient is ready and whose update is not issued
         self._pending_lock = threading.Lock()
         self._hooks = []
@@ -165,7 +174,9 @@ class Lattice(torch.optim.Optimizer):
                 self._pending.append(p)
                 first, full = len(self._pending) == 1, len(self._pending) >= self.hook_batch
             self._done.add(p)
-            if first:                                # whatever is left when the backward pass ends goes out then
+            if self.hook_flush == "reader":
+                p._bl_pending = self                 # readers of the weight have the batch issued first
+            elif first:                              # whatever is left when the backward pass ends goes out then
                 torch.autograd.Variable._execution_engine.queue_callback(self._flush_pending)
             if full:
                 self._flush_pending()
@@ -191,6 +202,8 @@ class Lattice(torch.optim.Optimizer):
                     self._apply(mine, g)
         for p in ps:
             p.grad = None
+            if self.hook_flush == "reader":
+                p._bl_pending = None
 
     def _apply(self, todo: list, g: dict) -> None:
         """Update the parameters ``todo`` of group ``g`` from their gradients: those that can share a library call
@@ -315,11 +328,16 @@ class Lattice(torch.optim.Optimizer):
         self._watch_gemm_status()
         return loss
 
+    _matrix: dict = {}             # id(parameter) -> whether it counts as a matrix (shape reads of a tensor subclass
+                                   # are slow and these run for every parameter of every step)
+
     @staticmethod
     def _kind(p, g: dict) -> str:
         """The direction of ``p``: matrices use ``direction``, vectors ``vector_direction`` (reference: lattice.py:472-473)."""
-        matrix = p.dim() >= 2 and min(p.shape[0], p.numel() // p.shape[0]) > 1
-        return g["direction"] if matrix else g["vector_direction"]
+        matrix = Lattice._matrix.get(id(p))
+        if matrix is None or matrix[0]() is not p:
+            matrix = Lattice._matrix[id(p)] = (weakref.ref(p), p.dim() >= 2 and min(p.shape[0], p.numel() // p.shape[0]) > 1)
+        return g["direction"] if matrix[1] else g["vector_direction"]
 
     @staticmethod
     def _fused(p, g: dict) -> bool:
@@ -328,10 +346,13 @@ class Lattice(torch.optim.Optimizer):
 
     @staticmethod
     def _batchable(p, g: dict, first) -> bool:
+        if g["momentum"] != "none" or g["normalize"] == "row":
+            return False
+        kind = Lattice._kind(p, g)
+        if kind not in FUSED_DIRECTIONS or (p is not first and kind != Lattice._kind(first, g)):
+            return False
         G = p.grad
-        return (g["momentum"] == "none" and Lattice._fused(p, g) and Lattice._kind(p, g) == Lattice._kind(first, g)
-                and p.is_cuda and p.device == first.device and p.fmt == first.fmt
-                and not G.is_sparse
+        return (p.is_cuda and p.device == first.device and (p.fmt is first.fmt or p.fmt == first.fmt) and not G.is_sparse
                 and G.dtype == first.grad.dtype and G.dtype in (torch.bfloat16, torch.float16, torch.float32)
                 and G.is_contiguous())
 

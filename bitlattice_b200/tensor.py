@@ -32,8 +32,13 @@ def is_lattice(t) -> bool:
 
 def wait_for_update(t) -> None:
     """Make the current stream wait for the last update of ``t`` that an optimizer issued on another stream
-    (``Lattice(overlap=True)`` leaves its event in ``t._bl_updated``). Every reader of the storage calls this first, so
-    an update that is still running beside the caller's stream is never raced, whatever the order of calls."""
+    (``Lattice(overlap=True)`` leaves its event in ``t._bl_updated``), after having an optimizer that still holds the
+    update back (``hook_flush='reader'``: ``t._bl_pending``) issue it. Every reader of the storage calls this first,
+    so an update that is pending or still running beside the caller's stream is never raced, whatever the order of
+    calls."""
+    opt = getattr(t, "_bl_pending", None)
+    if opt is not None:                  # its update has not been issued yet (an optimizer collecting gradients)
+        opt._flush_pending()
     ev = getattr(t, "_bl_updated", None)
     if ev is not None:
         torch.cuda.current_stream(t.packed.device).wait_event(ev)
@@ -125,7 +130,8 @@ class LatticeTensor(torch.Tensor):
         t = LatticeTensor(fn(self.packed), fn(self.scales), fn(self.global_scale), None, self.fmt,
                           shape or self.shape, dtype or self.dtype)
         t.compute = self.compute
-        keep = ("_bl_row_offset", "_bl_version", "_bl_updated") if shares_storage else ("_bl_row_offset",)
+        keep = (("_bl_row_offset", "_bl_version", "_bl_updated", "_bl_pending") if shares_storage
+                else ("_bl_row_offset",))
         for name in keep:
             if name in self.__dict__:
                 setattr(t, name, self.__dict__[name])

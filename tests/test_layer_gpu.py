@@ -312,8 +312,9 @@ def test_batched_step_reuses_its_plan_and_notices_new_storage():
         assert torch.equal(o1.state[p]["phase"], o2.state[q]["phase"])
 
 
+@pytest.mark.parametrize("flush", ["backward", "reader"])
 @pytest.mark.parametrize("overlap", [False, True])
-def test_hook_batches_match_immediate_updates(overlap):
+def test_hook_batches_match_immediate_updates(overlap, flush):
     """``hook_batch``: the backward hooks collect gradients and issue their updates several at a time (the rest when
     the backward pass ends, before anything reads the weights again); same weights and state as updating each
     parameter from its own hook, gradients freed either way."""
@@ -324,16 +325,28 @@ def test_hook_batches_match_immediate_updates(overlap):
     a, b = params(), params()
     o1 = bl.Lattice(a, lr=5e-3, direction="colnorm", phase_bits=4, seed=3, fused_backward=True)
     o2 = bl.Lattice(b, lr=5e-3, direction="colnorm", phase_bits=4, seed=3, fused_backward=True, overlap=overlap,
-                    hook_batch=2)
+                    hook_batch=2, hook_flush=flush)
     for ps, opt in ((a, o1), (b, o2)):
         for s in range(3):
             loss = 0
-            for p in ps:
+            for p in ps:       # (with 'reader', a weight whose update is still pending would be flushed here)
                 x = torch.randn(16, p.shape[1], generator=gen(200 + s)).to(DEV, torch.bfloat16)
                 loss = loss + torch.nn.functional.linear(x, p).float().square().mean()
             loss.backward()
-            assert all(p.grad is None for p in ps) and not opt._pending       # 5 parameters: 2 + 2 + the last one
+            if opt is o1 or flush == "backward":      # 5 parameters: 2 + 2 + the last one at the end of backward
+                assert all(p.grad is None for p in ps) and not opt._pending
+            else:                                     # the last one waits for step() or for a reader
+                assert len(opt._pending) == 1
+                held = opt._pending[0]
+                if s == 1:                            # a reader: the pending update goes out before the read
+                    held.dequantize(torch.float32)
+                    assert not opt._pending and held.grad is None
+                if s == 2:                            # a cached GEMM operand is not handed out for the old version
+                    version = held._bl_version
+                    bl.backend.weight_operand(held)
+                    assert not opt._pending and held._bl_version == version + 1
             opt.step()
+            assert not opt._pending
     torch.cuda.synchronize()
     for p, q in zip(a, b):
         assert torch.equal(p.packed, q.packed)
