@@ -48,6 +48,8 @@ _SIGNATURES = {
     "bl_nvfp4_amax": (_c.c_int, [_P, _c.c_int, _c.c_int64, _P, _c.c_int, _P]),
     "bl_nvfp4_quantize": (_c.c_int, [_P, _c.c_int, _c.c_int64, _c.c_int64, _P, _c.c_int64, _c.c_uint32, _P, _P,
                                      _c.c_int, _c.c_int, _P]),
+    "bl_nvfp4_amax_quantize": (_c.c_int, [_P, _c.c_int, _c.c_int64, _c.c_int64, _P, _c.c_int64, _c.c_uint32, _P, _P,
+                                          _c.c_int, _c.c_int, _P]),
     "bl_nvfp4_quantize_4over6": (_c.c_int, [_P, _c.c_int, _c.c_int64, _c.c_int64, _P, _c.c_int, _P, _P, _c.c_int,
                                             _c.c_int, _P]),
     "bl_nvfp4_quantize_general": (_c.c_int, [_P, _c.c_int, _c.c_int64, _c.c_int64, _c.c_int, _c.c_int, _c.c_int, _c.c_int,
@@ -132,7 +134,7 @@ def check(status: int) -> None:
 KERNELS_PER_CALL = {"bl_nvfp4_step_quantized": 1, "bl_nvfp4_lattice_update": 1, "bl_nvfp4_lattice_update_many": 0,
                     "bl_nvfp4_lattice_update_fixed_scratch": 1, "bl_direction": 1,
                     "bl_nvfp4_dequantize": 1, "bl_nvfp4_amax": 1, "bl_nvfp4_quantize": 1, "bl_nvfp4_quantize_t": 1,
-                    "bl_nvfp4_quantize_4over6": 1, "bl_nvfp4_quantize_general": 2, "bl_fp4_fold_scales": 1,
+                    "bl_nvfp4_quantize_4over6": 1, "bl_nvfp4_amax_quantize": 2, "bl_nvfp4_quantize_general": 2, "bl_fp4_fold_scales": 1,
                     "bl_nvfp4_requantize_t": 1, "bl_nvfp4_scales_to_blocked": 1, "bl_nvfp4_gemm": 1, "bl_nvfp4_gemm_accumulate": 1,
                     "bl_nvfp4_assemble_gathered": 1,
                     "bl_swiglu_fwd": 1, "bl_swiglu_bwd": 1}

@@ -346,6 +346,22 @@ def quantize_nvfp4(x: torch.Tensor, global_scale: torch.Tensor, seed: int = -1, 
     return packed, scales if blocked else scales.view(torch.float8_e4m3fn)
 
 
+def amax_quantize_nvfp4(x: torch.Tensor, seed: int = -1, step: int = 0, blocked: bool = False):
+    """``amax_global`` and ``quantize_nvfp4`` against the scale it finds, enqueued by one library call: returns
+    (packed, scales, amax [4]); the per-tensor scale is ``amax[1:2]``."""
+    _require(x, "x")
+    if x.dtype not in _C.DTYPE:
+        raise RuntimeError("x must be bf16, fp16 or fp32")
+    cols = x.shape[-1]
+    rows = x.numel() // cols
+    am = torch.empty(4, dtype=torch.float32, device=x.device)
+    packed = torch.empty(rows, cols // 2, dtype=torch.uint8, device=x.device)
+    scales = _scale_buffer(rows, cols // 16, blocked, x.device)
+    _C.call("bl_nvfp4_amax_quantize", _C.ptr(x), _C.DTYPE[x.dtype], rows, cols, _C.ptr(am), int(seed),
+            int(step) & 0xFFFFFFFF, _C.ptr(packed), _C.ptr(scales), int(blocked), _C.device_of(x), _C.stream_of(x))
+    return packed, scales if blocked else scales.view(torch.float8_e4m3fn), am
+
+
 def quantize_nvfp4_4over6(x: torch.Tensor, global_scale: torch.Tensor, select: str = "mse", blocked: bool = False):
     """The four-over-six round-to-nearest quantizer of forward activations: every block keeps the better of "maximum
     mapped to 6" and "maximum mapped to 4" (``select``: 'mse' or 'mae'). ``global_scale``: amax / (6 * 256), i.e.

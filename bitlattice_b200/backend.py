@@ -195,11 +195,9 @@ def to_blocked(s: torch.Tensor) -> torch.Tensor:
 def quantize_fp4(x2: torch.Tensor, stochastic: bool = False, blocked: bool = True) -> Fp4Operand:
     """NVFP4 quantization along the last dimension of a contiguous 2-D tensor: round to nearest, or stochastic rounding
     with a fresh seed per call (reference: backend.py:237-244). One amax pass, one quantization pass."""
-    am = _ops.amax_global(x2)
-    g = am[1:2]
     seed = _seed() if stochastic else -1
-    packed, scales = _ops.quantize_nvfp4(x2, g, seed, 0, blocked=blocked)
-    return Fp4Operand(packed, scales, g, blocked)
+    packed, scales, am = _ops.amax_quantize_nvfp4(x2, seed, 0, blocked=blocked)
+    return Fp4Operand(packed, scales, am[1:2], blocked)
 
 
 def _act_operand(x2: torch.Tensor, recipe: Fp4Recipe) -> Fp4Operand:

@@ -742,6 +742,16 @@ extern "C" int bl_nvfp4_quantize(const void* x, int dtype, int64_t rows, int64_t
   return quantize_rows_typed(static_cast<const float*>(x), rows, cols, global_scale, seed, step, codes, scales, sf_layout, device, st);
 }
 
+// The amax pass and the row quantizer against the per-tensor scale it finds, enqueued by one call (what
+// bitlattice/backend.py:237-244 does with two operators): amax4 as bl_nvfp4_amax's out, the rest as bl_nvfp4_quantize.
+extern "C" int bl_nvfp4_amax_quantize(const void* x, int dtype, int64_t rows, int64_t cols, float* amax4, int64_t seed,
+                                      uint32_t step, uint8_t* codes, uint8_t* scales, int sf_layout, int device,
+                                      bl_stream_t stream) {
+  BL_REQUIRE(rows > 0 && cols > 0, "amax_quantize: empty input");
+  if (int rc = bl_nvfp4_amax(x, dtype, rows * cols, amax4, device, stream)) return rc;
+  return bl_nvfp4_quantize(x, dtype, rows, cols, amax4 + 1, seed, step, codes, scales, sf_layout, device, stream);
+}
+
 extern "C" int bl_nvfp4_quantize_4over6(const void* x, int dtype, int64_t rows, int64_t cols, const float* global_scale,
                                         int select, uint8_t* codes, uint8_t* scales, int sf_layout, int device,
                                         bl_stream_t stream) {

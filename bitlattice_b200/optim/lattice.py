@@ -408,6 +408,7 @@ class Lattice(torch.optim.Optimizer):
         return super().state_dict()
 
     def zero_grad(self, set_to_none: bool = True):
+        self._flush_pending()                        # updates still held back need their gradients
         super().zero_grad(set_to_none=True)
 
     def remove_hooks(self) -> None:

@@ -44,9 +44,10 @@ import torch.distributed as dist
 
 from .tensor import LatticeTensor, wait_for_update
 
-__all__ = ["ColumnParallelFp4Linear", "ColumnParallelLinear", "GatheredWeights", "TokenParallelFp4Linear",
-           "TokenParallelLinear", "column_parallel_linear", "column_parallel_linears", "gathered_input_operands",
-           "shard_bounds", "shard_rows", "token_parallel_linear", "token_parallel_linears", "world"]
+__all__ = ["ColumnParallelFp4Linear", "ColumnParallelLinear", "GatheredWeights", "SharedInputFp4Linears",
+           "TokenParallelFp4Linear", "TokenParallelLinear", "column_parallel_linear", "column_parallel_linears",
+           "gathered_input_operands", "shard_bounds", "shard_rows", "shared_input_linears", "token_parallel_linear",
+           "token_parallel_linears", "world"]
 
 
 def world(group=None) -> tuple[int, int]:
@@ -243,6 +244,73 @@ class ColumnParallelFp4Linear(torch.autograd.Function):
         return (gx_out, None, None, *gws)
 
 
+class SharedInputFp4Linears(torch.autograd.Function):
+    """Several 'fp4_all' layers on one input in one process (q/k/v, gate/up; what the column-parallel function does
+    without its collectives): one quantization of the input for all of them, and in the backward the input gradients
+    of the projections are summed in the epilogue of their GEMMs (``fp4_dgrad(add_to=)``, the bits of adding the
+    tensors in the order of ``weights``) instead of by autograd's accumulation, which costs a pass over the gradient
+    per extra projection."""
+
+    @staticmethod
+    def forward(ctx, x, recipe, *weights):
+        from . import backend
+        K = x.shape[-1]
+        M = x.numel() // K
+        if any(ctx.needs_input_grad[2:]):
+            xq, xt = backend._shared(x, recipe, "fwd+t",
+                                     lambda: backend._input_operands(x, recipe, site=backend._site(weights[0], "x")))
+        else:
+            xq, xt = backend._shared(x, recipe, "fwd", lambda: backend._act_operand(
+                backend._pad_rows(x.reshape(-1, K), 16).contiguous(), recipe)), None
+        ctx.weights, ctx.recipe, ctx.xt = weights, recipe, xt
+        ctx.x_meta = (x.shape, x.dtype)
+        return tuple(backend.fp4_mm(xq, backend.weight_operand(w), x.dtype)[:M].reshape(*x.shape[:-1], w.shape[0])
+                     for w in weights)
+
+    @staticmethod
+    def backward(ctx, *gys):
+        from . import backend
+        shape, dtype = ctx.x_meta
+        M = 1
+        for d in shape[:-1]:
+            M *= d
+        staged, gx_sum = [], None
+        for w, gy in zip(ctx.weights, gys):
+            if gy is None:
+                staged.append(None)
+                continue
+            if ctx.needs_input_grad[0]:
+                if gx_sum is not None and M % 32 == 0 and gx_sum.is_contiguous():
+                    _, g2p, gq = backend.fp4_dgrad(gy, w, ctx.recipe, add_to=gx_sum)
+                else:
+                    gx, g2p, gq = backend.fp4_dgrad(gy, w, ctx.recipe)
+                    gx_sum = gx if gx_sum is None else gx_sum.add_(gx)
+            else:
+                g2p, gq = backend._pad_rows(gy.reshape(-1, gy.shape[-1]), 32).contiguous(), None
+            staged.append((g2p, gq))
+        gws = []
+        for i, (w, st) in enumerate(zip(ctx.weights, staged)):
+            if st is None or not ctx.needs_input_grad[2 + i] or ctx.xt is None:
+                gws.append(None)
+                continue
+            gws.append(backend.fp4_wgrad(st[0], st[1], ctx.xt, w, ctx.recipe).to(w.dtype))
+        gx = gx_sum.to(dtype).reshape(shape) if gx_sum is not None else None
+        return (gx, None, *gws)
+
+
+def shared_input_linears(x: torch.Tensor, weights) -> tuple:
+    """``F.linear(x, w)`` for every weight. When all of them take the 'fp4_all' route with the NVIDIA-recipe operands
+    they run as one function that quantizes the input once and sums their input gradients in the GEMM epilogues."""
+    weights = tuple(weights)
+    if len(weights) > 1 and x.is_cuda and all(isinstance(w, LatticeTensor) and w.dim() == 2 for w in weights):
+        from .compute_policy import route
+        routes = [route(x, w) for w in weights]
+        recipe = routes[0][1].nvfp4
+        if all(r[0] == "fp4_all" and r[1].nvfp4 == recipe for r in routes) and recipe.packed_exchange:
+            return SharedInputFp4Linears.apply(x, recipe, *weights)
+    return tuple(torch.nn.functional.linear(x, w) for w in weights)
+
+
 def _fp4_all_route(x_shard: torch.Tensor, w):
     """The NVFP4 recipe when the layer would take the 'fp4_all' route and the shard shapes allow packed gathering."""
     if not (isinstance(w, LatticeTensor) and x_shard.is_cuda and x_shard.dim() == 2):
@@ -275,6 +343,8 @@ def column_parallel_linears(x_shard: torch.Tensor, weights, group=None) -> tuple
         recipes = [_fp4_all_route(x_shard, w) for w in weights]
         if all(r is not None for r in recipes) and all(r == recipes[0] for r in recipes):
             return ColumnParallelFp4Linear.apply(x_shard, group, recipes[0], *weights)
+    else:
+        return shared_input_linears(x_shard, weights)
     return tuple(column_parallel_linear(x_shard, w, group) for w in weights)
 
 
@@ -542,7 +612,7 @@ def token_parallel_linears(x: torch.Tensor, weights, gathered: GatheredWeights |
         group = gathered.group
     fn = linear or torch.nn.functional.linear
     if world(group)[1] == 1:
-        return tuple(fn(x, w) for w in weights)
+        return shared_input_linears(x, weights) if linear is None else tuple(fn(x, w) for w in weights)
     if linear is None and x.is_cuda and all(isinstance(w, LatticeTensor) for w in weights):
         from .compute_policy import route
         routes = [route(x, w) for w in weights]

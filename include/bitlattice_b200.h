@@ -160,6 +160,12 @@ BL_API int bl_nvfp4_amax(const void* x, int dtype, int64_t n, float* out, int de
 BL_API int bl_nvfp4_quantize(const void* x, int dtype, int64_t rows, int64_t cols, const float* global_scale, int64_t seed,
                       uint32_t step, uint8_t* codes, uint8_t* scales, int sf_layout, int device, bl_stream_t stream);
 
+/* bl_nvfp4_amax followed by bl_nvfp4_quantize against the scale it finds (amax4[1]), enqueued by one call: the pair of
+ * operators of bitlattice/backend.py:237-244 (quantize_fp4). amax4: 4 floats as bl_nvfp4_amax's out. */
+BL_API int bl_nvfp4_amax_quantize(const void* x, int dtype, int64_t rows, int64_t cols, float* amax4, int64_t seed,
+                           uint32_t step, uint8_t* codes, uint8_t* scales, int sf_layout, int device,
+                           bl_stream_t stream);
+
 /* The forward-activation quantizer of the '4over6' recipe (bitlattice/backend.py:131, the general quantizer
  * torch.ops.bitlattice.nvfp4_quantize with four_over_six, csrc/nvfp4.cu:553-600; Python twin bitlattice/fp4ref.py:103-135):
  * round to nearest with ties to the even code, v * (1 / (scale*global)); every block is quantized with its maximum

@@ -539,6 +539,32 @@ def test_gemm_kernels_agree_bit_for_bit():
 
 
 @ALL_GEMM_KERNELS
+def test_gemm_on_reused_addresses_with_changing_shapes(gemm_kernel):
+    """The library keeps encoded tensor maps per (address, shape, box). Operands of different shapes that start at
+    the same addresses (slices of one allocation, as torch's caching allocator hands out) must each get their own map:
+    every product equals the one computed from freshly allocated copies of the operands."""
+    g0 = torch.Generator(device=DEV).manual_seed(9)
+    pool_a = torch.randint(0, 256, (1 << 21,), device=DEV, dtype=torch.uint8, generator=g0)
+    pool_b = torch.randint(0, 256, (1 << 21,), device=DEV, dtype=torch.uint8, generator=g0)
+    pool_sa = torch.randint(40, 72, (1 << 19,), device=DEV, dtype=torch.uint8, generator=g0)
+    pool_sb = torch.randint(40, 72, (1 << 19,), device=DEV, dtype=torch.uint8, generator=g0)
+    one = torch.ones(1, device=DEV)
+    _ops.gemm_select(gemm_kernel)
+    try:
+        for _ in range(2):                                                  # second round: every map comes from the cache
+            for M, N, K in [(512, 768, 1024), (768, 512, 1024), (512, 768, 512), (1024, 384, 2048), (512, 768, 1024)]:
+                a, b = pool_a[:M * K // 2].view(M, K // 2), pool_b[:N * K // 2].view(N, K // 2)
+                sa = pool_sa[:_ops.blocked_scale_bytes(M, K // 16)]
+                sb = pool_sb[:_ops.blocked_scale_bytes(N, K // 16)]
+                got = _ops.nvfp4_gemm(a, sa, one, b, sb, one, out_dtype=torch.float32)
+                want = _ops.nvfp4_gemm(a.clone(), sa.clone(), one, b.clone(), sb.clone(), one, out_dtype=torch.float32)
+                assert torch.equal(got, want), (M, N, K)
+    finally:
+        _ops.gemm_select("auto")
+    assert _ops.gemm_status(0) == 0
+
+
+@ALL_GEMM_KERNELS
 def test_gemm_is_linear_in_row_blocks_at_scale(gemm_kernel):
     """Size-independent property at a layer-sized problem: the product of stacked operands is the stack of products
     (bit for bit: tiles never mix rows), and equal inputs give equal outputs."""

@@ -285,6 +285,38 @@ def test_overlapped_updates_match_step():
         assert torch.equal(o1.state[p]["phase"], o3.state[r]["phase"])
 
 
+@pytest.mark.parametrize("M", [256, 40])
+def test_shared_input_linears_sum_their_input_gradients_in_the_gemm(M):
+    """parallel.shared_input_linears (q/k/v, gate/up in one process): outputs are those of F.linear per weight; the
+    input gradient is the sum of the projections' input gradients in the order of the weights, formed in the GEMM
+    epilogues (rows in multiples of 32) or by dense adds (padded rows) -- the same bits either way -- and the weight
+    gradients are those of the separate layers under the same stochastic-rounding seeds."""
+    from bitlattice_b200 import backend, parallel
+    g = gen(61)
+    ws = [torch.nn.Parameter(bl.LatticeTensor.from_float((torch.randn(n, 256, generator=g) * 0.05).to(DEV), "nvfp4",
+                                                         method="rtn", dtype=torch.bfloat16)) for n in (128, 64, 96)]
+    x = torch.randn(M, 256, generator=g).to(torch.bfloat16).to(DEV).requires_grad_(True)
+    gys = [(torch.randn(M, w.shape[0], generator=g) * 0.1).to(torch.bfloat16).to(DEV) for w in ws]
+    with bl.compute("fp4_all"):
+        ys = parallel.shared_input_linears(x, ws)
+        assert ys[0].grad_fn is ys[1].grad_fn                                # one function for all three
+        for y, w in zip(ys, ws):
+            assert torch.equal(y, torch.nn.functional.linear(x.detach(), w.detach()))
+        backend.set_sr_seed(900)
+        torch.autograd.backward(ys, gys)
+        # the same by hand: three input-gradient GEMMs (seeds 900..902), dense adds, three weight-gradient GEMMs (903..905)
+        backend.set_sr_seed(900)
+        recipe = backend.FP4_RECIPES["nvidia"]
+        parts = [backend.fp4_dgrad(gy, w, recipe) for gy, w in zip(gys, ws)]
+        want_gx = (parts[0][0] + parts[1][0]) + parts[2][0]
+        _, xt = backend._shared(x, recipe, "fwd+t", lambda: pytest.fail("the forward's operands should still be shared"))
+        want_gw = [backend.fp4_wgrad(p[1], p[2], xt, w, recipe) for p, w in zip(parts, ws)]
+    assert torch.equal(x.grad, want_gx)
+    for w, gw in zip(ws, want_gw):
+        assert torch.equal(w.grad, gw.to(w.dtype))
+    assert bl._ops.gemm_status(0) == 0
+
+
 def test_batched_step_reuses_its_plan_and_notices_new_storage():
     """step() marshals the static arguments of a batch of parameters once (an update plan) and reuses them; when a
     parameter's state or storage is replaced between steps the plan is rebuilt. Either way the result is that of the
