@@ -61,11 +61,12 @@ OPT = dict(lr=3e-3, direction="colnorm", phase_bits=4, rounding="sr", scale_rule
 BYTES_PER_WEIGHT = 4.125      # codes r+w 1.0, 4-bit phase r+w 1.0, bf16 gradient 2.0, E4M3 scales r+w 0.125
 # DRAM traffic (dram__bytes_read.sum + dram__bytes_write.sum) from ncu captures of small cases, scaled by the units a
 # launch processes (the summaries of those captures are kept with the other profiles of this repository):
-#   update of 12288 x 4096, colnorm: update_kernel 180.6 MB + colstats_kernel 100.9 MB + finalize 1.6 MB for 50.3 M
-#     weights (the update kernel finds part of the gradient in L2 after the statistics pass)
-#   gemm_pair_kernel 8192 x 12288 x K 4096: 157.3 MB for 0.825 TFLOP (operands stream from L2, the output is written)
-NCU_UPDATE_BYTES_PER_WEIGHT = (180.6e6 + 100.9e6 + 1.6e6) / (12288 * 4096)
-NCU_GEMM_BYTES_PER_FLOP = 157.3e6 / (2.0 * 8192 * 12288 * 4096)
+#   update of one layer's seven matrices as a batch (192.9 M weights), colnorm: update_kernel 771.3 MB +
+#     colstats_kernel 394.4 MB + finalize_kernel 6.0 MB
+#   gemm_pair_kernel 4096 x 4096 x K 8192 (a weight-gradient GEMM at 8192 tokens): 171.3 MB for 0.275 TFLOP (operands
+#     stream from L2, the output is written)
+NCU_UPDATE_BYTES_PER_WEIGHT = (771.3e6 + 394.4e6 + 6.0e6) / 192937984
+NCU_GEMM_BYTES_PER_FLOP = 171.3e6 / (2.0 * 4096 * 4096 * 8192)
 
 
 def parse():
@@ -606,7 +607,7 @@ def run_ours(a):
                                 "traffic": NCU_UPDATE_BYTES_PER_WEIGHT * weights / world,
                                 "traffic_note": "bytes per pass and GPU (update, column statistics and their "
                                                 "reduction), scaled by weights from the ncu capture of one "
-                                                "12288 x 4096 update",
+                                                "layer's seven matrices updated as a batch",
                                 "peak_note": f"per GPU against copy bandwidth ({peaks['source']}); nominal 8000"}},
     }
     if extra:
