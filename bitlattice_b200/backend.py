@@ -37,27 +37,27 @@ __all__ = ["FP4_RECIPES", "Fp4Operand", "Fp4Recipe", "as_recipe", "clear_shared"
            "set_sr_seed", "to_blocked", "weight_operand", "weight_t_operand", "weight_t_rotated_operand"]
 
 
+_CHOICES = {"activations": ("rtn", "4over6"), "gradients": ("sr", "eden"), "rotation": (16, 128),
+            "select": ("mse", "mae"), "dgrad_weight": ("requantize", "cached"), "dgrad_scale": ("current", "bound"),
+            "scale_source": ("current", "delayed")}
+
+
 @dataclass(frozen=True)
 class Fp4Recipe:
-    """Quantization of the GEMM operands under the FP4 policies (reference: bitlattice/backend.py:57-121).
+    """How the three GEMMs of a layer get their NVFP4 operands (field names, values and error messages are the
+    reference's, bitlattice/backend.py:57-121).
 
-    activations      'rtn' | '4over6'   forward input: round to nearest, with four-over-six block scales or not
-    gradients        'sr' | 'eden'      output gradient in backward: stochastic rounding, or MS-EDEN (round to nearest
-                                        plus stochastically rounded, bias-correcting block scales; needs rotation=128)
-    rotation         16 | 128           randomized Hadamard block along the token axis of the weight-gradient GEMM
-    rotate_dgrad     bool               also rotate (128) the output-feature axis of the input-gradient GEMM
-    backward_4over6  bool               four-over-six block scales for the backward operands too
-    select           'mse' | 'mae'      four-over-six criterion
-    dgrad_weight     'requantize' | 'cached'   with rotate_dgrad: the rotated W^T re-quantized in every backward, or
-                                        once per weight version (round to nearest, one rotation per version)
-    dgrad_scale      'current' | 'bound'   cached W^T per-tensor scale: from an amax pass over the rotated weight, or
-                                        the bound sqrt(128) * W.global_scale
-    scale_source     'current' | 'delayed'   per-tensor scales from an amax pass over the operand (exact), or from
-                                        the amax the previous call of the same layer saw (times scale_margin; no
-                                        extra pass; values beyond the range saturate). Applies to the operands of
-                                        the 128-rotation recipes; the first call of a layer is exact
-    scale_margin     float              headroom of delayed scales
-    """
+    Forward: ``activations`` -- plain round to nearest, or '4over6' (every block picks the better of two block scales,
+    judged by ``select``). Backward: ``gradients`` -- the output gradient stochastically rounded ('sr'), or MS-EDEN
+    ('eden': nearest codes with block scales that are rounded stochastically so that the product stays unbiased;
+    only with the 128-point rotation); ``backward_4over6`` extends the two-candidate block scales to the backward
+    operands. ``rotation`` is the size of the randomized Hadamard block applied along the token axis of both
+    weight-gradient operands; ``rotate_dgrad`` rotates the output-feature axis of both input-gradient operands the
+    same way. With ``rotate_dgrad`` the rotated W^T is made anew in every backward ('requantize') or once per weight
+    version ('cached'), its per-tensor scale then coming from a pass over the rotated weight ('current') or from the
+    bound sqrt(128) * W.global_scale ('bound'). ``scale_source='delayed'`` takes the per-tensor scales of the rotated
+    operands from the maximum the same layer saw one call earlier, times ``scale_margin``, which saves the amax pass
+    (the first call is exact; later values beyond the range saturate)."""
 
     activations: str = "rtn"
     gradients: str = "sr"
@@ -71,25 +71,14 @@ class Fp4Recipe:
     scale_margin: float = 2.0
 
     def __post_init__(self):
-        if self.activations not in ("rtn", "4over6"):
-            raise ValueError("activations must be 'rtn' or '4over6'")
-        if self.gradients not in ("sr", "eden"):
-            raise ValueError("gradients must be 'sr' or 'eden'")
-        if self.rotation not in (16, 128):
-            raise ValueError("rotation must be 16 or 128")
+        for name, allowed in _CHOICES.items():
+            if getattr(self, name) not in allowed:
+                raise ValueError(f"{name} must be {' or '.join(repr(v) if isinstance(v, str) else str(v) for v in allowed)}")
         if self.gradients == "eden" and self.rotation != 128:
             raise ValueError("MS-EDEN gradients need rotation=128")
-        if self.select not in ("mse", "mae"):
-            raise ValueError("select must be 'mse' or 'mae'")
-        if self.dgrad_weight not in ("requantize", "cached"):
-            raise ValueError("dgrad_weight must be 'requantize' or 'cached'")
-        if self.dgrad_scale not in ("current", "bound"):
-            raise ValueError("dgrad_scale must be 'current' or 'bound'")
-        if self.dgrad_scale == "bound" and not (self.dgrad_weight == "cached" and self.rotate_dgrad
-                                                and self.rotation == 128):
+        bound_ok = self.dgrad_weight == "cached" and self.rotate_dgrad and self.rotation == 128
+        if self.dgrad_scale == "bound" and not bound_ok:
             raise ValueError("dgrad_scale='bound' needs cached weights and the 128-element dgrad rotation")
-        if self.scale_source not in ("current", "delayed"):
-            raise ValueError("scale_source must be 'current' or 'delayed'")
         if not self.scale_margin >= 1.0:
             raise ValueError("scale_margin must be >= 1")
 
@@ -104,22 +93,21 @@ class Fp4Recipe:
         multi-GPU layers that exchange packed operands are written for."""
         return astuple(self)[1:5] + astuple(self)[6:] == _NVIDIA[1:5] + _NVIDIA[6:]
 
+    @property
+    def simple_backward(self) -> bool:
+        """Backward operands of the NVIDIA recipe: stochastic rounding, 16-point rotation, single block scales."""
+        return self.rotation == 16 and self.gradients == "sr" and not self.backward_4over6
+
 
 _NVIDIA = ("rtn", "sr", 16, False, False, "mse", "requantize", "current", "current", 2.0)
+_QUARTET2 = dict(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True)
 
-FP4_RECIPES: dict[str, Fp4Recipe] = {
-    "nvidia": Fp4Recipe(),
-    "4over6": Fp4Recipe(activations="4over6"),
-    "quartet2": Fp4Recipe(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True),
-    "quartet2_4o6": Fp4Recipe(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True,
-                              backward_4over6=True),
-    "quartet2_fast": Fp4Recipe(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True,
-                               dgrad_weight="cached"),
-    "quartet2_delayed": Fp4Recipe(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True,
-                                  dgrad_weight="cached", scale_source="delayed"),
-    "quartet2_bound": Fp4Recipe(activations="4over6", gradients="eden", rotation=128, rotate_dgrad=True,
-                                dgrad_weight="cached", dgrad_scale="bound"),
-}
+FP4_RECIPES: dict[str, Fp4Recipe] = {"nvidia": Fp4Recipe(), "4over6": Fp4Recipe(activations="4over6")}
+for _name, _extra in (("quartet2", {}), ("quartet2_4o6", dict(backward_4over6=True)),
+                      ("quartet2_fast", dict(dgrad_weight="cached")),
+                      ("quartet2_delayed", dict(dgrad_weight="cached", scale_source="delayed")),
+                      ("quartet2_bound", dict(dgrad_weight="cached", dgrad_scale="bound"))):
+    FP4_RECIPES[_name] = Fp4Recipe(**_QUARTET2, **_extra)
 
 
 def as_recipe(r) -> Fp4Recipe:
@@ -393,38 +381,38 @@ def _site(w, role: str) -> dict:
 
 def _q2(x2: torch.Tensor, row: dict | None, col: dict | None, recipe: Fp4Recipe, site: dict | None = None):
     """Row and column (x2^T) operands of x2; ``row`` / ``col``: keyword arguments of ``_q`` for that side, or None.
-    With ``scale_source='delayed'`` and a ``site`` the per-tensor scales come from the amax the site's previous call
-    saw, times the margin (the first call, and a side first used later, are exact), and the amax seen now is kept
-    (reference: bitlattice/backend.py:419-443; there one kernel makes both layouts from one read, here the general
-    quantizer runs once per side)."""
+
+    Delayed scales (``scale_source='delayed'``, reference: bitlattice/backend.py:419-443): ``site`` remembers, per
+    side, the largest magnitude the quantizer saw in the previous call. Once every side asked for has such a record,
+    its per-tensor scale is record * margin / (6 * top) -- rounded up to a power of two where the side wants one --
+    and no amax pass runs; until then the call is exact. Every call leaves its own maxima in the record. (The
+    reference makes both layouts in one kernel from one read; here the general quantizer runs once per side.)"""
     sides = (row, col)
-    on = (row is not None, col is not None)
-    given = [None, None]
+    delayed = recipe.scale_source == "delayed" and site is not None
+    scale = [None, None]
     seen = None
-    if recipe.scale_source == "delayed" and site is not None:
-        hist, known = site.get("amax"), site.get("known", (False, False))
-        if hist is not None and all(known[i] for i in range(2) if on[i]):
-            for i in range(2):
-                if on[i]:
-                    f = recipe.scale_margin / (6.0 * (256.0 if sides[i].get("four_over_six") else 448.0))
-                    gv = (hist[i:i + 1] * f).clamp_min(1e-30)               # device ops only, no synchronisation
-                    if sides[i].get("pow2"):                                # concatenated operands: powers of two
-                        gv = torch.exp2(torch.ceil(torch.log2(gv)))
-                    given[i] = gv
+    if delayed:
+        record, have = site.get("amax"), site.get("known", (False, False))
+        if record is not None and all(have[i] for i, kw in enumerate(sides) if kw is not None):
+            for i, kw in enumerate(sides):
+                if kw is None:
+                    continue
+                top = 256.0 if kw.get("four_over_six") else 448.0
+                g = (record[i:i + 1] * (recipe.scale_margin / (6.0 * top))).clamp_min(1e-30)    # stays on the device
+                scale[i] = torch.exp2(torch.ceil(torch.log2(g))) if kw.get("pow2") else g
         seen = torch.zeros(2, dtype=torch.float32, device=x2.device)
-    ops = []
+    out = [None, None]
     for i, kw in enumerate(sides):
-        if kw is None:
-            ops.append(None)
-            continue
-        ops.append(_q(x2, transpose=i == 1, recipe=recipe, given=given[i],
-                      amax_out=seen[i:i + 1] if seen is not None else None, **kw))
-    if seen is not None:
-        hist = site.get("amax")
-        site["amax"] = seen if hist is None else torch.stack([seen[i] if on[i] else hist[i] for i in range(2)])
-        known = site.get("known", (False, False))
-        site["known"] = (known[0] or on[0], known[1] or on[1])
-    return ops[0], ops[1]
+        if kw is not None:
+            out[i] = _q(x2, transpose=i == 1, recipe=recipe, given=scale[i],
+                        amax_out=None if seen is None else seen[i:i + 1], **kw)
+    if delayed:
+        record, have = site.get("amax"), site.get("known", (False, False))
+        if record is not None:               # a side that did not run keeps its old maximum
+            seen = torch.where(torch.tensor([kw is not None for kw in sides], device=seen.device), seen, record)
+        site["amax"] = seen
+        site["known"] = tuple(h or kw is not None for h, kw in zip(have, sides))
+    return out[0], out[1]
 
 
 # one quantization per input shared by its consumers (q / k / v, gate / up); reference: backend.py:471-499
@@ -524,107 +512,116 @@ def fp4_wgrad(g2p: torch.Tensor, gq: Fp4Operand | None, xt: Fp4Operand, w, recip
         return fp4_mm(gt, xt, w.dtype)
 
 
+def _rotated_weight_t(w, recipe: Fp4Recipe, mode: str, seed: int | None) -> Fp4Operand:
+    """The W^T operand of a rotated input-gradient GEMM: the per-version cache ('cached' recipes, ``seed`` None), or
+    a fresh quantization with the rotation ``seed`` -- MS-EDEN when the gradient is (both factors unbiased), else
+    round to nearest."""
+    if seed is None:
+        return weight_t_rotated_operand(w, recipe.backward_4over6, scale_source=recipe.dgrad_scale)
+    return _q(None, mode="eden" if mode == "eden" else "rtn", four_over_six=recipe.backward_4over6, recipe=recipe,
+              rotate_seed=seed, seed=_seed(), w=w)
+
+
 def fp4_backward(gy: torch.Tensor, w, xt: Fp4Operand | None, need_x: bool, need_w: bool,
                  recipe: Fp4Recipe = Fp4Recipe(), *, wt: Fp4Operand | None = None, keep: list | None = None):
     """Input and weight gradients of y = x W^T on FP4 tensor cores (reference: bitlattice/backend.py:560-634).
-    NVIDIA recipe: gx = Q_sr(gy) Q(W^T)^T, gw = Q_sr(rot16(gy^T)) Q(rot16(x^T))^T. 128-rotation recipes: the output
-    gradient is quantized rotated along N for the input gradient (against W^T rotated with the same signs) and
-    rotated along the tokens, with the rotation of the saved x^T, for the weight gradient; the rotations cancel in
-    the products.
 
-    wt     the rotated W^T operand to use (``dgrad_weight='cached'`` recipes; default: the per-version cache)
-    keep   the weight-gradient operands (g^T, x^T) are appended here instead of being multiplied or deferred"""
-    if (wt is not None or keep is not None) and not (
-            recipe.rotation == 128 and recipe.rotate_dgrad and recipe.dgrad_weight == "cached"
-            and gy.shape[-1] % 128 == 0 and (xt is None or xt.rotate_seed >= 0)):
-        raise RuntimeError("explicit W^T / kept operands need a 'quartet2_fast'-like recipe and output features in "
-                           "multiples of 128")
-    if recipe.rotation == 16 and not recipe.backward_4over6 and recipe.gradients == "sr" and not _defer_wgrad[0]:
+    NVIDIA-recipe operands: gx = Q_sr(gy) Q(W^T)^T and gw = Q_sr(rot16(gy^T)) Q(rot16(x^T))^T. The 128-rotation
+    recipes quantize the output gradient twice as well: along N, rotated with the signs of the W^T operand it meets,
+    and along the tokens, rotated with the signs of the saved x^T; each rotation cancels in its product. Layers whose
+    N is not a multiple of 128 cannot rotate along N and fall back to the unrotated input-gradient operands.
+
+    ``wt``: the rotated W^T operand to use instead of the per-version cache; ``keep``: a list that receives the
+    weight-gradient operands (g^T, x^T) instead of their product. Both need a recipe with cached rotated weights and
+    N in multiples of 128."""
+    N = gy.shape[-1]
+    rotated_dgrad = recipe.rotation == 128 and recipe.rotate_dgrad and N % 128 == 0
+    if wt is not None or keep is not None:
+        if not (rotated_dgrad and recipe.dgrad_weight == "cached" and (xt is None or xt.rotate_seed >= 0)):
+            raise RuntimeError("explicit W^T / kept operands need a 'quartet2_fast'-like recipe and output features "
+                               "in multiples of 128")
+    if recipe.simple_backward and not _defer_wgrad[0]:
         gx = gw = gq = g2p = None
         if need_x:
             gx, g2p, gq = fp4_dgrad(gy, w, recipe)
         if need_w:
             if g2p is None:
-                g2p = _pad_rows(gy.reshape(-1, gy.shape[-1]), 32).contiguous()
+                g2p = _pad_rows(gy.reshape(-1, N), 32).contiguous()
             gw = fp4_wgrad(g2p, gq, xt, w, recipe)
         return gx, gw
-    N = gy.shape[-1]
+
     g2 = gy.reshape(-1, N)
     M = g2.shape[0]
     g2p = _pad_rows(g2, _pad_to(recipe)).contiguous()
-    gx = gw = gq = None
-    b46 = recipe.backward_4over6
-    rotated_w = need_w and xt.rotate_seed >= 0
+    fos = recipe.backward_4over6
     mode = "eden" if recipe.gradients == "eden" else "sr"
-    if N % 128 == 0 and (rotated_w or not need_w) and (recipe.rotate_dgrad or not need_x):
-        if need_x and recipe.dgrad_weight == "cached" and wt is None:
-            wt = weight_t_rotated_operand(w, b46, scale_source=recipe.dgrad_scale)
+    rotated_wgrad = need_w and xt.rotate_seed >= 0
+    gx = gw = rows = cols = None
+
+    # ---- the operands of the output gradient
+    both_rotated = N % 128 == 0 and (rotated_wgrad or not need_w) and (rotated_dgrad or not need_x)
+    if need_x and rotated_dgrad:
+        cached = recipe.dgrad_weight == "cached"
+        if wt is None and cached:
+            wt = _rotated_weight_t(w, recipe, mode, None)
         r = wt.rotate_seed if wt is not None else _seed()
-        seed_row, seed_col = _seed(), _seed()
-        gq, gt = _q2(g2p,
-                     dict(mode=mode, four_over_six=b46, rotate_seed=r, seed=seed_row) if need_x else None,
-                     dict(mode=mode, four_over_six=b46, rotate_seed=xt.rotate_seed, seed=seed_col, pow2=True)
-                     if need_w else None, recipe, _site(w, "g"))
-        if need_x:
-            if wt is None:      # W^T: MS-EDEN with MS-EDEN gradients (both factors unbiased), else round to nearest
-                wt = _q(None, mode="eden" if mode == "eden" else "rtn", four_over_six=b46, recipe=recipe,
-                        rotate_seed=r, seed=_seed(), w=w)
-            gx = fp4_mm(gq, wt, gy.dtype)[:M]
-        if need_w:
-            if keep is not None:
-                keep.append((gt, xt))
-            else:
-                gw = _weight_grad(w, gt, xt)
-        return gx, gw
+        rows = dict(mode=mode, four_over_six=fos, rotate_seed=r, seed=_seed())
+    if rotated_wgrad:
+        cols = dict(mode=mode, four_over_six=fos, rotate_seed=xt.rotate_seed, seed=_seed(), pow2=True)
+    if both_rotated:                   # one site for both layouts of gy (delayed scales live there)
+        gq, gt = _q2(g2p, rows, cols, recipe, _site(w, "g"))
+    else:
+        gq = _q(g2p, recipe=recipe, **rows) if rows is not None else None
+        gt = _q(g2p, transpose=True, recipe=recipe, **cols) if cols is not None else None
+
+    # ---- input gradient
     if need_x:
-        if recipe.rotate_dgrad and N % 128 == 0:
-            wt = (weight_t_rotated_operand(w, b46, scale_source=recipe.dgrad_scale)
-                  if recipe.dgrad_weight == "cached" else None)
-            r = wt.rotate_seed if wt is not None else _seed()
-            gq = _q(g2p, mode=mode, four_over_six=b46, recipe=recipe, rotate_seed=r, seed=_seed())
+        if rotated_dgrad:
             if wt is None:
-                wt = _q(None, mode="eden" if mode == "eden" else "rtn", four_over_six=b46, recipe=recipe,
-                        rotate_seed=r, seed=_seed(), w=w)
+                wt = _rotated_weight_t(w, recipe, mode, rows["rotate_seed"])
             gx = fp4_mm(gq, wt, gy.dtype)[:M]
-            gq = None                                     # rotated: its per-tensor scale does not bound g^T
+            gq = None                                  # rotated: its per-tensor scale says nothing about g^T
         else:
-            gq = (_q(g2p, mode="sr", four_over_six=True, recipe=recipe, seed=_seed()) if b46
+            gq = (_q(g2p, mode="sr", four_over_six=True, recipe=recipe, seed=_seed()) if fos
                   else quantize_fp4(g2p, stochastic=True))
             gx = fp4_mm(gq, weight_t_operand(w), gy.dtype)[:M]
+
+    # ---- weight gradient
     if need_w:
-        if xt.rotate_seed >= 0:                                                        # g^T rotated (128), [N, Mp]
-            gt = _q(g2p, transpose=True, mode=mode, four_over_six=b46, recipe=recipe, rotate_seed=xt.rotate_seed,
-                    seed=_seed(), pow2=True)
-        else:
+        if not rotated_wgrad:          # the saved x^T carries the 16-point rotation: so must g^T
             if _defer_wgrad[0]:
                 name = getattr(w, "_bl_name", None) or f"weight {tuple(w.shape)}"
                 raise RuntimeError(f"{name}: deferred weight gradients need a recipe with the 128-element rotation "
                                    "(e.g. 'quartet2_fast'); this layer's recipe rotates by 16 and its weight-gradient "
                                    "operands cannot be folded")
-            seed = _seed()                                                             # g^T rotated (16), [N, Mp]
-            bound = gq.global_scale * (4.0 * (256.0 / 448.0 if b46 else 1.0)) if gq is not None else None
-            gt = Fp4Operand(*_ops.quantize_nvfp4_t(g2p, _hadamard16(g2p.device, torch.float32), seed, 0, bound,
+            bound = gq.global_scale * (4.0 * (256.0 / 448.0 if fos else 1.0)) if gq is not None else None
+            gt = Fp4Operand(*_ops.quantize_nvfp4_t(g2p, _hadamard16(g2p.device, torch.float32), _seed(), 0, bound,
                                                    blocked=True), True)
-            return gx, fp4_mm(gt, xt, w.dtype)                  # not power-of-two scaled: never deferred
-        gw = _weight_grad(w, gt, xt)
+            return gx, fp4_mm(gt, xt, w.dtype)
+        if keep is not None:
+            keep.append((gt, xt))
+        else:
+            gw = _weight_grad(w, gt, xt)
     return gx, gw
 
 
-# deferred weight gradients (reference: bitlattice/backend.py:637-746)
-# With micro-batches, every backward of a layer adds its weight gradient to .grad from a GEMM over that micro-batch's
-# tokens only. Inside ``defer_wgrad()`` the 128-rotation recipes keep the quantized operands (E^T, x^T: power-of-two
-# per-tensor scales) instead; ``flush_wgrad`` folds their block scales to a common per-tensor scale (exact: powers of
-# two shift E4M3 exponents), concatenates them along the token axis and runs one GEMM over all micro-batches.
+# ---- deferred weight gradients (the role of bitlattice/backend.py:637-746)
+# Under gradient accumulation every micro-batch's backward would run its own weight-gradient GEMM and add a full-size
+# result into .grad. Inside ``defer_wgrad()`` the 128-rotation recipes only remember the quantized operand pairs
+# (g^T, x^T); their per-tensor scales are powers of two by construction, so ``flush_wgrad`` can bring the pieces to the
+# largest scale by shifting the exponents of their block scales (exact unless a block scale leaves E4M3's normal
+# range; those are counted), lay the micro-batches side by side along the token axis and multiply once.
 
-_defer_wgrad = [0]
-_PENDING: OrderedDict = OrderedDict()             # id(param) -> (weakref(param), [(gt, xt), ...])
-_FOLD_ROUNDED: dict = {}                          # device -> int64 counter of block scales that were rounded
-_PIECES: dict = {}
+_defer_wgrad = [0]                               # nesting depth of defer_wgrad()
+_PENDING: OrderedDict = OrderedDict()            # id(parameter) -> (weak reference, list of operand pairs)
+_FOLD_ROUNDED: dict = {}                         # device -> int64 [1]: block scales that were rounded while folding
+_PIECES: dict = {}                               # (tile counts of the pieces, device) -> int32 piece of every column tile
 
 
 @contextlib.contextmanager
 def defer_wgrad():
-    """Keep the weight-gradient operands of FP4 layers instead of computing their gradients (see flush_wgrad)."""
+    """While active, FP4 layers of the 128-rotation recipes keep their weight-gradient operands for ``flush_wgrad``
+    instead of multiplying them."""
     _defer_wgrad[0] += 1
     try:
         yield
@@ -633,72 +630,74 @@ def defer_wgrad():
 
 
 def _weight_grad(w, gt: Fp4Operand, xt: Fp4Operand):
-    if not _defer_wgrad[0]:
+    """g^T x now, or -- deferred -- nothing yet."""
+    if _defer_wgrad[0] == 0:
         return fp4_mm(gt, xt, w.dtype)
-    entry = _PENDING.get(id(w))
-    if entry is None or entry[0]() is not w:
-        entry = _PENDING[id(w)] = (weakref.ref(w), [])
-    entry[1].append((gt, xt))
+    held = _PENDING.get(id(w))
+    if held is None or held[0]() is not w:
+        held = _PENDING[id(w)] = (weakref.ref(w), [])
+    held[1].append((gt, xt))
     return None
 
 
 def _concat(ops: list) -> Fp4Operand:
-    """Operands [rows, K_j] with power-of-two per-tensor scales and tiled block scales -> one operand [rows, sum K_j]
-    with the largest per-tensor scale; the others' block scales are multiplied by g_j / g_max = 2^-k. Exact while the
-    products stay in E4M3's normal range; smaller products are rounded and counted (``fold_rounded``)."""
+    """One operand [rows, K_1 + ... + K_n] from operands [rows, K_j] whose per-tensor scales are powers of two and
+    whose block scales are tiled: the largest per-tensor scale serves all, the block scales of the others are
+    multiplied by their 2^-k in place (``bl_fp4_fold_scales``)."""
     if len(ops) == 1:
         return ops[0]
-    packed = torch.cat([o.packed for o in ops], 1)
     rows = ops[0].packed.shape[0]
-    nr = -(-rows // 128)
-    dev = packed.device
-    count = _FOLD_ROUNDED.get(dev)
-    if count is None:
-        count = _FOLD_ROUNDED[dev] = torch.zeros(1, dtype=torch.int64, device=dev)
-    tiles = [o.scales.view(torch.uint8).view(nr, -1, 512) for o in ops]
-    g = torch.cat([o.global_scale.reshape(1).float() for o in ops])
-    scales = torch.cat(tiles, 1).contiguous()
-    widths = tuple(t.shape[1] for t in tiles)
+    row_tiles = (rows + 127) // 128
+    dev = ops[0].packed.device
+    tiled = [o.scales.view(torch.uint8).view(row_tiles, -1, 512) for o in ops]
+    widths = tuple(t.shape[1] for t in tiled)
     piece = _PIECES.get((widths, dev))
     if piece is None:
-        piece = _PIECES[(widths, dev)] = torch.tensor([j for j, n in enumerate(widths) for _ in range(n)],
-                                                      dtype=torch.int32, device=dev)
-    g_max = _ops.fp4_fold_scales(scales.view(-1), nr, piece, g, count)
-    return Fp4Operand(packed, scales.view(-1), g_max, True)
+        piece = _PIECES[(widths, dev)] = torch.repeat_interleave(
+            torch.arange(len(widths), dtype=torch.int32), torch.tensor(widths)).to(dev)
+    counter = _FOLD_ROUNDED.get(dev)
+    if counter is None:
+        counter = _FOLD_ROUNDED[dev] = torch.zeros(1, dtype=torch.int64, device=dev)
+    scales = torch.cat(tiled, 1).contiguous()
+    g_all = torch.cat([o.global_scale.reshape(1).float() for o in ops])
+    g_max = _ops.fp4_fold_scales(scales.view(-1), row_tiles, piece, g_all, counter)
+    return Fp4Operand(torch.cat([o.packed for o in ops], 1), scales.view(-1), g_max, True)
 
 
 def fold_rounded(reset: bool = False) -> int:
-    """Number of NVFP4 blocks whose scale was rounded when deferred weight-gradient operands of micro-batches with
-    different magnitudes were folded into one GEMM (0: the deferred gradients were exact). Synchronizes."""
-    n = int(sum(int(c.item()) for c in _FOLD_ROUNDED.values()))
+    """How many block scales had to be rounded so far when deferred operands of unequal magnitude were folded (0: every
+    deferred gradient was exactly the product of its operands). Reads device counters: synchronizes."""
+    total = sum(int(c.item()) for c in _FOLD_ROUNDED.values())
     if reset:
         for c in _FOLD_ROUNDED.values():
             c.zero_()
-    return n
+    return total
 
 
 def pending_wgrad() -> list:
-    """Parameters with deferred weight gradients."""
-    return [ref() for ref, _ in _PENDING.values() if ref() is not None]
+    """The parameters whose weight gradients are waiting in ``flush_wgrad``'s queue."""
+    alive = (ref() for ref, _ in _PENDING.values())
+    return [p for p in alive if p is not None]
 
 
 def flush_wgrad(params=None, optimizer=None) -> int:
-    """Compute deferred weight gradients (all, or of ``params``) with one GEMM per parameter, add them to ``.grad``
-    and, for a fused-backward optimizer, apply its update. Returns the number of parameters flushed."""
-    keys = list(_PENDING) if params is None else [id(p) for p in params if id(p) in _PENDING]
-    n = 0
-    for k in keys:
-        ref, items = _PENDING.pop(k)
+    """One weight-gradient GEMM per parameter over everything deferred for it (all parameters, or ``params``), added
+    to ``.grad``; a ``fused_backward`` optimizer then updates the parameter right away. Returns how many parameters
+    received a gradient."""
+    wanted = list(_PENDING) if params is None else [id(p) for p in params if id(p) in _PENDING]
+    done = 0
+    for key in wanted:
+        ref, pairs = _PENDING.pop(key)
         p = ref()
-        if p is None or not items:
+        if p is None or not pairs:
             continue
-        gt = _concat([a for a, _ in items])
-        xt = _concat([b for _, b in items])
-        items.clear()
-        gw = fp4_mm(gt, xt, p.dtype)
-        del gt, xt
-        p.grad = gw if p.grad is None else p.grad.add_(gw)
-        if optimizer is not None and getattr(optimizer, "fused_backward", False):
+        gw = fp4_mm(_concat([g for g, _ in pairs]), _concat([x for _, x in pairs]), p.dtype)
+        pairs.clear()
+        if p.grad is None:
+            p.grad = gw
+        else:
+            p.grad.add_(gw)
+        if getattr(optimizer, "fused_backward", False):
             optimizer._on_grad(p)
-        n += 1
-    return n
+        done += 1
+    return done
