@@ -207,6 +207,14 @@ __device__ __forceinline__ f32x2 fma2p(f32x2 a, f32x2 b, f32x2 c) {
   asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(c));
   return r;
 }
+// a * b per lane, rounded once, for products that FEED A SUM: written as a fused multiply-add with a +0 addend, which
+// the assembler can neither merge with the following add (it would have to fuse two roundings) nor turn back into a
+// plain multiply (the +0 turns a product of -0 into +0). Only for uses where the sign of a zero product cannot matter.
+__device__ __forceinline__ f32x2 prod2p(f32x2 a, f32x2 b) {
+  f32x2 r;
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(r) : "l"(a), "l"(b), "l"(0ull));
+  return r;
+}
 // x / y per lane from ny = -y and ry = rcp_rn(y): div_rn without its range check (the caller establishes the range)
 __device__ __forceinline__ f32x2 div2p(f32x2 x, f32x2 ny, f32x2 ry) {
   const f32x2 q0 = mul2p(x, ry);

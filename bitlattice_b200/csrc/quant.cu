@@ -664,6 +664,14 @@ __global__ void selftest_division_kernel(uint64_t n, uint32_t seed, unsigned lon
     upk(add2p(pk(__fmul_rn(x, y), __fmul_rn(x2, y)), pk(x2, x)), c0, c1);
     bad += __float_as_uint(c0) != __float_as_uint(__fadd_rn(__fmul_rn(x, y), x2));
     bad += __float_as_uint(c1) != __float_as_uint(__fadd_rn(__fmul_rn(x2, y), x));
+    // ... or by prod2p (a fused multiply-add with a +0 addend), which keeps its own rounding as well
+    float e0, e1;
+    upk(add2p(prod2p(pk(x, x2), pk(y, y)), pk(x2, x)), e0, e1);
+    bad += __float_as_uint(e0) != __float_as_uint(__fadd_rn(__fmul_rn(x, y), x2));
+    bad += __float_as_uint(e1) != __float_as_uint(__fadd_rn(__fmul_rn(x2, y), x));
+    upk(add2p(pk(x2, x), prod2p(pk(x, x2), pk(x, x2))), e0, e1);
+    bad += __float_as_uint(e0) != __float_as_uint(__fadd_rn(x2, __fmul_rn(x, x)));
+    bad += __float_as_uint(e1) != __float_as_uint(__fadd_rn(x, __fmul_rn(x2, x2)));
   }
   if (bad) atomicAdd(mismatches, bad);
 }

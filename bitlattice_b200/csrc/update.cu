@@ -555,6 +555,7 @@ __global__ void __launch_bounds__(kThreads, 2) update_kernel(const __grid_consta
     const bool fit = P.rule != BL_RULE_FIXED, latent = P.rule == BL_RULE_FIT_LATENT;
     const bool decay_one = P.decay == 1.0f;                   // no weight decay: the products by it are exact copies
     const f32x2 ndiv2 = pk(-div, -div), rdiv2 = pk(__frcp_rn(div), __frcp_rn(div));
+    const f32x2 nlr2 = pk(-P.lr, -P.lr), decay2 = pk(P.decay, P.decay);
 
     // column denominators of the thread's group as pairs (i, i + 8), and the range bounds that depend on them
     f32x2 nden2[DIR == 3 ? 8 : 1], rden2[DIR == 3 ? 8 : 1];
@@ -629,36 +630,30 @@ __global__ void __launch_bounds__(kThreads, 2) update_kernel(const __grid_consta
         }
         const float2 al0 = lutAL[ia], al1 = lutAL[ib];
         const float a0 = al0.x, a1 = al1.x, l0 = al0.y, l1 = al1.y;
-        // Products that feed a sum are scalar (__fmul_rn is never contracted; a packed product followed by a packed
-        // sum would be turned into one fused multiply-add, with one rounding instead of the reference's two).
-        float nl0, nl1;                                          // -(lr * d) of the pair
+        f32x2 nl2;                                               // -(lr * d) of the pair
         if constexpr (DIR == 2) {
           const float g0 = gv[i], g1 = gv[i + 8];
           const float n0 = __uint_as_float(__float_as_uint(nL) ^ (__float_as_uint(g0) & 0x80000000u));
           const float n1 = __uint_as_float(__float_as_uint(nL) ^ (__float_as_uint(g1) & 0x80000000u));
-          nl0 = g0 == 0.0f ? 0.0f : n0;
-          nl1 = g1 == 0.0f ? 0.0f : n1;
+          nl2 = pk(g0 == 0.0f ? 0.0f : n0, g1 == 0.0f ? 0.0f : n1);
         } else {
           const float g0 = gv[i], g1 = gv[i + 8];
           ok = ok && fabsf(g0) >= g_lo && fabsf(g0) <= g_hi && fabsf(g1) >= g_lo && fabsf(g1) <= g_hi;
           f32x2 u = pk(g0, g1);
           if constexpr (DIR == 3) u = div2p(u, nden2[i], rden2[i]);
           if (use_div) u = div2p(u, ndiv2, rdiv2);
-          float d0, d1;
-          upk(div2p(u, nsold2, rsold2), d0, d1);
-          nl0 = __fmul_rn(-P.lr, d0);
-          nl1 = __fmul_rn(-P.lr, d1);
+          nl2 = prod2p(nlr2, div2p(u, nsold2, rsold2));
         }
-        const f32x2 nl2 = pk(nl0, nl1);
-        const f32x2 ld2 = decay_one ? pk(l0, l1) : pk(__fmul_rn(l0, P.decay), __fmul_rn(l1, P.decay));
+        // Products that feed a sum keep their own rounding (prod2p; the sign of a zero product is immaterial: sums
+        // start at +0 and the targets' zeros are normalised when the codes are written).
+        const f32x2 a2 = pk(a0, a1);
+        const f32x2 ld2 = decay_one ? pk(l0, l1) : prod2p(pk(l0, l1), decay2);
         tau2[i] = add2p(ld2, nl2);
         if (fit) {
           f32x2 tf2 = tau2[i];
-          if (!latent) tf2 = add2p(decay_one ? pk(a0, a1) : pk(__fmul_rn(a0, P.decay), __fmul_rn(a1, P.decay)), nl2);
-          float tf0, tf1;
-          upk(tf2, tf0, tf1);
-          sat2 = add2p(sat2, pk(__fmul_rn(a0, tf0), __fmul_rn(a1, tf1)));
-          stt2 = add2p(stt2, pk(__fmul_rn(tf0, tf0), __fmul_rn(tf1, tf1)));
+          if (!latent) tf2 = add2p(decay_one ? a2 : prod2p(a2, decay2), nl2);
+          sat2 = add2p(sat2, prod2p(a2, tf2));
+          stt2 = add2p(stt2, prod2p(tf2, tf2));
         }
       }
 
