@@ -63,10 +63,11 @@ BYTES_PER_WEIGHT = 4.125      # codes r+w 1.0, 4-bit phase r+w 1.0, bf16 gradien
 # launch processes (the summaries of those captures are kept with the other profiles of this repository):
 #   update of one layer's seven matrices as a batch (192.9 M weights), colnorm: update_kernel 771.3 MB +
 #     colstats_kernel 394.4 MB + finalize_kernel 6.0 MB
-#   gemm_pair_kernel 4096 x 4096 x K 8192 (a weight-gradient GEMM at 8192 tokens): 171.3 MB for 0.275 TFLOP (operands
-#     stream from L2, the output is written)
+#   gemm_pair_kernel 8192 x 12288 x K 4096 (the down projection's input-gradient GEMM at 8192 tokens, the captured
+#     launch closest in shape to the workload's): 169.0 MB for 0.825 TFLOP (operands stream from L2, the output is
+#     written)
 NCU_UPDATE_BYTES_PER_WEIGHT = (771.3e6 + 394.4e6 + 6.0e6) / 192937984
-NCU_GEMM_BYTES_PER_FLOP = 171.3e6 / (2.0 * 4096 * 4096 * 8192)
+NCU_GEMM_BYTES_PER_FLOP = 169.0e6 / (2.0 * 8192 * 12288 * 4096)
 
 
 def parse():
