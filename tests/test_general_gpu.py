@@ -100,6 +100,22 @@ def test_observed_amax_with_and_without_a_given_scale():
             assert float(seen.item()) == float(want)
 
 
+@pytest.mark.parametrize("shape,transpose", [((37, 80), False), ((144, 72), True), ((208, 130), True), ((5, 16), False),
+                                             ((16, 5), True)])
+@pytest.mark.parametrize("dtype", [torch.float32, torch.bfloat16])
+def test_ragged_shapes_without_rotation(shape, transpose, dtype):
+    """Shapes that are not made of whole tiles (rows not a multiple of 64, quantized dimension not a multiple of 128,
+    source rows of odd length that take the scalar staging path): every mode without the rotation against the
+    oracle."""
+    g0 = torch.Generator().manual_seed(sum(shape))
+    x = (torch.randn(*shape, generator=g0) * 3.0).to(dtype)
+    xf = x.float().numpy()
+    for kw in (dict(mode="rtn"), dict(mode="sr", seed=3), dict(mode="rtn", four_over_six=True, select="mae")):
+        packed, sb, g = run(x.to(DEV), transpose=transpose, **kw)
+        codes, osb, og = G.quantize(xf, transpose=transpose, **kw)
+        assert g == float(og) and np.array_equal(sb, osb) and np.array_equal(packed, G.pack(codes)), kw
+
+
 def test_blocked_scale_layout_and_ragged_rows():
     x = torch.randn(200, 256, generator=torch.Generator().manual_seed(1)).to(torch.bfloat16).to(DEV)
     p0, s0, g0 = _ops.nvfp4_quantize_general(x, mode="eden", rotate=True, seed=3)
