@@ -50,6 +50,13 @@ __all__ = ["ColumnParallelFp4Linear", "ColumnParallelLinear", "GatheredWeights",
            "token_parallel_linears", "world"]
 
 
+# Column blocks of K the column-parallel backward splits its input-gradient GEMMs into, each block's reduce-scatter
+# running under the GEMMs that follow (same bits as the unsplit backward). 1: not split -- the default, because at two
+# GPUs the split measured slower (3301 against 3497 TFLOP/s on the 8B-class stack: four times the launches on a
+# quarter of the columns each, while the reduce-scatter already hides under the weight-gradient GEMMs).
+COLUMN_BLOCKS = 1
+
+
 def world(group=None) -> tuple[int, int]:
     """(rank, size) of ``group``; (0, 1) when torch.distributed is not initialised."""
     if not (dist.is_available() and dist.is_initialized()):
@@ -206,40 +213,67 @@ class ColumnParallelFp4Linear(torch.autograd.Function):
 
     @staticmethod
     def backward(ctx, *gys):
-        from . import backend
+        from . import _ops, backend
         shape, dtype = ctx.x_meta
         rank, size = world(ctx.group)
         need_x = ctx.needs_input_grad[0]
-        staged, gx_sum = [], None
-        for w, gy in zip(ctx.weights, gys):
-            if gy is None:
-                staged.append(None)
-                continue
-            if need_x:
-                # the partial input gradients of the projections are summed in the GEMM's epilogue (same bits as adding
-                # the tensors) whenever the rows need no padding; otherwise by a dense add
-                rows = gy.numel() // gy.shape[-1]
-                if gx_sum is not None and rows % 32 == 0 and gx_sum.shape[0] == rows and gx_sum.is_contiguous():
-                    _, g2p, gq = backend.fp4_dgrad(gy, w, ctx.recipe, add_to=gx_sum)
+        live = [(w, gy) for w, gy in zip(ctx.weights, gys) if gy is not None]
+        K = ctx.weights[0].shape[1]
+        rows = live[0][1].numel() // live[0][1].shape[-1] if live else 0
+        blocks = COLUMN_BLOCKS if (need_x and live and rows % (32 * size) == 0 and K % (COLUMN_BLOCKS * 128) == 0
+                                   and rows * K >= (1 << 24)) else 1
+        staged, gx_sum, gx_out, works, parts = {}, None, None, [], []
+        if need_x and blocks > 1:
+            # The input-gradient partial [M, K] is formed in column blocks of K: for every block the GEMMs of all
+            # projections (the first writes, the others add in their epilogues), then its reduce-scatter is started
+            # and runs under the GEMMs of the next blocks and under the weight-gradient GEMMs. A column block of the
+            # product needs the matching rows of W^T: a contiguous slice of its codes and of its tiled scales.
+            for w, gy in live:
+                g2p = gy.reshape(-1, gy.shape[-1]).contiguous()
+                staged[id(w)] = (g2p, backend.quantize_fp4(g2p, stochastic=True))
+            Kb = K // blocks
+            for b in range(blocks):
+                buf = torch.empty(rows, Kb, dtype=dtype, device=live[0][1].device)
+                for n, (w, gy) in enumerate(live):
+                    gq, wt = staged[id(w)][1], backend.weight_t_operand(w)
+                    tile_bytes = wt.scales.numel() // (K // 128)                # tiled scales of 128 rows of W^T
+                    _ops.nvfp4_gemm(gq.packed, gq.scales, gq.global_scale, wt.packed[b * Kb:(b + 1) * Kb],
+                                    wt.scales[b * (Kb // 128) * tile_bytes:(b + 1) * (Kb // 128) * tile_bytes],
+                                    wt.global_scale, dtype, out=buf, accumulate=n > 0)
+                part = torch.empty(rows // size, Kb, dtype=dtype, device=buf.device)
+                works.append((dist.reduce_scatter_tensor(part, buf, op=dist.ReduceOp.SUM, group=ctx.group,
+                                                         async_op=True), buf))
+                parts.append(part)
+        else:
+            for w, gy in live:
+                if need_x:
+                    # the partial input gradients of the projections are summed in the GEMM's epilogue (same bits as
+                    # adding the tensors) whenever the rows need no padding; otherwise by a dense add
+                    if gx_sum is not None and rows % 32 == 0 and gx_sum.shape[0] == rows and gx_sum.is_contiguous():
+                        _, g2p, gq = backend.fp4_dgrad(gy, w, ctx.recipe, add_to=gx_sum)
+                    else:
+                        gx, g2p, gq = backend.fp4_dgrad(gy, w, ctx.recipe)
+                        gx_sum = gx if gx_sum is None else gx_sum.add_(gx)
                 else:
-                    gx, g2p, gq = backend.fp4_dgrad(gy, w, ctx.recipe)
-                    gx_sum = gx if gx_sum is None else gx_sum.add_(gx)
-            else:
-                g2p, gq = backend._pad_rows(gy.reshape(-1, gy.shape[-1]), 32).contiguous(), None
-            staged.append((g2p, gq))
-        gx_out = work = None
-        if gx_sum is not None:
-            gx_sum = gx_sum.to(dtype).contiguous()
-            gx_out = torch.empty(gx_sum.shape[0] // size, gx_sum.shape[1], dtype=dtype, device=gx_sum.device)
-            work = dist.reduce_scatter_tensor(gx_out, gx_sum, op=dist.ReduceOp.SUM, group=ctx.group, async_op=True)
+                    g2p, gq = backend._pad_rows(gy.reshape(-1, gy.shape[-1]), 32).contiguous(), None
+                staged[id(w)] = (g2p, gq)
+            if gx_sum is not None:
+                gx_sum = gx_sum.to(dtype).contiguous()
+                gx_out = torch.empty(gx_sum.shape[0] // size, gx_sum.shape[1], dtype=dtype, device=gx_sum.device)
+                works.append((dist.reduce_scatter_tensor(gx_out, gx_sum, op=dist.ReduceOp.SUM, group=ctx.group,
+                                                         async_op=True), gx_sum))
         gws = []
-        for i, (w, st) in enumerate(zip(ctx.weights, staged)):
+        for i, (w, gy) in enumerate(zip(ctx.weights, gys)):
+            st = staged.get(id(w)) if gy is not None else None
             if st is None or not ctx.needs_input_grad[3 + i] or ctx.xt is None:
                 gws.append(None)
                 continue
             gws.append(backend.fp4_wgrad(st[0], st[1], ctx.xt.get(), w, ctx.recipe).to(w.dtype))
-        if work is not None:
+        for work, _ in works:
             work.wait()
+        if parts:
+            gx_out = torch.cat(parts, 1)
+        if gx_out is not None:
             gx_out = gx_out.reshape(shape)
         return (gx_out, None, None, *gws)
 

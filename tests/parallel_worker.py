@@ -156,6 +156,33 @@ def main():
         yo.backward(gyo[:, cols].contiguous())
     assert rel(xso.grad, (gyo.float() @ W)[ro]) < 0.25
     assert rel(po.grad, (gyo.float().t() @ xo.float())[cols]) < 0.25
+    # large enough for the backward to split its input-gradient GEMMs into column blocks whose reduce-scatters run
+    # under the following GEMMs: the same bits as the unsplit backward under the same stochastic-rounding seeds
+    from bitlattice_b200 import parallel
+    Mb, Kb, Nb = 4096 * world, 2048, (256, 128)
+    xb = torch.randn(Mb, Kb, device=dev, generator=gen).to(torch.bfloat16)
+    wbs = [bl.LatticeTensor.from_float(torch.randn(n, Kb, device=dev, generator=gen) * 0.02, "nvfp4", method="rtn",
+                                       dtype=torch.bfloat16) for n in Nb]
+    gbs = [(torch.randn(Mb, n, device=dev, generator=gen) * 1e-2).to(torch.bfloat16) for n in Nb]
+    rb = slice(rank * Mb // world, (rank + 1) * Mb // world)
+    got = {}
+    for blocks in (4, 1):
+        parallel.COLUMN_BLOCKS = blocks
+        backend.set_sr_seed(4242)
+        backend.clear_shared()
+        with bl.compute("fp4_all"):
+            ps = [torch.nn.Parameter(shard_rows(wb, rank, world)) for wb in wbs]
+            xsb = xb[rb].detach().contiguous().requires_grad_(True)
+            ys = column_parallel_linears(xsb, ps, None)
+            torch.autograd.backward(ys, [g[:, rank * n // world:(rank + 1) * n // world].contiguous()
+                                         for g, n in zip(gbs, Nb)])
+        got[blocks] = (xsb.grad, [q.grad for q in ps])
+    parallel.COLUMN_BLOCKS = 1
+    assert torch.equal(got[4][0], got[1][0]), "column blocks change the input gradient"
+    for a, b in zip(got[4][1], got[1][1]):
+        assert torch.equal(a, b)
+    exact = sum(g.float() @ wb.dequantize(torch.float32) for g, wb in zip(gbs, wbs))
+    assert rel(got[4][0], exact[rb]) < 0.25
     token_parallel_checks(rank, world, dev, w, x, gy, w2, gy2)
     assert bl._ops.gemm_status(local) == 0
     dist.barrier()
