@@ -184,6 +184,23 @@ def main():
     exact = sum(g.float() @ wb.dequantize(torch.float32) for g, wb in zip(gbs, wbs))
     assert rel(got[4][0], exact[rb]) < 0.25
     token_parallel_checks(rank, world, dev, w, x, gy, w2, gy2)
+    # a 128-rotation recipe does not exchange packed operands: both patterns take their generic routes (dense
+    # all-gather / reduce-scatter around the local layer) and stay within the reference's bound of the exact gradients
+    from bitlattice_b200.parallel import token_parallel_linear
+    for fn, xin, rsel in ((column_parallel_linear, x[rows].detach().contiguous(), rows),
+                          (token_parallel_linear, x[rows].detach().contiguous(), rows)):
+        with bl.compute("quartet2_fast"):
+            pq = torch.nn.Parameter(shard_rows(w, rank, world))
+            xq_ = xin.clone().requires_grad_(True)
+            if fn is column_parallel_linear:
+                yq = fn(xq_, pq, None)
+                yq.backward(gy[:, cols].contiguous())
+            else:
+                yq = fn(xq_, pq)
+                yq.backward(gy[rows].contiguous())
+        assert rel(xq_.grad, gx_exact[rsel]) < 0.25, (fn.__name__, rel(xq_.grad, gx_exact[rsel]))
+        want_gw = gw_exact[cols]
+        assert rel(pq.grad, want_gw) < 0.25, (fn.__name__, rel(pq.grad, want_gw))
     assert bl._ops.gemm_status(local) == 0
     dist.barrier()
     print(f"OK {rank}", flush=True)
