@@ -56,24 +56,28 @@ PRESETS: dict[str, Compute] = {
 
 
 def as_compute(c) -> Compute | None:
-    if c is None or c == "auto":
-        return None
+    """``c`` as a :class:`Compute`: itself, the preset of that name, or None for 'auto' / None (the weight's own)."""
     if isinstance(c, Compute):
         return c
-    if c not in PRESETS:
-        raise ValueError(f"unknown compute {c!r}; presets: {sorted(PRESETS)}")
-    return PRESETS[c]
+    if c in (None, "auto"):
+        return None
+    try:
+        return PRESETS[c]
+    except KeyError:
+        raise ValueError(f"unknown compute {c!r}; presets: {sorted(PRESETS)}") from None
 
 
-# Process-wide, not thread-local: the backward pass runs on autograd worker threads and must see the forward's setting
+# The innermost ``compute(...)`` block wins over the weights' own settings. One stack for the whole process: backward
+# (and recomputation under checkpointing) runs on autograd's threads and has to see what the forward pass saw
 # (reference: compute_policy.py:100-102).
 _scope: list[Compute] = []
 
 
 @contextlib.contextmanager
 def compute(c):
-    """Every lattice layer computes as ``c`` (a :class:`Compute` or preset name) inside the block."""
-    _scope.append(as_compute(c) or Compute())
+    """Inside the block every lattice layer computes as ``c`` (a :class:`Compute` or the name of a preset)."""
+    chosen = as_compute(c)
+    _scope.append(chosen if chosen is not None else Compute())
     try:
         yield
     finally:
@@ -81,14 +85,17 @@ def compute(c):
 
 
 def route(x: torch.Tensor, w) -> tuple[str, Compute]:
-    """(route, Compute) of a call of the lattice layer with weight ``w`` on input ``x``; RuntimeError when the
-    requirement cannot be met (reference: compute_policy.py:127-137)."""
-    c = _scope[-1] if _scope else getattr(w, "compute", None)
-    if c is None or c.gemm == "exact":
-        return "exact", c or Compute()
-    index = x.device.index if (x.is_cuda and x.device == w.device) else None
-    why = fp4_unfit(w, index, c.backward)
-    if why is not None:
-        name = getattr(w, "_bl_name", None) or f"weight {tuple(w.shape)}"
-        raise RuntimeError(f"{name}: cannot compute as {c.describe()}: {why}")
-    return c.route, c
+    """Which way the layer with weight ``w`` goes for input ``x``: ('exact' | 'fp4' | 'fp4_all', the Compute in
+    force). A setting the weight or the device cannot honour raises RuntimeError with the reason; nothing falls back
+    silently (reference: compute_policy.py:127-137)."""
+    setting = _scope[-1] if _scope else getattr(w, "compute", None)
+    if setting is None:
+        return "exact", Compute()
+    if setting.gemm == "exact":
+        return "exact", setting
+    same_gpu = x.is_cuda and x.device == w.device
+    reason = fp4_unfit(w, x.device.index if same_gpu else None, setting.backward)
+    if reason is None:
+        return setting.route, setting
+    label = getattr(w, "_bl_name", None) or f"weight {tuple(w.shape)}"
+    raise RuntimeError(f"{label}: cannot compute as {setting.describe()}: {reason}")

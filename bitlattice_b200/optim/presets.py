@@ -8,48 +8,52 @@ import torch
 
 __all__ = ["PRESETS", "param_groups"]
 
+# Row bands of 256 over the full width, Gram iteration in fp16 with the Polar Express coefficients: the cheap
+# orthogonalisation of the "_fast" presets.
+_BANDS = dict(block=(256, None), ns_dtype="fp16", ns_coeffs="polar_express")
+
+
+def _orthogonal(phase_bits: int = 2, **extra) -> dict[str, Any]:
+    """Newton-Schulz direction on blocks (512 x 512 unless ``extra`` says otherwise)."""
+    return dict(direction="muon_block", phase_bits=phase_bits, **extra)
+
+
 PRESETS: dict[str, dict[str, Any]] = {
-    # orthogonalised (Newton-Schulz) direction on 512 x 512 blocks, 2-bit phase
-    "muon": dict(direction="muon_block", phase_bits=2),
-    # bands of 256 rows over the full width, Gram iteration in fp16 with the Polar Express coefficients
-    "muon_fast": dict(direction="muon_block", phase_bits=2, block=(256, None), ns_dtype="fp16",
-                      ns_coeffs="polar_express"),
-    # the same with neuron-wise normalisation of the direction (one running mean square per row)
-    "normuon": dict(direction="muon_block", phase_bits=2, normalize="row"),
-    "normuon_fast": dict(direction="muon_block", phase_bits=2, block=(256, None), ns_dtype="fp16",
-                         ns_coeffs="polar_express", normalize="row"),
-    "muon_precise": dict(direction="muon_block", phase_bits=8),
-    # factored second-moment direction with a 1 / 2 / 8-bit phase
-    "light": dict(direction="factored", phase_bits=1),
-    "balanced": dict(direction="factored", phase_bits=2),
-    "precise": dict(direction="factored", phase_bits=8),
-    # no optimizer state at all
+    "muon": _orthogonal(),
+    "muon_fast": _orthogonal(**_BANDS),
+    "normuon": _orthogonal(normalize="row"),                  # one running mean square per row scales the direction
+    "normuon_fast": _orthogonal(**_BANDS, normalize="row"),
+    "muon_precise": _orthogonal(phase_bits=8),
+    # factored second-moment direction, 1 / 2 / 8 bits of phase
+    **{name: dict(direction="factored", phase_bits=bits) for name, bits in (("light", 1), ("balanced", 2), ("precise", 8))},
+    # nothing kept between steps
     "stateless": dict(direction="sinkhorn", vector_direction="sinkhorn", phase_bits=0, rounding="sr"),
 }
 
-_HEADS = ("lm_head", "embed_out", "output", "classifier", "head")
+_HEADS = frozenset(("lm_head", "embed_out", "output", "classifier", "head"))
+
+
+def _bucket(name: str, p: torch.Tensor, embeddings: set[int]) -> str:
+    owner = name.rpartition(".")[0].rpartition(".")[2]
+    if id(p) in embeddings or owner in _HEADS:
+        return "heads"
+    return "matrices" if p.dim() >= 2 else "vectors"
 
 
 def param_groups(model: torch.nn.Module, head_direction: str = "factored", head_momentum: str = "none",
                  no_decay_vectors: bool = True, weight_decay: float = 0.0) -> list[dict]:
-    """Three groups: embeddings and output heads (``head_direction``: orthogonalising a vocabulary-sized matrix is far
-    too expensive), other matrices (the optimizer's defaults), vectors (no weight decay unless asked)."""
-    embedding_ids = {id(m.weight) for m in model.modules() if isinstance(m, torch.nn.Embedding)}
-    buckets: dict[str, list] = {"heads": [], "matrices": [], "vectors": []}
-    seen: set[int] = set()
+    """Parameter groups for ``Lattice``: matrices with the optimizer's defaults; embeddings and output heads with
+    ``head_direction`` / ``head_momentum`` (orthogonalising a vocabulary-sized matrix costs far too much); vectors,
+    which are spared weight decay unless ``no_decay_vectors`` is off. Frozen, shared and meta-device parameters are
+    left out; empty groups are not returned."""
+    embeddings = {id(m.weight) for m in model.modules() if isinstance(m, torch.nn.Embedding)}
+    buckets: dict[str, list] = {"matrices": [], "heads": [], "vectors": []}
+    taken: set[int] = set()
     for name, p in model.named_parameters():
-        if not p.requires_grad or id(p) in seen or p.device.type == "meta":
-            continue
-        seen.add(id(p))
-        owner = name.rsplit(".", 1)[0].rsplit(".", 1)[-1] if "." in name else ""
-        kind = "heads" if id(p) in embedding_ids or owner in _HEADS else "matrices" if p.dim() >= 2 else "vectors"
-        buckets[kind].append(p)
-    groups = []
-    if buckets["matrices"]:
-        groups.append({"params": buckets["matrices"], "weight_decay": weight_decay})
-    if buckets["heads"]:
-        groups.append({"params": buckets["heads"], "direction": head_direction, "momentum": head_momentum,
-                       "weight_decay": weight_decay})
-    if buckets["vectors"]:
-        groups.append({"params": buckets["vectors"], "weight_decay": 0.0 if no_decay_vectors else weight_decay})
-    return groups
+        if p.requires_grad and id(p) not in taken and p.device.type != "meta":
+            taken.add(id(p))
+            buckets[_bucket(name, p, embeddings)].append(p)
+    options = {"matrices": {"weight_decay": weight_decay},
+               "heads": {"direction": head_direction, "momentum": head_momentum, "weight_decay": weight_decay},
+               "vectors": {"weight_decay": 0.0 if no_decay_vectors else weight_decay}}
+    return [{"params": ps, **options[kind]} for kind, ps in buckets.items() if ps]

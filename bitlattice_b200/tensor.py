@@ -151,95 +151,117 @@ class LatticeTensor(torch.Tensor):
 
     @classmethod
     def __torch_dispatch__(cls, func, types, args=(), kwargs=None):
+        """Operators that act on the storage itself are handled part by part (``_STORAGE_OPS``); every other operator
+        sees the dequantized weight."""
         kwargs = kwargs or {}
-        aten = torch.ops.aten
-        if func in (aten.detach.default, aten.alias.default):
-            return args[0]._map(lambda t: t, shares_storage=True)
-        if func is aten.clone.default:
-            wait_for_update(args[0])
-            return args[0]._map(lambda t: t.clone())
-        if func is aten._to_copy.default:
-            src = args[0]
-            device = kwargs.get("device", src.device)
-            dtype = kwargs.get("dtype", src.dtype)
-            keep = dtype if dtype is not None and dtype.is_floating_point else src.dtype
-            wait_for_update(src)
-            return src._map(lambda t: t.to(device), dtype=keep)
-        if func is aten.copy_.default:
-            dst, src = args[0], args[1]
-            wait_for_update(dst)                       # an update still running on another stream finishes first
-            if isinstance(src, LatticeTensor):
-                wait_for_update(src)
-            dst._bl_version = getattr(dst, "_bl_version", 0) + 1          # invalidates derived GEMM operands
-            if not (isinstance(src, LatticeTensor) and src.fmt == dst.fmt):
-                dense = src.dequantize(torch.float32) if isinstance(src, LatticeTensor) else src
-                src = LatticeTensor.from_float(dense.to(dst.device), dst.fmt, method="rtn", dtype=dst.dtype)
-            for k in _PARTS:
-                d, s = getattr(dst, k), getattr(src, k)
-                if d.shape == s.shape:
-                    d.copy_(s)
-                else:
-                    setattr(dst, k, s.to(dst.device).clone())
-            return dst
-        if func is aten.is_same_size.default:
-            return args[0].shape == args[1].shape
+        handler = _STORAGE_OPS.get(func)
+        if handler is not None:
+            return handler(*args, **kwargs)
+        dense = lambda t: t.dequantize() if isinstance(t, LatticeTensor) else t      # noqa: E731
+        return func(*tree_map(dense, args), **tree_map(dense, kwargs))
 
-        def unwrap(t):
-            return t.dequantize() if isinstance(t, LatticeTensor) else t
 
-        return func(*tree_map(unwrap, args), **tree_map(unwrap, kwargs))
+def _view_of(t: LatticeTensor) -> LatticeTensor:
+    """detach / alias: the same storage under a new tensor object (what ``nn.Parameter(t)`` is made of)."""
+    return t._map(lambda part: part, shares_storage=True)
+
+
+def _clone(t: LatticeTensor, **unused) -> LatticeTensor:
+    wait_for_update(t)
+    return t._map(torch.clone)
+
+
+def _to_copy(t: LatticeTensor, *, device=None, dtype=None, **unused) -> LatticeTensor:
+    """``.to(device)`` moves the parts; a floating dtype only changes the logical dtype (the storage has none)."""
+    wait_for_update(t)
+    target = t.device if device is None else device
+    logical = dtype if (dtype is not None and dtype.is_floating_point) else t.dtype
+    return t._map(lambda part: part.to(target), dtype=logical)
+
+
+def _copy_into(dst: LatticeTensor, src, *unused, **unused_kw) -> LatticeTensor:
+    """``dst.copy_(src)``: parts are copied when ``src`` is stored in the same format, else ``src`` (dense, or a lattice
+    tensor of another format) is quantized into ``dst``'s format first. Bumps the weight version."""
+    wait_for_update(dst)                       # an update still running on another stream finishes first
+    if isinstance(src, LatticeTensor):
+        wait_for_update(src)
+    same_format = isinstance(src, LatticeTensor) and src.fmt == dst.fmt
+    if not same_format:
+        values = src.dequantize(torch.float32) if isinstance(src, LatticeTensor) else src
+        src = LatticeTensor.from_float(values.to(dst.device), dst.fmt, method="rtn", dtype=dst.dtype)
+    dst._bl_version = getattr(dst, "_bl_version", 0) + 1          # derived GEMM operands are stale now
+    for name in _PARTS:
+        mine, theirs = getattr(dst, name), getattr(src, name)
+        if mine.shape == theirs.shape:
+            mine.copy_(theirs)
+        else:
+            setattr(dst, name, theirs.to(dst.device).clone())
+    return dst
+
+
+_aten = torch.ops.aten
+_STORAGE_OPS = {
+    _aten.detach.default: _view_of,
+    _aten.alias.default: _view_of,
+    _aten.clone.default: _clone,
+    _aten._to_copy.default: _to_copy,
+    _aten.copy_.default: _copy_into,
+    _aten.is_same_size.default: lambda a, b: a.shape == b.shape,
+}
 
 
 class _LatticeLinear(torch.autograd.Function):
-    """y = x W^T + b for a lattice weight; the route (exact / fp4 / fp4_all) comes from the compute policy
-    (reference: bitlattice/tensor.py:204-288)."""
+    """y = x W^T + b for a lattice weight. The compute policy decides the route when the layer is called
+    (reference: bitlattice/tensor.py:204-288):
+
+      exact    the weight is dequantized; forward and both gradients are dense GEMMs in the activations' dtype
+      fp4      forward on the FP4 tensor cores, gradients as for 'exact'
+      fp4_all  forward and both gradients on the FP4 tensor cores; instead of x the layer saves the quantized,
+               rotated x^T that the weight gradient needs
+    """
 
     @staticmethod
     def forward(ctx, x, w: LatticeTensor, bias):
         from . import backend
         from .compute_policy import route
-        ctx.w = w
-        ctx.has_bias = bias is not None
-        ctx.policy, comp = route(x, w)
-        ctx.recipe = comp.nvfp4                     # backward runs on other threads: keep the forward's choice
-        need_w = ctx.needs_input_grad[1]
-        if ctx.policy == "fp4_all":
-            ctx.x_meta = (x.shape, x.dtype)
-            if need_w:
-                y, xt = backend.fp4_forward_saving(x, w, bias, ctx.recipe)
-                meta = torch.tensor([int(xt.blocked), xt.rotate_seed], dtype=torch.int64)
-                ctx.save_for_backward(xt.packed, xt.scales, xt.global_scale, meta)
-                return y
+        policy, setting = route(x, w)
+        recipe = setting.nvfp4
+        wants_gw = ctx.needs_input_grad[1]
+        # backward may run on another thread, after the caller's compute(...) block has ended: keep what was chosen
+        ctx.w, ctx.policy, ctx.recipe, ctx.bias_grad = w, policy, recipe, bias is not None and ctx.needs_input_grad[2]
+        if policy != "fp4_all":
+            ctx.save_for_backward(x if wants_gw else None)
+            if policy == "fp4":
+                return backend.nvfp4_linear(x, w, bias, recipe)
+            return torch.nn.functional.linear(x, w.dequantize(x.dtype), bias)
+        ctx.x_like = (x.shape, x.dtype)
+        if not wants_gw:
             ctx.save_for_backward()
-            return backend.nvfp4_linear(x, w, bias, ctx.recipe)
-        ctx.save_for_backward(x if need_w else None)
-        if ctx.policy == "fp4":
-            return backend.nvfp4_linear(x, w, bias, ctx.recipe)
-        return torch.nn.functional.linear(x, w.dequantize(x.dtype), bias)
+            return backend.nvfp4_linear(x, w, bias, recipe)
+        y, xt = backend.fp4_forward_saving(x, w, bias, recipe)
+        ctx.xt_flags = (xt.blocked, xt.rotate_seed)
+        ctx.save_for_backward(xt.packed, xt.scales, xt.global_scale)
+        return y
 
     @staticmethod
     def backward(ctx, gy):
         w = ctx.w
-        gb = gy.reshape(-1, gy.shape[-1]).sum(0) if ctx.has_bias and ctx.needs_input_grad[2] else None
+        wants_gx, wants_gw = ctx.needs_input_grad[0], ctx.needs_input_grad[1]
+        g2 = gy.reshape(-1, gy.shape[-1])
+        gb = g2.sum(0) if ctx.bias_grad else None
         if ctx.policy == "fp4_all":
             from . import backend
-            shape, dtype = ctx.x_meta
-            saved = ctx.saved_tensors
-            xt = None
-            if saved:
-                blocked, seed = saved[3].tolist()
-                xt = backend.Fp4Operand(saved[0], saved[1], saved[2], bool(blocked), seed)
-            gx, gw = backend.fp4_backward(gy, w, xt, ctx.needs_input_grad[0],
-                                          ctx.needs_input_grad[1] and xt is not None, ctx.recipe)
-            gx = gx.to(dtype).reshape(shape) if gx is not None else None
-            gw = gw.to(w.dtype) if gw is not None else None
+            shape, dtype = ctx.x_like
+            xt = backend.Fp4Operand(*ctx.saved_tensors, *ctx.xt_flags) if ctx.saved_tensors else None
+            gx, gw = backend.fp4_backward(gy, w, xt, wants_gx, wants_gw and xt is not None, ctx.recipe)
+            if gx is not None:
+                gx = gx.to(dtype).reshape(shape)
+            if gw is not None:
+                gw = gw.to(w.dtype)
             return gx, gw, gb
         (x,) = ctx.saved_tensors
-        W = w.dequantize(gy.dtype)
-        gx = gy @ W if ctx.needs_input_grad[0] else None
-        gw = None
-        if ctx.needs_input_grad[1] and x is not None:
-            gw = (gy.reshape(-1, gy.shape[-1]).t() @ x.reshape(-1, x.shape[-1])).to(w.dtype)
+        gx = gy @ w.dequantize(gy.dtype) if wants_gx else None
+        gw = (g2.t() @ x.reshape(-1, x.shape[-1])).to(w.dtype) if (wants_gw and x is not None) else None
         return gx, gw, gb
 
 
