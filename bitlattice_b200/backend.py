@@ -408,8 +408,8 @@ def _q2(x2: torch.Tensor, row: dict | None, col: dict | None, recipe: Fp4Recipe,
                         amax_out=None if seen is None else seen[i:i + 1], **kw)
     if delayed:
         record, have = site.get("amax"), site.get("known", (False, False))
-        if record is not None:               # a side that did not run keeps its old maximum
-            seen = torch.where(torch.tensor([kw is not None for kw in sides], device=seen.device), seen, record)
+        if record is not None and None in sides:                # a side that did not run keeps its old maximum
+            seen = torch.cat([(seen if kw is not None else record)[i:i + 1] for i, kw in enumerate(sides)])
         site["amax"] = seen
         site["known"] = tuple(h or kw is not None for h, kw in zip(have, sides))
     return out[0], out[1]
