@@ -288,6 +288,65 @@ def lattice_update_many(items, fmt, *, lr: float, weight_decay: float, phase_bit
     _C.Counters.launches += launches.value
 
 
+def lattice_update_shards(items, fmt, exchange, *, lr: float, weight_decay: float, phase_bits: int, phase_cb: int,
+                          rounding: str, strata: int, scale_rule: str, trust: float, trust_lr: float, direction: str,
+                          clip: float = 1.0) -> None:
+    """The fused update of row shards whose direction normalises over the whole weight (colnorm; raw and sign with
+    clip < 1): together the owners of the shards reproduce the unsharded update bit for bit. ``items`` as for
+    ``lattice_update_many`` plus ``row0`` (the shard's first row in the weight) and ``total_rows``. Between the
+    statistics and the update ``exchange(arrays)`` is called with one entry per tensor, ``(panels, first, count)``:
+    ``panels`` is the fp32 [ceil(total_rows / 128), cols] panel array of the whole weight, of which this owner has
+    filled ``panels[first:first + count]``; on return every row must hold its owner's sums (an in-place all-gather,
+    issued on the current stream). A shard starts on a multiple of 128 rows."""
+    if direction not in _DIRECTION:
+        raise RuntimeError(f"direction {direction!r} is outside this build (raw, sign, colnorm are built)")
+    if not _is_nvfp4(fmt):
+        raise RuntimeError("only NVFP4 tensors (no zero points) are built")
+    for lo in range(0, len(items), 40):
+        part = items[lo:lo + 40]
+        n = len(part)
+        gdtype = part[0]["grad"].dtype
+        if gdtype not in _C.DTYPE:
+            raise RuntimeError("gradient: bf16, fp16 or fp32 with rows*cols elements")
+        for it in part:
+            _require(it["packed"], "packed", torch.uint8)
+            _require(it["scales"], "scales")
+            _require(it["global_scale"], "global_scale", torch.float32)
+            if phase_bits > 0:
+                _require(it["phase"], "phase", torch.uint8)
+            G = it["grad"]
+            if G.dtype != gdtype or G.numel() != int(it["rows"]) * int(it["cols"]) or not G.is_cuda or not G.is_contiguous():
+                raise RuntimeError("gradient: a contiguous CUDA tensor of the group's dtype with rows*cols elements")
+        i64 = lambda k: (ctypes.c_int64 * n)(*[int(it[k]) for it in part])
+        ptrs = lambda k: (ctypes.c_void_p * n)(*[it[k].data_ptr() for it in part])
+        rows, cols, row0, total = i64("rows"), i64("cols"), i64("row0"), i64("total_rows")
+        grad = ptrs("grad")
+        dev = part[0]["packed"]
+        need = int(_C.lib().bl_update_shards_scratch_bytes(n, cols, total))
+        scratch = _scratch_for(dev.device, need)
+        offs = (ctypes.c_uint64 * n)()
+        _C.call("bl_update_shard_stats", n, grad, rows, cols, row0, total, _C.DTYPE[gdtype], _DIRECTION[direction],
+                float(clip), _C.ptr(scratch), scratch.numel(), offs, _C.device_of(dev), _C.stream_of(dev))
+        arrays = []
+        for i, it in enumerate(part):
+            panels = (int(it["total_rows"]) + 127) // 128
+            view = scratch[offs[i]:offs[i] + panels * int(it["cols"]) * 4].view(torch.float32).view(panels, int(it["cols"]))
+            arrays.append((view, int(it["row0"]) // 128, (int(it["rows"]) + 127) // 128))
+        exchange(arrays)
+        sj = (ctypes.c_int * n)()
+        strat_k = 1
+        for i, it in enumerate(part):
+            sj[i], strat_k = strat_args(rounding, it["step"], strata)
+        _C.call("bl_nvfp4_lattice_update_shards", n, ptrs("packed"), ptrs("phase") if phase_bits > 0 else None,
+                ptrs("scales"), ptrs("global_scale"), grad, rows, cols, row0, total,
+                (ctypes.c_uint64 * n)(*[int(it["offset"]) & 0xFFFFFFFFFFFFFFFF for it in part]),
+                (ctypes.c_uint32 * n)(*[int(it["seed"]) & 0xFFFFFFFF for it in part]),
+                (ctypes.c_uint32 * n)(*[int(it["step"]) & 0xFFFFFFFF for it in part]), sj, _C.DTYPE[gdtype], phase_bits,
+                phase_cb, float(lr), float(1.0 - lr * weight_decay), _ROUNDING[rounding], strat_k, _RULE[scale_rule],
+                float(kappa(trust, trust_lr, lr)), _DIRECTION[direction], float(clip), _C.ptr(scratch), scratch.numel(),
+                _C.device_of(dev), _C.stream_of(dev))
+
+
 def direction(G, kind: str, r=None, c=None, k: int = 1, beta2: float = 0.95, block=0, ns_steps: int = 5,
               ns_dtype: str = "bf16", sinkhorn_iters: int = 2, clip: float = 1.0, **unused) -> torch.Tensor:
     """Update direction as float32 [rows, cols], RMS clipped to ``clip`` (reference: bitlattice/_ops.py:110-144).

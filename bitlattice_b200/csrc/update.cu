@@ -55,6 +55,9 @@ struct TensorDesc {
   uint32_t offset, key;     // RNG: index of element (0, 0) and hash key of (seed, step)
   float strat_j;
   uint32_t scratch256;      // offset of the tensor's scratch region in the batch scratch, in units of 256 bytes
+  // A row shard whose statistics cover the whole weight: stat_rows = rows of the whole weight, stat_panel0 = the
+  // shard's first 128-row panel in it. Everything else: stat_rows = rows, stat_panel0 = 0.
+  int stat_rows, stat_panel0;
 };
 
 struct Batch {
@@ -81,7 +84,7 @@ __device__ __forceinline__ ScratchDev scratch_of(unsigned char* base, const Tens
   auto up = [](size_t n) { return (n + 255) & ~size_t(255); };
   ScratchDev s;
   s.partial = reinterpret_cast<float*>(p);
-  p += up(static_cast<size_t>(stats_panels(t.rows)) * t.cols * 4);
+  p += up(static_cast<size_t>(stats_panels(t.stat_rows)) * t.cols * 4);
   s.denom = reinterpret_cast<float*>(p);
   p += up(static_cast<size_t>(t.cols) * 4);
   s.chunk = reinterpret_cast<double*>(p);
@@ -158,7 +161,7 @@ __global__ void __launch_bounds__(kThreads) colstats_kernel(const __grid_constan
     float tot = 0.0f;
 #pragma unroll
     for (int w = 0; w < kPanelRows / kSubRows; ++w) tot = tot + sub[w][threadIdx.x];
-    scratch_of(scratch, T, ti).partial[static_cast<int64_t>(panel) * T.cols + c] = tot;
+    scratch_of(scratch, T, ti).partial[static_cast<int64_t>(panel + T.stat_panel0) * T.cols + c] = tot;
   }
 }
 
@@ -179,7 +182,7 @@ __global__ void __launch_bounds__(256) finalize_kernel(const __grid_constant__ B
   }
   const TensorDesc& T = B.t[ti];
   const ScratchDev S = scratch_of(scratch, T, ti);
-  const int npanels = stats_panels(T.rows);
+  const int npanels = stats_panels(T.stat_rows);
   const int nchunks = stats_col_chunks(T.cols);
   const int c = blk * 256 + threadIdx.x;
   double colu = 0.0;
@@ -187,7 +190,7 @@ __global__ void __launch_bounds__(256) finalize_kernel(const __grid_constant__ B
     float tot = 0.0f;
     for (int p = 0; p < npanels; ++p) tot = tot + S.partial[static_cast<int64_t>(p) * T.cols + c];
     if (colnorm) {
-      const float d = sqrtf(tot / static_cast<float>(T.rows)) + 1e-30f;
+      const float d = sqrtf(tot / static_cast<float>(T.stat_rows)) + 1e-30f;
       S.denom[c] = d;
       colu = static_cast<double>(tot / (d * d));
     } else {
@@ -210,7 +213,7 @@ __global__ void __launch_bounds__(256) finalize_kernel(const __grid_constant__ B
     __threadfence();
     double acc = 0.0;
     for (int i = 0; i < nchunks; ++i) acc = acc + reinterpret_cast<volatile double*>(S.chunk)[i];
-    const float rho = static_cast<float>(sqrt(acc / (static_cast<double>(T.rows) * static_cast<double>(T.cols))));
+    const float rho = static_cast<float>(sqrt(acc / (static_cast<double>(T.stat_rows) * static_cast<double>(T.cols))));
     S.stats[0] = rho;
     S.stats[1] = fmaxf(rho / clip, 1.0f);
     *S.ticket = 0u;
@@ -832,6 +835,8 @@ static TensorDesc make_desc(uint8_t* codes, uint8_t* phase, const uint8_t* scale
   d.key = hash_key(seed, rounding == BL_ROUND_STRAT ? 0u : step);
   d.strat_j = static_cast<float>(strat_j);
   d.scratch256 = 0;
+  d.stat_rows = d.rows;
+  d.stat_panel0 = 0;
   return d;
 }
 
@@ -873,25 +878,46 @@ static int launch_update(int dir, int pcb, cudaStream_t st, const Batch& B, unsi
   return 0;
 }
 
-// column statistics + finalize of a batch into its scratch (regions assigned in B)
+// column statistics of a batch into its scratch (regions assigned in B): the panel sums only
 template <typename GT>
-static int run_stats(const Batch& B, int direction, double clip, unsigned char* scratch, cudaStream_t st) {
-  int64_t sblocks = 0, fblocks = 0;
-  for (int i = 0; i < B.count; ++i) {
+static int run_colstats(const Batch& B, int direction, unsigned char* scratch, cudaStream_t st) {
+  int64_t sblocks = 0;
+  for (int i = 0; i < B.count; ++i)
     sblocks += static_cast<int64_t>(stats_col_chunks(B.t[i].cols)) * stats_panels(B.t[i].rows);
-    fblocks += stats_col_chunks(B.t[i].cols);
-  }
   BL_REQUIRE(sblocks <= 0x7FFFFFFF, "direction: too many statistics blocks (%lld)", (long long)sblocks);
-  BL_CUDA(cudaMemsetAsync(scratch, 0, 256, st));                       // the batch's arrival counters
   if (direction == BL_DIR_SIGN)
     colstats_kernel<GT, true><<<static_cast<unsigned>(sblocks), kThreads, 0, st>>>(B, scratch);
   else
     colstats_kernel<GT, false><<<static_cast<unsigned>(sblocks), kThreads, 0, st>>>(B, scratch);
   BL_CUDA(cudaGetLastError());
+  return 0;
+}
+
+// panel sums -> denominators, RMS divisor
+static int run_finalize(const Batch& B, int direction, double clip, unsigned char* scratch, cudaStream_t st) {
+  int64_t fblocks = 0;
+  for (int i = 0; i < B.count; ++i) fblocks += stats_col_chunks(B.t[i].cols);
+  BL_CUDA(cudaMemsetAsync(scratch, 0, 256, st));                       // the batch's arrival counters
   finalize_kernel<<<static_cast<unsigned>(fblocks), 256, 0, st>>>(B, scratch, direction == BL_DIR_COLNORM ? 1 : 0,
                                                                  static_cast<float>(clip));
   BL_CUDA(cudaGetLastError());
   return 0;
+}
+
+template <typename GT>
+static int run_stats(const Batch& B, int direction, double clip, unsigned char* scratch, cudaStream_t st) {
+  if (int rc = run_colstats<GT>(B, direction, scratch, st)) return rc;
+  return run_finalize(B, direction, clip, scratch, st);
+}
+
+// scratch regions of a batch, in order, behind the 256 bytes of arrival counters; returns the bytes used
+static size_t assign_scratch(Batch& B) {
+  size_t off = 256;
+  for (int i = 0; i < B.count; ++i) {
+    B.t[i].scratch256 = static_cast<uint32_t>(off / 256);
+    off += tensor_scratch_bytes(B.t[i].stat_rows, B.t[i].cols);
+  }
+  return off;
 }
 
 // a batch through statistics (if the direction needs them) and the update; returns the kernels launched in *launches
@@ -900,11 +926,7 @@ static int run_batch(Batch& B, int pcb, const StepParams& P, int direction, doub
                      int* launches) {
   const bool stats = needs_stats(direction, clip);
   if (stats) {
-    size_t off = 256;
-    for (int i = 0; i < B.count; ++i) {
-      B.t[i].scratch256 = static_cast<uint32_t>(off / 256);
-      off += tensor_scratch_bytes(B.t[i].rows, B.t[i].cols);
-    }
+    assign_scratch(B);
     if (int rc = run_stats<GT>(B, direction, clip, static_cast<unsigned char*>(scratch), st)) return rc;
   }
   if (int rc = launch_update<GT>(direction + 1, pcb, st, B, static_cast<unsigned char*>(scratch), stats ? 1 : 0, P))
@@ -1077,6 +1099,122 @@ extern "C" int bl_nvfp4_lattice_update_many(int count, uint8_t* const* codes, ui
       return rc;
   }
   return 0;
+}
+
+// ---- row shards whose direction normalises over the whole weight ----
+// Every shard owner sums its own 128-row panels into the panel array of the WHOLE weight (at the panels of its rows),
+// the owners exchange the arrays (an all-gather in place: the host's job, between the two calls), and each finalizes
+// over all panels in ascending order: denominators, RMS and therefore every code, phase and scale byte equal those of
+// the unsharded update. Shards start on a panel boundary, so the panels are the unsharded ones.
+
+static int check_shards(const char* who, int count, const int64_t* rows, const int64_t* cols, const int64_t* row0,
+                        const int64_t* total_rows, int direction, double clip, const void* scratch,
+                        size_t scratch_bytes) {
+  BL_REQUIRE(count >= 0 && count <= kMaxBatch, "%s: between 0 and %d tensors per call, got %d", who, kMaxBatch, count);
+  BL_REQUIRE(count == 0 || (rows && cols && row0 && total_rows), "%s: null array", who);
+  BL_REQUIRE(needs_stats(direction, clip), "%s: this direction has no statistics (use the plain update)", who);
+  size_t need = 256;
+  for (int i = 0; i < count; ++i) {
+    BL_REQUIRE(rows[i] > 0 && cols[i] > 0 && cols[i] % 8 == 0 && total_rows[i] < (1ll << 31) && cols[i] < (1ll << 31),
+               "%s: tensor %d: [rows, cols] with cols a multiple of 8 and dimensions below 2^31", who, i);
+    BL_REQUIRE(row0[i] >= 0 && row0[i] % kPanelRows == 0 && row0[i] + rows[i] <= total_rows[i],
+               "%s: tensor %d: rows [%lld, %lld) of %lld: a shard starts on a multiple of %d rows inside the weight",
+               who, i, (long long)row0[i], (long long)(row0[i] + rows[i]), (long long)total_rows[i], kPanelRows);
+    BL_REQUIRE(rows[i] % kPanelRows == 0 || row0[i] + rows[i] == total_rows[i],
+               "%s: tensor %d: only the last shard may hold a partial panel of %d rows", who, i, kPanelRows);
+    need += tensor_scratch_bytes(total_rows[i], cols[i]);
+  }
+  BL_REQUIRE(count == 0 || (scratch != nullptr && aligned16(scratch) && scratch_bytes >= need),
+             "%s: needs %zu bytes of 16-byte aligned scratch, got %zu", who, need, scratch_bytes);
+  return 0;
+}
+
+extern "C" size_t bl_update_shards_scratch_bytes(int count, const int64_t* cols, const int64_t* total_rows) {
+  if (count <= 0 || cols == nullptr || total_rows == nullptr) return 0;
+  size_t need = 256;
+  for (int i = 0; i < count; ++i)
+    if (total_rows[i] > 0 && cols[i] > 0) need += tensor_scratch_bytes(total_rows[i], cols[i]);
+  return need;
+}
+
+template <typename GT>
+static int shard_stats_typed(Batch& B, int direction, unsigned char* scratch, cudaStream_t st) {
+  return run_colstats<GT>(B, direction, scratch, st);
+}
+
+extern "C" int bl_update_shard_stats(int count, const void* const* grad, const int64_t* rows, const int64_t* cols,
+                                     const int64_t* row0, const int64_t* total_rows, int grad_dtype, int direction,
+                                     double clip, void* scratch, size_t scratch_bytes, uint64_t* partial_offset,
+                                     int device, bl_stream_t stream) {
+  if (int rc = check_shards("update_shard_stats", count, rows, cols, row0, total_rows, direction, clip, scratch,
+                            scratch_bytes))
+    return rc;
+  BL_REQUIRE(count == 0 || (grad && partial_offset), "update_shard_stats: null array");
+  BL_REQUIRE(grad_dtype >= BL_F32 && grad_dtype <= BL_F16, "update_shard_stats: unknown gradient dtype %d", grad_dtype);
+  if (count == 0) return 0;
+  Batch B;
+  B.count = count;
+  for (int i = 0; i < count; ++i) {
+    BL_REQUIRE(grad[i] != nullptr && aligned16(grad[i]), "update_shard_stats: gradient %d: null or not 16-byte aligned", i);
+    B.t[i] = make_desc(nullptr, nullptr, nullptr, nullptr, nullptr, grad[i], rows[i], cols[i], 0, 0, 0, 0, 0);
+    B.t[i].stat_rows = static_cast<int>(total_rows[i]);
+    B.t[i].stat_panel0 = static_cast<int>(row0[i] / kPanelRows);
+  }
+  assign_scratch(B);
+  for (int i = 0; i < count; ++i) partial_offset[i] = static_cast<uint64_t>(B.t[i].scratch256) * 256;
+  BL_DEVICE(device);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  unsigned char* sc = static_cast<unsigned char*>(scratch);
+  if (grad_dtype == BL_BF16) return shard_stats_typed<__nv_bfloat16>(B, direction, sc, st);
+  if (grad_dtype == BL_F16) return shard_stats_typed<__half>(B, direction, sc, st);
+  return shard_stats_typed<float>(B, direction, sc, st);
+}
+
+template <typename GT>
+static int shard_update_typed(Batch& B, int pcb, const StepParams& P, int direction, double clip, unsigned char* scratch,
+                              cudaStream_t st) {
+  if (int rc = run_finalize(B, direction, clip, scratch, st)) return rc;
+  return launch_update<GT>(direction + 1, pcb, st, B, scratch, 1, P);
+}
+
+extern "C" int bl_nvfp4_lattice_update_shards(int count, uint8_t* const* codes, uint8_t* const* phase,
+                                              uint8_t* const* scales, const float* const* global_scale,
+                                              const void* const* grad, const int64_t* rows, const int64_t* cols,
+                                              const int64_t* row0, const int64_t* total_rows, const uint64_t* offset,
+                                              const uint32_t* seed, const uint32_t* step, const int* strat_j,
+                                              int grad_dtype, int phase_bits, int phase_cb, double lr, double decay,
+                                              int rounding, int strat_k, int rule, double kappa, int direction,
+                                              double clip, void* scratch, size_t scratch_bytes, int device,
+                                              bl_stream_t stream) {
+  if (int rc = check_shards("lattice_update_shards", count, rows, cols, row0, total_rows, direction, clip, scratch,
+                            scratch_bytes))
+    return rc;
+  BL_REQUIRE(count == 0 || (codes && scales && global_scale && grad && offset && seed && step),
+             "lattice_update_shards: null array");
+  BL_REQUIRE(phase_bits == 0 || phase != nullptr, "lattice_update_shards: null phase array");
+  if (count == 0) return 0;
+  Batch B;
+  B.count = count;
+  for (int i = 0; i < count; ++i) {
+    if (int rc = check_common(rows[i], cols[i], phase_bits, phase_cb, phase_bits ? phase[i] : nullptr, rounding, rule))
+      return rc;
+    if (int rc = check_update_args("lattice_update_shards", codes[i], phase_bits ? phase[i] : nullptr, scales[i],
+                                   global_scale[i], grad[i], grad_dtype, direction, clip))
+      return rc;
+    B.t[i] = make_desc(codes[i], phase_bits ? phase[i] : nullptr, scales[i], scales[i], global_scale[i], grad[i],
+                       rows[i], cols[i], offset[i], rounding, seed[i], step[i], strat_j ? strat_j[i] : 0);
+    B.t[i].stat_rows = static_cast<int>(total_rows[i]);
+    B.t[i].stat_panel0 = static_cast<int>(row0[i] / kPanelRows);
+  }
+  assign_scratch(B);
+  BL_DEVICE(device);
+  const StepParams P = make_params(lr, decay, phase_bits, rule, kappa, rounding, strat_k);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  unsigned char* sc = static_cast<unsigned char*>(scratch);
+  const int pcb = phase_bits ? phase_cb : 0;
+  if (grad_dtype == BL_BF16) return shard_update_typed<__nv_bfloat16>(B, pcb, P, direction, clip, sc, st);
+  if (grad_dtype == BL_F16) return shard_update_typed<__half>(B, pcb, P, direction, clip, sc, st);
+  return shard_update_typed<float>(B, pcb, P, direction, clip, sc, st);
 }
 
 extern "C" int bl_direction(const void* grad, int grad_dtype, int64_t rows, int64_t cols, int direction, double clip,

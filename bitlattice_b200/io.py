@@ -227,6 +227,7 @@ def load_into(module: torch.nn.Module, path: str, device=None, group=None) -> No
         new = torch.nn.Parameter(t, requires_grad=old.requires_grad and t.is_floating_point())
         if name in rows:
             new._bl_row_offset = rows[name][0]
+            new._bl_rows_total = int(meta["tensors"][name]["shape"][0])
         mod._parameters[leaf] = new
 
 

@@ -110,13 +110,20 @@ class Lattice(torch.optim.Optimizer):
                         batches then fill across several backward calls. Code that reads ``p.packed`` itself
                         between backward and step must use 'backward'
     ``seed``            base of the per-parameter RNG seeds: parameter number i uses (seed + 7919 * i) mod 2^32
-    A parameter that is a row shard of a larger weight sets ``p._bl_row_offset`` to its first global row: the update
-    then draws the random numbers of the unsharded tensor (as the reference's row tiles do, csrc/update.cpp:50).
+    ``shard_group``     the process group (True: the default group) whose ranks own the row shards of the sharded
+                        weights, in rank order and of equal size. Directions that normalise over the whole weight
+                        (colnorm; raw and sign with clip < 1) then exchange their 128-row panel sums (weights / 32
+                        bytes per step) and every shard receives exactly the update of its rows in the unsharded
+                        weight. None: such a direction treats every shard as a weight of its own, without
+                        communication
+    A parameter that is a row shard of a larger weight sets ``p._bl_row_offset`` to its first global row (and
+    ``p._bl_rows_total`` to the rows of the whole weight): the update then draws the random numbers of the unsharded
+    tensor (as the reference's row tiles do, csrc/update.cpp:50).
     """
 
     def __init__(self, params, preset: str | None = None, *, lr: float = DEFAULTS["lr"], state: str = "gpu",
                  fused_backward: bool = False, seed: int = 0, weight_decay: float = 0.0, overlap: bool = False,
-                 hook_batch: int = 1, hook_flush: str = "backward", **options):
+                 hook_batch: int = 1, hook_flush: str = "backward", shard_group=None, **options):
         from .presets import PRESETS
         if preset is not None:
             if preset not in PRESETS:
@@ -140,6 +147,7 @@ class Lattice(torch.optim.Optimizer):
         self.seed = int(seed)
         self.fused_backward = fused_backward
         self.overlap = bool(overlap)
+        self.shard_group = shard_group
         self._update_streams: dict = {}
         self._scratch: dict = {}
         self._plans: dict = {}            # (phase bits, ids of a batch of parameters) -> _ops.UpdatePlan
@@ -356,10 +364,54 @@ class Lattice(torch.optim.Optimizer):
                 and G.dtype == first.grad.dtype and G.dtype in (torch.bfloat16, torch.float16, torch.float32)
                 and G.is_contiguous())
 
+    def _whole_weight(self, ps, g: dict, kind: str) -> bool:
+        """Whether the update of ``ps`` needs the statistics of weights that other ranks hold rows of."""
+        return (self.shard_group is not None and not (kind == "sign" and g["clip"] >= 1.0)
+                and any(getattr(p, "_bl_rows_total", p.rows) != p.rows for p in ps))
+
+    def _exchange(self, arrays) -> None:
+        """The all-gather, in place, of the panel sums of sharded weights (``_ops.lattice_update_shards``)."""
+        import torch.distributed as dist
+        group = None if self.shard_group is True else self.shard_group
+        world, rank = dist.get_world_size(group), dist.get_rank(group)
+        for panels, first, count in arrays:
+            if count == panels.shape[0]:
+                continue                              # a weight this rank holds whole
+            if count * world != panels.shape[0] or first != count * rank:
+                raise RuntimeError(f"shard_group: {world} equal row shards in rank order expected, got panels "
+                                   f"[{first}, {first + count}) of {panels.shape[0]} on rank {rank}")
+            dist.all_gather_into_tensor(panels.view(-1), panels[first:first + count].view(-1), group=group)
+
+    def _update_shards(self, ps, g: dict, grads=None) -> None:
+        """The fused update of ``ps`` with the statistics of the whole weights (``shard_group``)."""
+        bits = g["phase_bits"]
+        cb = _ops.phase_container(bits)
+        items = []
+        for i, p in enumerate(ps):
+            st = self.state[p]
+            if grads is None:                         # the caller of the one-tensor form has advanced the step
+                self._invalidate(p)
+                st["step"] = st.get("step", 0) + 1
+            if bits and "phase" not in st:
+                st["phase"] = torch.zeros(p.rows, packed_cols(p.cols, cb), dtype=torch.uint8, device=p.packed.device)
+            row0 = int(getattr(p, "_bl_row_offset", 0))
+            items.append(dict(packed=p.packed, phase=st["phase"] if bits else None, scales=p.scales,
+                              global_scale=p.global_scale, grad=p.grad if grads is None else grads[i], rows=p.rows,
+                              cols=p.cols, row0=row0, total_rows=int(getattr(p, "_bl_rows_total", p.rows)),
+                              offset=row0 * p.cols, seed=(self.seed + 7919 * self._pid[p]) & 0xFFFFFFFF,
+                              step=st["step"]))
+        with _nvtx("bl.lattice_update"):
+            _ops.lattice_update_shards(items, ps[0].fmt, self._exchange, lr=g["lr"], weight_decay=g["weight_decay"],
+                                       phase_bits=bits, phase_cb=cb, rounding=g["rounding"], strata=g["strata"],
+                                       scale_rule=g["scale_rule"], trust=g["trust"], trust_lr=g["trust_lr"],
+                                       direction=self._kind(ps[0], g), clip=g["clip"])
+
     def _update_many(self, ps, g: dict) -> None:
         bits = g["phase_bits"]
         cb = _ops.phase_container(bits)
         kind = self._kind(ps[0], g)
+        if self._whole_weight(ps, g, kind):
+            return self._update_shards(ps, g)
         state, invalidate = self.state, self._invalidate
         steps, grads, tensors = [], [], []
         for p in ps:
@@ -460,6 +512,8 @@ class Lattice(torch.optim.Optimizer):
             _ops.step_quantized(p.packed, st.get("phase") if bits else None, p.scales, p.global_scale, None, D, p.fmt,
                                 rows, cols, inplace_scales=True, **common)
             return
+        if self._whole_weight((p,), g, kind):
+            return self._update_shards([p], g, [G2.contiguous()])
         scratch = None
         if self.overlap:                             # column statistics of updates that run beside the caller's stream
             need = _ops.update_scratch_bytes(rows, cols, kind, g["clip"])

@@ -82,6 +82,7 @@ def shard_rows(w: LatticeTensor, rank: int, size: int) -> LatticeTensor:
                       (hi - lo, *w.shape[1:]), w.dtype)
     t.compute = w.compute
     t._bl_row_offset = lo
+    t._bl_rows_total = w.rows
     return t
 
 

@@ -124,14 +124,15 @@ class LatticeTensor(torch.Tensor):
 
     def _map(self, fn, shape=None, dtype=None, shares_storage: bool = False) -> "LatticeTensor":
         """A LatticeTensor over ``fn`` of every part. The side attributes travel with it: a row shard stays a row
-        shard (``_bl_row_offset``: the optimizer's RNG offset and the checkpoint writer's gather depend on it), and a
+        shard (``_bl_row_offset``, ``_bl_rows_total``: the optimizer's RNG offset and the checkpoint writer's gather depend
+        on them), and a
         result that shares the storage (detach, alias: what ``nn.Parameter(t)`` is made of) also keeps the weight
         version and the event of an update still running on another stream."""
         t = LatticeTensor(fn(self.packed), fn(self.scales), fn(self.global_scale), None, self.fmt,
                           shape or self.shape, dtype or self.dtype)
         t.compute = self.compute
-        keep = (("_bl_row_offset", "_bl_version", "_bl_updated", "_bl_pending") if shares_storage
-                else ("_bl_row_offset",))
+        keep = (("_bl_row_offset", "_bl_rows_total", "_bl_version", "_bl_updated", "_bl_pending") if shares_storage
+                else ("_bl_row_offset", "_bl_rows_total"))
         for name in keep:
             if name in self.__dict__:
                 setattr(t, name, self.__dict__[name])

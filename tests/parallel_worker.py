@@ -201,6 +201,25 @@ def main():
         assert rel(xq_.grad, gx_exact[rsel]) < 0.25, (fn.__name__, rel(xq_.grad, gx_exact[rsel]))
         want_gw = gw_exact[cols]
         assert rel(pq.grad, want_gw) < 0.25, (fn.__name__, rel(pq.grad, want_gw))
+    # colnorm over row shards with the panel sums exchanged (shard_group): every rank ends with exactly its rows of
+    # the unsharded update, codes, scales and phase
+    Nu = 256 * world
+    wu = bl.LatticeTensor.from_float(torch.randn(Nu, K, device=dev, generator=gen) * 0.02, "nvfp4", method="rtn",
+                                     dtype=torch.bfloat16)
+    Gu = (torch.randn(Nu, K, device=dev, generator=gen) * 1e-2 * (1 + torch.arange(K, device=dev) % 5)).to(torch.bfloat16)
+    ru = slice(rank * 256, (rank + 1) * 256)
+    kw = dict(lr=3e-3, direction="colnorm", phase_bits=4, seed=21)
+    pu = torch.nn.Parameter(wu.detach().clone())
+    ou = bl.Lattice([pu], **kw)
+    psh = torch.nn.Parameter(shard_rows(wu, rank, world))
+    osh = bl.Lattice([psh], shard_group=True, **kw)
+    for _ in range(2):
+        pu.grad, psh.grad = Gu, Gu[ru].contiguous()
+        ou.step()
+        osh.step()
+    assert torch.equal(psh.packed, pu.packed[ru]), "sharded colnorm update differs from the unsharded one"
+    assert torch.equal(psh.scales.view(torch.uint8), pu.scales.view(torch.uint8)[ru])
+    assert torch.equal(osh.state[psh]["phase"], ou.state[pu]["phase"][ru])
     assert bl._ops.gemm_status(local) == 0
     dist.barrier()
     print(f"OK {rank}", flush=True)

@@ -457,6 +457,67 @@ def test_row_shard_update_equals_whole_update():
         assert torch.equal(os_.state[sh]["phase"], ow.state[whole]["phase"][rank * 64:(rank + 1) * 64])
 
 
+@pytest.mark.parametrize("direction,clip", [("colnorm", 1.0), ("colnorm", 0.25), ("raw", 0.5), ("sign", 0.5)])
+def test_row_shards_with_whole_weight_statistics_equal_the_whole_update(direction, clip):
+    """``Lattice(shard_group=...)``: directions that normalise over the whole weight exchange their 128-row panel sums,
+    and every shard then receives, bit for bit, the update of its rows in the unsharded weight. Four owners are played
+    in turn on one GPU: a first pass collects each owner's panel sums, a second hands every owner the others' sums
+    where the all-gather would have put them."""
+    from bitlattice_b200.parallel import shard_rows
+    world = 4
+    shapes = [(512, 256), (1024, 384)]
+    ws = [bl.LatticeTensor.from_float((torch.randn(*s, generator=gen(60 + i)) * 0.05).to(DEV), "nvfp4", method="rtn",
+                                      dtype=torch.bfloat16) for i, s in enumerate(shapes)]
+    Gs = [(torch.randn(*s, generator=gen(70 + i)) * (1e-2 * (1 + torch.arange(s[1]) % 7))).to(DEV, torch.bfloat16)
+          for i, s in enumerate(shapes)]
+    kw = dict(lr=3e-3, direction=direction, clip=clip, phase_bits=4, seed=11)
+    whole = [torch.nn.Parameter(w.detach().clone()) for w in ws]
+    ow = bl.Lattice(whole, **kw)
+    for p, G in zip(whole, Gs):
+        p.grad = G
+    ow.step()
+
+    class Stop(Exception):
+        pass
+
+    def owner(rank, exchange, **extra):
+        ps = [torch.nn.Parameter(shard_rows(w, rank, world)) for w in ws]
+        opt = bl.Lattice(ps, **kw, **extra)
+        opt._exchange = exchange
+        for p, G in zip(ps, Gs):
+            n = p.shape[0]
+            assert p._bl_rows_total == n * world
+            p.grad = G[rank * n:(rank + 1) * n].contiguous()
+        return ps, opt
+
+    sums = {}
+    for rank in range(world):
+        def collect(arrays, rank=rank):
+            sums[rank] = [a[f:f + c].clone() for a, f, c in arrays]
+            raise Stop
+        _, opt = owner(rank, collect, shard_group=True)
+        with pytest.raises(Stop):
+            opt.step()
+    for rank in range(world):
+        def fill(arrays):
+            for i, (a, f, c) in enumerate(arrays):
+                assert a.shape[0] == c * world
+                for other in range(world):
+                    a[other * c:(other + 1) * c] = sums[other][i]
+        ps, opt = owner(rank, fill, shard_group=True)
+        opt.step()
+        for p, q in zip(ps, whole):
+            n = p.shape[0]
+            rows = slice(rank * n, (rank + 1) * n)
+            assert torch.equal(p.packed, q.packed[rows]) and torch.equal(p.scales.view(torch.uint8), q.scales.view(torch.uint8)[rows])
+            assert torch.equal(opt.state[p]["phase"], ow.state[q]["phase"][rows])
+    # without the exchange a shard is a weight of its own: other statistics, another update
+    if direction == "colnorm":
+        ps, opt = owner(1, None)
+        opt.step()
+        assert not torch.equal(ps[0].packed, whole[0].packed[128:256])
+
+
 def test_converted_third_party_weights_dequantize_as_in_the_reference():
     """compressed-tensors / ModelOpt NVFP4 tensors converted to lattice weights decode to the reference's values
     (tests/golden/convert.npz, written by the reference's bitlattice.io.convert)."""
