@@ -89,6 +89,10 @@ def parse():
     ap.add_argument("--hook-batch", type=int, default=7,
                     help="gradients the optimizer's backward hooks collect before their updates go out as one batch "
                          "(Lattice(hook_batch=...)); 7 = the projections of one layer, 1 = every parameter on its own")
+    ap.add_argument("--whole-colnorm", type=int, default=0, choices=[0, 1],
+                    help="N > 1: 1 = the colnorm statistics cover the whole weight (Lattice(shard_group=...): the ranks "
+                         "exchange their 128-row panel sums and reproduce the unsharded update bit for bit); 0 = every "
+                         "row shard is normalised on its own, without communication")
     ap.add_argument("--kernel-summary", default=None, metavar="FILE",
                     help="after the measurements, run 2 more steps under torch.profiler on rank 0 and write per-kernel "
                          "launch counts and device time (text) to FILE")
@@ -327,10 +331,12 @@ def run_ours(a):
             p = torch.nn.Parameter(w)
             params.append(p)
             meta.append((name, N, K))
-    opt = bl.Lattice(params, fused_backward=True, overlap=bool(a.overlap), hook_batch=a.hook_batch, hook_flush="reader", **OPT)
+    group = dist.group.WORLD if world > 1 else None
+    shard_group = group if a.whole_colnorm else None
+    opt = bl.Lattice(params, fused_backward=True, overlap=bool(a.overlap), hook_batch=a.hook_batch, hook_flush="reader",
+                     shard_group=shard_group, **OPT)
     flops = sum(6.0 * M * N * K for _, N, K in meta)
     weights = sum(N * K for _, N, K in meta)
-    group = dist.group.WORLD if world > 1 else None
     # bytes crossing NVLink per step and rank, to pick the pattern: activations (column) against weights (token)
     moved = {"column": sum(3.125 * M * K for _, N, K in meta), "token": sum(3.125 * N * K for _, N, K in meta)}
     mode = a.parallel if a.parallel != "auto" else min(moved, key=moved.get)
@@ -477,7 +483,7 @@ def run_ours(a):
         """The 8B-class update workload: the lattice update alone over the whole weight set (every rank its shards),
         one distinct bf16 gradient ~ N(0, 1e-3^2) per parameter resident in HBM (so that no matrix finds a gradient in
         L2 that an earlier one pulled in), nothing else on the GPU. Returns seconds per pass (max over ranks)."""
-        plain = bl.Lattice(params, fused_backward=False, **OPT)         # in-line updates, own phase state
+        plain = bl.Lattice(params, fused_backward=False, shard_group=shard_group, **OPT)         # in-line updates, own phase state
         gen = torch.Generator(device=dev).manual_seed(99 + rank)
         with torch.no_grad():
             for p in params:
@@ -568,6 +574,8 @@ def run_ours(a):
                    "parallelism": f"x{world}: {names[mode]}" if world > 1 else "single GPU",
                    "nvlink_bytes_per_step_per_rank": {k: v * (world - 1) / world for k, v in moved.items()}
                    if world > 1 else None,
+                   "colnorm": ("whole weight (panel sums exchanged among the shard owners)" if shard_group is not None
+                               else "per row shard (no communication)") if world > 1 else "whole weight",
                    "l2": "inputs larger than L2 (weights, activations and gradients of a step exceed 126 MB)",
                    "host": "one Python thread per rank (autograd multithreading off)",
                    "updates": ("side stream (overlap=True)" if a.overlap else "in line") +

@@ -36,13 +36,13 @@ _SIGNATURES = {
                                                 _c.c_int, _c.c_double, _c.c_double, _c.c_int, _c.c_int, _c.c_int,
                                                 _c.c_double, _c.c_int, _c.c_double, _P, _c.c_size_t, _c.c_int, _P,
                                                 _c.POINTER(_c.c_int)]),
-    "bl_update_shards_scratch_bytes": (_c.c_size_t, [_c.c_int, _P, _P]),
-    "bl_update_shard_stats": (_c.c_int, [_c.c_int, _P, _P, _P, _P, _P, _c.c_int, _c.c_int, _c.c_double, _P, _c.c_size_t,
-                                         _P, _c.c_int, _P]),
-    "bl_nvfp4_lattice_update_shards": (_c.c_int, [_c.c_int, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _P, _c.c_int,
-                                                  _c.c_int, _c.c_int, _c.c_double, _c.c_double, _c.c_int, _c.c_int,
-                                                  _c.c_int, _c.c_double, _c.c_int, _c.c_double, _P, _c.c_size_t,
-                                                  _c.c_int, _P]),
+    "bl_update_shards_scratch_bytes": (_c.c_size_t, [_c.c_int, _P, _P, _c.c_int]),
+    "bl_update_shard_stats": (_c.c_int, [_c.c_int, _P, _P, _P, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_double, _P,
+                                         _c.c_size_t, _P, _P, _c.c_int, _P]),
+    "bl_nvfp4_lattice_update_shards": (_c.c_int, [_c.c_int, _P, _P, _P, _P, _P, _P, _P, _c.c_int, _c.c_int, _P, _P, _P,
+                                                  _P, _c.c_int, _c.c_int, _c.c_int, _c.c_double, _c.c_double, _c.c_int,
+                                                  _c.c_int, _c.c_int, _c.c_double, _c.c_int, _c.c_double, _P,
+                                                  _c.c_size_t, _c.c_int, _P]),
     "bl_update_select": (_c.c_int, [_c.c_int]),
     "bl_update_fixed_scratch_capacity": (_c.c_size_t, []),
     "bl_nvfp4_lattice_update_fixed_scratch": (_c.c_int, [_P, _P, _P, _P, _P, _c.c_int, _c.c_int64, _c.c_int64,

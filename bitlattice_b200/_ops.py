@@ -288,16 +288,16 @@ def lattice_update_many(items, fmt, *, lr: float, weight_decay: float, phase_bit
     _C.Counters.launches += launches.value
 
 
-def lattice_update_shards(items, fmt, exchange, *, lr: float, weight_decay: float, phase_bits: int, phase_cb: int,
-                          rounding: str, strata: int, scale_rule: str, trust: float, trust_lr: float, direction: str,
-                          clip: float = 1.0) -> None:
+def lattice_update_shards(items, fmt, world: int, rank: int, exchange, *, lr: float, weight_decay: float,
+                          phase_bits: int, phase_cb: int, rounding: str, strata: int, scale_rule: str, trust: float,
+                          trust_lr: float, direction: str, clip: float = 1.0) -> None:
     """The fused update of row shards whose direction normalises over the whole weight (colnorm; raw and sign with
-    clip < 1): together the owners of the shards reproduce the unsharded update bit for bit. ``items`` as for
-    ``lattice_update_many`` plus ``row0`` (the shard's first row in the weight) and ``total_rows``. Between the
-    statistics and the update ``exchange(arrays)`` is called with one entry per tensor, ``(panels, first, count)``:
-    ``panels`` is the fp32 [ceil(total_rows / 128), cols] panel array of the whole weight, of which this owner has
-    filled ``panels[first:first + count]``; on return every row must hold its owner's sums (an in-place all-gather,
-    issued on the current stream). A shard starts on a multiple of 128 rows."""
+    clip < 1): together the ``world`` owners of the shards reproduce the unsharded update bit for bit. ``items`` as for
+    ``lattice_update_many``; every tensor is owner ``rank``'s shard, rows [rank * rows, (rank + 1) * rows) of a weight
+    of ``world * rows`` rows (rows a multiple of 128; ``offset`` = the RNG index of the shard's first element). Between
+    the statistics and the update ``exchange(blocks)`` is called once per 40 tensors with an fp32 tensor [world, n] of
+    which this owner has filled row ``rank``; on return every row must hold its owner's sums (an in-place all-gather,
+    issued on the current stream)."""
     if direction not in _DIRECTION:
         raise RuntimeError(f"direction {direction!r} is outside this build (raw, sign, colnorm are built)")
     if not _is_nvfp4(fmt):
@@ -317,28 +317,25 @@ def lattice_update_shards(items, fmt, exchange, *, lr: float, weight_decay: floa
             G = it["grad"]
             if G.dtype != gdtype or G.numel() != int(it["rows"]) * int(it["cols"]) or not G.is_cuda or not G.is_contiguous():
                 raise RuntimeError("gradient: a contiguous CUDA tensor of the group's dtype with rows*cols elements")
-        i64 = lambda k: (ctypes.c_int64 * n)(*[int(it[k]) for it in part])
         ptrs = lambda k: (ctypes.c_void_p * n)(*[it[k].data_ptr() for it in part])
-        rows, cols, row0, total = i64("rows"), i64("cols"), i64("row0"), i64("total_rows")
+        rows = (ctypes.c_int64 * n)(*[int(it["rows"]) for it in part])
+        cols = (ctypes.c_int64 * n)(*[int(it["cols"]) for it in part])
         grad = ptrs("grad")
         dev = part[0]["packed"]
-        need = int(_C.lib().bl_update_shards_scratch_bytes(n, cols, total))
+        need = int(_C.lib().bl_update_shards_scratch_bytes(n, rows, cols, world))
         scratch = _scratch_for(dev.device, need)
-        offs = (ctypes.c_uint64 * n)()
-        _C.call("bl_update_shard_stats", n, grad, rows, cols, row0, total, _C.DTYPE[gdtype], _DIRECTION[direction],
-                float(clip), _C.ptr(scratch), scratch.numel(), offs, _C.device_of(dev), _C.stream_of(dev))
-        arrays = []
-        for i, it in enumerate(part):
-            panels = (int(it["total_rows"]) + 127) // 128
-            view = scratch[offs[i]:offs[i] + panels * int(it["cols"]) * 4].view(torch.float32).view(panels, int(it["cols"]))
-            arrays.append((view, int(it["row0"]) // 128, (int(it["rows"]) + 127) // 128))
-        exchange(arrays)
+        where, block = ctypes.c_uint64(0), ctypes.c_uint64(0)
+        _C.call("bl_update_shard_stats", n, grad, rows, cols, world, rank, _C.DTYPE[gdtype], _DIRECTION[direction],
+                float(clip), _C.ptr(scratch), scratch.numel(), ctypes.byref(where), ctypes.byref(block),
+                _C.device_of(dev), _C.stream_of(dev))
+        if world > 1:
+            exchange(scratch[where.value:where.value + world * block.value].view(torch.float32).view(world, -1))
         sj = (ctypes.c_int * n)()
         strat_k = 1
         for i, it in enumerate(part):
             sj[i], strat_k = strat_args(rounding, it["step"], strata)
         _C.call("bl_nvfp4_lattice_update_shards", n, ptrs("packed"), ptrs("phase") if phase_bits > 0 else None,
-                ptrs("scales"), ptrs("global_scale"), grad, rows, cols, row0, total,
+                ptrs("scales"), ptrs("global_scale"), grad, rows, cols, world, rank,
                 (ctypes.c_uint64 * n)(*[int(it["offset"]) & 0xFFFFFFFFFFFFFFFF for it in part]),
                 (ctypes.c_uint32 * n)(*[int(it["seed"]) & 0xFFFFFFFF for it in part]),
                 (ctypes.c_uint32 * n)(*[int(it["step"]) & 0xFFFFFFFF for it in part]), sj, _C.DTYPE[gdtype], phase_bits,

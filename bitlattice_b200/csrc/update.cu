@@ -56,12 +56,17 @@ struct TensorDesc {
   float strat_j;
   uint32_t scratch256;      // offset of the tensor's scratch region in the batch scratch, in units of 256 bytes
   // A row shard whose statistics cover the whole weight: stat_rows = rows of the whole weight, stat_panel0 = the
-  // shard's first 128-row panel in it. Everything else: stat_rows = rows, stat_panel0 = 0.
-  int stat_rows, stat_panel0;
+  // shard's first 128-row panel in it, stat_local = panels per owner, and the panel sums live in the batch's exchange
+  // area (one block per owner, Batch::stat_stride floats apart): gather256 = offset, in units of 256 bytes, of this
+  // tensor's slice in owner 0's block. Everything else: stat_rows = rows, stat_panel0 = 0, gather256 = 0 (the panel
+  // sums are the head of the tensor's own scratch region).
+  int stat_rows, stat_panel0, stat_local;
+  uint32_t gather256;
 };
 
 struct Batch {
   int count;
+  uint32_t stat_stride;     // floats between the blocks of consecutive owners in the exchange area (row shards)
   TensorDesc t[kMaxBatch];
 };
 
@@ -92,6 +97,15 @@ __device__ __forceinline__ ScratchDev scratch_of(unsigned char* base, const Tens
   s.stats = reinterpret_cast<float*>(p);
   s.ticket = reinterpret_cast<unsigned*>(base) + index;
   return s;
+}
+
+// the sums of 128-row panel p of tensor t, [cols] floats
+__device__ __forceinline__ float* panel_sums(unsigned char* base, const Batch& B, const TensorDesc& t, const ScratchDev& S,
+                                             int p) {
+  if (t.gather256 == 0) return S.partial + static_cast<int64_t>(p) * t.cols;
+  const int owner = p / t.stat_local, local = p - owner * t.stat_local;
+  return reinterpret_cast<float*>(base + static_cast<size_t>(t.gather256) * 256) +
+         static_cast<size_t>(owner) * B.stat_stride + static_cast<int64_t>(local) * t.cols;
 }
 
 // ------------------------------------------------------------------------------------------------ column statistics
@@ -161,7 +175,7 @@ __global__ void __launch_bounds__(kThreads) colstats_kernel(const __grid_constan
     float tot = 0.0f;
 #pragma unroll
     for (int w = 0; w < kPanelRows / kSubRows; ++w) tot = tot + sub[w][threadIdx.x];
-    scratch_of(scratch, T, ti).partial[static_cast<int64_t>(panel + T.stat_panel0) * T.cols + c] = tot;
+    panel_sums(scratch, B, T, scratch_of(scratch, T, ti), panel + T.stat_panel0)[c] = tot;
   }
 }
 
@@ -188,7 +202,7 @@ __global__ void __launch_bounds__(256) finalize_kernel(const __grid_constant__ B
   double colu = 0.0;
   if (c < T.cols) {
     float tot = 0.0f;
-    for (int p = 0; p < npanels; ++p) tot = tot + S.partial[static_cast<int64_t>(p) * T.cols + c];
+    for (int p = 0; p < npanels; ++p) tot = tot + panel_sums(scratch, B, T, S, p)[c];
     if (colnorm) {
       const float d = sqrtf(tot / static_cast<float>(T.stat_rows)) + 1e-30f;
       S.denom[c] = d;
@@ -837,6 +851,8 @@ static TensorDesc make_desc(uint8_t* codes, uint8_t* phase, const uint8_t* scale
   d.scratch256 = 0;
   d.stat_rows = d.rows;
   d.stat_panel0 = 0;
+  d.stat_local = stats_panels(d.rows);
+  d.gather256 = 0;
   return d;
 }
 
@@ -949,6 +965,8 @@ static int direction_typed(const GT* grad, int64_t rows, int64_t cols, int direc
   const float* stats = nullptr;
   if (needs_stats(direction, clip)) {
     Batch B;
+    B.stat_stride = 0;
+  B.stat_stride = 0;
     B.count = 1;
     B.t[0] = make_desc(nullptr, nullptr, nullptr, nullptr, nullptr, grad, rows, cols, 0, 0, 0, 0, 0);
     B.t[0].scratch256 = 1;
@@ -1011,6 +1029,7 @@ extern "C" int bl_nvfp4_step_quantized(uint8_t* codes, uint8_t* phase, const uin
   BL_DEVICE(device);
   const StepParams P = make_params(lr, decay, phase_bits, rule, kappa, rounding, strat_k);
   Batch B;
+  B.stat_stride = 0;
   B.count = 1;
   B.t[0] = make_desc(codes, phase, scales_in, scales_out, global_scale, D, rows, cols, offset, rounding, seed, step,
                      strat_j);
@@ -1044,6 +1063,7 @@ extern "C" int bl_nvfp4_lattice_update(uint8_t* codes, uint8_t* phase, uint8_t* 
   BL_DEVICE(device);
   const StepParams P = make_params(lr, decay, phase_bits, rule, kappa, rounding, strat_k);
   Batch B;
+  B.stat_stride = 0;
   B.count = 1;
   B.t[0] = make_desc(codes, phase, scales, scales, global_scale, grad, rows, cols, offset, rounding, seed, step, strat_j);
   return run_batch_dtype(B, grad_dtype, phase_bits ? phase_cb : 0, P, direction, clip, scratch,
@@ -1084,6 +1104,8 @@ extern "C" int bl_nvfp4_lattice_update_many(int count, uint8_t* const* codes, ui
   int i = 0;
   while (i < count) {
     Batch B;
+    B.stat_stride = 0;
+  B.stat_stride = 0;
     B.count = 0;
     size_t used = 256;
     while (i < count && B.count < kMaxBatch) {
@@ -1102,72 +1124,101 @@ extern "C" int bl_nvfp4_lattice_update_many(int count, uint8_t* const* codes, ui
 }
 
 // ---- row shards whose direction normalises over the whole weight ----
-// Every shard owner sums its own 128-row panels into the panel array of the WHOLE weight (at the panels of its rows),
-// the owners exchange the arrays (an all-gather in place: the host's job, between the two calls), and each finalizes
-// over all panels in ascending order: denominators, RMS and therefore every code, phase and scale byte equal those of
-// the unsharded update. Shards start on a panel boundary, so the panels are the unsharded ones.
+// `world` owners hold equal row shards of every weight, owner r the rows [r * rows, (r + 1) * rows). Each sums its own
+// 128-row panels into ITS block of the batch's exchange area, the owners exchange the blocks (ONE all-gather in place
+// per batch: the host's job, between the two calls), and each finalizes over all panels in ascending order:
+// denominators, RMS and therefore every code, phase and scale byte equal those of the unsharded update. A shard holds a
+// multiple of 128 rows, so the panels are the unsharded ones.
+//
+// Scratch: [256 B arrival counters][exchange area: world blocks][the tensors' regions]. A block holds, per tensor, the
+// [rows / 128, cols] sums of one owner, each slice rounded up to 256 bytes.
 
-static int check_shards(const char* who, int count, const int64_t* rows, const int64_t* cols, const int64_t* row0,
-                        const int64_t* total_rows, int direction, double clip, const void* scratch,
-                        size_t scratch_bytes) {
-  BL_REQUIRE(count >= 0 && count <= kMaxBatch, "%s: between 0 and %d tensors per call, got %d", who, kMaxBatch, count);
-  BL_REQUIRE(count == 0 || (rows && cols && row0 && total_rows), "%s: null array", who);
-  BL_REQUIRE(needs_stats(direction, clip), "%s: this direction has no statistics (use the plain update)", who);
-  size_t need = 256;
+struct ShardLayout {
+  size_t block_bytes, area_offset, total_bytes;
+};
+
+static size_t shard_slice_bytes(int64_t rows, int64_t cols) {
+  return (static_cast<size_t>(stats_panels(static_cast<int>(rows))) * cols * 4 + 255) & ~size_t(255);
+}
+
+static ShardLayout shard_layout(int count, const int64_t* rows, const int64_t* cols, int world) {
+  ShardLayout L{0, 256, 0};
+  size_t regions = 0;
   for (int i = 0; i < count; ++i) {
-    BL_REQUIRE(rows[i] > 0 && cols[i] > 0 && cols[i] % 8 == 0 && total_rows[i] < (1ll << 31) && cols[i] < (1ll << 31),
-               "%s: tensor %d: [rows, cols] with cols a multiple of 8 and dimensions below 2^31", who, i);
-    BL_REQUIRE(row0[i] >= 0 && row0[i] % kPanelRows == 0 && row0[i] + rows[i] <= total_rows[i],
-               "%s: tensor %d: rows [%lld, %lld) of %lld: a shard starts on a multiple of %d rows inside the weight",
-               who, i, (long long)row0[i], (long long)(row0[i] + rows[i]), (long long)total_rows[i], kPanelRows);
-    BL_REQUIRE(rows[i] % kPanelRows == 0 || row0[i] + rows[i] == total_rows[i],
-               "%s: tensor %d: only the last shard may hold a partial panel of %d rows", who, i, kPanelRows);
-    need += tensor_scratch_bytes(total_rows[i], cols[i]);
+    L.block_bytes += shard_slice_bytes(rows[i], cols[i]);
+    regions += tensor_scratch_bytes(rows[i] * world, cols[i]);
   }
-  BL_REQUIRE(count == 0 || (scratch != nullptr && aligned16(scratch) && scratch_bytes >= need),
-             "%s: needs %zu bytes of 16-byte aligned scratch, got %zu", who, need, scratch_bytes);
+  L.total_bytes = L.area_offset + L.block_bytes * world + regions;
+  return L;
+}
+
+static int check_shards(const char* who, int count, const int64_t* rows, const int64_t* cols, int world, int rank,
+                        int direction, double clip, const void* scratch, size_t scratch_bytes) {
+  BL_REQUIRE(count >= 0 && count <= kMaxBatch, "%s: between 0 and %d tensors per call, got %d", who, kMaxBatch, count);
+  BL_REQUIRE(count == 0 || (rows && cols), "%s: null array", who);
+  BL_REQUIRE(world >= 1 && rank >= 0 && rank < world, "%s: owner %d of %d", who, rank, world);
+  BL_REQUIRE(needs_stats(direction, clip), "%s: this direction has no statistics (use the plain update)", who);
+  for (int i = 0; i < count; ++i) {
+    BL_REQUIRE(rows[i] > 0 && cols[i] > 0 && cols[i] % 8 == 0 && rows[i] * world < (1ll << 31) && cols[i] < (1ll << 31),
+               "%s: tensor %d: [rows, cols] with cols a multiple of 8 and dimensions below 2^31", who, i);
+    BL_REQUIRE(rows[i] % kPanelRows == 0 || world == 1, "%s: tensor %d: a shard holds a multiple of %d rows, got %lld",
+               who, i, kPanelRows, (long long)rows[i]);
+  }
+  const ShardLayout L = shard_layout(count, rows, cols, world);
+  BL_REQUIRE(L.total_bytes < (size_t(1) << 39), "%s: statistics of %zu bytes", who, L.total_bytes);
+  BL_REQUIRE(count == 0 || (scratch != nullptr && aligned16(scratch) && scratch_bytes >= L.total_bytes),
+             "%s: needs %zu bytes of 16-byte aligned scratch, got %zu", who, L.total_bytes, scratch_bytes);
   return 0;
 }
 
-extern "C" size_t bl_update_shards_scratch_bytes(int count, const int64_t* cols, const int64_t* total_rows) {
-  if (count <= 0 || cols == nullptr || total_rows == nullptr) return 0;
-  size_t need = 256;
-  for (int i = 0; i < count; ++i)
-    if (total_rows[i] > 0 && cols[i] > 0) need += tensor_scratch_bytes(total_rows[i], cols[i]);
-  return need;
+// descriptors' statistics fields and scratch offsets for owner `rank` of `world`
+static void place_shards(Batch& B, const int64_t* rows, const int64_t* cols, int world, int rank) {
+  const ShardLayout L = shard_layout(B.count, rows, cols, world);
+  B.stat_stride = static_cast<uint32_t>(L.block_bytes / 4);
+  size_t slice = L.area_offset, region = L.area_offset + L.block_bytes * world;
+  for (int i = 0; i < B.count; ++i) {
+    TensorDesc& t = B.t[i];
+    t.stat_rows = static_cast<int>(rows[i] * world);
+    t.stat_local = stats_panels(static_cast<int>(rows[i]));
+    t.stat_panel0 = rank * t.stat_local;
+    t.gather256 = static_cast<uint32_t>(slice / 256);
+    t.scratch256 = static_cast<uint32_t>(region / 256);
+    slice += shard_slice_bytes(rows[i], cols[i]);
+    region += tensor_scratch_bytes(rows[i] * world, cols[i]);
+  }
 }
 
-template <typename GT>
-static int shard_stats_typed(Batch& B, int direction, unsigned char* scratch, cudaStream_t st) {
-  return run_colstats<GT>(B, direction, scratch, st);
+extern "C" size_t bl_update_shards_scratch_bytes(int count, const int64_t* rows, const int64_t* cols, int world) {
+  if (count <= 0 || rows == nullptr || cols == nullptr || world < 1) return 0;
+  return shard_layout(count, rows, cols, world).total_bytes;
 }
 
 extern "C" int bl_update_shard_stats(int count, const void* const* grad, const int64_t* rows, const int64_t* cols,
-                                     const int64_t* row0, const int64_t* total_rows, int grad_dtype, int direction,
-                                     double clip, void* scratch, size_t scratch_bytes, uint64_t* partial_offset,
-                                     int device, bl_stream_t stream) {
-  if (int rc = check_shards("update_shard_stats", count, rows, cols, row0, total_rows, direction, clip, scratch,
-                            scratch_bytes))
+                                     int world, int rank, int grad_dtype, int direction, double clip, void* scratch,
+                                     size_t scratch_bytes, uint64_t* exchange_offset, uint64_t* block_bytes, int device,
+                                     bl_stream_t stream) {
+  if (int rc = check_shards("update_shard_stats", count, rows, cols, world, rank, direction, clip, scratch, scratch_bytes))
     return rc;
-  BL_REQUIRE(count == 0 || (grad && partial_offset), "update_shard_stats: null array");
+  BL_REQUIRE(count == 0 || grad, "update_shard_stats: null array");
+  BL_REQUIRE(exchange_offset && block_bytes, "update_shard_stats: null output");
   BL_REQUIRE(grad_dtype >= BL_F32 && grad_dtype <= BL_F16, "update_shard_stats: unknown gradient dtype %d", grad_dtype);
+  const ShardLayout L = shard_layout(count, rows, cols, world);
+  *exchange_offset = L.area_offset;
+  *block_bytes = L.block_bytes;
   if (count == 0) return 0;
   Batch B;
   B.count = count;
   for (int i = 0; i < count; ++i) {
     BL_REQUIRE(grad[i] != nullptr && aligned16(grad[i]), "update_shard_stats: gradient %d: null or not 16-byte aligned", i);
     B.t[i] = make_desc(nullptr, nullptr, nullptr, nullptr, nullptr, grad[i], rows[i], cols[i], 0, 0, 0, 0, 0);
-    B.t[i].stat_rows = static_cast<int>(total_rows[i]);
-    B.t[i].stat_panel0 = static_cast<int>(row0[i] / kPanelRows);
   }
-  assign_scratch(B);
-  for (int i = 0; i < count; ++i) partial_offset[i] = static_cast<uint64_t>(B.t[i].scratch256) * 256;
+  place_shards(B, rows, cols, world, rank);
   BL_DEVICE(device);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   unsigned char* sc = static_cast<unsigned char*>(scratch);
-  if (grad_dtype == BL_BF16) return shard_stats_typed<__nv_bfloat16>(B, direction, sc, st);
-  if (grad_dtype == BL_F16) return shard_stats_typed<__half>(B, direction, sc, st);
-  return shard_stats_typed<float>(B, direction, sc, st);
+  if (grad_dtype == BL_BF16) return run_colstats<__nv_bfloat16>(B, direction, sc, st);
+  if (grad_dtype == BL_F16) return run_colstats<__half>(B, direction, sc, st);
+  return run_colstats<float>(B, direction, sc, st);
 }
 
 template <typename GT>
@@ -1180,13 +1231,12 @@ static int shard_update_typed(Batch& B, int pcb, const StepParams& P, int direct
 extern "C" int bl_nvfp4_lattice_update_shards(int count, uint8_t* const* codes, uint8_t* const* phase,
                                               uint8_t* const* scales, const float* const* global_scale,
                                               const void* const* grad, const int64_t* rows, const int64_t* cols,
-                                              const int64_t* row0, const int64_t* total_rows, const uint64_t* offset,
-                                              const uint32_t* seed, const uint32_t* step, const int* strat_j,
-                                              int grad_dtype, int phase_bits, int phase_cb, double lr, double decay,
-                                              int rounding, int strat_k, int rule, double kappa, int direction,
-                                              double clip, void* scratch, size_t scratch_bytes, int device,
-                                              bl_stream_t stream) {
-  if (int rc = check_shards("lattice_update_shards", count, rows, cols, row0, total_rows, direction, clip, scratch,
+                                              int world, int rank, const uint64_t* offset, const uint32_t* seed,
+                                              const uint32_t* step, const int* strat_j, int grad_dtype, int phase_bits,
+                                              int phase_cb, double lr, double decay, int rounding, int strat_k, int rule,
+                                              double kappa, int direction, double clip, void* scratch,
+                                              size_t scratch_bytes, int device, bl_stream_t stream) {
+  if (int rc = check_shards("lattice_update_shards", count, rows, cols, world, rank, direction, clip, scratch,
                             scratch_bytes))
     return rc;
   BL_REQUIRE(count == 0 || (codes && scales && global_scale && grad && offset && seed && step),
@@ -1203,10 +1253,8 @@ extern "C" int bl_nvfp4_lattice_update_shards(int count, uint8_t* const* codes, 
       return rc;
     B.t[i] = make_desc(codes[i], phase_bits ? phase[i] : nullptr, scales[i], scales[i], global_scale[i], grad[i],
                        rows[i], cols[i], offset[i], rounding, seed[i], step[i], strat_j ? strat_j[i] : 0);
-    B.t[i].stat_rows = static_cast<int>(total_rows[i]);
-    B.t[i].stat_panel0 = static_cast<int>(row0[i] / kPanelRows);
   }
-  assign_scratch(B);
+  place_shards(B, rows, cols, world, rank);
   BL_DEVICE(device);
   const StepParams P = make_params(lr, decay, phase_bits, rule, kappa, rounding, strat_k);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
@@ -1286,6 +1334,7 @@ extern "C" int bl_nvfp4_lattice_update_fixed_scratch(uint8_t* codes, uint8_t* ph
   if (int rc = fixed_scratch_address(device, &scratch)) return rc;
   const StepParams P = make_params(lr, decay, phase_bits, rule, kappa, rounding, strat_k);
   Batch B;
+  B.stat_stride = 0;
   B.count = 1;
   B.t[0] = make_desc(codes, phase, scales, scales, global_scale, grad, rows, cols, offset, rounding, seed, step, strat_j);
   // the statistics pass clears the arrival counter it uses and overwrites every statistic it later reads, so what an

@@ -364,54 +364,65 @@ class Lattice(torch.optim.Optimizer):
                 and G.dtype == first.grad.dtype and G.dtype in (torch.bfloat16, torch.float16, torch.float32)
                 and G.is_contiguous())
 
-    def _whole_weight(self, ps, g: dict, kind: str) -> bool:
-        """Whether the update of ``ps`` needs the statistics of weights that other ranks hold rows of."""
-        return (self.shard_group is not None and not (kind == "sign" and g["clip"] >= 1.0)
-                and any(getattr(p, "_bl_rows_total", p.rows) != p.rows for p in ps))
+    @staticmethod
+    def _is_shard(p) -> bool:
+        return getattr(p, "_bl_rows_total", p.rows) != p.rows
 
-    def _exchange(self, arrays) -> None:
-        """The all-gather, in place, of the panel sums of sharded weights (``_ops.lattice_update_shards``)."""
+    def _whole_weight(self, g: dict, kind: str) -> bool:
+        """Whether row shards are updated with the statistics of their whole weights (``shard_group``)."""
+        return self.shard_group is not None and not (kind == "sign" and g["clip"] >= 1.0)
+
+    def _shard_world(self):
         import torch.distributed as dist
         group = None if self.shard_group is True else self.shard_group
-        world, rank = dist.get_world_size(group), dist.get_rank(group)
-        for panels, first, count in arrays:
-            if count == panels.shape[0]:
-                continue                              # a weight this rank holds whole
-            if count * world != panels.shape[0] or first != count * rank:
-                raise RuntimeError(f"shard_group: {world} equal row shards in rank order expected, got panels "
-                                   f"[{first}, {first + count}) of {panels.shape[0]} on rank {rank}")
-            dist.all_gather_into_tensor(panels.view(-1), panels[first:first + count].view(-1), group=group)
+        return dist.get_world_size(group), dist.get_rank(group), group
+
+    def _exchange(self, blocks: torch.Tensor) -> None:
+        """The all-gather, in place, of the owners' panel sums (``_ops.lattice_update_shards``): row r of ``blocks``
+        is rank r's."""
+        import torch.distributed as dist
+        _, rank, group = self._shard_world()
+        dist.all_gather_into_tensor(blocks.view(-1), blocks[rank], group=group)
 
     def _update_shards(self, ps, g: dict, grads=None) -> None:
-        """The fused update of ``ps`` with the statistics of the whole weights (``shard_group``)."""
+        """The fused update of the row shards ``ps`` with the statistics of the whole weights (``shard_group``)."""
         bits = g["phase_bits"]
         cb = _ops.phase_container(bits)
+        world, rank, _ = self._shard_world()
         items = []
         for i, p in enumerate(ps):
+            row0 = int(getattr(p, "_bl_row_offset", 0))
+            if p._bl_rows_total != world * p.rows or row0 != rank * p.rows:
+                raise RuntimeError(f"shard_group: rank {rank} of {world} holds rows [{row0}, {row0 + p.rows}) of "
+                                   f"{p._bl_rows_total}; equal row shards in rank order are built")
             st = self.state[p]
             if grads is None:                         # the caller of the one-tensor form has advanced the step
                 self._invalidate(p)
                 st["step"] = st.get("step", 0) + 1
             if bits and "phase" not in st:
                 st["phase"] = torch.zeros(p.rows, packed_cols(p.cols, cb), dtype=torch.uint8, device=p.packed.device)
-            row0 = int(getattr(p, "_bl_row_offset", 0))
             items.append(dict(packed=p.packed, phase=st["phase"] if bits else None, scales=p.scales,
                               global_scale=p.global_scale, grad=p.grad if grads is None else grads[i], rows=p.rows,
-                              cols=p.cols, row0=row0, total_rows=int(getattr(p, "_bl_rows_total", p.rows)),
-                              offset=row0 * p.cols, seed=(self.seed + 7919 * self._pid[p]) & 0xFFFFFFFF,
+                              cols=p.cols, offset=row0 * p.cols, seed=(self.seed + 7919 * self._pid[p]) & 0xFFFFFFFF,
                               step=st["step"]))
         with _nvtx("bl.lattice_update"):
-            _ops.lattice_update_shards(items, ps[0].fmt, self._exchange, lr=g["lr"], weight_decay=g["weight_decay"],
-                                       phase_bits=bits, phase_cb=cb, rounding=g["rounding"], strata=g["strata"],
-                                       scale_rule=g["scale_rule"], trust=g["trust"], trust_lr=g["trust_lr"],
-                                       direction=self._kind(ps[0], g), clip=g["clip"])
+            _ops.lattice_update_shards(items, ps[0].fmt, world, rank, self._exchange, lr=g["lr"],
+                                       weight_decay=g["weight_decay"], phase_bits=bits, phase_cb=cb,
+                                       rounding=g["rounding"], strata=g["strata"], scale_rule=g["scale_rule"],
+                                       trust=g["trust"], trust_lr=g["trust_lr"], direction=self._kind(ps[0], g),
+                                       clip=g["clip"])
 
     def _update_many(self, ps, g: dict) -> None:
         bits = g["phase_bits"]
         cb = _ops.phase_container(bits)
         kind = self._kind(ps[0], g)
-        if self._whole_weight(ps, g, kind):
-            return self._update_shards(ps, g)
+        if self._whole_weight(g, kind):
+            shards = [p for p in ps if self._is_shard(p)]
+            if shards:
+                self._update_shards(shards, g)
+                ps = [p for p in ps if not self._is_shard(p)]
+                if not ps:
+                    return
         state, invalidate = self.state, self._invalidate
         steps, grads, tensors = [], [], []
         for p in ps:
@@ -512,7 +523,7 @@ class Lattice(torch.optim.Optimizer):
             _ops.step_quantized(p.packed, st.get("phase") if bits else None, p.scales, p.global_scale, None, D, p.fmt,
                                 rows, cols, inplace_scales=True, **common)
             return
-        if self._whole_weight((p,), g, kind):
+        if self._whole_weight(g, kind) and self._is_shard(p):
             return self._update_shards([p], g, [G2.contiguous()])
         scratch = None
         if self.overlap:                             # column statistics of updates that run beside the caller's stream

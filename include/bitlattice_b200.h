@@ -105,31 +105,34 @@ BL_API int bl_nvfp4_lattice_update_many(int count, uint8_t* const* codes, uint8_
                                  int direction, double clip, void* scratch, size_t scratch_bytes, int device,
                                  bl_stream_t stream, int* launches);
 
-/* Row shards of a weight [total_rows, cols] whose direction normalises over ALL rows (colnorm; raw and sign with
- * clip < 1). The reference has no sharded update; its unsharded one (bitlattice/optim/lattice.py:671-694 with the
- * colnorm of bitlattice/_ops.py:110-144) is what the owners of the shards reproduce together, bit for bit:
- *   1. bl_update_shard_stats: each owner sums the 128-row panels of ITS rows [row0, row0 + rows) into the panel array
- *      of the whole weight, fp32 [ceil(total_rows / 128), cols], which starts partial_offset[i] bytes into `scratch`;
- *   2. the host exchanges the arrays among the owners (an in-place all-gather: every owner wrote the slice of its own
- *      panels) -- the library makes no collective call;
- *   3. bl_nvfp4_lattice_update_shards: every owner sums all panels in ascending order (the unsharded order), derives
- *      the column denominators and the RMS divisor of the whole weight, and updates its rows. `offset` is the RNG
- *      index of the shard's first element (row0 * cols for a weight that is not itself a tile of something larger).
- * A shard starts on a multiple of 128 rows and, unless it is the last, holds a multiple of 128 rows. At most 40
- * tensors per call; both calls get the same rows / cols / row0 / total_rows arrays and the same scratch of
- * bl_update_shards_scratch_bytes(count, cols, total_rows) bytes, untouched in between except for step 2. Launches:
+/* Row shards of weights whose direction normalises over ALL rows (colnorm; raw and sign with clip < 1). The reference
+ * has no sharded update; its unsharded one (bitlattice/optim/lattice.py:671-694 with the colnorm of
+ * bitlattice/_ops.py:110-144) is what the owners of the shards reproduce together, bit for bit. `world` owners hold
+ * equal shards of every weight of the call, owner `rank` the rows [rank * rows, (rank + 1) * rows) of a weight
+ * [world * rows, cols]; rows is a multiple of 128.
+ *   1. bl_update_shard_stats: each owner sums the 128-row panels of ITS rows, all tensors of the call, into block
+ *      number `rank` of the call's exchange area: `world` blocks of *block_bytes bytes starting *exchange_offset bytes
+ *      into `scratch`;
+ *   2. the host exchanges the blocks among the owners (ONE in-place all-gather of world * block_bytes bytes on the
+ *      same stream) -- the library makes no collective call;
+ *   3. bl_nvfp4_lattice_update_shards: every owner sums all panels in ascending order of their rows (the unsharded
+ *      order), derives the column denominators and the RMS divisor of the whole weights, and updates its rows.
+ *      `offset` is the RNG index of the shard's first element (rank * rows * cols for a weight that is not itself a
+ *      tile of something larger).
+ * At most 40 tensors per call; both calls get the same rows / cols / world / rank and the same scratch of
+ * bl_update_shards_scratch_bytes(count, rows, cols, world) bytes, untouched in between except for step 2. Launches:
  * one (statistics); two (reduction, update). */
-BL_API size_t bl_update_shards_scratch_bytes(int count, const int64_t* cols, const int64_t* total_rows);
-BL_API int bl_update_shard_stats(int count, const void* const* grad, const int64_t* rows, const int64_t* cols,
-                          const int64_t* row0, const int64_t* total_rows, int grad_dtype, int direction, double clip,
-                          void* scratch, size_t scratch_bytes, uint64_t* partial_offset, int device, bl_stream_t stream);
+BL_API size_t bl_update_shards_scratch_bytes(int count, const int64_t* rows, const int64_t* cols, int world);
+BL_API int bl_update_shard_stats(int count, const void* const* grad, const int64_t* rows, const int64_t* cols, int world,
+                          int rank, int grad_dtype, int direction, double clip, void* scratch, size_t scratch_bytes,
+                          uint64_t* exchange_offset, uint64_t* block_bytes, int device, bl_stream_t stream);
 BL_API int bl_nvfp4_lattice_update_shards(int count, uint8_t* const* codes, uint8_t* const* phase, uint8_t* const* scales,
                                    const float* const* global_scale, const void* const* grad, const int64_t* rows,
-                                   const int64_t* cols, const int64_t* row0, const int64_t* total_rows,
-                                   const uint64_t* offset, const uint32_t* seed, const uint32_t* step,
-                                   const int* strat_j, int grad_dtype, int phase_bits, int phase_cb, double lr,
-                                   double decay, int rounding, int strat_k, int rule, double kappa, int direction,
-                                   double clip, void* scratch, size_t scratch_bytes, int device, bl_stream_t stream);
+                                   const int64_t* cols, int world, int rank, const uint64_t* offset,
+                                   const uint32_t* seed, const uint32_t* step, const int* strat_j, int grad_dtype,
+                                   int phase_bits, int phase_cb, double lr, double decay, int rounding, int strat_k,
+                                   int rule, double kappa, int direction, double clip, void* scratch,
+                                   size_t scratch_bytes, int device, bl_stream_t stream);
 
 /* The update kernel has two routes with identical results: a fast one (stochastic rounding, 1..7 phase bits: packed
  * fp32 pairs, one range check per element instead of one per division; single groups whose values leave that range

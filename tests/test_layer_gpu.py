@@ -484,6 +484,7 @@ def test_row_shards_with_whole_weight_statistics_equal_the_whole_update(directio
         ps = [torch.nn.Parameter(shard_rows(w, rank, world)) for w in ws]
         opt = bl.Lattice(ps, **kw, **extra)
         opt._exchange = exchange
+        opt._shard_world = lambda: (world, rank, None)
         for p, G in zip(ps, Gs):
             n = p.shape[0]
             assert p._bl_rows_total == n * world
@@ -492,18 +493,17 @@ def test_row_shards_with_whole_weight_statistics_equal_the_whole_update(directio
 
     sums = {}
     for rank in range(world):
-        def collect(arrays, rank=rank):
-            sums[rank] = [a[f:f + c].clone() for a, f, c in arrays]
+        def collect(blocks, rank=rank):
+            assert blocks.shape[0] == world
+            sums[rank] = blocks[rank].clone()
             raise Stop
         _, opt = owner(rank, collect, shard_group=True)
         with pytest.raises(Stop):
             opt.step()
     for rank in range(world):
-        def fill(arrays):
-            for i, (a, f, c) in enumerate(arrays):
-                assert a.shape[0] == c * world
-                for other in range(world):
-                    a[other * c:(other + 1) * c] = sums[other][i]
+        def fill(blocks):
+            for other in range(world):
+                blocks[other] = sums[other]
         ps, opt = owner(rank, fill, shard_group=True)
         opt.step()
         for p, q in zip(ps, whole):
