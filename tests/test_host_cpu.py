@@ -153,7 +153,7 @@ def test_side_attributes_travel_with_views_and_copies():
     for rank in range(2):
         sh = shard_rows(w, rank, 2)
         lo = rank * 32
-        assert sh._bl_row_offset == lo
+        assert sh._bl_row_offset == lo and sh._bl_rows_total == 64
         sh._bl_version = 3
         p = to_parameter(sh)
         assert p._bl_row_offset == lo and p._bl_version == 3
@@ -161,8 +161,33 @@ def test_side_attributes_travel_with_views_and_copies():
         assert p.detach()._bl_row_offset == lo and p.detach()._bl_version == 3
         c = p.detach().clone()
         assert c._bl_row_offset == lo and not hasattr(c, "_bl_version")       # fresh storage: fresh version
+        assert c._bl_rows_total == 64 and torch.nn.Parameter(sh)._bl_rows_total == 64
         assert p.detach().to(torch.float16)._bl_row_offset == lo
     assert not hasattr(to_parameter(w), "_bl_row_offset")
+
+
+def test_shard_group_selects_the_whole_weight_update_and_rejects_unequal_shards(monkeypatch):
+    """``Lattice(shard_group=...)``: which parameters and directions take the exchanged statistics, and the refusal of
+    shards that are not equal and in rank order (raised on the host, before any library call; the constructor's
+    refusal of CPU weights is switched off for this test of the host logic)."""
+    from bitlattice_b200 import _ops
+    from bitlattice_b200.optim.lattice import Lattice
+    from bitlattice_b200.parallel import shard_rows
+    monkeypatch.setattr(_ops, "cuda_ok", lambda *a: True)
+    w = cpu_weight(rows=256, requires_grad=False)
+    sh = torch.nn.Parameter(shard_rows(w, 1, 2))
+    whole = torch.nn.Parameter(cpu_weight(rows=64, requires_grad=False))
+    assert Lattice._is_shard(sh) and not Lattice._is_shard(whole)
+    plain = Lattice([sh], lr=1e-3, direction="colnorm")
+    assert not plain._whole_weight(plain.param_groups[0], "colnorm")
+    opt = Lattice([sh], lr=1e-3, direction="colnorm", shard_group=True)
+    g = opt.param_groups[0]
+    assert opt._whole_weight(g, "colnorm") and opt._whole_weight(g, "raw") and not opt._whole_weight(g, "sign")
+    assert opt._whole_weight({**g, "clip": 0.5}, "sign")
+    opt._shard_world = lambda: (4, 1, None)          # four ranks, but the shard is one half of its weight
+    sh.grad = torch.zeros(128, sh.shape[1], dtype=torch.bfloat16)
+    with pytest.raises(RuntimeError, match="equal row shards in rank order"):
+        opt._update_shards([sh], g)
 
 
 def test_newton_schulz_orthogonalises_and_matches_its_coefficients():
