@@ -38,11 +38,11 @@ _SIGNATURES = {
                                                 _c.POINTER(_c.c_int)]),
     "bl_update_shards_scratch_bytes": (_c.c_size_t, [_c.c_int, _P, _P, _c.c_int]),
     "bl_update_shard_stats": (_c.c_int, [_c.c_int, _P, _P, _P, _c.c_int, _c.c_int, _c.c_int, _c.c_int, _c.c_double, _P,
-                                         _c.c_size_t, _P, _P, _c.c_int, _P]),
+                                         _c.c_size_t, _P, _P, _c.c_int, _P, _c.POINTER(_c.c_int)]),
     "bl_nvfp4_lattice_update_shards": (_c.c_int, [_c.c_int, _P, _P, _P, _P, _P, _P, _P, _c.c_int, _c.c_int, _P, _P, _P,
                                                   _P, _c.c_int, _c.c_int, _c.c_int, _c.c_double, _c.c_double, _c.c_int,
                                                   _c.c_int, _c.c_int, _c.c_double, _c.c_int, _c.c_double, _P,
-                                                  _c.c_size_t, _c.c_int, _P]),
+                                                  _c.c_size_t, _c.c_int, _P, _c.POINTER(_c.c_int)]),
     "bl_update_select": (_c.c_int, [_c.c_int]),
     "bl_update_fixed_scratch_capacity": (_c.c_size_t, []),
     "bl_nvfp4_lattice_update_fixed_scratch": (_c.c_int, [_P, _P, _P, _P, _P, _c.c_int, _c.c_int64, _c.c_int64,
@@ -140,7 +140,7 @@ def check(status: int) -> None:
 # statistics, the transposed quantizer 2 without a scale bound
 KERNELS_PER_CALL = {"bl_nvfp4_step_quantized": 1, "bl_nvfp4_lattice_update": 1, "bl_nvfp4_lattice_update_many": 0,
                     "bl_nvfp4_lattice_update_fixed_scratch": 1, "bl_direction": 1,
-                    "bl_update_shard_stats": 1, "bl_nvfp4_lattice_update_shards": 2,
+                    "bl_update_shard_stats": 0, "bl_nvfp4_lattice_update_shards": 0,
                     "bl_nvfp4_dequantize": 1, "bl_nvfp4_amax": 1, "bl_nvfp4_quantize": 1, "bl_nvfp4_quantize_t": 1,
                     "bl_nvfp4_quantize_4over6": 1, "bl_nvfp4_amax_quantize": 2, "bl_nvfp4_quantize_general": 2, "bl_fp4_fold_scales": 1,
                     "bl_nvfp4_requantize_t": 1, "bl_nvfp4_scales_to_blocked": 1, "bl_nvfp4_gemm": 1, "bl_nvfp4_gemm_accumulate": 1,

@@ -290,58 +290,57 @@ def lattice_update_many(items, fmt, *, lr: float, weight_decay: float, phase_bit
 
 def lattice_update_shards(items, fmt, world: int, rank: int, exchange, *, lr: float, weight_decay: float,
                           phase_bits: int, phase_cb: int, rounding: str, strata: int, scale_rule: str, trust: float,
-                          trust_lr: float, direction: str, clip: float = 1.0) -> None:
+                          trust_lr: float, direction: str, clip: float = 1.0, plan: UpdatePlan | None = None,
+                          grads=None, steps=None) -> None:
     """The fused update of row shards whose direction normalises over the whole weight (colnorm; raw and sign with
-    clip < 1): together the ``world`` owners of the shards reproduce the unsharded update bit for bit. ``items`` as for
-    ``lattice_update_many``; every tensor is owner ``rank``'s shard, rows [rank * rows, (rank + 1) * rows) of a weight
-    of ``world * rows`` rows (rows a multiple of 128; ``offset`` = the RNG index of the shard's first element). Between
-    the statistics and the update ``exchange(blocks)`` is called once per 40 tensors with an fp32 tensor [world, n] of
-    which this owner has filled row ``rank``; on return every row must hold its owner's sums (an in-place all-gather,
-    issued on the current stream)."""
+    clip < 1): together the ``world`` owners of the shards reproduce the unsharded update bit for bit. ``items`` (or
+    ``plan``, ``grads``, ``steps``) as for ``lattice_update_many``; every tensor is owner ``rank``'s shard, rows
+    [rank * rows, (rank + 1) * rows) of a weight of ``world * rows`` rows (rows a multiple of 128; ``offset`` = the RNG
+    index of the shard's first element). Between the statistics and the update ``exchange(blocks)`` is called once
+    with an fp32 tensor [world, n] of which this owner has filled row ``rank``; on return every row must hold its
+    owner's sums (an in-place all-gather, issued on the current stream)."""
     if direction not in _DIRECTION:
         raise RuntimeError(f"direction {direction!r} is outside this build (raw, sign, colnorm are built)")
-    if not _is_nvfp4(fmt):
-        raise RuntimeError("only NVFP4 tensors (no zero points) are built")
-    for lo in range(0, len(items), 40):
-        part = items[lo:lo + 40]
-        n = len(part)
-        gdtype = part[0]["grad"].dtype
-        if gdtype not in _C.DTYPE:
-            raise RuntimeError("gradient: bf16, fp16 or fp32 with rows*cols elements")
-        for it in part:
-            _require(it["packed"], "packed", torch.uint8)
-            _require(it["scales"], "scales")
-            _require(it["global_scale"], "global_scale", torch.float32)
-            if phase_bits > 0:
-                _require(it["phase"], "phase", torch.uint8)
-            G = it["grad"]
-            if G.dtype != gdtype or G.numel() != int(it["rows"]) * int(it["cols"]) or not G.is_cuda or not G.is_contiguous():
-                raise RuntimeError("gradient: a contiguous CUDA tensor of the group's dtype with rows*cols elements")
-        ptrs = lambda k: (ctypes.c_void_p * n)(*[it[k].data_ptr() for it in part])
-        rows = (ctypes.c_int64 * n)(*[int(it["rows"]) for it in part])
-        cols = (ctypes.c_int64 * n)(*[int(it["cols"]) for it in part])
-        grad = ptrs("grad")
-        dev = part[0]["packed"]
-        need = int(_C.lib().bl_update_shards_scratch_bytes(n, rows, cols, world))
-        scratch = _scratch_for(dev.device, need)
-        where, block = ctypes.c_uint64(0), ctypes.c_uint64(0)
-        _C.call("bl_update_shard_stats", n, grad, rows, cols, world, rank, _C.DTYPE[gdtype], _DIRECTION[direction],
-                float(clip), _C.ptr(scratch), scratch.numel(), ctypes.byref(where), ctypes.byref(block),
-                _C.device_of(dev), _C.stream_of(dev))
-        if world > 1:
-            exchange(scratch[where.value:where.value + world * block.value].view(torch.float32).view(world, -1))
-        sj = (ctypes.c_int * n)()
-        strat_k = 1
-        for i, it in enumerate(part):
-            sj[i], strat_k = strat_args(rounding, it["step"], strata)
-        _C.call("bl_nvfp4_lattice_update_shards", n, ptrs("packed"), ptrs("phase") if phase_bits > 0 else None,
-                ptrs("scales"), ptrs("global_scale"), grad, rows, cols, world, rank,
-                (ctypes.c_uint64 * n)(*[int(it["offset"]) & 0xFFFFFFFFFFFFFFFF for it in part]),
-                (ctypes.c_uint32 * n)(*[int(it["seed"]) & 0xFFFFFFFF for it in part]),
-                (ctypes.c_uint32 * n)(*[int(it["step"]) & 0xFFFFFFFF for it in part]), sj, _C.DTYPE[gdtype], phase_bits,
-                phase_cb, float(lr), float(1.0 - lr * weight_decay), _ROUNDING[rounding], strat_k, _RULE[scale_rule],
-                float(kappa(trust, trust_lr, lr)), _DIRECTION[direction], float(clip), _C.ptr(scratch), scratch.numel(),
-                _C.device_of(dev), _C.stream_of(dev))
+    if plan is None:
+        if len(items) == 0:
+            return
+        plan = UpdatePlan(items, fmt, phase_bits)
+        grads = [it["grad"] for it in items]
+        steps = [it["step"] for it in items]
+    n, gdtype = plan.n, plan.gdtype
+    if gdtype not in _C.DTYPE:
+        raise RuntimeError("gradient: bf16, fp16 or fp32 with rows*cols elements")
+    grad, step, sj = plan.grad, plan.step, plan.strat_j
+    strat_k = 1
+    for i in range(n):
+        G = grads[i]
+        if G.dtype != gdtype or G.numel() != plan.numel[i] or not G.is_cuda or not G.is_contiguous():
+            raise RuntimeError("gradient: a contiguous CUDA tensor of the group's dtype with rows*cols elements")
+        grad[i] = G.data_ptr()
+        step[i] = int(steps[i]) & 0xFFFFFFFF
+        if rounding == "strat":
+            sj[i], strat_k = strat_args(rounding, steps[i], strata)
+    if rounding != "strat":
+        strat_k = strat_args(rounding, steps[0], strata)[1]
+    dev = plan.device
+    need = plan.scratch_need.get(("shards", world))
+    if need is None:
+        need = plan.scratch_need[("shards", world)] = int(_C.lib().bl_update_shards_scratch_bytes(n, plan.rows, plan.cols,
+                                                                                                  world))
+    scratch = _scratch_for(dev.device, need)
+    where, block, launches = ctypes.c_uint64(0), ctypes.c_uint64(0), ctypes.c_int(0)
+    _C.call("bl_update_shard_stats", n, grad, plan.rows, plan.cols, world, rank, _C.DTYPE[gdtype], _DIRECTION[direction],
+            float(clip), _C.ptr(scratch), scratch.numel(), ctypes.byref(where), ctypes.byref(block), _C.device_of(dev),
+            _C.stream_of(dev), ctypes.byref(launches))
+    _C.Counters.launches += launches.value
+    if world > 1:
+        exchange(scratch[where.value:where.value + world * block.value].view(torch.float32).view(world, -1))
+    _C.call("bl_nvfp4_lattice_update_shards", n, plan.packed, plan.phase, plan.scales, plan.gs, grad, plan.rows,
+            plan.cols, world, rank, plan.offset, plan.seed, step, sj, _C.DTYPE[gdtype], phase_bits, phase_cb, float(lr),
+            float(1.0 - lr * weight_decay), _ROUNDING[rounding], strat_k, _RULE[scale_rule],
+            float(kappa(trust, trust_lr, lr)), _DIRECTION[direction], float(clip), _C.ptr(scratch), scratch.numel(),
+            _C.device_of(dev), _C.stream_of(dev), ctypes.byref(launches))
+    _C.Counters.launches += launches.value
 
 
 def direction(G, kind: str, r=None, c=None, k: int = 1, beta2: float = 0.95, block=0, ns_steps: int = 5,

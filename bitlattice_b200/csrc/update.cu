@@ -1125,13 +1125,14 @@ extern "C" int bl_nvfp4_lattice_update_many(int count, uint8_t* const* codes, ui
 
 // ---- row shards whose direction normalises over the whole weight ----
 // `world` owners hold equal row shards of every weight, owner r the rows [r * rows, (r + 1) * rows). Each sums its own
-// 128-row panels into ITS block of the batch's exchange area, the owners exchange the blocks (ONE all-gather in place
-// per batch: the host's job, between the two calls), and each finalizes over all panels in ascending order:
+// 128-row panels into ITS block of the call's exchange area, the owners exchange the blocks (ONE all-gather in place
+// per call: the host's job, between the two calls), and each finalizes over all panels in ascending order:
 // denominators, RMS and therefore every code, phase and scale byte equal those of the unsharded update. A shard holds a
 // multiple of 128 rows, so the panels are the unsharded ones.
 //
-// Scratch: [256 B arrival counters][exchange area: world blocks][the tensors' regions]. A block holds, per tensor, the
-// [rows / 128, cols] sums of one owner, each slice rounded up to 256 bytes.
+// Scratch: [256 B arrival counters][exchange area: world blocks][the tensors' regions]. A block holds, per tensor of the
+// call, the [rows / 128, cols] sums of one owner, each slice rounded up to 256 bytes. A call may hold any number of
+// tensors: the kernels run over batches of up to kMaxBatch of them, the exchange covers them all at once.
 
 struct ShardLayout {
   size_t block_bytes, area_offset, total_bytes;
@@ -1154,7 +1155,7 @@ static ShardLayout shard_layout(int count, const int64_t* rows, const int64_t* c
 
 static int check_shards(const char* who, int count, const int64_t* rows, const int64_t* cols, int world, int rank,
                         int direction, double clip, const void* scratch, size_t scratch_bytes) {
-  BL_REQUIRE(count >= 0 && count <= kMaxBatch, "%s: between 0 and %d tensors per call, got %d", who, kMaxBatch, count);
+  BL_REQUIRE(count >= 0, "%s: negative count", who);
   BL_REQUIRE(count == 0 || (rows && cols), "%s: null array", who);
   BL_REQUIRE(world >= 1 && rank >= 0 && rank < world, "%s: owner %d of %d", who, rank, world);
   BL_REQUIRE(needs_stats(direction, clip), "%s: this direction has no statistics (use the plain update)", who);
@@ -1165,24 +1166,28 @@ static int check_shards(const char* who, int count, const int64_t* rows, const i
                who, i, kPanelRows, (long long)rows[i]);
   }
   const ShardLayout L = shard_layout(count, rows, cols, world);
-  BL_REQUIRE(L.total_bytes < (size_t(1) << 39), "%s: statistics of %zu bytes", who, L.total_bytes);
+  BL_REQUIRE(L.total_bytes < (size_t(1) << 39) && L.block_bytes / 4 < (size_t(1) << 32), "%s: statistics of %zu bytes",
+             who, L.total_bytes);
   BL_REQUIRE(count == 0 || (scratch != nullptr && aligned16(scratch) && scratch_bytes >= L.total_bytes),
              "%s: needs %zu bytes of 16-byte aligned scratch, got %zu", who, L.total_bytes, scratch_bytes);
   return 0;
 }
 
-// descriptors' statistics fields and scratch offsets for owner `rank` of `world`
-static void place_shards(Batch& B, const int64_t* rows, const int64_t* cols, int world, int rank) {
-  const ShardLayout L = shard_layout(B.count, rows, cols, world);
+// statistics fields and scratch offsets of the descriptors in B, which are the call's tensors [first, first + B.count),
+// for owner `rank` of `world`
+static void place_shards(Batch& B, int first, int count, const int64_t* rows, const int64_t* cols, int world, int rank) {
+  const ShardLayout L = shard_layout(count, rows, cols, world);
   B.stat_stride = static_cast<uint32_t>(L.block_bytes / 4);
   size_t slice = L.area_offset, region = L.area_offset + L.block_bytes * world;
-  for (int i = 0; i < B.count; ++i) {
-    TensorDesc& t = B.t[i];
-    t.stat_rows = static_cast<int>(rows[i] * world);
-    t.stat_local = stats_panels(static_cast<int>(rows[i]));
-    t.stat_panel0 = rank * t.stat_local;
-    t.gather256 = static_cast<uint32_t>(slice / 256);
-    t.scratch256 = static_cast<uint32_t>(region / 256);
+  for (int i = 0; i < first + B.count; ++i) {
+    if (i >= first) {
+      TensorDesc& t = B.t[i - first];
+      t.stat_rows = static_cast<int>(rows[i] * world);
+      t.stat_local = stats_panels(static_cast<int>(rows[i]));
+      t.stat_panel0 = rank * t.stat_local;
+      t.gather256 = static_cast<uint32_t>(slice / 256);
+      t.scratch256 = static_cast<uint32_t>(region / 256);
+    }
     slice += shard_slice_bytes(rows[i], cols[i]);
     region += tensor_scratch_bytes(rows[i] * world, cols[i]);
   }
@@ -1196,7 +1201,8 @@ extern "C" size_t bl_update_shards_scratch_bytes(int count, const int64_t* rows,
 extern "C" int bl_update_shard_stats(int count, const void* const* grad, const int64_t* rows, const int64_t* cols,
                                      int world, int rank, int grad_dtype, int direction, double clip, void* scratch,
                                      size_t scratch_bytes, uint64_t* exchange_offset, uint64_t* block_bytes, int device,
-                                     bl_stream_t stream) {
+                                     bl_stream_t stream, int* launches) {
+  if (launches) *launches = 0;
   if (int rc = check_shards("update_shard_stats", count, rows, cols, world, rank, direction, clip, scratch, scratch_bytes))
     return rc;
   BL_REQUIRE(count == 0 || grad, "update_shard_stats: null array");
@@ -1205,20 +1211,26 @@ extern "C" int bl_update_shard_stats(int count, const void* const* grad, const i
   const ShardLayout L = shard_layout(count, rows, cols, world);
   *exchange_offset = L.area_offset;
   *block_bytes = L.block_bytes;
-  if (count == 0) return 0;
-  Batch B;
-  B.count = count;
-  for (int i = 0; i < count; ++i) {
+  for (int i = 0; i < count; ++i)
     BL_REQUIRE(grad[i] != nullptr && aligned16(grad[i]), "update_shard_stats: gradient %d: null or not 16-byte aligned", i);
-    B.t[i] = make_desc(nullptr, nullptr, nullptr, nullptr, nullptr, grad[i], rows[i], cols[i], 0, 0, 0, 0, 0);
-  }
-  place_shards(B, rows, cols, world, rank);
   BL_DEVICE(device);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   unsigned char* sc = static_cast<unsigned char*>(scratch);
-  if (grad_dtype == BL_BF16) return run_colstats<__nv_bfloat16>(B, direction, sc, st);
-  if (grad_dtype == BL_F16) return run_colstats<__half>(B, direction, sc, st);
-  return run_colstats<float>(B, direction, sc, st);
+  for (int first = 0; first < count; first += kMaxBatch) {
+    Batch B;
+    B.count = count - first < kMaxBatch ? count - first : kMaxBatch;
+    for (int k = 0; k < B.count; ++k)
+      B.t[k] = make_desc(nullptr, nullptr, nullptr, nullptr, nullptr, grad[first + k], rows[first + k], cols[first + k],
+                         0, 0, 0, 0, 0);
+    place_shards(B, first, count, rows, cols, world, rank);
+    int rc;
+    if (grad_dtype == BL_BF16) rc = run_colstats<__nv_bfloat16>(B, direction, sc, st);
+    else if (grad_dtype == BL_F16) rc = run_colstats<__half>(B, direction, sc, st);
+    else rc = run_colstats<float>(B, direction, sc, st);
+    if (rc) return rc;
+    if (launches) *launches += 1;
+  }
+  return 0;
 }
 
 template <typename GT>
@@ -1235,34 +1247,43 @@ extern "C" int bl_nvfp4_lattice_update_shards(int count, uint8_t* const* codes, 
                                               const uint32_t* step, const int* strat_j, int grad_dtype, int phase_bits,
                                               int phase_cb, double lr, double decay, int rounding, int strat_k, int rule,
                                               double kappa, int direction, double clip, void* scratch,
-                                              size_t scratch_bytes, int device, bl_stream_t stream) {
+                                              size_t scratch_bytes, int device, bl_stream_t stream, int* launches) {
+  if (launches) *launches = 0;
   if (int rc = check_shards("lattice_update_shards", count, rows, cols, world, rank, direction, clip, scratch,
                             scratch_bytes))
     return rc;
   BL_REQUIRE(count == 0 || (codes && scales && global_scale && grad && offset && seed && step),
              "lattice_update_shards: null array");
   BL_REQUIRE(phase_bits == 0 || phase != nullptr, "lattice_update_shards: null phase array");
-  if (count == 0) return 0;
-  Batch B;
-  B.count = count;
   for (int i = 0; i < count; ++i) {
     if (int rc = check_common(rows[i], cols[i], phase_bits, phase_cb, phase_bits ? phase[i] : nullptr, rounding, rule))
       return rc;
     if (int rc = check_update_args("lattice_update_shards", codes[i], phase_bits ? phase[i] : nullptr, scales[i],
                                    global_scale[i], grad[i], grad_dtype, direction, clip))
       return rc;
-    B.t[i] = make_desc(codes[i], phase_bits ? phase[i] : nullptr, scales[i], scales[i], global_scale[i], grad[i],
-                       rows[i], cols[i], offset[i], rounding, seed[i], step[i], strat_j ? strat_j[i] : 0);
   }
-  place_shards(B, rows, cols, world, rank);
   BL_DEVICE(device);
   const StepParams P = make_params(lr, decay, phase_bits, rule, kappa, rounding, strat_k);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   unsigned char* sc = static_cast<unsigned char*>(scratch);
   const int pcb = phase_bits ? phase_cb : 0;
-  if (grad_dtype == BL_BF16) return shard_update_typed<__nv_bfloat16>(B, pcb, P, direction, clip, sc, st);
-  if (grad_dtype == BL_F16) return shard_update_typed<__half>(B, pcb, P, direction, clip, sc, st);
-  return shard_update_typed<float>(B, pcb, P, direction, clip, sc, st);
+  for (int first = 0; first < count; first += kMaxBatch) {
+    Batch B;
+    B.count = count - first < kMaxBatch ? count - first : kMaxBatch;
+    for (int k = 0; k < B.count; ++k) {
+      const int i = first + k;
+      B.t[k] = make_desc(codes[i], phase_bits ? phase[i] : nullptr, scales[i], scales[i], global_scale[i], grad[i],
+                         rows[i], cols[i], offset[i], rounding, seed[i], step[i], strat_j ? strat_j[i] : 0);
+    }
+    place_shards(B, first, count, rows, cols, world, rank);
+    int rc;
+    if (grad_dtype == BL_BF16) rc = shard_update_typed<__nv_bfloat16>(B, pcb, P, direction, clip, sc, st);
+    else if (grad_dtype == BL_F16) rc = shard_update_typed<__half>(B, pcb, P, direction, clip, sc, st);
+    else rc = shard_update_typed<float>(B, pcb, P, direction, clip, sc, st);
+    if (rc) return rc;
+    if (launches) *launches += 2;
+  }
+  return 0;
 }
 
 extern "C" int bl_direction(const void* grad, int grad_dtype, int64_t rows, int64_t cols, int direction, double clip,

@@ -384,45 +384,28 @@ class Lattice(torch.optim.Optimizer):
         _, rank, group = self._shard_world()
         dist.all_gather_into_tensor(blocks.view(-1), blocks[rank], group=group)
 
-    def _update_shards(self, ps, g: dict, grads=None) -> None:
-        """The fused update of the row shards ``ps`` with the statistics of the whole weights (``shard_group``)."""
-        bits = g["phase_bits"]
-        cb = _ops.phase_container(bits)
+    def _check_shards(self, ps) -> tuple[int, int]:
+        """(world, rank) after checking that every parameter of ``ps`` is this rank's equal share of its weight."""
         world, rank, _ = self._shard_world()
-        items = []
-        for i, p in enumerate(ps):
+        for p in ps:
             row0 = int(getattr(p, "_bl_row_offset", 0))
             if p._bl_rows_total != world * p.rows or row0 != rank * p.rows:
                 raise RuntimeError(f"shard_group: rank {rank} of {world} holds rows [{row0}, {row0 + p.rows}) of "
                                    f"{p._bl_rows_total}; equal row shards in rank order are built")
-            st = self.state[p]
-            if grads is None:                         # the caller of the one-tensor form has advanced the step
-                self._invalidate(p)
-                st["step"] = st.get("step", 0) + 1
-            if bits and "phase" not in st:
-                st["phase"] = torch.zeros(p.rows, packed_cols(p.cols, cb), dtype=torch.uint8, device=p.packed.device)
-            items.append(dict(packed=p.packed, phase=st["phase"] if bits else None, scales=p.scales,
-                              global_scale=p.global_scale, grad=p.grad if grads is None else grads[i], rows=p.rows,
-                              cols=p.cols, offset=row0 * p.cols, seed=(self.seed + 7919 * self._pid[p]) & 0xFFFFFFFF,
-                              step=st["step"]))
-        with _nvtx("bl.lattice_update"):
-            _ops.lattice_update_shards(items, ps[0].fmt, world, rank, self._exchange, lr=g["lr"],
-                                       weight_decay=g["weight_decay"], phase_bits=bits, phase_cb=cb,
-                                       rounding=g["rounding"], strata=g["strata"], scale_rule=g["scale_rule"],
-                                       trust=g["trust"], trust_lr=g["trust_lr"], direction=self._kind(ps[0], g),
-                                       clip=g["clip"])
+        return world, rank
 
     def _update_many(self, ps, g: dict) -> None:
         bits = g["phase_bits"]
         cb = _ops.phase_container(bits)
         kind = self._kind(ps[0], g)
+        shards = None
         if self._whole_weight(g, kind):
-            shards = [p for p in ps if self._is_shard(p)]
-            if shards:
-                self._update_shards(shards, g)
-                ps = [p for p in ps if not self._is_shard(p)]
-                if not ps:
-                    return
+            mine = [p for p in ps if self._is_shard(p)]
+            if mine and len(mine) < len(ps):          # shards and whole weights: each kind in a call of its own
+                self._update_many(mine, g)
+                return self._update_many([p for p in ps if not self._is_shard(p)], g)
+            if mine:
+                shards = self._check_shards(ps)
         state, invalidate = self.state, self._invalidate
         steps, grads, tensors = [], [], []
         for p in ps:
@@ -443,6 +426,13 @@ class Lattice(torch.optim.Optimizer):
                           seed=(self.seed + 7919 * self._pid[p]) & 0xFFFFFFFF, step=s)
                      for p, t, G, s in zip(ps, tensors, grads, steps)]
             plan = self._plans[key] = _ops.UpdatePlan(items, ps[0].fmt, bits)
+        common = dict(lr=g["lr"], weight_decay=g["weight_decay"], phase_bits=bits, phase_cb=cb, rounding=g["rounding"],
+                      strata=g["strata"], scale_rule=g["scale_rule"], trust=g["trust"], trust_lr=g["trust_lr"],
+                      direction=kind, clip=g["clip"], plan=plan, grads=grads, steps=steps)
+        if shards is not None:                       # statistics of the whole weights, exchanged among the owners
+            with _nvtx("bl.lattice_update"):
+                _ops.lattice_update_shards(None, ps[0].fmt, *shards, self._exchange, **common)
+            return
         scratch = None
         if self.overlap:                             # updates that run beside the caller's stream: a buffer of their own
             need = plan.scratch_bytes(kind, g["clip"])
@@ -451,10 +441,7 @@ class Lattice(torch.optim.Optimizer):
             if need and (scratch is None or scratch.numel() < need):
                 scratch = self._scratch[dev] = torch.empty(need, dtype=torch.uint8, device=dev)
         with _nvtx("bl.lattice_update"):
-            _ops.lattice_update_many(None, ps[0].fmt, lr=g["lr"], weight_decay=g["weight_decay"], phase_bits=bits,
-                                     phase_cb=cb, rounding=g["rounding"], strata=g["strata"], scale_rule=g["scale_rule"],
-                                     trust=g["trust"], trust_lr=g["trust_lr"], direction=kind, clip=g["clip"],
-                                     scratch=scratch, plan=plan, grads=grads, steps=steps)
+            _ops.lattice_update_many(None, ps[0].fmt, scratch=scratch, **common)
 
     @contextlib.contextmanager
     def accumulate(self):
@@ -524,7 +511,14 @@ class Lattice(torch.optim.Optimizer):
                                 rows, cols, inplace_scales=True, **common)
             return
         if self._whole_weight(g, kind) and self._is_shard(p):
-            return self._update_shards([p], g, [G2.contiguous()])
+            item = dict(packed=p.packed, phase=st.get("phase") if bits else None, scales=p.scales,
+                        global_scale=p.global_scale, grad=G2.contiguous(), rows=rows, cols=cols,
+                        offset=common["offset"], seed=seed, step=st["step"])
+            shared = {k: v for k, v in common.items() if k not in ("seed", "step", "offset")}
+            with _nvtx("bl.lattice_update"):
+                _ops.lattice_update_shards([item], p.fmt, *self._check_shards([p]), self._exchange, direction=kind,
+                                           clip=g["clip"], **shared)
+            return
         scratch = None
         if self.overlap:                             # column statistics of updates that run beside the caller's stream
             need = _ops.update_scratch_bytes(rows, cols, kind, g["clip"])

@@ -114,25 +114,27 @@ BL_API int bl_nvfp4_lattice_update_many(int count, uint8_t* const* codes, uint8_
  *      number `rank` of the call's exchange area: `world` blocks of *block_bytes bytes starting *exchange_offset bytes
  *      into `scratch`;
  *   2. the host exchanges the blocks among the owners (ONE in-place all-gather of world * block_bytes bytes on the
- *      same stream) -- the library makes no collective call;
+ *      same stream, whatever the number of tensors) -- the library makes no collective call;
  *   3. bl_nvfp4_lattice_update_shards: every owner sums all panels in ascending order of their rows (the unsharded
  *      order), derives the column denominators and the RMS divisor of the whole weights, and updates its rows.
  *      `offset` is the RNG index of the shard's first element (rank * rows * cols for a weight that is not itself a
  *      tile of something larger).
- * At most 40 tensors per call; both calls get the same rows / cols / world / rank and the same scratch of
- * bl_update_shards_scratch_bytes(count, rows, cols, world) bytes, untouched in between except for step 2. Launches:
- * one (statistics); two (reduction, update). */
+ * Both calls get the same rows / cols / world / rank and the same scratch of
+ * bl_update_shards_scratch_bytes(count, rows, cols, world) bytes, untouched in between except for step 2. Per 40
+ * tensors the first call launches one kernel (statistics) and the second two (reduction, update); launches (nullable)
+ * receives the number. */
 BL_API size_t bl_update_shards_scratch_bytes(int count, const int64_t* rows, const int64_t* cols, int world);
 BL_API int bl_update_shard_stats(int count, const void* const* grad, const int64_t* rows, const int64_t* cols, int world,
                           int rank, int grad_dtype, int direction, double clip, void* scratch, size_t scratch_bytes,
-                          uint64_t* exchange_offset, uint64_t* block_bytes, int device, bl_stream_t stream);
+                          uint64_t* exchange_offset, uint64_t* block_bytes, int device, bl_stream_t stream,
+                          int* launches);
 BL_API int bl_nvfp4_lattice_update_shards(int count, uint8_t* const* codes, uint8_t* const* phase, uint8_t* const* scales,
                                    const float* const* global_scale, const void* const* grad, const int64_t* rows,
                                    const int64_t* cols, int world, int rank, const uint64_t* offset,
                                    const uint32_t* seed, const uint32_t* step, const int* strat_j, int grad_dtype,
                                    int phase_bits, int phase_cb, double lr, double decay, int rounding, int strat_k,
                                    int rule, double kappa, int direction, double clip, void* scratch,
-                                   size_t scratch_bytes, int device, bl_stream_t stream);
+                                   size_t scratch_bytes, int device, bl_stream_t stream, int* launches);
 
 /* The update kernel has two routes with identical results: a fast one (stochastic rounding, 1..7 phase bits: packed
  * fp32 pairs, one range check per element instead of one per division; single groups whose values leave that range

@@ -185,9 +185,10 @@ def test_shard_group_selects_the_whole_weight_update_and_rejects_unequal_shards(
     assert opt._whole_weight(g, "colnorm") and opt._whole_weight(g, "raw") and not opt._whole_weight(g, "sign")
     assert opt._whole_weight({**g, "clip": 0.5}, "sign")
     opt._shard_world = lambda: (4, 1, None)          # four ranks, but the shard is one half of its weight
-    sh.grad = torch.zeros(128, sh.shape[1], dtype=torch.bfloat16)
     with pytest.raises(RuntimeError, match="equal row shards in rank order"):
-        opt._update_shards([sh], g)
+        opt._check_shards([sh])
+    opt._shard_world = lambda: (2, 1, None)
+    assert opt._check_shards([sh]) == (2, 1)
 
 
 def test_newton_schulz_orthogonalises_and_matches_its_coefficients():

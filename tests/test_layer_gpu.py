@@ -457,15 +457,16 @@ def test_row_shard_update_equals_whole_update():
         assert torch.equal(os_.state[sh]["phase"], ow.state[whole]["phase"][rank * 64:(rank + 1) * 64])
 
 
-@pytest.mark.parametrize("direction,clip", [("colnorm", 1.0), ("colnorm", 0.25), ("raw", 0.5), ("sign", 0.5)])
-def test_row_shards_with_whole_weight_statistics_equal_the_whole_update(direction, clip):
+@pytest.mark.parametrize("direction,clip,count", [("colnorm", 1.0, 2), ("colnorm", 0.25, 2), ("raw", 0.5, 2),
+                                                  ("sign", 0.5, 2), ("colnorm", 1.0, 45)])
+def test_row_shards_with_whole_weight_statistics_equal_the_whole_update(direction, clip, count):
     """``Lattice(shard_group=...)``: directions that normalise over the whole weight exchange their 128-row panel sums,
     and every shard then receives, bit for bit, the update of its rows in the unsharded weight. Four owners are played
     in turn on one GPU: a first pass collects each owner's panel sums, a second hands every owner the others' sums
-    where the all-gather would have put them."""
+    where the all-gather would have put them. 45 weights: more than one batch of kernels, still one exchange."""
     from bitlattice_b200.parallel import shard_rows
     world = 4
-    shapes = [(512, 256), (1024, 384)]
+    shapes = [(512, 256), (1024, 384)] + [(512, 64)] * (count - 2)
     ws = [bl.LatticeTensor.from_float((torch.randn(*s, generator=gen(60 + i)) * 0.05).to(DEV), "nvfp4", method="rtn",
                                       dtype=torch.bfloat16) for i, s in enumerate(shapes)]
     Gs = [(torch.randn(*s, generator=gen(70 + i)) * (1e-2 * (1 + torch.arange(s[1]) % 7))).to(DEV, torch.bfloat16)
@@ -494,7 +495,7 @@ def test_row_shards_with_whole_weight_statistics_equal_the_whole_update(directio
     sums = {}
     for rank in range(world):
         def collect(blocks, rank=rank):
-            assert blocks.shape[0] == world
+            assert blocks.shape[0] == world and rank not in sums          # one exchange per step
             sums[rank] = blocks[rank].clone()
             raise Stop
         _, opt = owner(rank, collect, shard_group=True)
