@@ -96,9 +96,7 @@ __device__ __forceinline__ int64_t scale_index(int layout, int64_t r, int64_t c1
 
 // ------------------------------------------------------------------------------------------------ rows
 
-// x [rows, cols] -> codes [rows, cols/2], scales. Every thread has kRowsUnroll independent blocks in flight (their
-// loads are issued before any arithmetic).
-constexpr int kRowsUnroll = 2;
+// x [rows, cols] -> codes [rows, cols/2], scales.
 
 // ---- rows, one thread per block of 16 ---------------------------------------------------------------------------------
 
@@ -213,12 +211,11 @@ __device__ __forceinline__ void unpack_raw16(const Raw16<T>& r, float v[16]) {
 }
 
 // block (bx, 256/bx): x covers the 16-element blocks of a row, y covers rows; a thread keeps its block column and walks
-// down the rows, kRowsUnroll rows in flight (their loads are issued before any arithmetic).
+// down the rows, the next row's block in flight while the current one is quantized.
 template <typename T, int MODE>
-__global__ void __launch_bounds__(kQThreads, 3) quantize_rows16_kernel(const T* __restrict__ x, int64_t rows, int64_t cols,
-                                                                    const float* __restrict__ global, uint32_t key,
-                                                                    uint8_t* __restrict__ codes,
-                                                                    uint8_t* __restrict__ scales, int layout) {
+__global__ void __launch_bounds__(kQThreads, MODE == kModeSr ? 4 : 3)
+    quantize_rows16_kernel(const T* __restrict__ x, int64_t rows, int64_t cols, const float* __restrict__ global,
+                           uint32_t key, uint8_t* __restrict__ codes, uint8_t* __restrict__ scales, int layout) {
   const float g = global[0];
   const float rg = __frcp_rn(g);
   const int64_t cb = static_cast<int64_t>(blockIdx.x) * blockDim.x + threadIdx.x;   // block column
@@ -229,27 +226,23 @@ __global__ void __launch_bounds__(kQThreads, 3) quantize_rows16_kernel(const T* 
   // ((r >> 5) & 3) * 4 + (cb & 3)
   const int64_t nc = (cols16 + 3) >> 2;
   const int64_t sf_col = layout == BL_SF_ROWMAJOR ? cb : (cb >> 2) * 512 + (cb & 3);
-  for (int64_t r0 = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y; r0 < rows;
-       r0 += row_step * kRowsUnroll) {
-    Raw16<T> raw[kRowsUnroll];
-#pragma unroll
-    for (int u = 0; u < kRowsUnroll; ++u) {
-      const int64_t r = r0 + u * row_step;
-      if (r < rows) load_raw16(x + r * cols + cb * 16, raw[u]);
-    }
-#pragma unroll
-    for (int u = 0; u < kRowsUnroll; ++u) {
-      const int64_t r = r0 + u * row_step;
-      if (r >= rows) break;
-      float v[16];
-      unpack_raw16(raw[u], v);
-      uint32_t sb;
-      const uint2 out = quantize_block<MODE>(v, 1.0f, g, rg, key, static_cast<uint32_t>(r * cols + cb * 16), &sb);
-      __stcs(reinterpret_cast<uint2*>(codes + r * (cols / 2)) + cb, out);
-      const int64_t sf_row = layout == BL_SF_ROWMAJOR ? r * cols16
-                                                      : (r >> 7) * nc * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4;
-      scales[sf_row + sf_col] = static_cast<uint8_t>(sb);
-    }
+  // the next row's block is loaded before the current one is worked on: a warp never waits for memory with nothing
+  // else to issue
+  int64_t r = static_cast<int64_t>(blockIdx.y) * blockDim.y + threadIdx.y;
+  Raw16<T> cur;
+  if (r < rows) load_raw16(x + r * cols + cb * 16, cur);
+  for (; r < rows; r += row_step) {
+    Raw16<T> next;
+    if (r + row_step < rows) load_raw16(x + (r + row_step) * cols + cb * 16, next);
+    float v[16];
+    unpack_raw16(cur, v);
+    uint32_t sb;
+    const uint2 out = quantize_block<MODE>(v, 1.0f, g, rg, key, static_cast<uint32_t>(r * cols + cb * 16), &sb);
+    __stcs(reinterpret_cast<uint2*>(codes + r * (cols / 2)) + cb, out);
+    const int64_t sf_row = layout == BL_SF_ROWMAJOR ? r * cols16
+                                                    : (r >> 7) * nc * 512 + (r & 31) * 16 + ((r >> 5) & 3) * 4;
+    scales[sf_row + sf_col] = static_cast<uint8_t>(sb);
+    cur = next;
   }
 }
 
@@ -263,7 +256,8 @@ static RowGeometry row_geometry(int64_t rows, int64_t cols, int device) {
   while (bx < kQThreads && bx < cpr) bx <<= 1;
   const int by = kQThreads / bx;
   const int64_t gx = (cpr + bx - 1) / bx;
-  int64_t gy = (static_cast<int64_t>(sm_count(device)) * 8 + gx - 1) / gx;
+  // whole waves whether an SM holds three or four CTAs (59-62 registers per thread): no partly filled last wave
+  int64_t gy = (static_cast<int64_t>(sm_count(device)) * 12) / gx;
   const int64_t max_gy = (rows + by - 1) / by;
   gy = gy < 1 ? 1 : (gy > max_gy ? max_gy : gy);
   if (gy > 65535) gy = 65535;
