@@ -358,9 +358,17 @@ __device__ __forceinline__ uint2 e2m1_rtn16(const float v[16], float pre, float 
 // of 2^24, in the bits below. The draw n = hash >> 8 rounds up iff n < that fraction, which is the carry of adding
 // (2^24 - 1 - n): so the code is ((A >> t) + (~hash >> 8) >> 24) + 2 t. Identical to comparing u * gap < a - lo in
 // real numbers, which is what the reference's fp32 expression evaluates without rounding.
+// (Shifts, adds and bit operations issue on the ALU pipe, which bounds this loop -- over 80 % busy with the multiply-add
+// pipe at a quarter. The 2 t and the merge of the nibble into the word are therefore integer multiply-adds, with the
+// multipliers read from constant memory so that the compiler cannot turn them back into shifts and ors: 7 % off the
+// transposed stochastic quantizer. High products and wide multiply-adds in place of the right shifts cost more than
+// the two ALU instructions they replace; measured and not kept.)
+static __device__ __constant__ uint32_t kPipeMul[9] = {2u, 1u, 1u << 4, 1u << 8, 1u << 12, 1u << 16, 1u << 20, 1u << 24, 1u << 28};
+
 __device__ __forceinline__ uint2 e2m1_sr16(const float v[16], float inv, uint32_t key, uint32_t idx0) {
   uint32_t w[2] = {0u, 0u};
   const uint32_t h0 = idx0 * 0x27D4EB2Fu + key;
+  const uint32_t two = kPipeMul[0];
 #pragma unroll
   for (int i = 0; i < 16; i += 2) {
     float x[2];
@@ -374,9 +382,9 @@ __device__ __forceinline__ uint2 e2m1_sr16(const float v[16], float inv, uint32_
       h = (h ^ (h >> 16)) * 0x7FEB352Du;
       h = (h ^ (h >> 15)) * 0x846CA68Bu;
       h = ~(h ^ (h >> 16));
-      const uint32_t k = (((A >> t) + (h >> 8)) >> 24) + 2u * t;
+      const uint32_t k = (((A >> t) + (h >> 8)) >> 24) + two * t;
       const uint32_t nib = k | ((__float_as_uint(x[e]) >> 28) & 8u);
-      w[(i + e) >> 3] |= nib << (4 * ((i + e) & 7));
+      w[(i + e) >> 3] = nib * kPipeMul[1 + ((i + e) & 7)] + w[(i + e) >> 3];   // nibbles do not overlap: + is |
     }
   }
   return make_uint2(e2m1_drop_negative_zero(w[0]), e2m1_drop_negative_zero(w[1]));

@@ -201,8 +201,15 @@ __global__ void __launch_bounds__(256) finalize_kernel(const __grid_constant__ B
   const int c = blk * 256 + threadIdx.x;
   double colu = 0.0;
   if (c < T.cols) {
+    // ascending sum; the loads of a run of panels are independent and issued ahead of the additions
     float tot = 0.0f;
-    for (int p = 0; p < npanels; ++p) tot = tot + panel_sums(scratch, B, T, S, p)[c];
+    const int owners = T.gather256 == 0 ? 1 : npanels / T.stat_local;
+    const int per = T.gather256 == 0 ? npanels : T.stat_local;
+    for (int o = 0; o < owners; ++o) {
+      const float* q = panel_sums(scratch, B, T, S, o * per) + c;
+#pragma unroll 8
+      for (int p = 0; p < per; ++p) tot = tot + q[static_cast<int64_t>(p) * T.cols];
+    }
     if (colnorm) {
       const float d = sqrtf(tot / static_cast<float>(T.stat_rows)) + 1e-30f;
       S.denom[c] = d;
