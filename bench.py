@@ -12,7 +12,8 @@ gate, up: 12288x4096; down: 4096x12288} NVFP4 weights, `--tokens` tokens (defaul
 linear: y = F.linear(x, W) under compute("fp4_all"), y.backward(gy) -> dgrad + wgrad, and the lattice update of W
 (colnorm direction, 4-bit phase, stochastic projection, scale refit with trust region 0.1) from the gradient hook.
 With N > 1 every weight (codes, scales, optimizer phase) is sharded along N (rows) over the ranks and the update is
-local; total work is fixed (strong scaling). Two exchange patterns over that storage (`--parallel`):
+local (colnorm normalises every shard on its own; `--whole-colnorm 1` has the ranks exchange their panel sums so that
+the shards receive the unsharded update bit for bit); total work is fixed (strong scaling). Two exchange patterns over that storage (`--parallel`):
   column  activations all-gathered (packed), input gradients reduce-scattered, each rank computes its N/p columns;
   token   packed weights all-gathered, weight-gradient partials reduce-scattered, each rank computes its M/p tokens;
   auto    (default) the one that moves fewer bytes for the workload: `token` when a step has more tokens than the
