@@ -115,7 +115,8 @@ class Lattice(torch.optim.Optimizer):
                         (colnorm; raw and sign with clip < 1) then exchange their 128-row panel sums (weights / 32
                         bytes per step) and every shard receives exactly the update of its rows in the unsharded
                         weight. None: such a direction treats every shard as a weight of its own, without
-                        communication
+                        communication. The directions computed outside the update kernel (muon, muon_block, factored,
+                        sinkhorn, normalize='row') always work on the shard they are given
     A parameter that is a row shard of a larger weight sets ``p._bl_row_offset`` to its first global row (and
     ``p._bl_rows_total`` to the rows of the whole weight): the update then draws the random numbers of the unsharded
     tensor (as the reference's row tiles do, csrc/update.cpp:50).
