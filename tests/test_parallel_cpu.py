@@ -141,3 +141,35 @@ def test_sharded_checkpoint_round_trip_on_gloo(tmp_path):
         p.join(180)
         assert p.exitcode == 0
     assert all(out.get(r) for r in range(size)), dict(out)
+
+
+def _exchange_worker(rank, size, port, out):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=size)
+    try:
+        from bitlattice_b200.optim.lattice import Lattice
+        opt = object.__new__(Lattice)                 # the exchange reads nothing but the group
+        opt.shard_group = True
+        blocks = torch.full((size, 37), -1.0)
+        blocks[rank] = torch.arange(37, dtype=torch.float32) + 100 * rank      # this owner's panel sums
+        opt._exchange(blocks)
+        want = torch.stack([torch.arange(37, dtype=torch.float32) + 100 * r for r in range(size)])
+        out[rank] = bool(torch.equal(blocks, want)) and opt._shard_world()[:2] == (size, rank)
+    finally:
+        dist.destroy_process_group()
+
+
+def test_panel_sum_exchange_is_an_in_place_all_gather_on_gloo():
+    """``Lattice._exchange`` (whole-weight statistics over row shards): every rank has written its own row of the
+    exchange area; afterwards every rank holds all rows."""
+    size = 2
+    ctx = mp.get_context("spawn")
+    out = ctx.Manager().dict()
+    port = _free_port()
+    procs = [ctx.Process(target=_exchange_worker, args=(r, size, port, out)) for r in range(size)]
+    for p in procs:
+        p.start()
+    for p in procs:
+        p.join(120)
+        assert p.exitcode == 0
+    assert all(out.get(r) for r in range(size)), dict(out)
