@@ -196,6 +196,40 @@ def gathered_input_operands(x_shard: torch.Tensor, group, want_t: bool):
     return xq, xt
 
 
+# With MATCH_UNSHARDED the column-parallel backward quantizes its gradient columns exactly as the unsharded layer
+# quantizes them: the per-tensor scale comes from the maximum over ALL columns (one all-reduce(MAX) of a float) and the
+# transposed operand draws the unsharded tensor's stochastic-rounding numbers (the hash index of element (m, n) is
+# n * M + m with the GLOBAL column n). The weight-gradient shard is then, bit for bit, the rows of the unsharded
+# weight gradient, and with ``Lattice(shard_group=...)`` so is the update: an N-GPU step leaves the weights a one-GPU
+# step leaves. (The input gradient is a sum of per-rank partial products and keeps its own rounding.) Off by default:
+# it costs a small collective per projection and backward pass.
+MATCH_UNSHARDED = False
+
+_HASH_INDEX_MUL = 0x27D4EB2F                        # the counter hash: h = index * this + key(seed, step)
+_HASH_STEP_INV = pow(0x85EBCA77, -1, 1 << 32)       # key(seed, step) = seed * 0x9E3779B1 + step * 0x85EBCA77
+
+
+def _matching_gradient_operands(g2p: torch.Tensor, group, need_rows: bool):
+    """(row operand or None, transposed rotated operand) of this rank's gradient columns ``g2p`` [M, N / p] with the
+    per-tensor scale and the transposed operand's rounding draws of the unsharded gradient [M, N]."""
+    from . import _ops, backend
+    rank, size = world(group)
+    am = _ops.amax_global(g2p)
+    if size > 1:
+        dist.all_reduce(am, op=dist.ReduceOp.MAX, group=group)      # every entry grows with the maximum
+    g = am[1:2]
+    s_rows, s_t = backend._seed(), backend._seed()                  # the unsharded order: rows, then transposed
+    gq = None
+    if need_rows:
+        gq = backend.Fp4Operand(*_ops.quantize_nvfp4(g2p, g, seed=s_rows, blocked=True), g, True)
+    M, cols = g2p.shape
+    # index offset of this rank's first column, carried by the step counter: key(seed, step') = key(seed, 0) + offset * mul
+    step = (rank * cols * M * _HASH_INDEX_MUL * _HASH_STEP_INV) & 0xFFFFFFFF
+    gt = backend.Fp4Operand(*_ops.quantize_nvfp4_t(g2p, backend._hadamard16(g2p.device, torch.float32), s_t, step,
+                                                   g * 4.0, blocked=True), True)
+    return gq, gt
+
+
 class ColumnParallelFp4Linear(torch.autograd.Function):
     """The 'fp4_all' route of the column-parallel layer for one or more weights that read the same input (q/k/v,
     gate/up): shard-local quantization and one packed all-gather for all of them; in the backward the partial input
@@ -221,8 +255,9 @@ class ColumnParallelFp4Linear(torch.autograd.Function):
         live = [(w, gy) for w, gy in zip(ctx.weights, gys) if gy is not None]
         K = ctx.weights[0].shape[1]
         rows = live[0][1].numel() // live[0][1].shape[-1] if live else 0
+        matching = MATCH_UNSHARDED and need_x and ctx.recipe.legacy and rows % 32 == 0
         blocks = COLUMN_BLOCKS if (need_x and live and rows % (32 * size) == 0 and K % (COLUMN_BLOCKS * 128) == 0
-                                   and rows * K >= (1 << 24)) else 1
+                                   and rows * K >= (1 << 24) and not matching) else 1
         staged, gx_sum, gx_out, works, parts = {}, None, None, [], []
         if need_x and blocks > 1:
             # The input-gradient partial [M, K] is formed in column blocks of K: for every block the GEMMs of all
@@ -247,6 +282,13 @@ class ColumnParallelFp4Linear(torch.autograd.Function):
                 parts.append(part)
         else:
             for w, gy in live:
+                if matching:
+                    g2p = gy.reshape(-1, gy.shape[-1]).contiguous()
+                    gq, gt = _matching_gradient_operands(g2p, ctx.group, True)
+                    gx = backend.fp4_mm(gq, backend.weight_t_operand(w), gy.dtype, add_to=gx_sum)
+                    gx_sum = gx if gx_sum is None else gx_sum
+                    staged[id(w)] = (g2p, gq, gt)
+                    continue
                 if need_x:
                     # the partial input gradients of the projections are summed in the GEMM's epilogue (same bits as
                     # adding the tensors) whenever the rows need no padding; otherwise by a dense add
@@ -269,7 +311,10 @@ class ColumnParallelFp4Linear(torch.autograd.Function):
             if st is None or not ctx.needs_input_grad[3 + i] or ctx.xt is None:
                 gws.append(None)
                 continue
-            gws.append(backend.fp4_wgrad(st[0], st[1], ctx.xt.get(), w, ctx.recipe).to(w.dtype))
+            if len(st) == 3:                          # operands quantized as the unsharded layer quantizes them
+                gws.append(backend.fp4_mm(st[2], ctx.xt.get(), w.dtype))
+            else:
+                gws.append(backend.fp4_wgrad(st[0], st[1], ctx.xt.get(), w, ctx.recipe).to(w.dtype))
         for work, _ in works:
             work.wait()
         if parts:

@@ -220,6 +220,37 @@ def main():
     assert torch.equal(psh.packed, pu.packed[ru]), "sharded colnorm update differs from the unsharded one"
     assert torch.equal(psh.scales.view(torch.uint8), pu.scales.view(torch.uint8)[ru])
     assert torch.equal(osh.state[psh]["phase"], ou.state[pu]["phase"][ru])
+    # MATCH_UNSHARDED: the gradient columns are quantized with the unsharded tensor's scale and rounding draws, so the
+    # weight-gradient shard equals the rows of the unsharded weight gradient bit for bit -- and with the panel sums
+    # exchanged the colnorm update leaves exactly the weights the one-GPU step leaves
+    Nm = 256 * world
+    wm = bl.LatticeTensor.from_float(torch.randn(Nm, K, device=dev, generator=gen) * 0.02, "nvfp4", method="rtn",
+                                     dtype=torch.bfloat16)
+    gym = (torch.randn(M, Nm, device=dev, generator=gen) * 1e-2).to(torch.bfloat16)
+    cm = slice(rank * 256, (rank + 1) * 256)
+    parallel.MATCH_UNSHARDED = True
+    try:
+        with bl.compute("fp4_all"):
+            backend.set_sr_seed(9000)
+            backend.clear_shared()
+            pf = torch.nn.Parameter(wm.detach().clone())
+            xf3 = x.detach().requires_grad_(True)
+            torch.nn.functional.linear(xf3, pf).backward(gym)
+            backend.set_sr_seed(9000)
+            backend.clear_shared()
+            pm = torch.nn.Parameter(shard_rows(wm, rank, world))
+            xs3 = x[rows].detach().contiguous().requires_grad_(True)
+            column_parallel_linear(xs3, pm, None).backward(gym[:, cm].contiguous())
+    finally:
+        parallel.MATCH_UNSHARDED = False
+    assert torch.equal(pm.grad, pf.grad[cm]), "weight-gradient shard differs from the unsharded weight gradient"
+    assert rel(xs3.grad, xf3.grad[rows]) < 0.2
+    kwm = dict(lr=3e-3, direction="colnorm", phase_bits=4, seed=33)
+    of, om = bl.Lattice([pf], **kwm), bl.Lattice([pm], shard_group=True, **kwm)
+    of.step()
+    om.step()
+    assert torch.equal(pm.packed, pf.packed[cm]) and torch.equal(om.state[pm]["phase"], of.state[pf]["phase"][cm])
+    assert torch.equal(pm.scales.view(torch.uint8), pf.scales.view(torch.uint8)[cm])
     assert bl._ops.gemm_status(local) == 0
     dist.barrier()
     print(f"OK {rank}", flush=True)

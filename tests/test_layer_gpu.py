@@ -519,6 +519,29 @@ def test_row_shards_with_whole_weight_statistics_equal_the_whole_update(directio
         assert not torch.equal(ps[0].packed, whole[0].packed[128:256])
 
 
+def test_column_slice_draws_the_rounding_numbers_of_the_whole_gradient():
+    """The column-parallel backward with ``parallel.MATCH_UNSHARDED``: a rank's gradient columns, quantized with the
+    whole tensor's scale and with the index offset of its first column folded into the step counter, give exactly the
+    rows of the whole gradient's transposed stochastic operand."""
+    from bitlattice_b200 import _ops, backend, parallel
+    M, N, p = 256, 384, 3
+    gy = (torch.randn(M, N, generator=gen(81)) * 1e-2).to(DEV, torch.bfloat16)
+    H = backend._hadamard16(gy.device, torch.float32)
+    bound = _ops.amax_global(gy)[1:2] * 4.0
+    whole = _ops.quantize_nvfp4_t(gy, H, 77, 0, bound, blocked=False)
+    cols = N // p
+    for rank in range(p):
+        part = gy[:, rank * cols:(rank + 1) * cols].contiguous()
+        step = (rank * cols * M * parallel._HASH_INDEX_MUL * parallel._HASH_STEP_INV) & 0xFFFFFFFF
+        got = _ops.quantize_nvfp4_t(part, H, 77, step, bound, blocked=False)
+        rows = slice(rank * cols, (rank + 1) * cols)
+        assert torch.equal(got[0], whole[0][rows])
+        assert torch.equal(got[1].view(torch.uint8), whole[1].view(torch.uint8)[rows])
+        if rank:        # without the offset the slice draws other numbers
+            other = _ops.quantize_nvfp4_t(part, H, 77, 0, bound, blocked=False)
+            assert not torch.equal(other[0], whole[0][rows])
+
+
 def test_converted_third_party_weights_dequantize_as_in_the_reference():
     """compressed-tensors / ModelOpt NVFP4 tensors converted to lattice weights decode to the reference's values
     (tests/golden/convert.npz, written by the reference's bitlattice.io.convert)."""
