@@ -14,6 +14,14 @@ On the FP4 routes each rank quantizes only its own token shard (after an all-red
 so that every rank derives the same per-tensor scale) and the ranks all-gather the packed operands instead of the
 bf16 activations: 0.5625 bytes per element instead of 2, and the quantization work shrinks with the world size.
 
+How close to the one-GPU step: the forward shard is the matching columns of the unsharded output bit for bit. By
+default a rank quantizes its gradient columns as a tensor of their own (own maximum, own rounding draws), so the
+gradients agree with the unsharded layer's statistically. With ``MATCH_UNSHARDED`` the gradient columns take the scale
+and the transposed operand's rounding draws of the unsharded gradient: the weight-gradient shard is then the rows of
+the unsharded weight gradient bit for bit, and with ``Lattice(shard_group=...)`` (colnorm statistics of the whole
+weight) the updated shard is the rows of the one-GPU step's updated weight. The input gradient, a sum of per-rank
+partial products, keeps its own rounding either way.
+
 The collectives are NCCL's (``torch.distributed``) over NVLink; gathered operands land in local HBM before any
 kernel reads them. ``gloo`` works for CPU tests of the bookkeeping. With ``group=None`` or a world of one the layer
 degenerates to the plain lattice linear.
