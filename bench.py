@@ -94,6 +94,10 @@ def parse():
                     help="N > 1: 1 = the colnorm statistics cover the whole weight (Lattice(shard_group=...): the ranks "
                          "exchange their 128-row panel sums and reproduce the unsharded update bit for bit); 0 = every "
                          "row shard is normalised on its own, without communication")
+    ap.add_argument("--match-unsharded", type=int, default=0, choices=[0, 1],
+                    help="N > 1, column-parallel: 1 = gradient columns are quantized with the unsharded tensor's scale "
+                         "and rounding draws (parallel.MATCH_UNSHARDED), which with --whole-colnorm 1 leaves the weights "
+                         "of the one-GPU step")
     ap.add_argument("--kernel-summary", default=None, metavar="FILE",
                     help="after the measurements, run 2 more steps under torch.profiler on rank 0 and write per-kernel "
                          "launch counts and device time (text) to FILE")
@@ -334,6 +338,9 @@ def run_ours(a):
             meta.append((name, N, K))
     group = dist.group.WORLD if world > 1 else None
     shard_group = group if a.whole_colnorm else None
+    if a.match_unsharded:
+        from bitlattice_b200 import parallel
+        parallel.MATCH_UNSHARDED = True
     opt = bl.Lattice(params, fused_backward=True, overlap=bool(a.overlap), hook_batch=a.hook_batch, hook_flush="reader",
                      shard_group=shard_group, **OPT)
     flops = sum(6.0 * M * N * K for _, N, K in meta)
@@ -575,6 +582,8 @@ def run_ours(a):
                    "parallelism": f"x{world}: {names[mode]}" if world > 1 else "single GPU",
                    "nvlink_bytes_per_step_per_rank": {k: v * (world - 1) / world for k, v in moved.items()}
                    if world > 1 else None,
+                   "gradient_quantization": ("as the unsharded layer (column-parallel)" if a.match_unsharded and world > 1
+                                             else "per rank"),
                    "colnorm": ("whole weight (panel sums exchanged among the shard owners)" if shard_group is not None
                                else "per row shard (no communication)") if world > 1 else "whole weight",
                    "l2": "inputs larger than L2 (weights, activations and gradients of a step exceed 126 MB)",
