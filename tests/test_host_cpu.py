@@ -208,3 +208,17 @@ def test_newton_schulz_orthogonalises_and_matches_its_coefficients():
     assert abs(a - 2.300652019954817 / 1.05) < 1e-12 and b < 0 < c
     with pytest.raises(ValueError):
         ns_coefficients("cubic", 0)
+
+
+def test_an_index_offset_of_the_counter_hash_is_a_value_of_its_step():
+    """``parallel.MATCH_UNSHARDED`` hands a rank's gradient columns the unsharded tensor's rounding draws through the
+    quantizer's ``step`` argument: with the oracle's statement of the reference's hash (bitlattice/reference.py:22-30),
+    u(index + offset, seed, 0) == u(index, seed, offset * mul / 0x85EBCA77 mod 2^32), also across the 2^32 wrap."""
+    from bitlattice_b200 import parallel
+    from oracle import fp4_general as G
+    rng = np.random.default_rng(5)
+    idx = rng.integers(0, 1 << 32, size=4096, dtype=np.uint64)
+    for offset in (0, 1, 256 * 384, 3 * 65536 * 4096, (1 << 32) - 7, 5 * (1 << 32) + 11):
+        step = (offset * parallel._HASH_INDEX_MUL * parallel._HASH_STEP_INV) & 0xFFFFFFFF
+        for seed in (0, 77, 0x7FFFFFFF):
+            assert np.array_equal(G.hash_u(idx + np.uint64(offset), seed, 0), G.hash_u(idx, seed, step))
